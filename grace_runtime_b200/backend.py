@@ -1,0 +1,360 @@
+"""ctypes binding of libgrace_b200.so with the module interface of the reference's GPU plug-in `_kk_<arch>`
+(python/kk/kk_module.cpp:200-275): initialize / finalize / arch / platform / memory_info, and the classes Model,
+System and Batch with the same argument names, defaults, result dicts and exception classes (ValueError for
+std::invalid_argument, RuntimeError otherwise; MemoryError is not used by the reference, out-of-memory is a
+RuntimeError there too).
+
+There is no CPU path: importing works anywhere (so that the symbols can be checked), but every call that needs the
+device fails unless libgrace_b200.so is built and a B200 is present.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+ABI = 7
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgrace_b200.so")
+_lib = None
+
+FLAG_ENERGIES, FLAG_ENERGY_ONLY, FLAG_UQ = 1, 2, 4
+
+# name -> (restype, argtypes); the symbols include/grace_b200.h declares
+_P, _I, _D, _I64 = C.c_void_p, C.c_int, C.c_double, C.c_int64
+SIGNATURES = {
+    "grace_initialize": (_I, [_I]),
+    "grace_finalize": (_I, []),
+    "grace_initialized": (_I, []),
+    "grace_device": (_I, []),
+    "grace_arch": (C.c_char_p, []),
+    "grace_platform": (C.c_char_p, []),
+    "grace_blas": (C.c_char_p, []),
+    "grace_abi": (_I, []),
+    "grace_memory_info": (_I, [_P, _P]),
+    "grace_debug_fail_alloc": (_I, [C.c_char_p, _I]),
+    "grace_debug_fail_launch": (_I, [_I]),
+    "grace_last_error": (C.c_char_p, []),
+    "grace_kernel_launches": (C.c_uint64, []),
+    "grace_model_load": (_I, [C.c_char_p, _I, _P]),
+    "grace_model_layers": (_I, [_P]),
+    "grace_model_has_uq": (_I, [_P]),
+    "grace_model_n_elements": (_I, [_P]),
+    "grace_model_element_name": (C.c_char_p, [_P, _I]),
+    "grace_model_engine_setups": (_I64, [_P]),
+    "grace_model_free": (None, [_P]),
+    "grace_system_create": (_I, [_P, _P, _I, _D, _I, _I, _P]),
+    "grace_system_cutoff": (_D, [_P]),
+    "grace_system_compute": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "grace_system_compute_device": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "grace_system_rebuilds": (_I64, [_P]),
+    "grace_system_chunksize": (_I, [_P]),
+    "grace_system_release_buffers": (_I, [_P]),
+    "grace_system_stage_ms": (_I, [_P, _P]),
+    "grace_system_free": (None, [_P]),
+    "grace_batch_create": (_I, [_P, _P, _I, _I, _I, _P]),
+    "grace_batch_cutoff": (_D, [_P]),
+    "grace_batch_compute": (_I, [_P, _I, _P, _I64, _P, _P, _P, _P, _I, _I64, _P, _P, _P, _P]),
+    "grace_batch_compute_device": (_I, [_P, _I, _P, _I64, _P, _P, _P, _P, _I, _I64, _P, _P, _P, _P]),
+    "grace_batch_passes": (_I, [_P]),
+    "grace_batch_host_seconds": (_D, [_P]),
+    "grace_batch_set_keep_buffers": (_I, [_P, _I]),
+    "grace_batch_release_buffers": (_I, [_P]),
+    "grace_batch_free": (None, [_P]),
+}
+
+
+def load_library(path=None):
+    """Loads libgrace_b200.so (built by grace_runtime_b200/build.py) and declares every entry point; raises
+    RuntimeError if the library is missing - there is nothing to fall back to."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = path or LIB_PATH
+    if not os.path.exists(p):
+        raise RuntimeError(f"{p} is not built: run `python -m grace_runtime_b200.build` (needs nvcc); this backend "
+                           "has no CPU path")
+    lib = C.CDLL(p)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)    # AttributeError: a symbol of the header is missing from the library
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def _check(rc):
+    if rc == 0:
+        return
+    msg = _lib.grace_last_error().decode(errors="replace")
+    if rc == 1:
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _names(species):
+    arr = (C.c_char_p * len(species))(*[str(s).encode() for s in species])
+    return arr
+
+
+# ---- module-level functions of the plug-in -----------------------------------------------------------------------
+def initialize(device=0):
+    _check(load_library().grace_initialize(int(device)))
+
+
+def finalize():
+    _check(load_library().grace_finalize())
+
+
+def initialized():
+    return bool(load_library().grace_initialized())
+
+
+def device():
+    return load_library().grace_device()
+
+
+def arch():
+    return load_library().grace_arch().decode()
+
+
+def archs():
+    return ["sm100"]
+
+
+def platform():
+    return load_library().grace_platform().decode()
+
+
+def blas():
+    return load_library().grace_blas().decode()
+
+
+def cublas():
+    return False
+
+
+def memory_info():
+    f, t = C.c_size_t(0), C.c_size_t(0)
+    _check(load_library().grace_memory_info(C.addressof(f), C.addressof(t)))
+    return f.value, t.value
+
+
+def kernel_launches():
+    return int(load_library().grace_kernel_launches())
+
+
+def _debug_fail_alloc(label, nth):
+    _check(load_library().grace_debug_fail_alloc(str(label).encode(), int(nth)))
+
+
+def _debug_fail_launch(nth):
+    _check(load_library().grace_debug_fail_launch(int(nth)))
+
+
+# ---- classes -----------------------------------------------------------------------------------------------------
+class Model:
+    """A loaded GRACE-1L / GRACE-2L kokkos.npz (kk_api.h:51-64)."""
+
+    def __init__(self, path, spline=1024, asi=""):
+        if asi:
+            raise ValueError("active-set files belong to PACE models, which this backend does not evaluate")
+        lib = load_library()
+        h = C.c_void_p()
+        _check(lib.grace_model_load(os.fsencode(path), int(spline), C.addressof(h)))
+        self._h = h
+        self.spline = int(spline)
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _lib is not None:
+            _lib.grace_model_free(self._h)
+            self._h = None
+
+    @property
+    def layers(self):
+        return _lib.grace_model_layers(self._h)
+
+    @property
+    def has_uq(self):
+        return bool(_lib.grace_model_has_uq(self._h))
+
+    @property
+    def slow_notice(self):
+        return ""
+
+    @property
+    def needs_generic(self):
+        return False
+
+    @property
+    def element_names(self):
+        return [_lib.grace_model_element_name(self._h, i).decode() for i in range(_lib.grace_model_n_elements(self._h))]
+
+    @property
+    def engine_setups(self):
+        return int(_lib.grace_model_engine_setups(self._h))
+
+    def validate_uq(self):
+        raise ValueError("the model has no UQ head usable by this backend")
+
+
+def _as(a, dtype, shape=None):
+    a = np.ascontiguousarray(a, dtype=dtype)
+    if shape is not None and a.shape != shape:
+        raise ValueError(f"array of shape {a.shape}, expected {shape}")
+    return a
+
+
+class System:
+    """One structure on the device with a Verlet-skin neighbour list (kk_api.h:68-90)."""
+
+    def __init__(self, model, species, skin=0.5, spline=1024, chunksize=-1):
+        lib = load_library()
+        h = C.c_void_p()
+        self._model = model
+        _check(lib.grace_system_create(model._h, _names(species), len(species), float(skin), int(spline),
+                                       int(chunksize), C.addressof(h)))
+        self._h = h
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _lib is not None:
+            _lib.grace_system_free(self._h)
+            self._h = None
+
+    @property
+    def cutoff(self):
+        return _lib.grace_system_cutoff(self._h)
+
+    @property
+    def rebuilds(self):
+        return int(_lib.grace_system_rebuilds(self._h))
+
+    @property
+    def chunksize(self):
+        return _lib.grace_system_chunksize(self._h)
+
+    @property
+    def stage_ms(self):
+        ms = np.zeros(5)
+        _lib.grace_system_stage_ms(self._h, _ptr(ms))
+        return dict(neighbor_list=ms[0], bonds=ms[1], forward=ms[2], reverse=ms[3], total=ms[4])
+
+    def release_buffers(self):
+        _check(_lib.grace_system_release_buffers(self._h))
+
+    def compute(self, types, positions, cell, pbc, energies=False, uq=False, energy_only=False):
+        """Result dict as python/kk/kk_module.cpp `compute`: energy, virial [6], forces [n, 3] (not with energy_only),
+        energies [n] (when asked)."""
+        types = _as(types, np.int32)
+        n = len(types)
+        positions = _as(positions, np.float64, (n, 3))
+        cell = _as(cell, np.float64, (3, 3))
+        pbc = _as(np.asarray(pbc).astype(bool), np.uint8, (3,))
+        flags = (FLAG_ENERGIES if energies else 0) | (FLAG_ENERGY_ONLY if energy_only else 0) | (FLAG_UQ if uq else 0)
+        e = np.zeros(1)
+        v = np.zeros(6)
+        f = None if energy_only else np.zeros((n, 3))
+        ea = np.zeros(n) if energies else None
+        _check(_lib.grace_system_compute(self._h, n, _ptr(types), _ptr(positions), _ptr(cell), _ptr(pbc), flags,
+                                         _ptr(e), None if energy_only else _ptr(v), _ptr(f), _ptr(ea)))
+        r = {"energy": float(e[0])}
+        if not energy_only:
+            r["forces"] = f
+            r["virial"] = v
+        if energies:
+            r["energies"] = ea
+        return r
+
+    def compute_device(self, n, types_ptr, positions_ptr, cell, pbc, energy_ptr, forces_ptr=0, virial_ptr=0,
+                       energies_ptr=0, energy_only=False):
+        """Device pointers (integers) for types int32 [n], positions float64 [n, 3] and the float64 outputs."""
+        cell = _as(cell, np.float64, (3, 3))
+        pbc = _as(np.asarray(pbc).astype(bool), np.uint8, (3,))
+        flags = (FLAG_ENERGIES if energies_ptr else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
+        _check(_lib.grace_system_compute_device(self._h, int(n), C.c_void_p(types_ptr), C.c_void_p(positions_ptr),
+                                                _ptr(cell), _ptr(pbc), flags, C.c_void_p(energy_ptr),
+                                                C.c_void_p(virial_ptr or None), C.c_void_p(forces_ptr or None),
+                                                C.c_void_p(energies_ptr or None)))
+
+
+class Batch:
+    """Many structures per engine pass (kk_api.h:92-156)."""
+
+    def __init__(self, model, species, spline=1024, chunksize=-1):
+        lib = load_library()
+        h = C.c_void_p()
+        self._model = model
+        _check(lib.grace_batch_create(model._h, _names(species), len(species), int(spline), int(chunksize),
+                                      C.addressof(h)))
+        self._h = h
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _lib is not None:
+            _lib.grace_batch_free(self._h)
+            self._h = None
+
+    @property
+    def cutoff(self):
+        return _lib.grace_batch_cutoff(self._h)
+
+    @property
+    def passes(self):
+        return _lib.grace_batch_passes(self._h)
+
+    @property
+    def last_host_seconds(self):
+        return _lib.grace_batch_host_seconds(self._h)
+
+    @property
+    def keep_buffers(self):
+        return getattr(self, "_keep", False)
+
+    @keep_buffers.setter
+    def keep_buffers(self, on):
+        self._keep = bool(on)
+        _check(_lib.grace_batch_set_keep_buffers(self._h, int(bool(on))))
+
+    def release_buffers(self):
+        _check(_lib.grace_batch_release_buffers(self._h))
+
+    def compute(self, natoms, types, positions, cells, pbc, energies=False, uq=False, energy_only=False,
+                max_nall=2097152, dispersion_parts=False):
+        natoms = _as(natoms, np.int32)
+        nsys = len(natoms)
+        types = _as(types, np.int32)
+        ntot = len(types)
+        positions = _as(positions, np.float64, (ntot, 3))
+        cells = _as(cells, np.float64, (nsys, 3, 3))
+        pbc = _as(np.asarray(pbc).astype(bool), np.uint8, (nsys, 3))
+        flags = (FLAG_ENERGIES if energies else 0) | (FLAG_ENERGY_ONLY if energy_only else 0) | (FLAG_UQ if uq else 0)
+        e = np.zeros(nsys)
+        v = np.zeros((nsys, 6))
+        f = None if energy_only else np.zeros((ntot, 3))
+        ea = np.zeros(ntot) if energies else None
+        _check(_lib.grace_batch_compute(self._h, nsys, _ptr(natoms), ntot, _ptr(types), _ptr(positions), _ptr(cells),
+                                        _ptr(pbc), flags, int(max_nall), _ptr(e), None if energy_only else _ptr(v),
+                                        _ptr(f), _ptr(ea)))
+        r = {"energy": e}
+        if not energy_only:
+            r["forces"] = f
+            r["virial"] = v
+        if energies:
+            r["energies"] = ea
+        return r
+
+    def compute_device(self, natoms, types_ptr, positions_ptr, cells, pbc, energy_ptr, forces_ptr=0, virial_ptr=0,
+                       energies_ptr=0, energy_only=False, max_nall=1 << 21):
+        natoms = _as(natoms, np.int32)
+        nsys = len(natoms)
+        cells = _as(cells, np.float64, (nsys, 3, 3))
+        pbc = _as(np.asarray(pbc).astype(bool), np.uint8, (nsys, 3))
+        flags = (FLAG_ENERGIES if energies_ptr else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
+        _check(_lib.grace_batch_compute_device(self._h, nsys, _ptr(natoms), int(natoms.sum()), C.c_void_p(types_ptr),
+                                               C.c_void_p(positions_ptr), _ptr(cells), _ptr(pbc), flags, int(max_nall),
+                                               C.c_void_p(energy_ptr), C.c_void_p(virial_ptr or None),
+                                               C.c_void_p(forces_ptr or None), C.c_void_p(energies_ptr or None)))

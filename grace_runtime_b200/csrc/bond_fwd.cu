@@ -1,0 +1,156 @@
+// Forward bond kernel: the neighbour sums of a layer,
+//   Q[(I, lm)][a][n] = sum_j Y_lm(rhat_ij) R[n, l](r_ij / rcut) msg_I(j)[n]
+// with msg_I the message functions of the neighbour (layer 2: I < n_msg) and, as the last I, its chemical weight
+// z[mu_j][n] (layer 1: A; layer 2: B0).  This is atom_scatter + atom_yi of the reference CPU driver
+// (libgrace/include/grace/fused_cpu.h:947-1025) in the dense (I, lm) form of its GPU kernels
+// (libgrace/include/grace/kk/grace_2l_fused_kk_impl.h:858-1070).
+//
+// One block of 4 warps per atom.  A lane owns channel n (NCH channels for C > 32); the 4 warps (and with C <= 16 the
+// two half-warps) take the atom's bonds in turn, every thread keeping all NIT x NLM partial sums of its channel in
+// registers; the partial sums of the warps are added in shared memory in a fixed order and written once, coalesced
+// over n: no global atomics, bit-reproducible.
+#include "bond_common.cuh"
+
+namespace gb {
+
+namespace {
+
+constexpr int EB = 64;    // bonds staged per round
+
+template<int LMAX, int NIT, int NCH, int LPE>
+__global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, SHTable sht, float *__restrict__ Q,
+                                                       int NA, int a0)
+{
+  constexpr int NL = LMAX + 1, NLM = NL * NL, NLMP = NLM | 1, NQ = NIT * NLM, CP = LPE * NCH, EPW = 32 / LPE;
+  __shared__ float Ys[EB][NLMP];
+  __shared__ float st[EB];
+  __shared__ int sk[EB], smu[EB], sj[EB];
+  __shared__ float red[NQ][CP];
+
+  const int a = blockIdx.x, i = a0 + a, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int ln = lane % LPE, esub = lane / LPE;
+  const int Ibase = blockIdx.y * NIT;
+  const long long base = b.off[i];
+  const int nb = b.cnt[i];
+  const int mui = b.mu[i];
+  const int C = L.C, nel = L.n_elements;
+
+  float acc[NIT][NLM][NCH];
+#pragma unroll
+  for (int I = 0; I < NIT; I++)
+#pragma unroll
+    for (int q = 0; q < NLM; q++)
+#pragma unroll
+      for (int ch = 0; ch < NCH; ch++) acc[I][q][ch] = 0.0f;
+
+  for (int b0 = 0; b0 < nb; b0 += EB) {
+    const int nbat = min(EB, nb - b0);
+    for (int e = tid; e < nbat; e += 128) {
+      const float4 rec = b.rec[base + b0 + e];
+      const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
+      const int j = __float_as_int(rec.w);
+      const int muj = b.mu[j];
+      int k;
+      float t;
+      spline_locate(r / L.rc[mui * nel + muj], L.N, k, t);
+      sk[e] = k; st[e] = t; smu[e] = muj; sj[e] = j;
+      float *y = Ys[e];
+      sph_harm<LMAX, false>(sht, rec.x * ir, rec.y * ir, rec.z * ir,
+                            [&](int lm, float v, float, float, float) { y[lm] = v; });
+    }
+    __syncthreads();
+    for (int e0 = w * EPW; e0 < nbat; e0 += 4 * EPW) {
+      const int e = e0 + esub;
+      if (e < nbat) {
+        const int k = sk[e], muj = smu[e], j = sj[e];
+        const float t = st[e];
+        const float *y = Ys[e];
+#pragma unroll
+        for (int ch = 0; ch < NCH; ch++) {
+          const int n = ln + ch * LPE;
+          if (n < C) {
+            const float *cf = L.tab + ((size_t) k * 4 * NL) * C + n;
+            float R[NL];
+#pragma unroll
+            for (int l = 0; l < NL; l++) {
+              const float c0 = __ldg(cf + (size_t) (0 * NL + l) * C), c1 = __ldg(cf + (size_t) (1 * NL + l) * C);
+              const float c2 = __ldg(cf + (size_t) (2 * NL + l) * C), c3 = __ldg(cf + (size_t) (3 * NL + l) * C);
+              R[l] = c0 + t * (c1 + t * (c2 + t * c3));
+            }
+#pragma unroll
+            for (int I = 0; I < NIT; I++) {
+              const int Ig = Ibase + I;
+              float m = 0.0f;
+              if (Ig < L.n_msg) m = __ldg(L.msg + ((size_t) j * L.n_msg + Ig) * C + n);
+              else if (Ig == L.n_msg) m = __ldg(L.z + (size_t) muj * C + n);
+#pragma unroll
+              for (int l = 0; l < NL; l++) {
+                const float rm = R[l] * m;
+#pragma unroll
+                for (int q = l * l; q < (l + 1) * (l + 1); q++) acc[I][q][ch] = fmaf(y[q], rm, acc[I][q][ch]);
+              }
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  if (EPW == 2) {    // the two half-warps worked on different bonds: add them
+#pragma unroll
+    for (int I = 0; I < NIT; I++)
+#pragma unroll
+      for (int q = 0; q < NLM; q++) acc[I][q][0] += __shfl_xor_sync(0xffffffffu, acc[I][q][0], 16);
+  }
+  for (int ww = 0; ww < 4; ww++) {
+    if (w == ww && esub == 0) {
+#pragma unroll
+      for (int I = 0; I < NIT; I++)
+#pragma unroll
+        for (int q = 0; q < NLM; q++)
+#pragma unroll
+          for (int ch = 0; ch < NCH; ch++) {
+            float *r = &red[I * NLM + q][ln + ch * LPE];
+            *r = (ww == 0) ? acc[I][q][ch] : *r + acc[I][q][ch];
+          }
+    }
+    __syncthreads();
+  }
+  for (int idx = tid; idx < NQ * C; idx += 128) {
+    const int q = idx / C, n = idx - q * C;
+    if (Ibase + q / NLM <= L.n_msg) Q[((size_t) (Ibase * NLM + q) * NA + a) * C + n] = red[q][n];
+  }
+}
+
+template<int LMAX, int NIT, int NCH, int LPE>
+void launch_t(const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na)
+{
+  const int tiles = (L.n_msg + 1 + NIT - 1) / NIT;
+  GB_LAUNCH((bond_fwd_kernel<LMAX, NIT, NCH, LPE>), dim3(na, tiles), 128, 0, b, L, sh_table_host(), Q, NA, a0);
+}
+
+template<int LMAX> void launch_l(const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na)
+{
+  const int C = L.C, nI = L.n_msg + 1;
+  if (C > 64) throw Unsupported("bond sums with more than 64 channels are not supported");
+  if (C > 32) launch_t<LMAX, 1, 2, 32>(b, L, Q, NA, a0, na);
+  else if (C > 16) { if (nI == 5) launch_t<LMAX, 5, 1, 32>(b, L, Q, NA, a0, na); else launch_t<LMAX, 1, 1, 32>(b, L, Q, NA, a0, na); }
+  else { if (nI == 5) launch_t<LMAX, 5, 1, 16>(b, L, Q, NA, a0, na); else launch_t<LMAX, 1, 1, 16>(b, L, Q, NA, a0, na); }
+}
+
+}    // namespace
+
+void launch_bond_fwd(int lmax, const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na)
+{
+  if (na == 0) return;
+  switch (lmax) {
+    case 1: launch_l<1>(b, L, Q, NA, a0, na); break;
+    case 2: launch_l<2>(b, L, Q, NA, a0, na); break;
+    case 3: launch_l<3>(b, L, Q, NA, a0, na); break;
+    case 4: launch_l<4>(b, L, Q, NA, a0, na); break;
+    default: throw Unsupported("lmax must be 1..4");
+  }
+}
+
+}    // namespace gb

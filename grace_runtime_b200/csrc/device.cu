@@ -1,0 +1,124 @@
+#include "device.h"
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+
+namespace gb {
+
+namespace {
+DeviceState g_dev;
+std::map<void *, size_t> g_live;
+size_t g_live_bytes = 0;
+}    // namespace
+
+DeviceState &dev() { return g_dev; }
+
+void require_initialized()
+{
+  if (!g_dev.initialized) throw DeviceError("the GPU backend is not initialised (call grace_initialize first) or was finalised");
+}
+
+void cuda_check(cudaError_t e, const char *what)
+{
+  if (e == cudaSuccess) return;
+  const std::string msg = std::string("CUDA error: ") + cudaGetErrorString(e) + " in " + what;
+  if (e == cudaErrorMemoryAllocation) {
+    (void) cudaGetLastError();    // the allocation error is not sticky: clear it so the context stays usable
+    throw OutOfMemory(msg);
+  }
+  throw DeviceError(msg);
+}
+
+void after_launch(const char *name)
+{
+  g_dev.launches++;
+  if (g_dev.fail_launch_nth > 0 && --g_dev.fail_launch_nth == 0)
+    throw OutOfMemory(std::string("kernel launch ran out of device memory (injected) in ") + name);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) cuda_check(e, name);
+}
+
+void *device_alloc(size_t bytes, const char *label)
+{
+  require_initialized();
+  if (bytes == 0) bytes = 16;
+  void *p = nullptr;
+  GB_CUDA(cudaMalloc(&p, bytes));
+  // the injected failure comes after the allocation, as the reference's hook does (kk_core.cpp:128-141): the buffer is
+  // returned to the device before the error is raised
+  if (g_dev.fail_alloc_nth > 0 && label && std::strstr(label, g_dev.fail_label.c_str()) != nullptr &&
+      --g_dev.fail_alloc_nth == 0) {
+    cudaFree(p);
+    throw OutOfMemory(std::string("out of device memory (injected) allocating '") + label + "'");
+  }
+  g_live[p] = bytes;
+  g_live_bytes += bytes;
+  return p;
+}
+
+void device_free(void *p)
+{
+  if (!p) return;
+  auto it = g_live.find(p);
+  if (it != g_live.end()) {
+    g_live_bytes -= it->second;
+    g_live.erase(it);
+  }
+  if (g_dev.initialized) cudaFree(p);
+}
+
+size_t device_bytes_live() { return g_live_bytes; }
+
+StageTimer::~StageTimer()
+{
+  if (!g_dev.initialized) return;
+  for (auto e : pool_) cudaEventDestroy(e);
+}
+
+cudaEvent_t StageTimer::take()
+{
+  if (used_ == pool_.size()) {
+    cudaEvent_t e;
+    GB_CUDA(cudaEventCreate(&e));
+    pool_.push_back(e);
+  }
+  return pool_[used_++];
+}
+
+void StageTimer::reset()
+{
+  spans_.clear();
+  used_ = 0;
+  for (int s = 0; s < NSTAGE; s++) open_[s] = -1;
+}
+
+void StageTimer::begin(int stage)
+{
+  Span sp{stage, take(), take()};
+  GB_CUDA(cudaEventRecord(sp.a, g_dev.stream));
+  open_[stage] = (int) spans_.size();
+  spans_.push_back(sp);
+}
+
+void StageTimer::end(int stage)
+{
+  if (open_[stage] < 0) return;
+  GB_CUDA(cudaEventRecord(spans_[open_[stage]].b, g_dev.stream));
+  open_[stage] = -1;
+}
+
+void StageTimer::collect(double *ms)
+{
+  for (int s = 0; s < NSTAGE; s++) ms[s] = 0.0;
+  for (size_t q = 0; q < spans_.size(); q++) {
+    bool closed = true;
+    for (int s = 0; s < NSTAGE; s++) closed = closed && open_[s] != (int) q;
+    if (!closed) continue;
+    float t = 0.0f;
+    if (cudaEventElapsedTime(&t, spans_[q].a, spans_[q].b) == cudaSuccess) ms[spans_[q].stage] += t;
+  }
+}
+
+}    // namespace gb

@@ -1,0 +1,654 @@
+#include "engine.h"
+
+#include "bond_common.cuh"
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+
+namespace gb {
+
+// ---- tables ----------------------------------------------------------------------------------------------------
+const SHTable &sh_table_host()
+{
+  static SHTable t = [] {
+    SHTable s{};
+    for (int l = 2; l <= 4; l++) {
+      for (int mm = 0; mm < l - 1; mm++) {
+        const double l2 = l * l, m2 = mm * mm, lm1 = l - 1;
+        s.a[l * (l + 1) / 2 + mm] = (float) std::sqrt((4.0 * l2 - 1.0) / (l2 - m2));
+        s.b[l * (l + 1) / 2 + mm] = (float) -std::sqrt((lm1 * lm1 - m2) / (4.0 * lm1 * lm1 - 1.0));
+      }
+      s.c[l] = (float) -std::sqrt(1.0 + 0.5 / l);
+      s.d[l] = (float) std::sqrt(2.0 * l + 1.0);
+    }
+    return s;
+  }();
+  return t;
+}
+
+std::vector<int> species_to_elements(const GraceModel &m, const std::vector<std::string> &species)
+{
+  if (species.empty()) throw InvalidArgument("species must name at least one element");
+  std::vector<int> t2m;
+  for (const auto &s : species) {
+    const int mu = m.element_index(s);
+    if (mu < 0) throw InvalidArgument("element " + s + " is not in the model");
+    t2m.push_back(mu);
+  }
+  return t2m;
+}
+
+// ---- engine ----------------------------------------------------------------------------------------------------
+namespace {
+
+__global__ void __launch_bounds__(256) types_to_mu(const int *__restrict__ types, const int *__restrict__ t2m, int ns,
+                                                   int *mu, int *flag, long long n)
+{
+  const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int t = types[i];
+  if (t < 1 || t > ns) {
+    atomicOr(flag, 1);
+    mu[i] = 0;
+  } else {
+    mu[i] = t2m[t - 1];
+  }
+}
+
+__global__ void __launch_bounds__(256) types_differ(const int *__restrict__ a, const int *__restrict__ b, int *flag,
+                                                    long long n)
+{
+  const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && a[i] != b[i]) atomicOr(flag, 2);
+}
+
+unsigned nblocks(long long n, int per) { return (unsigned) ((n + per - 1) / per); }
+
+}    // namespace
+
+void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
+{
+  E.plan = &P;
+  E.tab.set_label("engine:radial_table");
+  E.z.set_label("engine:chemical_weights");
+  E.tab.upload(P.radial.tab);
+  E.z.upload(P.z);
+  auto up_i = [&](const std::vector<int> &v) {
+    E.ibufs.emplace_back("engine:tables");
+    E.ibufs.back().upload(v);
+    return E.ibufs.back().get();
+  };
+  for (const MVOp &o : P.mv) {
+    MVDev d{};
+    d.row_out = up_i(o.row_out);
+    d.item_off = up_i(o.item_off);
+    E.itembufs.emplace_back("engine:tables");
+    E.itembufs.back().upload(o.items);
+    d.items = E.itembufs.back().get();
+    E.fbufs.emplace_back("engine:weights");
+    E.fbufs.back().upload(o.W);
+    d.W = E.fbufs.back().get();
+    d.ty_stride = o.ty_stride;
+    d.n_out = o.n_out;
+    d.nrows = (int) o.row_out.size();
+    d.accumulate = o.accumulate;
+    d.elem = o.elem;
+    d.dst = o.dst;
+    E.mv.push_back(d);
+  }
+  for (const ProdOp &o : P.prod) {
+    ProdDev d{};
+    d.row_out = up_i(o.row_out);
+    d.term_off = up_i(o.term_off);
+    E.termbufs.emplace_back("engine:tables");
+    E.termbufs.back().upload(o.terms);
+    d.terms = E.termbufs.back().get();
+    d.nrows = (int) o.row_out.size();
+    d.accumulate = o.accumulate;
+    d.dst = o.dst;
+    d.srcA = o.srcA;
+    d.srcB = o.srcB;
+    E.prod.push_back(d);
+  }
+  // tensors: values first, then the gradients that are zeroed per chunk (one contiguous range)
+  E.toff.assign(P.tensors.size(), 0);
+  long long at = 0;
+  for (int pass = 0; pass < 2; pass++) {
+    if (pass == 1) E.grad_begin = at;
+    for (size_t t = 0; t < P.tensors.size(); t++)
+      if ((int) P.tensors[t].grad == pass) {
+        E.toff[t] = at;
+        at += (long long) P.tensors[t].nfuncs * P.tensors[t].channels;
+      }
+  }
+  E.grad_end = at;
+  E.per_atom = at;
+  E.tensors.set_label("engine:tensor_table");
+  E.tensors_host.assign(P.tensors.size(), TensorDev{nullptr, 0});
+}
+
+Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n))
+{
+  require_initialized();
+  const ModelPlan &P = plan_;
+  if (P.lmax < 1 || P.lmax > 4) throw Unsupported("models with lmax outside 1..4 are not supported");
+  if (P.e_nin.size() > 4) throw Unsupported("energy MLPs with more than 4 layers are not supported");
+  for (size_t L = 0; L < P.e_nin.size(); L++)
+    if (P.e_nin[L] > 128 || P.e_nout[L] > 128) throw Unsupported("energy MLP widths above 128 are not supported");
+  if (P.nrho > 128) throw Unsupported("rho_n_out above 128 is not supported");
+  rcsq_.set_label("engine:cutoffs"); eW_.set_label("engine:energy_mlp"); shift_.set_label("engine:shift");
+  lnI_.set_label("engine:norm_scale"); ln0_.set_label("engine:norm_scale"); rcf_.set_label("engine:cutoffs");
+  arena_.set_label("work:chunk_tensors"); fv_.set_label("work:bond_forces"); I_rows_.set_label("work:messages");
+  gI_rows_.set_label("work:message_gradients"); rho_rows_.set_label("work:rho"); e_atom_.set_label("work:atom_energy");
+  vir_atom_.set_label("work:atom_virial"); grho_rows_.set_label("work:rho_gradients");
+  rcsq_.upload(P.rcsq);
+  std::vector<float> rcf(P.rc.begin(), P.rc.end());
+  rcf_.upload(rcf);
+  eW_.upload(P.eW);
+  shift_.upload(P.shift);
+  setup_layer(L1_, P.L1);
+  if (P.layers == 2) {
+    setup_layer(L2_, P.L2);
+    lnI_.upload(P.lnI);
+    ln0_.upload(P.ln0);
+  }
+  ReadoutDev &r = readout_;
+  r.W = eW_.get();
+  r.shift = shift_.get();
+  r.lnI = lnI_.get();
+  r.ln0 = ln0_.get();
+  r.nlay = (int) P.e_nin.size();
+  for (int L = 0; L < r.nlay; L++) {
+    r.n_in[L] = P.e_nin[L];
+    r.n_out[L] = P.e_nout[L];
+    r.norm[L] = P.e_norm[L];
+  }
+  r.act = P.e_act;
+  r.ln = P.e_ln;
+  r.rms = P.rms;
+  r.nrho = P.nrho;
+  r.out_scale = P.out_scale;
+  GB_CUDA(cudaStreamSynchronize(dev().stream));    // the uploads read host vectors of this scope
+}
+
+Engine::~Engine() = default;
+
+double Engine::per_atom_bytes() const { return 4.0 * (double) std::max(L1_.per_atom, L2_.per_atom); }
+
+int Engine::auto_chunk(int64_t n) const
+{
+  size_t free_b = 0, total_b = 0;
+  if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) free_b = (size_t) 8 << 30;
+  const double budget = 0.35 * (double) free_b + 4.0 * (double) arena_.capacity();
+  int64_t c = (int64_t) (budget / per_atom_bytes());
+  c = std::min<int64_t>(c, 32768);    // larger chunks do not lower the launch count per atom enough to matter
+  c = std::max<int64_t>(c, 512);
+  return (int) std::min<int64_t>(c, std::max<int64_t>(n, 1));
+}
+
+void Engine::release_work()
+{
+  arena_.release(); fv_.release(); I_rows_.release(); gI_rows_.release(); rho_rows_.release();
+  e_atom_.release(); vir_atom_.release(); grho_rows_.release();
+  arena_NA_ = 0;
+}
+
+void Engine::bind_arena(LayerEngine &E, int NA)
+{
+  if (!E.plan) return;
+  for (size_t t = 0; t < E.tensors_host.size(); t++)
+    E.tensors_host[t] = TensorDev{arena_.get() + E.toff[t] * NA, E.plan->tensors[t].channels};
+  E.tensors.upload(E.tensors_host);
+}
+
+LayerDev Engine::layer_dev(const LayerEngine &E) const
+{
+  LayerDev L{};
+  L.tab = E.tab.get();
+  L.z = E.z.get();
+  L.rc = rcf_.get();
+  L.msg = nullptr;
+  L.gmsg = nullptr;
+  L.N = E.plan->radial.N;
+  L.C = E.plan->C;
+  L.n_msg = E.plan->n_msg;
+  L.n_elements = plan_.n_elements;
+  return L;
+}
+
+void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA)
+{
+  // NA here is the number of atoms in use; the stride of the tensors is arena_NA_
+  for (const Op &o : prog.ops) {
+    if (o.kind == Op::MV) launch_mv(E.mv[o.index], E.tensors.get(), mu, arena_NA_, NA);
+    else launch_prod(E.prod[o.index], E.tensors.get(), arena_NA_, NA, E.plan->tensors[E.prod[o.index].dst].channels);
+  }
+}
+
+void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm)
+{
+  const int64_t n = nl.n();
+  const int nsys = nl.nsys();
+  cudaStream_t st = dev().stream;
+  if (n == 0) {
+    if (out.energy) GB_CUDA(cudaMemsetAsync(out.energy, 0, sizeof(double) * nsys, st));
+    if (out.virial && !energy_only) GB_CUDA(cudaMemsetAsync(out.virial, 0, sizeof(double) * 6 * nsys, st));
+    return;
+  }
+  const ModelPlan &P = plan_;
+  const int NA = (int) std::min<int64_t>(n, chunk > 0 ? chunk : n);
+  const long long per_atom = std::max(L1_.per_atom, L2_.per_atom);
+  const float *arena_before = arena_.get();
+  arena_.ensure((size_t) per_atom * NA);
+  if (arena_.get() != arena_before || arena_NA_ != NA) {
+    arena_NA_ = NA;
+    bind_arena(L1_, NA);
+    bind_arena(L2_, NA);
+  }
+  e_atom_.ensure(n);
+  if (!energy_only) vir_atom_.ensure(6 * n);
+  const BondsDev bonds = nl.bonds();
+  const int *mu = nl.mu_sorted();
+  float *fv = fv_.get();
+  auto zero_grads = [&](LayerEngine &E) {
+    GB_CUDA(cudaMemsetAsync(arena_.get() + E.grad_begin * NA, 0, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * NA, st));
+  };
+  auto T1 = [&](int t) { return L1_.tensors_host[t].p; };
+  auto T2 = [&](int t) { return L2_.tensors_host[t].p; };
+
+  if (P.layers == 1) {
+    const LayerDev L = layer_dev(L1_);
+    for (int64_t a0 = 0; a0 < n; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, n - a0);
+      if (tm) tm->begin(StageTimer::FWD);
+      launch_bond_fwd(P.lmax, bonds, L, T1(P.L1.tQ), NA, (int) a0, na);
+      run(L1_, P.L1.fwd, mu + a0, na);
+      launch_readout_1l(readout_, T1(P.t1_rho), T1(P.t1_grho), mu, e_atom_.get(), NA, na, (int) a0, !energy_only);
+      if (tm) tm->end(StageTimer::FWD);
+      if (energy_only) continue;
+      if (tm) tm->begin(StageTimer::BWD);
+      zero_grads(L1_);
+      run(L1_, P.L1.bwd, mu + a0, na);
+      launch_bond_bwd(P.lmax, bonds, L, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0);
+      if (tm) tm->end(StageTimer::BWD);
+    }
+  } else {
+    const int nI = P.nI, CR = P.cr, nrho = P.nrho;
+    I_rows_.ensure((size_t) n * nI * CR);
+    rho_rows_.ensure((size_t) n * nrho);
+    if (!energy_only) {
+      gI_rows_.ensure((size_t) n * nI * CR);
+      grho_rows_.ensure((size_t) n * nrho);
+      GB_CUDA(cudaMemsetAsync(gI_rows_.get(), 0, sizeof(float) * (size_t) n * nI * CR, st));
+    }
+    const LayerDev La = layer_dev(L1_);
+    LayerDev Lb = layer_dev(L2_);
+    Lb.msg = I_rows_.get();
+    Lb.gmsg = gI_rows_.get();
+    // layer 1 forward of every chunk: messages I and rho of all atoms
+    if (tm) tm->begin(StageTimer::FWD);
+    for (int64_t a0 = 0; a0 < n; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, n - a0);
+      launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
+      run(L1_, P.L1.fwd, mu + a0, na);
+      launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, NA, na, (int) a0);
+      launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, NA, na, (int) a0);
+    }
+    if (tm) tm->end(StageTimer::FWD);
+    // layer 2 forward, energy and layer-2 reverse per chunk
+    for (int64_t a0 = 0; a0 < n; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, n - a0);
+      if (tm) tm->begin(StageTimer::FWD);
+      launch_bond_fwd(P.lmax, bonds, Lb, T2(P.L2.tQ), NA, (int) a0, na);
+      run(L2_, P.L2.fwd, mu + a0, na);
+      launch_readout_2l(readout_, rho_rows_.get(), T2(P.t2_I2), grho_rows_.get(), T2(P.t2_gI2), mu, e_atom_.get(), NA,
+                        na, (int) a0, !energy_only);
+      if (tm) tm->end(StageTimer::FWD);
+      if (energy_only) continue;
+      if (tm) tm->begin(StageTimer::BWD);
+      zero_grads(L2_);
+      run(L2_, P.L2.bwd, mu + a0, na);
+      launch_bond_bwd(P.lmax, bonds, Lb, T2(P.L2.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0);
+      if (tm) tm->end(StageTimer::BWD);
+    }
+    // layer 1 again (recomputed) and its reverse, seeded with dE/dI and dE/drho of each atom
+    if (!energy_only) {
+      if (tm) tm->begin(StageTimer::BWD);
+      for (int64_t a0 = 0; a0 < n; a0 += NA) {
+        const int na = (int) std::min<int64_t>(NA, n - a0);
+        launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
+        run(L1_, P.L1.fwd, mu + a0, na);
+        zero_grads(L1_);
+        launch_chunk_from_rows(T1(P.t1_gI), gI_rows_.get(), nI, CR, NA, na, (int) a0);
+        launch_chunk_from_rows_f64(T1(P.t1_grho), grho_rows_.get(), 1, nrho, NA, na, (int) a0);
+        run(L1_, P.L1.bwd, mu + a0, na);
+        launch_bond_bwd(P.lmax, bonds, La, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 1);
+      }
+      if (tm) tm->end(StageTimer::BWD);
+    }
+  }
+  // sums and gathers that leave the engine
+  if (out.energy) launch_segment_sum(e_atom_.get(), 1, nl.seg(), nsys, out.energy);
+  if (out.energies) launch_scatter_f64(e_atom_.get(), nl.perm(), out.energies, (int) n);
+  if (!energy_only) {
+    if (out.virial) launch_segment_sum(vir_atom_.get(), 6, nl.seg(), nsys, out.virial);
+    if (out.forces) launch_force_gather(nl.off(), nl.rev(), fv, nl.perm(), out.forces, (int) n);
+  }
+}
+
+// ---- model -----------------------------------------------------------------------------------------------------
+std::shared_ptr<Engine> ModelObj::get_engine(int spline_n)
+{
+  std::lock_guard<std::mutex> lk(mu);
+  if (!engine) {
+    engine = std::make_shared<Engine>(model, spline_n);
+    setups++;
+  }
+  return engine;
+}
+
+// ---- system ----------------------------------------------------------------------------------------------------
+namespace {
+
+void label_ws(Workspace &w)
+{
+  w.pos.set_label("system:positions"); w.energy.set_label("system:energy"); w.virial.set_label("system:virial");
+  w.forces.set_label("system:forces"); w.energies.set_label("system:energies"); w.types.set_label("system:types");
+  w.mu.set_label("system:elements"); w.t2m.set_label("system:type_map"); w.flag.set_label("system:flag");
+  w.types_prev.set_label("system:types");
+}
+
+int read_int(const int *d)
+{
+  int h = 0;
+  GB_CUDA(cudaMemcpyAsync(&h, d, sizeof(int), cudaMemcpyDeviceToHost, dev().stream));
+  GB_CUDA(cudaStreamSynchronize(dev().stream));
+  return h;
+}
+
+void check_flags(int flags)
+{
+  if (flags & 4) throw Unsupported("the model has no UQ head usable by this backend");
+  if (flags & ~7) throw InvalidArgument("unknown compute flag");
+}
+
+}    // namespace
+
+SystemObj::SystemObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &species, double skin, int spline,
+                     int chunk)
+    : model_(std::move(m)), skin_(skin), chunk_req_(chunk)
+{
+  require_initialized();
+  if (!(skin >= 0.0) || !std::isfinite(skin)) throw InvalidArgument("skin must be >= 0");
+  t2m_ = species_to_elements(model_->model, species);
+  engine_ = model_->get_engine(spline > 0 ? spline : model_->spline);
+  cutoff_ = 0.0;
+  for (int a : t2m_)
+    for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));
+  label_ws(ws_);
+}
+
+void SystemObj::release()
+{
+  nl_.release();
+  ws_ = Workspace{};
+  label_ws(ws_);
+  have_list_ = false;
+  engine_->release_work();
+}
+
+void SystemObj::compute(int n, const int *types, const double *pos, bool device_in, const double *cell,
+                        const unsigned char *pbc, int flags, double *energy, double *virial, double *forces,
+                        double *energies, bool device_out)
+{
+  require_initialized();
+  check_flags(flags);
+  if (n < 0) throw InvalidArgument("negative atom count");
+  if (n > 0 && (!types || !pos)) throw InvalidArgument("types and positions must be given");
+  if (!cell || !pbc) throw InvalidArgument("cell and pbc must be given");
+  for (int k = 0; k < 9; k++)
+    if (!std::isfinite(cell[k])) throw InvalidArgument("the cell must be finite");
+  std::lock_guard<std::mutex> lk(engine_->mu);
+  int chunk = chunk_req_ < 0 ? engine_->auto_chunk(n) : chunk_req_;
+  for (;;) {
+    try {
+      compute_once(n, types, pos, device_in, cell, pbc, flags, energy, virial, forces, energies, device_out, chunk);
+      last_chunk = (chunk > 0 && chunk < n) ? chunk : 0;
+      return;
+    } catch (const OutOfMemory &e) {
+      // drop what was allocated, halve the pass down to 512 atoms, then give up (kk_core.cpp:420-497)
+      nl_.release();
+      have_list_ = false;
+      engine_->release_work();
+      const int cur = chunk > 0 ? std::min(chunk, std::max(n, 1)) : std::max(n, 1);
+      if (cur <= 512) throw OutOfMemory(std::string("the structure does not fit the device memory: ") + e.what());
+      chunk = std::max(512, cur / 2);
+    }
+  }
+}
+
+void SystemObj::compute_once(int n, const int *types, const double *pos, bool device_in, const double *cell,
+                             const unsigned char *pbc, int flags, double *energy, double *virial, double *forces,
+                             double *energies, bool device_out, int chunk)
+{
+  cudaStream_t st = dev().stream;
+  const bool eonly = flags & 2, want_e = flags & 1;
+  timer_.reset();
+  timer_.begin(StageTimer::TOTAL);
+  const int ns = (int) t2m_.size();
+  const int *d_types = types;
+  const double *d_pos = pos;
+  ws_.flag.ensure(1);
+  GB_CUDA(cudaMemsetAsync(ws_.flag.get(), 0, sizeof(int), st));
+  if (n > 0) {
+    if (!device_in) {
+      ws_.types.ensure(n);
+      ws_.pos.ensure(3 * (size_t) n);
+      GB_CUDA(cudaMemcpyAsync(ws_.types.get(), types, sizeof(int) * n, cudaMemcpyHostToDevice, st));
+      GB_CUDA(cudaMemcpyAsync(ws_.pos.get(), pos, sizeof(double) * 3 * n, cudaMemcpyHostToDevice, st));
+      d_types = ws_.types.get();
+      d_pos = ws_.pos.get();
+    }
+    ws_.mu.ensure(n);
+    ws_.t2m.upload(t2m_);
+    GB_LAUNCH(types_to_mu, nblocks(n, 256), 256, 0, d_types, ws_.t2m.get(), ns, ws_.mu.get(), ws_.flag.get(), (long long) n);
+  }
+  // rebuild when the atoms, cell or pbc changed or an atom moved more than half the skin (kk_core.cpp:691-708)
+  bool need = !have_list_ || list_n_ != n || ws_.h_cell.size() != 9 || std::memcmp(ws_.h_cell.data(), cell, 72) != 0 ||
+              std::memcmp(ws_.h_pbc.data(), pbc, 3) != 0;
+  if (n > 0) {
+    if (!need) GB_LAUNCH(types_differ, nblocks(n, 256), 256, 0, d_types, ws_.types_prev.get(), ws_.flag.get(), (long long) n);
+    const int fl = read_int(ws_.flag.get());
+    if (fl & 1) throw InvalidArgument("types must be 1 .. len(species)");
+    if (fl & 2) need = true;
+    if (!need && nl_.moved_beyond(d_pos, 0.5 * skin_)) need = true;
+  }
+  if (need) {
+    timer_.begin(StageTimer::NL);
+    have_list_ = false;
+    nl_.build(1, &n, n, d_pos, ws_.mu.get(), cell, pbc, cutoff_ + skin_);
+    ws_.h_cell.assign(cell, cell + 9);
+    ws_.h_pbc.assign(pbc, pbc + 3);
+    if (n > 0) {
+      ws_.types_prev.ensure(n);
+      GB_CUDA(cudaMemcpyAsync(ws_.types_prev.get(), d_types, sizeof(int) * n, cudaMemcpyDeviceToDevice, st));
+    }
+    list_n_ = n;
+    have_list_ = true;
+    rebuilds++;
+    timer_.end(StageTimer::NL);
+  }
+  timer_.begin(StageTimer::GEOM);
+  float *fv = engine_->bond_forces(nl_.nslots());
+  nl_.prepare(d_pos, engine_->rcsq(), model_->model.n_elements, fv);
+  timer_.end(StageTimer::GEOM);
+  OutputsDev o;
+  if (device_out) {
+    o.energy = energy;
+    o.virial = eonly ? nullptr : virial;
+    o.forces = eonly ? nullptr : forces;
+    o.energies = want_e ? energies : nullptr;
+  } else {
+    o.energy = ws_.energy.ensure(1);
+    if (!eonly && virial) o.virial = ws_.virial.ensure(6);
+    if (!eonly && forces) o.forces = ws_.forces.ensure(3 * (size_t) std::max(n, 1));
+    if (want_e && energies) o.energies = ws_.energies.ensure(std::max(n, 1));
+  }
+  engine_->evaluate(nl_, eonly, o, chunk, &timer_);
+  if (!device_out) {
+    if (energy) GB_CUDA(cudaMemcpyAsync(energy, o.energy, sizeof(double), cudaMemcpyDeviceToHost, st));
+    if (o.virial) GB_CUDA(cudaMemcpyAsync(virial, o.virial, sizeof(double) * 6, cudaMemcpyDeviceToHost, st));
+    if (o.forces && n > 0) GB_CUDA(cudaMemcpyAsync(forces, o.forces, sizeof(double) * 3 * n, cudaMemcpyDeviceToHost, st));
+    if (o.energies && n > 0) GB_CUDA(cudaMemcpyAsync(energies, o.energies, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+  }
+  timer_.end(StageTimer::TOTAL);
+  const int fl = n > 0 ? nl_.take_flag() : 0;    // synchronises the stream
+  GB_CUDA(cudaStreamSynchronize(st));
+  timer_.collect(stage_ms);
+  if (fl & 2) {
+    have_list_ = false;
+    throw InvalidArgument("two atoms at the same position (a bond of length 0): not a physical structure");
+  }
+}
+
+// ---- batch -----------------------------------------------------------------------------------------------------
+BatchObj::BatchObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &species, int spline, int chunk)
+    : model_(std::move(m)), chunk_req_(chunk)
+{
+  require_initialized();
+  t2m_ = species_to_elements(model_->model, species);
+  engine_ = model_->get_engine(spline > 0 ? spline : model_->spline);
+  cutoff_ = 0.0;
+  for (int a : t2m_)
+    for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));
+  label_ws(ws_);
+}
+
+void BatchObj::release()
+{
+  nl_.release();
+  ws_ = Workspace{};
+  label_ws(ws_);
+  engine_->release_work();
+}
+
+void BatchObj::compute(int nsys, const int *natoms, int64_t ntot, const int *types, const double *pos, bool device_io,
+                       const double *cell, const unsigned char *pbc, int flags, int64_t max_nall, double *energy,
+                       double *virial, double *forces, double *energies)
+{
+  require_initialized();
+  check_flags(flags);
+  if (nsys < 0 || ntot < 0) throw InvalidArgument("negative structure or atom count");
+  if (nsys > 0 && (!natoms || !cell || !pbc)) throw InvalidArgument("natoms, cell and pbc must be given");
+  if (ntot > 0 && (!types || !pos)) throw InvalidArgument("types and positions must be given");
+  int64_t sum = 0;
+  for (int s = 0; s < nsys; s++) {
+    if (natoms[s] < 0) throw InvalidArgument("negative atom count");
+    sum += natoms[s];
+  }
+  if (sum != ntot) throw InvalidArgument("natoms must sum to the atom count");
+  for (int64_t k = 0; k < 9 * (int64_t) nsys; k++)
+    if (!std::isfinite(cell[k])) throw InvalidArgument("the cells must be finite");
+  if (max_nall <= 0) max_nall = (int64_t) 1 << 21;
+  std::lock_guard<std::mutex> lk(engine_->mu);
+  int chunk = chunk_req_;
+  for (;;) {
+    try {
+      const int c = chunk < 0 ? engine_->auto_chunk(std::min<int64_t>(ntot, max_nall)) : chunk;
+      compute_once(nsys, natoms, ntot, types, pos, device_io, cell, pbc, flags, max_nall, energy, virial, forces,
+                   energies, c);
+      last_chunk = c;
+      if (!keep_buffers) {
+        nl_.release();
+        engine_->release_work();
+      }
+      return;
+    } catch (const OutOfMemory &e) {
+      // smaller passes: max_nall halved down to 16384 atoms, then give up (kk_core.cpp:1456-1483)
+      nl_.release();
+      engine_->release_work();
+      if (max_nall <= 16384) throw OutOfMemory(std::string("the batch does not fit the device memory: ") + e.what());
+      max_nall = std::max<int64_t>(16384, max_nall / 2);
+      if (chunk > 0) chunk = std::max(512, chunk / 2);
+    }
+  }
+}
+
+void BatchObj::compute_once(int nsys, const int *natoms, int64_t ntot, const int *types, const double *pos,
+                            bool device_io, const double *cell, const unsigned char *pbc, int flags, int64_t max_nall,
+                            double *energy, double *virial, double *forces, double *energies, int chunk)
+{
+  cudaStream_t st = dev().stream;
+  const bool eonly = flags & 2, want_e = flags & 1;
+  const int ns = (int) t2m_.size();
+  passes = 0;
+  host_seconds = 0.0;
+  const int *d_types = types;
+  const double *d_pos = pos;
+  ws_.flag.ensure(1);
+  GB_CUDA(cudaMemsetAsync(ws_.flag.get(), 0, sizeof(int), st));
+  if (ntot > 0) {
+    if (!device_io) {
+      ws_.types.ensure(ntot);
+      ws_.pos.ensure(3 * (size_t) ntot);
+      GB_CUDA(cudaMemcpyAsync(ws_.types.get(), types, sizeof(int) * ntot, cudaMemcpyHostToDevice, st));
+      GB_CUDA(cudaMemcpyAsync(ws_.pos.get(), pos, sizeof(double) * 3 * ntot, cudaMemcpyHostToDevice, st));
+      d_types = ws_.types.get();
+      d_pos = ws_.pos.get();
+    }
+    ws_.mu.ensure(ntot);
+    ws_.t2m.upload(t2m_);
+    GB_LAUNCH(types_to_mu, nblocks(ntot, 256), 256, 0, d_types, ws_.t2m.get(), ns, ws_.mu.get(), ws_.flag.get(), (long long) ntot);
+    if (read_int(ws_.flag.get()) & 1) throw InvalidArgument("types must be 1 .. len(species)");
+  }
+  OutputsDev all;
+  if (device_io) {
+    all.energy = energy;
+    all.virial = eonly ? nullptr : virial;
+    all.forces = eonly ? nullptr : forces;
+    all.energies = want_e ? energies : nullptr;
+  } else {
+    all.energy = ws_.energy.ensure(std::max(nsys, 1));
+    if (!eonly && virial) all.virial = ws_.virial.ensure(6 * (size_t) std::max(nsys, 1));
+    if (!eonly && forces) all.forces = ws_.forces.ensure(3 * (size_t) std::max<int64_t>(ntot, 1));
+    if (want_e && energies) all.energies = ws_.energies.ensure(std::max<int64_t>(ntot, 1));
+  }
+  // passes of whole structures with at most max_nall atoms (a single larger structure gets a pass of its own)
+  int s0 = 0;
+  int64_t a0 = 0;
+  bool zero_bond = false;
+  while (s0 < nsys) {
+    int s1 = s0;
+    int64_t na = 0;
+    while (s1 < nsys && (s1 == s0 || na + natoms[s1] <= max_nall)) na += natoms[s1++];
+    const auto t0 = std::chrono::steady_clock::now();
+    nl_.build(s1 - s0, natoms + s0, na, d_pos + 3 * a0, ws_.mu.get() + a0, cell + 9 * (size_t) s0, pbc + 3 * (size_t) s0,
+              cutoff_);
+    float *fv = engine_->bond_forces(nl_.nslots());
+    nl_.prepare(d_pos + 3 * a0, engine_->rcsq(), model_->model.n_elements, fv);
+    GB_CUDA(cudaStreamSynchronize(st));
+    host_seconds += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    OutputsDev o;
+    o.energy = all.energy ? all.energy + s0 : nullptr;
+    o.virial = all.virial ? all.virial + 6 * (size_t) s0 : nullptr;
+    o.forces = all.forces ? all.forces + 3 * a0 : nullptr;
+    o.energies = all.energies ? all.energies + a0 : nullptr;
+    engine_->evaluate(nl_, eonly, o, chunk, nullptr);
+    if (na > 0 && (nl_.take_flag() & 2)) zero_bond = true;
+    passes++;
+    s0 = s1;
+    a0 += na;
+  }
+  if (!device_io) {
+    if (energy && nsys > 0) GB_CUDA(cudaMemcpyAsync(energy, all.energy, sizeof(double) * nsys, cudaMemcpyDeviceToHost, st));
+    if (all.virial && nsys > 0) GB_CUDA(cudaMemcpyAsync(virial, all.virial, sizeof(double) * 6 * nsys, cudaMemcpyDeviceToHost, st));
+    if (all.forces && ntot > 0) GB_CUDA(cudaMemcpyAsync(forces, all.forces, sizeof(double) * 3 * ntot, cudaMemcpyDeviceToHost, st));
+    if (all.energies && ntot > 0) GB_CUDA(cudaMemcpyAsync(energies, all.energies, sizeof(double) * ntot, cudaMemcpyDeviceToHost, st));
+  }
+  GB_CUDA(cudaStreamSynchronize(st));
+  if (zero_bond) throw InvalidArgument("two atoms at the same position (a bond of length 0): not a physical structure");
+}
+
+}    // namespace gb

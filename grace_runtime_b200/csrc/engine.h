@@ -1,0 +1,148 @@
+// Model / System / Batch objects behind the C ABI: the device engine of a model (weights and tables, shared by the
+// Systems and Batches of the model as in python/kk/kk_core.cpp:199-221, 555-588) and the evaluation drivers
+// (System::compute python/kk/kk_core.cpp:802-958, Batch::compute :1276-1504; layer order of GRACE-2L as
+// libgrace/src/fused_2l.cpp:988-1091).
+#pragma once
+
+#include "kernels.h"
+#include "nlist.h"
+#include "plan.h"
+
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace gb {
+
+struct LayerEngine {
+  const LayerPlan *plan = nullptr;
+  DBuf<float> tab, z;
+  std::vector<DBuf<int>> ibufs;
+  std::vector<DBuf<float>> fbufs;
+  std::vector<DBuf<MVItem>> itembufs;
+  std::vector<DBuf<ProdTerm>> termbufs;
+  std::vector<MVDev> mv;
+  std::vector<ProdDev> prod;
+  std::vector<long long> toff;    // offset of each tensor in floats per atom
+  long long per_atom = 0, grad_begin = 0, grad_end = 0;
+  DBuf<TensorDev> tensors;
+  std::vector<TensorDev> tensors_host;
+};
+
+// outputs of one evaluation, device pointers (null: not wanted)
+struct OutputsDev {
+  double *energy = nullptr;      // [nsys]
+  double *virial = nullptr;      // [nsys][6]
+  double *forces = nullptr;      // [n][3] caller's order
+  double *energies = nullptr;    // [n] caller's order
+};
+
+class Engine {
+ public:
+  Engine(const GraceModel &m, int spline_n);
+  ~Engine();
+  const ModelPlan &plan() const { return plan_; }
+  // evaluates the structures of the neighbour list nl (positions prepared by nl.prepare); chunk: atoms per pass
+  void evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm);
+  // bond-force slots [3 * nslots] the list zeroes for bonds outside the cutoff (grown here)
+  float *bond_forces(int64_t nslots) { return fv_.ensure(3 * (size_t) std::max<int64_t>(nslots, 1)); }
+  const double *rcsq() const { return rcsq_.get(); }
+  int auto_chunk(int64_t n) const;
+  void release_work();
+  double per_atom_bytes() const;
+  std::mutex mu;    // one evaluation at a time per engine
+
+ private:
+  ModelPlan plan_;
+  LayerEngine L1_, L2_;
+  DBuf<double> rcsq_, eW_, shift_, lnI_, ln0_;
+  DBuf<float> rcf_;
+  ReadoutDev readout_{};
+  // work buffers
+  DBuf<float> arena_, fv_, I_rows_, gI_rows_, rho_rows_;
+  DBuf<double> e_atom_, vir_atom_, grho_rows_;
+  int arena_NA_ = 0;
+  void setup_layer(LayerEngine &E, const LayerPlan &P);
+  void bind_arena(LayerEngine &E, int NA);
+  void run(LayerEngine &E, const Program &prog, const int *mu, int NA);
+  LayerDev layer_dev(const LayerEngine &E) const;
+};
+
+struct ModelObj {
+  GraceModel model;
+  std::string path;
+  int spline = 1024;
+  std::mutex mu;
+  std::shared_ptr<Engine> engine;    // created by the first System / Batch
+  int64_t setups = 0;
+  std::shared_ptr<Engine> get_engine(int spline_n);
+};
+
+struct Workspace {
+  DBuf<double> pos, energy, virial, forces, energies;
+  DBuf<int> types, mu, t2m, flag, types_prev;
+  std::vector<double> h_cell;
+  std::vector<unsigned char> h_pbc;
+  std::vector<int> h_natoms;
+};
+
+class SystemObj {
+ public:
+  SystemObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &species, double skin, int spline, int chunk);
+  double cutoff() const { return cutoff_; }
+  void compute(int n, const int *types, const double *pos, bool device_in, const double *cell,
+               const unsigned char *pbc, int flags, double *energy, double *virial, double *forces, double *energies,
+               bool device_out);
+  int64_t rebuilds = 0;
+  int last_chunk = 0;
+  double stage_ms[StageTimer::NSTAGE] = {0, 0, 0, 0, 0};
+  void release();
+  std::mutex mu;
+
+ private:
+  void compute_once(int n, const int *types, const double *pos, bool device_in, const double *cell,
+                    const unsigned char *pbc, int flags, double *energy, double *virial, double *forces,
+                    double *energies, bool device_out, int chunk);
+  std::shared_ptr<ModelObj> model_;
+  std::shared_ptr<Engine> engine_;
+  std::vector<int> t2m_;
+  double skin_, cutoff_;
+  int chunk_req_;
+  NeighborList nl_;
+  Workspace ws_;
+  StageTimer timer_;
+  bool have_list_ = false;
+  int64_t list_n_ = -1;
+};
+
+class BatchObj {
+ public:
+  BatchObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &species, int spline, int chunk);
+  double cutoff() const { return cutoff_; }
+  void compute(int nsys, const int *natoms, int64_t ntot, const int *types, const double *pos, bool device_io,
+               const double *cell, const unsigned char *pbc, int flags, int64_t max_nall, double *energy,
+               double *virial, double *forces, double *energies);
+  int passes = 0;
+  int last_chunk = 0;
+  double host_seconds = 0.0;
+  bool keep_buffers = false;
+  void release();
+  std::mutex mu;
+
+ private:
+  void compute_once(int nsys, const int *natoms, int64_t ntot, const int *types, const double *pos, bool device_io,
+                    const double *cell, const unsigned char *pbc, int flags, int64_t max_nall, double *energy,
+                    double *virial, double *forces, double *energies, int chunk);
+  std::shared_ptr<ModelObj> model_;
+  std::shared_ptr<Engine> engine_;
+  std::vector<int> t2m_;
+  double cutoff_;
+  int chunk_req_;
+  NeighborList nl_;
+  Workspace ws_;
+};
+
+std::vector<int> species_to_elements(const GraceModel &m, const std::vector<std::string> &species);
+
+}    // namespace gb

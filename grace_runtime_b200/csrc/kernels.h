@@ -1,0 +1,90 @@
+// Device-side descriptors and host launchers of the CUDA kernels.  Tensors of the dense network are
+// [function][atom of the chunk][channel] fp32; geometry and all sums leaving the network are fp64.
+#pragma once
+
+#include "device.h"
+#include "plan.h"
+
+namespace gb {
+
+struct TensorDev {
+  float *p;
+  int C;
+};
+
+struct MVDev {
+  const int *row_out;
+  const int *item_off;
+  const MVItem *items;
+  const float *W;
+  long long ty_stride;
+  int n_out, nrows, accumulate, elem, dst;
+};
+
+struct ProdDev {
+  const int *row_out;
+  const int *term_off;
+  const ProdTerm *terms;
+  int nrows, accumulate, dst, srcA, srcB;
+};
+
+// the neighbour list of one pass and this call's bond records
+struct BondsDev {
+  const long long *off;    // [n + 1] slots of the list (built with cutoff + skin)
+  const int *cnt;          // [n] bonds inside the cutoff this call, compacted to the front of the atom's slots
+  const float4 *rec;       // per slot: bond vector x_j - x_i + S cell (fp32 of the fp64 difference), j in .w
+  const int *cslot;        // per compacted bond: the slot it came from
+  const int *mu;           // [n] model element of each atom (list order)
+};
+
+// per layer: radial table, chemical weights, messages
+struct LayerDev {
+  const float *tab;        // [N][4][nl][C]
+  const float *z;          // [n_elements][C]
+  const float *rc;         // [n_elements][n_elements] pair cutoffs
+  const float *msg;        // [n][n_msg][C] message rows of all atoms (layer 2) or null
+  float *gmsg;             // [n][n_msg][C] dE/dmsg rows, added to atomically by the reverse bond kernel
+  int N, C, n_msg, n_elements;
+};
+
+// element of a tensor: p[(f * NA + a) * C + c]; NA: atom stride of the chunk tensors, na <= NA: atoms in use
+void launch_mv(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na);
+void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, int C);
+
+// Q[(I, lm)][a][n] = sum over the bonds of atom a0 + a of Y_lm R[n, l] msg_I[n]
+void launch_bond_fwd(int lmax, const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na);
+// reverse: per bond dE/dx and dE/dY from gQ -> bond force (written or added at the bond's slot), per-atom virial,
+// dE/dmsg rows of the neighbours
+void launch_bond_bwd(int lmax, const BondsDev &b, const LayerDev &L, const float *gQ, int NA, int a0, int na,
+                     float *fv, double *vir_atom, int add);
+
+struct ReadoutDev {
+  const double *W;        // layers concatenated
+  const double *shift;    // [n_elements]
+  const double *lnI, *ln0;
+  int nlay, n_in[4], n_out[4];
+  double norm[4];
+  int act, ln, rms, nrho;
+  double out_scale;
+};
+// GRACE-1L: E_i = (MLP(rho[1:]) + rho[0]) scale + shift, dE/drho
+void launch_readout_1l(const ReadoutDev &r, const float *rho, float *grho, const int *mu, double *e_atom, int NA,
+                       int na, int a0, int want_grad);
+// GRACE-2L: rho from the per-atom rows, I2 of the chunk; dE/drho to the per-atom rows, dE/dI2 to the chunk
+void launch_readout_2l(const ReadoutDev &r, const float *rho_rows, const float *I2, double *grho_rows, float *gI2,
+                       const int *mu, double *e_atom, int NA, int na, int a0, int want_grad);
+
+// chunk tensor [nf][NA][C] <-> per-atom rows [n][nf][C] (message I, its gradient) and [n][C] (rho)
+void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0);
+void launch_chunk_from_rows(float *t, const float *rows, int nf, int C, int NA, int na, int a0);
+void launch_chunk_from_rows_f64(float *t, const double *rows, int nf, int C, int NA, int na, int a0);
+
+// F_i = sum over the slots q of atom i of fv[q] - fv[rev[q]], written at the caller's index of atom i
+void launch_force_gather(const long long *off, const int *rev, const float *fv, const int *perm, double *forces,
+                         int n);
+// per-structure sums of per-atom values: out[s][k] = sum_{i in [seg[s], seg[s+1])} v[i][k]
+void launch_segment_sum(const double *v, int K, const int *seg, int nseg, double *out);
+// out[perm[i]] = v[i]
+void launch_scatter_f64(const double *v, const int *perm, double *out, int n);
+
+}    // namespace gb

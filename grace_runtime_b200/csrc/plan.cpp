@@ -1,0 +1,536 @@
+#include "plan.h"
+
+#include <algorithm>
+#include <cmath>
+#include <map>
+
+namespace gb {
+
+double MVOp::flops_per_atom() const
+{
+  double f = 0.0;
+  for (const auto &it : items) f += 2.0 * it.n_in * n_out;
+  return f;
+}
+
+namespace {
+
+// ---- radial tables -------------------------------------------------------------------------------------------
+
+// g_k = T_k(2x - 1) fc_p(x), k = 1..nrb, and d/dx (libgrace/include/grace/radial_x.h:11-26)
+void radial_basis_x(double x, int p, int nrb, std::vector<double> &g, std::vector<double> &dg)
+{
+  const double xp = std::pow(x, p), xp1 = xp * x, xp2 = xp1 * x;
+  const double fc = 1.0 - 0.5 * (p + 1) * (p + 2) * xp + p * (p + 2) * xp1 - 0.5 * p * (p + 1) * xp2;
+  const double dfc = 0.5 * p * (p + 1) * (p + 2) * (-std::pow(x, p - 1) + 2.0 * xp - xp1);
+  const double t = 2.0 * x - 1.0;
+  double Tp = 1.0, Tc = t, dTp = 0.0, dTc = 2.0;
+  g.resize(nrb);
+  dg.resize(nrb);
+  for (int k = 0; k < nrb; k++) {
+    g[k] = Tc * fc;
+    dg[k] = dTc * fc + Tc * dfc;
+    const double Tn = 2.0 * t * Tc - Tp, dTn = 2.0 * (2.0 * Tc + t * dTc) - dTp;
+    Tp = Tc; dTp = dTc; Tc = Tn; dTc = dTn;
+  }
+}
+
+// value and d/dx of the radial MLP in forward mode (libgrace/include/grace/radial_x.h:30-60)
+void mlp_x(const std::vector<MlpLayer> &layers, std::vector<double> h, std::vector<double> dh, std::vector<double> &out,
+           std::vector<double> &dout, int act)
+{
+  const int n = (int) layers.size();
+  for (int il = 0; il < n; il++) {
+    const MlpLayer &L = layers[il];
+    std::vector<double> s(L.n_out, 0.0), ds(L.n_out, 0.0);
+    for (int k = 0; k < L.n_in; k++)
+      for (int j = 0; j < L.n_out; j++) {
+        const double w = L.W[(size_t) k * L.n_out + j];
+        s[j] += w * h[k];
+        ds[j] += w * dh[k];
+      }
+    for (int j = 0; j < L.n_out; j++) {
+      s[j] *= L.norm;
+      ds[j] *= L.norm;
+      if (il < n - 1 && act == 1) {
+        s[j] = std::tanh(s[j]);
+        ds[j] *= 1.0 - s[j] * s[j];
+      } else if (il < n - 1) {
+        const double sg = 1.0 / (1.0 + std::exp(-s[j]));
+        ds[j] = sg * (1.0 + s[j] * (1.0 - sg)) * ds[j];
+        s[j] = s[j] * sg;
+      }
+    }
+    h.swap(s);
+    dh.swap(ds);
+  }
+  out.swap(h);
+  dout.swap(dh);
+}
+
+// cubic Hermite coefficients of R[n][l](x) on N intervals of [0, 1], [N][4][nl][C] in fp32
+// (libgrace/src/fused_1l.cpp:102-129)
+RadialTable build_radial(const GraceModel &m, const std::vector<MlpLayer> &layers, int C, int N)
+{
+  RadialTable T;
+  T.N = N;
+  T.nl = m.lmax + 1;
+  T.C = C;
+  const int nl = T.nl, nout = layers.back().n_out;
+  if (nout != C * nl) throw ModelError("radial MLP output width mismatch");
+  const double h = 1.0 / N;
+  std::vector<double> fv((size_t) (N + 1) * nout), dv((size_t) (N + 1) * nout), g, dg, out, dout;
+  for (int k = 0; k <= N; k++) {
+    radial_basis_x(k * h, m.p, m.nradbase, g, dg);
+    mlp_x(layers, g, dg, out, dout, m.radial_activation);
+    for (int o = 0; o < nout; o++) {
+      fv[(size_t) k * nout + o] = out[o];
+      dv[(size_t) k * nout + o] = h * dout[o];
+    }
+  }
+  T.tab.assign((size_t) N * 4 * nl * C, 0.0f);
+  for (int k = 0; k < N; k++)
+    for (int n = 0; n < C; n++)
+      for (int l = 0; l < nl; l++) {
+        const int o = n * nl + l;
+        const double f0 = fv[(size_t) k * nout + o], f1 = fv[(size_t) (k + 1) * nout + o];
+        const double d0 = dv[(size_t) k * nout + o], d1 = dv[(size_t) (k + 1) * nout + o];
+        const double c[4] = {f0, d0, -3.0 * f0 - 2.0 * d0 + 3.0 * f1 - d1, 2.0 * f0 + d0 - 2.0 * f1 + d1};
+        for (int q = 0; q < 4; q++) T.tab[(((size_t) k * 4 + q) * nl + l) * C + n] = (float) c[q];
+      }
+  return T;
+}
+
+// ---- dense network -------------------------------------------------------------------------------------------
+
+struct ReduceGroup {
+  std::string name;
+  std::vector<const ReduceWeights *> src;    // per source (nullptr: absent)
+  std::vector<int> src_tensor, src_grad, src_row0;
+  int n_out = 0, nfo = 0;
+  bool elem = false;
+  int t_out = -1, t_gout = -1;
+};
+
+struct LayerBuilder {
+  LayerPlan &P;
+  const GraceModel &m;
+  std::vector<std::vector<Op>> adj;    // adjoint ops of each forward op, in forward order
+
+  int tensor(const std::string &name, int nf, int ch, bool grad = false)
+  {
+    P.tensors.push_back({name, nf, ch, grad});
+    return (int) P.tensors.size() - 1;
+  }
+  Op add(MVOp &&o)
+  {
+    o.item_off.push_back((int) o.items.size());    // closes the last row (rows push their start)
+    P.mv.push_back(std::move(o));
+    return {Op::MV, (int) P.mv.size() - 1};
+  }
+  Op add(ProdOp &&o)
+  {
+    o.term_off.push_back((int) o.terms.size());
+    P.prod.push_back(std::move(o));
+    return {Op::PROD, (int) P.prod.size() - 1};
+  }
+  void emit(Op fwd, std::vector<Op> adjoint)
+  {
+    P.fwd.ops.push_back(fwd);
+    adj.push_back(std::move(adjoint));
+  }
+  void finish()
+  {
+    for (size_t q = adj.size(); q-- > 0;)
+      for (const Op &o : adj[q]) P.bwd.ops.push_back(o);
+  }
+
+  // FC: dst = nof (Wl Xl + sum Wr Xr) on the live outputs, and its two adjoints
+  void fc(const std::string &name, const FCWeights &w, const std::vector<char> &live, int tL, int tR, int tD, int gL,
+          int gR, int gD)
+  {
+    const int no = w.n_out, nil = w.n_in_left, nir = w.n_in_right;
+    MVOp F, BL, BR;
+    F.name = name + ":fwd"; BL.name = name + ":adj_left"; BR.name = name + ":adj_right";
+    F.dst = tD; F.n_out = no;
+    BL.dst = gL; BL.n_out = nil; BL.accumulate = true;
+    BR.dst = gR; BR.n_out = nir; BR.accumulate = true;
+    const int base_r = w.tiles_left * nil * no;
+    F.W.assign((size_t) base_r + (size_t) w.tiles_right * nir * no, 0.0f);
+    BL.W.assign((size_t) w.tiles_left * no * nil, 0.0f);
+    BR.W.assign((size_t) w.tiles_right * no * nir, 0.0f);
+    for (int k = 0; k < no; k++) {
+      for (int n = 0; n < nil; n++)
+        for (int t = 0; t < w.tiles_left; t++) {
+          const float v = (float) (w.norm_left * w.w_left[((size_t) k * nil + n) * w.tiles_left + t]);
+          F.W[((size_t) t * nil + n) * no + k] = v;
+          BL.W[((size_t) t * no + k) * nil + n] = v;
+        }
+      for (int n = 0; n < nir; n++)
+        for (int t = 0; t < w.tiles_right; t++) {
+          const float v = (float) (w.norm_right * w.w_right[((size_t) k * nir + n) * w.tiles_right + t]);
+          F.W[(size_t) base_r + ((size_t) t * nir + n) * no + k] = v;
+          BR.W[((size_t) t * no + k) * nir + n] = v;
+        }
+    }
+    std::map<int, std::vector<int>> by_to, by_from;
+    for (size_t c = 0; c < w.collect_to.size(); c++)
+      if (live[w.collect_to[c]]) {
+        by_to[w.collect_to[c]].push_back((int) c);
+        by_from[w.collect_from[c]].push_back((int) c);
+      }
+    for (int f = 0; f < w.n_funcs; f++) {
+      if (!live[f]) continue;
+      const float nof = (float) w.nof[f];
+      F.row_out.push_back(f);
+      F.item_off.push_back((int) F.items.size());
+      F.items.push_back({w.tile_left[f] * nil * no, tL, f, nil, nof});
+      for (int c : by_to[f]) F.items.push_back({base_r + w.tile_right[c] * nir * no, tR, w.collect_from[c], nir, nof});
+      BL.row_out.push_back(f);
+      BL.item_off.push_back((int) BL.items.size());
+      BL.items.push_back({w.tile_left[f] * no * nil, gD, f, no, nof});
+    }
+    for (auto &kv : by_from) {
+      BR.row_out.push_back(kv.first);
+      BR.item_off.push_back((int) BR.items.size());
+      for (int c : kv.second)
+        BR.items.push_back({w.tile_right[c] * no * nir, gD, w.collect_to[c], no, (float) w.nof[w.collect_to[c]]});
+    }
+    const Op f = add(std::move(F));
+    std::vector<Op> a;
+    a.push_back(add(std::move(BL)));
+    a.push_back(add(std::move(BR)));
+    emit(f, a);
+  }
+
+  // CG product with pruned terms: dst[o] = sum c L[l] R[r]
+  void prod(const std::string &name, const CGProduct &p, const std::vector<char> &need, int tL, int tR, int tD, int gL,
+            int gR, int gD)
+  {
+    ProdOp F, BL, BR;
+    F.name = name + ":fwd"; BL.name = name + ":adj_left"; BR.name = name + ":adj_right";
+    F.dst = tD; F.srcA = tL; F.srcB = tR;
+    BL.dst = gL; BL.srcA = gD; BL.srcB = tR; BL.accumulate = true;
+    BR.dst = gR; BR.srcA = gD; BR.srcB = tL; BR.accumulate = true;
+    std::map<int, std::vector<int>> by_o, by_l, by_r;
+    for (size_t t = 0; t < p.cg.size(); t++)
+      if (need[p.m_sum[t]]) {
+        by_o[p.m_sum[t]].push_back((int) t);
+        by_l[p.left[t]].push_back((int) t);
+        by_r[p.right[t]].push_back((int) t);
+      }
+    for (auto &kv : by_o) {
+      F.row_out.push_back(kv.first);
+      F.term_off.push_back((int) F.terms.size());
+      for (int t : kv.second) F.terms.push_back({p.left[t], p.right[t], (float) p.cg[t]});
+    }
+    for (auto &kv : by_l) {
+      BL.row_out.push_back(kv.first);
+      BL.term_off.push_back((int) BL.terms.size());
+      for (int t : kv.second) BL.terms.push_back({p.m_sum[t], p.right[t], (float) p.cg[t]});
+    }
+    for (auto &kv : by_r) {
+      BR.row_out.push_back(kv.first);
+      BR.term_off.push_back((int) BR.terms.size());
+      for (int t : kv.second) BR.terms.push_back({p.m_sum[t], p.left[t], (float) p.cg[t]});
+    }
+    const Op f = add(std::move(F));
+    std::vector<Op> a;
+    a.push_back(add(std::move(BL)));
+    a.push_back(add(std::move(BR)));
+    emit(f, a);
+  }
+
+  // reduce of several sources into one tensor, and one adjoint per source
+  void reduce(const ReduceGroup &R)
+  {
+    MVOp F;
+    F.name = R.name + ":fwd";
+    F.dst = R.t_out;
+    F.n_out = R.n_out;
+    F.elem = R.elem;
+    const int nty = R.elem ? m.n_elements : 1;
+    std::vector<int64_t> base(R.src.size(), 0);
+    int64_t per_type = 0;
+    for (size_t s = 0; s < R.src.size(); s++)
+      if (R.src[s]) {
+        base[s] = per_type;
+        per_type += (int64_t) R.src[s]->w_shape * R.src[s]->n_in * R.n_out;
+      }
+    F.ty_stride = R.elem ? per_type : 0;
+    F.W.assign((size_t) per_type * nty, 0.0f);
+    std::vector<Op> adjoint;
+    for (size_t s = 0; s < R.src.size(); s++) {
+      if (!R.src[s]) continue;
+      const ReduceWeights &w = *R.src[s];
+      const int nin = w.n_in, ws = w.w_shape, no = R.n_out;
+      MVOp B;
+      B.name = R.name + ":adj_src" + std::to_string(s);
+      B.dst = R.src_grad[s];
+      B.n_out = nin;
+      B.accumulate = true;
+      B.elem = R.elem;
+      B.ty_stride = R.elem ? (int64_t) ws * no * nin : 0;
+      B.W.assign((size_t) ws * no * nin * nty, 0.0f);
+      for (int ty = 0; ty < nty; ty++)
+        for (int k = 0; k < no; k++)
+          for (int n = 0; n < nin; n++)
+            for (int t = 0; t < ws; t++) {
+              const size_t off = R.elem ? ((((size_t) ty * no + k) * nin + n) * ws + t) : (((size_t) k * nin + n) * ws + t);
+              const float v = (float) (w.norm * w.W[off]);
+              F.W[(size_t) ty * per_type + base[s] + ((size_t) t * nin + n) * no + k] = v;
+              B.W[(size_t) ty * ws * no * nin + ((size_t) t * no + k) * nin + n] = v;
+            }
+      std::map<int, std::vector<int>> by_ci;
+      for (size_t c = 0; c < w.collect.size(); c++) by_ci[w.collect[c]].push_back((int) c);
+      for (auto &kv : by_ci) {
+        B.row_out.push_back(R.src_row0[s] + kv.first);
+        B.item_off.push_back((int) B.items.size());
+        for (int c : kv.second) B.items.push_back({w.tile[c] * no * nin, R.t_gout, w.fo[c], no, 1.0f});
+      }
+      adjoint.push_back(add(std::move(B)));
+    }
+    for (int fo = 0; fo < R.nfo; fo++) {
+      bool any = false;
+      for (size_t s = 0; s < R.src.size(); s++) {
+        if (!R.src[s]) continue;
+        const ReduceWeights &w = *R.src[s];
+        for (size_t c = 0; c < w.collect.size(); c++)
+          if (w.fo[c] == fo) {
+            if (!any) {
+              F.row_out.push_back(fo);
+              F.item_off.push_back((int) F.items.size());
+              any = true;
+            }
+            F.items.push_back({(int) (base[s] + (int64_t) w.tile[c] * w.n_in * R.n_out), R.src_tensor[s],
+                               R.src_row0[s] + w.collect[c], w.n_in, 1.0f});
+          }
+      }
+    }
+    const Op f = add(std::move(F));
+    emit(f, adjoint);
+  }
+
+  struct ChainTensors {
+    int X0, X1, XX, XX1, XX2, XXX, XXXX;
+    int gX0, gX1, gXX, gXX1, gXX2, gXXX, gXXXX;
+  };
+
+  // the chain X1 .. XXXX of one layer; readers: the reduces that read (X0, XX, XXX, XXXX)
+  ChainTensors chain(const std::string &x, const Chain &c, int tX0, int gX0,
+                     const std::vector<const ReduceWeights *> &readers_XX,
+                     const std::vector<const ReduceWeights *> &readers_XXX,
+                     const std::vector<const ReduceWeights *> &readers_XXXX)
+  {
+    const int n0 = c.n0, nXX = c.pXX.n_out, nXXX = c.pXXX.n_out, nXXXX = c.order4 ? c.pXXXX.n_out : 0;
+    ChainTensors T{};
+    T.X0 = tX0;
+    T.gX0 = gX0;
+    const std::string xx = x + x, xxx = xx + x, xxxx = xxx + x;
+    T.X1 = tensor(x + "1", n0, c.cf);
+    T.XX = tensor(xx, nXX, c.cf);
+    T.XX1 = tensor(xx + "1", nXX, c.cf);
+    T.XXX = tensor(xxx, nXXX, c.cf);
+    T.gX1 = tensor("g" + x + "1", n0, c.cf, true);
+    T.gXX = tensor("g" + xx, nXX, c.cf, true);
+    T.gXX1 = tensor("g" + xx + "1", nXX, c.cf, true);
+    T.gXXX = tensor("g" + xxx, nXXX, c.cf, true);
+    T.XX2 = T.XXXX = T.gXX2 = T.gXXXX = -1;
+    if (c.order4) {
+      T.XX2 = tensor(xx + "2", nXX, c.cf);
+      T.XXXX = tensor(xxxx, nXXXX, c.cf);
+      T.gXX2 = tensor("g" + xx + "2", nXX, c.cf, true);
+      T.gXXXX = tensor("g" + xxxx, nXXXX, c.cf, true);
+    }
+    // liveness, backwards from the reduces
+    auto mark = [](const std::vector<const ReduceWeights *> &rs, std::vector<char> &need) {
+      for (auto *r : rs)
+        if (r)
+          for (int ci : r->collect) need[ci] = 1;
+    };
+    std::vector<char> needXXX(nXXX, 0), needXXXX(std::max(nXXXX, 1), 0), needXX(nXX, 0);
+    mark(readers_XXX, needXXX);
+    mark(readers_XXXX, needXXXX);
+    std::vector<char> liveXX1(nXX, 0), liveXX2(nXX, 0), liveX1(n0, 0);
+    for (size_t t = 0; t < c.pXXX.cg.size(); t++)
+      if (needXXX[c.pXXX.m_sum[t]]) {
+        liveXX1[c.pXXX.left[t]] = 1;
+        if (!c.xxx_right_x0) liveX1[c.pXXX.right[t]] = 1;
+      }
+    if (c.order4)
+      for (size_t t = 0; t < c.pXXXX.cg.size(); t++)
+        if (needXXXX[c.pXXXX.m_sum[t]]) liveXX2[c.pXXXX.left[t]] = liveXX2[c.pXXXX.right[t]] = 1;
+    for (int q = 0; q < nXX; q++) needXX[q] = liveXX1[q] || liveXX2[q];
+    mark(readers_XX, needXX);
+    for (size_t t = 0; t < c.pXX.cg.size(); t++)
+      if (needXX[c.pXX.m_sum[t]]) liveX1[c.pXX.left[t]] = liveX1[c.pXX.right[t]] = 1;
+
+    fc("fc_" + x + "1", c.fc1, liveX1, T.X0, T.X0, T.X1, T.gX0, T.gX0, T.gX1);
+    prod("prod_" + xx, c.pXX, needXX, T.X1, T.X1, T.XX, T.gX1, T.gX1, T.gXX);
+    fc("fc_" + xx + "1", c.fcXX1, liveXX1, T.XX, T.X0, T.XX1, T.gXX, T.gX0, T.gXX1);
+    if (c.order4) fc("fc_" + xx + "2", c.fcXX2, liveXX2, T.XX, T.X0, T.XX2, T.gXX, T.gX0, T.gXX2);
+    const int tR = c.xxx_right_x0 ? T.X0 : T.X1, gR = c.xxx_right_x0 ? T.gX0 : T.gX1;
+    prod("prod_" + xxx, c.pXXX, needXXX, T.XX1, tR, T.XXX, T.gXX1, gR, T.gXXX);
+    if (c.order4) prod("prod_" + xxxx, c.pXXXX, needXXXX, T.XX2, T.XX2, T.XXXX, T.gXX2, T.gXX2, T.gXXXX);
+    return T;
+  }
+
+  ReduceGroup reduce4(const std::string &name, const ReduceWeights *w, const ChainTensors &T, bool order4, int n_out,
+                      int nfo, bool elem, int t_out, int t_gout)
+  {
+    ReduceGroup R;
+    R.name = name;
+    R.src = {&w[0], &w[1], &w[2], order4 ? &w[3] : nullptr};
+    R.src_tensor = {T.X0, T.XX, T.XXX, T.XXXX};
+    R.src_grad = {T.gX0, T.gXX, T.gXXX, T.gXXXX};
+    R.src_row0 = {0, 0, 0, 0};
+    R.n_out = n_out; R.nfo = nfo; R.elem = elem; R.t_out = t_out; R.t_gout = t_gout;
+    return R;
+  }
+};
+
+}    // namespace
+
+ModelPlan build_plan(const GraceModel &m, int spline_n)
+{
+  if (spline_n < 16) throw std::invalid_argument("spline N must be >= 16");
+  ModelPlan P;
+  P.layers = m.layers;
+  P.lmax = m.lmax;
+  const int nl = m.lmax + 1, nlm = nl * nl;
+  P.nlm = nlm;
+  P.n_elements = m.n_elements;
+  P.rcsq.resize((size_t) m.n_elements * m.n_elements);
+  P.rc.resize(P.rcsq.size());
+  for (int a = 0; a < m.n_elements; a++)
+    for (int b = 0; b < m.n_elements; b++) {
+      const double rc = m.pair_cutoff(a, b);
+      P.rc[(size_t) a * m.n_elements + b] = rc;
+      P.rcsq[(size_t) a * m.n_elements + b] = rc * rc;
+      P.rc_max = std::max(P.rc_max, rc);
+    }
+  P.nrho = m.rho_n_out;
+
+  {    // layer 1
+    LayerPlan &L = P.L1;
+    LayerBuilder B{L, m, {}};
+    const Chain &c = m.chain1;
+    L.C = c.c0;
+    L.n_msg = 0;
+    L.radial = build_radial(m, m.rad1, c.c0, spline_n);
+    L.z.assign(m.zA.begin(), m.zA.end());
+    L.tQ = B.tensor("A", nlm, c.c0);
+    L.tGQ = B.tensor("gA", nlm, c.c0, true);
+    std::vector<const ReduceWeights *> rXX{&m.rho[1]}, rXXX{&m.rho[2]}, rXXXX{c.order4 ? &m.rho[3] : nullptr};
+    if (m.layers == 2) {
+      rXX.push_back(&m.I1[1]);
+      rXXX.push_back(&m.I1[2]);
+      rXXXX.push_back(c.order4 ? &m.I1[3] : nullptr);
+    }
+    const auto T = B.chain("A", c, L.tQ, L.tGQ, rXX, rXXX, rXXXX);
+    P.t1_rho = B.tensor("rho", 1, m.rho_n_out);
+    P.t1_grho = B.tensor("grho", 1, m.rho_n_out);    // written by the readout, not zeroed
+    if (m.layers == 2) {
+      const int tI1 = B.tensor("I1", m.nI1, m.i1_out), gI1 = B.tensor("gI1", m.nI1, m.i1_out, true);
+      P.t1_I = B.tensor("I", m.nI, m.cr);
+      P.t1_gI = B.tensor("gI", m.nI, m.cr);    // copied from the per-atom dE/dI rows, not zeroed
+      B.reduce(B.reduce4("I1", m.I1, T, c.order4, m.i1_out, m.nI1, true, tI1, gI1));
+      B.reduce(B.reduce4("rho", m.rho, T, c.order4, m.rho_n_out, 1, true, P.t1_rho, P.t1_grho));
+      ReduceGroup R;
+      R.name = "I";
+      R.src = {&m.I_from_I1};
+      R.src_tensor = {tI1};
+      R.src_grad = {gI1};
+      R.src_row0 = {0};
+      R.n_out = m.cr; R.nfo = m.nI; R.elem = false; R.t_out = P.t1_I; R.t_gout = P.t1_gI;
+      B.reduce(R);
+    } else {
+      B.reduce(B.reduce4("rho", m.rho, T, c.order4, m.rho_n_out, 1, true, P.t1_rho, P.t1_grho));
+    }
+    B.finish();
+  }
+  if (m.layers == 2) {
+    LayerPlan &L = P.L2;
+    LayerBuilder B{L, m, {}};
+    const Chain &c = m.chain2;
+    P.nI = m.nI;
+    P.cr = m.cr;
+    L.C = m.cr;
+    L.n_msg = m.nI;
+    L.radial = build_radial(m, m.rad2, m.cr, spline_n);
+    L.z.assign(m.zB0.begin(), m.zB0.end());
+    // bond sum Q[(I, lm)] = sum_j Y_lm R1[l] msg_I, I < nI the neighbour's message functions, I = nI the chemical
+    // weight (B0): the dense form of the YI pairs (libgrace/src/fused_2l.cpp:229-276)
+    const int nq = (m.nI + 1) * nlm;
+    L.tQ = B.tensor("Q", nq, m.cr);
+    L.tGQ = B.tensor("gQ", nq, m.cr, true);
+    const int tYI = B.tensor("YI", m.yi.n_out, m.cr), gYI = B.tensor("gYI", m.yi.n_out, m.cr, true);
+    {
+      CGProduct y;    // YI[o] = inv_avg sum_t cg_t Q[I_t nlm + y_t]
+      y.present = true;
+      y.n_out = m.yi.n_out;
+      for (size_t t = 0; t < m.yi.cg.size(); t++) {
+        y.left.push_back(m.yi.i[t] * nlm + m.yi.y[t]);
+        y.right.push_back(0);
+        y.m_sum.push_back(m.yi.m_sum[t]);
+        y.cg.push_back(m.yi.cg[t] * m.yi.inv_avg);
+      }
+      ProdOp F, A;
+      F.name = "YI:fwd"; A.name = "YI:adj";
+      F.dst = tYI; F.srcA = L.tQ; F.srcB = -1;
+      A.dst = L.tGQ; A.srcA = gYI; A.srcB = -1; A.accumulate = true;
+      std::map<int, std::vector<int>> by_o, by_l;
+      for (size_t t = 0; t < y.cg.size(); t++) {
+        by_o[y.m_sum[t]].push_back((int) t);
+        by_l[y.left[t]].push_back((int) t);
+      }
+      for (auto &kv : by_o) {
+        F.row_out.push_back(kv.first);
+        F.term_off.push_back((int) F.terms.size());
+        for (int t : kv.second) F.terms.push_back({y.left[t], 0, (float) y.cg[t]});
+      }
+      for (auto &kv : by_l) {
+        A.row_out.push_back(kv.first);
+        A.term_off.push_back((int) A.terms.size());
+        for (int t : kv.second) A.terms.push_back({y.m_sum[t], 0, (float) y.cg[t]});
+      }
+      const Op f = B.add(std::move(F));
+      B.emit(f, {B.add(std::move(A))});
+    }
+    const int tB = B.tensor("B", m.nB, c.c0), gB = B.tensor("gB", m.nB, c.c0, true);
+    {
+      ReduceGroup R;
+      R.name = "B";
+      R.src = {&m.B_from_YI, &m.B_from_B0};
+      R.src_tensor = {tYI, L.tQ};
+      R.src_grad = {gYI, L.tGQ};
+      R.src_row0 = {0, m.nI * nlm};
+      R.n_out = c.c0; R.nfo = m.nB; R.elem = false; R.t_out = tB; R.t_gout = gB;
+      B.reduce(R);
+    }
+    const auto T = B.chain("B", c, tB, gB, {&m.I2[1]}, {&m.I2[2]}, {c.order4 ? &m.I2[3] : nullptr});
+    P.t2_I2 = B.tensor("I2", 1, m.nI2);
+    P.t2_gI2 = B.tensor("gI2", 1, m.nI2);
+    B.reduce(B.reduce4("I2", m.I2, T, c.order4, m.nI2, 1, true, P.t2_I2, P.t2_gI2));
+    B.finish();
+  }
+  // readout
+  for (const auto &Lr : m.energy_mlp) {
+    P.eW.insert(P.eW.end(), Lr.W.begin(), Lr.W.end());
+    P.e_nin.push_back(Lr.n_in);
+    P.e_nout.push_back(Lr.n_out);
+    P.e_norm.push_back(Lr.norm);
+  }
+  P.e_act = m.energy_activation;
+  P.e_ln = m.energy_ln;
+  P.rms = m.rms;
+  P.out_scale = m.output_scale;
+  P.shift = m.shift;
+  P.lnI = m.lnI;
+  P.ln0 = m.ln0;
+  for (const LayerPlan *L : {&P.L1, &P.L2})
+    for (const auto &o : L->mv) P.dense_flops_per_atom += o.flops_per_atom();
+  return P;
+}
+
+}    // namespace gb

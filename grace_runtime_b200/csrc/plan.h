@@ -1,0 +1,112 @@
+// Execution plan of a model: the dense per-atom network of each layer as a list of two kinds of table-driven
+// operations on [function][atom][channel] tensors, with the pruning of outputs nothing reads that the reference
+// drivers apply (libgrace/src/fused_1l.cpp:176-214, libgrace/src/fused_2l.cpp:292-351), plus the radial tables.
+//
+//   MV   out[row] (+)= sum_items scale * M_item^T x[item.src][item.irow]        (FC, reduce and their adjoints)
+//   PROD out[row] (+)= sum_terms coef * A[term.a] * B[term.b]  (channel-wise)    (CG products, YI, their adjoints)
+//
+// Weights are fp32 with the norms folded in (as the reference packs them: libgrace/include/grace/fused_cpu.h:1131-1142,
+// 1229-1243).
+#pragma once
+
+#include "model.h"
+
+#include <string>
+#include <vector>
+
+namespace gb {
+
+struct TensorSpec {
+  std::string name;
+  int nfuncs = 0, channels = 0;
+  bool grad = false;    // zeroed before the reverse pass of a chunk
+};
+
+struct MVItem {
+  int mat;      // offset (floats) of the [n_in][n_out] matrix in the weight buffer (within the element's block)
+  int src;      // tensor id of the input
+  int irow;     // function of the input
+  int n_in;
+  float scale;
+};
+
+struct MVOp {
+  std::string name;
+  int dst = -1;
+  int n_out = 0;
+  bool accumulate = false;
+  bool elem = false;           // weights per central element: matrix at mu * ty_stride + item.mat
+  int64_t ty_stride = 0;
+  std::vector<int> row_out;    // output function of each row
+  std::vector<int> item_off;   // rows + 1
+  std::vector<MVItem> items;
+  std::vector<float> W;
+  double flops_per_atom() const;
+};
+
+struct ProdTerm {
+  int a, b;
+  float coef;
+};
+
+struct ProdOp {
+  std::string name;
+  int dst = -1, srcA = -1, srcB = -1;    // srcB < 0: out = sum coef * A[a]
+  bool accumulate = false;
+  std::vector<int> row_out;
+  std::vector<int> term_off;
+  std::vector<ProdTerm> terms;
+};
+
+struct Op {
+  enum Kind { MV, PROD } kind;
+  int index;    // into mv / prod
+};
+
+// one direction (forward or reverse) of the dense network of a layer
+struct Program {
+  std::vector<Op> ops;
+};
+
+struct RadialTable {
+  int N = 0, nl = 0, C = 0;
+  std::vector<float> tab;    // [N][4][nl][C]: cubic Hermite coefficients per interval
+};
+
+struct LayerPlan {
+  std::vector<TensorSpec> tensors;
+  std::vector<MVOp> mv;
+  std::vector<ProdOp> prod;
+  Program fwd, bwd;
+  int tQ = -1, tGQ = -1;    // the bond-sum tensor written by the forward bond kernel and its gradient
+  int n_msg = 0;            // message functions of the neighbours coupled in (layer 2: I_n_funcs; layer 1: 0)
+  int C = 0;                // channels of the bond sum
+  RadialTable radial;
+  std::vector<float> z;     // [n_elements][C] chemical weight of the neighbour (the virtual message function)
+};
+
+struct ModelPlan {
+  int layers = 0, lmax = 0, nlm = 0, n_elements = 0;
+  std::vector<double> rcsq;     // [n_elements][n_elements] squared pair cutoffs
+  std::vector<double> rc;       // [n_elements][n_elements]
+  double rc_max = 0.0;
+  LayerPlan L1, L2;
+  // tensors of the plans the drivers address by name
+  int t1_rho = -1, t1_grho = -1, t1_I = -1, t1_gI = -1;
+  int t2_I2 = -1, t2_gI2 = -1;
+  int nrho = 0, nI = 0, cr = 0;
+  // readout
+  std::vector<double> eW;       // energy MLP weights, layers concatenated, [n_in][n_out] each
+  std::vector<int> e_nin, e_nout;
+  std::vector<double> e_norm;
+  int e_act = 0;
+  bool e_ln = false, rms = true;
+  double out_scale = 1.0;
+  std::vector<double> shift;    // [n_elements]
+  std::vector<double> lnI, ln0;
+  double dense_flops_per_atom = 0.0;    // forward + reverse MV flops (diagnostics)
+};
+
+ModelPlan build_plan(const GraceModel &m, int spline_n);
+
+}    // namespace gb

@@ -1,0 +1,128 @@
+/* grace_b200 - C ABI of the B200-native GRACE evaluation backend (libgrace_b200.so).
+ *
+ * Every entry point replaces one member of the reference's GPU backend interface `namespace grace_runtime_kk`
+ * (python/kk/kk_api.h:14-156, "ABI 7"), which the reference binds to Python in python/kk/kk_module.cpp:200-275.
+ * Argument meaning, array conventions and error classes are the reference's:
+ *   - atom types are 1-based indices into the species list given at create time;
+ *   - positions [n][3] and cell [3][3] (rows = cell vectors, full rank; open directions padded by the caller) are
+ *     fp64; pbc is one byte per direction;
+ *   - forces [n][3] in the caller's atom order; virial[6] = sum over bonds (x_i - x_j) (x) f_i in the order
+ *     xx yy zz xy xz yz; stress = -virial[[0,1,2,5,4,3]] / V is left to the caller as in the reference
+ *     (python/grace_runtime/calculator.py:155-157);
+ *   - outputs are written, never accumulated; the caller owns inputs and outputs.
+ * Functions return a status: 0 ok, 1 invalid argument (reference: std::invalid_argument / ValueError), 2 runtime or
+ * device error (std::runtime_error), 3 out of device memory, 4 unsupported model or feature.  The message of the last
+ * failure of the calling thread is grace_last_error().  Nothing here aborts or traps.  All device work of a process
+ * is serialised internally (kk_core.cpp:58-63, 805-806), so any host thread may call.
+ * There is no CPU fallback: every compute call runs the CUDA kernels of this library on the initialised device.
+ */
+#ifndef GRACE_B200_H
+#define GRACE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)    /* the library is built with hidden visibility: only this ABI is exported */
+#endif
+
+#define GRACE_OK 0
+#define GRACE_INVALID_ARGUMENT 1
+#define GRACE_RUNTIME_ERROR 2
+#define GRACE_OUT_OF_MEMORY 3
+#define GRACE_UNSUPPORTED 4
+
+/* the integer the Python side compares with its own (python/grace_runtime/_gpu.py:18) */
+#define GRACE_B200_ABI 7
+
+/* compute flags (kk_api.h:84-86: energies, uq, energy_only) */
+#define GRACE_FLAG_ENERGIES 1     /* also write per-atom energies */
+#define GRACE_FLAG_ENERGY_ONLY 2  /* no reverse pass: forces and virial are not written */
+#define GRACE_FLAG_UQ 4           /* rejected with GRACE_UNSUPPORTED: no UQ head in this backend */
+
+typedef struct grace_model grace_model;
+typedef struct grace_system grace_system;
+typedef struct grace_batch grace_batch;
+
+/* ---- process / device (kk_api.h:16-33) ---- */
+int grace_initialize(int device);              /* initialize(device): one GPU per process */
+int grace_finalize(void);                      /* finalize(): releases the device buffers of every live object */
+int grace_initialized(void);                   /* initialized() */
+int grace_device(void);                        /* device() */
+const char *grace_arch(void);                  /* arch(): "sm100" */
+const char *grace_platform(void);              /* platform(): "cuda" */
+const char *grace_blas(void);                  /* blas(): "" (no GEMM library on the path) */
+int grace_abi(void);                           /* the module attribute ABI */
+int grace_memory_info(size_t *free_bytes, size_t *total_bytes);   /* memory_info() */
+/* tests: the nth device allocation from now on whose label contains `label` fails as out of memory (nth <= 0: off) */
+int grace_debug_fail_alloc(const char *label, int nth);           /* debug_fail_alloc(label, nth) */
+/* tests: the nth kernel launch check from now on reports an out-of-memory launch (0: off) */
+int grace_debug_fail_launch(int nth);                             /* debug_fail_launch(nth) */
+const char *grace_last_error(void);            /* what() of the exception the reference would have thrown */
+/* kernels launched by this library since the process started (diagnostics; no counterpart in the reference) */
+uint64_t grace_kernel_launches(void);
+
+/* ---- Model (kk_api.h:51-64): a loaded GRACE-1L / GRACE-2L kokkos.npz ---- */
+/* spline: intervals of the radial cubic Hermite tables (reference default 1024; >= 16) */
+int grace_model_load(const char *path, int spline, grace_model **out);   /* Model(path, spline) */
+int grace_model_layers(const grace_model *m);                            /* layers(): 1 or 2 */
+int grace_model_has_uq(const grace_model *m);                            /* has_uq(): 0 */
+int grace_model_n_elements(const grace_model *m);                        /* len(element_names()) */
+const char *grace_model_element_name(const grace_model *m, int i);       /* element_names()[i] */
+int64_t grace_model_engine_setups(const grace_model *m);                 /* engine_setups() */
+void grace_model_free(grace_model *m);
+
+/* ---- System (kk_api.h:68-90): one structure, neighbour list with a Verlet skin kept on the device ---- */
+/* chunksize: atoms per engine pass (0: all atoms in one pass; < 0: chosen from the free device memory) */
+int grace_system_create(const grace_model *m, const char *const *species, int n_species, double skin, int spline,
+                        int chunksize, grace_system **out);              /* System(model, species, skin, spline, chunk) */
+double grace_system_cutoff(const grace_system *s);                        /* cutoff() */
+/* System::compute: host arrays in, host arrays out.  energy [1]; virial6 [6], forces [n][3] (skipped with
+ * GRACE_FLAG_ENERGY_ONLY); energies [n] (with GRACE_FLAG_ENERGIES).  Null output pointers are skipped. */
+int grace_system_compute(grace_system *s, int n, const int32_t *types, const double *pos, const double *cell,
+                         const uint8_t *pbc, int flags, double *energy, double *virial6, double *forces,
+                         double *energies);
+/* the same with device pointers for types, positions and every output (cell and pbc stay on the host); the
+ * single-structure counterpart of Batch::compute_device (kk_api.h:139-145) */
+int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, const double *d_pos,
+                                const double *cell, const uint8_t *pbc, int flags, double *d_energy,
+                                double *d_virial6, double *d_forces, double *d_energies);
+int64_t grace_system_rebuilds(const grace_system *s);                     /* rebuilds() */
+int grace_system_chunksize(const grace_system *s);                        /* chunksize() */
+int grace_system_release_buffers(grace_system *s);                        /* release_device_buffers() */
+/* device milliseconds of the stages of the last compute (CUDA events): [0] neighbour list, [1] bond geometry,
+ * [2] forward, [3] reverse, [4] total; diagnostics of this backend (the reference exposes Batch::host_seconds) */
+int grace_system_stage_ms(const grace_system *s, double *ms5);
+void grace_system_free(grace_system *s);
+
+/* ---- Batch (kk_api.h:92-156): many structures per engine pass ---- */
+int grace_batch_create(const grace_model *m, const char *const *species, int n_species, int spline, int chunksize,
+                       grace_batch **out);                                /* Batch(model, species, spline, chunk) */
+double grace_batch_cutoff(const grace_batch *b);
+/* Batch::compute: natoms [nsys]; types [ntot]; pos [ntot][3]; cell [nsys][3][3]; pbc [nsys][3]; max_nall: atoms per
+ * engine pass (whole structures per pass; <= 0: the reference default 2^21).  energy [nsys]; virial [nsys][6];
+ * forces [ntot][3]; energies [ntot] */
+int grace_batch_compute(grace_batch *b, int nsys, const int32_t *natoms, int64_t ntot, const int32_t *types,
+                        const double *pos, const double *cell, const uint8_t *pbc, int flags, int64_t max_nall,
+                        double *energy, double *virial, double *forces, double *energies);
+/* Batch::compute_device: types, pos and the outputs are device pointers of the initialised GPU */
+int grace_batch_compute_device(grace_batch *b, int nsys, const int32_t *natoms, int64_t ntot, const int32_t *d_types,
+                               const double *d_pos, const double *cell, const uint8_t *pbc, int flags,
+                               int64_t max_nall, double *d_energy, double *d_virial, double *d_forces,
+                               double *d_energies);
+int grace_batch_passes(const grace_batch *b);                             /* passes() */
+double grace_batch_host_seconds(const grace_batch *b);                    /* host_seconds() */
+int grace_batch_set_keep_buffers(grace_batch *b, int on);                 /* set_keep_buffers(on) */
+int grace_batch_release_buffers(grace_batch *b);                          /* release_device_buffers() */
+void grace_batch_free(grace_batch *b);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,262 @@
+"""Parity of the CUDA path, called through the C ABI, against the committed golden vectors (TensorFlow fp64 and the
+reference CPU drivers), the numpy oracle and - where it travelled - the compiled reference; plus the size-independent
+properties the domain offers (symmetries, energy conservation of the forces, replication)."""
+import numpy as np
+import pytest
+
+from conftest import (EXTRA_CELLS, F32_MODELS, REF_TOL, TF_CELLS, TF_MODELS, TOL_E, TOL_F, TOL_S, compare_tf, model_path,
+                      stress_of)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(backend):
+    return {}
+
+
+def _model(backend, models, name):
+    if name not in models:
+        models[name] = backend.Model(model_path(name))
+    return models[name]
+
+
+def _compute(backend, model, c, **kw):
+    s = backend.System(model, c["species"], skin=kw.pop("skin", 0.5), chunksize=kw.pop("chunksize", -1))
+    return s.compute(c["types"], c["positions"], c["cell"], c["pbc"], energies=True, **kw)
+
+
+@pytest.mark.parametrize("cell", TF_CELLS)
+@pytest.mark.parametrize("name", TF_MODELS)
+def test_matches_tf_fp64_golden(backend, models, cells, tf_golden, name, cell):
+    """the reference's own golden test (python/tests/test_order3_tf.py) with its thresholds"""
+    c = cells.get(cell)
+    r = _compute(backend, _model(backend, models, name), c)
+    d = compare_tf(r, tf_golden, f"{name}/{cell}", c)
+    for q, v in d.items():
+        assert v < (2e-6 if q == "energy" and c["n"] < 10 else REF_TOL[q]), (q, v)
+
+
+@pytest.mark.parametrize("cell", TF_CELLS + EXTRA_CELLS)
+@pytest.mark.parametrize("name", TF_MODELS + F32_MODELS)
+def test_matches_reference_cpu_golden(backend, models, cells, ref_golden, name, cell):
+    """against frozen outputs of the reference CPU drivers: thresholds the reference accepts between its GPU and CPU
+    calculators (python/tests/test_gpu_calculator.py:74-76)"""
+    c = cells.get(cell)
+    r = _compute(backend, _model(backend, models, name), c)
+    k = f"{name}/{cell}"
+    assert abs(r["energy"] - ref_golden[f"{k}/energy"]) / c["n"] < 1e-5
+    assert np.abs(r["forces"] - ref_golden[f"{k}/forces"]).max() < 5e-5
+    assert np.abs(r["energies"] - ref_golden[f"{k}/energies"]).max() < 1e-5
+    ds = np.abs(stress_of(r["virial"], c["volume"]) - stress_of(ref_golden[f"{k}/virial"], c["volume"])).max()
+    assert ds < 1e-6
+
+
+def _config_case(tmp_path_factory, cfg, lattice, a, reps, nsp, sigma, seed):
+    from grace_runtime_b200 import modelgen, structures
+    els = modelgen._subset(11, nsp)
+    path = str(tmp_path_factory.mktemp("cfg") / f"{cfg}.npz")
+    modelgen.write_config_model(path, cfg, els, seed=seed)
+    types, pos, cell, pbc = structures.crystal(lattice, a, reps, n_species=nsp, sigma=sigma, seed=seed + 1)
+    return path, els, dict(species=els, types=types, positions=pos, cell=cell, pbc=pbc, n=len(types),
+                           volume=abs(np.linalg.det(cell)))
+
+
+@pytest.mark.parametrize("cfg,lattice,a,reps,nsp,sigma", [("1l", "bcc", 3.165, (4, 4, 4), 1, 0.05),
+                                                           ("1l", "bcc", 3.2, (4, 4, 5), 4, 0.05),
+                                                           ("2l", "fcc", 3.6, (3, 3, 3), 3, 0.08)])
+def test_benchmark_architectures_match_oracle(backend, tmp_path_factory, cfg, lattice, a, reps, nsp, sigma):
+    """scaled-down copies of the benchmark configurations (same architecture, lattice, displacements) against the
+    numpy oracle (exact radial MLP, fp64) within the stated tolerances"""
+    from oracle.grace_oracle import GraceOracle
+    path, els, c = _config_case(tmp_path_factory, cfg, lattice, a, reps, nsp, sigma, seed=5)
+    r = _compute(backend, backend.Model(path), c)
+    o = GraceOracle(path).compute(els, c["types"], c["positions"], c["cell"], c["pbc"])
+    assert abs(r["energy"] - o["energy"]) / c["n"] < TOL_E
+    assert np.abs(r["forces"] - o["forces"]).max() < TOL_F
+    assert np.abs(r["virial"] - o["virial"]).max() / c["volume"] < TOL_S
+    assert np.abs(r["energies"] - o["energies"]).max() < TOL_E
+
+
+def test_matches_compiled_reference_live(backend, tmp_path_factory):
+    """the reference's own CPU drivers (oracle/_ref), when the prebuilt library is present, on a 2L benchmark-shaped
+    case with larger displacements"""
+    from oracle import refcpu
+    if not refcpu.available():
+        pytest.skip("oracle/_ref is not built")
+    path, els, c = _config_case(tmp_path_factory, "2l", "fcc", 3.6, (3, 3, 4), 3, 0.15, seed=9)
+    r = _compute(backend, backend.Model(path), c)
+    ref = refcpu.RefModel(path, els).compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    assert abs(r["energy"] - ref["energy"]) / c["n"] < TOL_E
+    assert np.abs(r["forces"] - ref["forces"]).max() < TOL_F
+    assert np.abs(r["virial"] - ref["virial"]).max() / c["volume"] < TOL_S
+
+
+@pytest.mark.parametrize("name", ["grace_1l_order3", "grace_2l_order3"])
+def test_chunked_equals_one_pass(backend, models, cells, name):
+    """python/tests/test_gpu_chunk.py:49,101-102: 2e-6 eV/atom, 2e-5 eV/A"""
+    c = cells.get("WMo54")
+    m = _model(backend, models, name)
+    a = _compute(backend, m, c, chunksize=0)
+    b = _compute(backend, m, c, chunksize=16)
+    assert abs(a["energy"] - b["energy"]) / c["n"] < 2e-6
+    assert np.abs(a["forces"] - b["forces"]).max() < 2e-5
+    assert np.abs(a["virial"] - b["virial"]).max() < 2e-5 * c["n"]
+
+
+@pytest.mark.parametrize("name", ["grace_1l_order3", "grace_2l_order3"])
+def test_energy_only(backend, models, cells, name):
+    c = cells.get("W54")
+    m = _model(backend, models, name)
+    a = _compute(backend, m, c)
+    s = backend.System(m, c["species"])
+    b = s.compute(c["types"], c["positions"], c["cell"], c["pbc"], energy_only=True)
+    assert "forces" not in b and "virial" not in b
+    assert abs(a["energy"] - b["energy"]) < 1e-9 * max(1.0, abs(a["energy"]))
+
+
+@pytest.mark.parametrize("name", ["grace_1l_order3", "grace_2l_order3"])
+def test_deterministic_and_symmetric(backend, models, cells, name):
+    c = cells.get("slab36")
+    m = _model(backend, models, name)
+    a = _compute(backend, m, c)
+    b = _compute(backend, m, c)
+    assert a["energy"] == b["energy"]
+    if "_1l_" in name:      # no atomics anywhere on the GRACE-1L path: bit-identical forces
+        assert np.array_equal(a["forces"], b["forces"])
+    assert np.abs(a["forces"].sum(0)).max() < 1e-5          # Newton's third law
+    # translation along a periodic direction and permutation of the atoms
+    shift = np.array([1.234, -7.5, 0.0])
+    perm = np.random.default_rng(1).permutation(c["n"])
+    c2 = dict(c, positions=(c["positions"] + shift)[perm], types=c["types"][perm])
+    p = _compute(backend, m, c2)
+    assert abs(p["energy"] - a["energy"]) / c["n"] < 2e-6
+    assert np.abs(p["forces"] - a["forces"][perm]).max() < 2e-5
+    # rotation of the whole structure (cell and positions)
+    th = 0.7
+    R = np.array([[np.cos(th), -np.sin(th), 0], [np.sin(th), np.cos(th), 0], [0, 0, 1.0]])
+    c3 = dict(c, positions=c["positions"] @ R.T, cell=c["cell"] @ R.T)
+    q = _compute(backend, m, c3)
+    assert abs(q["energy"] - a["energy"]) / c["n"] < 2e-6
+    assert np.abs(q["forces"] - a["forces"] @ R.T).max() < 2e-5
+
+
+@pytest.mark.parametrize("name", ["grace_1l_small", "grace_2l_l3"])
+def test_forces_are_minus_energy_gradient(backend, models, cells, name):
+    c = cells.get("tri9")
+    m = _model(backend, models, name)
+    s = backend.System(m, c["species"], skin=0.5)
+    f = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])["forces"]
+    h = 2e-3
+    for (i, d) in [(0, 0), (4, 1), (8, 2)]:
+        p = c["positions"].copy(); p[i, d] += h
+        q = c["positions"].copy(); q[i, d] -= h
+        ep = s.compute(c["types"], p, c["cell"], c["pbc"], energy_only=True)["energy"]
+        em = s.compute(c["types"], q, c["cell"], c["pbc"], energy_only=True)["energy"]
+        assert abs(-(ep - em) / (2 * h) - f[i, d]) < 2e-3 * max(1.0, abs(f[i, d]))
+
+
+def test_neighbor_list_reuse_and_rebuild(backend, models, cells):
+    """Verlet skin: reused while no atom moved more than skin / 2, rebuilt when one did or the types / cell change
+    (python/kk/kk_core.cpp:691-708); results do not depend on it"""
+    c = cells.get("WMo54")
+    m = _model(backend, models, "grace_1l_order3")
+    s = backend.System(m, c["species"], skin=0.5)
+    r0 = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    assert s.rebuilds == 1
+    rng = np.random.default_rng(3)
+    p1 = c["positions"] + 0.1 * (rng.random(c["positions"].shape) - 0.5)       # < skin / 2
+    r1 = s.compute(c["types"], p1, c["cell"], c["pbc"])
+    assert s.rebuilds == 1
+    fresh = backend.System(m, c["species"], skin=0.0).compute(c["types"], p1, c["cell"], c["pbc"])
+    assert abs(r1["energy"] - fresh["energy"]) / c["n"] < 2e-6
+    assert np.abs(r1["forces"] - fresh["forces"]).max() < 2e-5
+    p2 = p1.copy(); p2[5] += [0.4, 0.0, 0.0]                                   # > skin / 2
+    s.compute(c["types"], p2, c["cell"], c["pbc"])
+    assert s.rebuilds == 2
+    t2 = c["types"].copy(); t2[0] = 3 - t2[0]
+    s.compute(t2, p2, c["cell"], c["pbc"])
+    assert s.rebuilds == 3
+    s.compute(t2, p2, c["cell"] * 1.01, c["pbc"])
+    assert s.rebuilds == 4
+    assert r0["energy"] != r1["energy"]
+
+
+def test_batch_equals_single(backend, models, cells):
+    """python/tests/test_gpu_batch.py:85-92: 2e-6 eV/atom, 2e-5 eV/A, virial / n 2e-5"""
+    for name in ["grace_1l_order3", "grace_2l_order3"]:
+        m = _model(backend, models, name)
+        cs = [cells.get(k) for k in ["W54", "tri9", "WMo54", "slab36", "atom1", "W2tri"]]
+        species = ["Mo", "W"]
+        def tt(c):   # types of the two-species batch
+            return np.array([species.index(c["species"][t - 1]) + 1 for t in c["types"]], dtype=np.int32)
+        natoms = np.array([c["n"] for c in cs], dtype=np.int32)
+        types = np.concatenate([tt(c) for c in cs])
+        pos = np.concatenate([c["positions"] for c in cs])
+        cell = np.stack([c["cell"] for c in cs])
+        pbc = np.stack([c["pbc"] for c in cs])
+        b = backend.Batch(m, species)
+        for max_nall in (1 << 21, 60):       # one pass; several passes of whole structures
+            r = b.compute(natoms, types, pos, cell, pbc, energies=True, max_nall=max_nall)
+            assert b.passes == (1 if max_nall > 1000 else 5)
+            at = 0
+            for q, c in enumerate(cs):
+                one = _compute(backend, m, c, skin=0.0)
+                assert abs(r["energy"][q] - one["energy"]) / c["n"] < 2e-6
+                assert np.abs(r["forces"][at:at + c["n"]] - one["forces"]).max() < 2e-5
+                assert np.abs(r["virial"][q] - one["virial"]).max() / c["n"] < 2e-5
+                assert np.abs(r["energies"][at:at + c["n"]] - one["energies"]).max() < 2e-6
+                at += c["n"]
+
+
+def test_replicated_cell_scales(backend, models, cells):
+    """2 x 2 x 2 copies of a cell give 8 x the energy and the same forces (tests/kk/test_kk_large.cpp:1-8)"""
+    c = cells.get("WMo54")
+    for name in ["grace_1l_order3", "grace_2l_order3"]:
+        m = _model(backend, models, name)
+        a = _compute(backend, m, c)
+        reps = [(i, j, k) for i in range(2) for j in range(2) for k in range(2)]
+        pos = np.concatenate([c["positions"] + np.array(r) @ c["cell"] for r in reps])
+        big = dict(c, positions=pos, types=np.tile(c["types"], 8), cell=2 * c["cell"], n=8 * c["n"])
+        b = _compute(backend, m, big, chunksize=100)
+        assert abs(b["energy"] - 8 * a["energy"]) / big["n"] < 2e-6
+        assert np.abs(b["forces"] - np.tile(a["forces"], (8, 1))).max() < 2e-5
+        assert np.abs(b["virial"] - 8 * a["virial"]).max() / big["n"] < 2e-5
+
+
+def test_errors(backend, models, cells):
+    c = cells.get("W54")
+    m = _model(backend, models, "grace_1l_order3")
+    with pytest.raises(ValueError, match="not in the model"):
+        backend.System(m, ["Xx"])
+    s = backend.System(m, ["W"])
+    with pytest.raises(ValueError, match="types must be"):
+        s.compute(c["types"] + 1, c["positions"], c["cell"], c["pbc"])
+    with pytest.raises(ValueError, match="full-rank"):
+        s.compute(c["types"], c["positions"], np.zeros((3, 3)), c["pbc"])
+    p = c["positions"].copy(); p[1] = p[0]
+    with pytest.raises(ValueError, match="same position"):
+        s.compute(c["types"], p, c["cell"], c["pbc"])
+    with pytest.raises(RuntimeError):
+        s.compute(c["types"], c["positions"], c["cell"], c["pbc"], uq=True)
+    r = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])       # usable after the failures
+    assert np.isfinite(r["energy"])
+    e = s.compute(np.zeros(0, dtype=np.int32), np.zeros((0, 3)), c["cell"], c["pbc"])
+    assert e["energy"] == 0.0 and e["forces"].shape == (0, 3)
+
+
+def test_injected_failures_recover(backend, models, cells):
+    """host-side fault injection (python/kk/kk_core.cpp:128-141,187-195): a failed allocation or launch halves the
+    pass and the call still succeeds; nothing faults the GPU"""
+    c = cells.get("WMo54")
+    m = _model(backend, models, "grace_2l_order3")
+    ok = _compute(backend, m, c)
+    s = backend.System(m, c["species"], chunksize=-1)
+    backend._debug_fail_alloc("work:", 1)
+    r = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    backend._debug_fail_alloc("", 0)
+    assert abs(r["energy"] - ok["energy"]) / c["n"] < 2e-6
+    backend._debug_fail_launch(3)
+    r = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    backend._debug_fail_launch(0)
+    assert np.abs(r["forces"] - ok["forces"]).max() < 2e-5
