@@ -37,6 +37,8 @@ SIGNATURES = {
     "grace_debug_fail_launch": (_I, [_I]),
     "grace_last_error": (C.c_char_p, []),
     "grace_kernel_launches": (C.c_uint64, []),
+    "grace_profile_enable": (_I, [_I]),
+    "grace_profile_report": (_I, [_P, C.c_size_t]),
     "grace_model_load": (_I, [C.c_char_p, _I, _P]),
     "grace_model_layers": (_I, [_P]),
     "grace_model_has_uq": (_I, [_P]),
@@ -147,6 +149,22 @@ def memory_info():
 
 def kernel_launches():
     return int(load_library().grace_kernel_launches())
+
+
+def profile_enable(on=True):
+    """CUDA events around every kernel launch of the library from now on (off: drop them)."""
+    _check(load_library().grace_profile_enable(int(bool(on))))
+
+
+def profile_report():
+    """{kernel name: (launches, total device ms)} since profile_enable(True)."""
+    buf = C.create_string_buffer(1 << 16)
+    _check(load_library().grace_profile_report(buf, len(buf)))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.rsplit(" ", 2)
+        out[name] = (int(n), float(ms))
+    return out
 
 
 def _debug_fail_alloc(label, nth):

@@ -126,6 +126,25 @@ int grace_abi(void) { return GRACE_B200_ABI; }
 const char *grace_last_error(void) { return g_error.c_str(); }
 uint64_t grace_kernel_launches(void) { return dev().launches; }
 
+int grace_profile_enable(int on)
+{
+  return guarded([&] {
+    require_initialized();
+    profile_enable(on != 0);
+  });
+}
+
+int grace_profile_report(char *buf, size_t len)
+{
+  return guarded([&] {
+    if (!buf || len == 0) throw InvalidArgument("buf must be given");
+    const std::string r = profile_report();
+    const size_t n = std::min(len - 1, r.size());
+    std::memcpy(buf, r.data(), n);
+    buf[n] = 0;
+  });
+}
+
 int grace_memory_info(size_t *free_bytes, size_t *total_bytes)
 {
   return guarded([&] {

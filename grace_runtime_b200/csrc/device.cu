@@ -31,8 +31,57 @@ void cuda_check(cudaError_t e, const char *what)
   throw DeviceError(msg);
 }
 
+namespace {
+struct ProfSpan { const char *name; cudaEvent_t a, b; };
+bool g_prof_on = false;
+std::vector<ProfSpan> g_prof;
+std::vector<cudaEvent_t> g_prof_pool;
+size_t g_prof_used = 0;
+cudaEvent_t prof_event()
+{
+  if (g_prof_used == g_prof_pool.size()) {
+    cudaEvent_t e;
+    GB_CUDA(cudaEventCreate(&e));
+    g_prof_pool.push_back(e);
+  }
+  return g_prof_pool[g_prof_used++];
+}
+}    // namespace
+
+void profile_enable(bool on)
+{
+  g_prof_on = on;
+  g_prof.clear();
+  g_prof_used = 0;
+}
+
+std::string profile_report()
+{
+  if (g_dev.initialized) cudaStreamSynchronize(g_dev.stream);
+  std::map<std::string, std::pair<long long, double>> acc;
+  for (const auto &s : g_prof) {
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, s.a, s.b) != cudaSuccess) continue;
+    auto &e = acc[s.name];
+    e.first++;
+    e.second += ms;
+  }
+  std::string out;
+  for (const auto &kv : acc) out += kv.first + " " + std::to_string(kv.second.first) + " " + std::to_string(kv.second.second) + "\n";
+  return out;
+}
+
+void before_launch(const char *name)
+{
+  if (!g_prof_on) return;
+  ProfSpan s{name, prof_event(), prof_event()};
+  cudaEventRecord(s.a, g_dev.stream);
+  g_prof.push_back(s);
+}
+
 void after_launch(const char *name)
 {
+  if (g_prof_on && !g_prof.empty()) cudaEventRecord(g_prof.back().b, g_dev.stream);
   g_dev.launches++;
   if (g_dev.fail_launch_nth > 0 && --g_dev.fail_launch_nth == 0)
     throw OutOfMemory(std::string("kernel launch ran out of device memory (injected) in ") + name);

@@ -46,12 +46,19 @@ struct DeviceState {
 DeviceState &dev();
 void require_initialized();
 
-// after every kernel launch: counts it, reports launch errors, and applies debug_fail_launch
+// around every kernel launch: count it, report launch errors, apply debug_fail_launch; with the kernel profile on,
+// a pair of CUDA events on the launch stream per launch
+void before_launch(const char *name);
 void after_launch(const char *name);
+// per-kernel device time (CUDA events around every launch while on)
+void profile_enable(bool on);
+// "name launches total_ms" lines of the launches since profile_enable(true); synchronises the stream
+std::string profile_report();
 
 #ifndef GB_CPU_EMU
 #define GB_LAUNCH(kernel, grid, block, smem, ...)                                   \
   do {                                                                              \
+    ::gb::before_launch(#kernel);                                                   \
     kernel<<<(grid), (block), (smem), ::gb::dev().stream>>>(__VA_ARGS__);           \
     ::gb::after_launch(#kernel);                                                    \
   } while (0)

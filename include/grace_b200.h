@@ -64,6 +64,11 @@ int grace_debug_fail_launch(int nth);                             /* debug_fail_
 const char *grace_last_error(void);            /* what() of the exception the reference would have thrown */
 /* kernels launched by this library since the process started (diagnostics; no counterpart in the reference) */
 uint64_t grace_kernel_launches(void);
+/* per-kernel device time: with on != 0 every launch is bracketed by CUDA events on the launch stream; the report is
+ * one "name launches total_ms" line per kernel since the profile was switched on, copied into buf (diagnostics; the
+ * reference labels its kernels for external profilers instead) */
+int grace_profile_enable(int on);
+int grace_profile_report(char *buf, size_t len);
 
 /* ---- Model (kk_api.h:51-64): a loaded GRACE-1L / GRACE-2L kokkos.npz ---- */
 /* spline: intervals of the radial cubic Hermite tables (reference default 1024; >= 16) */
