@@ -56,6 +56,8 @@ void profile_enable(bool on);
 std::string profile_report();
 
 #ifndef GB_CPU_EMU
+// dynamic shared memory of a kernel as an array of T
+#define GB_DYN_SMEM(T, name) extern __shared__ T name[]
 #define GB_LAUNCH(kernel, grid, block, smem, ...)                                   \
   do {                                                                              \
     ::gb::before_launch(#kernel);                                                   \

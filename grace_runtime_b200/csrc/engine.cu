@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace gb {
@@ -149,8 +150,12 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   eW_.upload(P.eW);
   shift_.upload(P.shift);
   setup_layer(L1_, P.L1);
+  setup_fused(L1_, P.L1);
+  fused_ = L1_.fused_TA > 0;
   if (P.layers == 2) {
     setup_layer(L2_, P.L2);
+    setup_fused(L2_, P.L2);
+    fused_ = fused_ && L2_.fused_TA > 0;
     lnI_.upload(P.lnI);
     ln0_.upload(P.ln0);
   }
@@ -170,12 +175,17 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   r.rms = P.rms;
   r.nrho = P.nrho;
   r.out_scale = P.out_scale;
+  if (getenv("GRACE_B200_NO_FUSED")) fused_ = false;    // the per-operation kernels, for comparison
   GB_CUDA(cudaStreamSynchronize(dev().stream));    // the uploads read host vectors of this scope
 }
 
 Engine::~Engine() = default;
 
-double Engine::per_atom_bytes() const { return 4.0 * (double) std::max(L1_.per_atom, L2_.per_atom); }
+double Engine::per_atom_bytes() const
+{
+  if (fused_) return 8.0 * (double) std::max(L1_.q_floats, L2_.q_floats);
+  return 4.0 * (double) std::max(L1_.per_atom, L2_.per_atom);
+}
 
 int Engine::auto_chunk(int64_t n) const
 {
@@ -183,7 +193,7 @@ int Engine::auto_chunk(int64_t n) const
   if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) free_b = (size_t) 8 << 30;
   const double budget = 0.35 * (double) free_b + 4.0 * (double) arena_.capacity();
   int64_t c = (int64_t) (budget / per_atom_bytes());
-  c = std::min<int64_t>(c, 32768);    // larger chunks do not lower the launch count per atom enough to matter
+  c = std::min<int64_t>(c, fused_ ? ((int64_t) 1 << 22) : 32768);
   c = std::max<int64_t>(c, 512);
   return (int) std::min<int64_t>(c, std::max<int64_t>(n, 1));
 }
@@ -227,18 +237,170 @@ void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA)
   }
 }
 
-void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm)
+// shared-memory layout of the tensors of an atom tile: every tensor padded to 4 floats per atom; a gradient that may
+// alias a forward tensor shares its offset; TA = the largest atom tile that fits the 227 KB of an SM
+void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
+{
+  const size_t nt = P.tensors.size();
+  std::vector<int> soff(nt, 0), tch(nt, 0);
+  std::vector<int2> zero, ops;
+  long long at = 0;
+  auto size_of = [&](size_t t) { return ((long long) P.tensors[t].nfuncs * P.tensors[t].channels + 3) / 4 * 4; };
+  for (size_t t = 0; t < nt; t++) {
+    tch[t] = P.tensors[t].channels;
+    if (P.tensors[t].alias >= 0) continue;
+    soff[t] = (int) at;
+    at += size_of(t);
+  }
+  for (size_t t = 0; t < nt; t++) {
+    if (P.tensors[t].alias >= 0) soff[t] = soff[P.tensors[t].alias];
+    if (P.tensors[t].grad) zero.push_back(make_int2(soff[t], (int) size_of(t)));
+  }
+  for (const Op &o : P.fwd.ops) ops.push_back(make_int2(o.kind == Op::MV ? 0 : 1, o.index));
+  for (const Op &o : P.bwd.ops) ops.push_back(make_int2(o.kind == Op::MV ? 0 : 1, o.index));
+  E.f_mv.set_label("engine:tables"); E.f_prod.set_label("engine:tables"); E.f_ops.set_label("engine:tables");
+  E.f_zero.set_label("engine:tables"); E.f_soff.set_label("engine:tables"); E.f_tch.set_label("engine:tables");
+  E.f_mv.upload(E.mv);
+  E.f_prod.upload(E.prod);
+  E.f_ops.upload(ops);
+  E.f_zero.upload(zero);
+  E.f_soff.upload(soff);
+  E.f_tch.upload(tch);
+  FusedLayerDev &F = E.fused;
+  F.mv = E.f_mv.get();
+  F.prod = E.f_prod.get();
+  F.ops = E.f_ops.get();
+  F.nfwd = (int) P.fwd.ops.size();
+  F.nbwd = (int) P.bwd.ops.size();
+  F.soff = E.f_soff.get();
+  F.tch = E.f_tch.get();
+  F.zero = E.f_zero.get();
+  F.nzero = (int) zero.size();
+  F.per_atom = (int) at;
+  E.q_floats = (long long) P.tensors[P.tQ].nfuncs * P.tensors[P.tQ].channels;
+  const long long limit = 227 * 1024 - 1024;
+  E.fused_TA = 0;
+  for (int ta : {8, 6, 4, 3, 2, 1})
+    if (at * 4 * ta <= limit) { E.fused_TA = ta; break; }
+  if (const char *env = getenv("GRACE_B200_TILE_ATOMS")) {
+    const int ta = atoi(env);
+    if ((ta == 1 || ta == 2 || ta == 3 || ta == 4 || ta == 6 || ta == 8) && at * 4 * ta <= limit) E.fused_TA = ta;
+  }
+  GB_CUDA(cudaStreamSynchronize(dev().stream));
+}
+
+void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu)
+{
+  const ModelPlan &P = plan_;
+  const LayerPlan &LP = *E.plan;
+  FusedIO io{};
+  io.mode = mode;
+  io.tQ = LP.tQ;
+  io.tGQ = LP.tGQ;
+  io.nQ = LP.tensors[LP.tQ].nfuncs;
+  io.CQ = LP.tensors[LP.tQ].channels;
+  io.Q = arena_.get();
+  io.gQ = arena_.get() + (size_t) E.q_floats * NA;
+  io.NA = NA;
+  io.nrho = P.nrho;
+  io.nI = P.nI;
+  io.CR = P.cr;
+  if (&E == &L1_) {
+    io.t_rho = P.t1_rho; io.t_grho = P.t1_grho; io.t_I = P.t1_I; io.t_gI = P.t1_gI;
+  } else {
+    io.t_I2 = P.t2_I2; io.t_gI2 = P.t2_gI2;
+  }
+  io.I_rows = I_rows_.get();
+  io.rho_rows = rho_rows_.get();
+  io.gI_rows = gI_rows_.get();
+  io.grho_rows = grho_rows_.get();
+  io.ro = readout_;
+  io.mu = mu;
+  io.e_atom = e_atom_.get();
+  io.a0 = a0;
+  io.na = na;
+  const int TA = E.fused_TA;
+  const int ntiles = (na + TA - 1) / TA;
+  const size_t smem = (size_t) E.fused.per_atom * TA * 4;
+  const int per_sm = (int) std::max<size_t>(1, std::min<size_t>(2, (size_t) (227 * 1024) / (smem + 1024)));
+  launch_chain_fused(TA, E.fused, io, std::min(ntiles, dev().sm_count * per_sm));
+}
+
+// bond sums -> fused dense network (forward, readout, reverse in one kernel) -> bond forces; only the bond-sum tensor
+// and its gradient live in global memory, so a pass can hold every atom of most structures
+void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm)
 {
   const int64_t n = nl.n();
-  const int nsys = nl.nsys();
   cudaStream_t st = dev().stream;
-  if (n == 0) {
-    if (out.energy) GB_CUDA(cudaMemsetAsync(out.energy, 0, sizeof(double) * nsys, st));
-    if (out.virial && !energy_only) GB_CUDA(cudaMemsetAsync(out.virial, 0, sizeof(double) * 6 * nsys, st));
+  const ModelPlan &P = plan_;
+  const long long qf = std::max(L1_.q_floats, L2_.q_floats);
+  arena_.ensure((size_t) 2 * qf * NA);
+  arena_NA_ = 0;    // the chunked layout, if it was bound, no longer is
+  const BondsDev bonds = nl.bonds();
+  const int *mu = nl.mu_sorted();
+  float *fv = fv_.get();
+  float *Q = arena_.get();
+  const int bwd = energy_only ? 0 : FUSED_BWD;
+  if (P.layers == 1) {
+    const LayerDev L = layer_dev(L1_);
+    const float *gQ = arena_.get() + (size_t) L1_.q_floats * NA;
+    for (int64_t a0 = 0; a0 < n; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, n - a0);
+      if (tm) tm->begin(StageTimer::FWD);
+      launch_bond_fwd(P.lmax, bonds, L, Q, NA, (int) a0, na);
+      run_fused(L1_, FUSED_READOUT_1L | bwd, NA, (int) a0, na, mu);
+      if (tm) tm->end(StageTimer::FWD);
+      if (energy_only) continue;
+      if (tm) tm->begin(StageTimer::BWD);
+      launch_bond_bwd(P.lmax, bonds, L, gQ, NA, (int) a0, na, fv, vir_atom_.get(), 0);
+      if (tm) tm->end(StageTimer::BWD);
+    }
     return;
   }
+  const int nI = P.nI, CR = P.cr, nrho = P.nrho;
+  I_rows_.ensure((size_t) n * nI * CR);
+  rho_rows_.ensure((size_t) n * nrho);
+  if (!energy_only) {
+    gI_rows_.ensure((size_t) n * nI * CR);
+    grho_rows_.ensure((size_t) n * nrho);
+    GB_CUDA(cudaMemsetAsync(gI_rows_.get(), 0, sizeof(float) * (size_t) n * nI * CR, st));
+  }
+  const LayerDev La = layer_dev(L1_);
+  LayerDev Lb = layer_dev(L2_);
+  Lb.msg = I_rows_.get();
+  Lb.gmsg = gI_rows_.get();
+  const float *gQ1 = arena_.get() + (size_t) L1_.q_floats * NA, *gQ2 = arena_.get() + (size_t) L2_.q_floats * NA;
+  if (tm) tm->begin(StageTimer::FWD);
+  for (int64_t a0 = 0; a0 < n; a0 += NA) {    // layer 1 forward: messages and rho of all atoms
+    const int na = (int) std::min<int64_t>(NA, n - a0);
+    launch_bond_fwd(P.lmax, bonds, La, Q, NA, (int) a0, na);
+    run_fused(L1_, FUSED_STORE_MSG, NA, (int) a0, na, mu);
+  }
+  for (int64_t a0 = 0; a0 < n; a0 += NA) {    // layer 2, energy, layer-2 reverse
+    const int na = (int) std::min<int64_t>(NA, n - a0);
+    launch_bond_fwd(P.lmax, bonds, Lb, Q, NA, (int) a0, na);
+    run_fused(L2_, FUSED_READOUT_2L | bwd, NA, (int) a0, na, mu);
+    if (!energy_only) launch_bond_bwd(P.lmax, bonds, Lb, gQ2, NA, (int) a0, na, fv, vir_atom_.get(), 0);
+  }
+  if (tm) tm->end(StageTimer::FWD);
+  if (energy_only) return;
+  if (tm) tm->begin(StageTimer::BWD);
+  for (int64_t a0 = 0; a0 < n; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
+    const int na = (int) std::min<int64_t>(NA, n - a0);
+    launch_bond_fwd(P.lmax, bonds, La, Q, NA, (int) a0, na);
+    run_fused(L1_, FUSED_LOAD_SEED | FUSED_BWD, NA, (int) a0, na, mu);
+    launch_bond_bwd(P.lmax, bonds, La, gQ1, NA, (int) a0, na, fv, vir_atom_.get(), 1);
+  }
+  if (tm) tm->end(StageTimer::BWD);
+}
+
+// the dense network as one kernel launch per operation on chunk tensors in global memory: the path for layers whose
+// tensors of a single atom do not fit the shared memory of an SM
+void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm)
+{
+  const int64_t n = nl.n();
+  cudaStream_t st = dev().stream;
   const ModelPlan &P = plan_;
-  const int NA = (int) std::min<int64_t>(n, chunk > 0 ? chunk : n);
   const long long per_atom = std::max(L1_.per_atom, L2_.per_atom);
   const float *arena_before = arena_.get();
   arena_.ensure((size_t) per_atom * NA);
@@ -247,8 +409,6 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
     bind_arena(L1_, NA);
     bind_arena(L2_, NA);
   }
-  e_atom_.ensure(n);
-  if (!energy_only) vir_atom_.ensure(6 * n);
   const BondsDev bonds = nl.bonds();
   const int *mu = nl.mu_sorted();
   float *fv = fv_.get();
@@ -329,6 +489,24 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
       if (tm) tm->end(StageTimer::BWD);
     }
   }
+}
+
+void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm)
+{
+  const int64_t n = nl.n();
+  const int nsys = nl.nsys();
+  cudaStream_t st = dev().stream;
+  if (n == 0) {
+    if (out.energy) GB_CUDA(cudaMemsetAsync(out.energy, 0, sizeof(double) * nsys, st));
+    if (out.virial && !energy_only) GB_CUDA(cudaMemsetAsync(out.virial, 0, sizeof(double) * 6 * nsys, st));
+    return;
+  }
+  const int NA = (int) std::min<int64_t>(n, chunk > 0 ? chunk : n);
+  e_atom_.ensure(n);
+  if (!energy_only) vir_atom_.ensure(6 * n);
+  if (fused_) evaluate_fused(nl, energy_only, NA, tm);
+  else evaluate_chunked(nl, energy_only, NA, tm);
+  float *fv = fv_.get();
   // sums and gathers that leave the engine
   if (out.energy) launch_segment_sum(e_atom_.get(), 1, nl.seg(), nsys, out.energy);
   if (out.energies) launch_scatter_f64(e_atom_.get(), nl.perm(), out.energies, (int) n);
@@ -418,13 +596,22 @@ void SystemObj::compute(int n, const int *types, const double *pos, bool device_
       last_chunk = (chunk > 0 && chunk < n) ? chunk : 0;
       return;
     } catch (const OutOfMemory &e) {
-      // drop what was allocated, halve the pass down to 512 atoms, then give up (kk_core.cpp:420-497)
+      // what was half grown is dropped, so the next call starts clean.  A fixed chunksize reports the failure; the
+      // automatic one retries with half the pass (from one pass: the power of two below n / 2) down to 512 atoms
+      // (python/kk/kk_core.cpp:451-497)
       nl_.release();
       have_list_ = false;
       engine_->release_work();
-      const int cur = chunk > 0 ? std::min(chunk, std::max(n, 1)) : std::max(n, 1);
-      if (cur <= 512) throw OutOfMemory(std::string("the structure does not fit the device memory: ") + e.what());
-      chunk = std::max(512, cur / 2);
+      if (chunk_req_ >= 0)
+        throw OutOfMemory(std::string("failed to allocate device memory with chunksize ") + std::to_string(chunk_req_) +
+                          " (chunksize -1 tries smaller ones): " + e.what());
+      int next;
+      if (chunk > 0 && chunk < n) next = chunk / 2;
+      else for (next = 1; (int64_t) next * 2 <= n / 2; next *= 2) {}
+      if (next < 512)
+        throw OutOfMemory("the structure (" + std::to_string(n) + " atoms) does not fit the GPU memory even with smaller "
+                          "chunks (down to 512 atoms): " + e.what());
+      chunk = next;
     }
   }
 }

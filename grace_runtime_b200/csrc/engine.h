@@ -28,6 +28,14 @@ struct LayerEngine {
   long long per_atom = 0, grad_begin = 0, grad_end = 0;
   DBuf<TensorDev> tensors;
   std::vector<TensorDev> tensors_host;
+  // the same operations on shared-memory tensors of an atom tile (chain_fused.cu)
+  DBuf<MVDev> f_mv;
+  DBuf<ProdDev> f_prod;
+  DBuf<int2> f_ops, f_zero;
+  DBuf<int> f_soff, f_tch;
+  FusedLayerDev fused{};
+  int fused_TA = 0;           // atoms per tile that fit the shared memory (0: the layer does not fit)
+  long long q_floats = 0;     // floats per atom of the bond-sum tensor
 };
 
 // outputs of one evaluation, device pointers (null: not wanted)
@@ -64,6 +72,11 @@ class Engine {
   DBuf<double> e_atom_, vir_atom_, grho_rows_;
   int arena_NA_ = 0;
   void setup_layer(LayerEngine &E, const LayerPlan &P);
+  void setup_fused(LayerEngine &E, const LayerPlan &P);
+  bool fused_ = false;        // both layers run as the fused shared-memory kernel
+  void evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm);
+  void evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm);
+  void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu);
   void bind_arena(LayerEngine &E, int NA);
   void run(LayerEngine &E, const Program &prog, const int *mu, int NA);
   LayerDev layer_dev(const LayerEngine &E) const;

@@ -74,6 +74,40 @@ void launch_readout_1l(const ReadoutDev &r, const float *rho, float *grho, const
 void launch_readout_2l(const ReadoutDev &r, const float *rho_rows, const float *I2, double *grho_rows, float *gI2,
                        const int *mu, double *e_atom, int NA, int na, int a0, int want_grad);
 
+// ---- the dense network of a layer as one kernel on shared-memory tensors (chain_fused.cu) ----
+enum { FUSED_STORE_MSG = 1, FUSED_READOUT_1L = 2, FUSED_READOUT_2L = 4, FUSED_BWD = 8, FUSED_LOAD_SEED = 16 };
+
+struct FusedLayerDev {
+  const MVDev *mv;
+  const ProdDev *prod;
+  const int2 *ops;      // (kind: 0 MV, 1 PROD; index), forward operations then reverse operations
+  int nfwd, nbwd;
+  const int *soff;      // per tensor: offset in floats per atom of the tile
+  const int *tch;       // per tensor: channels
+  const int2 *zero;     // (offset, length) in floats per atom of the gradients cleared before the reverse operations
+  int nzero;
+  int per_atom;         // shared-memory floats per atom
+};
+
+struct FusedIO {
+  int mode;
+  int tQ, tGQ, nQ, CQ;              // bond-sum tensor and its gradient: ids, rows, channels
+  const float *Q;                   // global [nQ][NA][CQ]
+  float *gQ;
+  long long NA;
+  int t_rho, t_grho, nrho, t_I, t_gI, nI, CR, t_I2, t_gI2;
+  float *I_rows, *rho_rows;         // GRACE-2L per-atom rows [n][nI][CR], [n][nrho]
+  const float *gI_rows;
+  double *grho_rows;
+  ReadoutDev ro;
+  const int *mu;                    // [n] elements in list order
+  double *e_atom;
+  int a0, na;                       // first atom of the chunk in list order, atoms of the chunk
+};
+
+// TA: atoms per tile (1, 2, 3, 4, 6, 8); grid CTAs loop over the tiles
+void launch_chain_fused(int TA, const FusedLayerDev &L, const FusedIO &io, int grid);
+
 // chunk tensor [nf][NA][C] <-> per-atom rows [n][nf][C] (message I, its gradient) and [n][C] (rho)
 void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0);
 void launch_chunk_from_rows(float *t, const float *rows, int nf, int C, int NA, int na, int a0);

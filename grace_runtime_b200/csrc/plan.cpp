@@ -341,7 +341,12 @@ struct LayerBuilder {
       T.XXXX = tensor(xxxx, nXXXX, c.cf);
       T.gXX2 = tensor("g" + xx + "2", nXX, c.cf, true);
       T.gXXXX = tensor("g" + xxxx, nXXXX, c.cf, true);
+      P.tensors[T.gXXXX].alias = T.XXXX;
     }
+    // XX, XXX, XXXX are read by forward operations only (the adjoints need X0, X1, XX1, XX2): libgrace/src/
+    // fused_1l.cpp:309-310 keeps their gradients in the same buffers
+    P.tensors[T.gXX].alias = T.XX;
+    P.tensors[T.gXXX].alias = T.XXX;
     // liveness, backwards from the reduces
     auto mark = [](const std::vector<const ReduceWeights *> &rs, std::vector<char> &need) {
       for (auto *r : rs)
@@ -389,6 +394,50 @@ struct LayerBuilder {
   }
 };
 
+// Rows (functions) of the internal tensors that no operation touches are dropped and the rest renumbered: the pruned
+// outputs take no memory.  A gradient and the value tensor it may alias keep the same rows.
+void compact_rows(LayerPlan &P)
+{
+  const size_t nt = P.tensors.size();
+  std::vector<std::vector<char>> used(nt);
+  for (size_t t = 0; t < nt; t++) used[t].assign(P.tensors[t].nfuncs, P.tensors[t].external ? 1 : 0);
+  for (const MVOp &o : P.mv) {
+    for (int r : o.row_out) used[o.dst][r] = 1;
+    for (const MVItem &it : o.items) used[it.src][it.irow] = 1;
+  }
+  for (const ProdOp &o : P.prod) {
+    for (int r : o.row_out) used[o.dst][r] = 1;
+    for (const ProdTerm &tm : o.terms) {
+      used[o.srcA][tm.a] = 1;
+      if (o.srcB >= 0) used[o.srcB][tm.b] = 1;
+    }
+  }
+  for (size_t t = 0; t < nt; t++)
+    if (P.tensors[t].alias >= 0) {
+      const int v = P.tensors[t].alias;
+      for (size_t r = 0; r < used[t].size(); r++) used[t][r] = used[v][r] = (used[t][r] || used[v][r]);
+    }
+  std::vector<std::vector<int>> map(nt);
+  for (size_t t = 0; t < nt; t++) {
+    map[t].assign(used[t].size(), -1);
+    int k = 0;
+    for (size_t r = 0; r < used[t].size(); r++)
+      if (used[t][r]) map[t][r] = k++;
+    P.tensors[t].nfuncs = k;
+  }
+  for (MVOp &o : P.mv) {
+    for (int &r : o.row_out) r = map[o.dst][r];
+    for (MVItem &it : o.items) it.irow = map[it.src][it.irow];
+  }
+  for (ProdOp &o : P.prod) {
+    for (int &r : o.row_out) r = map[o.dst][r];
+    for (ProdTerm &tm : o.terms) {
+      tm.a = map[o.srcA][tm.a];
+      if (o.srcB >= 0) tm.b = map[o.srcB][tm.b];
+    }
+  }
+}
+
 }    // namespace
 
 ModelPlan build_plan(const GraceModel &m, int spline_n)
@@ -421,6 +470,7 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
     L.z.assign(m.zA.begin(), m.zA.end());
     L.tQ = B.tensor("A", nlm, c.c0);
     L.tGQ = B.tensor("gA", nlm, c.c0, true);
+    L.tensors[L.tQ].external = L.tensors[L.tGQ].external = true;
     std::vector<const ReduceWeights *> rXX{&m.rho[1]}, rXXX{&m.rho[2]}, rXXXX{c.order4 ? &m.rho[3] : nullptr};
     if (m.layers == 2) {
       rXX.push_back(&m.I1[1]);
@@ -430,10 +480,12 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
     const auto T = B.chain("A", c, L.tQ, L.tGQ, rXX, rXXX, rXXXX);
     P.t1_rho = B.tensor("rho", 1, m.rho_n_out);
     P.t1_grho = B.tensor("grho", 1, m.rho_n_out);    // written by the readout, not zeroed
+    L.tensors[P.t1_rho].external = L.tensors[P.t1_grho].external = true;
     if (m.layers == 2) {
       const int tI1 = B.tensor("I1", m.nI1, m.i1_out), gI1 = B.tensor("gI1", m.nI1, m.i1_out, true);
       P.t1_I = B.tensor("I", m.nI, m.cr);
       P.t1_gI = B.tensor("gI", m.nI, m.cr);    // copied from the per-atom dE/dI rows, not zeroed
+      L.tensors[P.t1_I].external = L.tensors[P.t1_gI].external = true;
       B.reduce(B.reduce4("I1", m.I1, T, c.order4, m.i1_out, m.nI1, true, tI1, gI1));
       B.reduce(B.reduce4("rho", m.rho, T, c.order4, m.rho_n_out, 1, true, P.t1_rho, P.t1_grho));
       ReduceGroup R;
@@ -464,7 +516,10 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
     const int nq = (m.nI + 1) * nlm;
     L.tQ = B.tensor("Q", nq, m.cr);
     L.tGQ = B.tensor("gQ", nq, m.cr, true);
+    L.tensors[L.tQ].external = L.tensors[L.tGQ].external = true;
+    L.tensors[L.tGQ].alias = L.tQ;    // Q is read by the forward YI / B operations only
     const int tYI = B.tensor("YI", m.yi.n_out, m.cr), gYI = B.tensor("gYI", m.yi.n_out, m.cr, true);
+    L.tensors[gYI].alias = tYI;
     {
       CGProduct y;    // YI[o] = inv_avg sum_t cg_t Q[I_t nlm + y_t]
       y.present = true;
@@ -511,9 +566,12 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
     const auto T = B.chain("B", c, tB, gB, {&m.I2[1]}, {&m.I2[2]}, {c.order4 ? &m.I2[3] : nullptr});
     P.t2_I2 = B.tensor("I2", 1, m.nI2);
     P.t2_gI2 = B.tensor("gI2", 1, m.nI2);
+    L.tensors[P.t2_I2].external = L.tensors[P.t2_gI2].external = true;
     B.reduce(B.reduce4("I2", m.I2, T, c.order4, m.nI2, 1, true, P.t2_I2, P.t2_gI2));
     B.finish();
   }
+  compact_rows(P.L1);
+  if (m.layers == 2) compact_rows(P.L2);
   // readout
   for (const auto &Lr : m.energy_mlp) {
     P.eW.insert(P.eW.end(), Lr.W.begin(), Lr.W.end());

@@ -20,6 +20,9 @@ struct TensorSpec {
   std::string name;
   int nfuncs = 0, channels = 0;
   bool grad = false;    // zeroed before the reverse pass of a chunk
+  int alias = -1;       // gradient only: a value tensor of the same shape that no reverse operation reads, whose
+                        // storage the gradient may take over once the forward pass is done
+  bool external = false;    // written or read outside the program (bond kernels, readout): every row is kept
 };
 
 struct MVItem {

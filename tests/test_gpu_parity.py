@@ -245,18 +245,52 @@ def test_errors(backend, models, cells):
     assert e["energy"] == 0.0 and e["forces"].shape == (0, 3)
 
 
-def test_injected_failures_recover(backend, models, cells):
-    """host-side fault injection (python/kk/kk_core.cpp:128-141,187-195): a failed allocation or launch halves the
-    pass and the call still succeeds; nothing faults the GPU"""
+def test_injected_failures_recover(backend, models, cells, tmp_path_factory):
+    """host-side fault injection (python/kk/kk_core.cpp:128-141,187-195; python/tests/test_gpu_alloc_failure.py): a
+    failed allocation or launch is a RuntimeError that leaves the System usable; with the automatic chunk size a large
+    enough structure is retried with half the pass.  Nothing here faults the GPU."""
     c = cells.get("WMo54")
     m = _model(backend, models, "grace_2l_order3")
     ok = _compute(backend, m, c)
     s = backend.System(m, c["species"], chunksize=-1)
+    s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    s.release_buffers()
     backend._debug_fail_alloc("work:", 1)
+    try:
+        with pytest.raises(RuntimeError, match="does not fit|allocat"):
+            s.compute(c["types"], c["positions"], c["cell"], c["pbc"])     # 54 atoms: no smaller pass to try
+    finally:
+        backend._debug_fail_alloc("", 0)
     r = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
-    backend._debug_fail_alloc("", 0)
     assert abs(r["energy"] - ok["energy"]) / c["n"] < 2e-6
     backend._debug_fail_launch(3)
+    try:
+        with pytest.raises(RuntimeError):
+            s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    finally:
+        backend._debug_fail_launch(0)
     r = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
-    backend._debug_fail_launch(0)
     assert np.abs(r["forces"] - ok["forces"]).max() < 2e-5
+    # automatic chunk: 2000 atoms in one pass -> retried with 1024 atoms per pass
+    path, els, big = _config_case(tmp_path_factory, "1l", "bcc", 3.165, (10, 10, 10), 1, 0.05, seed=2)
+    mb = backend.Model(path)
+    ref = _compute(backend, mb, big)
+    sb = backend.System(mb, els, chunksize=-1)
+    backend._debug_fail_alloc("work:", 1)
+    try:
+        rb = sb.compute(big["types"], big["positions"], big["cell"], big["pbc"])
+    finally:
+        backend._debug_fail_alloc("", 0)
+    assert sb.chunksize == 1024
+    assert abs(rb["energy"] - ref["energy"]) / big["n"] < 2e-6
+    assert np.abs(rb["forces"] - ref["forces"]).max() < 2e-5
+    # fixed chunk: the failure is reported, the System works afterwards
+    sf = backend.System(mb, els, chunksize=512)
+    backend._debug_fail_alloc("work:", 1)
+    try:
+        with pytest.raises(RuntimeError, match="failed to allocate"):
+            sf.compute(big["types"], big["positions"], big["cell"], big["pbc"])
+    finally:
+        backend._debug_fail_alloc("", 0)
+    rf = sf.compute(big["types"], big["positions"], big["cell"], big["pbc"])
+    assert np.abs(rf["forces"] - ref["forces"]).max() < 2e-5
