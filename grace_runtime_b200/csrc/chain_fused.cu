@@ -12,70 +12,157 @@ namespace gb {
 
 namespace {
 
-constexpr int NT = 256;
+constexpr int NT = 512;
 
+// out[row][a][k] (+)= sum_items scale * sum_n M[n][k] x[item][a][n] on the tile's shared-memory tensors.
+// Fast path (all widths multiples of 4): a thread owns 4 consecutive output channels of one row for all TA atoms, so
+// a 16-byte weight load feeds 4 TA FMAs and a 16-byte activation load (broadcast in the warp) feeds 16.
 template<int TA>
 __device__ __forceinline__ void mv_tile(const MVDev &op, float *sm, const int *__restrict__ soff,
                                         const int *__restrict__ tch, const int *s_mu)
 {
-  int KP = 8;
-  while (KP < op.n_out) KP <<= 1;
-  const int tid = threadIdx.x, k = tid & (KP - 1), rstep = NT / KP;
+  const int tid = threadIdx.x;
   const int Cd = tch[op.dst];
   float *dst = sm + (size_t) soff[op.dst] * TA;
-  if (k >= op.n_out) return;
-  for (int row = tid / KP; row < op.nrows; row += rstep) {
-    float acc[TA];
+  if ((op.n_out & 3) == 0 && (Cd & 3) == 0) {
+    const int KQ = op.n_out >> 2;
+    int KQP = 1;
+    while (KQP < KQ) KQP <<= 1;
+    // S lanes share the items of one (row, channel quad) when the operation has fewer of those than threads
+    const int total = op.nrows * KQP;
+    int S = 1;
+    while (S < 32 && total * S * 2 <= NT) S <<= 1;
+    const int s = tid & (S - 1), per_pass = NT / S;
+    for (int base = 0; base < total; base += per_pass) {
+      const int rk = base + tid / S, row = rk / KQP, kq = rk - row * KQP;
+      const bool valid = rk < total && kq < KQ;
+      float4 acc[TA];
 #pragma unroll
-    for (int a = 0; a < TA; a++) acc[a] = 0.0f;
-    const int i0 = op.item_off[row], i1 = op.item_off[row + 1];
-    for (int it = i0; it < i1; it++) {
-      const MVItem item = op.items[it];
-      const int Cs = tch[item.src];
-      const float *x = sm + (size_t) soff[item.src] * TA + (size_t) item.irow * TA * Cs;
-      float part[TA];
+      for (int a = 0; a < TA; a++) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int i0 = valid ? op.item_off[row] + s : 0, i1 = valid ? op.item_off[row + 1] : 0;
+      for (int it = i0; it < i1; it += S) {
+        const MVItem item = op.items[it];
+        const int Cs = tch[item.src];
+        const float *x = sm + (size_t) soff[item.src] * TA + (size_t) item.irow * TA * Cs;
+        const float *M = op.W + item.mat + 4 * kq;
+        float4 part[TA];
 #pragma unroll
-      for (int a = 0; a < TA; a++) part[a] = 0.0f;
-      if (!op.elem) {
-        const float *M = op.W + item.mat + k;
-        if (((item.n_in | Cs) & 3) == 0) {
+        for (int a = 0; a < TA; a++) part[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (op.elem) {    // weights of each atom's element
+          for (int n = 0; n < item.n_in; n++) {
+#pragma unroll
+            for (int a = 0; a < TA; a++) {
+              const float4 w = __ldg(reinterpret_cast<const float4 *>(M + (size_t) s_mu[a] * op.ty_stride + (size_t) n * op.n_out));
+              const float xv = x[a * Cs + n];
+              part[a].x = fmaf(xv, w.x, part[a].x); part[a].y = fmaf(xv, w.y, part[a].y);
+              part[a].z = fmaf(xv, w.z, part[a].z); part[a].w = fmaf(xv, w.w, part[a].w);
+            }
+          }
+        } else if (((item.n_in | Cs) & 3) == 0) {
           for (int n = 0; n < item.n_in; n += 4) {
-            const float w0 = __ldg(M + (size_t) n * op.n_out), w1 = __ldg(M + (size_t) (n + 1) * op.n_out);
-            const float w2 = __ldg(M + (size_t) (n + 2) * op.n_out), w3 = __ldg(M + (size_t) (n + 3) * op.n_out);
+            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * op.n_out));
+            const float4 w1 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n + 1) * op.n_out));
+            const float4 w2 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n + 2) * op.n_out));
+            const float4 w3 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n + 3) * op.n_out));
 #pragma unroll
             for (int a = 0; a < TA; a++) {
               const float4 x4 = *reinterpret_cast<const float4 *>(x + a * Cs + n);
-              part[a] = fmaf(x4.x, w0, part[a]);
-              part[a] = fmaf(x4.y, w1, part[a]);
-              part[a] = fmaf(x4.z, w2, part[a]);
-              part[a] = fmaf(x4.w, w3, part[a]);
+              part[a].x = fmaf(x4.x, w0.x, part[a].x); part[a].y = fmaf(x4.x, w0.y, part[a].y);
+              part[a].z = fmaf(x4.x, w0.z, part[a].z); part[a].w = fmaf(x4.x, w0.w, part[a].w);
+              part[a].x = fmaf(x4.y, w1.x, part[a].x); part[a].y = fmaf(x4.y, w1.y, part[a].y);
+              part[a].z = fmaf(x4.y, w1.z, part[a].z); part[a].w = fmaf(x4.y, w1.w, part[a].w);
+              part[a].x = fmaf(x4.z, w2.x, part[a].x); part[a].y = fmaf(x4.z, w2.y, part[a].y);
+              part[a].z = fmaf(x4.z, w2.z, part[a].z); part[a].w = fmaf(x4.z, w2.w, part[a].w);
+              part[a].x = fmaf(x4.w, w3.x, part[a].x); part[a].y = fmaf(x4.w, w3.y, part[a].y);
+              part[a].z = fmaf(x4.w, w3.z, part[a].z); part[a].w = fmaf(x4.w, w3.w, part[a].w);
             }
           }
         } else {
           for (int n = 0; n < item.n_in; n++) {
-            const float w = __ldg(M + (size_t) n * op.n_out);
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * op.n_out));
 #pragma unroll
-            for (int a = 0; a < TA; a++) part[a] = fmaf(x[a * Cs + n], w, part[a]);
+            for (int a = 0; a < TA; a++) {
+              const float xv = x[a * Cs + n];
+              part[a].x = fmaf(xv, w.x, part[a].x); part[a].y = fmaf(xv, w.y, part[a].y);
+              part[a].z = fmaf(xv, w.z, part[a].z); part[a].w = fmaf(xv, w.w, part[a].w);
+            }
           }
         }
-      } else {
+#pragma unroll
+        for (int a = 0; a < TA; a++) {
+          acc[a].x = fmaf(item.scale, part[a].x, acc[a].x); acc[a].y = fmaf(item.scale, part[a].y, acc[a].y);
+          acc[a].z = fmaf(item.scale, part[a].z, acc[a].z); acc[a].w = fmaf(item.scale, part[a].w, acc[a].w);
+        }
+      }
+      for (int d = S >> 1; d > 0; d >>= 1) {
+#pragma unroll
+        for (int a = 0; a < TA; a++) {
+          acc[a].x += __shfl_xor_sync(0xffffffffu, acc[a].x, d); acc[a].y += __shfl_xor_sync(0xffffffffu, acc[a].y, d);
+          acc[a].z += __shfl_xor_sync(0xffffffffu, acc[a].z, d); acc[a].w += __shfl_xor_sync(0xffffffffu, acc[a].w, d);
+        }
+      }
+      if (!valid || s != 0) continue;
+      float *o = dst + (size_t) op.row_out[row] * TA * Cd + 4 * kq;
+#pragma unroll
+      for (int a = 0; a < TA; a++) {
+        float4 *p = reinterpret_cast<float4 *>(o + a * Cd);
+        if (op.accumulate) {
+          const float4 old = *p;
+          acc[a].x += old.x; acc[a].y += old.y; acc[a].z += old.z; acc[a].w += old.w;
+        }
+        *p = acc[a];
+      }
+    }
+    return;
+  }
+  // general path (widths that are no multiples of 4): one output channel per group of S lanes, which share the items
+  // of the row and add their partial sums by shuffles, so that a reduce with few outputs still uses the CTA
+  int KP = 8;
+  while (KP < op.n_out) KP <<= 1;
+  const int total = op.nrows * KP;
+  int S = 1;
+  while (S < 32 && total * S * 2 <= NT) S <<= 1;
+  const int s = tid & (S - 1), per_pass = NT / S;
+  for (int base = 0; base < total; base += per_pass) {
+    const int rk = base + tid / S, row = rk / KP, k = rk - row * KP;
+    const bool valid = rk < total && k < op.n_out;
+    float acc[TA];
+#pragma unroll
+    for (int a = 0; a < TA; a++) acc[a] = 0.0f;
+    if (valid) {
+      const int i0 = op.item_off[row], i1 = op.item_off[row + 1];
+      for (int it = i0 + s; it < i1; it += S) {
+        const MVItem item = op.items[it];
+        const int Cs = tch[item.src];
+        const float *x = sm + (size_t) soff[item.src] * TA + (size_t) item.irow * TA * Cs;
+        float part[TA];
         const float *M[TA];
 #pragma unroll
-        for (int a = 0; a < TA; a++) M[a] = op.W + (size_t) s_mu[a] * op.ty_stride + item.mat + k;
+        for (int a = 0; a < TA; a++) {
+          part[a] = 0.0f;
+          M[a] = op.W + (op.elem ? (size_t) s_mu[a] * op.ty_stride : 0) + item.mat + k;
+        }
         for (int n = 0; n < item.n_in; n++) {
 #pragma unroll
           for (int a = 0; a < TA; a++) part[a] = fmaf(x[a * Cs + n], __ldg(M[a] + (size_t) n * op.n_out), part[a]);
         }
+#pragma unroll
+        for (int a = 0; a < TA; a++) acc[a] = fmaf(item.scale, part[a], acc[a]);
       }
-#pragma unroll
-      for (int a = 0; a < TA; a++) acc[a] = fmaf(item.scale, part[a], acc[a]);
     }
-    float *o = dst + (size_t) op.row_out[row] * TA * Cd + k;
+    for (int d = S >> 1; d > 0; d >>= 1) {
 #pragma unroll
-    for (int a = 0; a < TA; a++) o[a * Cd] = op.accumulate ? o[a * Cd] + acc[a] : acc[a];
+      for (int a = 0; a < TA; a++) acc[a] += __shfl_xor_sync(0xffffffffu, acc[a], d);
+    }
+    if (valid && s == 0) {
+      float *o = dst + (size_t) op.row_out[row] * TA * Cd + k;
+#pragma unroll
+      for (int a = 0; a < TA; a++) o[a * Cd] = op.accumulate ? o[a * Cd] + acc[a] : acc[a];
+    }
   }
 }
 
+// out[row][i] (+)= sum_terms coef A[a][i] B[b][i] over the TA * C values of a row, four channels per thread
 template<int TA>
 __device__ __forceinline__ void prod_tile(const ProdDev &op, float *sm, const int *__restrict__ soff,
                                           const int *__restrict__ tch)
@@ -84,21 +171,41 @@ __device__ __forceinline__ void prod_tile(const ProdDev &op, float *sm, const in
   const float *A = sm + (size_t) soff[op.srcA] * TA;
   const float *B = op.srcB >= 0 ? sm + (size_t) soff[op.srcB] * TA : nullptr;
   float *D = sm + (size_t) soff[op.dst] * TA;
+  if ((tch[op.dst] & 3) == 0) {
+    const int Q = TAC >> 2, total = op.nrows * Q;
+    for (int idx = threadIdx.x; idx < total; idx += NT) {
+      const int row = idx / Q, i = (idx - row * Q) * 4;
+      const int t0 = op.term_off[row], t1 = op.term_off[row + 1];
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int t = t0; t < t1; t++) {
+        const ProdTerm tm = op.terms[t];
+        const float4 av = *reinterpret_cast<const float4 *>(A + tm.a * TAC + i);
+        if (B) {
+          const float4 bv = *reinterpret_cast<const float4 *>(B + tm.b * TAC + i);
+          acc.x = fmaf(tm.coef * av.x, bv.x, acc.x); acc.y = fmaf(tm.coef * av.y, bv.y, acc.y);
+          acc.z = fmaf(tm.coef * av.z, bv.z, acc.z); acc.w = fmaf(tm.coef * av.w, bv.w, acc.w);
+        } else {
+          acc.x = fmaf(tm.coef, av.x, acc.x); acc.y = fmaf(tm.coef, av.y, acc.y);
+          acc.z = fmaf(tm.coef, av.z, acc.z); acc.w = fmaf(tm.coef, av.w, acc.w);
+        }
+      }
+      float4 *o = reinterpret_cast<float4 *>(D + op.row_out[row] * TAC + i);
+      if (op.accumulate) {
+        const float4 old = *o;
+        acc.x += old.x; acc.y += old.y; acc.z += old.z; acc.w += old.w;
+      }
+      *o = acc;
+    }
+    return;
+  }
   const int total = op.nrows * TAC;
   for (int idx = threadIdx.x; idx < total; idx += NT) {
     const int row = idx / TAC, i = idx - row * TAC;
     const int t0 = op.term_off[row], t1 = op.term_off[row + 1];
     float acc = 0.0f;
-    if (B) {
-      for (int t = t0; t < t1; t++) {
-        const ProdTerm tm = op.terms[t];
-        acc = fmaf(tm.coef * A[tm.a * TAC + i], B[tm.b * TAC + i], acc);
-      }
-    } else {
-      for (int t = t0; t < t1; t++) {
-        const ProdTerm tm = op.terms[t];
-        acc = fmaf(tm.coef, A[tm.a * TAC + i], acc);
-      }
+    for (int t = t0; t < t1; t++) {
+      const ProdTerm tm = op.terms[t];
+      acc = fmaf(tm.coef * A[tm.a * TAC + i], B ? B[tm.b * TAC + i] : 1.0f, acc);
     }
     float *o = D + op.row_out[row] * TAC + i;
     *o = op.accumulate ? *o + acc : acc;
@@ -206,10 +313,10 @@ __global__ void __launch_bounds__(NT) chain_fused_kernel(FusedLayerDev L, FusedI
 template<int TA> void launch_ta(const FusedLayerDev &L, const FusedIO &io, int grid, size_t smem)
 {
 #ifndef GB_CPU_EMU
-  static bool attr_set = false;
-  if (!attr_set) {
-    GB_CUDA(cudaFuncSetAttribute(chain_fused_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set = true;
+  static size_t attr_smem = 48 * 1024;    // dynamic shared memory this instantiation may use so far
+  if (smem > attr_smem) {
+    GB_CUDA(cudaFuncSetAttribute(chain_fused_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    attr_smem = smem;
   }
 #endif
   GB_LAUNCH((chain_fused_kernel<TA>), grid, NT, smem, L, io);

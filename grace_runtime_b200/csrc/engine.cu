@@ -322,7 +322,7 @@ void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const i
   const int TA = E.fused_TA;
   const int ntiles = (na + TA - 1) / TA;
   const size_t smem = (size_t) E.fused.per_atom * TA * 4;
-  const int per_sm = (int) std::max<size_t>(1, std::min<size_t>(2, (size_t) (227 * 1024) / (smem + 1024)));
+  const int per_sm = (int) std::max<size_t>(1, std::min<size_t>(4, (size_t) (227 * 1024) / (smem + 1024)));
   launch_chain_fused(TA, E.fused, io, std::min(ntiles, dev().sm_count * per_sm));
 }
 
