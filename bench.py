@@ -34,6 +34,7 @@ UNIT = "us/atom/GPU"
 WORKLOADS = {
     # name: (config, lattice, a, reps, species, sigma)
     "grace1l_128k_bcc_alloy": dict(cfg="1l", lattice="bcc", a=3.2, reps=(40, 40, 40), nsp=4, sigma=0.05, full=True),
+    "grace1l_16k_bcc_alloy": dict(cfg="1l", lattice="bcc", a=3.2, reps=(20, 20, 20), nsp=4, sigma=0.05, full=True),
     "grace1l_2k_bcc_w": dict(cfg="1l", lattice="bcc", a=3.165, reps=(10, 10, 10), nsp=1, sigma=0.05, full=False),
     "grace2l_1m_fcc_alloy": dict(cfg="2l", lattice="fcc", a=3.6, reps=(40, 80, 80), nsp=3, sigma=0.08, full=True),
     "grace2l_128k_fcc_alloy": dict(cfg="2l", lattice="fcc", a=3.6, reps=(20, 40, 40), nsp=3, sigma=0.08, full=True),

@@ -40,13 +40,13 @@ __global__ void __launch_bounds__(128) mv_kernel(MVDev op, const TensorDev *__re
       for (int n = 0; n < item.n_in; n++) {
 #pragma unroll
         for (int i = 0; i < AT; i++)
-          part[i] = fmaf(__ldg(x[i] + n), __ldg(op.W + tyo[i] + item.mat + (size_t) n * op.n_out + k), part[i]);
+          part[i] = fmaf(__ldg(x[i] + n), __ldg(op.W + tyo[i] + item.mat + (size_t) n * op.ldw + k), part[i]);
       }
     } else {
       const float *M = op.W + item.mat + k;
 #pragma unroll 4
       for (int n = 0; n < item.n_in; n++) {
-        const float w = __ldg(M + (size_t) n * op.n_out);
+        const float w = __ldg(M + (size_t) n * op.ldw);
 #pragma unroll
         for (int i = 0; i < AT; i++) part[i] = fmaf(__ldg(x[i] + n), w, part[i]);
       }

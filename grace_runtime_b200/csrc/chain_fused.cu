@@ -12,97 +12,130 @@ namespace gb {
 
 namespace {
 
-constexpr int NT = 512;
+#ifndef GB_FUSED_THREADS
+#define GB_FUSED_THREADS 512
+#endif
+constexpr int NT = GB_FUSED_THREADS;
 
 // out[row][a][k] (+)= sum_items scale * sum_n M[n][k] x[item][a][n] on the tile's shared-memory tensors.
-// Fast path (all widths multiples of 4): a thread owns 4 consecutive output channels of one row for all TA atoms, so
-// a 16-byte weight load feeds 4 TA FMAs and a 16-byte activation load (broadcast in the warp) feeds 16.
+// A thread owns 4 consecutive output channels of one row for all TA atoms: a 16-byte weight load (rows of the weight
+// matrices are padded to 4 outputs) feeds 4 TA FMAs, a 16-byte activation load (broadcast in the warp) 16.  The weight
+// loads of a batch of input channels are issued before the first FMA needs one, because the L1 left beside the tile's
+// shared memory is small and every load is an L2 round trip.  When an operation has fewer (row, channel quad) pairs
+// than the CTA has threads, S lanes share the items of a pair and add their partial sums by shuffles.
 template<int TA>
 __device__ __forceinline__ void mv_tile(const MVDev &op, float *sm, const int *__restrict__ soff,
                                         const int *__restrict__ tch, const int *s_mu)
 {
   const int tid = threadIdx.x;
-  const int Cd = tch[op.dst];
+  const int Cd = tch[op.dst], ld = op.ldw;
   float *dst = sm + (size_t) soff[op.dst] * TA;
-  if ((op.n_out & 3) == 0 && (Cd & 3) == 0) {
-    const int KQ = op.n_out >> 2;
-    int KQP = 1;
-    while (KQP < KQ) KQP <<= 1;
-    // S lanes share the items of one (row, channel quad) when the operation has fewer of those than threads
-    const int total = op.nrows * KQP;
-    int S = 1;
-    while (S < 32 && total * S * 2 <= NT) S <<= 1;
-    const int s = tid & (S - 1), per_pass = NT / S;
-    for (int base = 0; base < total; base += per_pass) {
-      const int rk = base + tid / S, row = rk / KQP, kq = rk - row * KQP;
-      const bool valid = rk < total && kq < KQ;
-      float4 acc[TA];
+  const int KQ = ld >> 2;
+  int KQP = 1;
+  while (KQP < KQ) KQP <<= 1;
+  const int total = op.nrows * KQP;
+  int S = 1;
+  while (S < 32 && total * S * 2 <= NT) S <<= 1;
+  const int s = tid & (S - 1), per_pass = NT / S;
+  for (int base = 0; base < total; base += per_pass) {
+    const int rk = base + tid / S, row = rk / KQP, kq = rk - row * KQP;
+    const bool valid = rk < total && kq < KQ;
+    float4 acc[TA];
 #pragma unroll
-      for (int a = 0; a < TA; a++) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
-      const int i0 = valid ? op.item_off[row] + s : 0, i1 = valid ? op.item_off[row + 1] : 0;
-      for (int it = i0; it < i1; it += S) {
-        const MVItem item = op.items[it];
-        const int Cs = tch[item.src];
-        const float *x = sm + (size_t) soff[item.src] * TA + (size_t) item.irow * TA * Cs;
-        const float *M = op.W + item.mat + 4 * kq;
-        float4 part[TA];
+    for (int a = 0; a < TA; a++) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int i0 = valid ? op.item_off[row] + s : 0, i1 = valid ? op.item_off[row + 1] : 0;
+    for (int it = i0; it < i1; it += S) {
+      const MVItem item = op.items[it];
+      const int Cs = tch[item.src];
+      const float *x = sm + (size_t) soff[item.src] * TA + (size_t) item.irow * TA * Cs;
+      const float *M = op.W + item.mat + 4 * kq;
+      const float sc = item.scale;
+      if (op.elem) {    // weights of each atom's element: two atoms' loads of 8 input channels in flight
+        constexpr int NE = 8;
+        for (int n0 = 0; n0 < item.n_in; n0 += NE) {
 #pragma unroll
-        for (int a = 0; a < TA; a++) part[a] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (op.elem) {    // weights of each atom's element
-          for (int n = 0; n < item.n_in; n++) {
+          for (int a0 = 0; a0 < TA; a0 += 2) {
+            float4 w[2][NE];
 #pragma unroll
-            for (int a = 0; a < TA; a++) {
-              const float4 w = __ldg(reinterpret_cast<const float4 *>(M + (size_t) s_mu[a] * op.ty_stride + (size_t) n * op.n_out));
-              const float xv = x[a * Cs + n];
-              part[a].x = fmaf(xv, w.x, part[a].x); part[a].y = fmaf(xv, w.y, part[a].y);
-              part[a].z = fmaf(xv, w.z, part[a].z); part[a].w = fmaf(xv, w.w, part[a].w);
+            for (int h = 0; h < 2; h++) {
+              const float *Ma = M + (size_t) s_mu[min(a0 + h, TA - 1)] * op.ty_stride;
+#pragma unroll
+              for (int j = 0; j < NE; j++)
+                w[h][j] = (n0 + j < item.n_in) ? __ldg(reinterpret_cast<const float4 *>(Ma + (size_t) (n0 + j) * ld))
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-          }
-        } else if (((item.n_in | Cs) & 3) == 0) {
-          for (int n = 0; n < item.n_in; n += 4) {
-            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * op.n_out));
-            const float4 w1 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n + 1) * op.n_out));
-            const float4 w2 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n + 2) * op.n_out));
-            const float4 w3 = __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n + 3) * op.n_out));
 #pragma unroll
-            for (int a = 0; a < TA; a++) {
-              const float4 x4 = *reinterpret_cast<const float4 *>(x + a * Cs + n);
-              part[a].x = fmaf(x4.x, w0.x, part[a].x); part[a].y = fmaf(x4.x, w0.y, part[a].y);
-              part[a].z = fmaf(x4.x, w0.z, part[a].z); part[a].w = fmaf(x4.x, w0.w, part[a].w);
-              part[a].x = fmaf(x4.y, w1.x, part[a].x); part[a].y = fmaf(x4.y, w1.y, part[a].y);
-              part[a].z = fmaf(x4.y, w1.z, part[a].z); part[a].w = fmaf(x4.y, w1.w, part[a].w);
-              part[a].x = fmaf(x4.z, w2.x, part[a].x); part[a].y = fmaf(x4.z, w2.y, part[a].y);
-              part[a].z = fmaf(x4.z, w2.z, part[a].z); part[a].w = fmaf(x4.z, w2.w, part[a].w);
-              part[a].x = fmaf(x4.w, w3.x, part[a].x); part[a].y = fmaf(x4.w, w3.y, part[a].y);
-              part[a].z = fmaf(x4.w, w3.z, part[a].z); part[a].w = fmaf(x4.w, w3.w, part[a].w);
-            }
-          }
-        } else {
-          for (int n = 0; n < item.n_in; n++) {
-            const float4 w = __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * op.n_out));
+            for (int h = 0; h < 2; h++) {
+              if (a0 + h < TA) {
 #pragma unroll
-            for (int a = 0; a < TA; a++) {
-              const float xv = x[a * Cs + n];
-              part[a].x = fmaf(xv, w.x, part[a].x); part[a].y = fmaf(xv, w.y, part[a].y);
-              part[a].z = fmaf(xv, w.z, part[a].z); part[a].w = fmaf(xv, w.w, part[a].w);
+                for (int j = 0; j < NE; j++) {
+                  const float xv = (n0 + j < item.n_in) ? x[(a0 + h) * Cs + n0 + j] * sc : 0.0f;
+                  acc[a0 + h].x = fmaf(xv, w[h][j].x, acc[a0 + h].x); acc[a0 + h].y = fmaf(xv, w[h][j].y, acc[a0 + h].y);
+                  acc[a0 + h].z = fmaf(xv, w[h][j].z, acc[a0 + h].z); acc[a0 + h].w = fmaf(xv, w[h][j].w, acc[a0 + h].w);
+                }
+              }
             }
           }
         }
+      } else if (((item.n_in | Cs) & 3) == 0) {
+        constexpr int NB = 16;
+        for (int n0 = 0; n0 < item.n_in; n0 += NB) {
+          float4 w[NB];
 #pragma unroll
-        for (int a = 0; a < TA; a++) {
-          acc[a].x = fmaf(item.scale, part[a].x, acc[a].x); acc[a].y = fmaf(item.scale, part[a].y, acc[a].y);
-          acc[a].z = fmaf(item.scale, part[a].z, acc[a].z); acc[a].w = fmaf(item.scale, part[a].w, acc[a].w);
+          for (int j = 0; j < NB; j++)
+            w[j] = (n0 + j < item.n_in) ? __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n0 + j) * ld))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < NB; j += 4) {
+            if (n0 + j < item.n_in) {
+#pragma unroll
+              for (int a = 0; a < TA; a++) {
+                float4 x4 = *reinterpret_cast<const float4 *>(x + a * Cs + n0 + j);
+                x4.x *= sc; x4.y *= sc; x4.z *= sc; x4.w *= sc;
+                acc[a].x = fmaf(x4.x, w[j].x, acc[a].x); acc[a].y = fmaf(x4.x, w[j].y, acc[a].y);
+                acc[a].z = fmaf(x4.x, w[j].z, acc[a].z); acc[a].w = fmaf(x4.x, w[j].w, acc[a].w);
+                acc[a].x = fmaf(x4.y, w[j + 1].x, acc[a].x); acc[a].y = fmaf(x4.y, w[j + 1].y, acc[a].y);
+                acc[a].z = fmaf(x4.y, w[j + 1].z, acc[a].z); acc[a].w = fmaf(x4.y, w[j + 1].w, acc[a].w);
+                acc[a].x = fmaf(x4.z, w[j + 2].x, acc[a].x); acc[a].y = fmaf(x4.z, w[j + 2].y, acc[a].y);
+                acc[a].z = fmaf(x4.z, w[j + 2].z, acc[a].z); acc[a].w = fmaf(x4.z, w[j + 2].w, acc[a].w);
+                acc[a].x = fmaf(x4.w, w[j + 3].x, acc[a].x); acc[a].y = fmaf(x4.w, w[j + 3].y, acc[a].y);
+                acc[a].z = fmaf(x4.w, w[j + 3].z, acc[a].z); acc[a].w = fmaf(x4.w, w[j + 3].w, acc[a].w);
+              }
+            }
+          }
+        }
+      } else {    // input widths that are no multiples of 4: scalar activation loads
+        constexpr int NB = 8;
+        for (int n0 = 0; n0 < item.n_in; n0 += NB) {
+          float4 w[NB];
+#pragma unroll
+          for (int j = 0; j < NB; j++)
+            w[j] = (n0 + j < item.n_in) ? __ldg(reinterpret_cast<const float4 *>(M + (size_t) (n0 + j) * ld))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < NB; j++) {
+            if (n0 + j < item.n_in) {
+#pragma unroll
+              for (int a = 0; a < TA; a++) {
+                const float xv = x[a * Cs + n0 + j] * sc;
+                acc[a].x = fmaf(xv, w[j].x, acc[a].x); acc[a].y = fmaf(xv, w[j].y, acc[a].y);
+                acc[a].z = fmaf(xv, w[j].z, acc[a].z); acc[a].w = fmaf(xv, w[j].w, acc[a].w);
+              }
+            }
+          }
         }
       }
-      for (int d = S >> 1; d > 0; d >>= 1) {
+    }
+    for (int d = S >> 1; d > 0; d >>= 1) {
 #pragma unroll
-        for (int a = 0; a < TA; a++) {
-          acc[a].x += __shfl_xor_sync(0xffffffffu, acc[a].x, d); acc[a].y += __shfl_xor_sync(0xffffffffu, acc[a].y, d);
-          acc[a].z += __shfl_xor_sync(0xffffffffu, acc[a].z, d); acc[a].w += __shfl_xor_sync(0xffffffffu, acc[a].w, d);
-        }
+      for (int a = 0; a < TA; a++) {
+        acc[a].x += __shfl_xor_sync(0xffffffffu, acc[a].x, d); acc[a].y += __shfl_xor_sync(0xffffffffu, acc[a].y, d);
+        acc[a].z += __shfl_xor_sync(0xffffffffu, acc[a].z, d); acc[a].w += __shfl_xor_sync(0xffffffffu, acc[a].w, d);
       }
-      if (!valid || s != 0) continue;
-      float *o = dst + (size_t) op.row_out[row] * TA * Cd + 4 * kq;
+    }
+    if (!valid || s != 0) continue;
+    float *o = dst + (size_t) op.row_out[row] * TA * Cd + 4 * kq;
+    if (((Cd | op.n_out) & 3) == 0) {
 #pragma unroll
       for (int a = 0; a < TA; a++) {
         float4 *p = reinterpret_cast<float4 *>(o + a * Cd);
@@ -112,52 +145,13 @@ __device__ __forceinline__ void mv_tile(const MVDev &op, float *sm, const int *_
         }
         *p = acc[a];
       }
-    }
-    return;
-  }
-  // general path (widths that are no multiples of 4): one output channel per group of S lanes, which share the items
-  // of the row and add their partial sums by shuffles, so that a reduce with few outputs still uses the CTA
-  int KP = 8;
-  while (KP < op.n_out) KP <<= 1;
-  const int total = op.nrows * KP;
-  int S = 1;
-  while (S < 32 && total * S * 2 <= NT) S <<= 1;
-  const int s = tid & (S - 1), per_pass = NT / S;
-  for (int base = 0; base < total; base += per_pass) {
-    const int rk = base + tid / S, row = rk / KP, k = rk - row * KP;
-    const bool valid = rk < total && k < op.n_out;
-    float acc[TA];
+    } else {
+      const int nk = min(4, op.n_out - 4 * kq);
 #pragma unroll
-    for (int a = 0; a < TA; a++) acc[a] = 0.0f;
-    if (valid) {
-      const int i0 = op.item_off[row], i1 = op.item_off[row + 1];
-      for (int it = i0 + s; it < i1; it += S) {
-        const MVItem item = op.items[it];
-        const int Cs = tch[item.src];
-        const float *x = sm + (size_t) soff[item.src] * TA + (size_t) item.irow * TA * Cs;
-        float part[TA];
-        const float *M[TA];
-#pragma unroll
-        for (int a = 0; a < TA; a++) {
-          part[a] = 0.0f;
-          M[a] = op.W + (op.elem ? (size_t) s_mu[a] * op.ty_stride : 0) + item.mat + k;
-        }
-        for (int n = 0; n < item.n_in; n++) {
-#pragma unroll
-          for (int a = 0; a < TA; a++) part[a] = fmaf(x[a * Cs + n], __ldg(M[a] + (size_t) n * op.n_out), part[a]);
-        }
-#pragma unroll
-        for (int a = 0; a < TA; a++) acc[a] = fmaf(item.scale, part[a], acc[a]);
+      for (int a = 0; a < TA; a++) {
+        const float v[4] = {acc[a].x, acc[a].y, acc[a].z, acc[a].w};
+        for (int q = 0; q < nk; q++) o[a * Cd + q] = op.accumulate ? o[a * Cd + q] + v[q] : v[q];
       }
-    }
-    for (int d = S >> 1; d > 0; d >>= 1) {
-#pragma unroll
-      for (int a = 0; a < TA; a++) acc[a] += __shfl_xor_sync(0xffffffffu, acc[a], d);
-    }
-    if (valid && s == 0) {
-      float *o = dst + (size_t) op.row_out[row] * TA * Cd + k;
-#pragma unroll
-      for (int a = 0; a < TA; a++) o[a * Cd] = op.accumulate ? o[a * Cd] + acc[a] : acc[a];
     }
   }
 }
@@ -225,11 +219,22 @@ __global__ void __launch_bounds__(NT) chain_fused_kernel(FusedLayerDev L, FusedI
     const int nta = min(TA, io.na - al0);
     if (tid < TA) s_mu[tid] = io.mu[io.a0 + al0 + min(tid, nta - 1)];
     {    // bond sums of the tile: global [f][NA][C] -> shared [f][TA][C]; atoms past the end are zero
-      const int C = io.CQ, total = io.nQ * TA * C;
+      const int C = io.CQ;
       float *q = sm + (size_t) L.soff[io.tQ] * TA;
-      for (int idx = tid; idx < total; idx += NT) {
-        const int c = idx % C, a = (idx / C) % TA, f = idx / (C * TA);
-        q[idx] = a < nta ? __ldg(io.Q + ((size_t) f * io.NA + al0 + a) * C + c) : 0.0f;
+      if ((C & 3) == 0) {
+        const int C4 = C >> 2, total = io.nQ * TA * C4;
+        for (int idx = tid; idx < total; idx += NT) {
+          const int c = idx % C4, a = (idx / C4) % TA, f = idx / (C4 * TA);
+          reinterpret_cast<float4 *>(q)[idx] =
+              a < nta ? __ldg(reinterpret_cast<const float4 *>(io.Q + ((size_t) f * io.NA + al0 + a) * C) + c)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      } else {
+        const int total = io.nQ * TA * C;
+        for (int idx = tid; idx < total; idx += NT) {
+          const int c = idx % C, a = (idx / C) % TA, f = idx / (C * TA);
+          q[idx] = a < nta ? __ldg(io.Q + ((size_t) f * io.NA + al0 + a) * C + c) : 0.0f;
+        }
       }
     }
     __syncthreads();
@@ -299,11 +304,21 @@ __global__ void __launch_bounds__(NT) chain_fused_kernel(FusedLayerDev L, FusedI
         else prod_tile<TA>(L.prod[op.y], sm, L.soff, L.tch);
         __syncthreads();
       }
-      const int C = io.CQ, total = io.nQ * TA * C;
+      const int C = io.CQ;
       const float *g = sm + (size_t) L.soff[io.tGQ] * TA;
-      for (int idx = tid; idx < total; idx += NT) {
-        const int c = idx % C, a = (idx / C) % TA, f = idx / (C * TA);
-        if (a < nta) io.gQ[((size_t) f * io.NA + al0 + a) * C + c] = g[idx];
+      if ((C & 3) == 0) {
+        const int C4 = C >> 2, total = io.nQ * TA * C4;
+        for (int idx = tid; idx < total; idx += NT) {
+          const int c = idx % C4, a = (idx / C4) % TA, f = idx / (C4 * TA);
+          if (a < nta)
+            reinterpret_cast<float4 *>(io.gQ + ((size_t) f * io.NA + al0 + a) * C)[c] = reinterpret_cast<const float4 *>(g)[idx];
+        }
+      } else {
+        const int total = io.nQ * TA * C;
+        for (int idx = tid; idx < total; idx += NT) {
+          const int c = idx % C, a = (idx / C) % TA, f = idx / (C * TA);
+          if (a < nta) io.gQ[((size_t) f * io.NA + al0 + a) * C + c] = g[idx];
+        }
       }
       __syncthreads();
     }

@@ -93,6 +93,7 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
     d.W = E.fbufs.back().get();
     d.ty_stride = o.ty_stride;
     d.n_out = o.n_out;
+    d.ldw = o.ldw;
     d.nrows = (int) o.row_out.size();
     d.accumulate = o.accumulate;
     d.elem = o.elem;

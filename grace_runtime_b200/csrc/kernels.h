@@ -18,7 +18,7 @@ struct MVDev {
   const MVItem *items;
   const float *W;
   long long ty_stride;
-  int n_out, nrows, accumulate, elem, dst;
+  int n_out, ldw, nrows, accumulate, elem, dst;
 };
 
 struct ProdDev {

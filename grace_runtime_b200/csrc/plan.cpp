@@ -103,6 +103,8 @@ RadialTable build_radial(const GraceModel &m, const std::vector<MlpLayer> &layer
 
 // ---- dense network -------------------------------------------------------------------------------------------
 
+inline int pad4(int n) { return (n + 3) / 4 * 4; }
+
 struct ReduceGroup {
   std::string name;
   std::vector<const ReduceWeights *> src;    // per source (nullptr: absent)
@@ -150,27 +152,29 @@ struct LayerBuilder {
           int gR, int gD)
   {
     const int no = w.n_out, nil = w.n_in_left, nir = w.n_in_right;
+    // weight rows are padded to a multiple of 4 outputs (16-byte loads of 4 output channels)
+    const int ldo = pad4(no), ldl = pad4(nil), ldr = pad4(nir);
     MVOp F, BL, BR;
     F.name = name + ":fwd"; BL.name = name + ":adj_left"; BR.name = name + ":adj_right";
-    F.dst = tD; F.n_out = no;
-    BL.dst = gL; BL.n_out = nil; BL.accumulate = true;
-    BR.dst = gR; BR.n_out = nir; BR.accumulate = true;
-    const int base_r = w.tiles_left * nil * no;
-    F.W.assign((size_t) base_r + (size_t) w.tiles_right * nir * no, 0.0f);
-    BL.W.assign((size_t) w.tiles_left * no * nil, 0.0f);
-    BR.W.assign((size_t) w.tiles_right * no * nir, 0.0f);
+    F.dst = tD; F.n_out = no; F.ldw = ldo;
+    BL.dst = gL; BL.n_out = nil; BL.ldw = ldl; BL.accumulate = true;
+    BR.dst = gR; BR.n_out = nir; BR.ldw = ldr; BR.accumulate = true;
+    const int base_r = w.tiles_left * nil * ldo;
+    F.W.assign((size_t) base_r + (size_t) w.tiles_right * nir * ldo, 0.0f);
+    BL.W.assign((size_t) w.tiles_left * no * ldl, 0.0f);
+    BR.W.assign((size_t) w.tiles_right * no * ldr, 0.0f);
     for (int k = 0; k < no; k++) {
       for (int n = 0; n < nil; n++)
         for (int t = 0; t < w.tiles_left; t++) {
           const float v = (float) (w.norm_left * w.w_left[((size_t) k * nil + n) * w.tiles_left + t]);
-          F.W[((size_t) t * nil + n) * no + k] = v;
-          BL.W[((size_t) t * no + k) * nil + n] = v;
+          F.W[((size_t) t * nil + n) * ldo + k] = v;
+          BL.W[((size_t) t * no + k) * ldl + n] = v;
         }
       for (int n = 0; n < nir; n++)
         for (int t = 0; t < w.tiles_right; t++) {
           const float v = (float) (w.norm_right * w.w_right[((size_t) k * nir + n) * w.tiles_right + t]);
-          F.W[(size_t) base_r + ((size_t) t * nir + n) * no + k] = v;
-          BR.W[((size_t) t * no + k) * nir + n] = v;
+          F.W[(size_t) base_r + ((size_t) t * nir + n) * ldo + k] = v;
+          BR.W[((size_t) t * no + k) * ldr + n] = v;
         }
     }
     std::map<int, std::vector<int>> by_to, by_from;
@@ -184,17 +188,17 @@ struct LayerBuilder {
       const float nof = (float) w.nof[f];
       F.row_out.push_back(f);
       F.item_off.push_back((int) F.items.size());
-      F.items.push_back({w.tile_left[f] * nil * no, tL, f, nil, nof});
-      for (int c : by_to[f]) F.items.push_back({base_r + w.tile_right[c] * nir * no, tR, w.collect_from[c], nir, nof});
+      F.items.push_back({w.tile_left[f] * nil * ldo, tL, f, nil, nof});
+      for (int c : by_to[f]) F.items.push_back({base_r + w.tile_right[c] * nir * ldo, tR, w.collect_from[c], nir, nof});
       BL.row_out.push_back(f);
       BL.item_off.push_back((int) BL.items.size());
-      BL.items.push_back({w.tile_left[f] * no * nil, gD, f, no, nof});
+      BL.items.push_back({w.tile_left[f] * no * ldl, gD, f, no, nof});
     }
     for (auto &kv : by_from) {
       BR.row_out.push_back(kv.first);
       BR.item_off.push_back((int) BR.items.size());
       for (int c : kv.second)
-        BR.items.push_back({w.tile_right[c] * no * nir, gD, w.collect_to[c], no, (float) w.nof[w.collect_to[c]]});
+        BR.items.push_back({w.tile_right[c] * no * ldr, gD, w.collect_to[c], no, (float) w.nof[w.collect_to[c]]});
     }
     const Op f = add(std::move(F));
     std::vector<Op> a;
@@ -248,6 +252,7 @@ struct LayerBuilder {
     F.name = R.name + ":fwd";
     F.dst = R.t_out;
     F.n_out = R.n_out;
+    F.ldw = pad4(R.n_out);
     F.elem = R.elem;
     const int nty = R.elem ? m.n_elements : 1;
     std::vector<int64_t> base(R.src.size(), 0);
@@ -255,7 +260,7 @@ struct LayerBuilder {
     for (size_t s = 0; s < R.src.size(); s++)
       if (R.src[s]) {
         base[s] = per_type;
-        per_type += (int64_t) R.src[s]->w_shape * R.src[s]->n_in * R.n_out;
+        per_type += (int64_t) R.src[s]->w_shape * R.src[s]->n_in * pad4(R.n_out);
       }
     F.ty_stride = R.elem ? per_type : 0;
     F.W.assign((size_t) per_type * nty, 0.0f);
@@ -263,30 +268,31 @@ struct LayerBuilder {
     for (size_t s = 0; s < R.src.size(); s++) {
       if (!R.src[s]) continue;
       const ReduceWeights &w = *R.src[s];
-      const int nin = w.n_in, ws = w.w_shape, no = R.n_out;
+      const int nin = w.n_in, ws = w.w_shape, no = R.n_out, ldf = pad4(no), ldb = pad4(nin);
       MVOp B;
       B.name = R.name + ":adj_src" + std::to_string(s);
       B.dst = R.src_grad[s];
       B.n_out = nin;
+      B.ldw = ldb;
       B.accumulate = true;
       B.elem = R.elem;
-      B.ty_stride = R.elem ? (int64_t) ws * no * nin : 0;
-      B.W.assign((size_t) ws * no * nin * nty, 0.0f);
+      B.ty_stride = R.elem ? (int64_t) ws * no * ldb : 0;
+      B.W.assign((size_t) ws * no * ldb * nty, 0.0f);
       for (int ty = 0; ty < nty; ty++)
         for (int k = 0; k < no; k++)
           for (int n = 0; n < nin; n++)
             for (int t = 0; t < ws; t++) {
               const size_t off = R.elem ? ((((size_t) ty * no + k) * nin + n) * ws + t) : (((size_t) k * nin + n) * ws + t);
               const float v = (float) (w.norm * w.W[off]);
-              F.W[(size_t) ty * per_type + base[s] + ((size_t) t * nin + n) * no + k] = v;
-              B.W[(size_t) ty * ws * no * nin + ((size_t) t * no + k) * nin + n] = v;
+              F.W[(size_t) ty * per_type + base[s] + ((size_t) t * nin + n) * ldf + k] = v;
+              B.W[(size_t) ty * ws * no * ldb + ((size_t) t * no + k) * ldb + n] = v;
             }
       std::map<int, std::vector<int>> by_ci;
       for (size_t c = 0; c < w.collect.size(); c++) by_ci[w.collect[c]].push_back((int) c);
       for (auto &kv : by_ci) {
         B.row_out.push_back(R.src_row0[s] + kv.first);
         B.item_off.push_back((int) B.items.size());
-        for (int c : kv.second) B.items.push_back({w.tile[c] * no * nin, R.t_gout, w.fo[c], no, 1.0f});
+        for (int c : kv.second) B.items.push_back({w.tile[c] * no * ldb, R.t_gout, w.fo[c], no, 1.0f});
       }
       adjoint.push_back(add(std::move(B)));
     }
@@ -302,7 +308,7 @@ struct LayerBuilder {
               F.item_off.push_back((int) F.items.size());
               any = true;
             }
-            F.items.push_back({(int) (base[s] + (int64_t) w.tile[c] * w.n_in * R.n_out), R.src_tensor[s],
+            F.items.push_back({(int) (base[s] + (int64_t) w.tile[c] * w.n_in * pad4(R.n_out)), R.src_tensor[s],
                                R.src_row0[s] + w.collect[c], w.n_in, 1.0f});
           }
       }

@@ -37,6 +37,7 @@ struct MVOp {
   std::string name;
   int dst = -1;
   int n_out = 0;
+  int ldw = 0;                 // row stride of the weight matrices: n_out rounded up to a multiple of 4
   bool accumulate = false;
   bool elem = false;           // weights per central element: matrix at mu * ty_stride + item.mat
   int64_t ty_stride = 0;
