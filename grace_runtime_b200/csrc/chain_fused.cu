@@ -15,7 +15,91 @@ namespace {
 #ifndef GB_FUSED_THREADS
 #define GB_FUSED_THREADS 512
 #endif
-constexpr int NT = GB_FUSED_THREADS;
+constexpr int NTB = GB_FUSED_THREADS;    // threads of the CTA
+constexpr int NG = 2;                     // independent groups of warps, each on its own atom tile
+constexpr int NT = NTB / NG;              // threads of a group
+
+// barrier of the calling thread's group (named barrier 1 + group)
+__device__ __forceinline__ void group_sync()
+{
+#ifdef GB_CPU_EMU
+  emu_named_barrier(1 + (int) threadIdx.x / NT, NT);
+#else
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + (int) threadIdx.x / NT), "r"(NT) : "memory");
+#endif
+}
+__device__ __forceinline__ int gtid() { return (int) threadIdx.x % NT; }
+
+// Matrix-major form of an operation with shared weights: a warp takes one unit = one weight matrix (32 of its output
+// channels, lane = channel) and keeps that matrix column in registers, one 128-byte coalesced load per input channel,
+// all in flight at once; it then applies it to the unit's few input rows for all TA atoms with the activations
+// broadcast from shared memory.  A weight is fetched once per tile and unit instead of once per row, and the only
+// global-memory latency is one round trip per unit.  Units of a slot write disjoint output rows; slots are separated
+// by a CTA barrier (an output row gets its left and right terms in consecutive slots), so the sums are ordered and
+// bit-reproducible.
+template<int TA, int NMAX, bool EXACT>
+__device__ __forceinline__ void mv_units(const MVDev &op, float *sm, const int *__restrict__ soff,
+                                         const int *__restrict__ tch)
+{
+  const int warp = gtid() >> 5, lane = gtid() & 31, nwarp = NT / 32;
+  // EXACT: every width of the operation (inputs, outputs, channel strides) equals NMAX, the usual case of equal
+  // radial and FC channel counts: no bounds predicates, constant address strides
+  const int Cd = EXACT ? NMAX : tch[op.dst];
+  float *dst = sm + (size_t) soff[op.dst] * TA;
+  for (int slot = 0; slot < op.nslots; slot++) {
+    for (int u = op.slot_off[slot] + warp; u < op.slot_off[slot + 1]; u += nwarp) {
+      const int *d = op.unit_desc + 5 * u;
+      const int n_in = EXACT ? NMAX : d[1], k = d[2] + lane;
+      const bool kv = EXACT || k < op.n_out;
+      const float *M = op.W + d[0] + (kv ? k : 0);
+      float w[NMAX];
+#pragma unroll
+      for (int n = 0; n < NMAX; n++) w[n] = (n < n_in && kv) ? __ldg(M + (size_t) n * op.ldw) : 0.0f;
+      for (int e = d[3]; e < d[4]; e++) {
+        const MVItem ent = op.unit_ent[e];
+        const int Cs = EXACT ? NMAX : tch[ent.src];
+        const float *x = sm + (size_t) soff[ent.src] * TA + (size_t) ent.irow * TA * Cs;
+        float *o = dst + (size_t) ent.mat * TA * Cd + k;
+        // TA independent sums, input channels outermost: the activation loads of all atoms for 4 channels are in
+        // flight together and the FMA chains of the atoms interleave
+        float sum[TA];
+#pragma unroll
+        for (int a = 0; a < TA; a++) sum[a] = 0.0f;
+        if ((Cs & 3) == 0) {
+#pragma unroll
+          for (int n = 0; n < NMAX; n += 4) {
+            if (n < n_in) {
+              float4 x4[TA];
+#pragma unroll
+              for (int a = 0; a < TA; a++) x4[a] = *reinterpret_cast<const float4 *>(x + a * Cs + n);
+#pragma unroll
+              for (int a = 0; a < TA; a++) {
+                sum[a] = fmaf(x4[a].x, w[n], sum[a]);
+                sum[a] = fmaf(x4[a].y, w[n + 1], sum[a]);
+                sum[a] = fmaf(x4[a].z, w[n + 2], sum[a]);
+                sum[a] = fmaf(x4[a].w, w[n + 3], sum[a]);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int n = 0; n < NMAX; n++) {
+            if (n < n_in) {
+#pragma unroll
+              for (int a = 0; a < TA; a++) sum[a] = fmaf(x[a * Cs + n], w[n], sum[a]);
+            }
+          }
+        }
+        if (kv) {
+#pragma unroll
+          for (int a = 0; a < TA; a++)
+            o[a * Cd] = (slot > 0 || op.accumulate) ? fmaf(ent.scale, sum[a], o[a * Cd]) : ent.scale * sum[a];
+        }
+      }
+    }
+    group_sync();
+  }
+}
 
 // out[row][a][k] (+)= sum_items scale * sum_n M[n][k] x[item][a][n] on the tile's shared-memory tensors.
 // A thread owns 4 consecutive output channels of one row for all TA atoms: a 16-byte weight load (rows of the weight
@@ -27,12 +111,63 @@ template<int TA>
 __device__ __forceinline__ void mv_tile(const MVDev &op, float *sm, const int *__restrict__ soff,
                                         const int *__restrict__ tch, const int *s_mu)
 {
-  const int tid = threadIdx.x;
+  const int tid = gtid();
   const int Cd = tch[op.dst], ld = op.ldw;
   float *dst = sm + (size_t) soff[op.dst] * TA;
   const int KQ = ld >> 2;
   int KQP = 1;
   while (KQP < KQ) KQP <<= 1;
+  if (op.elem) {
+    // weights of each atom's own element: nothing is shared between the atoms of the tile, so the unit of work is
+    // (row, channel quad, atom) and S lanes split the input channels of all items of the row; 8 independent 16-byte
+    // weight loads are in flight per lane before the first FMA
+    const int total_e = op.nrows * KQP * TA;
+    int S = 1;
+    while (S < 32 && total_e * S * 2 <= NT) S <<= 1;
+    const int s = tid & (S - 1), per_pass = NT / S;
+    for (int base = 0; base < total_e; base += per_pass) {
+      const int u = base + tid / S, a = u % TA, rk = u / TA, row = rk / KQP, kq = rk - row * KQP;
+      const bool valid = u < total_e && kq < KQ;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (valid) {
+        const float *Wa = op.W + (size_t) s_mu[a] * op.ty_stride + 4 * kq;
+        const int i0 = op.item_off[row], i1 = op.item_off[row + 1];
+        for (int it = i0; it < i1; it++) {
+          const MVItem item = op.items[it];
+          const int Cs = tch[item.src];
+          const float *x = sm + (size_t) soff[item.src] * TA + ((size_t) item.irow * TA + a) * Cs;
+          const float *M = Wa + item.mat;
+          constexpr int NE = 8;
+          for (int n0 = s; n0 < item.n_in; n0 += NE * S) {
+            float4 w[NE];
+            float xv[NE];
+#pragma unroll
+            for (int j = 0; j < NE; j++) {
+              const int n = n0 + j * S;
+              const bool in = n < item.n_in;
+              w[j] = in ? __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * ld)) : make_float4(0.f, 0.f, 0.f, 0.f);
+              xv[j] = in ? x[n] * item.scale : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < NE; j++) {
+              acc.x = fmaf(xv[j], w[j].x, acc.x); acc.y = fmaf(xv[j], w[j].y, acc.y);
+              acc.z = fmaf(xv[j], w[j].z, acc.z); acc.w = fmaf(xv[j], w[j].w, acc.w);
+            }
+          }
+        }
+      }
+      for (int d = S >> 1; d > 0; d >>= 1) {
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, d); acc.y += __shfl_xor_sync(0xffffffffu, acc.y, d);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, d); acc.w += __shfl_xor_sync(0xffffffffu, acc.w, d);
+      }
+      if (!valid || s != 0) continue;
+      float *o = dst + ((size_t) op.row_out[row] * TA + a) * Cd + 4 * kq;
+      const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+      const int nk = min(4, op.n_out - 4 * kq);
+      for (int q = 0; q < nk; q++) o[q] = op.accumulate ? o[q] + v[q] : v[q];
+    }
+    return;
+  }
   const int total = op.nrows * KQP;
   int S = 1;
   while (S < 32 && total * S * 2 <= NT) S <<= 1;
@@ -50,34 +185,7 @@ __device__ __forceinline__ void mv_tile(const MVDev &op, float *sm, const int *_
       const float *x = sm + (size_t) soff[item.src] * TA + (size_t) item.irow * TA * Cs;
       const float *M = op.W + item.mat + 4 * kq;
       const float sc = item.scale;
-      if (op.elem) {    // weights of each atom's element: two atoms' loads of 8 input channels in flight
-        constexpr int NE = 8;
-        for (int n0 = 0; n0 < item.n_in; n0 += NE) {
-#pragma unroll
-          for (int a0 = 0; a0 < TA; a0 += 2) {
-            float4 w[2][NE];
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-              const float *Ma = M + (size_t) s_mu[min(a0 + h, TA - 1)] * op.ty_stride;
-#pragma unroll
-              for (int j = 0; j < NE; j++)
-                w[h][j] = (n0 + j < item.n_in) ? __ldg(reinterpret_cast<const float4 *>(Ma + (size_t) (n0 + j) * ld))
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-              if (a0 + h < TA) {
-#pragma unroll
-                for (int j = 0; j < NE; j++) {
-                  const float xv = (n0 + j < item.n_in) ? x[(a0 + h) * Cs + n0 + j] * sc : 0.0f;
-                  acc[a0 + h].x = fmaf(xv, w[h][j].x, acc[a0 + h].x); acc[a0 + h].y = fmaf(xv, w[h][j].y, acc[a0 + h].y);
-                  acc[a0 + h].z = fmaf(xv, w[h][j].z, acc[a0 + h].z); acc[a0 + h].w = fmaf(xv, w[h][j].w, acc[a0 + h].w);
-                }
-              }
-            }
-          }
-        }
-      } else if (((item.n_in | Cs) & 3) == 0) {
+      if (((item.n_in | Cs) & 3) == 0) {
         constexpr int NB = 16;
         for (int n0 = 0; n0 < item.n_in; n0 += NB) {
           float4 w[NB];
@@ -156,6 +264,20 @@ __device__ __forceinline__ void mv_tile(const MVDev &op, float *sm, const int *_
   }
 }
 
+template<int TA>
+__device__ __forceinline__ void mv_any(const MVDev &op, float *sm, const int *__restrict__ soff,
+                                       const int *__restrict__ tch, const int *s_mu)
+{
+  if (op.nslots > 0) {
+    if (op.unit_exact == 32) mv_units<TA, 32, true>(op, sm, soff, tch);
+    else if (op.unit_exact == 64) mv_units<TA, 64, true>(op, sm, soff, tch);
+    else if (op.unit_nmax <= 32) mv_units<TA, 32, false>(op, sm, soff, tch);
+    else mv_units<TA, 64, false>(op, sm, soff, tch);
+  } else {
+    mv_tile<TA>(op, sm, soff, tch, s_mu);
+  }
+}
+
 // out[row][i] (+)= sum_terms coef A[a][i] B[b][i] over the TA * C values of a row, four channels per thread
 template<int TA>
 __device__ __forceinline__ void prod_tile(const ProdDev &op, float *sm, const int *__restrict__ soff,
@@ -167,7 +289,7 @@ __device__ __forceinline__ void prod_tile(const ProdDev &op, float *sm, const in
   float *D = sm + (size_t) soff[op.dst] * TA;
   if ((tch[op.dst] & 3) == 0) {
     const int Q = TAC >> 2, total = op.nrows * Q;
-    for (int idx = threadIdx.x; idx < total; idx += NT) {
+    for (int idx = gtid(); idx < total; idx += NT) {
       const int row = idx / Q, i = (idx - row * Q) * 4;
       const int t0 = op.term_off[row], t1 = op.term_off[row + 1];
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -193,7 +315,7 @@ __device__ __forceinline__ void prod_tile(const ProdDev &op, float *sm, const in
     return;
   }
   const int total = op.nrows * TAC;
-  for (int idx = threadIdx.x; idx < total; idx += NT) {
+  for (int idx = gtid(); idx < total; idx += NT) {
     const int row = idx / TAC, i = idx - row * TAC;
     const int t0 = op.term_off[row], t1 = op.term_off[row + 1];
     float acc = 0.0f;
@@ -207,20 +329,57 @@ __device__ __forceinline__ void prod_tile(const ProdDev &op, float *sm, const in
 }
 
 template<int TA>
-__global__ void __launch_bounds__(NT) chain_fused_kernel(FusedLayerDev L, FusedIO io)
+__global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, FusedIO io)
 {
   GB_DYN_SMEM(float4, smem4);
-  float *sm = reinterpret_cast<float *>(smem4);
-  __shared__ int s_mu[TA];
-  const int tid = threadIdx.x;
+  __shared__ int s_mu_all[NG][TA];
+  const int btid = threadIdx.x, grp = btid / NT, tid = btid % NT;
+  int *s_mu = s_mu_all[grp];
   const int ntiles = (io.na + TA - 1) / TA;
-  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+  // tables first, the tile's tensors behind them
+  char *tp = reinterpret_cast<char *>(smem4);
+  MVDev *s_mv = reinterpret_cast<MVDev *>(tp);            tp += sizeof(MVDev) * L.nmv;
+  ProdDev *s_prod = reinterpret_cast<ProdDev *>(tp);      tp += sizeof(ProdDev) * L.nprod;
+  int2 *s_ops = reinterpret_cast<int2 *>(tp);             tp += sizeof(int2) * (L.nfwd + L.nbwd);
+  int2 *s_zero = reinterpret_cast<int2 *>(tp);            tp += sizeof(int2) * L.nzero;
+  int *s_soff = reinterpret_cast<int *>(tp);              tp += sizeof(int) * L.ntensors;
+  int *s_tch = reinterpret_cast<int *>(tp);               tp += sizeof(int) * L.ntensors;
+  int *s_itab = reinterpret_cast<int *>(tp);              tp += sizeof(int) * L.n_itab;
+  MVItem *s_items = reinterpret_cast<MVItem *>(tp);       tp += sizeof(MVItem) * L.n_items;
+  ProdTerm *s_terms = reinterpret_cast<ProdTerm *>(tp);
+  float *sm = reinterpret_cast<float *>(smem4) + L.tab_floats + (size_t) grp * L.per_atom * TA;
+  for (int q = btid; q < L.nmv; q += NTB) {
+    MVDev d = L.mv[q];
+    d.row_out = s_itab + (d.row_out - L.itab);
+    d.item_off = s_itab + (d.item_off - L.itab);
+    d.items = s_items + (d.items - L.items);
+    d.unit_desc = s_itab + (d.unit_desc - L.itab);
+    d.slot_off = s_itab + (d.slot_off - L.itab);
+    d.unit_ent = s_items + (d.unit_ent - L.items);
+    s_mv[q] = d;
+  }
+  for (int q = btid; q < L.nprod; q += NTB) {
+    ProdDev d = L.prod[q];
+    d.row_out = s_itab + (d.row_out - L.itab);
+    d.term_off = s_itab + (d.term_off - L.itab);
+    if (L.stage_terms) d.terms = s_terms + (d.terms - L.terms);
+    s_prod[q] = d;
+  }
+  for (int q = btid; q < L.nfwd + L.nbwd; q += NTB) s_ops[q] = L.ops[q];
+  for (int q = btid; q < L.nzero; q += NTB) s_zero[q] = L.zero[q];
+  for (int q = btid; q < L.ntensors; q += NTB) { s_soff[q] = L.soff[q]; s_tch[q] = L.tch[q]; }
+  for (int q = btid; q < L.n_itab; q += NTB) s_itab[q] = L.itab[q];
+  for (int q = btid; q < L.n_items; q += NTB) s_items[q] = L.items[q];
+  if (L.stage_terms)
+    for (int q = btid; q < L.n_terms; q += NTB) s_terms[q] = L.terms[q];
+  __syncthreads();
+  for (int tile = blockIdx.x * NG + grp; tile < ntiles; tile += gridDim.x * NG) {
     const int al0 = tile * TA;                      // first atom of the tile, chunk-local
     const int nta = min(TA, io.na - al0);
     if (tid < TA) s_mu[tid] = io.mu[io.a0 + al0 + min(tid, nta - 1)];
     {    // bond sums of the tile: global [f][NA][C] -> shared [f][TA][C]; atoms past the end are zero
       const int C = io.CQ;
-      float *q = sm + (size_t) L.soff[io.tQ] * TA;
+      float *q = sm + (size_t) s_soff[io.tQ] * TA;
       if ((C & 3) == 0) {
         const int C4 = C >> 2, total = io.nQ * TA * C4;
         for (int idx = tid; idx < total; idx += NT) {
@@ -237,75 +396,75 @@ __global__ void __launch_bounds__(NT) chain_fused_kernel(FusedLayerDev L, FusedI
         }
       }
     }
-    __syncthreads();
+    group_sync();
     for (int o = 0; o < L.nfwd; o++) {
-      const int2 op = L.ops[o];
-      if (op.x == 0) mv_tile<TA>(L.mv[op.y], sm, L.soff, L.tch, s_mu);
-      else prod_tile<TA>(L.prod[op.y], sm, L.soff, L.tch);
-      __syncthreads();
+      const int2 op = s_ops[o];
+      if (op.x == 0) mv_any<TA>(s_mv[op.y], sm, s_soff, s_tch, s_mu);
+      else prod_tile<TA>(s_prod[op.y], sm, s_soff, s_tch);
+      group_sync();
     }
     if (io.mode & FUSED_STORE_MSG) {    // GRACE-2L layer 1: message rows [n][nI][CR] and rho rows [n][nrho]
       const int CR = io.CR, nI = io.nI, total = nta * nI * CR;
-      const float *I = sm + (size_t) L.soff[io.t_I] * TA;
+      const float *I = sm + (size_t) s_soff[io.t_I] * TA;
       for (int idx = tid; idx < total; idx += NT) {
         const int c = idx % CR, f = (idx / CR) % nI, a = idx / (CR * nI);
         io.I_rows[((size_t) (io.a0 + al0 + a) * nI + f) * CR + c] = I[(f * TA + a) * CR + c];
       }
-      const float *rho = sm + (size_t) L.soff[io.t_rho] * TA;
+      const float *rho = sm + (size_t) s_soff[io.t_rho] * TA;
       for (int idx = tid; idx < nta * io.nrho; idx += NT)
         io.rho_rows[(size_t) (io.a0 + al0) * io.nrho + idx] = rho[idx];
     }
     const bool bwd = io.mode & FUSED_BWD;
     if (bwd) {    // gradients start at zero; those that alias forward tensors take their storage over now
       for (int z = 0; z < L.nzero; z++) {
-        const int2 zr = L.zero[z];
+        const int2 zr = s_zero[z];
         float4 *p = reinterpret_cast<float4 *>(sm + (size_t) zr.x * TA);
         for (int idx = tid; idx < zr.y * TA / 4; idx += NT) p[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
     if (io.mode & FUSED_READOUT_1L) {
       if (tid < nta) {
-        const float *rho = sm + (size_t) L.soff[io.t_rho] * TA + tid * io.nrho;
-        float *grho = sm + (size_t) L.soff[io.t_grho] * TA + tid * io.nrho;
+        const float *rho = sm + (size_t) s_soff[io.t_rho] * TA + tid * io.nrho;
+        float *grho = sm + (size_t) s_soff[io.t_grho] * TA + tid * io.nrho;
         io.e_atom[io.a0 + al0 + tid] = readout_1l_atom(io.ro, rho, s_mu[tid], grho, bwd);
       } else if (tid < TA && bwd) {
-        float *grho = sm + (size_t) L.soff[io.t_grho] * TA + tid * io.nrho;
+        float *grho = sm + (size_t) s_soff[io.t_grho] * TA + tid * io.nrho;
         for (int k = 0; k < io.nrho; k++) grho[k] = 0.0f;
       }
     }
     if (io.mode & FUSED_READOUT_2L) {
       if (tid < nta) {
         const size_t i = io.a0 + al0 + tid;
-        const float *I2 = sm + (size_t) L.soff[io.t_I2] * TA + tid * io.nrho;
-        float *gI2 = sm + (size_t) L.soff[io.t_gI2] * TA + tid * io.nrho;
+        const float *I2 = sm + (size_t) s_soff[io.t_I2] * TA + tid * io.nrho;
+        float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + tid * io.nrho;
         io.e_atom[i] = readout_2l_atom(io.ro, io.rho_rows + i * io.nrho, I2, s_mu[tid], io.grho_rows + i * io.nrho,
                                        gI2, bwd);
       } else if (tid < TA && bwd) {
-        float *gI2 = sm + (size_t) L.soff[io.t_gI2] * TA + tid * io.nrho;
+        float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + tid * io.nrho;
         for (int k = 0; k < io.nrho; k++) gI2[k] = 0.0f;
       }
     }
     if (io.mode & FUSED_LOAD_SEED) {    // GRACE-2L layer 1 reverse: dE/dI and dE/drho of each atom
       const int CR = io.CR, nI = io.nI, total = TA * nI * CR;
-      float *gI = sm + (size_t) L.soff[io.t_gI] * TA;
+      float *gI = sm + (size_t) s_soff[io.t_gI] * TA;
       for (int idx = tid; idx < total; idx += NT) {
         const int c = idx % CR, a = (idx / CR) % TA, f = idx / (CR * TA);
         gI[idx] = a < nta ? io.gI_rows[((size_t) (io.a0 + al0 + a) * nI + f) * CR + c] : 0.0f;
       }
-      float *grho = sm + (size_t) L.soff[io.t_grho] * TA;
+      float *grho = sm + (size_t) s_soff[io.t_grho] * TA;
       for (int idx = tid; idx < TA * io.nrho; idx += NT)
         grho[idx] = idx < nta * io.nrho ? (float) io.grho_rows[(size_t) (io.a0 + al0) * io.nrho + idx] : 0.0f;
     }
-    __syncthreads();
+    group_sync();
     if (bwd) {
       for (int o = L.nfwd; o < L.nfwd + L.nbwd; o++) {
-        const int2 op = L.ops[o];
-        if (op.x == 0) mv_tile<TA>(L.mv[op.y], sm, L.soff, L.tch, s_mu);
-        else prod_tile<TA>(L.prod[op.y], sm, L.soff, L.tch);
-        __syncthreads();
+        const int2 op = s_ops[o];
+        if (op.x == 0) mv_any<TA>(s_mv[op.y], sm, s_soff, s_tch, s_mu);
+        else prod_tile<TA>(s_prod[op.y], sm, s_soff, s_tch);
+        group_sync();
       }
       const int C = io.CQ;
-      const float *g = sm + (size_t) L.soff[io.tGQ] * TA;
+      const float *g = sm + (size_t) s_soff[io.tGQ] * TA;
       if ((C & 3) == 0) {
         const int C4 = C >> 2, total = io.nQ * TA * C4;
         for (int idx = tid; idx < total; idx += NT) {
@@ -320,7 +479,7 @@ __global__ void __launch_bounds__(NT) chain_fused_kernel(FusedLayerDev L, FusedI
           if (a < nta) io.gQ[((size_t) f * io.NA + al0 + a) * C + c] = g[idx];
         }
       }
-      __syncthreads();
+      group_sync();
     }
   }
 }
@@ -334,20 +493,23 @@ template<int TA> void launch_ta(const FusedLayerDev &L, const FusedIO &io, int g
     attr_smem = smem;
   }
 #endif
-  GB_LAUNCH((chain_fused_kernel<TA>), grid, NT, smem, L, io);
+  GB_LAUNCH((chain_fused_kernel<TA>), grid, NTB, smem, L, io);
 }
 
 }    // namespace
 
+int fused_groups() { return NG; }
+
 void launch_chain_fused(int TA, const FusedLayerDev &L, const FusedIO &io, int grid)
 {
   if (io.na == 0) return;
-  const size_t smem = (size_t) L.per_atom * TA * sizeof(float);
+  const size_t smem = ((size_t) L.tab_floats + (size_t) L.per_atom * TA * fused_groups()) * sizeof(float);
   switch (TA) {
     case 1: launch_ta<1>(L, io, grid, smem); break;
     case 2: launch_ta<2>(L, io, grid, smem); break;
     case 3: launch_ta<3>(L, io, grid, smem); break;
     case 4: launch_ta<4>(L, io, grid, smem); break;
+    case 5: launch_ta<5>(L, io, grid, smem); break;
     case 6: launch_ta<6>(L, io, grid, smem); break;
     case 8: launch_ta<8>(L, io, grid, smem); break;
     default: throw DeviceError("fused dense network: unsupported atom tile");

@@ -76,18 +76,55 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
   E.z.set_label("engine:chemical_weights");
   E.tab.upload(P.radial.tab);
   E.z.upload(P.z);
-  auto up_i = [&](const std::vector<int> &v) {
-    E.ibufs.emplace_back("engine:tables");
-    E.ibufs.back().upload(v);
-    return E.ibufs.back().get();
+  // all index tables of the layer in one buffer each (the fused kernel copies them to shared memory as a whole)
+  std::vector<int> itab;
+  std::vector<MVItem> items;
+  std::vector<ProdTerm> terms;
+  std::vector<size_t> mv_row, mv_off, mv_item, mv_ud, mv_so, mv_ue, pr_row, pr_off, pr_term;
+  auto put = [&](const std::vector<int> &v) {
+    const size_t at = itab.size();
+    itab.insert(itab.end(), v.begin(), v.end());
+    return at;
   };
   for (const MVOp &o : P.mv) {
+    mv_row.push_back(put(o.row_out));
+    mv_off.push_back(put(o.item_off));
+    mv_item.push_back(items.size());
+    items.insert(items.end(), o.items.begin(), o.items.end());
+    mv_ud.push_back(put(o.unit_desc));
+    mv_so.push_back(put(o.slot_off));
+    mv_ue.push_back(items.size());
+    items.insert(items.end(), o.unit_ent.begin(), o.unit_ent.end());
+  }
+  for (const ProdOp &o : P.prod) {
+    pr_row.push_back(put(o.row_out));
+    pr_off.push_back(put(o.term_off));
+    pr_term.push_back(terms.size());
+    terms.insert(terms.end(), o.terms.begin(), o.terms.end());
+  }
+  E.itab.set_label("engine:tables"); E.items.set_label("engine:tables"); E.terms.set_label("engine:tables");
+  E.itab.upload(itab);
+  E.items.upload(items);
+  E.terms.upload(terms);
+  E.n_itab = (int) itab.size(); E.n_items = (int) items.size(); E.n_terms = (int) terms.size();
+  for (size_t q = 0; q < P.mv.size(); q++) {
+    const MVOp &o = P.mv[q];
     MVDev d{};
-    d.row_out = up_i(o.row_out);
-    d.item_off = up_i(o.item_off);
-    E.itembufs.emplace_back("engine:tables");
-    E.itembufs.back().upload(o.items);
-    d.items = E.itembufs.back().get();
+    d.row_out = E.itab.get() + mv_row[q];
+    d.item_off = E.itab.get() + mv_off[q];
+    d.items = E.items.get() + mv_item[q];
+    d.unit_desc = E.itab.get() + mv_ud[q];
+    d.slot_off = E.itab.get() + mv_so[q];
+    d.unit_ent = E.items.get() + mv_ue[q];
+    d.nslots = o.slot_off.empty() ? 0 : (int) o.slot_off.size() - 1;
+    d.unit_nmax = 0;
+    bool same = true;
+    for (const MVItem &it : o.items) {
+      d.unit_nmax = std::max(d.unit_nmax, it.n_in);
+      same = same && it.n_in == o.n_out && P.tensors[it.src].channels == o.n_out;
+    }
+    same = same && P.tensors[o.dst].channels == o.n_out && (o.n_out == 32 || o.n_out == 64);
+    d.unit_exact = same ? o.n_out : 0;
     E.fbufs.emplace_back("engine:weights");
     E.fbufs.back().upload(o.W);
     d.W = E.fbufs.back().get();
@@ -100,13 +137,12 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
     d.dst = o.dst;
     E.mv.push_back(d);
   }
-  for (const ProdOp &o : P.prod) {
+  for (size_t q = 0; q < P.prod.size(); q++) {
+    const ProdOp &o = P.prod[q];
     ProdDev d{};
-    d.row_out = up_i(o.row_out);
-    d.term_off = up_i(o.term_off);
-    E.termbufs.emplace_back("engine:tables");
-    E.termbufs.back().upload(o.terms);
-    d.terms = E.termbufs.back().get();
+    d.row_out = E.itab.get() + pr_row[q];
+    d.term_off = E.itab.get() + pr_off[q];
+    d.terms = E.terms.get() + pr_term[q];
     d.nrows = (int) o.row_out.size();
     d.accumulate = o.accumulate;
     d.dst = o.dst;
@@ -279,13 +315,31 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
   F.nzero = (int) zero.size();
   F.per_atom = (int) at;
   E.q_floats = (long long) P.tensors[P.tQ].nfuncs * P.tensors[P.tQ].channels;
+  F.nmv = (int) E.mv.size();
+  F.nprod = (int) E.prod.size();
+  F.ntensors = (int) nt;
+  F.itab = E.itab.get();
+  F.items = E.items.get();
+  F.terms = E.terms.get();
+  F.n_itab = E.n_itab;
+  F.n_items = E.n_items;
+  F.n_terms = E.n_terms;
+  // shared memory: the tables, then TA atoms of tensors; the product terms are staged only if a tile still fits
   const long long limit = 227 * 1024 - 1024;
+  auto tab_bytes = [&](bool with_terms) {
+    long long b = (long long) sizeof(MVDev) * F.nmv + sizeof(ProdDev) * F.nprod + sizeof(int2) * (ops.size() + zero.size()) +
+                  sizeof(int) * (2 * nt + E.n_itab) + sizeof(MVItem) * E.n_items + (with_terms ? sizeof(ProdTerm) * E.n_terms : 0);
+    return (b + 15) / 16 * 16;
+  };
+  F.stage_terms = tab_bytes(true) + at * 4 * fused_groups() <= limit;
+  const long long tb = tab_bytes(F.stage_terms);
+  F.tab_floats = (int) (tb / 4);
   E.fused_TA = 0;
-  for (int ta : {8, 6, 4, 3, 2, 1})
-    if (at * 4 * ta <= limit) { E.fused_TA = ta; break; }
+  for (int ta : {8, 6, 5, 4, 3, 2, 1})
+    if (tb + at * 4 * ta * fused_groups() <= limit) { E.fused_TA = ta; break; }
   if (const char *env = getenv("GRACE_B200_TILE_ATOMS")) {
     const int ta = atoi(env);
-    if ((ta == 1 || ta == 2 || ta == 3 || ta == 4 || ta == 6 || ta == 8) && at * 4 * ta <= limit) E.fused_TA = ta;
+    if (ta >= 1 && ta <= 8 && ta != 7 && tb + at * 4 * ta * fused_groups() <= limit) E.fused_TA = ta;
   }
   GB_CUDA(cudaStreamSynchronize(dev().stream));
 }
@@ -321,10 +375,8 @@ void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const i
   io.a0 = a0;
   io.na = na;
   const int TA = E.fused_TA;
-  const int ntiles = (na + TA - 1) / TA;
-  const size_t smem = (size_t) E.fused.per_atom * TA * 4;
-  const int per_sm = (int) std::max<size_t>(1, std::min<size_t>(4, (size_t) (227 * 1024) / (smem + 1024)));
-  launch_chain_fused(TA, E.fused, io, std::min(ntiles, dev().sm_count * per_sm));
+  const int ntiles = (na + TA - 1) / TA, nctas = (ntiles + fused_groups() - 1) / fused_groups();
+  launch_chain_fused(TA, E.fused, io, std::min(nctas, dev().sm_count));
 }
 
 // bond sums -> fused dense network (forward, readout, reverse in one kernel) -> bond forces; only the bond-sum tensor

@@ -18,10 +18,11 @@ namespace gb {
 struct LayerEngine {
   const LayerPlan *plan = nullptr;
   DBuf<float> tab, z;
-  std::vector<DBuf<int>> ibufs;
+  DBuf<int> itab;            // row / offset tables of every operation
+  DBuf<MVItem> items;
+  DBuf<ProdTerm> terms;
+  int n_itab = 0, n_items = 0, n_terms = 0;
   std::vector<DBuf<float>> fbufs;
-  std::vector<DBuf<MVItem>> itembufs;
-  std::vector<DBuf<ProdTerm>> termbufs;
   std::vector<MVDev> mv;
   std::vector<ProdDev> prod;
   std::vector<long long> toff;    // offset of each tensor in floats per atom

@@ -19,6 +19,13 @@ struct MVDev {
   const float *W;
   long long ty_stride;
   int n_out, ldw, nrows, accumulate, elem, dst;
+  // matrix-major work list (plan.h MVOp::unit_desc); nslots == 0: none
+  const int *unit_desc;
+  const int *slot_off;
+  const MVItem *unit_ent;
+  int nslots;
+  int unit_nmax;     // largest n_in of the units
+  int unit_exact;    // 32 or 64 when every n_in, n_out and channel stride of the operation equals it, else 0
 };
 
 struct ProdDev {
@@ -87,6 +94,15 @@ struct FusedLayerDev {
   const int2 *zero;     // (offset, length) in floats per atom of the gradients cleared before the reverse operations
   int nzero;
   int per_atom;         // shared-memory floats per atom
+  // the tables every operation reads (copied to shared memory once per CTA: reading them from global memory is a chain
+  // of dependent L2 round trips per operation and tile)
+  int nmv, nprod, ntensors;
+  const int *itab;      // row_out / item_off / term_off arrays of all operations, contiguous
+  const MVItem *items;
+  const ProdTerm *terms;
+  int n_itab, n_items, n_terms;
+  int stage_terms;      // the product terms fit the shared memory next to the tile
+  int tab_floats;       // shared-memory floats in front of the tile's tensors that hold the tables
 };
 
 struct FusedIO {
@@ -107,6 +123,8 @@ struct FusedIO {
 
 // TA: atoms per tile (1, 2, 3, 4, 6, 8); grid CTAs loop over the tiles
 void launch_chain_fused(int TA, const FusedLayerDev &L, const FusedIO &io, int grid);
+// independent warp groups per CTA, each working on its own tile of TA atoms
+int fused_groups();
 
 // chunk tensor [nf][NA][C] <-> per-atom rows [n][nf][C] (message I, its gradient) and [n][C] (rho)
 void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0);

@@ -444,6 +444,41 @@ void compact_rows(LayerPlan &P)
   }
 }
 
+// matrix-major work list of an operation with shared weights (see MVOp::unit_desc)
+void build_units(MVOp &o)
+{
+  o.unit_desc.clear();
+  o.slot_off.clear();
+  o.unit_ent.clear();
+  if (o.elem) return;
+  for (const MVItem &it : o.items)
+    if (it.n_in > 64) return;
+  constexpr int RMAX = 3;    // input rows per unit: enough units per slot to occupy the warps of a CTA
+  int nslots = 0;
+  for (size_t r = 0; r + 1 < o.item_off.size(); r++) nslots = std::max(nslots, o.item_off[r + 1] - o.item_off[r]);
+  o.slot_off.push_back(0);
+  for (int slot = 0; slot < nslots; slot++) {
+    std::map<std::pair<int, int>, std::vector<MVItem>> by_mat;    // (mat, n_in) -> entries
+    for (size_t r = 0; r + 1 < o.item_off.size(); r++) {
+      const int i = o.item_off[r] + slot;
+      if (i >= o.item_off[r + 1]) continue;
+      MVItem e = o.items[i];
+      const int mat = e.mat;
+      e.mat = o.row_out[r];
+      by_mat[{mat, e.n_in}].push_back(e);
+    }
+    for (auto &kv : by_mat)
+      for (size_t c0 = 0; c0 < kv.second.size(); c0 += RMAX)
+        for (int k0 = 0; k0 < o.n_out; k0 += 32) {
+          const int e0 = (int) o.unit_ent.size();
+          for (size_t c = c0; c < std::min(kv.second.size(), c0 + RMAX); c++) o.unit_ent.push_back(kv.second[c]);
+          const int d[5] = {kv.first.first, kv.first.second, k0, e0, (int) o.unit_ent.size()};
+          o.unit_desc.insert(o.unit_desc.end(), d, d + 5);
+        }
+    o.slot_off.push_back((int) o.unit_desc.size() / 5);
+  }
+}
+
 }    // namespace
 
 ModelPlan build_plan(const GraceModel &m, int spline_n)
@@ -477,6 +512,8 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
     L.tQ = B.tensor("A", nlm, c.c0);
     L.tGQ = B.tensor("gA", nlm, c.c0, true);
     L.tensors[L.tQ].external = L.tensors[L.tGQ].external = true;
+    // with AAA = AA1 x A1 no adjoint reads A itself, so its gradient may take over its storage
+    if (!c.xxx_right_x0) L.tensors[L.tGQ].alias = L.tQ;
     std::vector<const ReduceWeights *> rXX{&m.rho[1]}, rXXX{&m.rho[2]}, rXXXX{c.order4 ? &m.rho[3] : nullptr};
     if (m.layers == 2) {
       rXX.push_back(&m.I1[1]);
@@ -578,6 +615,8 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
   }
   compact_rows(P.L1);
   if (m.layers == 2) compact_rows(P.L2);
+  for (LayerPlan *L : {&P.L1, &P.L2})
+    for (MVOp &o : L->mv) build_units(o);
   // readout
   for (const auto &Lr : m.energy_mlp) {
     P.eW.insert(P.eW.end(), Lr.W.begin(), Lr.W.end());

@@ -45,6 +45,12 @@ struct MVOp {
   std::vector<int> item_off;   // rows + 1
   std::vector<MVItem> items;
   std::vector<float> W;
+  // the same work ordered by weight matrix for the fused kernel: a unit is one matrix (a block of 32 of its output
+  // channels) applied to up to a few input rows; units of one slot never write the same output row, slots run one
+  // after the other (slot = position of an item in its row).  Per unit 5 ints: mat, n_in, k0, first entry, end entry;
+  // an entry is an MVItem whose `mat` field holds the OUTPUT row.  Empty for per-element weights or n_in > 64.
+  std::vector<int> unit_desc, slot_off;
+  std::vector<MVItem> unit_ent;
   double flops_per_atom() const;
 };
 

@@ -271,21 +271,23 @@ def test_injected_failures_recover(backend, models, cells, tmp_path_factory):
         backend._debug_fail_launch(0)
     r = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
     assert np.abs(r["forces"] - ok["forces"]).max() < 2e-5
-    # automatic chunk: 2000 atoms in one pass -> retried with 1024 atoms per pass
+    # automatic chunk: 2000 atoms in one pass -> retried with the power of two below n / 2 = 512 atoms per pass
     path, els, big = _config_case(tmp_path_factory, "1l", "bcc", 3.165, (10, 10, 10), 1, 0.05, seed=2)
     mb = backend.Model(path)
     ref = _compute(backend, mb, big)
     sb = backend.System(mb, els, chunksize=-1)
+    sb.release_buffers()           # the work buffers are shared by the Systems of a model: grown again below
     backend._debug_fail_alloc("work:", 1)
     try:
         rb = sb.compute(big["types"], big["positions"], big["cell"], big["pbc"])
     finally:
         backend._debug_fail_alloc("", 0)
-    assert sb.chunksize == 1024
+    assert sb.chunksize == 512
     assert abs(rb["energy"] - ref["energy"]) / big["n"] < 2e-6
     assert np.abs(rb["forces"] - ref["forces"]).max() < 2e-5
     # fixed chunk: the failure is reported, the System works afterwards
     sf = backend.System(mb, els, chunksize=512)
+    sf.release_buffers()
     backend._debug_fail_alloc("work:", 1)
     try:
         with pytest.raises(RuntimeError, match="failed to allocate"):
