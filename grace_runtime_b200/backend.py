@@ -39,6 +39,7 @@ SIGNATURES = {
     "grace_kernel_launches": (C.c_uint64, []),
     "grace_profile_enable": (_I, [_I]),
     "grace_profile_report": (_I, [_P, C.c_size_t]),
+    "grace_sum_rows_static": (_I, [_P, _I64, _I, _P]),
     "grace_model_load": (_I, [C.c_char_p, _I, _P]),
     "grace_model_layers": (_I, [_P]),
     "grace_model_has_uq": (_I, [_P]),
@@ -149,6 +150,13 @@ def memory_info():
 
 def kernel_launches():
     return int(load_library().grace_kernel_launches())
+
+
+def sum_rows_static(d_values, n, k, d_out):
+    """Column sums of the device matrix values[n][k] (doubles, row-major; device addresses as integers) into the
+    device array out[k], with no device allocation: the partial sums use a static device array shared by all calls
+    (k <= 8, n <= 16,777,216; beyond that ValueError).  No counterpart in the reference."""
+    _check(load_library().grace_sum_rows_static(C.c_void_p(int(d_values)), int(n), int(k), C.c_void_p(int(d_out))))
 
 
 def profile_enable(on=True):

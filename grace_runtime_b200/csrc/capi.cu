@@ -231,6 +231,13 @@ int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, 
   });
 }
 
+#ifndef GB_CPU_EMU
+int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_out)
+{
+  return guarded([&] { static_sum(d_values, (long long) n, k, d_out); });
+}
+#endif
+
 int64_t grace_system_rebuilds(const grace_system *s) { return s ? s->s->rebuilds : 0; }
 int grace_system_chunksize(const grace_system *s) { return s ? s->s->last_chunk : 0; }
 int grace_system_release_buffers(grace_system *s)

@@ -135,6 +135,11 @@ void launch_chunk_from_rows_f64(float *t, const double *rows, int nf, int C, int
 void launch_force_gather(const long long *off, const int *rev, const float *fv, const int *perm, double *forces,
                          int n);
 // per-structure sums of per-atom values: out[s][k] = sum_{i in [seg[s], seg[s+1])} v[i][k]
+// column sums of values[n][K] into out[K] with the partial sums in a static device array: no allocation
+// (static_sum.cu); throws InvalidArgument beyond static_sum_max_rows() / static_sum_max_cols()
+void static_sum(const double *d_values, long long n, int K, double *d_out);
+long long static_sum_max_rows();
+int static_sum_max_cols();
 void launch_segment_sum(const double *v, int K, const int *seg, int nseg, double *out);
 // out[perm[i]] = v[i]
 void launch_scatter_f64(const double *v, const int *perm, double *out, int n);

@@ -70,6 +70,17 @@ uint64_t grace_kernel_launches(void);
 int grace_profile_enable(int on);
 int grace_profile_report(char *buf, size_t len);
 
+/* Column sums of a row-major device matrix values[n][k] of doubles (per-atom energies, k = 1, or per-atom virial rows,
+ * k = 6, to totals) into out[k] on the device, WITHOUT any device allocation.  No counterpart in the reference.
+ * The per-block partial sums live in one statically allocated device array (65,792 bytes per device) instead of
+ * allocator memory, for callers that cannot allocate when they need the sum: a host code that has given all free
+ * device memory to its own pool, or a time-step loop that must not meet the device-wide synchronisation an
+ * allocation can imply.  Limits: k <= 8, n <= 16,777,216 rows; larger sizes return GRACE_INVALID_ARGUMENT.
+ * Deterministic (fixed summation tree).  Runs on the library's stream and returns after it has finished.  Every call
+ * shares the array, so calls must not overlap in time on a device (the library's lock orders calls made through
+ * this ABI).  The first call on a device also looks up the array's address: make it before any stream capture. */
+int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_out);
+
 /* ---- Model (kk_api.h:51-64): a loaded GRACE-1L / GRACE-2L kokkos.npz ---- */
 /* spline: intervals of the radial cubic Hermite tables (reference default 1024; >= 16) */
 int grace_model_load(const char *path, int spline, grace_model **out);   /* Model(path, spline) */
