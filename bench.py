@@ -116,34 +116,55 @@ def algorithmic_bytes(kernel, model_cfg, n_atoms, n_bonds, slots):
 
 def run_ours(args, rank, world, local_rank):
     import torch
+    import torch.distributed as dist
 
     from grace_runtime_b200 import backend as B
+    from grace_runtime_b200 import domain
 
-    if world > 1:
-        raise SystemExit("bench.py: domain-decomposed runs are not implemented in this build (N = 1 only)")
     torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     B.initialize(local_rank)
     tmp = tempfile.mkdtemp(prefix="grace_bench_")
-    path, species, types, pos, cell, pbc = make_workload(args.workload, tmp)
+    path, species, types, pos, cell, pbc = make_workload(args.workload, tmp)     # every rank: the same seeded structure
     n = len(types)
+    wl = WORKLOADS[args.workload]
     model = B.Model(path)
-    system = B.System(model, species, skin=0.5, chunksize=args.chunk)
-    dev = torch.device("cuda", local_rank)
-    d_types = torch.from_numpy(types).to(dev)
-    d_pos = torch.from_numpy(pos).to(dev)
-    d_e = torch.zeros(1, dtype=torch.float64, device=dev)
-    d_v = torch.zeros(6, dtype=torch.float64, device=dev)
-    d_f = torch.zeros((n, 3), dtype=torch.float64, device=dev)
-    torch.cuda.synchronize()
+    skin = 0.5
+    cutoff = B.System(model, species, skin=skin).cutoff
+    # slabs across the longest cell direction, one per rank, with a ghost halo of layers x (cutoff + skin)
+    plan = domain.make_plan(pos, cell, pbc, world, model.layers, cutoff, skin)
+    ds = domain.DistributedSystem(plan, rank, types, pos, species=species, model=model, skin=skin,
+                                  chunksize=args.chunk, device=dev)
+    system = ds.system
+    n_sub, n_own = ds.n, ds.nlocal
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def step_device():
-        system.compute_device(n, d_types.data_ptr(), d_pos.data_ptr(), cell, pbc, d_e.data_ptr(), d_f.data_ptr(),
-                              d_v.data_ptr())
-        return system.stage_ms
+        """device time of one step on this rank: the library's own events on its launch stream around the evaluation,
+        torch events on the stream of the collectives around the exchange (the two run one after the other)"""
+        ds.evaluate_local()
+        ms = system.stage_ms
+        t = ms["total"]
+        if world > 1:
+            ev0.record()
+            ds.exchange()
+            ev1.record()
+            ev1.synchronize()
+            t += ev0.elapsed_time(ev1)
+        return t, ms
 
     for _ in range(max(args.warmup, 1)):
         step_device()
-    torch.cuda.synchronize()
+    barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
     l0 = B.kernel_launches()
@@ -151,48 +172,79 @@ def run_ours(args, rank, world, local_rank):
     t0 = time.perf_counter()
     dev_ms, stages = 0.0, dict(neighbor_list=0.0, bonds=0.0, forward=0.0, reverse=0.0)
     for _ in range(args.steps):
-        ms = step_device()
-        dev_ms += ms["total"]
+        t, ms = step_device()
+        dev_ms += t
         for k in stages:
             stages[k] += ms[k] / args.steps
-    torch.cuda.synchronize()
+    barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
     prof = B.profile_report()
     B.profile_enable(False)
     launches = B.kernel_launches() - l0
     clocks = sampler.stop()
-    ms_per_step = dev_ms / args.steps
-    value = ms_per_step * 1e3 / n          # us per atom on this one GPU
-    energy = float(d_e.item())
+    times = torch.tensor([dev_ms / args.steps, wall_ms / args.steps], dtype=torch.float64, device=dev)
+    counts = torch.tensor([float(launches), float(n_sub), float(n_own)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(counts, op=dist.ReduceOp.SUM)
+    ms_per_step, wall_ms_per_step = float(times[0]), float(times[1])
+    value = ms_per_step * 1e3 * world / n          # GPU-microseconds per atom: step time x GPUs / atoms
+    energy = ds.energy
 
-    # end to end: host buffers in pinned memory through the host-pointer entry point, copies inside the timed region
-    h_types = torch.from_numpy(types).pin_memory().numpy()
-    h_pos = torch.from_numpy(pos).pin_memory().numpy()
-    h_f = torch.zeros((n, 3), dtype=torch.float64).pin_memory().numpy()
-    lib = B.load_library()
-    import ctypes as C
-    e1, v6 = np.zeros(1), np.zeros(6)
-    pbc8 = np.ascontiguousarray(pbc, dtype=np.uint8)
-    cell64 = np.ascontiguousarray(cell, dtype=np.float64)
+    # end to end with host buffers
+    if world == 1:
+        # the reference-facing host-pointer entry point, pinned host memory, copies inside the timed region
+        h_types = torch.from_numpy(types).pin_memory().numpy()
+        h_pos = torch.from_numpy(pos).pin_memory().numpy()
+        h_f = torch.zeros((n, 3), dtype=torch.float64).pin_memory().numpy()
+        lib = B.load_library()
+        import ctypes as C
+        e1, v6 = np.zeros(1), np.zeros(6)
+        pbc8 = np.ascontiguousarray(pbc, dtype=np.uint8)
+        cell64 = np.ascontiguousarray(cell, dtype=np.float64)
 
-    def step_host():
-        rc = lib.grace_system_compute(system._h, n, h_types.ctypes.data_as(C.c_void_p), h_pos.ctypes.data_as(C.c_void_p),
-                                      cell64.ctypes.data_as(C.c_void_p), pbc8.ctypes.data_as(C.c_void_p), 0,
-                                      e1.ctypes.data_as(C.c_void_p), v6.ctypes.data_as(C.c_void_p),
-                                      h_f.ctypes.data_as(C.c_void_p), None)
-        if rc:
-            raise RuntimeError(lib.grace_last_error().decode())
+        def step_host():
+            rc = lib.grace_system_compute(system._h, n, h_types.ctypes.data_as(C.c_void_p),
+                                          h_pos.ctypes.data_as(C.c_void_p), cell64.ctypes.data_as(C.c_void_p),
+                                          pbc8.ctypes.data_as(C.c_void_p), 0, e1.ctypes.data_as(C.c_void_p),
+                                          v6.ctypes.data_as(C.c_void_p), h_f.ctypes.data_as(C.c_void_p), None)
+            if rc:
+                raise RuntimeError(lib.grace_last_error().decode())
+        h2d, d2h = 28 * n, 24 * n + 56
+    else:
+        # every rank: its sub-system's positions from pinned host memory, its owned forces and the totals back
+        h_pos = torch.from_numpy(ds.pos).pin_memory()
+        h_f = torch.zeros((max(n_own, 1), 3), dtype=torch.float64).pin_memory()
+        h_ev = torch.zeros(7, dtype=torch.float64).pin_memory()
+
+        def step_host():
+            ds.load_positions(h_pos)
+            torch.cuda.current_stream().synchronize()
+            ds.step()
+            h_f[:n_own].copy_(ds.owned_forces, non_blocking=True)
+            h_ev.copy_(ds.d_ev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        h2d, d2h = 24 * int(counts[1]), 24 * n + 56 * world
 
     for _ in range(max(args.warmup, 3)):     # the first host-path calls grow the staging buffers and touch the pinned pages
         step_host()
+    barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step_host()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    e2e = {"value": e2e_ms * 1e3 / n, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(28 * n),
-           "d2h_bytes_per_step": int(24 * n + 56)}
+    barrier()
+    e2e_t = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(e2e_t[0])
+    e2e = {"value": e2e_ms * 1e3 * world / n, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(h2d),
+           "d2h_bytes_per_step": int(d2h)}
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
-    # dominant kernel and its roofline
+    # dominant kernel of rank 0 and its roofline
     peaks = {}
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
@@ -203,39 +255,63 @@ def run_ours(args, rank, world, local_rank):
     shares = {k: {"launches": v[0], "ms_per_step": v[1] / args.steps, "share": v[1] / tot} for k, v in kern[:8]}
     top, (top_n, top_ms) = kern[0]
     top = top.strip("()").split("<")[0]
-    n_bonds = None
-    roof = {"bound": "hbm", "kernel": top, "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "traffic": None}
-    # bonds inside the cutoff and list slots: from the model of the workload (58 bonds per atom in bcc at 6 A;
-    # slots with the 0.5 A skin scale as (6.5 / 6)^3)
-    wl = WORKLOADS[args.workload]
+    # atoms this rank evaluates, their bonds inside the cutoff and list slots: from the lattice of the workload (58
+    # bonds per atom in bcc at 6 A, 78 in fcc; slots with the 0.5 A skin scale as (6.5 / 6)^3)
     per_atom_bonds = 58.0 if wl["lattice"] == "bcc" else 78.0
-    n_bonds = per_atom_bonds * n
-    slots = n_bonds * (6.5 / 6.0) ** 3
-    ab = algorithmic_bytes(top, wl["cfg"], n, n_bonds, slots)
-    if ab is not None:
-        passes_per_step = 1.0      # every bond / gather kernel covers the structure once per step (in chunks)
-        per_launch_bytes = ab * passes_per_step * args.steps / top_n
-        per_launch_s = top_ms / top_n * 1e-3
-        roof.update(achieved=per_launch_bytes / per_launch_s / 1e9, algorithmic_bytes_per_launch=per_launch_bytes,
-                    avg_launch_ms=top_ms / top_n)
-        roof["frac"] = roof["achieved"] / hbm_peak
+    n_bonds = per_atom_bonds * n_own
+    slots = per_atom_bonds * n_sub * (6.5 / 6.0) ** 3
+    per_launch_ms = top_ms / top_n
+    sm_mhz = clocks.get("sm_mhz") or 1965.0
+    if top == "chain_fused_kernel":
+        # FMA-bound: useful fp32 multiply-adds of the dense network (forward + adjoints) against the SIMT peak of the
+        # SMs at the clock sampled during the run
+        # (GRACE-2L evaluates layer 1 twice, once more for the reverse pass: only one is counted as useful)
+        flop = model.dense_flops * n_own * args.steps / top_n
+        peak_tf = 148 * 128 * 2 * sm_mhz * 1e6 / 1e12
+        ach = flop / (per_launch_ms * 1e-3) / 1e12
+        roof = {"bound": "fp32", "kernel": top, "peak": peak_tf, "peak_source": "148 SMs x 128 FMA lanes x 2 flop x sampled SM clock (no measured SIMT peak in MEASURED_PEAKS.json)",
+                "unit": "TFLOP/s", "achieved": ach, "frac": ach / peak_tf, "traffic": None,
+                "flop_per_launch": flop, "flop_per_atom": model.dense_flops, "avg_launch_ms": per_launch_ms,
+                "note": "dense-network kernel: shared-memory resident fp32 SIMT work, neither HBM- nor tensor-bound; "
+                        "its DRAM traffic (ncu) is in profiles/"}
     else:
-        roof.update(achieved=None, frac=None, note="dense-network kernel: compute bound on fp32 FMA, no HBM roofline")
+        roof = {"bound": "hbm", "kernel": top, "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "traffic": None}
+        ab = algorithmic_bytes(top, wl["cfg"], n_own, n_bonds, slots)
+        if ab is not None:
+            per_launch_bytes = ab * args.steps / top_n
+            roof.update(achieved=per_launch_bytes / (per_launch_ms * 1e-3) / 1e9,
+                        algorithmic_bytes_per_launch=per_launch_bytes, avg_launch_ms=per_launch_ms)
+            roof["frac"] = roof["achieved"] / hbm_peak
+        else:
+            roof.update(achieved=None, frac=None)
+    # the HBM-bound kernels of the step, each against the measured copy bandwidth
+    hbm_kernels = {}
+    for k, v in kern:
+        name = k.strip("()").split("<")[0]
+        ab = algorithmic_bytes(name, wl["cfg"], n_own, n_bonds, slots)
+        if ab is not None and v[0] > 0:
+            gbs = ab * args.steps / v[0] / (v[1] / v[0] * 1e-3) / 1e9
+            hbm_kernels[name] = {"achieved_GBs": gbs, "frac_of_measured_hbm": gbs / hbm_peak, "avg_launch_ms": v[1] / v[0]}
 
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
            "dtype": "f32", "data": "synthetic",
            "config": {"workload": args.workload, "atoms": int(n), "model": "GRACE-1L" if wl["cfg"] == "1l" else "GRACE-2L",
-                      "elements_in_model": 89 if wl["full"] else 1, "species": species, "cutoff_A": 6.0, "skin_A": 0.5,
+                      "elements_in_model": 89 if wl["full"] else 1, "species": species, "cutoff_A": cutoff, "skin_A": skin,
                       "neighbor_list": "reused (built in warm-up)", "chunk_atoms": system.chunksize,
+                      "parallelism": f"slabs{world}" if world > 1 else "single",
+                      "value_definition": "max-over-ranks device time per step x n_gpus / atoms",
+                      "atoms_evaluated_all_ranks": int(counts[2]), "atoms_with_ghosts_all_ranks": int(counts[1]),
                       "l2": "per-step working set (bond records + chunk tensors) exceeds the 126 MB L2",
                       "radial": "cubic Hermite tables, 1024 intervals"},
-           "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
-           "stages_ms_per_step": stages, "kernels": shares, "wall_ms_per_step": wall_ms / args.steps,
+           "e2e": e2e, "gpu_launches": int(counts[0]), "clocks": clocks, "roofline": roof, "hbm_kernels": hbm_kernels,
+           "stages_ms_per_step": stages, "kernels": shares, "wall_ms_per_step": wall_ms_per_step,
            "energy_eV": energy, "atoms_per_s": n / (ms_per_step * 1e-3)}
-    if not args.no_cpu:
+    if not args.no_cpu and world == 1:
         out["cpu_baseline"] = cpu_baseline(args, path, species, types, pos, cell, pbc, bounded=True)
     print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def cpu_baseline(args, path, species, types, pos, cell, pbc, bounded):

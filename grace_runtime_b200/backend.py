@@ -46,11 +46,13 @@ SIGNATURES = {
     "grace_model_n_elements": (_I, [_P]),
     "grace_model_element_name": (C.c_char_p, [_P, _I]),
     "grace_model_engine_setups": (_I64, [_P]),
+    "grace_model_dense_flops": (_D, [_P]),
     "grace_model_free": (None, [_P]),
     "grace_system_create": (_I, [_P, _P, _I, _D, _I, _I, _P]),
     "grace_system_cutoff": (_D, [_P]),
     "grace_system_compute": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "grace_system_compute_device": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
+    "grace_system_set_owned": (_I, [_P, _I, _I]),
     "grace_system_rebuilds": (_I64, [_P]),
     "grace_system_chunksize": (_I, [_P]),
     "grace_system_release_buffers": (_I, [_P]),
@@ -225,6 +227,11 @@ class Model:
     def engine_setups(self):
         return int(_lib.grace_model_engine_setups(self._h))
 
+    @property
+    def dense_flops(self):
+        """fp32 flops per atom of the dense network (forward + reverse) in the engine's plan; 0 before the first System"""
+        return float(_lib.grace_model_dense_flops(self._h))
+
     def validate_uq(self):
         raise ValueError("the model has no UQ head usable by this backend")
 
@@ -272,6 +279,11 @@ class System:
 
     def release_buffers(self):
         _check(_lib.grace_system_release_buffers(self._h))
+
+    def set_owned(self, nlocal, ninner=-1):
+        """Atoms [0, nlocal) are owned, the rest are ghosts of a domain decomposition (-1: all owned); ghosts behind
+        ninner only serve as neighbours (GRACE-2L: ghosts no owned atom has inside cutoff + skin)."""
+        _check(_lib.grace_system_set_owned(self._h, int(nlocal), int(ninner)))
 
     def compute(self, types, positions, cell, pbc, energies=False, uq=False, energy_only=False):
         """Result dict as python/kk/kk_module.cpp `compute`: energy, virial [6], forces [n, 3] (not with energy_only),

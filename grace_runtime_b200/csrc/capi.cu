@@ -191,6 +191,12 @@ const char *grace_model_element_name(const grace_model *m, int i)
   return m->m->model.element_names[i].c_str();
 }
 int64_t grace_model_engine_setups(const grace_model *m) { return m ? m->m->setups : 0; }
+double grace_model_dense_flops(const grace_model *m)
+{
+  if (!m) return 0.0;
+  std::lock_guard<std::mutex> lk(m->m->mu);
+  return m->m->engine ? m->m->engine->plan().dense_flops_per_atom : 0.0;
+}
 void grace_model_free(grace_model *m)
 {
   std::lock_guard<std::recursive_mutex> lk(g_device_mu);
@@ -231,12 +237,23 @@ int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, 
   });
 }
 
-#ifndef GB_CPU_EMU
 int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_out)
 {
+#ifndef GB_CPU_EMU
   return guarded([&] { static_sum(d_values, (long long) n, k, d_out); });
-}
+#else
+  return guarded([&] { throw Unsupported("not part of the host-emulated build"); });
 #endif
+}
+
+int grace_system_set_owned(grace_system *s, int nlocal, int ninner)
+{
+  return guarded([&] {
+    if (!s) throw InvalidArgument("system must be given");
+    std::lock_guard<std::mutex> lk(s->s->mu);
+    s->s->set_owned(nlocal, ninner);
+  });
+}
 
 int64_t grace_system_rebuilds(const grace_system *s) { return s ? s->s->rebuilds : 0; }
 int grace_system_chunksize(const grace_system *s) { return s ? s->s->last_chunk : 0; }

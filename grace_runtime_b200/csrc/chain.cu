@@ -120,7 +120,8 @@ __global__ void __launch_bounds__(64) readout_1l_kernel(ReadoutDev r, const floa
 {
   const int a = blockIdx.x * blockDim.x + threadIdx.x;
   if (a >= na) return;
-  e_atom[a0 + a] = readout_1l_atom(r, rho + (size_t) a * r.nrho, mu[a0 + a], grho + (size_t) a * r.nrho, want_grad);
+  e_atom[a0 + a] = readout_1l_atom(r, rho + (size_t) a * r.nrho, mu[a0 + a], grho + (size_t) a * r.nrho, want_grad,
+                                   r.owned(a0 + a));
 }
 
 void launch_readout_1l(const ReadoutDev &r, const float *rho, float *grho, const int *mu, double *e_atom, int NA,
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(64) readout_2l_kernel(ReadoutDev r, const floa
   if (a >= na) return;
   const int nr = r.nrho;
   e_atom[a0 + a] = readout_2l_atom(r, rho_rows + (size_t) (a0 + a) * nr, I2 + (size_t) a * nr, mu[a0 + a],
-                                   grho_rows + (size_t) (a0 + a) * nr, gI2 + (size_t) a * nr, want_grad);
+                                   grho_rows + (size_t) (a0 + a) * nr, gI2 + (size_t) a * nr, want_grad, r.owned(a0 + a));
 }
 
 void launch_readout_2l(const ReadoutDev &r, const float *rho_rows, const float *I2, double *grho_rows, float *gI2,

@@ -426,7 +426,7 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
       if (tid < nta) {
         const float *rho = sm + (size_t) s_soff[io.t_rho] * TA + tid * io.nrho;
         float *grho = sm + (size_t) s_soff[io.t_grho] * TA + tid * io.nrho;
-        io.e_atom[io.a0 + al0 + tid] = readout_1l_atom(io.ro, rho, s_mu[tid], grho, bwd);
+        io.e_atom[io.a0 + al0 + tid] = readout_1l_atom(io.ro, rho, s_mu[tid], grho, bwd, io.ro.owned(io.a0 + al0 + tid));
       } else if (tid < TA && bwd) {
         float *grho = sm + (size_t) s_soff[io.t_grho] * TA + tid * io.nrho;
         for (int k = 0; k < io.nrho; k++) grho[k] = 0.0f;
@@ -438,7 +438,7 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
         const float *I2 = sm + (size_t) s_soff[io.t_I2] * TA + tid * io.nrho;
         float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + tid * io.nrho;
         io.e_atom[i] = readout_2l_atom(io.ro, io.rho_rows + i * io.nrho, I2, s_mu[tid], io.grho_rows + i * io.nrho,
-                                       gI2, bwd);
+                                       gI2, bwd, io.ro.owned(i));
       } else if (tid < TA && bwd) {
         float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + tid * io.nrho;
         for (int k = 0; k < io.nrho; k++) gI2[k] = 0.0f;

@@ -1,5 +1,7 @@
 #include "engine.h"
 
+#include <climits>
+
 #include "bond_common.cuh"
 
 #include <algorithm>
@@ -381,7 +383,7 @@ void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const i
 
 // bond sums -> fused dense network (forward, readout, reverse in one kernel) -> bond forces; only the bond-sum tensor
 // and its gradient live in global memory, so a pass can hold every atom of most structures
-void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm)
+void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R)
 {
   const int64_t n = nl.n();
   cudaStream_t st = dev().stream;
@@ -397,8 +399,8 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   if (P.layers == 1) {
     const LayerDev L = layer_dev(L1_);
     const float *gQ = arena_.get() + (size_t) L1_.q_floats * NA;
-    for (int64_t a0 = 0; a0 < n; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, n - a0);
+    for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
       if (tm) tm->begin(StageTimer::FWD);
       launch_bond_fwd(P.lmax, bonds, L, Q, NA, (int) a0, na);
       run_fused(L1_, FUSED_READOUT_1L | bwd, NA, (int) a0, na, mu);
@@ -424,13 +426,13 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   Lb.gmsg = gI_rows_.get();
   const float *gQ1 = arena_.get() + (size_t) L1_.q_floats * NA, *gQ2 = arena_.get() + (size_t) L2_.q_floats * NA;
   if (tm) tm->begin(StageTimer::FWD);
-  for (int64_t a0 = 0; a0 < n; a0 += NA) {    // layer 1 forward: messages and rho of all atoms
-    const int na = (int) std::min<int64_t>(NA, n - a0);
+  for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {    // layer 1 forward: messages and rho of all atoms
+    const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
     launch_bond_fwd(P.lmax, bonds, La, Q, NA, (int) a0, na);
     run_fused(L1_, FUSED_STORE_MSG, NA, (int) a0, na, mu);
   }
-  for (int64_t a0 = 0; a0 < n; a0 += NA) {    // layer 2, energy, layer-2 reverse
-    const int na = (int) std::min<int64_t>(NA, n - a0);
+  for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {    // layer 2, energy, layer-2 reverse
+    const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
     launch_bond_fwd(P.lmax, bonds, Lb, Q, NA, (int) a0, na);
     run_fused(L2_, FUSED_READOUT_2L | bwd, NA, (int) a0, na, mu);
     if (!energy_only) launch_bond_bwd(P.lmax, bonds, Lb, gQ2, NA, (int) a0, na, fv, vir_atom_.get(), 0);
@@ -438,8 +440,8 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   if (tm) tm->end(StageTimer::FWD);
   if (energy_only) return;
   if (tm) tm->begin(StageTimer::BWD);
-  for (int64_t a0 = 0; a0 < n; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
-    const int na = (int) std::min<int64_t>(NA, n - a0);
+  for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
+    const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
     launch_bond_fwd(P.lmax, bonds, La, Q, NA, (int) a0, na);
     run_fused(L1_, FUSED_LOAD_SEED | FUSED_BWD, NA, (int) a0, na, mu);
     launch_bond_bwd(P.lmax, bonds, La, gQ1, NA, (int) a0, na, fv, vir_atom_.get(), 1);
@@ -449,7 +451,7 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
 
 // the dense network as one kernel launch per operation on chunk tensors in global memory: the path for layers whose
 // tensors of a single atom do not fit the shared memory of an SM
-void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm)
+void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R)
 {
   const int64_t n = nl.n();
   cudaStream_t st = dev().stream;
@@ -473,8 +475,8 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
 
   if (P.layers == 1) {
     const LayerDev L = layer_dev(L1_);
-    for (int64_t a0 = 0; a0 < n; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, n - a0);
+    for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
       if (tm) tm->begin(StageTimer::FWD);
       launch_bond_fwd(P.lmax, bonds, L, T1(P.L1.tQ), NA, (int) a0, na);
       run(L1_, P.L1.fwd, mu + a0, na);
@@ -502,8 +504,8 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     Lb.gmsg = gI_rows_.get();
     // layer 1 forward of every chunk: messages I and rho of all atoms
     if (tm) tm->begin(StageTimer::FWD);
-    for (int64_t a0 = 0; a0 < n; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, n - a0);
+    for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
       launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
       run(L1_, P.L1.fwd, mu + a0, na);
       launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, NA, na, (int) a0);
@@ -511,8 +513,8 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     }
     if (tm) tm->end(StageTimer::FWD);
     // layer 2 forward, energy and layer-2 reverse per chunk
-    for (int64_t a0 = 0; a0 < n; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, n - a0);
+    for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
       if (tm) tm->begin(StageTimer::FWD);
       launch_bond_fwd(P.lmax, bonds, Lb, T2(P.L2.tQ), NA, (int) a0, na);
       run(L2_, P.L2.fwd, mu + a0, na);
@@ -529,8 +531,8 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     // layer 1 again (recomputed) and its reverse, seeded with dE/dI and dE/drho of each atom
     if (!energy_only) {
       if (tm) tm->begin(StageTimer::BWD);
-      for (int64_t a0 = 0; a0 < n; a0 += NA) {
-        const int na = (int) std::min<int64_t>(NA, n - a0);
+      for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {
+        const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
         launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
         run(L1_, P.L1.fwd, mu + a0, na);
         zero_grads(L1_);
@@ -544,21 +546,81 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
   }
 }
 
-void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm)
+// smallest and one past the largest list position of the atoms with caller index < nlocal ([0], [1]) and < ninner
+// ([2], [3])
+__global__ void __launch_bounds__(256) active_range_kernel(const int *__restrict__ perm, int nlocal, int ninner,
+                                                           int *r, long long n)
+{
+  const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int p = perm[i];
+  if (p < nlocal) { atomicMin(&r[0], (int) i); atomicMax(&r[1], (int) i + 1); }
+  if (p < ninner) { atomicMin(&r[2], (int) i); atomicMax(&r[3], (int) i + 1); }
+}
+
+ActiveRanges Engine::active_ranges(NeighborList &nl, int nlocal, int ninner)
+{
+  ActiveRanges R;
+  const int64_t n = nl.n();
+  R.hi0 = R.hi1 = n;
+  if (nlocal < 0 || n == 0) return R;
+  R.nlocal = nlocal;
+  const int init[4] = {INT_MAX, 0, INT_MAX, 0};
+  int *d = range_buf_.ensure(4);
+  cudaStream_t st = dev().stream;
+  GB_CUDA(cudaMemcpyAsync(d, init, sizeof(init), cudaMemcpyHostToDevice, st));
+  const int *perm = nl.perm();
+  const int ni = ninner < 0 ? INT_MAX : ninner;
+  GB_LAUNCH(active_range_kernel, nblocks(n, 256), 256, 0, perm, nlocal, ni, d, (long long) n);
+  int h[4];
+  GB_CUDA(cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaStreamSynchronize(st));
+  R.lo0 = h[1] > 0 ? h[0] : 0; R.hi0 = h[1];
+  R.lo1 = h[3] > 0 ? h[2] : 0; R.hi1 = h[3];
+  // the owned atoms need their own layer-1 outputs
+  R.lo1 = std::min(R.lo1, R.lo0);
+  R.hi1 = std::max(R.hi1, R.hi0);
+  return R;
+}
+
+void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm,
+                      const ActiveRanges *act)
 {
   const int64_t n = nl.n();
   const int nsys = nl.nsys();
+  ActiveRanges R;
+  if (act && act->nlocal >= 0) R = *act;
+  else R.hi0 = R.hi1 = n;
+  readout_.perm = R.nlocal >= 0 ? nl.perm() : nullptr;
+  readout_.nlocal = R.nlocal;
   cudaStream_t st = dev().stream;
   if (n == 0) {
     if (out.energy) GB_CUDA(cudaMemsetAsync(out.energy, 0, sizeof(double) * nsys, st));
     if (out.virial && !energy_only) GB_CUDA(cudaMemsetAsync(out.virial, 0, sizeof(double) * 6 * nsys, st));
     return;
   }
-  const int NA = (int) std::min<int64_t>(n, chunk > 0 ? chunk : n);
+  const bool partial = R.lo0 > 0 || R.hi0 < n || R.lo1 > 0 || R.hi1 < n;
+  const int64_t widest = std::max<int64_t>(1, std::max(R.hi0 - R.lo0, R.hi1 - R.lo1));
+  const int NA = (int) std::min<int64_t>(widest, chunk > 0 ? chunk : n);
   e_atom_.ensure(n);
   if (!energy_only) vir_atom_.ensure(6 * n);
-  if (fused_) evaluate_fused(nl, energy_only, NA, tm);
-  else evaluate_chunked(nl, energy_only, NA, tm);
+  if (partial) {    // what the skipped atoms would have written is read below or by the active atoms: zeros
+    GB_CUDA(cudaMemsetAsync(e_atom_.get(), 0, sizeof(double) * n, st));
+    if (!energy_only) {
+      GB_CUDA(cudaMemsetAsync(vir_atom_.get(), 0, sizeof(double) * 6 * n, st));
+      GB_CUDA(cudaMemsetAsync(fv_.get(), 0, sizeof(float) * 3 * (size_t) nl.nslots(), st));
+    }
+    if (plan_.layers == 2) {
+      I_rows_.ensure((size_t) n * plan_.nI * plan_.cr);
+      GB_CUDA(cudaMemsetAsync(I_rows_.get(), 0, sizeof(float) * (size_t) n * plan_.nI * plan_.cr, st));
+      if (!energy_only) {
+        grho_rows_.ensure((size_t) n * plan_.nrho);
+        GB_CUDA(cudaMemsetAsync(grho_rows_.get(), 0, sizeof(double) * (size_t) n * plan_.nrho, st));
+      }
+    }
+  }
+  if (fused_) evaluate_fused(nl, energy_only, NA, tm, R);
+  else evaluate_chunked(nl, energy_only, NA, tm, R);
   float *fv = fv_.get();
   // sums and gathers that leave the engine
   if (out.energy) launch_segment_sum(e_atom_.get(), 1, nl.seg(), nsys, out.energy);
@@ -628,6 +690,13 @@ void SystemObj::release()
   label_ws(ws_);
   have_list_ = false;
   engine_->release_work();
+}
+
+void SystemObj::set_owned(int nlocal_, int ninner_)
+{
+  nlocal = nlocal_ < 0 ? -1 : nlocal_;
+  ninner = ninner_ < 0 ? -1 : std::max(ninner_, nlocal);
+  have_list_ = false;    // the active ranges belong to the list: rebuilt by the next compute
 }
 
 void SystemObj::compute(int n, const int *types, const double *pos, bool device_in, const double *cell,
@@ -718,6 +787,7 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     list_n_ = n;
     have_list_ = true;
     rebuilds++;
+    if (nlocal >= 0) ranges = engine_->active_ranges(nl_, std::min(nlocal, n), ninner < 0 ? n : std::min(ninner, n));
     timer_.end(StageTimer::NL);
   }
   timer_.begin(StageTimer::GEOM);
@@ -736,7 +806,7 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     if (!eonly && forces) o.forces = ws_.forces.ensure(3 * (size_t) std::max(n, 1));
     if (want_e && energies) o.energies = ws_.energies.ensure(std::max(n, 1));
   }
-  engine_->evaluate(nl_, eonly, o, chunk, &timer_);
+  engine_->evaluate(nl_, eonly, o, chunk, &timer_, nlocal >= 0 ? &ranges : nullptr);
   if (!device_out) {
     if (energy) GB_CUDA(cudaMemcpyAsync(energy, o.energy, sizeof(double), cudaMemcpyDeviceToHost, st));
     if (o.virial) GB_CUDA(cudaMemcpyAsync(virial, o.virial, sizeof(double) * 6, cudaMemcpyDeviceToHost, st));

@@ -39,6 +39,14 @@ struct LayerEngine {
   long long q_floats = 0;     // floats per atom of the bond-sum tensor
 };
 
+// Atoms a domain-decomposed caller wants evaluated, as ranges of the list order: [lo0, hi0) covers the owned atoms
+// (energy, last layer), [lo1, hi1) the atoms whose layer-1 outputs the owned atoms read (GRACE-2L); everything else
+// is only a neighbour.  nlocal < 0: every atom is owned and the ranges are the whole list.
+struct ActiveRanges {
+  int nlocal = -1;
+  int64_t lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
+};
+
 // outputs of one evaluation, device pointers (null: not wanted)
 struct OutputsDev {
   double *energy = nullptr;      // [nsys]
@@ -53,7 +61,11 @@ class Engine {
   ~Engine();
   const ModelPlan &plan() const { return plan_; }
   // evaluates the structures of the neighbour list nl (positions prepared by nl.prepare); chunk: atoms per pass
-  void evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm);
+  // act (optional): owned atoms and active ranges of a domain-decomposed caller
+  void evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm,
+                const ActiveRanges *act = nullptr);
+  // ranges of the list order that hold the atoms with caller index < nlocal / < ninner (reads back 4 integers)
+  ActiveRanges active_ranges(NeighborList &nl, int nlocal, int ninner);
   // bond-force slots [3 * nslots] the list zeroes for bonds outside the cutoff (grown here)
   float *bond_forces(int64_t nslots) { return fv_.ensure(3 * (size_t) std::max<int64_t>(nslots, 1)); }
   const double *rcsq() const { return rcsq_.get(); }
@@ -75,8 +87,9 @@ class Engine {
   void setup_layer(LayerEngine &E, const LayerPlan &P);
   void setup_fused(LayerEngine &E, const LayerPlan &P);
   bool fused_ = false;        // both layers run as the fused shared-memory kernel
-  void evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm);
-  void evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm);
+  void evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
+  void evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
+  DBuf<int> range_buf_;
   void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu);
   void bind_arena(LayerEngine &E, int NA);
   void run(LayerEngine &E, const Program &prog, const int *mu, int NA);
@@ -110,6 +123,9 @@ class SystemObj {
                bool device_out);
   int64_t rebuilds = 0;
   int last_chunk = 0;
+  int nlocal = -1, ninner = -1;    // owned atoms / atoms with layer-1 outputs of a domain-decomposed caller (-1: all)
+  ActiveRanges ranges;
+  void set_owned(int nlocal_, int ninner_);
   double stage_ms[StageTimer::NSTAGE] = {0, 0, 0, 0, 0};
   void release();
   std::mutex mu;

@@ -73,6 +73,12 @@ struct ReadoutDev {
   double norm[4];
   int act, ln, rms, nrho;
   double out_scale;
+  // owned atoms of a domain-decomposed caller: atoms whose caller index perm[i] is >= nlocal are ghosts, which
+  // take part in every neighbour sum but whose own energy (and its gradient seed) is left out (the nlocal / ghost
+  // convention of the reference's engine interface, libgrace/include/grace/kk/grace_2l_kk.h:87-107).  perm null: all owned
+  const int *perm;
+  int nlocal;
+  __host__ __device__ bool owned(long long i) const { return perm == nullptr || perm[i] < nlocal; }
 };
 // GRACE-1L: E_i = (MLP(rho[1:]) + rho[0]) scale + shift, dE/drho
 void launch_readout_1l(const ReadoutDev &r, const float *rho, float *grho, const int *mu, double *e_atom, int NA,

@@ -631,8 +631,11 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
   P.shift = m.shift;
   P.lnI = m.lnI;
   P.ln0 = m.ln0;
-  for (const LayerPlan *L : {&P.L1, &P.L2})
+  for (const LayerPlan *L : {&P.L1, &P.L2}) {
     for (const auto &o : L->mv) P.dense_flops_per_atom += o.flops_per_atom();
+    for (const auto &o : L->prod)    // 3 flop per (term, channel): libgrace/include/grace/fused_cpu.h:411-429
+      P.dense_flops_per_atom += 3.0 * (double) o.terms.size() * L->tensors[o.dst].channels;
+  }
   return P;
 }
 

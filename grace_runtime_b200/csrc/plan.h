@@ -114,7 +114,7 @@ struct ModelPlan {
   double out_scale = 1.0;
   std::vector<double> shift;    // [n_elements]
   std::vector<double> lnI, ln0;
-  double dense_flops_per_atom = 0.0;    // forward + reverse MV flops (diagnostics)
+  double dense_flops_per_atom = 0.0;    // FC / reduce / product flops of the forward and reverse programs (diagnostics)
 };
 
 ModelPlan build_plan(const GraceModel &m, int spline_n);

@@ -78,9 +78,14 @@ __device__ inline double energy_mlp(const ReadoutDev &r, double *x, int nin, dou
 
 // GRACE-2L: RMSNorms of rho[1:] and I2, MLP on their sum, and the reverse; returns E_i (without writing it)
 __device__ inline double readout_2l_atom(const ReadoutDev &r, const float *rho, const float *i2, int mu, double *gr,
-                                         float *go, bool want_grad)
+                                         float *go, bool want_grad, bool owned = true)
 {
   const int nr = r.nrho;
+  if (!owned) {    // a ghost atom: no energy of its own, no gradient seed
+    if (want_grad)
+      for (int k = 0; k < nr; k++) { gr[k] = 0.0; go[k] = 0.0f; }
+    return 0.0;
+  }
   double ms1 = 0.0, ms0 = 0.0;
   for (int k = 1; k < nr; k++) ms1 += (double) rho[k] * rho[k];
   for (int k = 0; k < nr; k++) ms0 += (double) i2[k] * i2[k];
@@ -109,9 +114,15 @@ __device__ inline double readout_2l_atom(const ReadoutDev &r, const float *rho, 
 }
 
 // GRACE-1L: E_i = (MLP(rho[1:]) + rho[0]) scale + shift and dE/drho
-__device__ inline double readout_1l_atom(const ReadoutDev &r, const float *ra, int mu, float *ga, bool want_grad)
+__device__ inline double readout_1l_atom(const ReadoutDev &r, const float *ra, int mu, float *ga, bool want_grad,
+                                         bool owned = true)
 {
   const int nr = r.nrho;
+  if (!owned) {
+    if (want_grad)
+      for (int k = 0; k < nr; k++) ga[k] = 0.0f;
+    return 0.0;
+  }
   double x[RW], g[RW];
   for (int k = 1; k < nr; k++) x[k - 1] = ra[k];
   const double val = energy_mlp(r, x, nr - 1, want_grad ? g : nullptr);

@@ -89,6 +89,10 @@ int grace_model_has_uq(const grace_model *m);                            /* has_
 int grace_model_n_elements(const grace_model *m);                        /* len(element_names()) */
 const char *grace_model_element_name(const grace_model *m, int i);       /* element_names()[i] */
 int64_t grace_model_engine_setups(const grace_model *m);                 /* engine_setups() */
+/* fp32 flops per atom of the dense network (FC layers, products, reduces; forward and reverse programs, each once)
+ * of the engine's plan; 0 before the first System / Batch of the model.  Diagnostics for roofline figures; no
+ * counterpart in the reference. */
+double grace_model_dense_flops(const grace_model *m);
 void grace_model_free(grace_model *m);
 
 /* ---- System (kk_api.h:68-90): one structure, neighbour list with a Verlet skin kept on the device ---- */
@@ -106,6 +110,17 @@ int grace_system_compute(grace_system *s, int n, const int32_t *types, const dou
 int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, const double *d_pos,
                                 const double *cell, const uint8_t *pbc, int flags, double *d_energy,
                                 double *d_virial6, double *d_forces, double *d_energies);
+/* Domain decomposition: from now on only the atoms with index < nlocal are owned by this System; the atoms behind
+ * them are ghosts (copies of atoms another rank owns), which enter every neighbour sum but whose own energies are
+ * left out of `energy`, `energies` (0 there) and the gradient, while forces and virial of everything the owned
+ * energies depend on are returned, ghost rows included, for the caller to send back to the owners.  The ghosts
+ * [nlocal, ninner) are those whose layer-1 outputs owned atoms read (GRACE-2L: ghosts within cutoff + skin of an owned
+ * atom; ninner < 0: all ghosts); ghosts behind ninner only serve as neighbours, and nothing but the neighbour list is
+ * computed for them.  Work is skipped for runs of the spatially sorted atom order, so it pays to make the cell's first
+ * vector the one the domains are cut across.  nlocal < 0: all atoms are owned (default).  Counterpart of nlocal / ghost atoms in the reference's engine input
+ * (libgrace/include/grace/kk/grace_2l_kk.h:87-107) and of inum / ilist in its CPU drivers
+ * (libgrace/include/grace/system.h:113-121); the plug-in interface kk_api.h itself is single-GPU. */
+int grace_system_set_owned(grace_system *s, int nlocal, int ninner);
 int64_t grace_system_rebuilds(const grace_system *s);                     /* rebuilds() */
 int grace_system_chunksize(const grace_system *s);                        /* chunksize() */
 int grace_system_release_buffers(grace_system *s);                        /* release_device_buffers() */
