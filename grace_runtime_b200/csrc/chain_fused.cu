@@ -101,6 +101,40 @@ __device__ __forceinline__ void mv_units(const MVDev &op, float *sm, const int *
   }
 }
 
+// One (row, channel quad, atom) unit of an operation with per-element weights whose items all have PI x S input
+// channels: lane s takes the channels s, s + S, ... of every item, and the weight loads of NE / PI items (every one an
+// L2 round trip) are in flight together.
+template<int TA, int PI>
+__device__ __forceinline__ void elem_items(const MVDev &op, const float *sm, const int *__restrict__ soff,
+                                           const int *__restrict__ tch, const float *Wa, int i0, int i1, int a, int s,
+                                           int S, float4 &acc)
+{
+  constexpr int NE = 8, IB = NE / PI;
+  const int ld = op.ldw;
+  for (int it0 = i0; it0 < i1; it0 += IB) {
+    float4 w[NE];
+    float xv[NE];
+#pragma unroll
+    for (int jj = 0; jj < IB; jj++) {
+      const bool in = it0 + jj < i1;
+      const MVItem &item = op.items[in ? it0 + jj : i0];
+      const float *x = sm + (size_t) soff[item.src] * TA + ((size_t) item.irow * TA + a) * tch[item.src];
+      const float *M = Wa + item.mat;
+#pragma unroll
+      for (int q = 0; q < PI; q++) {
+        const int n = s + S * q;
+        w[jj * PI + q] = in ? __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * ld)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        xv[jj * PI + q] = in ? x[n] * item.scale : 0.0f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NE; j++) {
+      acc.x = fmaf(xv[j], w[j].x, acc.x); acc.y = fmaf(xv[j], w[j].y, acc.y);
+      acc.z = fmaf(xv[j], w[j].z, acc.z); acc.w = fmaf(xv[j], w[j].w, acc.w);
+    }
+  }
+}
+
 // out[row][a][k] (+)= sum_items scale * sum_n M[n][k] x[item][a][n] on the tile's shared-memory tensors.
 // A thread owns 4 consecutive output channels of one row for all TA atoms: a 16-byte weight load (rows of the weight
 // matrices are padded to 4 outputs) feeds 4 TA FMAs, a 16-byte activation load (broadcast in the warp) 16.  The weight
@@ -119,39 +153,46 @@ __device__ __forceinline__ void mv_tile(const MVDev &op, float *sm, const int *_
   while (KQP < KQ) KQP <<= 1;
   if (op.elem) {
     // weights of each atom's own element: nothing is shared between the atoms of the tile, so the unit of work is
-    // (row, channel quad, atom) and S lanes split the input channels of all items of the row; 8 independent 16-byte
-    // weight loads are in flight per lane before the first FMA
-    const int total_e = op.nrows * KQP * TA;
+    // (row, channel quad, atom) and S lanes split the (item, input channel) pairs of the row.  Every weight is an L2
+    // round trip (the matrices of one element exceed the L1 left beside the tile), so the pairs of ALL items are one
+    // flat index space and NE independent 16-byte weight loads are in flight per lane before the first FMA.
+    const int total_e = op.nrows * KQ * TA;
     int S = 1;
     while (S < 32 && total_e * S * 2 <= NT) S <<= 1;
     const int s = tid & (S - 1), per_pass = NT / S;
     for (int base = 0; base < total_e; base += per_pass) {
-      const int u = base + tid / S, a = u % TA, rk = u / TA, row = rk / KQP, kq = rk - row * KQP;
-      const bool valid = u < total_e && kq < KQ;
+      const int u = base + tid / S, a = u % TA, rk = u / TA, row = rk / KQ, kq = rk - row * KQ;
+      const bool valid = u < total_e;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       if (valid) {
         const float *Wa = op.W + (size_t) s_mu[a] * op.ty_stride + 4 * kq;
         const int i0 = op.item_off[row], i1 = op.item_off[row + 1];
-        for (int it = i0; it < i1; it++) {
-          const MVItem item = op.items[it];
-          const int Cs = tch[item.src];
-          const float *x = sm + (size_t) soff[item.src] * TA + ((size_t) item.irow * TA + a) * Cs;
-          const float *M = Wa + item.mat;
-          constexpr int NE = 8;
-          for (int n0 = s; n0 < item.n_in; n0 += NE * S) {
-            float4 w[NE];
-            float xv[NE];
+        constexpr int NE = 8;
+        const int per_item = op.n_uniform > 0 && op.n_uniform % S == 0 ? op.n_uniform / S : 0;
+        if (per_item == 1) elem_items<TA, 1>(op, sm, soff, tch, Wa, i0, i1, a, s, S, acc);
+        else if (per_item == 2) elem_items<TA, 2>(op, sm, soff, tch, Wa, i0, i1, a, s, S, acc);
+        else if (per_item == 4) elem_items<TA, 4>(op, sm, soff, tch, Wa, i0, i1, a, s, S, acc);
+        else {
+          for (int it = i0; it < i1; it++) {
+            const MVItem item = op.items[it];
+            const int Cs = tch[item.src];
+            const float *x = sm + (size_t) soff[item.src] * TA + ((size_t) item.irow * TA + a) * Cs;
+            const float *M = Wa + item.mat;
+            for (int n0 = s; n0 < item.n_in; n0 += NE * S) {
+              float4 w[NE];
+              float xv[NE];
 #pragma unroll
-            for (int j = 0; j < NE; j++) {
-              const int n = n0 + j * S;
-              const bool in = n < item.n_in;
-              w[j] = in ? __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * ld)) : make_float4(0.f, 0.f, 0.f, 0.f);
-              xv[j] = in ? x[n] * item.scale : 0.0f;
-            }
+              for (int j = 0; j < NE; j++) {
+                const int n = n0 + j * S;
+                const bool in = n < item.n_in;
+                w[j] = in ? __ldg(reinterpret_cast<const float4 *>(M + (size_t) n * ld)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                xv[j] = in ? x[n] * item.scale : 0.0f;
+              }
 #pragma unroll
-            for (int j = 0; j < NE; j++) {
-              acc.x = fmaf(xv[j], w[j].x, acc.x); acc.y = fmaf(xv[j], w[j].y, acc.y);
-              acc.z = fmaf(xv[j], w[j].z, acc.z); acc.w = fmaf(xv[j], w[j].w, acc.w);
+              for (int j = 0; j < NE; j++) {
+                acc.x = fmaf(xv[j], w[j].x, acc.x); acc.y = fmaf(xv[j], w[j].y, acc.y);
+                acc.z = fmaf(xv[j], w[j].z, acc.z); acc.w = fmaf(xv[j], w[j].w, acc.w);
+              }
             }
           }
         }
@@ -422,26 +463,31 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
         for (int idx = tid; idx < zr.y * TA / 4; idx += NT) p[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    if (io.mode & FUSED_READOUT_1L) {
-      if (tid < nta) {
-        const float *rho = sm + (size_t) s_soff[io.t_rho] * TA + tid * io.nrho;
-        float *grho = sm + (size_t) s_soff[io.t_grho] * TA + tid * io.nrho;
-        io.e_atom[io.a0 + al0 + tid] = readout_1l_atom(io.ro, rho, s_mu[tid], grho, bwd, io.ro.owned(io.a0 + al0 + tid));
-      } else if (tid < TA && bwd) {
-        float *grho = sm + (size_t) s_soff[io.t_grho] * TA + tid * io.nrho;
-        for (int k = 0; k < io.nrho; k++) grho[k] = 0.0f;
+    if (io.mode & FUSED_READOUT_1L) {    // one warp per atom
+      const int w = tid >> 5, ln = tid & 31;
+      if (w < nta) {
+        const float *rho = sm + (size_t) s_soff[io.t_rho] * TA + w * io.nrho;
+        float *grho = sm + (size_t) s_soff[io.t_grho] * TA + w * io.nrho;
+        const size_t i = io.a0 + al0 + w;
+        const double e = readout_1l_warp(io.ro, rho, s_mu[w], grho, bwd, io.ro.owned(i));
+        if (ln == 0) io.e_atom[i] = e;
+      } else if (w < TA && bwd) {
+        float *grho = sm + (size_t) s_soff[io.t_grho] * TA + w * io.nrho;
+        for (int k = ln; k < io.nrho; k += 32) grho[k] = 0.0f;
       }
     }
     if (io.mode & FUSED_READOUT_2L) {
-      if (tid < nta) {
-        const size_t i = io.a0 + al0 + tid;
-        const float *I2 = sm + (size_t) s_soff[io.t_I2] * TA + tid * io.nrho;
-        float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + tid * io.nrho;
-        io.e_atom[i] = readout_2l_atom(io.ro, io.rho_rows + i * io.nrho, I2, s_mu[tid], io.grho_rows + i * io.nrho,
-                                       gI2, bwd, io.ro.owned(i));
-      } else if (tid < TA && bwd) {
-        float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + tid * io.nrho;
-        for (int k = 0; k < io.nrho; k++) gI2[k] = 0.0f;
+      const int w = tid >> 5, ln = tid & 31;
+      if (w < nta) {
+        const size_t i = io.a0 + al0 + w;
+        const float *I2 = sm + (size_t) s_soff[io.t_I2] * TA + w * io.nrho;
+        float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + w * io.nrho;
+        const double e = readout_2l_warp(io.ro, io.rho_rows + i * io.nrho, I2, s_mu[w], io.grho_rows + i * io.nrho, gI2,
+                                         bwd, io.ro.owned(i));
+        if (ln == 0) io.e_atom[i] = e;
+      } else if (w < TA && bwd) {
+        float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + w * io.nrho;
+        for (int k = ln; k < io.nrho; k += 32) gI2[k] = 0.0f;
       }
     }
     if (io.mode & FUSED_LOAD_SEED) {    // GRACE-2L layer 1 reverse: dE/dI and dE/drho of each atom

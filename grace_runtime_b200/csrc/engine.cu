@@ -1,6 +1,7 @@
 #include "engine.h"
 
 #include <climits>
+#include <cstdio>
 
 #include "bond_common.cuh"
 
@@ -120,6 +121,9 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
     d.unit_ent = E.items.get() + mv_ue[q];
     d.nslots = o.slot_off.empty() ? 0 : (int) o.slot_off.size() - 1;
     d.unit_nmax = 0;
+    d.n_uniform = o.items.empty() ? 0 : o.items[0].n_in;
+    for (const MVItem &it : o.items)
+      if (it.n_in != d.n_uniform) d.n_uniform = 0;
     bool same = true;
     for (const MVItem &it : o.items) {
       d.unit_nmax = std::max(d.unit_nmax, it.n_in);
@@ -187,6 +191,18 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   std::vector<float> rcf(P.rc.begin(), P.rc.end());
   rcf_.upload(rcf);
   eW_.upload(P.eW);
+  {    // transposed copies of the energy MLP layers for the reverse pass of the warp readout
+    std::vector<double> wt(P.eW.size());
+    size_t at = 0;
+    for (size_t L = 0; L < P.e_nin.size(); L++) {
+      const int ni = P.e_nin[L], no = P.e_nout[L];
+      for (int a = 0; a < ni; a++)
+        for (int c = 0; c < no; c++) wt[at + (size_t) c * ni + a] = P.eW[at + (size_t) a * no + c];
+      at += (size_t) ni * no;
+    }
+    eWT_.set_label("engine:energy_mlp");
+    eWT_.upload(wt);
+  }
   shift_.upload(P.shift);
   setup_layer(L1_, P.L1);
   setup_fused(L1_, P.L1);
@@ -200,6 +216,7 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   }
   ReadoutDev &r = readout_;
   r.W = eW_.get();
+  r.WT = eWT_.get();
   r.shift = shift_.get();
   r.lnI = lnI_.get();
   r.ln0 = ln0_.get();
@@ -297,6 +314,25 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
   }
   for (const Op &o : P.fwd.ops) ops.push_back(make_int2(o.kind == Op::MV ? 0 : 1, o.index));
   for (const Op &o : P.bwd.ops) ops.push_back(make_int2(o.kind == Op::MV ? 0 : 1, o.index));
+  if (getenv("GRACE_B200_PRINT_PLAN")) {    // diagnostics: the operation list of the layer
+    int k = 0;
+    for (const Program *prog : {&P.fwd, &P.bwd})
+      for (const Op &o : prog->ops) {
+        if (o.kind == Op::MV) {
+          const MVOp &m = P.mv[o.index];
+          int nmin = 1 << 30, nmax = 0;
+          for (const MVItem &it : m.items) { nmin = std::min(nmin, it.n_in); nmax = std::max(nmax, it.n_in); }
+          fprintf(stderr, "op %2d MV   %-18s rows %4zu n_out %3d items %4zu n_in %d..%d elem %d slots %zu units %zu\n", k,
+                  m.name.c_str(), m.row_out.size(), m.n_out, m.items.size(), nmin, nmax, (int) m.elem,
+                  m.slot_off.empty() ? (size_t) 0 : m.slot_off.size() - 1, m.unit_desc.size() / 5);
+        } else {
+          const ProdOp &q = P.prod[o.index];
+          fprintf(stderr, "op %2d PROD %-18s rows %4zu terms %5zu channels %d\n", k, q.name.c_str(), q.row_out.size(),
+                  q.terms.size(), P.tensors[q.dst].channels);
+        }
+        k++;
+      }
+  }
   E.f_mv.set_label("engine:tables"); E.f_prod.set_label("engine:tables"); E.f_ops.set_label("engine:tables");
   E.f_zero.set_label("engine:tables"); E.f_soff.set_label("engine:tables"); E.f_tch.set_label("engine:tables");
   E.f_mv.upload(E.mv);

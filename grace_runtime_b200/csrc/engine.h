@@ -77,7 +77,7 @@ class Engine {
  private:
   ModelPlan plan_;
   LayerEngine L1_, L2_;
-  DBuf<double> rcsq_, eW_, shift_, lnI_, ln0_;
+  DBuf<double> rcsq_, eW_, eWT_, shift_, lnI_, ln0_;
   DBuf<float> rcf_;
   ReadoutDev readout_{};
   // work buffers

@@ -24,6 +24,7 @@ struct MVDev {
   const int *slot_off;
   const MVItem *unit_ent;
   int nslots;
+  int n_uniform;     // n_in of the items when they all agree, else 0
   int unit_nmax;     // largest n_in of the units
   int unit_exact;    // 32 or 64 when every n_in, n_out and channel stride of the operation equals it, else 0
 };
@@ -66,7 +67,8 @@ void launch_bond_bwd(int lmax, const BondsDev &b, const LayerDev &L, const float
                      float *fv, double *vir_atom, int add);
 
 struct ReadoutDev {
-  const double *W;        // layers concatenated
+  const double *W;        // layers concatenated, [n_in][n_out] each
+  const double *WT;       // the same layers transposed, [n_out][n_in] each
   const double *shift;    // [n_elements]
   const double *lnI, *ln0;
   int nlay, n_in[4], n_out[4];

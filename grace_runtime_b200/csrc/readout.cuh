@@ -133,4 +133,203 @@ __device__ inline double readout_1l_atom(const ReadoutDev &r, const float *ra, i
   return (val + (double) ra[0]) * r.out_scale + r.shift[mu];
 }
 
+// ---- the same readouts by one warp per atom: lane l owns the channels l, l + 32, l + 64, l + 96 of every vector, a
+// matrix-vector product broadcasts one input channel at a time by shuffle and reads a coalesced weight row; the
+// reverse uses the transposed copies of the weights (WT) the same way.  fp64 throughout, same formulas as above.
+constexpr int RJ = RW / 32;
+
+__device__ inline double warp_sum(double v)
+{
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+  return v;
+}
+
+__device__ inline double act_value(int act, double v) { return act == 1 ? tanh(v) : v / (1.0 + exp(-v)); }
+__device__ inline double act_slope(int act, double v)
+{
+  if (act == 1) {
+    const double t = tanh(v);
+    return 1.0 - t * t;
+  }
+  const double sg = 1.0 / (1.0 + exp(-v));
+  return sg * (1.0 + v * (1.0 - sg));
+}
+
+// x, g: this lane's channels; returns the value (all lanes); g = dvalue/dx scaled by out_scale when want_grad
+__device__ inline double energy_mlp_warp(const ReadoutDev &r, double (&x)[RJ], int nin, double (&g)[RJ], bool want_grad)
+{
+  const int lane = threadIdx.x & 31;
+  double x0[RJ], pre[3][RJ], h[RJ];
+  double q = 0.0;
+#pragma unroll
+  for (int j = 0; j < RJ; j++) {
+    if (lane + 32 * j >= nin) x[j] = 0.0;
+    x0[j] = x[j];
+  }
+  if (r.ln) {
+    double ms = 0.0;
+#pragma unroll
+    for (int j = 0; j < RJ; j++) ms += x[j] * x[j];
+    ms = warp_sum(ms);
+    q = 1.0 / sqrt(ms / nin + 1e-16);
+#pragma unroll
+    for (int j = 0; j < RJ; j++) x[j] *= q;
+  }
+#pragma unroll
+  for (int j = 0; j < RJ; j++) h[j] = x[j];
+  const double *W = r.W;
+  for (int L = 0; L < r.nlay; L++) {
+    const int n_in = r.n_in[L], n_out = r.n_out[L];
+    double v[RJ];
+#pragma unroll
+    for (int j = 0; j < RJ; j++) v[j] = 0.0;
+#pragma unroll
+    for (int ja = 0; ja < RJ; ja++) {
+      if (ja * 32 >= n_in) break;
+      const int la = min(32, n_in - ja * 32);
+      for (int l = 0; l < la; l++) {
+        const double ha = __shfl_sync(0xffffffffu, h[ja], l);
+        const double *Wr = W + (size_t) (ja * 32 + l) * n_out + lane;
+#pragma unroll
+        for (int j = 0; j < RJ; j++)
+          if (lane + 32 * j < n_out) v[j] += ha * Wr[32 * j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < RJ; j++) {
+      v[j] *= r.norm[L];
+      if (L < r.nlay - 1) {
+        if (L < 3) pre[L][j] = v[j];
+        h[j] = lane + 32 * j < n_out ? act_value(r.act, v[j]) : 0.0;
+      } else {
+        h[j] = v[j];
+      }
+    }
+    W += (size_t) n_in * n_out;
+  }
+  const double val = __shfl_sync(0xffffffffu, h[0], 0);
+  if (!want_grad) return val;
+#pragma unroll
+  for (int j = 0; j < RJ; j++) g[j] = 0.0;
+  if (lane == 0) g[0] = r.out_scale;
+  const double *WT = r.WT + (W - r.W);
+  for (int L = r.nlay - 1; L >= 0; L--) {
+    const int n_in = r.n_in[L], n_out = r.n_out[L];
+    WT -= (size_t) n_in * n_out;
+    if (L < r.nlay - 1) {
+#pragma unroll
+      for (int j = 0; j < RJ; j++) g[j] = lane + 32 * j < n_out ? g[j] * act_slope(r.act, pre[L][j]) : 0.0;
+    }
+    double gn[RJ];
+#pragma unroll
+    for (int j = 0; j < RJ; j++) gn[j] = 0.0;
+#pragma unroll
+    for (int jc = 0; jc < RJ; jc++) {
+      if (jc * 32 >= n_out) break;
+      const int lc = min(32, n_out - jc * 32);
+      for (int l = 0; l < lc; l++) {
+        const double gc = __shfl_sync(0xffffffffu, g[jc], l);
+        const double *Wr = WT + (size_t) (jc * 32 + l) * n_in + lane;
+#pragma unroll
+        for (int j = 0; j < RJ; j++)
+          if (lane + 32 * j < n_in) gn[j] += gc * Wr[32 * j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < RJ; j++) g[j] = gn[j] * r.norm[L];
+  }
+  if (r.ln) {
+    double t = 0.0;
+#pragma unroll
+    for (int j = 0; j < RJ; j++) t += g[j] * x0[j];
+    t = warp_sum(t);
+#pragma unroll
+    for (int j = 0; j < RJ; j++) g[j] = q * (g[j] - x0[j] * t * q * q / nin);
+  }
+  return val;
+}
+
+// GRACE-1L, one warp: lane 0 holds the returned energy; ga (dE/drho of the atom) is written by the lanes
+__device__ inline double readout_1l_warp(const ReadoutDev &r, const float *ra, int mu, float *ga, bool want_grad, bool owned)
+{
+  const int lane = threadIdx.x & 31, nr = r.nrho;
+  if (!owned) {
+    if (want_grad)
+      for (int k = lane; k < nr; k += 32) ga[k] = 0.0f;
+    return 0.0;
+  }
+  double x[RJ], g[RJ];
+#pragma unroll
+  for (int j = 0; j < RJ; j++) x[j] = lane + 32 * j < nr - 1 ? (double) ra[lane + 32 * j + 1] : 0.0;
+  const double val = energy_mlp_warp(r, x, nr - 1, g, want_grad);
+  if (want_grad) {
+    if (lane == 0) ga[0] = (float) r.out_scale;
+#pragma unroll
+    for (int j = 0; j < RJ; j++)
+      if (lane + 32 * j < nr - 1) ga[lane + 32 * j + 1] = (float) g[j];
+  }
+  return (val + (double) ra[0]) * r.out_scale + r.shift[mu];
+}
+
+// GRACE-2L, one warp
+__device__ inline double readout_2l_warp(const ReadoutDev &r, const float *rho, const float *i2, int mu, double *gr,
+                                         float *go, bool want_grad, bool owned)
+{
+  const int lane = threadIdx.x & 31, nr = r.nrho;
+  if (!owned) {
+    if (want_grad)
+      for (int k = lane; k < nr; k += 32) { gr[k] = 0.0; go[k] = 0.0f; }
+    return 0.0;
+  }
+  // this lane's channels c = lane + 32 j of x[0 .. nr - 1) are rho[c + 1], i2[c + 1]
+  double rh[RJ], iv[RJ], ms1 = 0.0, ms0 = 0.0;
+#pragma unroll
+  for (int j = 0; j < RJ; j++) {
+    const int c = lane + 32 * j;
+    rh[j] = c < nr - 1 ? (double) rho[c + 1] : 0.0;
+    iv[j] = c < nr - 1 ? (double) i2[c + 1] : 0.0;
+    ms1 += rh[j] * rh[j];
+    ms0 += iv[j] * iv[j];
+  }
+  const double i20 = (double) i2[0], rho0 = (double) rho[0];
+  ms1 = warp_sum(ms1);
+  ms0 = warp_sum(ms0) + i20 * i20;
+  const double eps = 1e-10;
+  const double s1 = r.rms ? sqrt(ms1 / (nr - 1) + eps) : 1.0, s0 = r.rms ? sqrt(ms0 / nr + eps) : 1.0;
+  double x[RJ], g[RJ], lI[RJ], l0[RJ];
+#pragma unroll
+  for (int j = 0; j < RJ; j++) {
+    const int c = lane + 32 * j;
+    lI[j] = c < nr - 1 ? r.lnI[c] : 0.0;
+    l0[j] = c < nr - 1 ? r.ln0[c + 1] : 0.0;
+    x[j] = rh[j] / s1 * lI[j] + iv[j] / s0 * l0[j];
+  }
+  const double val = energy_mlp_warp(r, x, nr - 1, g, want_grad);
+  const double e = (val + rho0 + i20 / s0 * r.ln0[0]) * r.out_scale + r.shift[mu];
+  if (!want_grad) return e;
+  double t1 = 0.0, t0 = 0.0;
+  if (r.rms) {
+#pragma unroll
+    for (int j = 0; j < RJ; j++) {
+      t1 += g[j] * lI[j] * rh[j];
+      t0 += g[j] * l0[j] * iv[j];
+    }
+    t1 = warp_sum(t1);
+    t0 = warp_sum(t0) + r.out_scale * r.ln0[0] * i20;
+  }
+  if (lane == 0) {
+    gr[0] = r.out_scale;
+    go[0] = (float) (r.out_scale * r.ln0[0] / s0 - i20 * t0 / (nr * s0 * s0 * s0));
+  }
+#pragma unroll
+  for (int j = 0; j < RJ; j++) {
+    const int c = lane + 32 * j;
+    if (c < nr - 1) {
+      gr[c + 1] = g[j] * lI[j] / s1 - rh[j] * t1 / ((nr - 1) * s1 * s1 * s1);
+      go[c + 1] = (float) (g[j] * l0[j] / s0 - iv[j] * t0 / (nr * s0 * s0 * s0));
+    }
+  }
+  return e;
+}
+
 }    // namespace gb
