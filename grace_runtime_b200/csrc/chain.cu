@@ -240,9 +240,43 @@ __global__ void __launch_bounds__(256) segment_sum_kernel(const double *__restri
   if (threadIdx.x == 0) out[(size_t) s * K + k] = sh[0];
 }
 
-void launch_segment_sum(const double *v, int K, const int *seg, int nseg, double *out)
+// few long segments (one large structure): NB blocks per (segment, component) write partial sums over equal slices
+// of the segment, a second launch adds them in slice order - still a fixed tree
+__global__ void __launch_bounds__(256) segment_partial_kernel(const double *__restrict__ v, int K,
+                                                              const int *__restrict__ seg, double *partial)
+{
+  __shared__ double sh[256];
+  const int s = blockIdx.x, k = blockIdx.y, b = blockIdx.z, NB = gridDim.z;
+  const long long s0 = seg[s], len = seg[s + 1] - s0, per = (len + NB - 1) / NB;
+  const long long lo = s0 + b * per, hi = min(s0 + len, lo + per);
+  double acc = 0.0;
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) acc += v[(size_t) i * K + k];
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  for (int st = 128; st > 0; st >>= 1) {
+    if ((int) threadIdx.x < st) sh[threadIdx.x] += sh[threadIdx.x + st];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[((size_t) s * K + k) * NB + b] = sh[0];
+}
+
+__global__ void __launch_bounds__(32) segment_final_kernel(const double *__restrict__ partial, int NB, double *out)
+{
+  const int sk = blockIdx.x;    // segment * K + component
+  if (threadIdx.x != 0) return;
+  double acc = 0.0;
+  for (int b = 0; b < NB; b++) acc += partial[(size_t) sk * NB + b];
+  out[sk] = acc;
+}
+
+void launch_segment_sum(const double *v, int K, const int *seg, int nseg, double *out, double *scratch, int nb)
 {
   if (nseg == 0) return;
+  if (scratch && nb > 1) {
+    GB_LAUNCH(segment_partial_kernel, dim3(nseg, K, nb), 256, 0, v, K, seg, scratch);
+    GB_LAUNCH(segment_final_kernel, nseg * K, 32, 0, scratch, nb, out);
+    return;
+  }
   GB_LAUNCH(segment_sum_kernel, dim3(nseg, K), 256, 0, v, K, seg, out);
 }
 

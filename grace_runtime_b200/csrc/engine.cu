@@ -186,7 +186,7 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   lnI_.set_label("engine:norm_scale"); ln0_.set_label("engine:norm_scale"); rcf_.set_label("engine:cutoffs");
   arena_.set_label("work:chunk_tensors"); fv_.set_label("work:bond_forces"); I_rows_.set_label("work:messages");
   gI_rows_.set_label("work:message_gradients"); rho_rows_.set_label("work:rho"); e_atom_.set_label("work:atom_energy");
-  vir_atom_.set_label("work:atom_virial"); grho_rows_.set_label("work:rho_gradients");
+  vir_atom_.set_label("work:atom_virial"); sum_scratch_.set_label("work:sums"); grho_rows_.set_label("work:rho_gradients");
   rcsq_.upload(P.rcsq);
   std::vector<float> rcf(P.rc.begin(), P.rc.end());
   rcf_.upload(rcf);
@@ -257,7 +257,7 @@ int Engine::auto_chunk(int64_t n) const
 void Engine::release_work()
 {
   arena_.release(); fv_.release(); I_rows_.release(); gI_rows_.release(); rho_rows_.release();
-  e_atom_.release(); vir_atom_.release(); grho_rows_.release();
+  e_atom_.release(); vir_atom_.release(); grho_rows_.release(); sum_scratch_.release();
   arena_NA_ = 0;
 }
 
@@ -659,10 +659,13 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
   else evaluate_chunked(nl, energy_only, NA, tm, R);
   float *fv = fv_.get();
   // sums and gathers that leave the engine
-  if (out.energy) launch_segment_sum(e_atom_.get(), 1, nl.seg(), nsys, out.energy);
+  // one or a few large structures: partial sums by 64 blocks per structure and component
+  const int nb = (nsys <= 8 && n > 16384) ? 64 : 1;
+  double *scr = nb > 1 ? sum_scratch_.ensure((size_t) nsys * 6 * nb) : nullptr;
+  if (out.energy) launch_segment_sum(e_atom_.get(), 1, nl.seg(), nsys, out.energy, scr, nb);
   if (out.energies) launch_scatter_f64(e_atom_.get(), nl.perm(), out.energies, (int) n);
   if (!energy_only) {
-    if (out.virial) launch_segment_sum(vir_atom_.get(), 6, nl.seg(), nsys, out.virial);
+    if (out.virial) launch_segment_sum(vir_atom_.get(), 6, nl.seg(), nsys, out.virial, scr, nb);
     if (out.forces) launch_force_gather(nl.off(), nl.rev(), fv, nl.perm(), out.forces, (int) n);
   }
 }

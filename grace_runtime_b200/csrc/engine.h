@@ -82,7 +82,7 @@ class Engine {
   ReadoutDev readout_{};
   // work buffers
   DBuf<float> arena_, fv_, I_rows_, gI_rows_, rho_rows_;
-  DBuf<double> e_atom_, vir_atom_, grho_rows_;
+  DBuf<double> e_atom_, vir_atom_, grho_rows_, sum_scratch_;
   int arena_NA_ = 0;
   void setup_layer(LayerEngine &E, const LayerPlan &P);
   void setup_fused(LayerEngine &E, const LayerPlan &P);

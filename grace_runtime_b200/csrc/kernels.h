@@ -148,7 +148,10 @@ void launch_force_gather(const long long *off, const int *rev, const float *fv, 
 void static_sum(const double *d_values, long long n, int K, double *d_out);
 long long static_sum_max_rows();
 int static_sum_max_cols();
-void launch_segment_sum(const double *v, int K, const int *seg, int nseg, double *out);
+// scratch (nseg * K * nb doubles) with nb > 1: two launches with nb partial sums per (segment, component), for few long
+// segments
+void launch_segment_sum(const double *v, int K, const int *seg, int nseg, double *out, double *scratch = nullptr,
+                        int nb = 1);
 // out[perm[i]] = v[i]
 void launch_scatter_f64(const double *v, const int *perm, double *out, int n);
 
