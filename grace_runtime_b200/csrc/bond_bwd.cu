@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
   __shared__ float fe[EBB][4];     // g (3), dE/dx
   __shared__ double vred[4][6];
 
-  const int a = blockIdx.x, i = a0 + a, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int a = blockIdx.x, i = b.ilist ? b.ilist[a0 + a] : a0 + a, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
   const int ln = lane % LPE, esub = lane / LPE;
   const long long base = b.off[i];
   const int nb = b.cnt[i];

@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, S
   __shared__ int sk[EB], smu[EB], sj[EB];
   __shared__ float red[NQ][CP];
 
-  const int a = blockIdx.x, i = a0 + a, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int a = blockIdx.x, i = b.ilist ? b.ilist[a0 + a] : a0 + a, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
   const int ln = lane % LPE, esub = lane / LPE;
   const int Ibase = blockIdx.y * NIT;
   const long long base = b.off[i];

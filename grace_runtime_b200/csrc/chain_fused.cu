@@ -373,9 +373,9 @@ template<int TA>
 __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, FusedIO io)
 {
   GB_DYN_SMEM(float4, smem4);
-  __shared__ int s_mu_all[NG][TA];
+  __shared__ int s_mu_all[NG][TA], s_at_all[NG][TA];
   const int btid = threadIdx.x, grp = btid / NT, tid = btid % NT;
-  int *s_mu = s_mu_all[grp];
+  int *s_mu = s_mu_all[grp], *s_at = s_at_all[grp];    // element and list index of the tile's atoms
   const int ntiles = (io.na + TA - 1) / TA;
   // tables first, the tile's tensors behind them
   char *tp = reinterpret_cast<char *>(smem4);
@@ -417,7 +417,11 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
   for (int tile = blockIdx.x * NG + grp; tile < ntiles; tile += gridDim.x * NG) {
     const int al0 = tile * TA;                      // first atom of the tile, chunk-local
     const int nta = min(TA, io.na - al0);
-    if (tid < TA) s_mu[tid] = io.mu[io.a0 + al0 + min(tid, nta - 1)];
+    if (tid < TA) {
+      const int q = io.a0 + al0 + min(tid, nta - 1), i = io.ilist ? io.ilist[q] : q;
+      s_at[tid] = i;
+      s_mu[tid] = io.mu[i];
+    }
     {    // bond sums of the tile: global [f][NA][C] -> shared [f][TA][C]; atoms past the end are zero
       const int C = io.CQ;
       float *q = sm + (size_t) s_soff[io.tQ] * TA;
@@ -449,11 +453,11 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
       const float *I = sm + (size_t) s_soff[io.t_I] * TA;
       for (int idx = tid; idx < total; idx += NT) {
         const int c = idx % CR, f = (idx / CR) % nI, a = idx / (CR * nI);
-        io.I_rows[((size_t) (io.a0 + al0 + a) * nI + f) * CR + c] = I[(f * TA + a) * CR + c];
+        io.I_rows[((size_t) s_at[a] * nI + f) * CR + c] = I[(f * TA + a) * CR + c];
       }
       const float *rho = sm + (size_t) s_soff[io.t_rho] * TA;
       for (int idx = tid; idx < nta * io.nrho; idx += NT)
-        io.rho_rows[(size_t) (io.a0 + al0) * io.nrho + idx] = rho[idx];
+        io.rho_rows[(size_t) s_at[idx / io.nrho] * io.nrho + idx % io.nrho] = rho[idx];
     }
     const bool bwd = io.mode & FUSED_BWD;
     if (bwd) {    // gradients start at zero; those that alias forward tensors take their storage over now
@@ -468,7 +472,7 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
       if (w < nta) {
         const float *rho = sm + (size_t) s_soff[io.t_rho] * TA + w * io.nrho;
         float *grho = sm + (size_t) s_soff[io.t_grho] * TA + w * io.nrho;
-        const size_t i = io.a0 + al0 + w;
+        const size_t i = s_at[w];
         const double e = readout_1l_warp(io.ro, rho, s_mu[w], grho, bwd, io.ro.owned(i));
         if (ln == 0) io.e_atom[i] = e;
       } else if (w < TA && bwd) {
@@ -479,7 +483,7 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
     if (io.mode & FUSED_READOUT_2L) {
       const int w = tid >> 5, ln = tid & 31;
       if (w < nta) {
-        const size_t i = io.a0 + al0 + w;
+        const size_t i = s_at[w];
         const float *I2 = sm + (size_t) s_soff[io.t_I2] * TA + w * io.nrho;
         float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + w * io.nrho;
         const double e = readout_2l_warp(io.ro, io.rho_rows + i * io.nrho, I2, s_mu[w], io.grho_rows + i * io.nrho, gI2,
@@ -495,11 +499,11 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
       float *gI = sm + (size_t) s_soff[io.t_gI] * TA;
       for (int idx = tid; idx < total; idx += NT) {
         const int c = idx % CR, a = (idx / CR) % TA, f = idx / (CR * TA);
-        gI[idx] = a < nta ? io.gI_rows[((size_t) (io.a0 + al0 + a) * nI + f) * CR + c] : 0.0f;
+        gI[idx] = a < nta ? io.gI_rows[((size_t) s_at[a] * nI + f) * CR + c] : 0.0f;
       }
       float *grho = sm + (size_t) s_soff[io.t_grho] * TA;
       for (int idx = tid; idx < TA * io.nrho; idx += NT)
-        grho[idx] = idx < nta * io.nrho ? (float) io.grho_rows[(size_t) (io.a0 + al0) * io.nrho + idx] : 0.0f;
+        grho[idx] = idx < nta * io.nrho ? (float) io.grho_rows[(size_t) s_at[idx / io.nrho] * io.nrho + idx % io.nrho] : 0.0f;
     }
     group_sync();
     if (bwd) {

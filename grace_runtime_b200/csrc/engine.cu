@@ -382,7 +382,7 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
   GB_CUDA(cudaStreamSynchronize(dev().stream));
 }
 
-void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu)
+void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist)
 {
   const ModelPlan &P = plan_;
   const LayerPlan &LP = *E.plan;
@@ -412,6 +412,7 @@ void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const i
   io.e_atom = e_atom_.get();
   io.a0 = a0;
   io.na = na;
+  io.ilist = ilist;
   const int TA = E.fused_TA;
   const int ntiles = (na + TA - 1) / TA, nctas = (ntiles + fused_groups() - 1) / fused_groups();
   launch_chain_fused(TA, E.fused, io, std::min(nctas, dev().sm_count));
@@ -427,23 +428,28 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   const long long qf = std::max(L1_.q_floats, L2_.q_floats);
   arena_.ensure((size_t) 2 * qf * NA);
   arena_NA_ = 0;    // the chunked layout, if it was bound, no longer is
-  const BondsDev bonds = nl.bonds();
   const int *mu = nl.mu_sorted();
   float *fv = fv_.get();
   float *Q = arena_.get();
   const int bwd = energy_only ? 0 : FUSED_BWD;
+  // atoms evaluated per layer: all of the list, or the exact sets of a domain-decomposed caller (positions a0 .. of
+  // the set are the chunk's atoms)
+  BondsDev b0 = nl.bonds(), b1 = nl.bonds();
+  b0.ilist = R.list0;
+  b1.ilist = R.list1;
+  const int64_t n0 = R.list0 ? R.n0 : n, n1 = R.list1 ? R.n1 : n;
   if (P.layers == 1) {
     const LayerDev L = layer_dev(L1_);
     const float *gQ = arena_.get() + (size_t) L1_.q_floats * NA;
-    for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
+    for (int64_t a0 = 0; a0 < n0; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, n0 - a0);
       if (tm) tm->begin(StageTimer::FWD);
-      launch_bond_fwd(P.lmax, bonds, L, Q, NA, (int) a0, na);
-      run_fused(L1_, FUSED_READOUT_1L | bwd, NA, (int) a0, na, mu);
+      launch_bond_fwd(P.lmax, b0, L, Q, NA, (int) a0, na);
+      run_fused(L1_, FUSED_READOUT_1L | bwd, NA, (int) a0, na, mu, R.list0);
       if (tm) tm->end(StageTimer::FWD);
       if (energy_only) continue;
       if (tm) tm->begin(StageTimer::BWD);
-      launch_bond_bwd(P.lmax, bonds, L, gQ, NA, (int) a0, na, fv, vir_atom_.get(), 0);
+      launch_bond_bwd(P.lmax, b0, L, gQ, NA, (int) a0, na, fv, vir_atom_.get(), 0);
       if (tm) tm->end(StageTimer::BWD);
     }
     return;
@@ -462,25 +468,25 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   Lb.gmsg = gI_rows_.get();
   const float *gQ1 = arena_.get() + (size_t) L1_.q_floats * NA, *gQ2 = arena_.get() + (size_t) L2_.q_floats * NA;
   if (tm) tm->begin(StageTimer::FWD);
-  for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {    // layer 1 forward: messages and rho of all atoms
-    const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
-    launch_bond_fwd(P.lmax, bonds, La, Q, NA, (int) a0, na);
-    run_fused(L1_, FUSED_STORE_MSG, NA, (int) a0, na, mu);
+  for (int64_t a0 = 0; a0 < n1; a0 += NA) {    // layer 1 forward: messages and rho of the atoms layer 2 reads
+    const int na = (int) std::min<int64_t>(NA, n1 - a0);
+    launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
+    run_fused(L1_, FUSED_STORE_MSG, NA, (int) a0, na, mu, R.list1);
   }
-  for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {    // layer 2, energy, layer-2 reverse
-    const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
-    launch_bond_fwd(P.lmax, bonds, Lb, Q, NA, (int) a0, na);
-    run_fused(L2_, FUSED_READOUT_2L | bwd, NA, (int) a0, na, mu);
-    if (!energy_only) launch_bond_bwd(P.lmax, bonds, Lb, gQ2, NA, (int) a0, na, fv, vir_atom_.get(), 0);
+  for (int64_t a0 = 0; a0 < n0; a0 += NA) {    // layer 2, energy, layer-2 reverse
+    const int na = (int) std::min<int64_t>(NA, n0 - a0);
+    launch_bond_fwd(P.lmax, b0, Lb, Q, NA, (int) a0, na);
+    run_fused(L2_, FUSED_READOUT_2L | bwd, NA, (int) a0, na, mu, R.list0);
+    if (!energy_only) launch_bond_bwd(P.lmax, b0, Lb, gQ2, NA, (int) a0, na, fv, vir_atom_.get(), 0);
   }
   if (tm) tm->end(StageTimer::FWD);
   if (energy_only) return;
   if (tm) tm->begin(StageTimer::BWD);
-  for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
-    const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
-    launch_bond_fwd(P.lmax, bonds, La, Q, NA, (int) a0, na);
-    run_fused(L1_, FUSED_LOAD_SEED | FUSED_BWD, NA, (int) a0, na, mu);
-    launch_bond_bwd(P.lmax, bonds, La, gQ1, NA, (int) a0, na, fv, vir_atom_.get(), 1);
+  for (int64_t a0 = 0; a0 < n1; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
+    const int na = (int) std::min<int64_t>(NA, n1 - a0);
+    launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
+    run_fused(L1_, FUSED_LOAD_SEED | FUSED_BWD, NA, (int) a0, na, mu, R.list1);
+    launch_bond_bwd(P.lmax, b1, La, gQ1, NA, (int) a0, na, fv, vir_atom_.get(), 1);
   }
   if (tm) tm->end(StageTimer::BWD);
 }
@@ -582,40 +588,36 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
   }
 }
 
-// smallest and one past the largest list position of the atoms with caller index < nlocal ([0], [1]) and < ninner
-// ([2], [3])
-__global__ void __launch_bounds__(256) active_range_kernel(const int *__restrict__ perm, int nlocal, int ninner,
-                                                           int *r, long long n)
-{
-  const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  const int p = perm[i];
-  if (p < nlocal) { atomicMin(&r[0], (int) i); atomicMax(&r[1], (int) i + 1); }
-  if (p < ninner) { atomicMin(&r[2], (int) i); atomicMax(&r[3], (int) i + 1); }
-}
-
-ActiveRanges Engine::active_ranges(NeighborList &nl, int nlocal, int ninner)
+ActiveRanges Engine::active_ranges(NeighborList &nl, int nlocal, int ninner, DBuf<int> &list0, DBuf<int> &list1)
 {
   ActiveRanges R;
   const int64_t n = nl.n();
-  R.hi0 = R.hi1 = n;
+  R.hi0 = R.hi1 = R.n0 = R.n1 = n;
   if (nlocal < 0 || n == 0) return R;
   R.nlocal = nlocal;
-  const int init[4] = {INT_MAX, 0, INT_MAX, 0};
-  int *d = range_buf_.ensure(4);
+  // once per list build: the order of the list on the host, the two sets in that order back to the device
+  std::vector<int> perm((size_t) n), l0, l1;
   cudaStream_t st = dev().stream;
-  GB_CUDA(cudaMemcpyAsync(d, init, sizeof(init), cudaMemcpyHostToDevice, st));
-  const int *perm = nl.perm();
-  const int ni = ninner < 0 ? INT_MAX : ninner;
-  GB_LAUNCH(active_range_kernel, nblocks(n, 256), 256, 0, perm, nlocal, ni, d, (long long) n);
-  int h[4];
-  GB_CUDA(cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaMemcpyAsync(perm.data(), nl.perm(), sizeof(int) * (size_t) n, cudaMemcpyDeviceToHost, st));
   GB_CUDA(cudaStreamSynchronize(st));
-  R.lo0 = h[1] > 0 ? h[0] : 0; R.hi0 = h[1];
-  R.lo1 = h[3] > 0 ? h[2] : 0; R.hi1 = h[3];
-  // the owned atoms need their own layer-1 outputs
-  R.lo1 = std::min(R.lo1, R.lo0);
-  R.hi1 = std::max(R.hi1, R.hi0);
+  const int ni = ninner < 0 ? INT_MAX : std::max(ninner, nlocal);
+  for (int64_t i = 0; i < n; i++) {
+    if (perm[(size_t) i] < nlocal) l0.push_back((int) i);
+    if (perm[(size_t) i] < ni) l1.push_back((int) i);
+  }
+  R.n0 = (int64_t) l0.size();
+  R.n1 = (int64_t) l1.size();
+  R.lo0 = l0.empty() ? 0 : l0.front(); R.hi0 = l0.empty() ? 0 : l0.back() + 1;
+  R.lo1 = l1.empty() ? 0 : l1.front(); R.hi1 = l1.empty() ? 0 : l1.back() + 1;
+  list0.set_label("work:active_atoms");
+  list1.set_label("work:active_atoms");
+  list0.ensure(std::max<size_t>(l0.size(), 1));
+  list1.ensure(std::max<size_t>(l1.size(), 1));
+  if (!l0.empty()) GB_CUDA(cudaMemcpyAsync(list0.get(), l0.data(), sizeof(int) * l0.size(), cudaMemcpyHostToDevice, st));
+  if (!l1.empty()) GB_CUDA(cudaMemcpyAsync(list1.get(), l1.data(), sizeof(int) * l1.size(), cudaMemcpyHostToDevice, st));
+  GB_CUDA(cudaStreamSynchronize(st));    // the host vectors go out of scope
+  R.list0 = list0.get();
+  R.list1 = list1.get();
   return R;
 }
 
@@ -635,8 +637,9 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
     if (out.virial && !energy_only) GB_CUDA(cudaMemsetAsync(out.virial, 0, sizeof(double) * 6 * nsys, st));
     return;
   }
-  const bool partial = R.lo0 > 0 || R.hi0 < n || R.lo1 > 0 || R.hi1 < n;
-  const int64_t widest = std::max<int64_t>(1, std::max(R.hi0 - R.lo0, R.hi1 - R.lo1));
+  if (!fused_) R.list0 = R.list1 = nullptr;    // the per-operation path evaluates the enclosing ranges
+  const bool partial = R.list0 ? (R.n0 < n || R.n1 < n) : (R.lo0 > 0 || R.hi0 < n || R.lo1 > 0 || R.hi1 < n);
+  const int64_t widest = std::max<int64_t>(1, R.list0 ? std::max(R.n0, R.n1) : std::max(R.hi0 - R.lo0, R.hi1 - R.lo1));
   const int NA = (int) std::min<int64_t>(widest, chunk > 0 ? chunk : n);
   e_atom_.ensure(n);
   if (!energy_only) vir_atom_.ensure(6 * n);
@@ -826,7 +829,7 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     list_n_ = n;
     have_list_ = true;
     rebuilds++;
-    if (nlocal >= 0) ranges = engine_->active_ranges(nl_, std::min(nlocal, n), ninner < 0 ? n : std::min(ninner, n));
+    if (nlocal >= 0) ranges = engine_->active_ranges(nl_, std::min(nlocal, n), ninner < 0 ? n : std::min(ninner, n), list0_, list1_);
     timer_.end(StageTimer::NL);
   }
   timer_.begin(StageTimer::GEOM);

@@ -45,6 +45,10 @@ struct LayerEngine {
 struct ActiveRanges {
   int nlocal = -1;
   int64_t lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
+  // the same sets exactly, as lists of list positions in increasing order (device; the fused path evaluates these,
+  // the per-operation path the enclosing ranges)
+  const int *list0 = nullptr, *list1 = nullptr;
+  int64_t n0 = 0, n1 = 0;
 };
 
 // outputs of one evaluation, device pointers (null: not wanted)
@@ -65,7 +69,7 @@ class Engine {
   void evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm,
                 const ActiveRanges *act = nullptr);
   // ranges of the list order that hold the atoms with caller index < nlocal / < ninner (reads back 4 integers)
-  ActiveRanges active_ranges(NeighborList &nl, int nlocal, int ninner);
+  ActiveRanges active_ranges(NeighborList &nl, int nlocal, int ninner, DBuf<int> &list0, DBuf<int> &list1);
   // bond-force slots [3 * nslots] the list zeroes for bonds outside the cutoff (grown here)
   float *bond_forces(int64_t nslots) { return fv_.ensure(3 * (size_t) std::max<int64_t>(nslots, 1)); }
   const double *rcsq() const { return rcsq_.get(); }
@@ -89,8 +93,7 @@ class Engine {
   bool fused_ = false;        // both layers run as the fused shared-memory kernel
   void evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
   void evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
-  DBuf<int> range_buf_;
-  void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu);
+  void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist);
   void bind_arena(LayerEngine &E, int NA);
   void run(LayerEngine &E, const Program &prog, const int *mu, int NA);
   LayerDev layer_dev(const LayerEngine &E) const;
@@ -125,6 +128,7 @@ class SystemObj {
   int last_chunk = 0;
   int nlocal = -1, ninner = -1;    // owned atoms / atoms with layer-1 outputs of a domain-decomposed caller (-1: all)
   ActiveRanges ranges;
+  DBuf<int> list0_, list1_;
   void set_owned(int nlocal_, int ninner_);
   double stage_ms[StageTimer::NSTAGE] = {0, 0, 0, 0, 0};
   void release();

@@ -43,6 +43,7 @@ struct BondsDev {
   const float4 *rec;       // per slot: bond vector x_j - x_i + S cell (fp32 of the fp64 difference), j in .w
   const int *cslot;        // per compacted bond: the slot it came from
   const int *mu;           // [n] model element of each atom (list order)
+  const int *ilist;        // atoms to evaluate, in list order (null: all): position a0 + a of it is chunk atom a
 };
 
 // per layer: radial table, chemical weights, messages
@@ -126,7 +127,8 @@ struct FusedIO {
   ReadoutDev ro;
   const int *mu;                    // [n] elements in list order
   double *e_atom;
-  int a0, na;                       // first atom of the chunk in list order, atoms of the chunk
+  int a0, na;                       // first atom of the chunk in list order (or position in ilist), atoms of the chunk
+  const int *ilist;                 // atoms to evaluate (null: all)
 };
 
 // TA: atoms per tile (1, 2, 3, 4, 6, 8); grid CTAs loop over the tiles

@@ -543,6 +543,7 @@ BondsDev NeighborList::bonds() const
   b.rec = rec_.get();
   b.cslot = cslot_.get();
   b.mu = mu_s_.get();
+  b.ilist = nullptr;
   return b;
 }
 

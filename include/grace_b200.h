@@ -116,8 +116,7 @@ int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, 
  * energies depend on are returned, ghost rows included, for the caller to send back to the owners.  The ghosts
  * [nlocal, ninner) are those whose layer-1 outputs owned atoms read (GRACE-2L: ghosts within cutoff + skin of an owned
  * atom; ninner < 0: all ghosts); ghosts behind ninner only serve as neighbours, and nothing but the neighbour list is
- * computed for them.  Work is skipped for runs of the spatially sorted atom order, so it pays to make the cell's first
- * vector the one the domains are cut across.  nlocal < 0: all atoms are owned (default).  Counterpart of nlocal / ghost atoms in the reference's engine input
+ * computed for them.  nlocal < 0: all atoms are owned (default).  Counterpart of nlocal / ghost atoms in the reference's engine input
  * (libgrace/include/grace/kk/grace_2l_kk.h:87-107) and of inum / ilist in its CPU drivers
  * (libgrace/include/grace/system.h:113-121); the plug-in interface kk_api.h itself is single-GPU. */
 int grace_system_set_owned(grace_system *s, int nlocal, int ninner);
