@@ -47,6 +47,8 @@ SIGNATURES = {
     "grace_model_element_name": (C.c_char_p, [_P, _I]),
     "grace_model_engine_setups": (_I64, [_P]),
     "grace_model_dense_flops": (_D, [_P]),
+    "grace_model_radial_mlp_device": (_I, [_P, _I, _I64, _P, _P, _P]),
+    "grace_model_radial_mlp_width": (_I, [_P, _I]),
     "grace_model_free": (None, [_P]),
     "grace_system_create": (_I, [_P, _P, _I, _D, _I, _I, _P]),
     "grace_system_cutoff": (_D, [_P]),
@@ -231,6 +233,14 @@ class Model:
     def dense_flops(self):
         """fp32 flops per atom of the dense network (forward + reverse) in the engine's plan; 0 before the first System"""
         return float(_lib.grace_model_dense_flops(self._h))
+
+    def radial_mlp_width(self, layer=1):
+        return int(_lib.grace_model_radial_mlp_width(self._h, int(layer)))
+
+    def radial_mlp_device(self, layer, nb, x_ptr, R_ptr, dR_ptr):
+        """Exact radial MLP of a layer on the tensor cores: device pointers to x [nb] and the outputs [nb, width]."""
+        _check(_lib.grace_model_radial_mlp_device(self._h, int(layer), int(nb), C.c_void_p(x_ptr), C.c_void_p(R_ptr),
+                                                  C.c_void_p(dR_ptr)))
 
     def validate_uq(self):
         raise ValueError("the model has no UQ head usable by this backend")

@@ -197,6 +197,19 @@ double grace_model_dense_flops(const grace_model *m)
   std::lock_guard<std::mutex> lk(m->m->mu);
   return m->m->engine ? m->m->engine->plan().dense_flops_per_atom : 0.0;
 }
+int grace_model_radial_mlp_device(grace_model *m, int layer, int64_t nb, const float *d_x, float *d_R, float *d_dR)
+{
+  return guarded([&] {
+    if (!m) throw InvalidArgument("model must be given");
+    m->m->radial_exact(layer, d_x, (long long) nb, d_R, d_dR);
+  });
+}
+int grace_model_radial_mlp_width(const grace_model *m, int layer)
+{
+  if (!m || layer < 1 || layer > m->m->model.layers) return 0;
+  const auto &L = layer == 1 ? m->m->model.rad1 : m->m->model.rad2;
+  return L.empty() ? 0 : L.back().n_out;
+}
 void grace_model_free(grace_model *m)
 {
   std::lock_guard<std::recursive_mutex> lk(g_device_mu);

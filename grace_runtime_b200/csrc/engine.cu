@@ -674,6 +674,21 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
 }
 
 // ---- model -----------------------------------------------------------------------------------------------------
+void ModelObj::radial_exact(int layer, const float *d_x, long long nb, float *d_R, float *d_dR)
+{
+  require_initialized();
+  if (layer < 1 || layer > model.layers) throw InvalidArgument("layer must be 1 .. layers of the model");
+  if (nb < 0 || (nb > 0 && (!d_x || !d_R || !d_dR))) throw InvalidArgument("distances and outputs must be given");
+  std::lock_guard<std::mutex> lk(mu);
+  RadialMlpTC &r = radial_tc[layer - 1];
+  if (!r.ready()) {
+    if (layer == 1) r.setup(model, model.rad1, model.chain1.c0);
+    else r.setup(model, model.rad2, model.cr);
+  }
+  r.run(d_x, nb, d_R, d_dR);
+  r.check();
+}
+
 std::shared_ptr<Engine> ModelObj::get_engine(int spline_n)
 {
   std::lock_guard<std::mutex> lk(mu);

@@ -7,6 +7,7 @@
 #include "kernels.h"
 #include "nlist.h"
 #include "plan.h"
+#include "radial_mlp_tc.h"
 
 #include <memory>
 #include <mutex>
@@ -107,6 +108,9 @@ struct ModelObj {
   std::shared_ptr<Engine> engine;    // created by the first System / Batch
   int64_t setups = 0;
   std::shared_ptr<Engine> get_engine(int spline_n);
+  // exact radial MLP of layer 1 or 2 on the tensor cores (set up by the first call)
+  RadialMlpTC radial_tc[2];
+  void radial_exact(int layer, const float *d_x, long long nb, float *d_R, float *d_dR);
 };
 
 struct Workspace {

@@ -93,6 +93,13 @@ int64_t grace_model_engine_setups(const grace_model *m);                 /* engi
  * of the engine's plan; 0 before the first System / Batch of the model.  Diagnostics for roofline figures; no
  * counterpart in the reference. */
 double grace_model_dense_flops(const grace_model *m);
+/* The exact radial MLP of layer 1 or 2 (no tables) for nb scaled distances x = r / r_cut in (0, 1): value R[nb][w] and
+ * derivative dR/dx [nb][w] with w = grace_model_radial_mlp_width(), outputs ordered [l][channel]; device pointers, fp32.
+ * Runs as tcgen05 tensor-core GEMMs with fused activations (shapes: up to 8 basis functions, two hidden layers of 64,
+ * w a multiple of 32 up to 192; other shapes return GRACE_UNSUPPORTED).  Counterpart of compute_mlp_radial of the
+ * reference's generic engine (libgrace/include/grace/kk/grace_1l_kk_impl.h:1592-1751). */
+int grace_model_radial_mlp_device(grace_model *m, int layer, int64_t nb, const float *d_x, float *d_R, float *d_dR);
+int grace_model_radial_mlp_width(const grace_model *m, int layer);
 void grace_model_free(grace_model *m);
 
 /* ---- System (kk_api.h:68-90): one structure, neighbour list with a Verlet skin kept on the device ---- */
