@@ -87,14 +87,23 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
           for (int ch = 0; ch < NCH; ch++) {
             const int n = ln + ch * LPE;
             if (n < C) {
-              const float *cf = L.tab + ((size_t) k * 4 * NL) * C + n;
               float R[NL], dR[NL];
+              if (L.Rex) {    // exact radial MLP, evaluated per slot beforehand
+                const size_t ro = (size_t) (base + b0 + e) * (NL * C) + n;
 #pragma unroll
-              for (int l = 0; l < NL; l++) {
-                const float c0 = __ldg(cf + (size_t) (0 * NL + l) * C), c1 = __ldg(cf + (size_t) (1 * NL + l) * C);
-                const float c2 = __ldg(cf + (size_t) (2 * NL + l) * C), c3 = __ldg(cf + (size_t) (3 * NL + l) * C);
-                R[l] = c0 + t * (c1 + t * (c2 + t * c3));
-                dR[l] = (c1 + t * (2.0f * c2 + t * 3.0f * c3)) * fN;
+                for (int l = 0; l < NL; l++) {
+                  R[l] = __ldg(L.Rex + ro + l * C);
+                  dR[l] = __ldg(L.dRex + ro + l * C);
+                }
+              } else {
+                const float *cf = L.tab + ((size_t) k * 4 * NL) * C + n;
+#pragma unroll
+                for (int l = 0; l < NL; l++) {
+                  const float c0 = __ldg(cf + (size_t) (0 * NL + l) * C), c1 = __ldg(cf + (size_t) (1 * NL + l) * C);
+                  const float c2 = __ldg(cf + (size_t) (2 * NL + l) * C), c3 = __ldg(cf + (size_t) (3 * NL + l) * C);
+                  R[l] = c0 + t * (c1 + t * (c2 + t * c3));
+                  dR[l] = (c1 + t * (2.0f * c2 + t * 3.0f * c3)) * fN;
+                }
               }
 #pragma unroll
               for (int I = 0; I < NIT; I++) {

@@ -69,13 +69,19 @@ __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, S
         for (int ch = 0; ch < NCH; ch++) {
           const int n = ln + ch * LPE;
           if (n < C) {
-            const float *cf = L.tab + ((size_t) k * 4 * NL) * C + n;
             float R[NL];
+            if (L.Rex) {    // exact radial MLP, evaluated per slot beforehand
+              const float *rr = L.Rex + (size_t) (base + b0 + e) * (NL * C) + n;
 #pragma unroll
-            for (int l = 0; l < NL; l++) {
-              const float c0 = __ldg(cf + (size_t) (0 * NL + l) * C), c1 = __ldg(cf + (size_t) (1 * NL + l) * C);
-              const float c2 = __ldg(cf + (size_t) (2 * NL + l) * C), c3 = __ldg(cf + (size_t) (3 * NL + l) * C);
-              R[l] = c0 + t * (c1 + t * (c2 + t * c3));
+              for (int l = 0; l < NL; l++) R[l] = __ldg(rr + l * C);
+            } else {
+              const float *cf = L.tab + ((size_t) k * 4 * NL) * C + n;
+#pragma unroll
+              for (int l = 0; l < NL; l++) {
+                const float c0 = __ldg(cf + (size_t) (0 * NL + l) * C), c1 = __ldg(cf + (size_t) (1 * NL + l) * C);
+                const float c2 = __ldg(cf + (size_t) (2 * NL + l) * C), c3 = __ldg(cf + (size_t) (3 * NL + l) * C);
+                R[l] = c0 + t * (c1 + t * (c2 + t * c3));
+              }
             }
 #pragma unroll
             for (int I = 0; I < NIT; I++) {
@@ -140,6 +146,28 @@ template<int LMAX> void launch_l(const BondsDev &b, const LayerDev &L, float *Q,
 }
 
 }    // namespace
+
+__global__ void __launch_bounds__(128) bond_x_kernel(BondsDev b, const float *__restrict__ rc, int nel, float *x)
+{
+  const int i = blockIdx.x;
+  const long long base = b.off[i];
+  const int ns = (int) (b.off[i + 1] - base), nb = b.cnt[i], mui = b.mu[i];
+  for (int s = threadIdx.x; s < ns; s += 128) {
+    float v = 0.5f;
+    if (s < nb) {
+      const float4 rec = b.rec[base + s];
+      const int j = __float_as_int(rec.w);
+      v = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z) / rc[mui * nel + b.mu[j]];
+    }
+    x[base + s] = v;
+  }
+}
+
+void launch_bond_x(const BondsDev &b, const float *rc, int n_elements, float *x, long long n)
+{
+  if (n == 0) return;
+  GB_LAUNCH(bond_x_kernel, (unsigned) n, 128, 0, b, rc, n_elements, x);
+}
 
 void launch_bond_fwd(int lmax, const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na)
 {

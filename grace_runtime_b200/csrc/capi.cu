@@ -173,7 +173,7 @@ int grace_model_load(const char *path, int spline, grace_model **out)
 {
   return guarded([&] {
     if (!path || !out) throw InvalidArgument("path and out must be given");
-    if (spline < 16) throw InvalidArgument("spline N must be >= 16");
+    if (spline != 0 && spline < 16) throw InvalidArgument("spline N must be >= 16 (or 0: exact radial MLP)");
     auto m = std::make_shared<ModelObj>();
     m->model = GraceModel::load(path);
     m->path = path;

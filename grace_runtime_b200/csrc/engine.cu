@@ -173,8 +173,15 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
   E.tensors_host.assign(P.tensors.size(), TensorDev{nullptr, 0});
 }
 
-Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n))
+Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n > 0 ? spline_n : 1024))
 {
+  if (spline_n == 0) {    // exact radial MLP (what the reference's generic engine evaluates), tensor-core kernel
+    exact_ = true;
+    rad1_.setup(m, m.rad1, m.chain1.c0);
+    if (m.layers == 2) rad2_.setup(m, m.rad2, m.cr);
+    xs_.set_label("work:radial"); R1_.set_label("work:radial"); dR1_.set_label("work:radial");
+    R2_.set_label("work:radial"); dR2_.set_label("work:radial");
+  }
   require_initialized();
   const ModelPlan &P = plan_;
   if (P.lmax < 1 || P.lmax > 4) throw Unsupported("models with lmax outside 1..4 are not supported");
@@ -258,6 +265,7 @@ void Engine::release_work()
 {
   arena_.release(); fv_.release(); I_rows_.release(); gI_rows_.release(); rho_rows_.release();
   e_atom_.release(); vir_atom_.release(); grho_rows_.release(); sum_scratch_.release();
+  xs_.release(); R1_.release(); dR1_.release(); R2_.release(); dR2_.release();
   arena_NA_ = 0;
 }
 
@@ -281,6 +289,8 @@ LayerDev Engine::layer_dev(const LayerEngine &E) const
   L.C = E.plan->C;
   L.n_msg = E.plan->n_msg;
   L.n_elements = plan_.n_elements;
+  L.Rex = exact_ ? (&E == &L1_ ? R1_.get() : R2_.get()) : nullptr;
+  L.dRex = exact_ ? (&E == &L1_ ? dR1_.get() : dR2_.get()) : nullptr;
   return L;
 }
 
@@ -658,8 +668,28 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
       }
     }
   }
+  if (exact_) {    // R and dR/dx of every list slot by the tensor-core MLP (memory: slots x outputs x 8 bytes per layer)
+    const long long ns = nl.nslots();
+    if (tm) tm->begin(StageTimer::FWD);
+    launch_bond_x(nl.bonds(), rcf_.get(), plan_.n_elements, xs_.ensure((size_t) std::max<long long>(ns, 1)), (long long) n);
+    const size_t w1 = (size_t) rad1_.n_out();
+    R1_.ensure(w1 * (size_t) std::max<long long>(ns, 1));
+    dR1_.ensure(w1 * (size_t) std::max<long long>(ns, 1));
+    rad1_.run(xs_.get(), ns, R1_.get(), dR1_.get());
+    if (plan_.layers == 2) {
+      const size_t w2 = (size_t) rad2_.n_out();
+      R2_.ensure(w2 * (size_t) std::max<long long>(ns, 1));
+      dR2_.ensure(w2 * (size_t) std::max<long long>(ns, 1));
+      rad2_.run(xs_.get(), ns, R2_.get(), dR2_.get());
+    }
+    if (tm) tm->end(StageTimer::FWD);
+  }
   if (fused_) evaluate_fused(nl, energy_only, NA, tm, R);
   else evaluate_chunked(nl, energy_only, NA, tm, R);
+  if (exact_) {
+    rad1_.check();
+    if (plan_.layers == 2) rad2_.check();
+  }
   float *fv = fv_.get();
   // sums and gathers that leave the engine
   // one or a few large structures: partial sums by 64 blocks per structure and component

@@ -92,6 +92,10 @@ class Engine {
   void setup_layer(LayerEngine &E, const LayerPlan &P);
   void setup_fused(LayerEngine &E, const LayerPlan &P);
   bool fused_ = false;        // both layers run as the fused shared-memory kernel
+  // exact radial MLP per bond on the tensor cores instead of the tables (spline N = 0)
+  bool exact_ = false;
+  RadialMlpTC rad1_, rad2_;
+  DBuf<float> xs_, R1_, dR1_, R2_, dR2_;
   void evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
   void evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
   void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist);

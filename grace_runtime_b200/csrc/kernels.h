@@ -54,11 +54,16 @@ struct LayerDev {
   const float *msg;        // [n][n_msg][C] message rows of all atoms (layer 2) or null
   float *gmsg;             // [n][n_msg][C] dE/dmsg rows, added to atomically by the reverse bond kernel
   int N, C, n_msg, n_elements;
+  // exact radial MLP instead of the tables: value and d/dx per list slot, [slot][l][C] (null: tables)
+  const float *Rex, *dRex;
 };
 
 // element of a tensor: p[(f * NA + a) * C + c]; NA: atom stride of the chunk tensors, na <= NA: atoms in use
 void launch_mv(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na);
 void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, int C);
+
+// x[slot] = r / r_cut of the bond compacted into the slot (0.5 for slots without a bond): input of the exact radial MLP
+void launch_bond_x(const BondsDev &b, const float *rc, int n_elements, float *x, long long n);
 
 // Q[(I, lm)][a][n] = sum over the bonds of atom a0 + a of Y_lm R[n, l] msg_I[n]
 void launch_bond_fwd(int lmax, const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na);

@@ -5,9 +5,9 @@
 // every intermediate in global memory (libgrace/include/grace/kk/grace_1l_kk_impl.h:1592-1751); forward-mode
 // derivative as libgrace/include/grace/radial_x.h:30-60.
 //
-// One CTA of 128 threads per SM loops over tiles of 64 bonds.  A tile is a 128-row operand: rows 0-63 carry the values
-// (g, h1, h2), rows 64-127 the derivatives (dg, dh1, dh2), so one MMA chain propagates both; thread t owns row t and
-// tensor-memory lane t.  Operands live in shared memory in the canonical K-major layout without swizzle (8-row x
+// One CTA of 256 threads per SM loops over tiles of 64 bonds.  A tile is a 128-row operand: rows 0-63 carry the values
+// (g, h1, h2), rows 64-127 the derivatives (dg, dh1, dh2), so one MMA chain propagates both; threads t and t + 128 own
+// row t = tensor-memory lane t and take 32 of its columns each.  Operands live in shared memory in the canonical K-major layout without swizzle (8-row x
 // 16-byte core matrices); the weights are converted to that layout, transposed, scaled and split into tf32 hi + lo on
 // the host once.  fp32-level accuracy comes from the split: a b ~ a_lo b_hi + a_hi b_lo + a_hi b_hi.
 //
@@ -23,6 +23,7 @@ namespace gb {
 namespace {
 
 constexpr int TM = 128;         // rows of a tile = tensor-memory lanes
+constexpr int NTH = 256;        // threads: two per row
 constexpr int TB = 64;          // bonds of a tile
 constexpr int KH = 64;          // hidden width (both hidden layers)
 constexpr int KG = 8;           // padded width of the radial basis
@@ -100,7 +101,7 @@ struct Act {
       h = tanhf(s);
       slope = 1.0f - h * h;
     } else {
-      const float sg = 1.0f / (1.0f + expf(-s));
+      const float sg = __frcp_rn(1.0f + __expf(-s));
       h = s * sg;
       slope = sg * (1.0f + s * (1.0f - sg));
     }
@@ -109,45 +110,40 @@ struct Act {
 
 // value rows: h = act(pre), slope kept for the derivative rows; derivative rows: dh = slope dpre.  Both as hi / lo
 // operand rows of the next layer.
-__device__ __forceinline__ void hidden_epilogue(unsigned tmem_row, int col0, int t, Act act, float *slope /* [TB][KH + 1] */,
-                                                char *Hhi, char *Hlo)
+__device__ __forceinline__ void hidden_epilogue(unsigned tmem_row, int col0, int r, int half, Act act,
+                                                float *slope /* [TB][KH + 1] */, char *Hhi, char *Hlo)
 {
-  float pre[2][32];
-  tmem_ld32(tmem_row + col0, pre[0]);
-  tmem_ld32(tmem_row + col0 + 32, pre[1]);
+  float pre[32];
+  tmem_ld32(tmem_row + col0 + 32 * half, pre);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  if (t < TB) {
+  if (r < TB) {
 #pragma unroll
-    for (int half = 0; half < 2; half++)
+    for (int c4 = 0; c4 < 8; c4++) {
+      float hi[4], lo[4];
 #pragma unroll
-      for (int c4 = 0; c4 < 8; c4++) {
-        float hi[4], lo[4];
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          float h, sl;
-          act(pre[half][4 * c4 + q], h, sl);
-          slope[t * (KH + 1) + 32 * half + 4 * c4 + q] = sl;
-          split_tf32(h, hi[q], lo[q]);
-        }
-        const int off = tile_off(t, 32 * half + 4 * c4, KH);
-        *reinterpret_cast<float4 *>(Hhi + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<float4 *>(Hlo + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+      for (int q = 0; q < 4; q++) {
+        float h, sl;
+        act(pre[4 * c4 + q], h, sl);
+        slope[r * (KH + 1) + 32 * half + 4 * c4 + q] = sl;
+        split_tf32(h, hi[q], lo[q]);
       }
+      const int off = tile_off(r, 32 * half + 4 * c4, KH);
+      *reinterpret_cast<float4 *>(Hhi + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<float4 *>(Hlo + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
   }
   __syncthreads();
-  if (t >= TB) {
+  if (r >= TB) {
 #pragma unroll
-    for (int half = 0; half < 2; half++)
+    for (int c4 = 0; c4 < 8; c4++) {
+      float hi[4], lo[4];
 #pragma unroll
-      for (int c4 = 0; c4 < 8; c4++) {
-        float hi[4], lo[4];
-#pragma unroll
-        for (int q = 0; q < 4; q++)
-          split_tf32(slope[(t - TB) * (KH + 1) + 32 * half + 4 * c4 + q] * pre[half][4 * c4 + q], hi[q], lo[q]);
-        const int off = tile_off(t, 32 * half + 4 * c4, KH);
-        *reinterpret_cast<float4 *>(Hhi + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<float4 *>(Hlo + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-      }
+      for (int q = 0; q < 4; q++)
+        split_tf32(slope[(r - TB) * (KH + 1) + 32 * half + 4 * c4 + q] * pre[4 * c4 + q], hi[q], lo[q]);
+      const int off = tile_off(r, 32 * half + 4 * c4, KH);
+      *reinterpret_cast<float4 *>(Hhi + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+      *reinterpret_cast<float4 *>(Hlo + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncthreads();
@@ -168,13 +164,13 @@ __device__ __forceinline__ void issue_layer(unsigned tmem_d, unsigned a_hi, unsi
   }
 }
 
-__global__ void __launch_bounds__(TM, 1) radial_mlp_tc_kernel(RadialMlpTCDev m, const float *__restrict__ x, long long nb,
+__global__ void __launch_bounds__(NTH, 1) radial_mlp_tc_kernel(RadialMlpTCDev m, const float *__restrict__ x, long long nb,
                                                               float *__restrict__ R, float *__restrict__ dR, int *error)
 {
   extern __shared__ __align__(1024) char smem[];
   __shared__ unsigned long long s_mbar;
   __shared__ unsigned s_tmem;
-  const int t = threadIdx.x, warp = t >> 5;
+  const int t = threadIdx.x, warp = t >> 5, r = t & (TM - 1), half = t >> 7;    // row and column half of this thread
   const int NO = m.n_out;
   // shared memory: operand tiles of the activations, then the weights
   char *Ghi = smem, *Glo = Ghi + TM * KG * 4, *Hhi = Glo + TM * KG * 4, *Hlo = Hhi + TM * KH * 4;
@@ -184,7 +180,7 @@ __global__ void __launch_bounds__(TM, 1) radial_mlp_tc_kernel(RadialMlpTCDev m, 
   {    // the weight images are byte-for-byte the shared-memory layout
     const int4 *src = reinterpret_cast<const int4 *>(m.weights);
     int4 *dst = reinterpret_cast<int4 *>(W1hi);
-    for (int i = t; i < m.weight_bytes / 16; i += TM) dst[i] = src[i];
+    for (int i = t; i < m.weight_bytes / 16; i += NTH) dst[i] = src[i];
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
@@ -199,7 +195,7 @@ __global__ void __launch_bounds__(TM, 1) radial_mlp_tc_kernel(RadialMlpTCDev m, 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = s_tmem, mbar = smem_u32(&s_mbar);
-  const unsigned tmem_row = tmem + ((unsigned) (warp * 32) << 16);    // this warp's lanes
+  const unsigned tmem_row = tmem + ((unsigned) ((warp & 3) * 32) << 16);    // this warp's lanes
   const Act act{m.act};
   unsigned phase = 0;
   bool ok = true;
@@ -253,7 +249,7 @@ __global__ void __launch_bounds__(TM, 1) radial_mlp_tc_kernel(RadialMlpTCDev m, 
     phase ^= 1;
     if (!ok) break;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    hidden_epilogue(tmem_row, 0, t, act, slope, Hhi, Hlo);
+    hidden_epilogue(tmem_row, 0, r, half, act, slope, Hhi, Hlo);
     // layer 2
     if (t == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -264,7 +260,7 @@ __global__ void __launch_bounds__(TM, 1) radial_mlp_tc_kernel(RadialMlpTCDev m, 
     phase ^= 1;
     if (!ok) break;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    hidden_epilogue(tmem_row, KH, t, act, slope, Hhi, Hlo);
+    hidden_epilogue(tmem_row, KH, r, half, act, slope, Hhi, Hlo);
     // output layer
     if (t == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -275,16 +271,15 @@ __global__ void __launch_bounds__(TM, 1) radial_mlp_tc_kernel(RadialMlpTCDev m, 
     phase ^= 1;
     if (!ok) break;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    {    // rows 0-63 -> R, rows 64-127 -> dR of bond b0 + (t mod 64)
-      const long long b = b0 + (t & (TB - 1));
-      float *dst = (t < TB ? R : dR) + (size_t) b * NO;
-      for (int c0 = 0; c0 < NO; c0 += 32) {
+    {    // rows 0-63 -> R, rows 64-127 -> dR of bond b0 + (row mod 64); the two threads of a row alternate 32-column blocks
+      const long long b = b0 + (r & (TB - 1));
+      float *dst = (r < TB ? R : dR) + (size_t) b * NO;
+      for (int c0 = 32 * half; c0 < NO; c0 += 64) {
         float v[32];
         tmem_ld32(tmem_row + 2 * KH + c0, v);
         if (b < nb) {
 #pragma unroll
-          for (int q = 0; q < 32; q += 4)
-            if (c0 + q < NO) *reinterpret_cast<float4 *>(dst + c0 + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+          for (int q = 0; q < 32; q += 4) *reinterpret_cast<float4 *>(dst + c0 + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -381,7 +376,7 @@ void RadialMlpTC::run(const float *d_x, long long nb, float *d_R, float *d_dR)
   GB_CUDA(cudaFuncSetAttribute(radial_mlp_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
   const long long ntiles = (nb + TB - 1) / TB;
   const int grid = (int) std::min<long long>(ntiles, dev().sm_count);
-  GB_LAUNCH(radial_mlp_tc_kernel, grid, TM, smem, d_, d_x, nb, d_R, d_dR, error_.get());
+  GB_LAUNCH(radial_mlp_tc_kernel, grid, NTH, smem, d_, d_x, nb, d_R, d_dR, error_.get());
 #endif
 }
 

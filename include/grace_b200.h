@@ -82,7 +82,9 @@ int grace_profile_report(char *buf, size_t len);
 int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_out);
 
 /* ---- Model (kk_api.h:51-64): a loaded GRACE-1L / GRACE-2L kokkos.npz ---- */
-/* spline: intervals of the radial cubic Hermite tables (reference default 1024; >= 16) */
+/* spline: intervals of the radial cubic Hermite tables (reference default 1024; >= 16), or 0: no tables, the exact
+ * radial MLP per bond as in the reference's generic engine (tensor-core kernel; needs slots x outputs x 8 bytes of
+ * device memory per layer and an 8 -> 64 -> 64 -> n radial MLP) */
 int grace_model_load(const char *path, int spline, grace_model **out);   /* Model(path, spline) */
 int grace_model_layers(const grace_model *m);                            /* layers(): 1 or 2 */
 int grace_model_has_uq(const grace_model *m);                            /* has_uq(): 0 */

@@ -44,3 +44,32 @@ def test_radial_mlp_matches_fp64(backend, tmp_path_factory, cfg, layer, nb):
     assert np.isfinite(gR).all() and np.isfinite(gdR).all()
     assert np.abs(gR - eR).max() <= 2e-6 * max(1.0, np.abs(eR).max())
     assert np.abs(gdR - edR).max() <= 1e-5 * max(1.0, np.abs(edR).max())
+
+
+@pytest.mark.parametrize("cfg,lattice,a,reps,nsp,sigma", [("1l", "bcc", 3.2, (4, 4, 5), 4, 0.05),
+                                                           ("2l", "fcc", 3.6, (3, 3, 3), 3, 0.08)])
+def test_exact_radial_mode_matches_oracle(backend, tmp_path_factory, cfg, lattice, a, reps, nsp, sigma):
+    """spline = 0: energies, forces and virial with the radial MLP evaluated per bond by the tensor-core kernel, against
+    the numpy oracle with its exact MLP, and against the table mode of the same library (whose interpolation error is
+    the only difference)"""
+    from conftest import TOL_E, TOL_F, TOL_S
+    from grace_runtime_b200 import modelgen, structures
+    from oracle.grace_oracle import GraceOracle
+    els = modelgen._subset(11, nsp)
+    path = str(tmp_path_factory.mktemp("exact") / f"{cfg}.npz")
+    modelgen.write_config_model(path, cfg, els, seed=5)
+    types, pos, cell, pbc = structures.crystal(lattice, a, reps, n_species=nsp, sigma=sigma, seed=6)
+    n, vol = len(types), abs(np.linalg.det(cell))
+    exact = backend.System(backend.Model(path, spline=0), els, spline=0)
+    r = exact.compute(types, pos, cell, pbc, energies=True)
+    r2 = exact.compute(types, pos, cell, pbc, energies=True)
+    # (GRACE-2L adds dE/dmessage into neighbour rows with fp32 atomics: forces repeat to rounding, not to the bit)
+    assert r["energy"] == r2["energy"] and np.abs(r["forces"] - r2["forces"]).max() < 1e-6
+    o = GraceOracle(path).compute(els, types, pos, cell, pbc)
+    assert abs(r["energy"] - o["energy"]) / n < TOL_E * 0.1
+    assert np.abs(r["forces"] - o["forces"]).max() < TOL_F
+    assert np.abs(r["virial"] - o["virial"]).max() / vol < TOL_S
+    assert np.abs(r["energies"] - o["energies"]).max() < TOL_E
+    t = backend.System(backend.Model(path), els).compute(types, pos, cell, pbc)
+    assert abs(r["energy"] - t["energy"]) / n < TOL_E
+    assert np.abs(r["forces"] - t["forces"]).max() < TOL_F
