@@ -19,7 +19,7 @@ namespace {
 
 constexpr int EBB = 32;    // bonds staged per round
 
-template<int LMAX, int NIT, int NCH, int LPE>
+template<int LMAX, int NIT, int NCH, int LPE, bool EXACT>
 __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, SHTable sht,
                                                        const float *__restrict__ gQ, int NA, int a0,
                                                        float *__restrict__ fv, double *__restrict__ vir_atom, int add)
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
             const int n = ln + ch * LPE;
             if (n < C) {
               float R[NL], dR[NL];
-              if (L.Rex) {    // exact radial MLP, evaluated per slot beforehand
+              if (EXACT) {    // exact radial MLP, evaluated per slot beforehand
                 const size_t ro = (size_t) (base + b0 + e) * (NL * C) + n;
 #pragma unroll
                 for (int l = 0; l < NL; l++) {
@@ -181,7 +181,8 @@ template<int LMAX, int NIT, int NCH, int LPE>
 void launch_t(const BondsDev &b, const LayerDev &L, const float *gQ, int NA, int a0, int na, float *fv,
               double *vir_atom, int add)
 {
-  GB_LAUNCH((bond_bwd_kernel<LMAX, NIT, NCH, LPE>), na, 128, 0, b, L, sh_table_host(), gQ, NA, a0, fv, vir_atom, add);
+  if (L.Rex) GB_LAUNCH((bond_bwd_kernel<LMAX, NIT, NCH, LPE, true>), na, 128, 0, b, L, sh_table_host(), gQ, NA, a0, fv, vir_atom, add);
+  else GB_LAUNCH((bond_bwd_kernel<LMAX, NIT, NCH, LPE, false>), na, 128, 0, b, L, sh_table_host(), gQ, NA, a0, fv, vir_atom, add);
 }
 
 template<int LMAX>

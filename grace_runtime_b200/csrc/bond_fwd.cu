@@ -17,7 +17,7 @@ namespace {
 
 constexpr int EB = 64;    // bonds staged per round
 
-template<int LMAX, int NIT, int NCH, int LPE>
+template<int LMAX, int NIT, int NCH, int LPE, bool EXACT>
 __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, SHTable sht, float *__restrict__ Q,
                                                        int NA, int a0)
 {
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, S
           const int n = ln + ch * LPE;
           if (n < C) {
             float R[NL];
-            if (L.Rex) {    // exact radial MLP, evaluated per slot beforehand
+            if (EXACT) {    // exact radial MLP, evaluated per slot beforehand
               const float *rr = L.Rex + (size_t) (base + b0 + e) * (NL * C) + n;
 #pragma unroll
               for (int l = 0; l < NL; l++) R[l] = __ldg(rr + l * C);
@@ -133,7 +133,8 @@ template<int LMAX, int NIT, int NCH, int LPE>
 void launch_t(const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na)
 {
   const int tiles = (L.n_msg + 1 + NIT - 1) / NIT;
-  GB_LAUNCH((bond_fwd_kernel<LMAX, NIT, NCH, LPE>), dim3(na, tiles), 128, 0, b, L, sh_table_host(), Q, NA, a0);
+  if (L.Rex) GB_LAUNCH((bond_fwd_kernel<LMAX, NIT, NCH, LPE, true>), dim3(na, tiles), 128, 0, b, L, sh_table_host(), Q, NA, a0);
+  else GB_LAUNCH((bond_fwd_kernel<LMAX, NIT, NCH, LPE, false>), dim3(na, tiles), 128, 0, b, L, sh_table_host(), Q, NA, a0);
 }
 
 template<int LMAX> void launch_l(const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na)
