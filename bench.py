@@ -38,6 +38,8 @@ WORKLOADS = {
     "grace1l_2k_bcc_w": dict(cfg="1l", lattice="bcc", a=3.165, reps=(10, 10, 10), nsp=1, sigma=0.05, full=False),
     "grace2l_1m_fcc_alloy": dict(cfg="2l", lattice="fcc", a=3.6, reps=(40, 80, 80), nsp=3, sigma=0.08, full=True),
     "grace2l_128k_fcc_alloy": dict(cfg="2l", lattice="fcc", a=3.6, reps=(20, 40, 40), nsp=3, sigma=0.08, full=True),
+    # 4096 small periodic structures (16-256 atoms, triclinic, 0.06-0.09 atoms/A^3) through the Batch entry points
+    "grace2l_batch4096": dict(cfg="2l", batch=4096, unique=128, nmin=16, nmax=256, nsp=89, full=True),
 }
 DEFAULT = "grace1l_128k_bcc_alloy"
 
@@ -112,6 +114,117 @@ def algorithmic_bytes(kernel, model_cfg, n_atoms, n_bonds, slots):
     if kernel == "force_gather_kernel":   # bond force and reverse index in, force out
         return (12.0 + 4.0 + 12.0) * slots + 24.0 * n_atoms
     return None
+
+
+def run_batch(args, rank, world, local_rank):
+    """Batches of small structures: sharded by structure over the ranks (greedy by atom count), no data-path
+    collective; `value` = max-over-ranks time per step x n_gpus / total atoms."""
+    import torch
+    import torch.distributed as dist
+
+    from grace_runtime_b200 import backend as B
+
+    wl = WORKLOADS[args.workload]
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    B.initialize(local_rank)
+    tmp = tempfile.mkdtemp(prefix="grace_bench_")
+    species = list(modelgen.ELEMENTS)
+    path = modelgen.write_config_model(os.path.join(tmp, "batch.npz"), wl["cfg"], modelgen.ELEMENTS, seed=0)
+    # `unique` generated structures (rejection sampling is slow), repeated with rigid shifts to the full batch
+    un, ut, up, uc, upbc = structures.random_batch(wl["unique"], wl["nmin"], wl["nmax"], wl["nsp"], seed=1)
+    rng = np.random.default_rng(2)
+    start = np.concatenate([[0], np.cumsum(un)])
+    natoms, T, P, Cc = [], [], [], []
+    for s in range(wl["batch"]):
+        u = s % wl["unique"]
+        sl = slice(start[u], start[u + 1])
+        natoms.append(un[u]); T.append(ut[sl]); Cc.append(uc[u])
+        P.append(up[sl] + rng.random(3) @ uc[u])
+    natoms = np.array(natoms, dtype=np.int32)
+    n_total = int(natoms.sum())
+    # this rank's structures: greedy by atom count
+    order = np.argsort(-natoms, kind="stable")
+    load = np.zeros(world, dtype=np.int64)
+    owner = np.zeros(len(natoms), dtype=np.int64)
+    for s in order:
+        r = int(np.argmin(load)); owner[s] = r; load[r] += natoms[s]
+    mine = np.nonzero(owner == rank)[0]
+    my_n = natoms[mine]
+    my_t = np.concatenate([T[s] for s in mine]).astype(np.int32)
+    my_p = np.ascontiguousarray(np.concatenate([P[s] for s in mine]))
+    my_c = np.stack([Cc[s] for s in mine])
+    my_pbc = np.ones((len(mine), 3), dtype=np.uint8)
+    model = B.Model(path)
+    batch = B.Batch(model, species, chunksize=args.chunk)
+    batch.keep_buffers = True
+    d_t = torch.from_numpy(my_t).to(dev); d_p = torch.from_numpy(my_p).to(dev)
+    d_e = torch.zeros(len(mine), dtype=torch.float64, device=dev)
+    d_v = torch.zeros((len(mine), 6), dtype=torch.float64, device=dev)
+    d_f = torch.zeros((len(my_t), 3), dtype=torch.float64, device=dev)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(); torch.cuda.synchronize()
+
+    def step_device():
+        batch.compute_device(my_n, d_t.data_ptr(), d_p.data_ptr(), my_c, my_pbc, d_e.data_ptr(), d_f.data_ptr(), d_v.data_ptr())
+
+    def step_host():
+        return batch.compute(my_n, my_t, my_p, my_c, my_pbc)
+
+    for _ in range(max(args.warmup, 1)):
+        step_device()
+    barrier()
+    sampler = ClockSampler(local_rank); sampler.start()
+    l0 = B.kernel_launches()
+    B.profile_enable(True)
+    ev0.record()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_device()
+    ev1.record(); ev1.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    dev_ms = ev0.elapsed_time(ev1) / args.steps
+    prof = B.profile_report(); B.profile_enable(False)
+    launches = B.kernel_launches() - l0
+    clocks = sampler.stop()
+    for _ in range(max(args.warmup, 3)):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_host()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    red = torch.tensor([dev_ms, wall_ms, e2e_ms], dtype=torch.float64, device=dev)
+    cnt = torch.tensor([float(launches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(red, op=dist.ReduceOp.MAX); dist.all_reduce(cnt, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        ms = float(red[0])
+        tot = sum(v[1] for v in prof.values()) or 1.0
+        kern = sorted(prof.items(), key=lambda kv: -kv[1][1])
+        out = {"metric": METRIC, "value": ms * 1e3 * world / n_total, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+               "dtype": "f32", "data": "synthetic",
+               "config": {"workload": args.workload, "structures": int(wl["batch"]), "atoms": n_total, "model": "GRACE-2L",
+                          "elements_in_model": 89, "atoms_per_structure": [int(wl["nmin"]), int(wl["nmax"])],
+                          "unique_structures": int(wl["unique"]), "parallelism": f"structures over {world} rank(s)",
+                          "passes": batch.passes, "neighbor_list": "built every step (Batch semantics)",
+                          "value_definition": "max-over-ranks time per step x n_gpus / atoms"},
+               "structures_per_s": wl["batch"] / (ms * 1e-3),
+               "e2e": {"value": float(red[2]) * 1e3 * world / n_total, "unit": UNIT, "ms_per_step": float(red[2]),
+                       "h2d_bytes_per_step": int(28 * n_total + 75 * wl["batch"]), "d2h_bytes_per_step": int(24 * n_total + 56 * wl["batch"])},
+               "gpu_launches": int(cnt[0]), "clocks": clocks, "roofline": None,
+               "kernels": {k: {"launches": v[0], "ms_per_step": v[1] / args.steps, "share": v[1] / tot} for k, v in kern[:8]},
+               "wall_ms_per_step": float(red[1])}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_ours(args, rank, world, local_rank):
@@ -346,6 +459,9 @@ def run_reference(args, rank, world):
         return
     tmp = tempfile.mkdtemp(prefix="grace_bench_ref_")
     wl = WORKLOADS[args.workload]
+    if "batch" in wl:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm times single structures; not wired for the batch workload"}))
+        return
     reps = wl["reps"]
     if np.prod(reps) * (2 if wl["lattice"] == "bcc" else 4) > 32000:
         reps = (20, 20, 40) if wl["lattice"] == "bcc" else (16, 16, 32)
@@ -392,6 +508,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif "batch" in WORKLOADS[args.workload]:
+        run_batch(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <map>
 
 namespace gb {
@@ -453,7 +454,9 @@ void build_units(MVOp &o)
   if (o.elem) return;
   for (const MVItem &it : o.items)
     if (it.n_in > 64) return;
-  constexpr int RMAX = 3;    // input rows per unit: enough units per slot to occupy the warps of a CTA
+  // input rows per unit: enough units per slot to occupy the warps of a CTA (GRACE_B200_UNIT_ROWS overrides, for tuning)
+  int RMAX = 4;
+  if (const char *env = getenv("GRACE_B200_UNIT_ROWS")) RMAX = std::max(1, atoi(env));
   int nslots = 0;
   for (size_t r = 0; r + 1 < o.item_off.size(); r++) nslots = std::max(nslots, o.item_off[r + 1] - o.item_off[r]);
   o.slot_off.push_back(0);
