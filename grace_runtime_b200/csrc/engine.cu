@@ -389,6 +389,9 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
     const int ta = atoi(env);
     if (ta >= 1 && ta <= 8 && ta != 7 && tb + at * 4 * ta * fused_groups() <= limit) E.fused_TA = ta;
   }
+  if (getenv("GRACE_B200_PRINT_PLAN"))
+    fprintf(stderr, "fused layer: %lld floats per atom, tables %lld bytes, tile atoms %d x %d groups\n", at, tb, E.fused_TA,
+            fused_groups());
   GB_CUDA(cudaStreamSynchronize(dev().stream));
 }
 
