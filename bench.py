@@ -100,6 +100,11 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per atom of one launch, from the ncu captures summarised in profiles/
+NCU_DRAM_BYTES_PER_ATOM = {("chain_fused_kernel", "1l"): 781.5e6 / 128000, ("bond_fwd_kernel", "1l"): 488.2e6 / 128000,
+                           ("bond_bwd_kernel", "1l"): 696.4e6 / 128000}
+
+
 def algorithmic_bytes(kernel, model_cfg, n_atoms, n_bonds, slots):
     """Bytes one pass of a kernel over the whole structure must move at least (fp32 network, 16-byte bond records)."""
     c = modelgen.CONFIGS[model_cfg]
@@ -383,7 +388,11 @@ def run_ours(args, rank, world, local_rank):
         peak_tf = 148 * 128 * 2 * sm_mhz * 1e6 / 1e12
         ach = flop / (per_launch_ms * 1e-3) / 1e12
         roof = {"bound": "fp32", "kernel": top, "peak": peak_tf, "peak_source": "148 SMs x 128 FMA lanes x 2 flop x sampled SM clock (no measured SIMT peak in MEASURED_PEAKS.json)",
-                "unit": "TFLOP/s", "achieved": ach, "frac": ach / peak_tf, "traffic": None,
+                "unit": "TFLOP/s", "achieved": ach, "frac": ach / peak_tf,
+                # DRAM bytes per launch from the ncu capture of this kernel on this workload (profiles/), scaled by the
+                # atoms of a launch: traffic grows in proportion to the atoms
+                "traffic": (NCU_DRAM_BYTES_PER_ATOM.get((top, wl["cfg"]), 0.0) * n_own * args.steps / top_n) or None,
+                "algorithmic_bytes_per_launch": 2.0 * 4.0 * (modelgen.CONFIGS[wl["cfg"]]["lmax"] + 1) ** 2 * modelgen.CONFIGS[wl["cfg"]]["c1"] * n_own * args.steps / top_n,
                 "flop_per_launch": flop, "flop_per_atom": model.dense_flops, "avg_launch_ms": per_launch_ms,
                 "note": "dense-network kernel: shared-memory resident fp32 SIMT work, neither HBM- nor tensor-bound; "
                         "its DRAM traffic (ncu) is in profiles/"}
@@ -393,7 +402,8 @@ def run_ours(args, rank, world, local_rank):
         if ab is not None:
             per_launch_bytes = ab * args.steps / top_n
             roof.update(achieved=per_launch_bytes / (per_launch_ms * 1e-3) / 1e9,
-                        algorithmic_bytes_per_launch=per_launch_bytes, avg_launch_ms=per_launch_ms)
+                        algorithmic_bytes_per_launch=per_launch_bytes, avg_launch_ms=per_launch_ms,
+                        traffic=(NCU_DRAM_BYTES_PER_ATOM.get((top, wl["cfg"]), 0.0) * n_own * args.steps / top_n) or None)
             roof["frac"] = roof["achieved"] / hbm_peak
         else:
             roof.update(achieved=None, frac=None)
