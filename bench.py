@@ -182,10 +182,10 @@ def run_batch(args, rank, world, local_rank):
     def step_host():
         return batch.compute(my_n, my_t, my_p, my_c, my_pbc)
 
+    sampler = ClockSampler(local_rank); sampler.start()
     for _ in range(max(args.warmup, 1)):
         step_device()
     barrier()
-    sampler = ClockSampler(local_rank); sampler.start()
     l0 = B.kernel_launches()
     B.profile_enable(True)
     ev0.record()
@@ -280,11 +280,13 @@ def run_ours(args, rank, world, local_rank):
             t += ev0.elapsed_time(ev1)
         return t, ms
 
+    # the clock sampler starts before the warm-up: nvidia-smi takes ~100 ms to come up and must not do that inside a
+    # timed region of a few milliseconds per step; its samples cover warm-up and timed steps (the same work)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(args.warmup, 1)):
         step_device()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     l0 = B.kernel_launches()
     B.profile_enable(True)
     t0 = time.perf_counter()
