@@ -369,6 +369,39 @@ __device__ __forceinline__ void prod_tile(const ProdDev &op, float *sm, const in
   }
 }
 
+// The forward tensors a later reverse pass reads (L.save: shared-memory offset, functions, channels and offset in the
+// per-atom record of each) to or from global memory, [position of the atom in the evaluation][save_floats]; a tensor
+// is [f][TA][C] in shared memory and [f][C] in the record.
+template<int TA, bool SAVE>
+__device__ __forceinline__ void move_saved(const FusedLayerDev &L, const FusedIO &io, float *sm, int al0, int nta, int tid)
+{
+  for (int z = 0; z < L.nsave; z++) {
+    const int4 sv = L.save[z];
+    float *t = sm + (size_t) sv.x * TA;
+    const int nf = sv.y, C = sv.z;
+    float *g0 = io.saved + (size_t) (io.a0 + al0) * L.save_floats + sv.w;
+    if ((C & 3) == 0 && (L.save_floats & 3) == 0 && (sv.w & 3) == 0) {
+      const int C4 = C >> 2, total = nf * nta * C4;
+      for (int idx = tid; idx < total; idx += NT) {
+        const int c = idx % C4, fa = idx / C4, a = fa % nta, f = fa / nta;
+        float4 *g = reinterpret_cast<float4 *>(g0 + (size_t) a * L.save_floats + f * C) + c;
+        float4 *p = reinterpret_cast<float4 *>(t + (size_t) (f * TA + a) * C) + c;
+        if (SAVE) *g = *p;
+        else *p = *g;
+      }
+    } else {
+      const int total = nf * nta * C;
+      for (int idx = tid; idx < total; idx += NT) {
+        const int c = idx % C, fa = idx / C, a = fa % nta, f = fa / nta;
+        float *g = g0 + (size_t) a * L.save_floats + f * C + c;
+        float *p = t + (size_t) (f * TA + a) * C + c;
+        if (SAVE) *g = *p;
+        else *p = *g;
+      }
+    }
+  }
+}
+
 template<int TA>
 __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, FusedIO io)
 {
@@ -422,32 +455,38 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
       s_at[tid] = i;
       s_mu[tid] = io.mu[i];
     }
-    {    // bond sums of the tile: global [f][NA][C] -> shared [f][TA][C]; atoms past the end are zero
-      const int C = io.CQ;
-      float *q = sm + (size_t) s_soff[io.tQ] * TA;
-      if ((C & 3) == 0) {
-        const int C4 = C >> 2, total = io.nQ * TA * C4;
-        for (int idx = tid; idx < total; idx += NT) {
-          const int c = idx % C4, a = (idx / C4) % TA, f = idx / (C4 * TA);
-          reinterpret_cast<float4 *>(q)[idx] =
-              a < nta ? __ldg(reinterpret_cast<const float4 *>(io.Q + ((size_t) f * io.NA + al0 + a) * C) + c)
-                      : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-      } else {
-        const int total = io.nQ * TA * C;
-        for (int idx = tid; idx < total; idx += NT) {
-          const int c = idx % C, a = (idx / C) % TA, f = idx / (C * TA);
-          q[idx] = a < nta ? __ldg(io.Q + ((size_t) f * io.NA + al0 + a) * C + c) : 0.0f;
+    if (io.mode & FUSED_RESTORE) {    // forward tensors kept by an earlier FUSED_SAVE launch instead of a second evaluation
+      move_saved<TA, false>(L, io, sm, al0, nta, tid);
+      group_sync();
+    } else {
+      {    // bond sums of the tile: global [f][NA][C] -> shared [f][TA][C]; atoms past the end are zero
+        const int C = io.CQ;
+        float *q = sm + (size_t) s_soff[io.tQ] * TA;
+        if ((C & 3) == 0) {
+          const int C4 = C >> 2, total = io.nQ * TA * C4;
+          for (int idx = tid; idx < total; idx += NT) {
+            const int c = idx % C4, a = (idx / C4) % TA, f = idx / (C4 * TA);
+            reinterpret_cast<float4 *>(q)[idx] =
+                a < nta ? __ldg(reinterpret_cast<const float4 *>(io.Q + ((size_t) f * io.NA + al0 + a) * C) + c)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        } else {
+          const int total = io.nQ * TA * C;
+          for (int idx = tid; idx < total; idx += NT) {
+            const int c = idx % C, a = (idx / C) % TA, f = idx / (C * TA);
+            q[idx] = a < nta ? __ldg(io.Q + ((size_t) f * io.NA + al0 + a) * C + c) : 0.0f;
+          }
         }
       }
-    }
-    group_sync();
-    for (int o = 0; o < L.nfwd; o++) {
-      const int2 op = s_ops[o];
-      if (op.x == 0) mv_any<TA>(s_mv[op.y], sm, s_soff, s_tch, s_mu);
-      else prod_tile<TA>(s_prod[op.y], sm, s_soff, s_tch);
       group_sync();
+      for (int o = 0; o < L.nfwd; o++) {
+        const int2 op = s_ops[o];
+        if (op.x == 0) mv_any<TA>(s_mv[op.y], sm, s_soff, s_tch, s_mu);
+        else prod_tile<TA>(s_prod[op.y], sm, s_soff, s_tch);
+        group_sync();
+      }
     }
+    if (io.mode & FUSED_SAVE) move_saved<TA, true>(L, io, sm, al0, nta, tid);
     if (io.mode & FUSED_STORE_MSG) {    // GRACE-2L layer 1: message rows [n][nI][CR] and rho rows [n][nrho]
       const int CR = io.CR, nI = io.nI, total = nta * nI * CR;
       const float *I = sm + (size_t) s_soff[io.t_I] * TA;

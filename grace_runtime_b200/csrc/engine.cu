@@ -189,6 +189,8 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   for (size_t L = 0; L < P.e_nin.size(); L++)
     if (P.e_nin[L] > 128 || P.e_nout[L] > 128) throw Unsupported("energy MLP widths above 128 are not supported");
   if (P.nrho > 128) throw Unsupported("rho_n_out above 128 is not supported");
+  l1_saved_.set_label("work:layer1_tensors");
+  if (getenv("GRACE_B200_RECOMPUTE_L1")) keep_l1_ = false;
   rcsq_.set_label("engine:cutoffs"); eW_.set_label("engine:energy_mlp"); shift_.set_label("engine:shift");
   lnI_.set_label("engine:norm_scale"); ln0_.set_label("engine:norm_scale"); rcf_.set_label("engine:cutoffs");
   arena_.set_label("work:chunk_tensors"); fv_.set_label("work:bond_forces"); I_rows_.set_label("work:messages");
@@ -265,7 +267,7 @@ void Engine::release_work()
 {
   arena_.release(); fv_.release(); I_rows_.release(); gI_rows_.release(); rho_rows_.release();
   e_atom_.release(); vir_atom_.release(); grho_rows_.release(); sum_scratch_.release();
-  xs_.release(); R1_.release(); dR1_.release(); R2_.release(); dR2_.release();
+  xs_.release(); R1_.release(); dR1_.release(); R2_.release(); dR2_.release(); l1_saved_.release();
   arena_NA_ = 0;
 }
 
@@ -349,6 +351,28 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
   E.f_prod.upload(E.prod);
   E.f_ops.upload(ops);
   E.f_zero.upload(zero);
+  // forward tensors some reverse operation reads (operands of product adjoints, inputs of reduces over them)
+  std::vector<int4> save;
+  long long save_floats = 0;
+  {
+    std::vector<char> read(nt, 0);
+    for (const Op &o : P.bwd.ops) {
+      if (o.kind == Op::MV) {
+        for (const MVItem &it : P.mv[o.index].items) read[it.src] = 1;
+      } else {
+        const ProdOp &q = P.prod[o.index];
+        read[q.srcA] = 1;
+        if (q.srcB >= 0) read[q.srcB] = 1;
+      }
+    }
+    for (size_t t = 0; t < nt; t++)
+      if (read[t] && !P.tensors[t].grad) {
+        save.push_back(make_int4(soff[t], P.tensors[t].nfuncs, P.tensors[t].channels, (int) save_floats));
+        save_floats += size_of(t);
+      }
+  }
+  E.f_save.set_label("engine:tables");
+  E.f_save.upload(save);
   E.f_soff.upload(soff);
   E.f_tch.upload(tch);
   FusedLayerDev &F = E.fused;
@@ -361,6 +385,9 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
   F.tch = E.f_tch.get();
   F.zero = E.f_zero.get();
   F.nzero = (int) zero.size();
+  F.save = E.f_save.get();
+  F.nsave = (int) save.size();
+  F.save_floats = (int) save_floats;
   F.per_atom = (int) at;
   E.q_floats = (long long) P.tensors[P.tQ].nfuncs * P.tensors[P.tQ].channels;
   F.nmv = (int) E.mv.size();
@@ -395,7 +422,7 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
   GB_CUDA(cudaStreamSynchronize(dev().stream));
 }
 
-void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist)
+void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist, float *saved)
 {
   const ModelPlan &P = plan_;
   const LayerPlan &LP = *E.plan;
@@ -426,6 +453,7 @@ void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const i
   io.a0 = a0;
   io.na = na;
   io.ilist = ilist;
+  io.saved = saved;
   const int TA = E.fused_TA;
   const int ntiles = (na + TA - 1) / TA, nctas = (ntiles + fused_groups() - 1) / fused_groups();
   launch_chain_fused(TA, E.fused, io, std::min(nctas, dev().sm_count));
@@ -481,10 +509,20 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   Lb.gmsg = gI_rows_.get();
   const float *gQ1 = arena_.get() + (size_t) L1_.q_floats * NA, *gQ2 = arena_.get() + (size_t) L2_.q_floats * NA;
   if (tm) tm->begin(StageTimer::FWD);
+  // the layer-1 tensors its reverse pass reads are kept in global memory between the passes when they fit (else layer
+  // 1 is evaluated a second time)
+  float *saved = nullptr;
+  if (!energy_only && keep_l1_ && L1_.fused.save_floats > 0) {
+    try {
+      saved = l1_saved_.ensure((size_t) L1_.fused.save_floats * (size_t) n1);
+    } catch (const OutOfMemory &) {
+      keep_l1_ = false;
+    }
+  }
   for (int64_t a0 = 0; a0 < n1; a0 += NA) {    // layer 1 forward: messages and rho of the atoms layer 2 reads
     const int na = (int) std::min<int64_t>(NA, n1 - a0);
     launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
-    run_fused(L1_, FUSED_STORE_MSG, NA, (int) a0, na, mu, R.list1);
+    run_fused(L1_, FUSED_STORE_MSG | (saved ? FUSED_SAVE : 0), NA, (int) a0, na, mu, R.list1, saved);
   }
   for (int64_t a0 = 0; a0 < n0; a0 += NA) {    // layer 2, energy, layer-2 reverse
     const int na = (int) std::min<int64_t>(NA, n0 - a0);
@@ -497,8 +535,8 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   if (tm) tm->begin(StageTimer::BWD);
   for (int64_t a0 = 0; a0 < n1; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
     const int na = (int) std::min<int64_t>(NA, n1 - a0);
-    launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
-    run_fused(L1_, FUSED_LOAD_SEED | FUSED_BWD, NA, (int) a0, na, mu, R.list1);
+    if (!saved) launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
+    run_fused(L1_, FUSED_LOAD_SEED | FUSED_BWD | (saved ? FUSED_RESTORE : 0), NA, (int) a0, na, mu, R.list1, saved);
     launch_bond_bwd(P.lmax, b1, La, gQ1, NA, (int) a0, na, fv, vir_atom_.get(), 1);
   }
   if (tm) tm->end(StageTimer::BWD);

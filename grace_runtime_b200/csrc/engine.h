@@ -34,6 +34,7 @@ struct LayerEngine {
   DBuf<MVDev> f_mv;
   DBuf<ProdDev> f_prod;
   DBuf<int2> f_ops, f_zero;
+  DBuf<int4> f_save;
   DBuf<int> f_soff, f_tch;
   FusedLayerDev fused{};
   int fused_TA = 0;           // atoms per tile that fit the shared memory (0: the layer does not fit)
@@ -96,9 +97,12 @@ class Engine {
   bool exact_ = false;
   RadialMlpTC rad1_, rad2_;
   DBuf<float> xs_, R1_, dR1_, R2_, dR2_;
+  // GRACE-2L: forward tensors of layer 1 its reverse pass reads, kept between the passes instead of recomputed
+  DBuf<float> l1_saved_;
+  bool keep_l1_ = true;
   void evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
   void evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
-  void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist);
+  void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist, float *saved = nullptr);
   void bind_arena(LayerEngine &E, int NA);
   void run(LayerEngine &E, const Program &prog, const int *mu, int NA);
   LayerDev layer_dev(const LayerEngine &E) const;

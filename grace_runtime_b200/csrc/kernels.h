@@ -96,7 +96,10 @@ void launch_readout_2l(const ReadoutDev &r, const float *rho_rows, const float *
                        const int *mu, double *e_atom, int NA, int na, int a0, int want_grad);
 
 // ---- the dense network of a layer as one kernel on shared-memory tensors (chain_fused.cu) ----
-enum { FUSED_STORE_MSG = 1, FUSED_READOUT_1L = 2, FUSED_READOUT_2L = 4, FUSED_BWD = 8, FUSED_LOAD_SEED = 16 };
+// FUSED_SAVE: after the forward operations, the tensors the reverse operations read go to global memory;
+// FUSED_RESTORE: they come back from there instead of the bond sums and the forward operations being run again
+enum { FUSED_STORE_MSG = 1, FUSED_READOUT_1L = 2, FUSED_READOUT_2L = 4, FUSED_BWD = 8, FUSED_LOAD_SEED = 16, FUSED_SAVE = 32,
+       FUSED_RESTORE = 64 };
 
 struct FusedLayerDev {
   const MVDev *mv;
@@ -116,6 +119,10 @@ struct FusedLayerDev {
   const ProdTerm *terms;
   int n_itab, n_items, n_terms;
   int stage_terms;      // the product terms fit the shared memory next to the tile
+  // forward tensors that reverse operations read: (shared-memory offset in floats per atom, functions, channels,
+  // offset in the per-atom record), and the floats of a record
+  const int4 *save;
+  int nsave, save_floats;
   int tab_floats;       // shared-memory floats in front of the tile's tensors that hold the tables
 };
 
@@ -134,6 +141,7 @@ struct FusedIO {
   double *e_atom;
   int a0, na;                       // first atom of the chunk in list order (or position in ilist), atoms of the chunk
   const int *ilist;                 // atoms to evaluate (null: all)
+  float *saved;                     // [atoms of the evaluation][save_floats]: FUSED_SAVE / FUSED_RESTORE, by position a0 + a
 };
 
 // TA: atoms per tile (1, 2, 3, 4, 6, 8); grid CTAs loop over the tiles
