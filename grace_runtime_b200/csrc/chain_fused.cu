@@ -446,6 +446,16 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
   for (int q = btid; q < L.n_items; q += NTB) s_items[q] = L.items[q];
   if (L.stage_terms)
     for (int q = btid; q < L.n_terms; q += NTB) s_terms[q] = L.terms[q];
+  ReadoutDev ro = io.ro;
+  if (L.stage_ro > 0) {    // the energy MLP and its transpose, read row by row by the warp readout
+    double *s_ro = reinterpret_cast<double *>(reinterpret_cast<char *>(smem4) + L.ro_offset);
+    for (int q = btid; q < L.stage_ro; q += NTB) {
+      s_ro[q] = io.ro.W[q];
+      s_ro[L.stage_ro + q] = io.ro.WT[q];
+    }
+    ro.W = s_ro;
+    ro.WT = s_ro + L.stage_ro;
+  }
   __syncthreads();
   for (int tile = blockIdx.x * NG + grp; tile < ntiles; tile += gridDim.x * NG) {
     const int al0 = tile * TA;                      // first atom of the tile, chunk-local
@@ -512,7 +522,7 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
         const float *rho = sm + (size_t) s_soff[io.t_rho] * TA + w * io.nrho;
         float *grho = sm + (size_t) s_soff[io.t_grho] * TA + w * io.nrho;
         const size_t i = s_at[w];
-        const double e = readout_1l_warp(io.ro, rho, s_mu[w], grho, bwd, io.ro.owned(i));
+        const double e = readout_1l_warp(ro, rho, s_mu[w], grho, bwd, ro.owned(i));
         if (ln == 0) io.e_atom[i] = e;
       } else if (w < TA && bwd) {
         float *grho = sm + (size_t) s_soff[io.t_grho] * TA + w * io.nrho;
@@ -525,8 +535,8 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
         const size_t i = s_at[w];
         const float *I2 = sm + (size_t) s_soff[io.t_I2] * TA + w * io.nrho;
         float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + w * io.nrho;
-        const double e = readout_2l_warp(io.ro, io.rho_rows + i * io.nrho, I2, s_mu[w], io.grho_rows + i * io.nrho, gI2,
-                                         bwd, io.ro.owned(i));
+        const double e = readout_2l_warp(ro, io.rho_rows + i * io.nrho, I2, s_mu[w], io.grho_rows + i * io.nrho, gI2,
+                                         bwd, ro.owned(i));
         if (ln == 0) io.e_atom[i] = e;
       } else if (w < TA && bwd) {
         float *gI2 = sm + (size_t) s_soff[io.t_gI2] * TA + w * io.nrho;

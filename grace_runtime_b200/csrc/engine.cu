@@ -407,7 +407,24 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
     return (b + 15) / 16 * 16;
   };
   F.stage_terms = tab_bytes(true) + at * 4 * fused_groups() <= limit;
-  const long long tb = tab_bytes(F.stage_terms);
+  long long tb = tab_bytes(F.stage_terms);
+  // a small energy MLP goes to shared memory too (its rows are read one after the other by the warp readout: from
+  // global memory every row is an L2 round trip), unless that would cost an atom of the tile
+  F.stage_ro = 0;
+  F.ro_offset = 0;
+  auto tile_for = [&](long long tbytes) {
+    for (int ta : {8, 6, 5, 4, 3, 2, 1})
+      if (tbytes + at * 4 * ta * fused_groups() <= limit) return ta;
+    return 0;
+  };
+  {
+    const long long nd = (long long) plan_.eW.size(), extra = (2 * nd * 8 + 15) / 16 * 16;
+    if (nd > 0 && extra <= 16384 && tile_for(tb) > 0 && tile_for(tb + extra) == tile_for(tb)) {
+      F.stage_ro = (int) nd;
+      F.ro_offset = (int) tb;
+      tb += extra;
+    }
+  }
   F.tab_floats = (int) (tb / 4);
   E.fused_TA = 0;
   for (int ta : {8, 6, 5, 4, 3, 2, 1})

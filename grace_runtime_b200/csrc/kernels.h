@@ -124,6 +124,8 @@ struct FusedLayerDev {
   const int4 *save;
   int nsave, save_floats;
   int tab_floats;       // shared-memory floats in front of the tile's tensors that hold the tables
+  int stage_ro;         // doubles of the energy MLP (layers concatenated) staged behind the tables, twice (W, WT); 0: none
+  int ro_offset;        // byte offset of that copy in the dynamic shared memory
 };
 
 struct FusedIO {
