@@ -16,7 +16,11 @@ namespace {
 #define GB_FUSED_THREADS 512
 #endif
 constexpr int NTB = GB_FUSED_THREADS;    // threads of the CTA
-constexpr int NG = 2;                     // independent groups of warps, each on its own atom tile
+#ifndef GB_FUSED_GROUPS
+#define GB_FUSED_GROUPS 2
+#endif
+constexpr int NG = GB_FUSED_GROUPS;       // independent groups of warps, each on its own atom tile (this file is
+                                          // compiled once more with one group of all warps: chain_fused_g1.cu)
 constexpr int NT = NTB / NG;              // threads of a group
 
 // barrier of the calling thread's group (named barrier 1 + group)
@@ -597,12 +601,14 @@ template<int TA> void launch_ta(const FusedLayerDev &L, const FusedIO &io, int g
 
 }    // namespace
 
-int fused_groups() { return NG; }
-
+#if GB_FUSED_GROUPS == 2
 void launch_chain_fused(int TA, const FusedLayerDev &L, const FusedIO &io, int grid)
+#else
+void launch_chain_fused_g1(int TA, const FusedLayerDev &L, const FusedIO &io, int grid)
+#endif
 {
   if (io.na == 0) return;
-  const size_t smem = ((size_t) L.tab_floats + (size_t) L.per_atom * TA * fused_groups()) * sizeof(float);
+  const size_t smem = ((size_t) L.tab_floats + (size_t) L.per_atom * TA * NG) * sizeof(float);
   switch (TA) {
     case 1: launch_ta<1>(L, io, grid, smem); break;
     case 2: launch_ta<2>(L, io, grid, smem); break;

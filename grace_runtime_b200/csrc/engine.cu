@@ -406,36 +406,46 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
                   sizeof(int) * (2 * nt + E.n_itab) + sizeof(MVItem) * E.n_items + (with_terms ? sizeof(ProdTerm) * E.n_terms : 0);
     return (b + 15) / 16 * 16;
   };
-  F.stage_terms = tab_bytes(true) + at * 4 * fused_groups() <= limit;
+  // two warp groups per CTA (each on its own tile) unless they would get one atom each while a single group of all
+  // warps gets a tile of two or more: then the atoms of the tile share every weight fetched (GRACE_B200_GROUPS
+  // overrides)
+  auto tile_for = [&](long long tbytes, int ng) {
+    for (int ta : {8, 6, 5, 4, 3, 2, 1})
+      if (tbytes + at * 4 * ta * ng <= limit) return ta;
+    return 0;
+  };
+  int ng = 2;
+  {
+    const long long t2 = tab_bytes(tab_bytes(true) + at * 4 * 2 <= limit), t1 = tab_bytes(tab_bytes(true) + at * 4 <= limit);
+    if (tile_for(t2, 2) <= 1 && tile_for(t1, 1) >= 2) ng = 1;
+    if (const char *env = getenv("GRACE_B200_GROUPS")) {
+      const int g = atoi(env);
+      if (g == 1 || g == 2) ng = g;
+    }
+  }
+  E.fused_NG = ng;
+  F.stage_terms = tab_bytes(true) + at * 4 * ng <= limit;
   long long tb = tab_bytes(F.stage_terms);
   // a small energy MLP goes to shared memory too (its rows are read one after the other by the warp readout: from
   // global memory every row is an L2 round trip), unless that would cost an atom of the tile
   F.stage_ro = 0;
   F.ro_offset = 0;
-  auto tile_for = [&](long long tbytes) {
-    for (int ta : {8, 6, 5, 4, 3, 2, 1})
-      if (tbytes + at * 4 * ta * fused_groups() <= limit) return ta;
-    return 0;
-  };
   {
     const long long nd = (long long) plan_.eW.size(), extra = (2 * nd * 8 + 15) / 16 * 16;
-    if (nd > 0 && extra <= 16384 && tile_for(tb) > 0 && tile_for(tb + extra) == tile_for(tb)) {
+    if (nd > 0 && extra <= 16384 && tile_for(tb, ng) > 0 && tile_for(tb + extra, ng) == tile_for(tb, ng)) {
       F.stage_ro = (int) nd;
       F.ro_offset = (int) tb;
       tb += extra;
     }
   }
   F.tab_floats = (int) (tb / 4);
-  E.fused_TA = 0;
-  for (int ta : {8, 6, 5, 4, 3, 2, 1})
-    if (tb + at * 4 * ta * fused_groups() <= limit) { E.fused_TA = ta; break; }
+  E.fused_TA = tile_for(tb, ng);
   if (const char *env = getenv("GRACE_B200_TILE_ATOMS")) {
     const int ta = atoi(env);
-    if (ta >= 1 && ta <= 8 && ta != 7 && tb + at * 4 * ta * fused_groups() <= limit) E.fused_TA = ta;
+    if (ta >= 1 && ta <= 8 && ta != 7 && tb + at * 4 * ta * ng <= limit) E.fused_TA = ta;
   }
   if (getenv("GRACE_B200_PRINT_PLAN"))
-    fprintf(stderr, "fused layer: %lld floats per atom, tables %lld bytes, tile atoms %d x %d groups\n", at, tb, E.fused_TA,
-            fused_groups());
+    fprintf(stderr, "fused layer: %lld floats per atom, tables %lld bytes, tile atoms %d x %d groups\n", at, tb, E.fused_TA, ng);
   GB_CUDA(cudaStreamSynchronize(dev().stream));
 }
 
@@ -472,8 +482,9 @@ void Engine::run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const i
   io.ilist = ilist;
   io.saved = saved;
   const int TA = E.fused_TA;
-  const int ntiles = (na + TA - 1) / TA, nctas = (ntiles + fused_groups() - 1) / fused_groups();
-  launch_chain_fused(TA, E.fused, io, std::min(nctas, dev().sm_count));
+  const int ntiles = (na + TA - 1) / TA, nctas = (ntiles + E.fused_NG - 1) / E.fused_NG;
+  if (E.fused_NG == 1) launch_chain_fused_g1(TA, E.fused, io, std::min(nctas, dev().sm_count));
+  else launch_chain_fused(TA, E.fused, io, std::min(nctas, dev().sm_count));
 }
 
 // bond sums -> fused dense network (forward, readout, reverse in one kernel) -> bond forces; only the bond-sum tensor

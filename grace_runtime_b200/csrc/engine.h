@@ -38,6 +38,7 @@ struct LayerEngine {
   DBuf<int> f_soff, f_tch;
   FusedLayerDev fused{};
   int fused_TA = 0;           // atoms per tile that fit the shared memory (0: the layer does not fit)
+  int fused_NG = 2;           // warp groups per CTA the layer runs with (2, or 1 when two would get one atom each)
   long long q_floats = 0;     // floats per atom of the bond-sum tensor
 };
 

@@ -147,9 +147,8 @@ struct FusedIO {
 };
 
 // TA: atoms per tile (1, 2, 3, 4, 6, 8); grid CTAs loop over the tiles
-void launch_chain_fused(int TA, const FusedLayerDev &L, const FusedIO &io, int grid);
-// independent warp groups per CTA, each working on its own tile of TA atoms
-int fused_groups();
+void launch_chain_fused(int TA, const FusedLayerDev &L, const FusedIO &io, int grid);       // two groups per CTA
+void launch_chain_fused_g1(int TA, const FusedLayerDev &L, const FusedIO &io, int grid);    // one group per CTA
 
 // chunk tensor [nf][NA][C] <-> per-atom rows [n][nf][C] (message I, its gradient) and [n][C] (rho)
 void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0);
