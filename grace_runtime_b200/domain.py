@@ -5,7 +5,8 @@ the atoms of one slab of the cell and evaluates them together with a halo of gho
 own, periodic images included) as a sub-system that is open along the slab axis and keeps the cell's other two
 directions.  The library leaves the ghosts' own energies out (`System.set_owned`), so the forces it returns are the
 gradient of the owned energies with respect to every atom of the sub-system; the ghost rows go back to their owners
-(one all-to-all of force rows), energy and virial are summed over the ranks (one all-reduce of 7 doubles).  This is the
+(one all-to-all of force rows, whose blocks also carry each rank's energy and virial, so the totals need no second
+collective).  This is the
 "halo = layers x cutoff, one return" scheme; the reference's own multi-GPU runs go through LAMMPS' ghost atoms and
 forward / reverse communication (libgrace/include/grace/system.h:56-60, libgrace/include/grace/kk/grace_2l_kk.h:136-153).
 
@@ -156,10 +157,25 @@ class DistributedSystem:
         self.types, self.pos, self.nlocal = plan.subsystem(rank, types, positions)
         self.n = len(self.types)
         self.device = device if device is not None else torch.device("cpu")
-        self.send_splits = [int(c) for c in plan.send_counts(rank)]
-        self.recv_splits = [int(c) for c in plan.recv_counts(rank)]
-        self.recv_idx = torch.from_numpy(plan.recv_index(rank)).to(self.device)
-        self.send_idx = torch.from_numpy(plan.send_order(rank) + self.nlocal).to(self.device)
+        # every block of the all-to-all carries the ghost rows for that owner and 3 more rows with this rank's energy and
+        # virial (9 doubles, 7 used), so that one collective both returns the forces and sums the totals
+        W = plan.world
+        sc, rc = plan.send_counts(rank), plan.recv_counts(rank)
+        self.send_splits = [int(c) + 3 for c in sc]
+        self.recv_splits = [int(c) + 3 for c in rc]
+        n = self.n
+        order = plan.send_order(rank) + self.nlocal
+        send_idx, at = [], 0
+        for d in range(W):
+            send_idx.append(order[at:at + int(sc[d])]); at += int(sc[d])
+            send_idx.append(np.array([n, n + 1, n + 2], dtype=np.int64))          # the rows behind the forces: energy, virial
+        self.send_idx = torch.from_numpy(np.concatenate(send_idx)).to(self.device)
+        ridx, recv_idx, at = plan.recv_index(rank), [], 0
+        for r in range(W):
+            recv_idx.append(ridx[at:at + int(rc[r])]); at += int(rc[r])
+            # the totals of the other ranks add onto this rank's own rows; its own copy goes to a scratch row
+            recv_idx.append(np.array([n, n + 1, n + 2] if r != rank else [n + 3, n + 3, n + 3], dtype=np.int64))
+        self.recv_idx = torch.from_numpy(np.concatenate(recv_idx)).to(self.device)
         self.layers = 1
         self.engine = engine
         if engine is None:
@@ -171,9 +187,11 @@ class DistributedSystem:
         dev = self.device
         self.d_types = torch.from_numpy(self.types).to(dev)
         self.d_pos = torch.from_numpy(self.pos).to(dev)
-        self.d_ev = torch.zeros(7, dtype=torch.float64, device=dev)           # energy, virial[6]
-        self.d_f = torch.zeros((max(self.n, 1), 3), dtype=torch.float64, device=dev)
-        self.d_recv = torch.zeros((max(sum(self.recv_splits), 1), 3), dtype=torch.float64, device=dev)
+        # forces [n, 3], then 3 rows holding energy and virial[6] (and 2 unused doubles), then a scratch row
+        self.d_fx = torch.zeros((self.n + 4, 3), dtype=torch.float64, device=dev)
+        self.d_f = self.d_fx[:max(self.n, 1)]
+        self.d_ev = self.d_fx.view(-1)[3 * self.n:3 * self.n + 7]
+        self.d_recv = torch.zeros((sum(self.recv_splits), 3), dtype=torch.float64, device=dev)
 
     def load_positions(self, sub_positions_pinned):
         """host -> device copy of this rank's sub-system positions (the end-to-end leg)"""
@@ -198,12 +216,10 @@ class DistributedSystem:
         torch = self.torch
         if self.plan.world == 1:
             return
-        send = self.d_f.index_select(0, self.send_idx)
-        recv = self.d_recv[:sum(self.recv_splits)]
-        dist.all_to_all_single(recv, send, self.recv_splits, self.send_splits, group=self.group)
-        if recv.shape[0]:
-            self.d_f.index_add_(0, self.recv_idx, recv)
-        dist.all_reduce(self.d_ev, group=self.group)
+        self.d_fx.view(-1)[3 * self.n + 7:3 * self.n + 12].zero_()    # the unused doubles of the total rows, the scratch row
+        send = self.d_fx.index_select(0, self.send_idx)
+        dist.all_to_all_single(self.d_recv, send, self.recv_splits, self.send_splits, group=self.group)
+        self.d_fx.index_add_(0, self.recv_idx, self.d_recv)
 
     def step(self):
         self.evaluate_local()
