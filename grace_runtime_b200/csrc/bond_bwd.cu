@@ -96,13 +96,12 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
                   dR[l] = __ldg(L.dRex + ro + l * C);
                 }
               } else {
-                const float *cf = L.tab + ((size_t) k * 4 * NL) * C + n;
+                const float4 *cf = reinterpret_cast<const float4 *>(L.tab) + (size_t) k * NL * C + n;
 #pragma unroll
                 for (int l = 0; l < NL; l++) {
-                  const float c0 = __ldg(cf + (size_t) (0 * NL + l) * C), c1 = __ldg(cf + (size_t) (1 * NL + l) * C);
-                  const float c2 = __ldg(cf + (size_t) (2 * NL + l) * C), c3 = __ldg(cf + (size_t) (3 * NL + l) * C);
-                  R[l] = c0 + t * (c1 + t * (c2 + t * c3));
-                  dR[l] = (c1 + t * (2.0f * c2 + t * 3.0f * c3)) * fN;
+                  const float4 c = __ldg(cf + l * C);
+                  R[l] = c.x + t * (c.y + t * (c.z + t * c.w));
+                  dR[l] = (c.y + t * (2.0f * c.z + t * 3.0f * c.w)) * fN;
                 }
               }
 #pragma unroll

@@ -48,7 +48,7 @@ struct BondsDev {
 
 // per layer: radial table, chemical weights, messages
 struct LayerDev {
-  const float *tab;        // [N][4][nl][C]
+  const float *tab;        // [N][nl][C][4]: cubic Hermite coefficients
   const float *z;          // [n_elements][C]
   const float *rc;         // [n_elements][n_elements] pair cutoffs
   const float *msg;        // [n][n_msg][C] message rows of all atoms (layer 2) or null

@@ -69,7 +69,8 @@ void mlp_x(const std::vector<MlpLayer> &layers, std::vector<double> h, std::vect
   dout.swap(dh);
 }
 
-// cubic Hermite coefficients of R[n][l](x) on N intervals of [0, 1], [N][4][nl][C] in fp32
+// cubic Hermite coefficients of R[n][l](x) on N intervals of [0, 1], [N][nl][C][4] in fp32 (the four coefficients of a
+// channel side by side: one 16-byte load per lane and l)
 // (libgrace/src/fused_1l.cpp:102-129)
 RadialTable build_radial(const GraceModel &m, const std::vector<MlpLayer> &layers, int C, int N)
 {
@@ -97,7 +98,7 @@ RadialTable build_radial(const GraceModel &m, const std::vector<MlpLayer> &layer
         const double f0 = fv[(size_t) k * nout + o], f1 = fv[(size_t) (k + 1) * nout + o];
         const double d0 = dv[(size_t) k * nout + o], d1 = dv[(size_t) (k + 1) * nout + o];
         const double c[4] = {f0, d0, -3.0 * f0 - 2.0 * d0 + 3.0 * f1 - d1, 2.0 * f0 + d0 - 2.0 * f1 + d1};
-        for (int q = 0; q < 4; q++) T.tab[(((size_t) k * 4 + q) * nl + l) * C + n] = (float) c[q];
+        for (int q = 0; q < 4; q++) T.tab[((((size_t) k * nl + l) * C + n) << 2) + q] = (float) c[q];
       }
   return T;
 }

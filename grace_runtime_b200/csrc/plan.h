@@ -80,7 +80,7 @@ struct Program {
 
 struct RadialTable {
   int N = 0, nl = 0, C = 0;
-  std::vector<float> tab;    // [N][4][nl][C]: cubic Hermite coefficients per interval
+  std::vector<float> tab;    // [N][nl][C][4]: cubic Hermite coefficients per interval
 };
 
 struct LayerPlan {
