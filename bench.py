@@ -102,7 +102,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per atom of one launch, from the ncu captures summarised in profiles/
 NCU_DRAM_BYTES_PER_ATOM = {("chain_fused_kernel", "1l"): 781.5e6 / 128000, ("bond_fwd_kernel", "1l"): 488.2e6 / 128000,
-                           ("bond_bwd_kernel", "1l"): 696.4e6 / 128000}
+                           ("bond_bwd_kernel", "1l"): 693.2e6 / 128000}
 
 
 def algorithmic_bytes(kernel, model_cfg, n_atoms, n_bonds, slots):
