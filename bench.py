@@ -2,12 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Workload at one GPU: the 128,000-atom GRACE-1L configuration (random 4-component bcc alloy, 89-element model) - the
-single-GPU configuration the metric is quoted on.  Prints one JSON line (rank 0).  `value` is microseconds per atom
-per GPU with the inputs resident in HBM and the neighbour list reused, timed with CUDA events on the stream the
-kernels are launched on; `e2e` is the same through the host-buffer C ABI call (pinned host memory, copies inside the
-timed region).  The reference arm (--impl reference) times the reference's own CPU drivers (oracle/_ref) on the host
-cores on a bounded sample of the same workload.
+Default workload: the 1,024,000-atom GRACE-2L configuration (random 3-component fcc alloy, 89-element model), which
+fits one GPU in one pass; the 128,000-atom GRACE-1L configuration is reported beside it (`also`, one GPU).  Prints one
+JSON line (rank 0).  `value` is the step time divided by the atoms of the structure (microseconds per atom of the whole
+job: at N GPUs it falls as 1 / N under ideal strong scaling; `us_per_atom_per_gpu` = value x N) with the inputs resident
+in HBM and the neighbour list reused, timed with CUDA events; `e2e` is the same through the host-buffer call (pinned
+host memory, copies inside the timed region).  `parity` holds the differences between the library and the reference's
+CPU drivers on the block of the workload the CPU leg is timed on.  The reference arm (--impl reference) times the
+reference's own CPU drivers (oracle/_ref) on the host cores on that block.
 """
 from __future__ import annotations
 
@@ -28,8 +30,8 @@ if ROOT not in sys.path:
 
 from grace_runtime_b200 import modelgen, structures  # noqa: E402
 
-METRIC = "us_per_atom_per_gpu_energy_forces_stress"
-UNIT = "us/atom/GPU"
+METRIC = "us_per_atom_energy_forces_stress"
+UNIT = "us/atom"
 
 WORKLOADS = {
     # name: (config, lattice, a, reps, species, sigma)
@@ -41,7 +43,8 @@ WORKLOADS = {
     # 4096 small periodic structures (16-256 atoms, triclinic, 0.06-0.09 atoms/A^3) through the Batch entry points
     "grace2l_batch4096": dict(cfg="2l", batch=4096, unique=128, nmin=16, nmax=256, nsp=89, full=True),
 }
-DEFAULT = "grace1l_128k_bcc_alloy"
+DEFAULT = "grace2l_1m_fcc_alloy"      # the 1,024,000-atom GRACE-2L configuration the target is stated on
+ALSO = "grace1l_128k_bcc_alloy"       # reported beside it at one GPU (`also`)
 
 
 def make_workload(name, tmp, reps=None):
@@ -98,11 +101,6 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum per atom of one launch, from the ncu captures summarised in profiles/
-NCU_DRAM_BYTES_PER_ATOM = {("chain_fused_kernel", "1l"): 781.5e6 / 128000, ("bond_fwd_kernel", "1l"): 488.2e6 / 128000,
-                           ("bond_bwd_kernel", "1l"): 693.2e6 / 128000}
 
 
 def algorithmic_bytes(kernel, model_cfg, n_atoms, n_bonds, slots):
@@ -213,16 +211,14 @@ def run_batch(args, rank, world, local_rank):
         ms = float(red[0])
         tot = sum(v[1] for v in prof.values()) or 1.0
         kern = sorted(prof.items(), key=lambda kv: -kv[1][1])
-        out = {"metric": METRIC, "value": ms * 1e3 * world / n_total, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        out = {"metric": METRIC, "value": ms * 1e3 / n_total, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-               "dtype": "f32", "data": "synthetic",
-               "config": {"workload": args.workload, "structures": int(wl["batch"]), "atoms": n_total, "model": "GRACE-2L",
-                          "elements_in_model": 89, "atoms_per_structure": [int(wl["nmin"]), int(wl["nmax"])],
-                          "unique_structures": int(wl["unique"]), "parallelism": f"structures over {world} rank(s)",
-                          "passes": batch.passes, "neighbor_list": "built every step (Batch semantics)",
-                          "value_definition": "max-over-ranks time per step x n_gpus / atoms"},
+               "dtype": "f32", "data": "synthetic", "config": base_config(args.workload, world),
+               "value_definition": "max-over-ranks time per step / atoms of the batch (whole job)",
+               "details": {"atoms": n_total, "unique_structures": int(wl["unique"]), "passes": batch.passes,
+                           "neighbor_list": "built every step (Batch semantics)"},
                "structures_per_s": wl["batch"] / (ms * 1e-3),
-               "e2e": {"value": float(red[2]) * 1e3 * world / n_total, "unit": UNIT, "ms_per_step": float(red[2]),
+               "e2e": {"value": float(red[2]) * 1e3 / n_total, "unit": UNIT, "ms_per_step": float(red[2]),
                        "h2d_bytes_per_step": int(28 * n_total + 75 * wl["batch"]), "d2h_bytes_per_step": int(24 * n_total + 56 * wl["batch"])},
                "gpu_launches": int(cnt[0]), "clocks": clocks, "roofline": None,
                "kernels": {k: {"launches": v[0], "ms_per_step": v[1] / args.steps, "share": v[1] / tot} for k, v in kern[:8]},
@@ -230,6 +226,124 @@ def run_batch(args, rank, world, local_rank):
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def base_config(workload, world):
+    """The `config` object of the JSON line, the same for both arms (--impl ours / reference)."""
+    wl = WORKLOADS[workload]
+    if "batch" in wl:
+        return {"workload": workload, "structures": int(wl["batch"]), "model": "GRACE-2L", "elements_in_model": 89,
+                "atoms_per_structure": [int(wl["nmin"]), int(wl["nmax"])], "parallelism": f"structures over {world} rank(s)"}
+    n = int(np.prod(wl["reps"])) * (2 if wl["lattice"] == "bcc" else 4)
+    return {"workload": workload, "atoms": n, "model": "GRACE-1L" if wl["cfg"] == "1l" else "GRACE-2L",
+            "elements_in_model": 89 if wl["full"] else 1, "species_in_structure": int(wl["nsp"]),
+            "lattice": wl["lattice"], "lattice_constant_A": wl["a"], "cells": list(wl["reps"]),
+            "displacement_sigma_A": wl["sigma"], "cutoff_A": 6.0, "skin_A": 0.5,
+            "neighbor_list": "reused (built in warm-up)", "radial": "cubic Hermite tables, 1024 intervals",
+            "parallelism": f"slabs{world}" if world > 1 else "single",
+            "l2": "per-step working set (bond records + chunk tensors) exceeds the 126 MB L2"}
+
+
+def sample_reps(wl):
+    """The block of the workload the CPU legs run on (the same lattice, alloy, displacements and model; about 32,000
+    atoms, so that a CPU step takes a fraction of a second): None when the workload itself is that small."""
+    n = int(np.prod(wl["reps"])) * (2 if wl["lattice"] == "bcc" else 4)
+    if n <= 40000:
+        return None
+    return (20, 20, 40) if wl["lattice"] == "bcc" else (16, 16, 32)
+
+
+def load_traffic():
+    """ncu DRAM traffic per atom of a launch, by (kernel, workload): profiles/traffic.json names the capture each
+    figure came from; a kernel / workload pair without an entry gets traffic null."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            return {(e["kernel"], e["model"]): e for e in json.load(f)["entries"]}
+    except (OSError, ValueError, KeyError):
+        return {}
+
+
+def time_device_steps(step, steps, torch):
+    """K steps between two CUDA events with a synchronize on both sides; every library call ends with a synchronize of
+    its own stream, so events on torch's stream bracket all of its work.  Returns (ms per step, per-step list)."""
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    torch.cuda.synchronize()
+    evs[0].record()
+    for k in range(steps):
+        step()
+        evs[k + 1].record()
+    evs[-1].synchronize()
+    torch.cuda.synchronize()
+    per = [evs[k].elapsed_time(evs[k + 1]) for k in range(steps)]
+    return evs[0].elapsed_time(evs[-1]) / steps, per
+
+
+def parity_and_cpu(args, B, model, path, species, wl):
+    """The CPU legs of the bench (rank 0, one GPU): the reference's CPU drivers timed on a block of the workload, and
+    the SAME block through the library (host-pointer entry) with the differences against the reference."""
+    from oracle import refcpu
+    reps = sample_reps(wl) or wl["reps"]
+    types, pos, cell, pbc = structures.crystal(wl["lattice"], wl["a"], reps, n_species=wl["nsp"], sigma=wl["sigma"], seed=1)
+    n, vol = len(types), abs(np.linalg.det(cell))
+    cores = len(os.sched_getaffinity(0))
+    block = f"{n} atoms ({'x'.join(str(r) for r in reps)} cells) of the same alloy, model and seeds"
+    if not refcpu.available():
+        from oracle.grace_oracle import GraceOracle
+        types, pos, cell, pbc = structures.crystal(wl["lattice"], wl["a"], (4, 4, 4), n_species=wl["nsp"], sigma=wl["sigma"], seed=1)
+        n, vol = len(types), abs(np.linalg.det(cell))
+        o = GraceOracle(path)
+        t0 = time.perf_counter()
+        ref = o.compute(species, types, pos, cell, pbc)
+        dt = time.perf_counter() - t0
+        base = {"value": dt * 1e6 / n, "unit": "us/atom", "cores": 1, "kind": "port",
+                "sample": f"{n} atoms, numpy fp64 restatement, one call", "neighbor_search_us_per_atom": None}
+    else:
+        rm = refcpu.RefModel(path, species)
+        rm.compute(types, pos, cell, pbc, nthreads=cores)               # warm-up (tables, buffers)
+        ref = rm.compute(types, pos, cell, pbc, nthreads=cores, repeats=3)
+        base = {"value": ref["seconds_median"] * 1e6 / n, "unit": "us/atom", "cores": cores, "kind": "reference",
+                "sample": block + ", median of 3 calls after the first, neighbour search not included in `value`",
+                "neighbor_search_us_per_atom": ref["seconds_nlist"] * 1e6 / n,
+                "energy_eV_per_atom": ref["energy"] / n}
+    s = B.System(model, species, skin=0.5)
+    r = s.compute(types, pos, cell, pbc)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        r = s.compute(types, pos, cell, pbc)
+    gpu_us = (time.perf_counter() - t0) / 3 * 1e6 / n
+    s.release_buffers()
+    de = abs(r["energy"] - ref["energy"]) / n
+    df = float(np.abs(r["forces"] - ref["forces"]).max())
+    dv = float(np.abs(r["virial"] - ref["virial"]).max() / vol)
+    parity = {"against": base["kind"], "atoms": n, "block": block, "dE_per_atom_eV": de, "dF_max_eV_per_A": df,
+              "dstress_max_eV_per_A3": dv, "tolerance": {"energy": 1e-5, "forces": 1e-4, "stress": 1e-4},
+              "tolerance_met": bool(de <= 1e-5 and df <= 1e-4 and dv <= 1e-4),
+              "F_max_eV_per_A": float(np.abs(ref["forces"]).max()),
+              "gpu_us_per_atom_on_block_e2e": gpu_us}
+    return base, parity
+
+
+def run_also(args, B, torch, name):
+    """A second workload on the same GPU, device-resident, reported beside the headline (one GPU only)."""
+    tmp = tempfile.mkdtemp(prefix="grace_bench_also_")
+    path, species, types, pos, cell, pbc = make_workload(name, tmp)
+    n = len(types)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model = B.Model(path)
+    s = B.System(model, species, skin=0.5)
+    d_t = torch.from_numpy(types).to(dev); d_x = torch.from_numpy(pos).to(dev)
+    e = torch.zeros(1, dtype=torch.float64, device=dev); v = torch.zeros(6, dtype=torch.float64, device=dev)
+    f = torch.zeros((n, 3), dtype=torch.float64, device=dev)
+
+    def step():
+        s.compute_device(d_t, d_x, cell, pbc, e, forces=f, virial=v)
+    for _ in range(3):
+        step()
+    k = max(3, min(args.steps, 10))
+    ms, per = time_device_steps(step, k, torch)
+    s.release_buffers()
+    return {"workload": name, "atoms": n, "model": base_config(name, 1)["model"], "value": ms * 1e3 / n, "unit": UNIT,
+            "ms_per_step": ms, "steps": k, "warmup": 3, "ms_per_step_median": float(np.median(per))}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -251,12 +365,6 @@ def run_ours(args, rank, world, local_rank):
     model = B.Model(path)
     skin = 0.5
     cutoff = B.System(model, species, skin=skin).cutoff
-    # slabs across the longest cell direction, one per rank, with a ghost halo of layers x (cutoff + skin)
-    plan = domain.make_plan(pos, cell, pbc, world, model.layers, cutoff, skin)
-    ds = domain.DistributedSystem(plan, rank, types, pos, species=species, model=model, skin=skin,
-                                  chunksize=args.chunk, device=dev)
-    system = ds.system
-    n_sub, n_own = ds.n, ds.nlocal
 
     def barrier():
         torch.cuda.synchronize()
@@ -264,65 +372,87 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
             torch.cuda.synchronize()
 
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the denominators of the compute-bound rooflines, measured on this GPU before the warm-up
+    peaks_here = {"fp32_simt_tflops": B.measure_peak("fp32"), "tf32_tensor_tflops": B.measure_peak("tf32")}
 
-    def step_device():
-        """device time of one step on this rank: the library's own events on its launch stream around the evaluation,
-        torch events on the stream of the collectives around the exchange (the two run one after the other)"""
-        ds.evaluate_local()
-        ms = system.stage_ms
-        t = ms["total"]
-        if world > 1:
-            ev0.record()
-            ds.exchange()
-            ev1.record()
-            ev1.synchronize()
-            t += ev0.elapsed_time(ev1)
-        return t, ms
+    # at N > 1, once before anything is timed: the whole structure on rank 0's GPU alone, as the check of the
+    # decomposed forces (workloads that fit one GPU)
+    f_single = e_single = None
+    if world > 1 and rank == 0 and n <= 2_500_000:
+        r1 = B.System(model, species, skin=skin)
+        d_t = torch.from_numpy(types).to(dev); d_x = torch.from_numpy(pos).to(dev)
+        e1 = torch.zeros(1, dtype=torch.float64, device=dev); f1 = torch.zeros((n, 3), dtype=torch.float64, device=dev)
+        v1 = torch.zeros(6, dtype=torch.float64, device=dev)
+        r1.compute_device(d_t, d_x, cell, pbc, e1, forces=f1, virial=v1)
+        f_single, e_single = f1.cpu().numpy(), float(e1.item())
+        r1.release_buffers()
+        del r1, d_t, d_x, f1
+        torch.cuda.empty_cache()
+
+    # slabs across the longest cell direction, one per rank, with a ghost halo of layers x (cutoff + skin)
+    plan = domain.make_plan(pos, cell, pbc, world, model.layers, cutoff, skin)
+    ds = domain.DistributedSystem(plan, rank, types, pos, species=species, model=model, skin=skin,
+                                  chunksize=args.chunk, device=dev)
+    system = ds.system
+    n_sub, n_own = ds.n, ds.nlocal
 
     # the clock sampler starts before the warm-up: nvidia-smi takes ~100 ms to come up and must not do that inside a
     # timed region of a few milliseconds per step; its samples cover warm-up and timed steps (the same work)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    for _ in range(max(args.warmup, 1)):
-        step_device()
+    for _ in range(max(args.warmup, 3)):
+        ds.step()
     barrier()
     l0 = B.kernel_launches()
     B.profile_enable(True)
-    # the K steps between two CUDA events, a synchronize on both sides (the library's stream is synchronised by every
-    # call, so the events on torch's stream see all of its work); the sum of the per-step device intervals is kept as
-    # `device_busy_ms_per_step`
-    evA, evB = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    evA.record()
-    t0 = time.perf_counter()
-    dev_ms, stages = 0.0, dict(neighbor_list=0.0, bonds=0.0, forward=0.0, reverse=0.0)
-    for _ in range(args.steps):
-        t, ms = step_device()
-        dev_ms += t
+    stages = dict(neighbor_list=0.0, bonds=0.0, forward=0.0, reverse=0.0)
+    busy = [0.0]
+
+    def step_device():
+        ds.step()
+        ms = system.stage_ms
+        busy[0] += ms["total"]
         for k in stages:
             stages[k] += ms[k] / args.steps
-    torch.cuda.synchronize()
-    evB.record()
-    evB.synchronize()
-    bracket_ms = evA.elapsed_time(evB)
+
+    t0 = time.perf_counter()
+    ms_mean, per_step = time_device_steps(step_device, args.steps, torch)
     wall_ms = (time.perf_counter() - t0) * 1e3
     barrier()
     prof = B.profile_report()
     B.profile_enable(False)
     launches = B.kernel_launches() - l0
     clocks = sampler.stop()
-    times = torch.tensor([bracket_ms / args.steps, wall_ms / args.steps, dev_ms / args.steps], dtype=torch.float64, device=dev)
+    times = torch.tensor([ms_mean, wall_ms / args.steps, busy[0] / args.steps, float(np.median(per_step)),
+                          float(np.max(per_step))], dtype=torch.float64, device=dev)
     counts = torch.tensor([float(launches), float(n_sub), float(n_own)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(counts, op=dist.ReduceOp.SUM)
     ms_per_step, wall_ms_per_step, busy_ms_per_step = float(times[0]), float(times[1]), float(times[2])
-    value = ms_per_step * 1e3 * world / n          # GPU-microseconds per atom: step time x GPUs / atoms
+    value = ms_per_step * 1e3 / n          # whole job: step time / atoms (the driver's strong-scaling formula v_1 / (N v_N))
     energy = ds.energy
 
-    # end to end with host buffers
+    # the decomposed forces against the single-GPU evaluation: every rank's owned rows gathered on rank 0
+    digest = None
+    if world > 1:
+        fo = ds.owned_forces.cpu().numpy()
+        gathered = [None] * world if rank == 0 else None
+        dist.gather_object((plan.owned[rank], fo), gathered, dst=0)
+        if rank == 0:
+            F = np.zeros((n, 3))
+            for own, f in gathered:
+                F[own] = f
+            digest = {"F_max_abs": float(np.abs(F).max()), "F_sum_sq": float((F * F).sum()),
+                      "F_net_max_abs": float(np.abs(F.sum(0)).max())}
+            if f_single is not None:
+                digest.update(dF_max_vs_single_gpu=float(np.abs(F - f_single).max()),
+                              dE_per_atom_vs_single_gpu=abs(energy - e_single) / n,
+                              tolerance_met=bool(np.abs(F - f_single).max() <= 1e-4 and abs(energy - e_single) / n <= 1e-5))
+
+    # end to end with host buffers: every step copies its inputs from pinned host memory and its results back
     if world == 1:
-        # the reference-facing host-pointer entry point, pinned host memory, copies inside the timed region
+        # the reference-facing host-pointer entry point
         h_types = torch.from_numpy(types).pin_memory().numpy()
         h_pos = torch.from_numpy(pos).pin_memory().numpy()
         h_f = torch.zeros((n, 3), dtype=torch.float64).pin_memory().numpy()
@@ -348,7 +478,6 @@ def run_ours(args, rank, world, local_rank):
 
         def step_host():
             ds.load_positions(h_pos)
-            torch.cuda.current_stream().synchronize()
             ds.step()
             h_f[:n_own].copy_(ds.owned_forces, non_blocking=True)
             h_ev.copy_(ds.d_ev, non_blocking=True)
@@ -358,16 +487,20 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(max(args.warmup, 3)):     # the first host-path calls grow the staging buffers and touch the pinned pages
         step_host()
     barrier()
+    e2e_steps = []
     t0 = time.perf_counter()
     for _ in range(args.steps):
+        t1 = time.perf_counter()
         step_host()
+        e2e_steps.append((time.perf_counter() - t1) * 1e3)
     barrier()
-    e2e_t = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps], dtype=torch.float64, device=dev)
+    e2e_t = torch.tensor([(time.perf_counter() - t0) * 1e3 / args.steps, float(np.median(e2e_steps)), float(np.max(e2e_steps))],
+                         dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_ms = float(e2e_t[0])
-    e2e = {"value": e2e_ms * 1e3 * world / n, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(h2d),
-           "d2h_bytes_per_step": int(d2h)}
+    e2e = {"value": e2e_ms * 1e3 / n, "unit": UNIT, "ms_per_step": e2e_ms, "ms_per_step_median": float(e2e_t[1]),
+           "ms_per_step_max": float(e2e_t[2]), "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -381,7 +514,7 @@ def run_ours(args, rank, world, local_rank):
     hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
     tot = sum(v[1] for v in prof.values()) or 1.0
     kern = sorted(prof.items(), key=lambda kv: -kv[1][1])
-    shares = {k: {"launches": v[0], "ms_per_step": v[1] / args.steps, "share": v[1] / tot} for k, v in kern[:8]}
+    shares = {k: {"launches": v[0], "ms_per_step": v[1] / args.steps, "share": v[1] / tot} for k, v in kern[:10]}
     top, (top_n, top_ms) = kern[0]
     top = top.strip("()").split("<")[0]
     # atoms this rank evaluates, their bonds inside the cutoff and list slots: from the lattice of the workload (58
@@ -390,31 +523,39 @@ def run_ours(args, rank, world, local_rank):
     n_bonds = per_atom_bonds * n_own
     slots = per_atom_bonds * n_sub * (6.5 / 6.0) ** 3
     per_launch_ms = top_ms / top_n
-    sm_mhz = clocks.get("sm_mhz") or 1965.0
-    if top == "chain_fused_kernel":
-        # FMA-bound: useful fp32 multiply-adds of the dense network (forward + adjoints) against the SIMT peak of the
-        # SMs at the clock sampled during the run
-        # (GRACE-2L evaluates layer 1 twice, once more for the reverse pass: only one is counted as useful)
-        flop = model.dense_flops * n_own * args.steps / top_n
-        peak_tf = 148 * 128 * 2 * sm_mhz * 1e6 / 1e12
+    traffic_tab = load_traffic()
+
+    def traffic_of(kernel, launches_per_step):
+        e = traffic_tab.get((kernel, wl["cfg"]))
+        return e["dram_bytes_per_atom"] * n_own / launches_per_step if e else None
+
+    if top.startswith("chain_"):
+        # dense network: useful fp32 multiply-adds of the forward and reverse programs (GRACE-2L may evaluate layer 1
+        # twice: counted once) per launch, against the measured peak of the unit the kernel computes on
+        lps = top_n / args.steps
+        flop = model.dense_flops * n_own / lps
         ach = flop / (per_launch_ms * 1e-3) / 1e12
-        roof = {"bound": "fp32", "kernel": top, "peak": peak_tf, "peak_source": "148 SMs x 128 FMA lanes x 2 flop x sampled SM clock (no measured SIMT peak in MEASURED_PEAKS.json)",
-                "unit": "TFLOP/s", "achieved": ach, "frac": ach / peak_tf,
-                # DRAM bytes per launch from the ncu capture of this kernel on this workload (profiles/), scaled by the
-                # atoms of a launch: traffic grows in proportion to the atoms
-                "traffic": (NCU_DRAM_BYTES_PER_ATOM.get((top, wl["cfg"]), 0.0) * n_own * args.steps / top_n) or None,
-                "algorithmic_bytes_per_launch": 2.0 * 4.0 * (modelgen.CONFIGS[wl["cfg"]]["lmax"] + 1) ** 2 * modelgen.CONFIGS[wl["cfg"]]["c1"] * n_own * args.steps / top_n,
+        tensor = top.startswith("chain_tc")
+        # a 3 x tf32 product issues three tensor-core instructions per useful multiply-add
+        peak_tf = peaks_here["tf32_tensor_tflops"] / 3.0 if tensor else peaks_here["fp32_simt_tflops"]
+        roof = {"bound": "tensor" if tensor else "fp32", "kernel": top, "peak": peak_tf,
+                "peak_source": ("tf32 tcgen05 microbenchmark of this run / 3 (three tf32 instructions per fp32-accurate product)"
+                                if tensor else "fp32 FFMA microbenchmark of this run (measured in this run)"),
+                "unit": "TFLOP/s", "achieved": ach, "frac": ach / peak_tf, "traffic": traffic_of(top, lps),
+                "algorithmic_bytes_per_launch": 2.0 * 4.0 * (modelgen.CONFIGS[wl["cfg"]]["lmax"] + 1) ** 2 * modelgen.CONFIGS[wl["cfg"]]["c1"] * n_own / lps,
                 "flop_per_launch": flop, "flop_per_atom": model.dense_flops, "avg_launch_ms": per_launch_ms,
-                "note": "dense-network kernel: shared-memory resident fp32 SIMT work, neither HBM- nor tensor-bound; "
-                        "its DRAM traffic (ncu) is in profiles/"}
+                "launches_per_step": lps,
+                "note": "dense-network kernel: shared-memory resident, compute-bound (not HBM-bound); useful fp32-equivalent "
+                        "flops of the plan / average launch time"}
     else:
         roof = {"bound": "hbm", "kernel": top, "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "traffic": None}
         ab = algorithmic_bytes(top, wl["cfg"], n_own, n_bonds, slots)
         if ab is not None:
-            per_launch_bytes = ab * args.steps / top_n
+            lps = top_n / args.steps
+            per_launch_bytes = ab / lps
             roof.update(achieved=per_launch_bytes / (per_launch_ms * 1e-3) / 1e9,
                         algorithmic_bytes_per_launch=per_launch_bytes, avg_launch_ms=per_launch_ms,
-                        traffic=(NCU_DRAM_BYTES_PER_ATOM.get((top, wl["cfg"]), 0.0) * n_own * args.steps / top_n) or None)
+                        traffic=traffic_of(top, lps))
             roof["frac"] = roof["achieved"] / hbm_peak
         else:
             roof.update(achieved=None, frac=None)
@@ -429,54 +570,34 @@ def run_ours(args, rank, world, local_rank):
 
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-           "dtype": "f32", "data": "synthetic",
-           "config": {"workload": args.workload, "atoms": int(n), "model": "GRACE-1L" if wl["cfg"] == "1l" else "GRACE-2L",
-                      "elements_in_model": 89 if wl["full"] else 1, "species": species, "cutoff_A": cutoff, "skin_A": skin,
-                      "neighbor_list": "reused (built in warm-up)", "chunk_atoms": system.chunksize,
-                      "parallelism": f"slabs{world}" if world > 1 else "single",
-                      "value_definition": "max over ranks of (CUDA-event time of the K steps / K) x n_gpus / atoms",
-                      "atoms_evaluated_all_ranks": int(counts[2]), "atoms_with_ghosts_all_ranks": int(counts[1]),
-                      "l2": "per-step working set (bond records + chunk tensors) exceeds the 126 MB L2",
-                      "radial": "cubic Hermite tables, 1024 intervals"},
+           "dtype": "f32", "data": "synthetic", "config": base_config(args.workload, world),
+           "value_definition": "max over ranks of (CUDA-event time of the K steps / K) / atoms of the structure (whole job)",
+           "us_per_atom_per_gpu": value * world,
+           "ms_per_step_median": float(times[3]), "ms_per_step_max": float(times[4]),
            "e2e": e2e, "gpu_launches": int(counts[0]), "clocks": clocks, "roofline": roof, "hbm_kernels": hbm_kernels,
+           "measured_peaks": peaks_here,
+           "details": {"species": species, "cutoff_A": cutoff, "chunk_atoms": system.chunksize,
+                       "atoms_evaluated_all_ranks": int(counts[2]), "atoms_with_ghosts_all_ranks": int(counts[1])},
            "stages_ms_per_step": stages, "kernels": shares, "wall_ms_per_step": wall_ms_per_step,
            "device_busy_ms_per_step": busy_ms_per_step,
            "energy_eV": energy, "atoms_per_s": n / (ms_per_step * 1e-3)}
-    if not args.no_cpu and world == 1:
-        out["cpu_baseline"] = cpu_baseline(args, path, species, types, pos, cell, pbc, bounded=True)
+    if digest is not None:
+        out["force_digest"] = digest
+    if world == 1:
+        ds = None
+        system.release_buffers()
+        if not args.no_cpu:
+            out["cpu_baseline"], out["parity"] = parity_and_cpu(args, B, model, path, species, wl)
+        if args.workload == DEFAULT and not args.no_also:
+            out["also"] = run_also(args, B, torch, ALSO)
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
 
 
-def cpu_baseline(args, path, species, types, pos, cell, pbc, bounded):
-    """The reference's own CPU drivers on the host cores (oracle/_ref), or the numpy port when it did not travel."""
-    from oracle import refcpu
-    wl = WORKLOADS[args.workload]
-    cores = len(os.sched_getaffinity(0))
-    if refcpu.available():
-        if bounded and len(types) > 32000:      # about 10-30 s of CPU work: a smaller block of the same alloy
-            reps = (20, 20, 40) if wl["lattice"] == "bcc" else (16, 16, 32)
-            types, pos, cell, pbc = structures.crystal(wl["lattice"], wl["a"], reps, n_species=wl["nsp"],
-                                                       sigma=wl["sigma"], seed=1)
-        rm = refcpu.RefModel(path, species)
-        rm.compute(types, pos, cell, pbc, nthreads=cores)               # warm-up (tables, buffers)
-        r = rm.compute(types, pos, cell, pbc, nthreads=cores, repeats=3)
-        return {"value": r["seconds_median"] * 1e6 / len(types), "unit": "us/atom", "cores": cores, "kind": "reference",
-                "sample": f"{len(types)} atoms of the same alloy and model, median of 3 calls after the first, "
-                          f"neighbour search ({r['seconds_nlist'] * 1e6 / len(types):.2f} us/atom) not included",
-                "energy_eV_per_atom": r["energy"] / len(types)}
-    from oracle.grace_oracle import GraceOracle
-    types, pos, cell, pbc = structures.crystal(wl["lattice"], wl["a"], (4, 4, 4), n_species=wl["nsp"], sigma=wl["sigma"], seed=1)
-    o = GraceOracle(path)
-    t0 = time.perf_counter()
-    o.compute(species, types, pos, cell, pbc)
-    dt = time.perf_counter() - t0
-    return {"value": dt * 1e6 / len(types), "unit": "us/atom", "cores": 1, "kind": "port",
-            "sample": f"{len(types)} atoms, numpy fp64 restatement, one call"}
-
-
 def run_reference(args, rank, world):
+    """The reference's own CPU drivers (oracle/_ref) on the host cores: each step one evaluation of a bounded block
+    of the workload (same alloy, model and seeds), rank 0 only."""
     if rank != 0:
         return
     tmp = tempfile.mkdtemp(prefix="grace_bench_ref_")
@@ -484,17 +605,24 @@ def run_reference(args, rank, world):
     if "batch" in wl:
         print(json.dumps({"impl": "reference", "unavailable": "the reference arm times single structures; not wired for the batch workload"}))
         return
-    reps = wl["reps"]
-    if np.prod(reps) * (2 if wl["lattice"] == "bcc" else 4) > 32000:
-        reps = (20, 20, 40) if wl["lattice"] == "bcc" else (16, 16, 32)
+    reps = sample_reps(wl) or wl["reps"]
     path, species, types, pos, cell, pbc = make_workload(args.workload, tmp, reps)
     from oracle import refcpu
     cores = len(os.sched_getaffinity(0))
     n = len(types)
+    nl_us = None
     if not refcpu.available():
-        base = cpu_baseline(args, path, species, types, pos, cell, pbc, bounded=True)
-        value, kind, sample = base["value"], base["kind"], base["sample"]
-        ms = value * n / 1e3
+        from oracle.grace_oracle import GraceOracle
+        types, pos, cell, pbc = structures.crystal(wl["lattice"], wl["a"], (4, 4, 4), n_species=wl["nsp"], sigma=wl["sigma"], seed=1)
+        n = len(types)
+        o = GraceOracle(path)
+        t = []
+        for _ in range(max(1, min(args.steps, 3))):
+            t0 = time.perf_counter()
+            o.compute(species, types, pos, cell, pbc)
+            t.append(time.perf_counter() - t0)
+        ms, kind, cores = float(np.mean(t)) * 1e3, "port", 1
+        sample = f"{n} atoms, numpy fp64 restatement of the path"
     else:
         rm = refcpu.RefModel(path, species)
         for _ in range(max(1, min(args.warmup, 2))):
@@ -503,14 +631,17 @@ def run_reference(args, rank, world):
         for _ in range(args.steps):
             r = rm.compute(types, pos, cell, pbc, nthreads=cores)
             t.append(r["seconds_best"])
-        ms = float(np.mean(t)) * 1e3
-        value, kind = ms * 1e3 / n, "reference"
-        sample = f"{n} atoms of the same alloy and model per step (the reference's CPU drivers, neighbour search excluded)"
+            nl_us = r["seconds_nlist"] * 1e6 / n
+        ms, kind = float(np.mean(t)) * 1e3, "reference"
+        sample = (f"{n} atoms ({'x'.join(str(r) for r in reps)} cells) of the same alloy, model and seeds per step: the "
+                  "reference's CPU drivers, neighbour search excluded")
+    value = ms * 1e3 / n
     out = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-           "dtype": "f32", "data": "synthetic",
-           "config": {"workload": args.workload, "atoms": int(n), "model": "GRACE-1L" if wl["cfg"] == "1l" else "GRACE-2L"},
-           "cpu_baseline": {"value": value, "unit": "us/atom", "cores": cores, "kind": kind, "sample": sample},
+           "dtype": "f32", "data": "synthetic", "config": base_config(args.workload, world),
+           "sample_atoms": int(n),
+           "cpu_baseline": {"value": value, "unit": "us/atom", "cores": cores, "kind": kind, "sample": sample,
+                            "neighbor_search_us_per_atom": nl_us},
            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out))
 
@@ -523,7 +654,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--chunk", type=int, default=-1)
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and parity legs")
+    ap.add_argument("--no-also", action="store_true", help="skip the second workload reported beside the default one")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -35,6 +35,10 @@ SIGNATURES = {
     "grace_memory_info": (_I, [_P, _P]),
     "grace_debug_fail_alloc": (_I, [C.c_char_p, _I]),
     "grace_debug_fail_launch": (_I, [_I]),
+    "grace_measure_peak": (_I, [_I, _P]),
+    "grace_debug_track_alloc": (_I, [_I]),
+    "grace_debug_peak_alloc": (C.c_uint64, []),
+    "grace_debug_live_alloc": (_I, [_P, C.c_size_t]),
     "grace_last_error": (C.c_char_p, []),
     "grace_kernel_launches": (C.c_uint64, []),
     "grace_profile_enable": (_I, [_I]),
@@ -55,6 +59,7 @@ SIGNATURES = {
     "grace_system_compute": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "grace_system_compute_device": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "grace_system_set_owned": (_I, [_P, _I, _I]),
+    "grace_system_neighbor_list": (_I, [_P, _I64, _P, _P, _P, _P]),
     "grace_system_rebuilds": (_I64, [_P]),
     "grace_system_chunksize": (_I, [_P]),
     "grace_system_release_buffers": (_I, [_P]),
@@ -102,6 +107,15 @@ def _check(rc):
 
 def _ptr(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _len_of(a, name):
+    cai = getattr(a, "__cuda_array_interface__", None)
+    if cai is not None:
+        return int(cai["shape"][0])
+    if hasattr(a, "shape"):
+        return int(a.shape[0])
+    raise ValueError(f"{name}: the atom count must be given with raw device addresses")
 
 
 def _names(species):
@@ -185,6 +199,135 @@ def _debug_fail_alloc(label, nth):
 
 def _debug_fail_launch(nth):
     _check(load_library().grace_debug_fail_launch(int(nth)))
+
+
+def measure_peak(kind):
+    """TFLOP/s of a microbenchmark on the module's GPU: "fp32" (SIMT FMA lanes) or "tf32" (tcgen05 tensor cores)."""
+    v = C.c_double(0.0)
+    _check(load_library().grace_measure_peak({"fp32": 0, "tf32": 1}[kind], C.addressof(v)))
+    return v.value
+
+
+def _debug_track_alloc(on):
+    """From now on (True) every device allocation of the library is recorded by label; False stops and forgets."""
+    _check(load_library().grace_debug_track_alloc(int(bool(on))))
+
+
+def _debug_peak_alloc():
+    """High-water mark in bytes of the device allocations made since _debug_track_alloc(True)."""
+    return int(load_library().grace_debug_peak_alloc())
+
+
+def _debug_live_alloc():
+    """[(label, bytes)] of the tracked allocations still alive, largest first."""
+    buf = C.create_string_buffer(1 << 16)
+    _check(load_library().grace_debug_live_alloc(buf, len(buf)))
+    out = []
+    for line in buf.value.decode().splitlines():
+        name, b = line.rsplit("\t", 1)
+        out.append((name, int(b)))
+    return out
+
+
+# ---- device arrays -----------------------------------------------------------------------------------------------
+# The reference's compute_device takes DLPack arrays of the module's GPU "without implicit conversion: a converted
+# output would be a temporary copy (results lost), a converted input a hidden host -> device copy per call"
+# (python/kk/kk_module.cpp:142-197,258-266).  Here an argument may be an object with __cuda_array_interface__ (torch,
+# CuPy, numba), an object with __dlpack__ (its capsule is read with ctypes), or - an extension - a raw device address
+# as int.  Host arrays are refused with ValueError; nothing is ever copied or cast.
+_KDLCUDA = 2
+_TYPESTR = {np.dtype(np.float64): "<f8", np.dtype(np.int32): "<i4"}
+
+
+class _DLDevice(C.Structure):
+    _fields_ = [("device_type", C.c_int), ("device_id", C.c_int)]
+
+
+class _DLDataType(C.Structure):
+    _fields_ = [("code", C.c_uint8), ("bits", C.c_uint8), ("lanes", C.c_uint16)]
+
+
+class _DLTensor(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("device", _DLDevice), ("ndim", C.c_int), ("dtype", _DLDataType),
+                ("shape", C.POINTER(C.c_int64)), ("strides", C.POINTER(C.c_int64)), ("byte_offset", C.c_uint64)]
+
+
+class _DLManagedTensor(C.Structure):
+    pass
+
+
+_DLManagedTensor._fields_ = [("dl_tensor", _DLTensor), ("manager_ctx", C.c_void_p),
+                             ("deleter", C.CFUNCTYPE(None, C.POINTER(_DLManagedTensor)))]
+
+
+def _c_contiguous(shape, strides, itemsize, in_bytes):
+    if strides is None:
+        return True
+    want = itemsize if in_bytes else 1
+    for n, st in zip(reversed(shape), reversed(strides)):
+        if n > 1 and st != want:
+            return False
+        want *= max(n, 1)
+    return True
+
+
+def _from_dlpack(a, name, dtype, shape):
+    cap = a.__dlpack__()
+    api = C.pythonapi
+    api.PyCapsule_GetPointer.restype = C.c_void_p
+    api.PyCapsule_GetPointer.argtypes = [C.py_object, C.c_char_p]
+    api.PyCapsule_SetName.argtypes = [C.py_object, C.c_char_p]
+    p = api.PyCapsule_GetPointer(cap, b"dltensor")
+    if not p:
+        raise ValueError(f"{name}: not a DLPack capsule")
+    mt = C.cast(p, C.POINTER(_DLManagedTensor))
+    t = mt.contents.dl_tensor
+    try:
+        if t.device.device_type != _KDLCUDA or t.device.device_id != device():
+            raise ValueError(f"{name} must be on the module's GPU (cuda:{device()})")
+        code = {np.dtype(np.float64): (2, 64), np.dtype(np.int32): (0, 32)}[np.dtype(dtype)]
+        if (t.dtype.code, t.dtype.bits, t.dtype.lanes) != (code[0], code[1], 1):
+            raise ValueError(f"{name} must have dtype {np.dtype(dtype).name} (no conversion is made)")
+        shp = tuple(int(t.shape[k]) for k in range(t.ndim))
+        if shp != tuple(shape):
+            raise ValueError(f"{name}: wrong shape {shp}, expected {tuple(shape)}")
+        strides = None if not t.strides else tuple(int(t.strides[k]) for k in range(t.ndim))
+        if not _c_contiguous(shp, strides, 1, False):
+            raise ValueError(f"{name} must be C-contiguous")
+        return int(t.data or 0) + int(t.byte_offset)
+    finally:    # the capsule was consumed: run its deleter now; the producer `a` stays alive in the caller
+        api.PyCapsule_SetName(cap, b"used_dltensor")
+        if mt.contents.deleter:
+            mt.contents.deleter(mt)
+
+
+def _dev_ptr(a, name, dtype, shape, optional=False):
+    """Device address of `a` after the checks of the reference binding (device, dtype, shape, contiguity)."""
+    if a is None:
+        if optional:
+            return None
+        raise ValueError(f"{name} must be given")
+    if isinstance(a, (int, np.integer)):
+        if int(a) == 0 and optional:
+            return None
+        return C.c_void_p(int(a))
+    cai = getattr(a, "__cuda_array_interface__", None)
+    if cai is not None:
+        if cai.get("typestr") != _TYPESTR[np.dtype(dtype)]:
+            raise ValueError(f"{name} must have dtype {np.dtype(dtype).name} (no conversion is made)")
+        if tuple(cai["shape"]) != tuple(shape):
+            raise ValueError(f"{name}: wrong shape {tuple(cai['shape'])}, expected {tuple(shape)}")
+        if not _c_contiguous(tuple(cai["shape"]), cai.get("strides"), np.dtype(dtype).itemsize, True):
+            raise ValueError(f"{name} must be C-contiguous")
+        dv = getattr(a, "device", None)
+        idx = getattr(dv, "index", getattr(dv, "id", None))
+        if idx is not None and int(idx) != device():
+            raise ValueError(f"{name} must be on the module's GPU (cuda:{device()})")
+        return C.c_void_p(int(cai["data"][0]))
+    if hasattr(a, "__dlpack__") and not isinstance(a, np.ndarray):
+        return C.c_void_p(_from_dlpack(a, name, dtype, shape))
+    raise ValueError(f"{name} must be a device array of the module's GPU (DLPack / __cuda_array_interface__); host "
+                     "arrays are not converted")
 
 
 # ---- classes -----------------------------------------------------------------------------------------------------
@@ -318,16 +461,34 @@ class System:
             r["energies"] = ea
         return r
 
-    def compute_device(self, n, types_ptr, positions_ptr, cell, pbc, energy_ptr, forces_ptr=0, virial_ptr=0,
-                       energies_ptr=0, energy_only=False):
-        """Device pointers (integers) for types int32 [n], positions float64 [n, 3] and the float64 outputs."""
+    def compute_device(self, types, positions, cell, pbc, energy, forces=None, virial=None, energies=None,
+                       energy_only=False, n=None):
+        """Device inputs and outputs, no copies (an extension: the reference has compute_device on Batch only; same
+        argument rules): types int32 [n], positions float64 [n, 3], energy float64 [1], forces [n, 3], virial [6],
+        energies [n] on the module's GPU; cell and pbc on the host.  Raw device addresses (int) need `n`."""
+        if n is None:
+            n = _len_of(types, "types")
+        n = int(n)
         cell = _as(cell, np.float64, (3, 3))
         pbc = _as(np.asarray(pbc).astype(bool), np.uint8, (3,))
-        flags = (FLAG_ENERGIES if energies_ptr else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
-        _check(_lib.grace_system_compute_device(self._h, int(n), C.c_void_p(types_ptr), C.c_void_p(positions_ptr),
-                                                _ptr(cell), _ptr(pbc), flags, C.c_void_p(energy_ptr),
-                                                C.c_void_p(virial_ptr or None), C.c_void_p(forces_ptr or None),
-                                                C.c_void_p(energies_ptr or None)))
+        e = _dev_ptr(energy, "energy", np.float64, (1,))
+        f = _dev_ptr(forces, "forces", np.float64, (n, 3), optional=True)
+        v = _dev_ptr(virial, "virial", np.float64, (6,), optional=True)
+        ea = _dev_ptr(energies, "energies", np.float64, (n,), optional=True)
+        flags = (FLAG_ENERGIES if ea else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
+        _check(_lib.grace_system_compute_device(self._h, n, _dev_ptr(types, "types", np.int32, (n,)),
+                                                _dev_ptr(positions, "positions", np.float64, (n, 3)), _ptr(cell),
+                                                _ptr(pbc), flags, e, v, f, ea))
+
+    def neighbor_list(self):
+        """Diagnostics: the device neighbour list of the last build (radius cutoff + skin) as (i, j, S [nb, 3]) in the
+        caller's atom order; bond vector = x_j - x_i + S @ cell."""
+        cnt = C.c_int64(0)
+        _check(_lib.grace_system_neighbor_list(self._h, 0, None, None, None, C.addressof(cnt)))
+        nb = cnt.value
+        bi, bj, bs = np.zeros(nb, np.int32), np.zeros(nb, np.int32), np.zeros((nb, 3), np.int32)
+        _check(_lib.grace_system_neighbor_list(self._h, nb, _ptr(bi), _ptr(bj), _ptr(bs), C.addressof(cnt)))
+        return bi.astype(np.int64), bj.astype(np.int64), bs.astype(np.int64)
 
 
 class Batch:
@@ -395,14 +556,29 @@ class Batch:
             r["energies"] = ea
         return r
 
-    def compute_device(self, natoms, types_ptr, positions_ptr, cells, pbc, energy_ptr, forces_ptr=0, virial_ptr=0,
-                       energies_ptr=0, energy_only=False, max_nall=1 << 21):
+    def compute_device(self, natoms, types, positions, cells, pbc, energy, forces=None, virial=None, energies=None,
+                       gamma=None, atomic_sigma=None, gmm_cluster=None, energy_only=False, max_nall=1 << 21,
+                       dispersion_energy=None, dispersion_forces=None, dispersion_virial=None,
+                       dispersion_energies=None):
+        """Batch.compute_device of the reference (python/kk/kk_module.cpp:142-197,258-266): types int32 [N], positions
+        float64 [N, 3] and the float64 outputs energy [S], forces [N, 3], virial [S, 6], energies [N] on the module's
+        GPU, taken without conversion; natoms, cells, pbc on the host.  UQ and dispersion outputs are not part of this
+        backend: asking for one raises RuntimeError (unsupported)."""
         natoms = _as(natoms, np.int32)
         nsys = len(natoms)
+        ntot = int(natoms.sum())
+        if any(x is not None for x in (gamma, atomic_sigma, gmm_cluster)):
+            raise RuntimeError("the model has no UQ head usable by this backend")
+        if any(x is not None for x in (dispersion_energy, dispersion_forces, dispersion_virial, dispersion_energies)):
+            raise RuntimeError("dispersion corrections are not part of this backend")
         cells = _as(cells, np.float64, (nsys, 3, 3))
         pbc = _as(np.asarray(pbc).astype(bool), np.uint8, (nsys, 3))
-        flags = (FLAG_ENERGIES if energies_ptr else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
-        _check(_lib.grace_batch_compute_device(self._h, nsys, _ptr(natoms), int(natoms.sum()), C.c_void_p(types_ptr),
-                                               C.c_void_p(positions_ptr), _ptr(cells), _ptr(pbc), flags, int(max_nall),
-                                               C.c_void_p(energy_ptr), C.c_void_p(virial_ptr or None),
-                                               C.c_void_p(forces_ptr or None), C.c_void_p(energies_ptr or None)))
+        t = _dev_ptr(types, "types", np.int32, (ntot,))
+        x = _dev_ptr(positions, "positions", np.float64, (ntot, 3))
+        e = _dev_ptr(energy, "energy", np.float64, (nsys,))
+        f = _dev_ptr(forces, "forces", np.float64, (ntot, 3), optional=True)
+        v = _dev_ptr(virial, "virial", np.float64, (nsys, 6), optional=True)
+        ea = _dev_ptr(energies, "energies", np.float64, (ntot,), optional=True)
+        flags = (FLAG_ENERGIES if ea else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
+        _check(_lib.grace_batch_compute_device(self._h, nsys, _ptr(natoms), ntot, t, x, _ptr(cells), _ptr(pbc), flags,
+                                               int(max_nall), e, v, f, ea))

@@ -4,6 +4,7 @@
 #include "../../include/grace_b200.h"
 
 #include "engine.h"
+#include "peaks.h"
 
 #include <cstring>
 #include <mutex>
@@ -32,6 +33,9 @@ template<class F> int guarded(F &&f)
 {
   try {
     std::lock_guard<std::recursive_mutex> lk(g_device_mu);
+    // the current device is a per-thread setting of the CUDA runtime: a host thread other than the one that called
+    // grace_initialize would otherwise allocate and launch on device 0
+    if (dev().initialized) GB_CUDA(cudaSetDevice(dev().device));
     f();
     return GRACE_OK;
   } catch (const InvalidArgument &e) {
@@ -169,6 +173,39 @@ int grace_debug_fail_launch(int nth)
   return guarded([&] { dev().fail_launch_nth = nth > 0 ? nth : 0; });
 }
 
+int grace_measure_peak(int kind, double *tflops)
+{
+  return guarded([&] {
+    if (!tflops) throw InvalidArgument("tflops must be given");
+    if (kind == 0) *tflops = measure_peak_fp32_tflops();
+    else if (kind == 1) *tflops = measure_peak_tf32_tflops();
+    else throw InvalidArgument("kind must be 0 (fp32 FMA) or 1 (tf32 tensor cores)");
+  });
+}
+
+int grace_debug_track_alloc(int on)
+{
+  return guarded([&] { track_alloc(on != 0); });
+}
+
+uint64_t grace_debug_peak_alloc(void)
+{
+  std::lock_guard<std::recursive_mutex> lk(g_device_mu);
+  return (uint64_t) tracked_peak_bytes();
+}
+
+int grace_debug_live_alloc(char *buf, size_t len)
+{
+  return guarded([&] {
+    if (!buf || len == 0) throw InvalidArgument("buf must be given");
+    std::string r;
+    for (const auto &kv : tracked_live()) r += kv.first + "\t" + std::to_string(kv.second) + "\n";
+    const size_t n = std::min(len - 1, r.size());
+    std::memcpy(buf, r.data(), n);
+    buf[n] = 0;
+  });
+}
+
 int grace_model_load(const char *path, int spline, grace_model **out)
 {
   return guarded([&] {
@@ -195,7 +232,7 @@ double grace_model_dense_flops(const grace_model *m)
 {
   if (!m) return 0.0;
   std::lock_guard<std::mutex> lk(m->m->mu);
-  return m->m->engine ? m->m->engine->plan().dense_flops_per_atom : 0.0;
+  return m->m->engines.empty() ? 0.0 : m->m->engines.begin()->second->plan().dense_flops_per_atom;
 }
 int grace_model_radial_mlp_device(grace_model *m, int layer, int64_t nb, const float *d_x, float *d_R, float *d_dR)
 {
@@ -252,11 +289,7 @@ int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, 
 
 int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_out)
 {
-#ifndef GB_CPU_EMU
   return guarded([&] { static_sum(d_values, (long long) n, k, d_out); });
-#else
-  return guarded([&] { throw Unsupported("not part of the host-emulated build"); });
-#endif
 }
 
 int grace_system_set_owned(grace_system *s, int nlocal, int ninner)
@@ -265,6 +298,22 @@ int grace_system_set_owned(grace_system *s, int nlocal, int ninner)
     if (!s) throw InvalidArgument("system must be given");
     std::lock_guard<std::mutex> lk(s->s->mu);
     s->s->set_owned(nlocal, ninner);
+  });
+}
+
+int grace_system_neighbor_list(grace_system *s, int64_t capacity, int32_t *bi, int32_t *bj, int32_t *bS, int64_t *count)
+{
+  return guarded([&] {
+    if (!s || !count) throw InvalidArgument("system and count must be given");
+    if (!s->s->has_list()) throw InvalidArgument("the system has no neighbour list yet: call compute first");
+    std::vector<int> i, j, S;
+    s->s->neighbor_list().export_host(i, j, S);
+    *count = (int64_t) i.size();
+    if (capacity < (int64_t) i.size()) return;    // the caller asks again with room for `count` bonds
+    if (!i.empty() && (!bi || !bj || !bS)) throw InvalidArgument("output arrays must be given");
+    std::memcpy(bi, i.data(), sizeof(int) * i.size());
+    std::memcpy(bj, j.data(), sizeof(int) * j.size());
+    std::memcpy(bS, S.data(), sizeof(int) * S.size());
   });
 }
 

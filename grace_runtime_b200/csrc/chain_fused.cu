@@ -26,11 +26,7 @@ constexpr int NT = NTB / NG;              // threads of a group
 // barrier of the calling thread's group (named barrier 1 + group)
 __device__ __forceinline__ void group_sync()
 {
-#ifdef GB_CPU_EMU
-  emu_named_barrier(1 + (int) threadIdx.x / NT, NT);
-#else
   asm volatile("bar.sync %0, %1;" ::"r"(1 + (int) threadIdx.x / NT), "r"(NT) : "memory");
-#endif
 }
 __device__ __forceinline__ int gtid() { return (int) threadIdx.x % NT; }
 
@@ -589,13 +585,11 @@ __global__ void __launch_bounds__(NTB) chain_fused_kernel(FusedLayerDev L, Fused
 
 template<int TA> void launch_ta(const FusedLayerDev &L, const FusedIO &io, int grid, size_t smem)
 {
-#ifndef GB_CPU_EMU
   static size_t attr_smem = 48 * 1024;    // dynamic shared memory this instantiation may use so far
   if (smem > attr_smem) {
     GB_CUDA(cudaFuncSetAttribute(chain_fused_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     attr_smem = smem;
   }
-#endif
   GB_LAUNCH((chain_fused_kernel<TA>), grid, NTB, smem, L, io);
 }
 

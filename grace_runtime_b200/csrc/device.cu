@@ -1,5 +1,6 @@
 #include "device.h"
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -11,7 +12,30 @@ namespace {
 DeviceState g_dev;
 std::map<void *, size_t> g_live;
 size_t g_live_bytes = 0;
+// allocations made since track_alloc(true), by label, with their high-water mark: the reference's
+// _debug_track_alloc / _debug_live_alloc / _debug_peak_alloc (python/kk/kk_core.cpp:143-184)
+bool g_track = false;
+std::map<void *, std::pair<std::string, size_t>> g_tracked;
+size_t g_tracked_bytes = 0, g_tracked_peak = 0;
 }    // namespace
+
+void track_alloc(bool on)
+{
+  g_tracked.clear();
+  g_tracked_bytes = g_tracked_peak = 0;
+  g_track = on;
+}
+
+size_t tracked_peak_bytes() { return g_tracked_peak; }
+
+std::vector<std::pair<std::string, size_t>> tracked_live()
+{
+  std::map<std::string, size_t> by;
+  for (const auto &kv : g_tracked) by[kv.second.first] += kv.second.second;
+  std::vector<std::pair<std::string, size_t>> v(by.begin(), by.end());
+  std::sort(v.begin(), v.end(), [](const auto &a, const auto &b) { return a.second > b.second; });
+  return v;
+}
 
 DeviceState &dev() { return g_dev; }
 
@@ -104,6 +128,11 @@ void *device_alloc(size_t bytes, const char *label)
   }
   g_live[p] = bytes;
   g_live_bytes += bytes;
+  if (g_track) {
+    g_tracked[p] = {label ? label : "buffer", bytes};
+    g_tracked_bytes += bytes;
+    g_tracked_peak = std::max(g_tracked_peak, g_tracked_bytes);
+  }
   return p;
 }
 
@@ -114,6 +143,11 @@ void device_free(void *p)
   if (it != g_live.end()) {
     g_live_bytes -= it->second;
     g_live.erase(it);
+  }
+  auto tr = g_tracked.find(p);
+  if (tr != g_tracked.end()) {    // allocated before tracking started: not counted
+    g_tracked_bytes -= tr->second.second;
+    g_tracked.erase(tr);
   }
   if (g_dev.initialized) cudaFree(p);
 }

@@ -3,14 +3,13 @@
 // kernel launch macro with launch counting, and a stream-ordered event timer.
 #pragma once
 
-#ifndef GB_CPU_EMU
 #include <cuda_runtime.h>
-#endif
 
 #include <cstddef>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace gb {
@@ -55,7 +54,6 @@ void profile_enable(bool on);
 // "name launches total_ms" lines of the launches since profile_enable(true); synchronises the stream
 std::string profile_report();
 
-#ifndef GB_CPU_EMU
 // dynamic shared memory of a kernel as an array of T
 #define GB_DYN_SMEM(T, name) extern __shared__ T name[]
 #define GB_LAUNCH(kernel, grid, block, smem, ...)                                   \
@@ -64,7 +62,6 @@ std::string profile_report();
     kernel<<<(grid), (block), (smem), ::gb::dev().stream>>>(__VA_ARGS__);           \
     ::gb::after_launch(#kernel);                                                    \
   } while (0)
-#endif
 
 void *device_alloc(size_t bytes, const char *label);
 void device_free(void *p);
@@ -121,6 +118,11 @@ template<class T> class DBuf {
 
 // bytes currently allocated through device_alloc (diagnostics)
 size_t device_bytes_live();
+// allocation tracking of the reference's test interface (python/kk/kk_core.cpp:143-184): from track_alloc(true) on,
+// every device_alloc is recorded by label; live bytes by label (largest first) and their high-water mark
+void track_alloc(bool on);
+size_t tracked_peak_bytes();
+std::vector<std::pair<std::string, size_t>> tracked_live();
 
 // device time per stage of one compute call: pairs of CUDA events on the launch stream, summed per stage after the
 // call's synchronize (a stage may be entered once per chunk)

@@ -791,11 +791,18 @@ void ModelObj::radial_exact(int layer, const float *d_x, long long nb, float *d_
 std::shared_ptr<Engine> ModelObj::get_engine(int spline_n)
 {
   std::lock_guard<std::mutex> lk(mu);
-  if (!engine) {
-    engine = std::make_shared<Engine>(model, spline_n);
+  if (spline_n != 0 && spline_n < 16) throw InvalidArgument("spline N must be >= 16 (or 0: exact radial MLP)");
+  std::shared_ptr<Engine> &e = engines[spline_n];
+  if (!e) {
+    try {
+      e = std::make_shared<Engine>(model, spline_n);
+    } catch (...) {
+      engines.erase(spline_n);
+      throw;
+    }
     setups++;
   }
-  return engine;
+  return e;
 }
 
 // ---- system ----------------------------------------------------------------------------------------------------
@@ -832,7 +839,7 @@ SystemObj::SystemObj(std::shared_ptr<ModelObj> m, const std::vector<std::string>
   require_initialized();
   if (!(skin >= 0.0) || !std::isfinite(skin)) throw InvalidArgument("skin must be >= 0");
   t2m_ = species_to_elements(model_->model, species);
-  engine_ = model_->get_engine(spline > 0 ? spline : model_->spline);
+  engine_ = model_->get_engine(model_->effective_spline(spline));
   cutoff_ = 0.0;
   for (int a : t2m_)
     for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));
@@ -985,7 +992,7 @@ BatchObj::BatchObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &
 {
   require_initialized();
   t2m_ = species_to_elements(model_->model, species);
-  engine_ = model_->get_engine(spline > 0 ? spline : model_->spline);
+  engine_ = model_->get_engine(model_->effective_spline(spline));
   cutoff_ = 0.0;
   for (int a : t2m_)
     for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));

@@ -9,6 +9,7 @@
 #include "plan.h"
 #include "radial_mlp_tc.h"
 
+#include <map>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -114,9 +115,14 @@ struct ModelObj {
   std::string path;
   int spline = 1024;
   std::mutex mu;
-  std::shared_ptr<Engine> engine;    // created by the first System / Batch
+  // one engine per radial mode (table intervals, or 0: exact radial MLP), created by the first System / Batch that
+  // asks for it and shared by all of them (python/kk/kk_core.cpp:232,268-300 keeps one per (spline, chunksize); the
+  // pass size is an argument of every evaluation here, so the key is the spline alone)
+  std::map<int, std::shared_ptr<Engine>> engines;
   int64_t setups = 0;
   std::shared_ptr<Engine> get_engine(int spline_n);
+  // spline argument of a System / Batch: > 0 table intervals, 0 exact radial MLP, < 0 the value the model was loaded with
+  int effective_spline(int spline_arg) const { return spline_arg >= 0 ? spline_arg : spline; }
   // exact radial MLP of layer 1 or 2 on the tensor cores (set up by the first call)
   RadialMlpTC radial_tc[2];
   void radial_exact(int layer, const float *d_x, long long nb, float *d_R, float *d_dR);
@@ -146,6 +152,8 @@ class SystemObj {
   double stage_ms[StageTimer::NSTAGE] = {0, 0, 0, 0, 0};
   void release();
   std::mutex mu;
+  const NeighborList &neighbor_list() const { return nl_; }
+  bool has_list() const { return have_list_; }
 
  private:
   void compute_once(int n, const int *types, const double *pos, bool device_in, const double *cell,

@@ -547,6 +547,33 @@ BondsDev NeighborList::bonds() const
   return b;
 }
 
+void NeighborList::export_host(std::vector<int> &bi, std::vector<int> &bj, std::vector<int> &bS) const
+{
+  bi.clear(); bj.clear(); bS.clear();
+  if (n_ == 0 || nslots_ == 0) return;
+  cudaStream_t st = dev().stream;
+  std::vector<long long> off((size_t) n_ + 1);
+  std::vector<int> j((size_t) nslots_), S((size_t) nslots_), perm((size_t) n_), img(3 * (size_t) n_);
+  GB_CUDA(cudaMemcpyAsync(off.data(), off_.get(), sizeof(long long) * off.size(), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaMemcpyAsync(j.data(), nbr_j_.get(), sizeof(int) * j.size(), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaMemcpyAsync(S.data(), nbr_S_.get(), sizeof(int) * S.size(), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaMemcpyAsync(perm.data(), perm_.get(), sizeof(int) * perm.size(), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaMemcpyAsync(img.data(), img_s_.get(), sizeof(int) * img.size(), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaStreamSynchronize(st));
+  bi.reserve((size_t) nslots_); bj.reserve((size_t) nslots_); bS.reserve(3 * (size_t) nslots_);
+  for (int64_t q = 0; q < n_; q++)
+    for (long long e = off[(size_t) q]; e < off[(size_t) q + 1]; e++) {
+      const int p = j[(size_t) e];
+      bi.push_back(perm[(size_t) q]);
+      bj.push_back(perm[(size_t) p]);
+      // the list holds wrapped positions x - img cell: back in the caller's frame the shift is S - img_j + img_i
+      for (int k = 0; k < 3; k++) {
+        const int sk = (int) (signed char) ((S[(size_t) e] >> (8 * k)) & 0xff);
+        bS.push_back(sk - img[3 * (size_t) p + k] + img[3 * (size_t) q + k]);
+      }
+    }
+}
+
 void NeighborList::release()
 {
   frac_.release(); xs_.release(); xbuild_.release(); lohi_.release(); img_.release(); img_s_.release();

@@ -47,6 +47,9 @@ class NeighborList {
   int take_flag();
   void release();
   size_t bytes() const;
+  // diagnostics: the list of the last build (radius cutoff + skin) on the host, in the caller's atom order and frame:
+  // per slot the atoms i, j and the integer cell shift S [3] with bond vector x_j - x_i + S cell
+  void export_host(std::vector<int> &bi, std::vector<int> &bj, std::vector<int> &bS) const;
 
  private:
   int64_t n_ = 0, nslots_ = 0;

@@ -1,0 +1,13 @@
+// Measured compute peaks of the device (microbenchmarks, peaks.cu): the denominators of the compute-bound rooflines.
+#pragma once
+
+#include "device.h"
+
+namespace gb {
+
+// fp32 FMA rate of the SIMT lanes in TFLOP/s (2 flop per FMA), best of 3 launches after a warm-up launch
+double measure_peak_fp32_tflops();
+// tf32 tensor-core rate in TFLOP/s: tcgen05.mma kind::tf32 M = 128, N = 256, operands in shared memory
+double measure_peak_tf32_tflops();
+
+}    // namespace gb

@@ -33,7 +33,6 @@ constexpr long long WAIT_CYCLES = 40000000LL;    // ~20 ms: far beyond any tile,
 // byte offset of element (r, k) of a K-major operand tile with K columns (canonical layout, no swizzle)
 __host__ __device__ inline int tile_off(int r, int k, int K) { return (r >> 3) * (K >> 2) * 128 + (k >> 2) * 128 + (r & 7) * 16 + (k & 3) * 4; }
 
-#ifndef GB_CPU_EMU
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned) __cvta_generic_to_shared(p); }
 
 // shared-memory matrix descriptor: start address, leading (K direction) and stride (8-row group) byte offsets in
@@ -291,7 +290,6 @@ __global__ void __launch_bounds__(NTH, 1) radial_mlp_tc_kernel(RadialMlpTCDev m,
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
-#endif    // GB_CPU_EMU
 
 }    // namespace
 
@@ -368,16 +366,11 @@ void RadialMlpTC::run(const float *d_x, long long nb, float *d_R, float *d_dR)
 {
   if (!ready_) throw DeviceError("radial MLP kernel used before its set-up");
   if (nb <= 0) return;
-#ifdef GB_CPU_EMU
-  (void) d_x; (void) d_R; (void) d_dR;
-  throw Unsupported("the tensor-core radial MLP is not part of the host-emulated build");
-#else
   const size_t smem = smem_bytes(d_.n_out);
   GB_CUDA(cudaFuncSetAttribute(radial_mlp_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
   const long long ntiles = (nb + TB - 1) / TB;
   const int grid = (int) std::min<long long>(ntiles, dev().sm_count);
   GB_LAUNCH(radial_mlp_tc_kernel, grid, NTH, smem, d_, d_x, nb, d_R, d_dR, error_.get());
-#endif
 }
 
 void RadialMlpTC::check()

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(SS_THREADS) static_sum_kernel(const double *__
   __threadfence();
   for (int k = 0; k < K; k++) {
     double s = 0.0;
-    for (int b = t; b < B; b += SS_THREADS) s += partial[(size_t) b * SS_MAX_COLS + k];
+    for (int b = t; b < B; b += SS_THREADS) s += __ldcg(partial + (size_t) b * SS_MAX_COLS + k);    // written by other blocks: read past L1
     sh[t] = s;
     __syncthreads();
     for (int st = SS_THREADS / 2; st > 0; st >>= 1) {

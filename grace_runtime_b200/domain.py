@@ -207,8 +207,8 @@ class DistributedSystem:
                 self.d_f[:self.n].copy_(self.torch.from_numpy(np.asarray(f)))
             return
         ev = self.d_ev.data_ptr()
-        self.system.compute_device(self.n, self.d_types.data_ptr(), self.d_pos.data_ptr(), self.plan.sub_cell,
-                                   self.plan.sub_pbc, ev, self.d_f.data_ptr(), ev + 8)
+        self.system.compute_device(self.d_types.data_ptr(), self.d_pos.data_ptr(), self.plan.sub_cell,
+                                   self.plan.sub_pbc, ev, forces=self.d_f.data_ptr(), virial=ev + 8, n=self.n)
 
     def exchange(self):
         """ghost forces back to their owners, energy and virial summed over the ranks"""

@@ -61,6 +61,18 @@ int grace_memory_info(size_t *free_bytes, size_t *total_bytes);   /* memory_info
 int grace_debug_fail_alloc(const char *label, int nth);           /* debug_fail_alloc(label, nth) */
 /* tests: the nth kernel launch check from now on reports an out-of-memory launch (0: off) */
 int grace_debug_fail_launch(int nth);                             /* debug_fail_launch(nth) */
+/* Microbenchmarks of this device's compute peaks in TFLOP/s, the denominators of compute-bound rooflines: kind 0 the
+ * fp32 FMA rate of the SIMT lanes (register-only FFMA loop at full occupancy), kind 1 the tf32 rate of the tensor
+ * cores (tcgen05.mma kind::tf32, M = 128, N = 256, operands in shared memory).  A few milliseconds each.  Diagnostics;
+ * no counterpart in the reference. */
+int grace_measure_peak(int kind, double *tflops);
+/* _debug_track_alloc(on), _debug_peak_alloc(), _debug_live_alloc() (kk_module.cpp:221-224, kk_core.cpp:143-184): from
+ * track_alloc(1) on every device allocation of the library is recorded by label; peak = high-water mark in bytes of
+ * the allocations made since then (the reference's torch-sim adapter sizes its batches from it,
+ * python/grace_runtime/torchsim.py:143-148); live = "label<TAB>bytes" lines, largest first. */
+int grace_debug_track_alloc(int on);
+uint64_t grace_debug_peak_alloc(void);
+int grace_debug_live_alloc(char *buf, size_t len);
 const char *grace_last_error(void);            /* what() of the exception the reference would have thrown */
 /* kernels launched by this library since the process started (diagnostics; no counterpart in the reference) */
 uint64_t grace_kernel_launches(void);
@@ -105,7 +117,11 @@ int grace_model_radial_mlp_width(const grace_model *m, int layer);
 void grace_model_free(grace_model *m);
 
 /* ---- System (kk_api.h:68-90): one structure, neighbour list with a Verlet skin kept on the device ---- */
-/* chunksize: atoms per engine pass (0: all atoms in one pass; < 0: chosen from the free device memory) */
+/* spline: radial mode of this System, as the reference's System argument (kk_api.h:75; the reference ignores the
+ * Model's value, python/kk/kk_core.cpp:321): > 0 cubic Hermite tables with that many intervals (>= 16, default 1024);
+ * 0 the exact radial MLP per bond; < 0 the value the model was loaded with.  Systems and Batches of one model that ask
+ * for the same spline share one device engine; grace_model_engine_setups() counts the engines built.
+ * chunksize: atoms per engine pass (0: all atoms in one pass; < 0: chosen from the free device memory) */
 int grace_system_create(const grace_model *m, const char *const *species, int n_species, double skin, int spline,
                         int chunksize, grace_system **out);              /* System(model, species, skin, spline, chunk) */
 double grace_system_cutoff(const grace_system *s);                        /* cutoff() */
@@ -129,6 +145,11 @@ int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, 
  * (libgrace/include/grace/kk/grace_2l_kk.h:87-107) and of inum / ilist in its CPU drivers
  * (libgrace/include/grace/system.h:113-121); the plug-in interface kk_api.h itself is single-GPU. */
 int grace_system_set_owned(grace_system *s, int nlocal, int ninner);
+/* Diagnostics: the device neighbour list of the last build (radius cutoff + skin) copied to the host in the caller's
+ * atom order: per bond the atoms bi, bj and the integer cell shift bS [3] with bond vector x_j - x_i + S cell.  *count
+ * receives the number of bonds; nothing is written when capacity is smaller.  For bond-for-bond comparison with a CPU
+ * search as the reference's own test does (tests/kk/test_kk_neighbors.cpp:1-6). */
+int grace_system_neighbor_list(grace_system *s, int64_t capacity, int32_t *bi, int32_t *bj, int32_t *bS, int64_t *count);
 int64_t grace_system_rebuilds(const grace_system *s);                     /* rebuilds() */
 int grace_system_chunksize(const grace_system *s);                        /* chunksize() */
 int grace_system_release_buffers(grace_system *s);                        /* release_device_buffers() */

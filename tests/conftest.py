@@ -15,7 +15,7 @@ F32_MODELS = ["grace_1l_small", "grace_2l_small", "grace_1l_w48", "grace_2l_l3",
 TF_CELLS = ["W54", "WMo54", "W2tri"]
 EXTRA_CELLS = ["cluster13", "slab36", "tri9", "atom1"]
 
-# tolerances of BASELINE.json's north star (energy eV/atom, forces eV/A, stress eV/A^3); the golden comparisons use
+# target tolerances of the build (energy eV/atom, forces eV/A, stress eV/A^3); the golden comparisons use
 # the reference's own tighter fp32-vs-fp64 thresholds (python/tests/test_ref_tf.py:22)
 TOL_E, TOL_F, TOL_S = 1e-5, 1e-4, 1e-4
 REF_TOL = {"energy": 1e-6, "forces": 2e-5, "energies": 1e-5, "stress": 1e-5}

@@ -99,3 +99,33 @@ def test_no_compute_without_a_device(B):
 def test_order3_file_has_no_order4_arrays():
     z = np.load(model_path("grace_1l_order3"))
     assert not any("AAAA" in k for k in z.files)
+
+
+class _FakeDeviceArray:
+    """stands in for a torch / CuPy array: only the attributes the binding reads"""
+
+    def __init__(self, shape, typestr, strides=None, ptr=0x7f0000000000):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False),
+                                         "strides": strides, "version": 3}
+
+
+def test_device_array_arguments_are_checked_not_converted(B):
+    """argument rules of the reference's compute_device (python/kk/kk_module.cpp:142-197, `noconvert`): the binding
+    takes the address of a device array as it is, or refuses it"""
+    import torch
+    ok = _FakeDeviceArray((5, 3), "<f8")
+    assert B._dev_ptr(ok, "positions", np.float64, (5, 3)).value == 0x7f0000000000
+    assert B._dev_ptr(_FakeDeviceArray((5, 3), "<f8", strides=(24, 8)), "positions", np.float64, (5, 3)).value
+    with pytest.raises(ValueError, match="dtype"):
+        B._dev_ptr(_FakeDeviceArray((5, 3), "<f4"), "positions", np.float64, (5, 3))
+    with pytest.raises(ValueError, match="shape"):
+        B._dev_ptr(_FakeDeviceArray((5, 2), "<f8"), "positions", np.float64, (5, 3))
+    with pytest.raises(ValueError, match="contiguous"):
+        B._dev_ptr(_FakeDeviceArray((5, 3), "<f8", strides=(48, 8)), "positions", np.float64, (5, 3))
+    with pytest.raises(ValueError, match="device array"):
+        B._dev_ptr(np.zeros((5, 3)), "positions", np.float64, (5, 3))
+    with pytest.raises(ValueError, match="GPU"):       # a DLPack producer on the host
+        B._dev_ptr(torch.zeros((5, 3), dtype=torch.float64), "positions", np.float64, (5, 3))
+    assert B._dev_ptr(None, "forces", np.float64, (5, 3), optional=True) is None
+    with pytest.raises(ValueError):
+        B._dev_ptr(None, "energy", np.float64, (1,))

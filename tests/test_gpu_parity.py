@@ -296,3 +296,161 @@ def test_injected_failures_recover(backend, models, cells, tmp_path_factory):
         backend._debug_fail_alloc("", 0)
     rf = sf.compute(big["types"], big["positions"], big["cell"], big["pbc"])
     assert np.abs(rf["forces"] - ref["forces"]).max() < 2e-5
+
+
+# ---- the benchmark configurations at (or near) their stated sizes, against the compiled reference live -----------
+@pytest.mark.parametrize("cfg,lattice,a,reps,nsp,sigma,full", [
+    ("1l", "bcc", 3.165, (10, 10, 10), 1, 0.05, False),     # configuration 1 as stated: 2,000 atoms of bcc W
+    ("1l", "bcc", 3.2, (20, 20, 20), 4, 0.05, True),        # a 16,000-atom block of configuration 2 (89-element model)
+    ("2l", "fcc", 3.6, (13, 13, 13), 3, 0.08, True),        # an 8,788-atom block of configuration 3 (89-element model)
+])
+def test_stated_configurations_match_compiled_reference(backend, tmp_path_factory, cfg, lattice, a, reps, nsp, sigma, full):
+    """energy, forces, stress and per-atom energies of the benchmark workloads themselves (same model generator, same
+    structure generator, same seeds as bench.py) against the reference's CPU drivers, within the stated tolerances"""
+    from grace_runtime_b200 import modelgen, structures
+    from oracle import refcpu
+    if not refcpu.available():
+        pytest.skip("oracle/_ref is not built")
+    species = modelgen._subset(2024, nsp) if full else ["W"]
+    elements = modelgen.ELEMENTS if full else species
+    path = modelgen.write_config_model(str(tmp_path_factory.mktemp("stated") / f"{cfg}.npz"), cfg, elements, seed=0)
+    types, pos, cell, pbc = structures.crystal(lattice, a, reps, n_species=nsp, sigma=sigma, seed=1)
+    n, vol = len(types), abs(np.linalg.det(cell))
+    r = backend.System(backend.Model(path), species).compute(types, pos, cell, pbc, energies=True)
+    ref = refcpu.RefModel(path, species).compute(types, pos, cell, pbc, nthreads=0)
+    assert abs(r["energy"] - ref["energy"]) / n < TOL_E
+    assert np.abs(r["forces"] - ref["forces"]).max() < TOL_F
+    assert np.abs(r["virial"] - ref["virial"]).max() / vol < TOL_S
+    assert np.abs(r["energies"] - ref["energies"]).max() < TOL_E
+
+
+@pytest.mark.parametrize("cell", TF_CELLS + ["slab36", "tri9", "cluster13"])
+def test_device_neighbor_list_equals_cpu_search(backend, models, cells, cell):
+    """the device list bond for bond against the CPU cell-list search, as the reference checks its own device list
+    (tests/kk/test_kk_neighbors.cpp:1-6): same (i, j, cell shift) multiset at radius cutoff + skin"""
+    from oracle.grace_oracle import neighbor_list
+    c = cells.get(cell)
+    s = backend.System(_model(backend, models, "grace_1l_order3"), c["species"], skin=0.5)
+    s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    bi, bj, bs = s.neighbor_list()
+    a = neighbor_list(c["positions"], c["cell"], c["pbc"], s.cutoff + 0.5)
+    got = sorted(zip(bi.tolist(), bj.tolist(), map(tuple, bs.tolist())))
+    want = sorted(zip(a[0].tolist(), a[1].tolist(), map(tuple, a[2].tolist())))
+    assert len(got) == len(want) and got == want
+
+
+def test_device_neighbor_list_equals_reference_search_large(backend, tmp_path_factory):
+    """the same on 2,000 displaced bcc atoms against the reference's own search (python/src/neighbors.cpp)"""
+    from oracle import refcpu
+    if not refcpu.available():
+        pytest.skip("oracle/_ref is not built")
+    path, els, c = _config_case(tmp_path_factory, "1l", "bcc", 3.165, (10, 10, 10), 1, 0.05, seed=3)
+    s = backend.System(backend.Model(path), els, skin=0.5)
+    s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    bi, bj, bs = s.neighbor_list()
+    ri, rj, rs = refcpu.neighbors(c["positions"], c["cell"], c["pbc"], s.cutoff + 0.5)
+    key = lambda i, j, S: np.lexsort((S[:, 2], S[:, 1], S[:, 0], j, i))
+    ka, kb = key(bi, bj, bs), key(ri, rj, rs)
+    assert len(bi) == len(ri)
+    assert np.array_equal(bi[ka], ri[kb]) and np.array_equal(bj[ka], rj[kb]) and np.array_equal(bs[ka], rs[kb])
+
+
+def test_one_engine_per_spline(backend, cells):
+    """Systems of one model share an engine per radial mode (python/kk/kk_core.cpp:232,268-300; engine_setups counts
+    them): the same spline reuses it, another resolution builds a second one whose energy differs at table-error
+    level"""
+    c = cells.get("WMo54")
+    m = backend.Model(model_path("grace_1l_order3"))
+    a = backend.System(m, c["species"], spline=1024).compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    assert m.engine_setups == 1
+    a2 = backend.System(m, c["species"], spline=1024).compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    assert m.engine_setups == 1 and a2["energy"] == a["energy"]
+    b = backend.System(m, c["species"], spline=64).compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    assert m.engine_setups == 2
+    d = abs(a["energy"] - b["energy"]) / c["n"]
+    assert 0.0 < d < 1e-3, d
+    with pytest.raises(ValueError):
+        backend.System(m, c["species"], spline=8)
+
+
+def test_calls_from_a_second_host_thread(backend, models, cells):
+    """any host thread may call (python/kk/kk_core.cpp:58-63): the current CUDA device is a per-thread setting, which
+    the library sets itself"""
+    import threading
+    import torch
+    c = cells.get("W54")
+    m = _model(backend, models, "grace_2l_order3")
+    want = _compute(backend, m, c)
+    got = {}
+
+    def work():
+        try:
+            got["r"] = _compute(backend, m, c)
+            v = torch.arange(12, dtype=torch.float64, device="cuda:0").reshape(4, 3)
+            out = torch.zeros(3, dtype=torch.float64, device="cuda:0")
+            backend.sum_rows_static(v.data_ptr(), 4, 3, out.data_ptr())
+            got["s"] = out.cpu().numpy()
+        except Exception as e:      # surfaced by the assert below
+            got["err"] = e
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "err" not in got, got.get("err")
+    assert got["r"]["energy"] == want["energy"]
+    assert np.abs(got["r"]["forces"] - want["forces"]).max() < 1e-6
+    assert np.array_equal(got["s"], np.array([18.0, 22.0, 26.0]))
+
+
+def test_compute_device_takes_device_arrays_without_conversion(backend, models, cells):
+    """Batch.compute_device with torch tensors of the GPU (python/kk/kk_module.cpp:142-197): results equal compute();
+    host arrays, wrong dtypes and wrong shapes are ValueErrors, nothing is converted"""
+    import torch
+    c = cells.get("WMo54")
+    m = _model(backend, models, "grace_2l_order3")
+    b = backend.Batch(m, c["species"])
+    natoms = np.array([c["n"], c["n"]], dtype=np.int32)
+    types = np.concatenate([c["types"], c["types"]]).astype(np.int32)
+    pos = np.concatenate([c["positions"], c["positions"] + 0.01])
+    cells2 = np.stack([c["cell"], c["cell"]])
+    pbc2 = np.stack([c["pbc"], c["pbc"]])
+    want = b.compute(natoms, types, pos, cells2, pbc2, energies=True)
+    dev = torch.device("cuda", 0)
+    d_t, d_x = torch.from_numpy(types).to(dev), torch.from_numpy(pos).to(dev)
+    e = torch.zeros(2, dtype=torch.float64, device=dev)
+    f = torch.zeros((2 * c["n"], 3), dtype=torch.float64, device=dev)
+    v = torch.zeros((2, 6), dtype=torch.float64, device=dev)
+    ea = torch.zeros(2 * c["n"], dtype=torch.float64, device=dev)
+    b.compute_device(natoms, d_t, d_x, cells2, pbc2, e, forces=f, virial=v, energies=ea)
+    assert np.abs(e.cpu().numpy() - want["energy"]).max() < 1e-9
+    assert np.abs(f.cpu().numpy() - want["forces"]).max() < 1e-6
+    assert np.abs(v.cpu().numpy() - want["virial"]).max() < 1e-6
+    assert np.abs(ea.cpu().numpy() - want["energies"]).max() < 1e-9
+    with pytest.raises(ValueError):
+        b.compute_device(natoms, types, d_x, cells2, pbc2, e)                       # host types
+    with pytest.raises(ValueError):
+        b.compute_device(natoms, d_t, d_x.float(), cells2, pbc2, e)                 # float32 positions
+    with pytest.raises(ValueError):
+        b.compute_device(natoms, d_t, d_x, cells2, pbc2, e, forces=f[:, :2])        # wrong shape / not contiguous
+    with pytest.raises(ValueError):
+        b.compute_device(natoms, d_t, d_x, cells2, pbc2, e.cpu())                   # host output
+    with pytest.raises(RuntimeError):
+        b.compute_device(natoms, d_t, d_x, cells2, pbc2, e, gamma=ea)               # no UQ head
+
+
+def test_allocation_tracking(backend, models, cells):
+    """_debug_track_alloc / _debug_peak_alloc / _debug_live_alloc (python/kk/kk_core.cpp:143-184)"""
+    c = cells.get("W54")
+    m = _model(backend, models, "grace_1l_order3")
+    s = backend.System(m, c["species"])
+    s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+    s.release_buffers()
+    backend._debug_track_alloc(True)
+    try:
+        s.compute(c["types"], c["positions"], c["cell"], c["pbc"])
+        peak = backend._debug_peak_alloc()
+        live = backend._debug_live_alloc()
+    finally:
+        backend._debug_track_alloc(False)
+    assert peak > 0 and live and sum(b for _, b in live) <= peak
+    assert backend._debug_peak_alloc() == 0
