@@ -33,7 +33,8 @@ def sources():
 
 
 def _compile(src, obj, verbose):
-    cmd = [nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
+    extra = os.environ.get("GRACE_B200_NVCC_FLAGS", "").split()    # e.g. -D switches of a diagnostic build
+    cmd = [nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     return src, r.returncode, r.stdout + r.stderr
 

@@ -5,6 +5,8 @@
 #include "kernels.h"
 #include "readout.cuh"
 
+#include <algorithm>
+
 namespace gb {
 
 // ---- MV: out[row][a][k] (+)= sum_items scale * sum_n M[n][k] x[item][a][n] ----------------------------------
@@ -66,9 +68,120 @@ __global__ void __launch_bounds__(128) mv_kernel(MVDev op, const TensorDev *__re
   }
 }
 
+// Per-element weights (reduces over the central atom's element and their adjoints) for a tile of atoms: the weight
+// matrices of the elements present in the tile are staged in shared memory item by item, so a weight is fetched from
+// global memory once per tile and element instead of once per atom; a thread owns 4 output channels of one atom and
+// reads its activations with loads the other threads of the atom share.  Same summation order as mv_kernel.
+constexpr int ELEM_MAXS = 4;    // elements staged at a time (tiles with more run the items once more per group)
+constexpr int ELEM_GROUP = 4;   // items whose weights are staged together
+__global__ void __launch_bounds__(256) mv_elem_tile_kernel(MVDev op, const TensorDev *__restrict__ T,
+                                                           const int *__restrict__ mu, int NA, int na, int TA, int KQ,
+                                                           int n_in_max)
+{
+  extern __shared__ __align__(16) float wsm[];    // [ELEM_GROUP][ELEM_MAXS][n_in_max][ldw]
+  __shared__ int s_slot[128], s_el[128], s_nsp;
+  const int row = blockIdx.y, a0 = blockIdx.x * TA, nta = min(TA, na - a0), t = threadIdx.x;
+  const int p = t / KQ, kq = t - p * KQ, ld = op.ldw, ld4 = ld >> 2;
+  const bool active = p < nta;
+  __shared__ int s_mu[128];
+  if (t < nta) s_mu[t] = mu[a0 + t];
+  __syncthreads();
+  if (t == 0) {    // distinct elements of the tile, in order of first appearance
+    int ns = 0;
+    for (int a = 0; a < nta; a++) {
+      const int e = s_mu[a];
+      int s = 0;
+      while (s < ns && s_el[s] != e) s++;
+      if (s == ns) s_el[ns++] = e;
+      s_slot[a] = s;
+    }
+    s_nsp = ns;
+  }
+  __syncthreads();
+  const int nsp = s_nsp, slot = active ? s_slot[p] : -1;
+  const int i0 = op.item_off[row], i1 = op.item_off[row + 1];
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 *w4 = reinterpret_cast<const float4 *>(wsm);
+  const int wstride = n_in_max * ld4;    // float4 per (item of the group, element)
+  for (int s0 = 0; s0 < nsp; s0 += ELEM_MAXS) {
+    const int ng = min(ELEM_MAXS, nsp - s0);
+    for (int it0 = i0; it0 < i1; it0 += ELEM_GROUP) {    // the weights of a group of items are staged together
+      const int nit = min(ELEM_GROUP, i1 - it0);
+      __syncthreads();    // the weights of the previous group are no longer read
+      for (int g = 0; g < nit; g++) {
+        const MVItem item = op.items[it0 + g];
+        const int per = item.n_in * ld4;
+        for (int q = t; q < ng * per; q += 256) {
+          const int s = q / per, r = q - s * per;
+          reinterpret_cast<float4 *>(wsm)[(size_t) (g * ELEM_MAXS + s) * wstride + r] =
+              __ldg(reinterpret_cast<const float4 *>(op.W + (size_t) s_el[s0 + s] * op.ty_stride + item.mat) + r);
+        }
+      }
+      __syncthreads();
+      if (slot >= s0 && slot < s0 + ng) {
+        for (int g = 0; g < nit; g++) {
+          const MVItem item = op.items[it0 + g];
+          const TensorDev src = T[item.src];
+          const float *x = src.p + ((size_t) item.irow * NA + a0 + p) * src.C;
+          const float4 *w = w4 + (size_t) (g * ELEM_MAXS + slot - s0) * wstride + kq;
+          float4 part = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (((src.C | item.n_in) & 3) == 0) {    // 16-byte activation loads, eight of them in flight
+            for (int n0 = 0; n0 < item.n_in; n0 += 32) {
+              float4 xv[8];
+#pragma unroll
+              for (int j = 0; j < 8; j++)
+                xv[j] = n0 + 4 * j < item.n_in ? __ldg(reinterpret_cast<const float4 *>(x + n0) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                if (n0 + 4 * j < item.n_in) {
+                  const float xs[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+#pragma unroll
+                  for (int q = 0; q < 4; q++) {
+                    const float4 wv = w[(size_t) (n0 + 4 * j + q) * ld4];
+                    part.x = fmaf(xs[q], wv.x, part.x); part.y = fmaf(xs[q], wv.y, part.y);
+                    part.z = fmaf(xs[q], wv.z, part.z); part.w = fmaf(xs[q], wv.w, part.w);
+                  }
+                }
+              }
+            }
+          } else {
+            for (int n = 0; n < item.n_in; n++) {
+              const float xv = __ldg(x + n);
+              const float4 wv = w[(size_t) n * ld4];
+              part.x = fmaf(xv, wv.x, part.x); part.y = fmaf(xv, wv.y, part.y);
+              part.z = fmaf(xv, wv.z, part.z); part.w = fmaf(xv, wv.w, part.w);
+            }
+          }
+          acc.x = fmaf(item.scale, part.x, acc.x); acc.y = fmaf(item.scale, part.y, acc.y);
+          acc.z = fmaf(item.scale, part.z, acc.z); acc.w = fmaf(item.scale, part.w, acc.w);
+        }
+      }
+    }
+  }
+  if (!active) return;
+  const TensorDev dst = T[op.dst];
+  float *o = dst.p + ((size_t) op.row_out[row] * NA + a0 + p) * dst.C + 4 * kq;
+  const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+  const int nk = min(4, op.n_out - 4 * kq);
+  for (int q = 0; q < nk; q++) o[q] = op.accumulate ? o[q] + v[q] : v[q];
+}
+
 void launch_mv(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na)
 {
   if (op.nrows == 0 || na == 0) return;
+  if (op.elem && (op.ldw & 3) == 0 && (op.ty_stride & 3) == 0 && op.unit_nmax > 0) {
+    const int KQ = op.ldw >> 2, TA = std::min(128, 256 / KQ);
+    const size_t smem = (size_t) ELEM_GROUP * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float);
+    if (KQ <= 64 && smem <= 96 * 1024) {
+      static bool attr = false;    // static shared memory counts against the 48 KB a kernel gets without the attribute
+      if (!attr && smem > 32 * 1024) {
+        GB_CUDA(cudaFuncSetAttribute(mv_elem_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        attr = true;
+      }
+      GB_LAUNCH(mv_elem_tile_kernel, dim3((na + TA - 1) / TA, op.nrows), 256, smem, op, tensors, mu, NA, na, TA, KQ, op.unit_nmax);
+      return;
+    }
+  }
   int KP = 8;
   while (KP < op.n_out) KP *= 2;
   if (KP > 128) throw Unsupported("dense network: more than 128 channels are not supported");
@@ -105,9 +218,103 @@ __global__ void __launch_bounds__(256) prod_kernel(ProdDev op, const TensorDev *
   *o = op.accumulate ? *o + acc : acc;
 }
 
-void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, int C)
+// The same for a tile of TA atoms with the input rows staged in shared memory: every input value comes from global
+// memory once (coalesced, TA x C contiguous floats per function) however many terms read it, and the term loop runs on
+// shared memory.  srcB == srcA or srcB < 0: one staged tensor.
+__global__ void __launch_bounds__(256) prod_tile_kernel(ProdDev op, const TensorDev *__restrict__ T, int NA, int na, int TA,
+                                                        int nfA, int nfB, int C, int nterms)
+{
+  extern __shared__ __align__(16) float psm[];
+  const int C4 = C >> 2, TAC4 = TA * C4, t = threadIdx.x;
+  const int a0 = blockIdx.x * TA, nta = min(TA, na - a0);
+  float4 *sA = reinterpret_cast<float4 *>(psm);
+  float4 *sB = sA + (size_t) nfA * TAC4;
+  ProdTerm *sT = reinterpret_cast<ProdTerm *>(sB + (size_t) nfB * TAC4);
+  const bool two = op.srcB >= 0 && op.srcB != op.srcA;
+  {
+    // eight independent 16-byte loads per thread in flight: the tile's rows come from nf separate regions of the
+    // tensor, and a CTA has nothing else to do until they are there
+    auto stage = [&](const float *G, float4 *S, int nf) {
+      const int total = nf * TAC4;
+      for (int base = 0; base < total; base += 256 * 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int idx = base + j * 256 + t, f = idx / TAC4, r = idx - f * TAC4;
+          v[j] = (idx < total && r / C4 < nta) ? __ldg(reinterpret_cast<const float4 *>(G + ((size_t) f * NA + a0) * C) + r)
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int idx = base + j * 256 + t;
+          if (idx < total) S[idx] = v[j];
+        }
+      }
+    };
+    stage(T[op.srcA].p, sA, nfA);
+    if (two) stage(T[op.srcB].p, sB, nfB);
+    for (int idx = t; idx < nterms; idx += 256) sT[idx] = op.terms[idx];
+  }
+  __syncthreads();
+  const float4 *Bs = op.srcB < 0 ? nullptr : (two ? sB : sA);
+  float *D = T[op.dst].p;
+  const int nvalid = nta * C4, warp = t >> 5, lane = t & 31;
+  // a warp takes an output row and walks its TA x C values 32 float4 at a time: the term loop is uniform in the warp
+  // and a term is one broadcast read
+  for (int row = warp; row < op.nrows; row += 8) {
+    const int t0 = op.term_off[row], t1 = op.term_off[row + 1];
+    float4 *orow = reinterpret_cast<float4 *>(D + ((size_t) op.row_out[row] * NA + a0) * C);
+    for (int r = lane; r < nvalid; r += 32) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (Bs) {
+        for (int q = t0; q < t1; q++) {
+          const ProdTerm tm = sT[q];
+          const float4 av = sA[tm.a * TAC4 + r], bv = Bs[tm.b * TAC4 + r];
+          acc.x = fmaf(tm.coef * av.x, bv.x, acc.x); acc.y = fmaf(tm.coef * av.y, bv.y, acc.y);
+          acc.z = fmaf(tm.coef * av.z, bv.z, acc.z); acc.w = fmaf(tm.coef * av.w, bv.w, acc.w);
+        }
+      } else {
+        for (int q = t0; q < t1; q++) {
+          const ProdTerm tm = sT[q];
+          const float4 av = sA[tm.a * TAC4 + r];
+          acc.x = fmaf(tm.coef, av.x, acc.x); acc.y = fmaf(tm.coef, av.y, acc.y);
+          acc.z = fmaf(tm.coef, av.z, acc.z); acc.w = fmaf(tm.coef, av.w, acc.w);
+        }
+      }
+      if (op.accumulate) {
+        const float4 old = orow[r];
+        acc.x += old.x; acc.y += old.y; acc.z += old.z; acc.w += old.w;
+      }
+      orow[r] = acc;
+    }
+  }
+}
+
+void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, int C, int nfA, int nfB, int nterms)
 {
   if (op.nrows == 0 || na == 0) return;
+  // tiled form: channels a multiple of 4 and at least one atom of input rows in shared memory
+  if ((C & 3) == 0 && nfA > 0) {
+    const bool two = op.srcB >= 0 && op.srcB != op.srcA;
+    const size_t per_atom = (size_t) (nfA + (two ? nfB : 0)) * C * 4, fixed = (size_t) nterms * sizeof(ProdTerm) + 64;
+    // several CTAs per SM (the load, compute and store phases of a tile overlap only across CTAs): a quarter of the
+    // shared memory when that holds 4+ atoms, else half, else all of it
+    const size_t quarter = 54 * 1024, half = 110 * 1024, large = 200 * 1024;
+    size_t budget = quarter;
+    if (fixed + 4 * per_atom > quarter) budget = half;
+    if (fixed + 4 * per_atom > half) budget = large;
+    int TA = fixed < budget ? (int) std::min<size_t>(32, (budget - fixed) / per_atom) : 0;
+    if (TA >= 1) {
+      const size_t smem = fixed + (size_t) TA * per_atom;
+      static size_t attr = 48 * 1024;
+      if (smem > attr) {
+        GB_CUDA(cudaFuncSetAttribute(prod_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) large));
+        attr = large;
+      }
+      GB_LAUNCH(prod_tile_kernel, (na + TA - 1) / TA, 256, smem, op, tensors, NA, na, TA, nfA, two ? nfB : 0, C, nterms);
+      return;
+    }
+  }
   const long long row_len = (long long) NA * C, act_len = (long long) na * C;
   const dim3 grid(op.nrows, (unsigned) ((act_len + 255) / 256));
   GB_LAUNCH(prod_kernel, grid, 256, 0, op, tensors, row_len, act_len);

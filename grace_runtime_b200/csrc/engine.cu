@@ -156,6 +156,21 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
     d.srcB = o.srcB;
     E.prod.push_back(d);
   }
+  // tensor-core form of the operations with shared weights
+  {
+    double covered = 0.0, all = 0.0;
+    E.mv_tc.clear();
+    E.mv_tc.resize(P.mv.size());
+    for (size_t q = 0; q < P.mv.size(); q++) {
+      const double fl = P.mv[q].flops_per_atom();
+      all += fl;
+      if (MVTensorCore::eligible(P.mv[q], P.tensors)) {
+        E.mv_tc[q].setup(P.mv[q]);
+        covered += fl;
+      }
+    }
+    E.tc_flop_share = all > 0.0 ? covered / all : 0.0;
+  }
   // tensors: values first, then the gradients that are zeroed per chunk (one contiguous range)
   E.toff.assign(P.tensors.size(), 0);
   long long at = 0;
@@ -241,14 +256,37 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   r.nrho = P.nrho;
   r.out_scale = P.out_scale;
   if (getenv("GRACE_B200_NO_FUSED")) fused_ = false;    // the per-operation kernels, for comparison
+  if (const char *env = getenv("GRACE_B200_DENSE")) {
+    const std::string v = env;
+    dense_ = v == "fused" ? Dense::Fused : v == "tc" ? Dense::Tc : v == "ops" ? Dense::Ops : Dense::Auto;
+  }
+  if (const char *env = getenv("GRACE_B200_TC_MIN_ATOMS")) tc_min_atoms_ = std::max(1, atoi(env));
+  // the tensor-core path pays when it covers most of the MV work of every layer
+  tc_ready_ = L1_.tc_flop_share > 0.5 && (P.layers == 1 || L2_.tc_flop_share > 0.5);
+  tc_error_.set_label("engine:flag");
+  tc_error_.ensure(1);
+  GB_CUDA(cudaMemsetAsync(tc_error_.get(), 0, sizeof(int), dev().stream));
   GB_CUDA(cudaStreamSynchronize(dev().stream));    // the uploads read host vectors of this scope
 }
 
 Engine::~Engine() = default;
 
-double Engine::per_atom_bytes() const
+bool Engine::use_tc(int64_t n_eval) const
 {
-  if (fused_) return 8.0 * (double) std::max(L1_.q_floats, L2_.q_floats);
+  if (!tc_ready_ || dense_ == Dense::Fused || dense_ == Dense::Ops) return false;
+  if (dense_ == Dense::Tc) return true;
+  return n_eval >= tc_min_atoms_ || !fused_;
+}
+
+bool Engine::use_fused(int64_t n_eval) const
+{
+  if (!fused_ || dense_ == Dense::Ops) return false;
+  return !use_tc(n_eval);
+}
+
+double Engine::per_atom_bytes(int64_t n_eval) const
+{
+  if (use_fused(n_eval)) return 8.0 * (double) std::max(L1_.q_floats, L2_.q_floats);
   return 4.0 * (double) std::max(L1_.per_atom, L2_.per_atom);
 }
 
@@ -257,8 +295,9 @@ int Engine::auto_chunk(int64_t n) const
   size_t free_b = 0, total_b = 0;
   if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) free_b = (size_t) 8 << 30;
   const double budget = 0.35 * (double) free_b + 4.0 * (double) arena_.capacity();
-  int64_t c = (int64_t) (budget / per_atom_bytes());
-  c = std::min<int64_t>(c, fused_ ? ((int64_t) 1 << 22) : 32768);
+  int64_t c = (int64_t) (budget / per_atom_bytes(n));
+  // per-operation passes: large enough that the atom tiles of a pass fill the GPU, small enough to bound the work memory
+  c = std::min<int64_t>(c, use_fused(n) ? ((int64_t) 1 << 22) : (use_tc(n) ? 262144 : 32768));
   c = std::max<int64_t>(c, 512);
   return (int) std::min<int64_t>(c, std::max<int64_t>(n, 1));
 }
@@ -300,8 +339,18 @@ void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA)
 {
   // NA here is the number of atoms in use; the stride of the tensors is arena_NA_
   for (const Op &o : prog.ops) {
-    if (o.kind == Op::MV) launch_mv(E.mv[o.index], E.tensors.get(), mu, arena_NA_, NA);
-    else launch_prod(E.prod[o.index], E.tensors.get(), arena_NA_, NA, E.plan->tensors[E.prod[o.index].dst].channels);
+    if (o.kind == Op::MV) {
+      if (tc_now_ && E.mv_tc[o.index].ready())
+        E.mv_tc[o.index].launch(E.mv[o.index], E.tensors.get(), (int) E.tensors_host.size(), arena_NA_, NA, tc_error_.get());
+      else launch_mv(E.mv[o.index], E.tensors.get(), mu, arena_NA_, NA);
+    } else {
+      const ProdDev &pd = E.prod[o.index];
+      const auto &ts = E.plan->tensors;
+      const int C = ts[pd.dst].channels;
+      const bool same = ts[pd.srcA].channels == C && (pd.srcB < 0 || ts[pd.srcB].channels == C);
+      launch_prod(pd, E.tensors.get(), arena_NA_, NA, C, same ? ts[pd.srcA].nfuncs : 0,
+                  pd.srcB >= 0 ? ts[pd.srcB].nfuncs : 0, (int) E.plan->prod[o.index].terms.size());
+    }
   }
 }
 
@@ -716,10 +765,15 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
     if (out.virial && !energy_only) GB_CUDA(cudaMemsetAsync(out.virial, 0, sizeof(double) * 6 * nsys, st));
     return;
   }
-  if (!fused_) R.list0 = R.list1 = nullptr;    // the per-operation path evaluates the enclosing ranges
+  const int64_t n_eval = R.list0 ? std::max(R.n0, R.n1) : std::max(R.hi0 - R.lo0, R.hi1 - R.lo1);
+  const bool fused_now = use_fused(n_eval);
+  tc_now_ = !fused_now && use_tc(n_eval);
+  if (!fused_now) R.list0 = R.list1 = nullptr;    // the per-operation path evaluates the enclosing ranges
   const bool partial = R.list0 ? (R.n0 < n || R.n1 < n) : (R.lo0 > 0 || R.hi0 < n || R.lo1 > 0 || R.hi1 < n);
   const int64_t widest = std::max<int64_t>(1, R.list0 ? std::max(R.n0, R.n1) : std::max(R.hi0 - R.lo0, R.hi1 - R.lo1));
-  const int NA = (int) std::min<int64_t>(widest, chunk > 0 ? chunk : n);
+  // atoms per pass, rounded up to a multiple of 4: it is the atom stride of the chunk tensors, whose rows the vector
+  // loads of the kernels want 16-byte aligned whatever the channel counts are
+  const int NA = (int) ((std::min<int64_t>(widest, chunk > 0 ? chunk : n) + 3) / 4 * 4);
   e_atom_.ensure(n);
   if (!energy_only) vir_atom_.ensure(6 * n);
   if (partial) {    // what the skipped atoms would have written is read below or by the active atoms: zeros
@@ -753,8 +807,17 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
     }
     if (tm) tm->end(StageTimer::FWD);
   }
-  if (fused_) evaluate_fused(nl, energy_only, NA, tm, R);
+  if (fused_now) evaluate_fused(nl, energy_only, NA, tm, R);
   else evaluate_chunked(nl, energy_only, NA, tm, R);
+  if (tc_now_) {
+    int e = 0;
+    GB_CUDA(cudaMemcpyAsync(&e, tc_error_.get(), sizeof(int), cudaMemcpyDeviceToHost, st));
+    GB_CUDA(cudaStreamSynchronize(st));
+    if (e) {
+      GB_CUDA(cudaMemsetAsync(tc_error_.get(), 0, sizeof(int), st));
+      throw DeviceError("the tensor-core FC kernel gave up waiting for its matrix instructions");
+    }
+  }
   if (exact_) {
     rad1_.check();
     if (plan_.layers == 2) rad2_.check();

@@ -5,6 +5,7 @@
 #pragma once
 
 #include "kernels.h"
+#include "mv_tc.h"
 #include "nlist.h"
 #include "plan.h"
 #include "radial_mlp_tc.h"
@@ -41,6 +42,9 @@ struct LayerEngine {
   int fused_TA = 0;           // atoms per tile that fit the shared memory (0: the layer does not fit)
   int fused_NG = 2;           // warp groups per CTA the layer runs with (2, or 1 when two would get one atom each)
   long long q_floats = 0;     // floats per atom of the bond-sum tensor
+  // tensor-core form of each MV operation on chunk tensors (mv_tc.cu); not ready: the operation runs as mv_kernel
+  std::vector<MVTensorCore> mv_tc;
+  double tc_flop_share = 0.0;    // share of the layer's MV flops the tensor-core kernel covers
 };
 
 // Atoms a domain-decomposed caller wants evaluated, as ranges of the list order: [lo0, hi0) covers the owned atoms
@@ -79,7 +83,7 @@ class Engine {
   const double *rcsq() const { return rcsq_.get(); }
   int auto_chunk(int64_t n) const;
   void release_work();
-  double per_atom_bytes() const;
+  double per_atom_bytes(int64_t n_eval) const;
   std::mutex mu;    // one evaluation at a time per engine
 
  private:
@@ -94,7 +98,20 @@ class Engine {
   int arena_NA_ = 0;
   void setup_layer(LayerEngine &E, const LayerPlan &P);
   void setup_fused(LayerEngine &E, const LayerPlan &P);
-  bool fused_ = false;        // both layers run as the fused shared-memory kernel
+  bool fused_ = false;        // both layers fit the fused shared-memory kernel
+  // Dense-network path of an evaluation.  Large evaluations stream the network operation by operation over chunk
+  // tensors in global memory with the FC layers on the tensor cores (atoms are the long GEMM dimension: 128-atom
+  // tiles fill an MMA); small ones (too few atom tiles to fill the GPU) and shapes the tensor-core kernel does not
+  // cover run as the fused shared-memory kernel.  GRACE_B200_DENSE = fused | tc | ops overrides (ops: every operation
+  // as its SIMT kernel).
+  enum class Dense { Auto, Fused, Tc, Ops };
+  Dense dense_ = Dense::Auto;
+  bool tc_ready_ = false;
+  int64_t tc_min_atoms_ = 16384;
+  DBuf<int> tc_error_;
+  bool use_fused(int64_t n_eval) const;
+  bool use_tc(int64_t n_eval) const;
+  bool tc_now_ = false;       // the evaluation in progress runs eligible MV operations on the tensor cores
   // exact radial MLP per bond on the tensor cores instead of the tables (spline N = 0)
   bool exact_ = false;
   RadialMlpTC rad1_, rad2_;

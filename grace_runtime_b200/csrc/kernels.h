@@ -60,7 +60,8 @@ struct LayerDev {
 
 // element of a tensor: p[(f * NA + a) * C + c]; NA: atom stride of the chunk tensors, na <= NA: atoms in use
 void launch_mv(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na);
-void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, int C);
+// nfA, nfB: functions of the source tensors; nterms: terms of the operation (all staged in shared memory per atom tile)
+void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, int C, int nfA, int nfB, int nterms);
 
 // x[slot] = r / r_cut of the bond compacted into the slot (0.5 for slots without a bond): input of the exact radial MLP
 void launch_bond_x(const BondsDev &b, const float *rc, int n_elements, float *x, long long n);

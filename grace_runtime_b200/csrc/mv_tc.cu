@@ -1,0 +1,477 @@
+// FC layers, non-element reduces and their adjoints of the dense network on the 5th-generation tensor cores.
+//
+// On chunk tensors [function][atom][channel] an operation  out[row] (+)= sum_items scale * W_item^T x[item]  is a
+// grouped GEMM whose long dimension is the atoms: for an output row and a tile of 128 atoms,
+//     D[128 atoms][n_out] = sum_items X_item[128 atoms][K] . W_item[K][n_out],
+// with X_item a contiguous block of the source tensor.  A CTA owns up to 512 / n_out atom tiles at a time and keeps one
+// fp32 accumulator per tile in tensor memory; for every item of the row it converts the tile's activations to tf32
+// hi + lo operand images in shared memory (canonical K-major layout, 8-row x 16-byte core matrices) and issues
+// tcgen05.mma kind::tf32 M = 128, N = n_out against the item's weight image (converted and split on the host once):
+// a b ~ a_lo b_hi + a_hi b_lo + a_hi b_hi keeps fp32-level accuracy.  Activation tiles are double-buffered and the next
+// tile's global loads are in flight while the current one is converted, so the tensor cores, the conversion and the
+// memory system overlap; all items of a row accumulate in tensor memory and each output row is written once.
+// Same mathematics as mv_kernel (chain.cu); reference: fc_fwd / mv_batch, libgrace/include/grace/fused_cpu.h:294-356,
+// GPU fc_fwd4 libgrace/include/grace/kk/fused_dense.h:441-495.
+//
+// Every wait on the tensor cores is bounded: a wait that runs out sets the error flag, the CTA frees its tensor memory
+// and returns, and the host reports the failure.
+#include "mv_tc.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <map>
+
+namespace gb {
+
+namespace {
+
+constexpr int TM = 128;         // atoms of a tile = rows of an MMA = tensor-memory lanes
+constexpr int NTH = 256;
+constexpr int NW = NTH / 32;
+constexpr int TMEM_COLS = 512;
+constexpr int MAX_TILES = 16;   // atom tiles a CTA holds accumulators for
+constexpr int MAX_TENSORS = 64;
+constexpr long long WAIT_CYCLES = 40000000LL;    // ~20 ms: far beyond any tile, far below a watchdog
+
+// byte offset of element (r, k) of a K-major operand tile with K columns (canonical layout, no swizzle)
+__host__ __device__ inline int tile_off(int r, int k, int K) { return (r >> 3) * (K >> 2) * 128 + (k >> 2) * 128 + (r & 7) * 16 + (k & 3) * 4; }
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long make_desc(unsigned addr, int K)
+{
+  const unsigned long long lbo = 128 >> 4, sbo = ((K >> 2) * 128) >> 4;
+  return (unsigned long long) ((addr & 0x3ffff) >> 4) | (lbo << 16) | (sbo << 32) | (1ull << 46);
+}
+
+// fp32 accumulate, tf32 x tf32, both operands K-major, M = 128, N = n
+__device__ __forceinline__ unsigned make_idesc(int n) { return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned) (n >> 3) << 17) | ((unsigned) (TM >> 4) << 24); }
+
+__device__ __forceinline__ void mma_tf32_ss(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc, bool accumulate)
+{
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"((unsigned) accumulate) : "memory");
+}
+
+__device__ __forceinline__ void split4(float4 x, float sc, float4 &hi, float4 &lo)
+{
+  const float v[4] = {x.x * sc, x.y * sc, x.z * sc, x.w * sc};
+  float h[4], l[4];
+#pragma unroll
+  for (int q = 0; q < 4; q++) {
+    unsigned a, b;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(a) : "f"(v[q]));
+    h[q] = __uint_as_float(a);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(v[q] - h[q]));
+    l[q] = __uint_as_float(b);
+  }
+  hi = make_float4(h[0], h[1], h[2], h[3]);
+  lo = make_float4(l[0], l[1], l[2], l[3]);
+}
+
+template<int NC> __device__ __forceinline__ void tmem_ld(unsigned taddr, float (&v)[NC]);
+
+template<> __device__ __forceinline__ void tmem_ld<32>(unsigned taddr, float (&v)[32])
+{
+  unsigned r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+template<> __device__ __forceinline__ void tmem_ld<16>(unsigned taddr, float (&v)[16])
+{
+  unsigned r[16];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// waits for the phase `parity` of the barrier; false when the limit ran out
+__device__ __forceinline__ bool mbar_wait(unsigned mbar, unsigned parity)
+{
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+    if (ok) return true;
+    if (clock64() - t0 > WAIT_CYCLES) return false;
+  }
+}
+
+// position in the loop nest (round of tiles, output row, item of the row, tile of the round)
+struct Cursor {
+  int tile0, nt, row, it, i0, i1, tt;
+  bool valid;
+};
+
+// Activation tile of a fill: K4 = K / 4 float4 per atom row.  A warp instruction covers 8 atom rows x 4 consecutive
+// float4 (64 contiguous bytes of each row in global memory, 512 contiguous bytes = 4 core matrices in shared memory:
+// no bank conflicts); the 16 x CG such units of a tile go round the warps.
+template<int K> struct TileRegs {
+  static constexpr int K4 = K / 4, CG = (K4 + 3) / 4, UNITS = 16 * CG, PER = (UNITS + NW - 1) / NW;
+  float4 v[PER];
+};
+
+// K <= 32: two CTAs per SM (80 KB of shared memory and at most 256 tensor-memory columns each)
+template<int K, int CB>
+__global__ void __launch_bounds__(NTH, (K <= 32 ? 2 : 1)) mv_tc_kernel(MVTCDev op, const TensorDev *__restrict__ Tg, int ntensors,
+                                                                       int NA, int na, int TB, int tmem_cols, int *error)
+{
+  using TR = TileRegs<K>;
+  constexpr int K4 = TR::K4, CG = TR::CG, UNITS = TR::UNITS, PER = TR::PER;
+  constexpr int A_BYTES = TM * K * 4;    // one image (hi or lo) of an activation tile
+  extern __shared__ __align__(1024) char smem[];
+  __shared__ unsigned long long s_bar[2];
+  __shared__ unsigned s_tmem;
+  __shared__ TensorDev s_T[MAX_TENSORS];
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int N = op.n_out;
+  const int W_BYTES = N * K * 4;         // one image of a weight matrix
+  char *A_st = smem;                     // stage s at s * 2 * A_BYTES: hi, then lo
+  char *W_st = smem + 4 * A_BYTES;       // buffer b at b * 2 * W_BYTES: hi, then lo
+  for (int q = t; q < ntensors; q += NTH) s_T[q] = Tg[q];
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (t == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_bar[0])) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_bar[1])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem = s_tmem;
+  const unsigned bar[2] = {smem_u32(&s_bar[0]), smem_u32(&s_bar[1])};
+  const unsigned idesc = make_idesc(N);
+  const int ntiles = (na + TM - 1) / TM, per_round = gridDim.x * TB;
+  const TensorDev dstT = s_T[op.dst];
+
+  auto start = [&](Cursor &c, int tile0, int row) {
+    c.tile0 = tile0;
+    c.row = row;
+    c.valid = tile0 < ntiles && row < op.nrows;
+    if (!c.valid) return;
+    c.nt = min(TB, ntiles - tile0);
+    c.i0 = c.it = op.item_off[row];
+    c.i1 = op.item_off[row + 1];
+    c.tt = 0;
+  };
+  auto advance = [&](Cursor &c) {
+    if (++c.tt < c.nt) return;
+    c.tt = 0;
+    if (++c.it < c.i1) return;
+    int row = c.row + gridDim.y, tile0 = c.tile0;
+    if (row >= op.nrows) {
+      row = blockIdx.y;
+      tile0 += per_round;
+    }
+    start(c, tile0, row);
+  };
+  // global loads of the activation tile at the cursor into registers (zeros past the last atom)
+  auto load_tile = [&](const Cursor &c, TR &r) {
+    const MVItem item = op.items[c.it];
+    const TensorDev src = s_T[item.src];
+    const int atom0 = (c.tile0 + c.tt) * TM, valid = min(TM, na - atom0);
+    const float *base = src.p + ((size_t) item.irow * NA + atom0) * src.C;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+      const int u = warp + NW * j, row = (u % 16) * 8 + (lane & 7), c4 = (u / 16) * 4 + (lane >> 3);
+      r.v[j] = (u < UNITS && row < valid && c4 < K4) ? __ldg(reinterpret_cast<const float4 *>(base + (size_t) row * src.C) + c4)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+
+  // The global loads of two tiles are in flight ahead of the one being converted: two register sets take turns (the
+  // loop body is written once and instantiated for both roles, so no register is copied and no load is waited for
+  // before its tile is converted).
+  Cursor cur, nxt, nxt2;
+  start(cur, blockIdx.x * TB, blockIdx.y);
+  TR regsA, regsB;
+  if (cur.valid) load_tile(cur, regsA);
+  nxt = cur;
+  if (cur.valid) advance(nxt);
+  if (nxt.valid) load_tile(nxt, regsB);
+  unsigned phase[2] = {0, 0};
+  bool pending[2] = {false, false}, ok = true;
+  int fill = 0, wsel = 0;
+  // one fill: `mine` holds the tile at `cur`; after its conversion it receives the tile two fills ahead
+#ifdef GB_TC_TIMING
+  long long tm_[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq_ = clock64();
+#define GB_TICK(i) do { const long long now_ = clock64(); tm_[i] += now_ - tq_; tq_ = now_; } while (0)
+#else
+#define GB_TICK(i) do {} while (0)
+#endif
+  auto step = [&](TR &mine) {
+    GB_TICK(7);
+    nxt2 = nxt;
+    if (nxt.valid) advance(nxt2);
+    const int s = fill & 1;
+    // the matrix instructions that read this stage two fills ago (and everything issued before them) are done
+    if (pending[s]) {
+      ok = __syncthreads_and(mbar_wait(bar[s], phase[s]));
+      phase[s] ^= 1;
+      pending[s] = false;
+      if (!ok) return;
+    }
+    GB_TICK(0);
+    const MVItem item = op.items[cur.it];
+    if (cur.tt == 0) {    // first tile of an item: its weight image (hi + lo, byte for byte the operand layout)
+      wsel ^= 1;
+      const int4 *src = reinterpret_cast<const int4 *>(op.images + (size_t) item.mat * 2 * W_BYTES);
+      int4 *dst = reinterpret_cast<int4 *>(W_st + (size_t) wsel * 2 * W_BYTES);
+      for (int q = t; q < 2 * W_BYTES / 16; q += NTH) dst[q] = __ldg(src + q);
+    }
+    GB_TICK(1);
+    {    // registers -> tf32 hi / lo operand images of stage s
+      char *hi = A_st + (size_t) s * 2 * A_BYTES, *lo = hi + A_BYTES;
+#pragma unroll
+      for (int j = 0; j < PER; j++) {
+        const int u = warp + NW * j, c4 = (u / 16) * 4 + (lane >> 3);
+        if (u < UNITS && c4 < K4) {
+          const int off = ((u % 16) * K4 + c4) * 128 + (lane & 7) * 16;
+          float4 h, l;
+          split4(mine.v[j], item.scale, h, l);
+          *reinterpret_cast<float4 *>(hi + off) = h;
+          *reinterpret_cast<float4 *>(lo + off) = l;
+        }
+      }
+    }
+    GB_TICK(2);
+    if (nxt2.valid) load_tile(nxt2, mine);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    GB_TICK(3);
+    if (t == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // descriptors of the first K step; a step of 8 columns is 256 bytes further in either tile (16 in the address
+      // field, which cannot carry: shared-memory addresses stay below 2^18).  One thread issues everything, so the
+      // instruction chain per matrix instruction is kept to an add.
+      const unsigned a_hi = smem_u32(A_st + (size_t) s * 2 * A_BYTES), b_hi = smem_u32(W_st + (size_t) wsel * 2 * W_BYTES);
+      const unsigned long long dA[2] = {make_desc(a_hi, K), make_desc(a_hi + A_BYTES, K)};
+      const unsigned long long dB[2] = {make_desc(b_hi, K), make_desc(b_hi + W_BYTES, K)};
+      const unsigned d = tmem + (unsigned) (cur.tt * N);
+      const bool acc0 = cur.it != cur.i0;
+#pragma unroll
+      for (int pass = 0; pass < 3; pass++) {    // small terms first: a_lo b_hi, a_hi b_lo, a_hi b_hi
+        const unsigned long long a = dA[pass == 0 ? 1 : 0], b = dB[pass == 1 ? 1 : 0];
+#pragma unroll
+        for (int ks = 0; ks < K / 8; ks++) mma_tf32_ss(d, a + (unsigned long long) (ks * 16), b + (unsigned long long) (ks * 16), idesc, acc0 || pass > 0 || ks > 0);
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar[s]) : "memory");
+    }
+    pending[s] = true;
+    fill++;
+    GB_TICK(4);
+    const bool row_done = !nxt.valid || nxt.row != cur.row || nxt.tile0 != cur.tile0;
+    if (row_done) {    // every item of the row is in the accumulators: tensor memory -> global, once per output row
+      for (int q = 0; q < 2 && ok; q++) {
+        const int sq = (fill + q) & 1;    // the older commit first
+        if (pending[sq]) {
+          ok = __syncthreads_and(mbar_wait(bar[sq], phase[sq]));
+          phase[sq] ^= 1;
+          pending[sq] = false;
+        }
+      }
+      if (!ok) return;
+      GB_TICK(5);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // Each warp moves blocks of 32 atoms x CB columns: tensor memory -> registers (a lane holds one atom's columns)
+      // -> a padded transpose buffer of its own in the activation stages, which no matrix instruction reads any more
+      // -> global memory with a warp writing whole 128-byte lines (row = atom, CB / 4 lanes per row).
+      const int orow = op.row_out[cur.row], quarter = warp & 3, half = warp >> 2, nblk = N / CB;
+      float *tr = reinterpret_cast<float *>(A_st) + warp * (32 * (CB + 4));
+      constexpr int LPR = CB / 4, RPI = 32 / LPR;    // lanes per atom row, atom rows per store instruction
+      for (int b = half; b < cur.nt * nblk; b += 2) {
+        const int tt = b / nblk, c0 = (b - tt * nblk) * CB;
+        float v[CB];
+        tmem_ld<CB>(tmem + ((unsigned) (quarter * 32) << 16) + (unsigned) (tt * N + c0), v);
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < CB / 4; q++)
+          *reinterpret_cast<float4 *>(tr + lane * (CB + 4) + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        __syncwarp();
+        const int atom0 = (cur.tile0 + tt) * TM + quarter * 32;
+        float4 old[32 / RPI];
+        if (op.accumulate) {    // all loads of the old values first: independent, in flight together
+#pragma unroll
+          for (int j = 0; j < 32 / RPI; j++) {
+            const int r = j * RPI + lane / LPR, cq = lane % LPR;
+            old[j] = atom0 + r < na ? __ldcg(reinterpret_cast<const float4 *>(dstT.p + ((size_t) orow * NA + atom0 + r) * dstT.C + c0) + cq)
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32 / RPI; j++) {
+          const int r = j * RPI + lane / LPR, cq = lane % LPR;
+          if (atom0 + r < na) {
+            float4 w = *reinterpret_cast<const float4 *>(tr + r * (CB + 4) + 4 * cq);
+            if (op.accumulate) {
+              w.x += old[j].x; w.y += old[j].y; w.z += old[j].z; w.w += old[j].w;
+            }
+            reinterpret_cast<float4 *>(dstT.p + ((size_t) orow * NA + atom0 + r) * dstT.C + c0)[cq] = w;
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncthreads();    // the accumulators are free for the next row
+      GB_TICK(6);
+    }
+    cur = nxt;
+    nxt = nxt2;
+  };
+  while (cur.valid && ok) {
+    step(regsA);
+    if (!cur.valid || !ok) break;
+    step(regsB);
+  }
+#ifdef GB_TC_TIMING
+  if (t == 0 && blockIdx.x == 1 && blockIdx.y == 0)
+    printf("mv_tc K %d N %d rows %d fills %d TB %d grid %d: stage-wait %lld W %lld convert %lld loads+sync %lld issue %lld drain %lld epilogue %lld other %lld\n",
+           K, N, op.nrows, fill, TB, (int) gridDim.x, tm_[0], tm_[1], tm_[2], tm_[3], tm_[4], tm_[5], tm_[6], tm_[7]);
+#endif
+  if (!ok && t == 0) atomicExch(error, 1);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+}
+
+// activation stages and weight buffers; at least the transpose buffers of the epilogue (one per warp, in the same space)
+size_t smem_bytes(int K, int N)
+{
+  const size_t cb = N % 32 == 0 ? 32 : 16;
+  return std::max((size_t) 4 * TM * K * 4 + (size_t) 4 * N * K * 4, (size_t) NW * 32 * (cb + 4) * 4);
+}
+
+template<int K> void launch_k(const MVTCDev &op, const TensorDev *T, int ntensors, int NA, int na, int TB, dim3 grid, int *error)
+{
+  int tmem_cols = 32;    // a power of two that holds the accumulators of TB tiles
+  while (tmem_cols < TB * op.n_out) tmem_cols *= 2;
+  const size_t smem = smem_bytes(K, op.n_out);
+  if (op.n_out % 32 == 0) {
+    static size_t attr = 0;
+    if (smem > attr) {
+      GB_CUDA(cudaFuncSetAttribute(mv_tc_kernel<K, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      attr = smem;
+    }
+    GB_LAUNCH((mv_tc_kernel<K, 32>), grid, NTH, smem, op, T, ntensors, NA, na, TB, tmem_cols, error);
+  } else {
+    static size_t attr = 0;
+    if (smem > attr) {
+      GB_CUDA(cudaFuncSetAttribute(mv_tc_kernel<K, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      attr = smem;
+    }
+    GB_LAUNCH((mv_tc_kernel<K, 16>), grid, NTH, smem, op, T, ntensors, NA, na, TB, tmem_cols, error);
+  }
+}
+
+}    // namespace
+
+bool MVTensorCore::eligible(const MVOp &o, const std::vector<TensorSpec> &tensors)
+{
+  if (o.elem || o.items.empty() || o.row_out.empty()) return false;
+  if ((int) tensors.size() > MAX_TENSORS) return false;
+  const int K = o.items[0].n_in;
+  if (K != 8 && K != 16 && K != 32 && K != 64) return false;
+  if (o.n_out % 16 != 0 || o.n_out < 16 || o.n_out > 256) return false;
+  if (tensors[o.dst].channels % 4 != 0 || tensors[o.dst].channels < o.n_out) return false;
+  for (const MVItem &it : o.items)
+    if (it.n_in != K || tensors[it.src].channels % 4 != 0 || tensors[it.src].channels < K) return false;
+  for (size_t r = 0; r + 1 < o.item_off.size(); r++)
+    if (o.item_off[r + 1] == o.item_off[r]) return false;    // a row without items has no accumulator to write
+  return smem_bytes(K, o.n_out) <= 227 * 1024;
+}
+
+void MVTensorCore::setup(const MVOp &o)
+{
+  K_ = o.items[0].n_in;
+  const int N = o.n_out, K = K_;
+  // one operand image per distinct matrix: B[n][k] = W[k][n] as tf32 hi, then lo (canonical K-major layout)
+  std::map<int, int> index;
+  std::vector<char> img;
+  std::vector<MVItem> items = o.items;
+  for (MVItem &it : items) {
+    auto f = index.find(it.mat);
+    if (f == index.end()) {
+      const int id = (int) index.size();
+      f = index.emplace(it.mat, id).first;
+      std::vector<char> hi((size_t) N * K * 4, 0), lo((size_t) N * K * 4, 0);
+      for (int n = 0; n < N; n++)
+        for (int k = 0; k < K; k++) {
+          const float w = o.W[(size_t) it.mat + (size_t) k * o.ldw + n];
+          unsigned u;
+          std::memcpy(&u, &w, 4);
+          u = (u + 0x1000u) & 0xffffe000u;    // round to nearest tf32 (10-bit mantissa)
+          float h;
+          std::memcpy(&h, &u, 4);
+          const float r = w - h;
+          unsigned v;
+          std::memcpy(&v, &r, 4);
+          v = (v + 0x1000u) & 0xffffe000u;
+          std::memcpy(hi.data() + tile_off(n, k, K), &u, 4);
+          std::memcpy(lo.data() + tile_off(n, k, K), &v, 4);
+        }
+      img.insert(img.end(), hi.begin(), hi.end());
+      img.insert(img.end(), lo.begin(), lo.end());
+    }
+    it.mat = f->second;    // image index instead of the offset in the fp32 weights
+  }
+  images_.set_label("engine:weights_tf32");
+  items_.set_label("engine:tables");
+  images_.ensure(img.size());
+  GB_CUDA(cudaMemcpyAsync(images_.get(), img.data(), img.size(), cudaMemcpyHostToDevice, dev().stream));
+  items_.upload(items);
+  GB_CUDA(cudaStreamSynchronize(dev().stream));
+  ready_ = true;
+}
+
+void MVTensorCore::launch(const MVDev &d, const TensorDev *tensors, int ntensors, int NA, int na, int *error) const
+{
+  if (!ready_) throw DeviceError("tensor-core FC used before its set-up");
+  if (d.nrows == 0 || na == 0) return;
+  MVTCDev op{};
+  op.row_out = d.row_out;
+  op.item_off = d.item_off;
+  op.items = items_.get();
+  op.images = images_.get();
+  op.n_out = d.n_out;
+  op.nrows = d.nrows;
+  op.accumulate = d.accumulate;
+  op.dst = d.dst;
+  // CTAs resident at a time: two per SM for narrow inputs, each with half of the tensor memory
+  const int per_sm = K_ <= 32 && smem_bytes(K_, d.n_out) <= 100 * 1024 ? 2 : 1;
+  const int ntiles = (na + TM - 1) / TM, G = dev().sm_count * per_sm;
+  const int tb_max = std::max(1, std::min(MAX_TILES, TMEM_COLS / per_sm / d.n_out));
+  const int TB = std::max(1, std::min(tb_max, (ntiles + G - 1) / G));
+  const int gx = std::min(G, (ntiles + TB - 1) / TB);
+  const int gy = std::max(1, std::min(d.nrows, G / gx));
+  const dim3 grid(gx, gy);
+  switch (K_) {
+    case 8: launch_k<8>(op, tensors, ntensors, NA, na, TB, grid, error); break;
+    case 16: launch_k<16>(op, tensors, ntensors, NA, na, TB, grid, error); break;
+    case 32: launch_k<32>(op, tensors, ntensors, NA, na, TB, grid, error); break;
+    case 64: launch_k<64>(op, tensors, ntensors, NA, na, TB, grid, error); break;
+    default: throw DeviceError("tensor-core FC: unsupported input width");
+  }
+}
+
+}    // namespace gb
