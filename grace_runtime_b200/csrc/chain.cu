@@ -68,118 +68,171 @@ __global__ void __launch_bounds__(128) mv_kernel(MVDev op, const TensorDev *__re
   }
 }
 
-// Per-element weights (reduces over the central atom's element and their adjoints) for a tile of atoms: the weight
-// matrices of the elements present in the tile are staged in shared memory item by item, so a weight is fetched from
-// global memory once per tile and element instead of once per atom; a thread owns 4 output channels of one atom and
-// reads its activations with loads the other threads of the atom share.  Same summation order as mv_kernel.
-constexpr int ELEM_MAXS = 4;    // elements staged at a time (tiles with more run the items once more per group)
+// Per-element weights (reduces over the central atom's element and their adjoints) for a tile of 256 atoms, one thread
+// per atom with all NQ x 4 output channels of a row in registers.  The atoms of the tile are taken in order of their
+// element, so the lanes of a warp mostly read the same weights (one broadcast shared-memory read serves them).  A CTA
+// walks the (row, item) pairs of its rows in groups; the weight matrices of a group, for the elements present in the
+// tile, are staged in shared memory together: a weight is fetched from global memory once per tile and element and a
+// group costs two barriers.  Same summation order as mv_kernel.
+constexpr int ELEM_MAXS = 4;    // elements staged at a time (tiles with more walk the items once more per group of elements)
 constexpr int ELEM_GROUP = 4;   // items whose weights are staged together
-__global__ void __launch_bounds__(256) mv_elem_tile_kernel(MVDev op, const TensorDev *__restrict__ T,
-                                                           const int *__restrict__ mu, int NA, int na, int TA, int KQ,
-                                                           int n_in_max)
+constexpr int ELEM_TA = 256;
+template<int NQ>
+__global__ void __launch_bounds__(ELEM_TA) mv_elem_tile_kernel(MVDev op, const TensorDev *__restrict__ T,
+                                                               const int *__restrict__ mu, int NA, int na, int n_in_max,
+                                                               int rows_per_cta)
 {
-  extern __shared__ __align__(16) float wsm[];    // [ELEM_GROUP][ELEM_MAXS][n_in_max][ldw]
-  __shared__ int s_slot[128], s_el[128], s_nsp;
-  const int row = blockIdx.y, a0 = blockIdx.x * TA, nta = min(TA, na - a0), t = threadIdx.x;
-  const int p = t / KQ, kq = t - p * KQ, ld = op.ldw, ld4 = ld >> 2;
-  const bool active = p < nta;
-  __shared__ int s_mu[128];
+  extern __shared__ __align__(16) float wsm[];    // [ELEM_GROUP][ELEM_MAXS][n_in_max][NQ * 4]
+  __shared__ int s_slot[ELEM_TA], s_el[ELEM_TA], s_mu[ELEM_TA], s_order[ELEM_TA], s_cnt[ELEM_TA + 1], s_nsp;
+  const int a0 = blockIdx.x * ELEM_TA, nta = min(ELEM_TA, na - a0), t = threadIdx.x;
+  const int row_lo = blockIdx.y * rows_per_cta, row_hi = min(op.nrows, row_lo + rows_per_cta);
   if (t < nta) s_mu[t] = mu[a0 + t];
   __syncthreads();
-  if (t == 0) {    // distinct elements of the tile, in order of first appearance
+  if (t == 0) {    // distinct elements of the tile in order of first appearance, and the atoms grouped by them
     int ns = 0;
     for (int a = 0; a < nta; a++) {
       const int e = s_mu[a];
       int s = 0;
       while (s < ns && s_el[s] != e) s++;
-      if (s == ns) s_el[ns++] = e;
+      if (s == ns) { s_el[ns] = e; s_cnt[ns++] = 0; }
       s_slot[a] = s;
+      s_cnt[s]++;
     }
+    int at = 0;
+    for (int s = 0; s < ns; s++) { const int c = s_cnt[s]; s_cnt[s] = at; at += c; }
+    for (int a = 0; a < nta; a++) s_order[s_cnt[s_slot[a]]++] = a;
     s_nsp = ns;
   }
   __syncthreads();
+  const bool active = t < nta;
+  const int p = active ? s_order[t] : 0;    // this thread's atom of the tile
   const int nsp = s_nsp, slot = active ? s_slot[p] : -1;
-  const int i0 = op.item_off[row], i1 = op.item_off[row + 1];
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int i_lo = op.item_off[row_lo], i_hi = op.item_off[row_hi];
   const float4 *w4 = reinterpret_cast<const float4 *>(wsm);
-  const int wstride = n_in_max * ld4;    // float4 per (item of the group, element)
+  const int wstride = n_in_max * NQ;    // float4 per (item of the group, element)
+  const TensorDev dst = T[op.dst];
   for (int s0 = 0; s0 < nsp; s0 += ELEM_MAXS) {
     const int ng = min(ELEM_MAXS, nsp - s0);
-    for (int it0 = i0; it0 < i1; it0 += ELEM_GROUP) {    // the weights of a group of items are staged together
-      const int nit = min(ELEM_GROUP, i1 - it0);
+    const bool mine = slot >= s0 && slot < s0 + ng;
+    int row = row_lo;
+    float4 acc[NQ];
+#pragma unroll
+    for (int k = 0; k < NQ; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto flush = [&]() {    // the sums of `row` are complete
+      if (mine) {
+        float *o = dst.p + ((size_t) op.row_out[row] * NA + a0 + p) * dst.C;
+        if ((dst.C & 3) == 0 && op.n_out == 4 * NQ) {
+#pragma unroll
+          for (int k = 0; k < NQ; k++) {
+            float4 v = acc[k];
+            if (op.accumulate) {
+              const float4 old = reinterpret_cast<const float4 *>(o)[k];
+              v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            reinterpret_cast<float4 *>(o)[k] = v;
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < NQ; k++) {
+            const float v[4] = {acc[k].x, acc[k].y, acc[k].z, acc[k].w};
+            for (int q = 0; q < 4; q++)
+              if (4 * k + q < op.n_out) o[4 * k + q] = op.accumulate ? o[4 * k + q] + v[q] : v[q];
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < NQ; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      row++;
+    };
+    for (int it0 = i_lo; it0 < i_hi; it0 += ELEM_GROUP) {
+      const int nit = min(ELEM_GROUP, i_hi - it0);
       __syncthreads();    // the weights of the previous group are no longer read
       for (int g = 0; g < nit; g++) {
         const MVItem item = op.items[it0 + g];
-        const int per = item.n_in * ld4;
-        for (int q = t; q < ng * per; q += 256) {
+        const int per = item.n_in * NQ;
+        for (int q = t; q < ng * per; q += ELEM_TA) {
           const int s = q / per, r = q - s * per;
           reinterpret_cast<float4 *>(wsm)[(size_t) (g * ELEM_MAXS + s) * wstride + r] =
               __ldg(reinterpret_cast<const float4 *>(op.W + (size_t) s_el[s0 + s] * op.ty_stride + item.mat) + r);
         }
       }
       __syncthreads();
-      if (slot >= s0 && slot < s0 + ng) {
-        for (int g = 0; g < nit; g++) {
-          const MVItem item = op.items[it0 + g];
-          const TensorDev src = T[item.src];
-          const float *x = src.p + ((size_t) item.irow * NA + a0 + p) * src.C;
-          const float4 *w = w4 + (size_t) (g * ELEM_MAXS + slot - s0) * wstride + kq;
-          float4 part = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (((src.C | item.n_in) & 3) == 0) {    // 16-byte activation loads, eight of them in flight
-            for (int n0 = 0; n0 < item.n_in; n0 += 32) {
-              float4 xv[8];
+      for (int g = 0; g < nit; g++) {
+        while (it0 + g >= op.item_off[row + 1]) flush();
+        if (!mine) continue;
+        const MVItem item = op.items[it0 + g];
+        const TensorDev src = T[item.src];
+        const float *x = src.p + ((size_t) item.irow * NA + a0 + p) * src.C;
+        const float4 *w = w4 + (size_t) (g * ELEM_MAXS + slot - s0) * wstride;
+        float4 part[NQ];
 #pragma unroll
-              for (int j = 0; j < 8; j++)
-                xv[j] = n0 + 4 * j < item.n_in ? __ldg(reinterpret_cast<const float4 *>(x + n0) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < NQ; k++) part[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        auto one = [&](float xv, int n) {
 #pragma unroll
-              for (int j = 0; j < 8; j++) {
-                if (n0 + 4 * j < item.n_in) {
-                  const float xs[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+          for (int k = 0; k < NQ; k++) {
+            const float4 wv = w[(size_t) n * NQ + k];
+            part[k].x = fmaf(xv, wv.x, part[k].x); part[k].y = fmaf(xv, wv.y, part[k].y);
+            part[k].z = fmaf(xv, wv.z, part[k].z); part[k].w = fmaf(xv, wv.w, part[k].w);
+          }
+        };
+        if (((src.C | item.n_in) & 3) == 0) {    // 16-byte activation loads, eight of them in flight
+          for (int n0 = 0; n0 < item.n_in; n0 += 32) {
+            float4 xv[8];
 #pragma unroll
-                  for (int q = 0; q < 4; q++) {
-                    const float4 wv = w[(size_t) (n0 + 4 * j + q) * ld4];
-                    part.x = fmaf(xs[q], wv.x, part.x); part.y = fmaf(xs[q], wv.y, part.y);
-                    part.z = fmaf(xs[q], wv.z, part.z); part.w = fmaf(xs[q], wv.w, part.w);
-                  }
-                }
+            for (int j = 0; j < 8; j++)
+              xv[j] = n0 + 4 * j < item.n_in ? __ldg(reinterpret_cast<const float4 *>(x + n0) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              if (n0 + 4 * j < item.n_in) {
+                one(xv[j].x, n0 + 4 * j); one(xv[j].y, n0 + 4 * j + 1); one(xv[j].z, n0 + 4 * j + 2); one(xv[j].w, n0 + 4 * j + 3);
               }
             }
-          } else {
-            for (int n = 0; n < item.n_in; n++) {
-              const float xv = __ldg(x + n);
-              const float4 wv = w[(size_t) n * ld4];
-              part.x = fmaf(xv, wv.x, part.x); part.y = fmaf(xv, wv.y, part.y);
-              part.z = fmaf(xv, wv.z, part.z); part.w = fmaf(xv, wv.w, part.w);
-            }
           }
-          acc.x = fmaf(item.scale, part.x, acc.x); acc.y = fmaf(item.scale, part.y, acc.y);
-          acc.z = fmaf(item.scale, part.z, acc.z); acc.w = fmaf(item.scale, part.w, acc.w);
+        } else {
+          for (int n = 0; n < item.n_in; n++) one(__ldg(x + n), n);
+        }
+#pragma unroll
+        for (int k = 0; k < NQ; k++) {
+          acc[k].x = fmaf(item.scale, part[k].x, acc[k].x); acc[k].y = fmaf(item.scale, part[k].y, acc[k].y);
+          acc[k].z = fmaf(item.scale, part[k].z, acc[k].z); acc[k].w = fmaf(item.scale, part[k].w, acc[k].w);
         }
       }
     }
+    while (row < row_hi) flush();    // the last row, and rows without items
   }
-  if (!active) return;
-  const TensorDev dst = T[op.dst];
-  float *o = dst.p + ((size_t) op.row_out[row] * NA + a0 + p) * dst.C + 4 * kq;
-  const float v[4] = {acc.x, acc.y, acc.z, acc.w};
-  const int nk = min(4, op.n_out - 4 * kq);
-  for (int q = 0; q < nk; q++) o[q] = op.accumulate ? o[q] + v[q] : v[q];
+}
+
+template<int NQ> void launch_elem(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na)
+{
+  const size_t smem = (size_t) ELEM_GROUP * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float);
+  static bool attr = false;    // static shared memory counts against the 48 KB a kernel gets without the attribute
+  if (!attr && smem > 32 * 1024) {
+    GB_CUDA(cudaFuncSetAttribute(mv_elem_tile_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    attr = true;
+  }
+  // rows of a tile go to one CTA unless the tiles alone cannot fill the GPU
+  const int tiles = (na + ELEM_TA - 1) / ELEM_TA, want = 4 * dev().sm_count;
+  const int gy = std::max(1, std::min(op.nrows, (want + tiles - 1) / tiles));
+  const int rows_per_cta = (op.nrows + gy - 1) / gy;
+  GB_LAUNCH((mv_elem_tile_kernel<NQ>), dim3(tiles, (op.nrows + rows_per_cta - 1) / rows_per_cta), ELEM_TA, smem, op, tensors, mu,
+            NA, na, op.unit_nmax, rows_per_cta);
 }
 
 void launch_mv(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na)
 {
   if (op.nrows == 0 || na == 0) return;
-  if (op.elem && (op.ldw & 3) == 0 && (op.ty_stride & 3) == 0 && op.unit_nmax > 0) {
-    const int KQ = op.ldw >> 2, TA = std::min(128, 256 / KQ);
-    const size_t smem = (size_t) ELEM_GROUP * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float);
-    if (KQ <= 64 && smem <= 96 * 1024) {
-      static bool attr = false;    // static shared memory counts against the 48 KB a kernel gets without the attribute
-      if (!attr && smem > 32 * 1024) {
-        GB_CUDA(cudaFuncSetAttribute(mv_elem_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        attr = true;
-      }
-      GB_LAUNCH(mv_elem_tile_kernel, dim3((na + TA - 1) / TA, op.nrows), 256, smem, op, tensors, mu, NA, na, TA, KQ, op.unit_nmax);
-      return;
+  if (op.elem && (op.ldw & 3) == 0 && (op.ty_stride & 3) == 0 && op.unit_nmax > 0 &&
+      (size_t) ELEM_GROUP * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float) <= 96 * 1024) {
+    switch (op.ldw >> 2) {
+      case 1: launch_elem<1>(op, tensors, mu, NA, na); return;
+      case 2: launch_elem<2>(op, tensors, mu, NA, na); return;
+      case 3: launch_elem<3>(op, tensors, mu, NA, na); return;
+      case 4: launch_elem<4>(op, tensors, mu, NA, na); return;
+      case 5: launch_elem<5>(op, tensors, mu, NA, na); return;
+      case 8: launch_elem<8>(op, tensors, mu, NA, na); return;
+      case 12: launch_elem<12>(op, tensors, mu, NA, na); return;
+      case 16: launch_elem<16>(op, tensors, mu, NA, na); return;
+      default: break;    // other widths: the per-atom kernel below
     }
   }
   int KP = 8;

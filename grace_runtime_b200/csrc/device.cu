@@ -56,7 +56,8 @@ void cuda_check(cudaError_t e, const char *what)
 }
 
 namespace {
-struct ProfSpan { const char *name; cudaEvent_t a, b; };
+struct ProfSpan { std::string name; cudaEvent_t a, b; };
+const char *g_tag = nullptr;
 bool g_prof_on = false;
 std::vector<ProfSpan> g_prof;
 std::vector<cudaEvent_t> g_prof_pool;
@@ -71,6 +72,8 @@ cudaEvent_t prof_event()
   return g_prof_pool[g_prof_used++];
 }
 }    // namespace
+
+void launch_tag(const char *tag) { g_tag = tag; }
 
 void profile_enable(bool on)
 {
@@ -98,7 +101,7 @@ std::string profile_report()
 void before_launch(const char *name)
 {
   if (!g_prof_on) return;
-  ProfSpan s{name, prof_event(), prof_event()};
+  ProfSpan s{g_tag ? std::string(name) + ":" + g_tag : std::string(name), prof_event(), prof_event()};
   cudaEventRecord(s.a, g_dev.stream);
   g_prof.push_back(s);
 }

@@ -49,6 +49,9 @@ void require_initialized();
 // a pair of CUDA events on the launch stream per launch
 void before_launch(const char *name);
 void after_launch(const char *name);
+// label appended to the kernel name of the launches that follow in the kernel profile (null: none); the engine tags
+// the operations of the dense network with their names when GRACE_B200_PROFILE_OPS is set
+void launch_tag(const char *tag);
 // per-kernel device time (CUDA events around every launch while on)
 void profile_enable(bool on);
 // "name launches total_ms" lines of the launches since profile_enable(true); synchronises the stream

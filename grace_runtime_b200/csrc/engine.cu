@@ -338,7 +338,9 @@ LayerDev Engine::layer_dev(const LayerEngine &E) const
 void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA)
 {
   // NA here is the number of atoms in use; the stride of the tensors is arena_NA_
+  static const bool tag_ops = getenv("GRACE_B200_PROFILE_OPS") != nullptr;
   for (const Op &o : prog.ops) {
+    if (tag_ops) launch_tag(o.kind == Op::MV ? E.plan->mv[o.index].name.c_str() : E.plan->prod[o.index].name.c_str());
     if (o.kind == Op::MV) {
       if (tc_now_ && E.mv_tc[o.index].ready())
         E.mv_tc[o.index].launch(E.mv[o.index], E.tensors.get(), (int) E.tensors_host.size(), arena_NA_, NA, tc_error_.get());
@@ -352,6 +354,7 @@ void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA)
                   pd.srcB >= 0 ? ts[pd.srcB].nfuncs : 0, (int) E.plan->prod[o.index].terms.size());
     }
   }
+  if (tag_ops) launch_tag(nullptr);
 }
 
 // shared-memory layout of the tensors of an atom tile: every tensor padded to 4 floats per atom; a gradient that may
