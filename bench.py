@@ -358,6 +358,8 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     B.initialize(local_rank)
+    if world > 1:
+        domain.init_library_comm(rank, world)      # the halo exchange runs inside the library, on its own NCCL communicator
     tmp = tempfile.mkdtemp(prefix="grace_bench_")
     path, species, types, pos, cell, pbc = make_workload(args.workload, tmp)     # every rank: the same seeded structure
     n = len(types)

@@ -59,6 +59,12 @@ SIGNATURES = {
     "grace_system_compute": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "grace_system_compute_device": (_I, [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P]),
     "grace_system_set_owned": (_I, [_P, _I, _I]),
+    "grace_system_set_exchange": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
+    "grace_comm_unique_id": (_I, [_P]),
+    "grace_comm_init": (_I, [_P, _I, _I]),
+    "grace_comm_finalize": (_I, []),
+    "grace_comm_rank": (_I, []),
+    "grace_comm_size": (_I, []),
     "grace_system_neighbor_list": (_I, [_P, _I64, _P, _P, _P, _P]),
     "grace_system_rebuilds": (_I64, [_P]),
     "grace_system_chunksize": (_I, [_P]),
@@ -199,6 +205,32 @@ def _debug_fail_alloc(label, nth):
 
 def _debug_fail_launch(nth):
     _check(load_library().grace_debug_fail_launch(int(nth)))
+
+
+def comm_unique_id():
+    """128 bytes made by rank 0 that every rank passes to comm_init (send them with any transport)."""
+    buf = C.create_string_buffer(128)
+    _check(load_library().grace_comm_unique_id(buf))
+    return buf.raw
+
+
+def comm_init(unique_id, rank, world):
+    """Joins the library's NCCL communicator (collective; after initialize(device))."""
+    if len(unique_id) != 128:
+        raise ValueError("the unique id has 128 bytes")
+    _check(load_library().grace_comm_init(C.c_char_p(bytes(unique_id)), int(rank), int(world)))
+
+
+def comm_finalize():
+    _check(load_library().grace_comm_finalize())
+
+
+def comm_rank():
+    return load_library().grace_comm_rank()
+
+
+def comm_size():
+    return load_library().grace_comm_size()
 
 
 def measure_peak(kind):
@@ -437,6 +469,13 @@ class System:
         """Atoms [0, nlocal) are owned, the rest are ghosts of a domain decomposition (-1: all owned); ghosts behind
         ninner only serve as neighbours (GRACE-2L: ghosts no owned atom has inside cutoff + skin)."""
         _check(_lib.grace_system_set_owned(self._h, int(nlocal), int(ninner)))
+
+    def set_exchange(self, n, nlocal, ninner, send_counts, send_index, recv_counts, recv_index):
+        """Domain decomposition over the library's communicator (comm_init): as set_owned, and every compute returns
+        the ghost force rows to their owners and sums energy and virial over the ranks (collective)."""
+        sc, si = _as(send_counts, np.int32), _as(send_index, np.int32)
+        rc, ri = _as(recv_counts, np.int32), _as(recv_index, np.int32)
+        _check(_lib.grace_system_set_exchange(self._h, int(n), int(nlocal), int(ninner), _ptr(sc), _ptr(si), _ptr(rc), _ptr(ri)))
 
     def compute(self, types, positions, cell, pbc, energies=False, uq=False, energy_only=False):
         """Result dict as python/kk/kk_module.cpp `compute`: energy, virial [6], forces [n, 3] (not with energy_only),

@@ -114,6 +114,7 @@ int grace_finalize(void)
       if (s->s) s->s->release();
     for (auto *b : g_batches)
       if (b->b) b->b->release();
+    comm_finalize();
     cudaStreamSynchronize(d.stream);
     cudaStreamDestroy(d.stream);
     d.stream = nullptr;
@@ -290,6 +291,34 @@ int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, 
 int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_out)
 {
   return guarded([&] { static_sum(d_values, (long long) n, k, d_out); });
+}
+
+int grace_comm_unique_id(void *id128)
+{
+  return guarded([&] { comm_unique_id(id128); });
+}
+
+int grace_comm_init(const void *id128, int rank, int world)
+{
+  return guarded([&] { comm_init(id128, rank, world); });
+}
+
+int grace_comm_finalize(void)
+{
+  return guarded([&] { comm_finalize(); });
+}
+
+int grace_comm_rank(void) { return comm_rank(); }
+int grace_comm_size(void) { return comm_size(); }
+
+int grace_system_set_exchange(grace_system *s, int n, int nlocal, int ninner, const int32_t *send_counts,
+                              const int32_t *send_index, const int32_t *recv_counts, const int32_t *recv_index)
+{
+  return guarded([&] {
+    if (!s) throw InvalidArgument("system must be given");
+    std::lock_guard<std::mutex> lk(s->s->mu);
+    s->s->set_exchange(n, nlocal, ninner, send_counts, send_index, recv_counts, recv_index);
+  });
 }
 
 int grace_system_set_owned(grace_system *s, int nlocal, int ninner)

@@ -928,6 +928,13 @@ void SystemObj::set_owned(int nlocal_, int ninner_)
   have_list_ = false;    // the active ranges belong to the list: rebuilt by the next compute
 }
 
+void SystemObj::set_exchange(int n, int nlocal_, int ninner_, const int32_t *send_counts, const int32_t *send_index,
+                             const int32_t *recv_counts, const int32_t *recv_index)
+{
+  exchange.setup(n, nlocal_, send_counts, send_index, recv_counts, recv_index);
+  set_owned(nlocal_, ninner_);
+}
+
 void SystemObj::compute(int n, const int *types, const double *pos, bool device_in, const double *cell,
                         const unsigned char *pbc, int flags, double *energy, double *virial, double *forces,
                         double *energies, bool device_out)
@@ -993,15 +1000,18 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     ws_.t2m.upload(t2m_);
     GB_LAUNCH(types_to_mu, nblocks(n, 256), 256, 0, d_types, ws_.t2m.get(), ns, ws_.mu.get(), ws_.flag.get(), (long long) n);
   }
-  // rebuild when the atoms, cell or pbc changed or an atom moved more than half the skin (kk_core.cpp:691-708)
+  // rebuild when the atoms, cell or pbc changed or an atom moved more than half the skin (kk_core.cpp:691-708); the
+  // three device-side checks (types in range, types unchanged, displacements) set bits of one flag, read back once
   bool need = !have_list_ || list_n_ != n || ws_.h_cell.size() != 9 || std::memcmp(ws_.h_cell.data(), cell, 72) != 0 ||
               std::memcmp(ws_.h_pbc.data(), pbc, 3) != 0;
   if (n > 0) {
-    if (!need) GB_LAUNCH(types_differ, nblocks(n, 256), 256, 0, d_types, ws_.types_prev.get(), ws_.flag.get(), (long long) n);
+    if (!need) {
+      GB_LAUNCH(types_differ, nblocks(n, 256), 256, 0, d_types, ws_.types_prev.get(), ws_.flag.get(), (long long) n);
+      nl_.moved_launch(d_pos, 0.5 * skin_, ws_.flag.get(), 4);
+    }
     const int fl = read_int(ws_.flag.get());
     if (fl & 1) throw InvalidArgument("types must be 1 .. len(species)");
-    if (fl & 2) need = true;
-    if (!need && nl_.moved_beyond(d_pos, 0.5 * skin_)) need = true;
+    if (fl & 6) need = true;
   }
   if (need) {
     timer_.begin(StageTimer::NL);
@@ -1036,6 +1046,10 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     if (want_e && energies) o.energies = ws_.energies.ensure(std::max(n, 1));
   }
   engine_->evaluate(nl_, eonly, o, chunk, &timer_, nlocal >= 0 ? &ranges : nullptr);
+  if (exchange.active()) {
+    if (n != exchange.n()) throw InvalidArgument("the atom count differs from the one the exchange plan was made for");
+    exchange.run(eonly ? nullptr : o.forces, o.energy, eonly ? nullptr : o.virial);
+  }
   if (!device_out) {
     if (energy) GB_CUDA(cudaMemcpyAsync(energy, o.energy, sizeof(double), cudaMemcpyDeviceToHost, st));
     if (o.virial) GB_CUDA(cudaMemcpyAsync(virial, o.virial, sizeof(double) * 6, cudaMemcpyDeviceToHost, st));

@@ -4,6 +4,7 @@
 // libgrace/src/fused_2l.cpp:988-1091).
 #pragma once
 
+#include "comm.h"
 #include "kernels.h"
 #include "mv_tc.h"
 #include "nlist.h"
@@ -166,6 +167,11 @@ class SystemObj {
   ActiveRanges ranges;
   DBuf<int> list0_, list1_;
   void set_owned(int nlocal_, int ninner_);
+  // domain decomposition over the library's communicator: as set_owned, and after every evaluation the ghost force rows
+  // go back to their owners and energy and virial are summed over the ranks (comm.h)
+  void set_exchange(int n, int nlocal_, int ninner_, const int32_t *send_counts, const int32_t *send_index,
+                    const int32_t *recv_counts, const int32_t *recv_index);
+  Exchange exchange;
   double stage_ms[StageTimer::NSTAGE] = {0, 0, 0, 0, 0};
   void release();
   std::mutex mu;

@@ -272,13 +272,13 @@ __global__ void __launch_bounds__(128) nl_reverse(const long long *__restrict__ 
 }
 
 __global__ void __launch_bounds__(256) nl_moved(const double *__restrict__ pos, const double *__restrict__ xbuild,
-                                                double lim2, int *flag, long long n)
+                                                double lim2, int *flag, int bit, long long n)
 {
   const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const double dx = pos[3 * i] - xbuild[3 * i], dy = pos[3 * i + 1] - xbuild[3 * i + 1],
                dz = pos[3 * i + 2] - xbuild[3 * i + 2];
-  if (!(dx * dx + dy * dy + dz * dz <= lim2)) atomicOr(flag, 1);    // NaN counts as moved
+  if (!(dx * dx + dy * dy + dz * dz <= lim2)) atomicOr(flag, bit);    // NaN counts as moved
 }
 
 // this call's positions in list order, shifted by the images of the build
@@ -518,8 +518,14 @@ bool NeighborList::moved_beyond(const double *d_pos, double half_skin)
 {
   if (n_ == 0) return false;
   GB_CUDA(cudaMemsetAsync(flag_.get(), 0, sizeof(int), dev().stream));
-  GB_LAUNCH(nl_moved, blocks(n_, 256), 256, 0, d_pos, xbuild_.get(), half_skin * half_skin, flag_.get(), (long long) n_);
+  GB_LAUNCH(nl_moved, blocks(n_, 256), 256, 0, d_pos, xbuild_.get(), half_skin * half_skin, flag_.get(), 1, (long long) n_);
   return read_flag(flag_.get()) != 0;
+}
+
+void NeighborList::moved_launch(const double *d_pos, double half_skin, int *d_flag, int bit)
+{
+  if (n_ == 0) return;
+  GB_LAUNCH(nl_moved, blocks(n_, 256), 256, 0, d_pos, xbuild_.get(), half_skin * half_skin, d_flag, bit, (long long) n_);
 }
 
 void NeighborList::prepare(const double *d_pos, const double *d_rcsq, int n_elements, float *fv)

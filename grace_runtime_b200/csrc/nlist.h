@@ -29,6 +29,8 @@ class NeighborList {
              const unsigned char *pbc, double radius);
   // true when an atom moved more than half the skin since the build (device max-reduce, one int read back)
   bool moved_beyond(const double *d_pos, double half_skin);
+  // the same check without the read-back: sets `bit` of the caller's device flag
+  void moved_launch(const double *d_pos, double half_skin, int *d_flag, int bit);
   // positions of this call into list order (wrapped with the images of the build) and the bonds inside the pair
   // cutoffs rcsq [n_elements][n_elements]: records compacted to the front of each atom's slots; bond forces of the
   // slots left out are zeroed in fv

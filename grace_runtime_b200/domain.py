@@ -11,7 +11,9 @@ collective).  This is the
 forward / reverse communication (libgrace/include/grace/system.h:56-60, libgrace/include/grace/kk/grace_2l_kk.h:136-153).
 
 The plan is plain numpy and is computed by every rank for all ranks from the replicated structure (no communication at
-set-up); only `DistributedSystem.step` talks to other ranks."""
+set-up); only `DistributedSystem.step` talks to other ranks.  With the CUDA library the exchange runs inside the
+library's compute call on its own stream (NCCL send / receive pairs, `backend.System.set_exchange`); the torch.distributed
+exchange below serves engines injected for tests (CPU, gloo)."""
 import numpy as np
 
 
@@ -144,10 +146,21 @@ def make_plan(positions, cell, pbc, world, layers, cutoff, skin):
                     inner=halo_width(1, cutoff, skin) if layers > 1 else None)
 
 
+def init_library_comm(rank, world):
+    """Creates the library's NCCL communicator of a torch.distributed job: rank 0's unique id goes round through the
+    job's default process group."""
+    import torch.distributed as dist
+    from . import backend as B
+    ids = [B.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    B.comm_init(ids[0], rank, world)
+
+
 class DistributedSystem:
     """One rank's part of a decomposed structure on its GPU: `step()` evaluates the sub-system through the C ABI
-    (device pointers), returns ghost forces to their owners over the process group and sums energy and virial.
-    `compute(positions, ...)` callables other than the CUDA library can be injected for tests (`engine=`)."""
+    (device pointers); the library returns ghost forces to their owners and sums energy and virial over its
+    communicator inside that call (`init_library_comm` first).  `compute(positions, ...)` callables other than the CUDA
+    library can be injected for tests (`engine=`): their exchange goes through torch.distributed."""
 
     def __init__(self, plan, rank, types, positions, species=None, model=None, skin=0.5, chunksize=-1, device=None,
                  engine=None, group=None):
@@ -178,12 +191,18 @@ class DistributedSystem:
         self.recv_idx = torch.from_numpy(np.concatenate(recv_idx)).to(self.device)
         self.layers = 1
         self.engine = engine
+        self.library_exchange = False
         if engine is None:
             from . import backend as B
             self.system = B.System(model, species, skin=skin, chunksize=chunksize)
             self.layers = model.layers
             if plan.world > 1:     # one layer: no ghost needs anything but its position
-                self.system.set_owned(self.nlocal, self.nlocal + (plan.n_inner[rank] if self.layers > 1 else 0))
+                ninner = self.nlocal + (plan.n_inner[rank] if self.layers > 1 else 0)
+                if B.comm_size() == plan.world:
+                    self.system.set_exchange(self.n, self.nlocal, ninner, sc, order, rc, plan.recv_index(rank))
+                    self.library_exchange = True
+                else:      # no library communicator (single-process checks): owned / ghost split only
+                    self.system.set_owned(self.nlocal, ninner)
         dev = self.device
         self.d_types = torch.from_numpy(self.types).to(dev)
         self.d_pos = torch.from_numpy(self.pos).to(dev)
@@ -214,7 +233,7 @@ class DistributedSystem:
         """ghost forces back to their owners, energy and virial summed over the ranks"""
         import torch.distributed as dist
         torch = self.torch
-        if self.plan.world == 1:
+        if self.plan.world == 1 or self.library_exchange:
             return
         self.d_fx.view(-1)[3 * self.n + 7:3 * self.n + 12].zero_()    # the unused doubles of the total rows, the scratch row
         send = self.d_fx.index_select(0, self.send_idx)

@@ -158,6 +158,28 @@ int grace_system_release_buffers(grace_system *s);                        /* rel
 int grace_system_stage_ms(const grace_system *s, double *ms5);
 void grace_system_free(grace_system *s);
 
+/* ---- multi-GPU: one process per GPU, NCCL between the processes ----
+ * Extension (kk_api.h is one GPU per process, python/kk/kk_core.cpp:86-98): the reference's multi-GPU runs go through
+ * LAMMPS' ghost atoms with forward / reverse communication around its engine interface
+ * (libgrace/include/grace/system.h:53-64, libgrace/include/grace/kk/grace_2l_kk.h:136-153).  Here a host code splits the
+ * structure into domains, gives every rank its owned atoms followed by a ghost halo of layers x (cutoff + skin), and
+ * the library returns the ghost force rows to their owners and sums energy and virial inside the compute call, on its
+ * own stream (ncclSend / ncclRecv pairs and one 7-value all-reduce; NCCL is loaded at run time from libnccl.so.2).
+ * grace_comm_unique_id: rank 0 fills 128 bytes the caller passes to every rank (any transport);
+ * grace_comm_init: every rank, after grace_initialize; collective.  One communicator per process. */
+int grace_comm_unique_id(void *id128);
+int grace_comm_init(const void *id128, int rank, int world);
+int grace_comm_finalize(void);
+int grace_comm_rank(void);                                                /* -1 without a communicator */
+int grace_comm_size(void);                                                /* 0 without a communicator */
+/* Exchange plan of a decomposed System of n atoms: atoms [0, nlocal) owned, [nlocal, ninner) ghosts whose layer-1
+ * outputs owned atoms read, the rest neighbours only (as grace_system_set_owned).  send_index: indices (into the n atoms)
+ * of the ghost atoms whose force rows leave, grouped by owner rank, send_counts[world] rows per rank; recv_index: for the
+ * rows arriving from rank 0, 1, ... in that order (recv_counts[world]), the owned atom each is added to.  After it, every
+ * compute of the system is collective: forces of owned atoms, energy and virial are the totals of the structure. */
+int grace_system_set_exchange(grace_system *s, int n, int nlocal, int ninner, const int32_t *send_counts,
+                              const int32_t *send_index, const int32_t *recv_counts, const int32_t *recv_index);
+
 /* ---- Batch (kk_api.h:92-156): many structures per engine pass ---- */
 int grace_batch_create(const grace_model *m, const char *const *species, int n_species, int spline, int chunksize,
                        grace_batch **out);                                /* Batch(model, species, spline, chunk) */

@@ -87,11 +87,13 @@ def _nccl_rank(rank, world, port, path, els, out):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         B.initialize(rank)
+        domain.init_library_comm(rank, world)
         types, pos, cell, pbc = structures.crystal("bcc", 3.2, (5, 5, 24), n_species=4, sigma=0.05, seed=22)
         m = B.Model(path)
         cutoff = B.System(m, els).cutoff
         plan = domain.make_plan(pos, cell, pbc, world, m.layers, cutoff, 0.5)
         ds = domain.DistributedSystem(plan, rank, types, pos, species=els, model=m, device=torch.device("cuda", rank))
+        assert ds.library_exchange
         for _ in range(2):
             ds.step()
         torch.cuda.synchronize()
