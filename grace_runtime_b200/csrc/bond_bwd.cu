@@ -9,8 +9,9 @@
 // One block of 4 warps per atom; a lane owns channel n and keeps gQ of its channel in registers; warps (half-warps
 // for C <= 16) take the bonds in turn and reduce the four bond scalars over the channels by shuffles.  The bond force
 // is stored at the bond's slot of the neighbour list (no atomics; forces are gathered afterwards through the
-// reverse-bond index), the virial as one fp64 row per atom.  dE/dmsg rows of the neighbours are the only atomics
-// (fp32 adds into rows shared between the bonds that point at the same neighbour).
+// reverse-bond index), the virial as one fp64 row per atom.  A bond's share of dE/dmsg of its neighbour goes to the
+// bond's slot too and is summed per neighbour by msg_grad_gather_kernel (chain.cu); only when that buffer could not be
+// allocated the shares are added with fp32 atomics, as the reference does.
 #include "bond_common.cuh"
 
 namespace gb {
@@ -28,7 +29,7 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
   __shared__ float4 YG[EBB][NLM];
   __shared__ float su[EBB][4];     // rhat, r
   __shared__ float srci[EBB], st[EBB];
-  __shared__ int sk[EBB], smu[EBB], sj[EBB];
+  __shared__ int sk[EBB], smu[EBB], sj[EBB], scs[EBB];
   __shared__ float fe[EBB][4];     // g (3), dE/dx
   __shared__ double vred[4][6];
 
@@ -54,6 +55,7 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
       float t;
       spline_locate(r / rc, L.N, k, t);
       sk[e] = k; st[e] = t; smu[e] = muj; sj[e] = j;
+      scs[e] = b.cslot[base + b0 + e];
       srci[e] = 1.0f / rc;
       su[e][0] = rec.x * ir; su[e][1] = rec.y * ir; su[e][2] = rec.z * ir; su[e][3] = r;
       float4 *yg = YG[e];
@@ -104,9 +106,8 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
                   dR[l] = (c.y + t * (2.0f * c.z + t * 3.0f * c.w)) * fN;
                 }
               }
-#pragma unroll
-              for (int I = 0; I < NIT; I++) {
-                const int Ig = Ibase + I;
+              if constexpr (NIT == 1) {    // one message function per pass: nothing to contract first
+                const int Ig = Ibase;
                 float m = 0.0f;
                 if (Ig < L.n_msg) m = __ldg(L.msg + ((size_t) j * L.n_msg + Ig) * C + n);
                 else if (Ig == L.n_msg) m = __ldg(L.z + (size_t) muj * C + n);
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
 #pragma unroll
                   for (int q = l * l; q < (l + 1) * (l + 1); q++) {
                     const float4 y4 = yg[q];
-                    const float gq = g[I][q][ch];
+                    const float gq = g[0][q][ch];
                     S = fmaf(y4.x, gq, S);
                     const float p = gq * rm;
                     gx = fmaf(p, y4.y, gx);
@@ -128,7 +129,57 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
                   dedx = fmaf(S * m, dR[l], dedx);
                   gm = fmaf(S, R[l], gm);
                 }
-                if (Ig < L.n_msg) atomicAdd(L.gmsg + ((size_t) j * L.n_msg + Ig) * C + n, gm);
+                if (Ig < L.n_msg) {
+                  if (L.gmsg_slot) L.gmsg_slot[((size_t) scs[e] * L.n_msg + Ig) * C + n] = gm;
+                  else atomicAdd(L.gmsg + ((size_t) j * L.n_msg + Ig) * C + n, gm);
+                }
+              } else {
+                // messages of this tile first, then one contraction over them per lm: h[q] = sum_I msg_I gQ[I][q] carries
+                // everything dE/dx and the direction gradient need, so the harmonics are applied once per bond and
+                // channel instead of once per message function
+                float m[NIT];
+  #pragma unroll
+                for (int I = 0; I < NIT; I++) {
+                  const int Ig = Ibase + I;
+                  m[I] = 0.0f;
+                  if (Ig < L.n_msg) m[I] = __ldg(L.msg + ((size_t) j * L.n_msg + Ig) * C + n);
+                  else if (Ig == L.n_msg) m[I] = __ldg(L.z + (size_t) muj * C + n);
+                }
+  #pragma unroll
+                for (int l = 0; l < NL; l++) {
+                  float T = 0.0f, vx = 0.0f, vy = 0.0f, vz = 0.0f;
+  #pragma unroll
+                  for (int q = l * l; q < (l + 1) * (l + 1); q++) {
+                    float h = 0.0f;
+  #pragma unroll
+                    for (int I = 0; I < NIT; I++) h = fmaf(m[I], g[I][q][ch], h);
+                    const float4 y4 = yg[q];
+                    T = fmaf(y4.x, h, T);
+                    vx = fmaf(h, y4.y, vx);
+                    vy = fmaf(h, y4.z, vy);
+                    vz = fmaf(h, y4.w, vz);
+                  }
+                  dedx = fmaf(T, dR[l], dedx);
+                  gx = fmaf(R[l], vx, gx);
+                  gy = fmaf(R[l], vy, gy);
+                  gz = fmaf(R[l], vz, gz);
+                }
+  #pragma unroll
+                for (int I = 0; I < NIT; I++) {    // dE/dmsg_I = sum_l R_l sum_{m} Y_lm gQ[I][lm]
+                  const int Ig = Ibase + I;
+                  if (Ig < L.n_msg) {
+                    float gm = 0.0f;
+  #pragma unroll
+                    for (int l = 0; l < NL; l++) {
+                      float S = 0.0f;
+  #pragma unroll
+                      for (int q = l * l; q < (l + 1) * (l + 1); q++) S = fmaf(yg[q].x, g[I][q][ch], S);
+                      gm = fmaf(S, R[l], gm);
+                    }
+                    if (L.gmsg_slot) L.gmsg_slot[((size_t) scs[e] * L.n_msg + Ig) * C + n] = gm;
+                    else atomicAdd(L.gmsg + ((size_t) j * L.n_msg + Ig) * C + n, gm);
+                  }
+                }
               }
             }
           }
@@ -154,7 +205,7 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
       const float f0 = dEdr * ux + (gxx - gr * ux) * ir;
       const float f1 = dEdr * uy + (gyy - gr * uy) * ir;
       const float f2 = dEdr * uz + (gzz - gr * uz) * ir;
-      float *o = fv + 3 * (size_t) b.cslot[base + b0 + e];
+      float *o = fv + 3 * (size_t) scs[e];
       if (add) { o[0] += f0; o[1] += f1; o[2] += f2; }
       else { o[0] = f0; o[1] = f1; o[2] = f2; }
       const double dx = -(double) ux * r, dy = -(double) uy * r, dz = -(double) uz * r;

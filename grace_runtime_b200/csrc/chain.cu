@@ -482,6 +482,40 @@ void launch_force_gather(const long long *off, const int *rev, const float *fv, 
   GB_LAUNCH(force_gather_kernel, (n + 3) / 4, 128, 0, off, rev, fv, perm, forces, n);
 }
 
+// one warp per atom j: lanes over the `width` floats of a row, the atom's bonds one after the other
+__global__ void __launch_bounds__(128) msg_grad_gather_kernel(BondsDev b, const int *__restrict__ rev,
+                                                              const float *__restrict__ gslot, float *gmsg, int width,
+                                                              const int *__restrict__ ilist, long long n,
+                                                              const int *__restrict__ perm, int nlocal)
+{
+  const long long a = (long long) blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  const int lane = threadIdx.x & 31;
+  if (a >= n) return;
+  const long long j = ilist ? ilist[a] : a;
+  const long long base = b.off[j];
+  const int nb = b.cnt[j];
+  for (int c0 = 0; c0 < width; c0 += 128) {    // 4 floats per lane and pass
+    const int c = c0 + 4 * lane;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < width) {
+      for (int e = 0; e < nb; e++) {
+        if (perm && perm[__float_as_int(b.rec[base + e].w)] >= nlocal) continue;
+        const size_t p = (size_t) rev[b.cslot[base + e]];
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(gslot + p * width + c));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      *reinterpret_cast<float4 *>(gmsg + (size_t) j * width + c) = acc;
+    }
+  }
+}
+
+void launch_msg_grad_gather(const BondsDev &b, const int *rev, const float *gslot, float *gmsg, int width, const int *ilist,
+                            long long n, const int *perm, int nlocal)
+{
+  if (n == 0) return;
+  GB_LAUNCH(msg_grad_gather_kernel, (unsigned) ((n + 3) / 4), 128, 0, b, rev, gslot, gmsg, width, ilist, n, perm, nlocal);
+}
+
 // ---- per-structure sums (deterministic: fixed tree per segment) ------------------------------------------------
 // one block per (segment, component)
 __global__ void __launch_bounds__(256) segment_sum_kernel(const double *__restrict__ v, int K,

@@ -209,6 +209,7 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   rcsq_.set_label("engine:cutoffs"); eW_.set_label("engine:energy_mlp"); shift_.set_label("engine:shift");
   lnI_.set_label("engine:norm_scale"); ln0_.set_label("engine:norm_scale"); rcf_.set_label("engine:cutoffs");
   arena_.set_label("work:chunk_tensors"); fv_.set_label("work:bond_forces"); I_rows_.set_label("work:messages");
+  gmsg_slot_.set_label("work:message_gradient_shares");
   gI_rows_.set_label("work:message_gradients"); rho_rows_.set_label("work:rho"); e_atom_.set_label("work:atom_energy");
   vir_atom_.set_label("work:atom_virial"); sum_scratch_.set_label("work:sums"); grho_rows_.set_label("work:rho_gradients");
   rcsq_.upload(P.rcsq);
@@ -306,7 +307,7 @@ void Engine::release_work()
 {
   arena_.release(); fv_.release(); I_rows_.release(); gI_rows_.release(); rho_rows_.release();
   e_atom_.release(); vir_atom_.release(); grho_rows_.release(); sum_scratch_.release();
-  xs_.release(); R1_.release(); dR1_.release(); R2_.release(); dR2_.release(); l1_saved_.release();
+  xs_.release(); R1_.release(); dR1_.release(); R2_.release(); dR2_.release(); l1_saved_.release(); gmsg_slot_.release();
   arena_NA_ = 0;
 }
 
@@ -326,6 +327,7 @@ LayerDev Engine::layer_dev(const LayerEngine &E) const
   L.rc = rcf_.get();
   L.msg = nullptr;
   L.gmsg = nullptr;
+  L.gmsg_slot = nullptr;
   L.N = E.plan->radial.N;
   L.C = E.plan->C;
   L.n_msg = E.plan->n_msg;
@@ -333,6 +335,40 @@ LayerDev Engine::layer_dev(const LayerEngine &E) const
   L.Rex = exact_ ? (&E == &L1_ ? R1_.get() : R2_.get()) : nullptr;
   L.dRex = exact_ ? (&E == &L1_ ? dR1_.get() : dR2_.get()) : nullptr;
   return L;
+}
+
+namespace {
+struct TagScope {
+  bool on;
+  TagScope(const char *t) : on(getenv("GRACE_B200_PROFILE_OPS") != nullptr) { if (on) launch_tag(t); }
+  ~TagScope() { if (on) launch_tag(nullptr); }
+};
+}    // namespace
+
+// Buffer for the per-bond shares of dE/dmsg (one row of n_msg x C floats per list slot), when it can be had: the
+// reverse bond kernel of layer 2 then stores instead of adding atomically and gather_message_gradients() sums the shares
+// per neighbour in list order.  Null (the buffer does not fit): fp32 atomics into the zeroed rows, as the reference does.
+float *Engine::message_gradient_slots(NeighborList &nl)
+{
+  const size_t need = (size_t) std::max<int64_t>(nl.nslots(), 1) * plan_.nI * plan_.cr;
+  cudaStream_t st = dev().stream;
+  float *p = nullptr;
+  if (!getenv("GRACE_B200_MSG_ATOMICS")) {
+    try {
+      p = gmsg_slot_.ensure(need);
+    } catch (const OutOfMemory &) {
+      p = nullptr;
+    }
+  }
+  if (!p) GB_CUDA(cudaMemsetAsync(gI_rows_.get(), 0, sizeof(float) * (size_t) nl.n() * plan_.nI * plan_.cr, st));
+  return p;
+}
+
+void Engine::gather_message_gradients(NeighborList &nl, const float *slots, const ActiveRanges &R)
+{
+  if (!slots) return;
+  launch_msg_grad_gather(nl.bonds(), nl.rev(), slots, gI_rows_.get(), plan_.nI * plan_.cr, nullptr, (long long) nl.n(),
+                         R.nlocal >= 0 ? nl.perm() : nullptr, R.nlocal);
 }
 
 void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA)
@@ -578,15 +614,17 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   const int nI = P.nI, CR = P.cr, nrho = P.nrho;
   I_rows_.ensure((size_t) n * nI * CR);
   rho_rows_.ensure((size_t) n * nrho);
+  float *gslots = nullptr;
   if (!energy_only) {
     gI_rows_.ensure((size_t) n * nI * CR);
     grho_rows_.ensure((size_t) n * nrho);
-    GB_CUDA(cudaMemsetAsync(gI_rows_.get(), 0, sizeof(float) * (size_t) n * nI * CR, st));
+    gslots = message_gradient_slots(nl);
   }
   const LayerDev La = layer_dev(L1_);
   LayerDev Lb = layer_dev(L2_);
   Lb.msg = I_rows_.get();
   Lb.gmsg = gI_rows_.get();
+  Lb.gmsg_slot = gslots;
   const float *gQ1 = arena_.get() + (size_t) L1_.q_floats * NA, *gQ2 = arena_.get() + (size_t) L2_.q_floats * NA;
   if (tm) tm->begin(StageTimer::FWD);
   // the layer-1 tensors its reverse pass reads are kept in global memory between the passes when they fit (else layer
@@ -613,6 +651,7 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   if (tm) tm->end(StageTimer::FWD);
   if (energy_only) return;
   if (tm) tm->begin(StageTimer::BWD);
+  gather_message_gradients(nl, gslots, R);
   for (int64_t a0 = 0; a0 < n1; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
     const int na = (int) std::min<int64_t>(NA, n1 - a0);
     if (!saved) launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
@@ -666,20 +705,22 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     const int nI = P.nI, CR = P.cr, nrho = P.nrho;
     I_rows_.ensure((size_t) n * nI * CR);
     rho_rows_.ensure((size_t) n * nrho);
+    float *gslots = nullptr;
     if (!energy_only) {
       gI_rows_.ensure((size_t) n * nI * CR);
       grho_rows_.ensure((size_t) n * nrho);
-      GB_CUDA(cudaMemsetAsync(gI_rows_.get(), 0, sizeof(float) * (size_t) n * nI * CR, st));
+      gslots = message_gradient_slots(nl);
     }
     const LayerDev La = layer_dev(L1_);
     LayerDev Lb = layer_dev(L2_);
     Lb.msg = I_rows_.get();
     Lb.gmsg = gI_rows_.get();
+    Lb.gmsg_slot = gslots;
     // layer 1 forward of every chunk: messages I and rho of all atoms
     if (tm) tm->begin(StageTimer::FWD);
     for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {
       const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
-      launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
+      { TagScope tg("layer1"); launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na); }
       run(L1_, P.L1.fwd, mu + a0, na);
       launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, NA, na, (int) a0);
       launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, NA, na, (int) a0);
@@ -689,7 +730,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
       const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
       if (tm) tm->begin(StageTimer::FWD);
-      launch_bond_fwd(P.lmax, bonds, Lb, T2(P.L2.tQ), NA, (int) a0, na);
+      { TagScope tg("layer2"); launch_bond_fwd(P.lmax, bonds, Lb, T2(P.L2.tQ), NA, (int) a0, na); }
       run(L2_, P.L2.fwd, mu + a0, na);
       launch_readout_2l(readout_, rho_rows_.get(), T2(P.t2_I2), grho_rows_.get(), T2(P.t2_gI2), mu, e_atom_.get(), NA,
                         na, (int) a0, !energy_only);
@@ -698,12 +739,13 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       if (tm) tm->begin(StageTimer::BWD);
       zero_grads(L2_);
       run(L2_, P.L2.bwd, mu + a0, na);
-      launch_bond_bwd(P.lmax, bonds, Lb, T2(P.L2.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0);
+      { TagScope tg("layer2"); launch_bond_bwd(P.lmax, bonds, Lb, T2(P.L2.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0); }
       if (tm) tm->end(StageTimer::BWD);
     }
     // layer 1 again (recomputed) and its reverse, seeded with dE/dI and dE/drho of each atom
     if (!energy_only) {
       if (tm) tm->begin(StageTimer::BWD);
+      gather_message_gradients(nl, gslots, R);
       for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {
         const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
         launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
@@ -712,7 +754,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
         launch_chunk_from_rows(T1(P.t1_gI), gI_rows_.get(), nI, CR, NA, na, (int) a0);
         launch_chunk_from_rows_f64(T1(P.t1_grho), grho_rows_.get(), 1, nrho, NA, na, (int) a0);
         run(L1_, P.L1.bwd, mu + a0, na);
-        launch_bond_bwd(P.lmax, bonds, La, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 1);
+        { TagScope tg("layer1"); launch_bond_bwd(P.lmax, bonds, La, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 1); }
       }
       if (tm) tm->end(StageTimer::BWD);
     }

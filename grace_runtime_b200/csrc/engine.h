@@ -94,7 +94,9 @@ class Engine {
   DBuf<float> rcf_;
   ReadoutDev readout_{};
   // work buffers
-  DBuf<float> arena_, fv_, I_rows_, gI_rows_, rho_rows_;
+  DBuf<float> arena_, fv_, I_rows_, gI_rows_, rho_rows_, gmsg_slot_;
+  float *message_gradient_slots(NeighborList &nl);
+  void gather_message_gradients(NeighborList &nl, const float *slots, const ActiveRanges &R);
   DBuf<double> e_atom_, vir_atom_, grho_rows_, sum_scratch_;
   int arena_NA_ = 0;
   void setup_layer(LayerEngine &E, const LayerPlan &P);

@@ -52,7 +52,9 @@ struct LayerDev {
   const float *z;          // [n_elements][C]
   const float *rc;         // [n_elements][n_elements] pair cutoffs
   const float *msg;        // [n][n_msg][C] message rows of all atoms (layer 2) or null
-  float *gmsg;             // [n][n_msg][C] dE/dmsg rows, added to atomically by the reverse bond kernel
+  float *gmsg;             // [n][n_msg][C] dE/dmsg rows, added to atomically by the reverse bond kernel when gmsg_slot is null
+  float *gmsg_slot;        // [list slots][n_msg][C]: each bond's share of dE/dmsg of its neighbour, stored at the bond's slot
+                           // and summed per neighbour afterwards through the reverse-bond index (no atomics)
   int N, C, n_msg, n_elements;
   // exact radial MLP instead of the tables: value and d/dx per list slot, [slot][l][C] (null: tables)
   const float *Rex, *dRex;
@@ -156,6 +158,11 @@ void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, 
 void launch_chunk_from_rows(float *t, const float *rows, int nf, int C, int NA, int na, int a0);
 void launch_chunk_from_rows_f64(float *t, const double *rows, int nf, int C, int NA, int na, int a0);
 
+// gmsg[j] = sum over the bonds e of atom j inside the cutoff of gslot[rev[slot of e]]: the shares the bonds i -> j stored,
+// added in the order of j's own list (bit-reproducible).  width = n_msg * C floats per row.  perm / nlocal (optional):
+// bonds whose other atom is a ghost (perm[i] >= nlocal) are left out - its layer was not evaluated, its slots hold nothing
+void launch_msg_grad_gather(const BondsDev &b, const int *rev, const float *gslot, float *gmsg, int width, const int *ilist,
+                            long long n, const int *perm, int nlocal);
 // F_i = sum over the slots q of atom i of fv[q] - fv[rev[q]], written at the caller's index of atom i
 void launch_force_gather(const long long *off, const int *rev, const float *fv, const int *perm, double *forces,
                          int n);

@@ -122,8 +122,7 @@ def test_deterministic_and_symmetric(backend, models, cells, name):
     a = _compute(backend, m, c)
     b = _compute(backend, m, c)
     assert a["energy"] == b["energy"]
-    if "_1l_" in name:      # no atomics anywhere on the GRACE-1L path: bit-identical forces
-        assert np.array_equal(a["forces"], b["forces"])
+    assert np.array_equal(a["forces"], b["forces"])      # no atomics on either path: bit-identical forces
     assert np.abs(a["forces"].sum(0)).max() < 1e-5          # Newton's third law
     # translation along a periodic direction and permutation of the atoms
     shift = np.array([1.234, -7.5, 0.0])
