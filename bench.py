@@ -119,6 +119,23 @@ def algorithmic_bytes(kernel, model_cfg, n_atoms, n_bonds, slots):
     return None
 
 
+def bond_flops(kernel, model_cfg, n_bonds, launches_per_step):
+    """Useful fp32 flops of the bond kernels per step: 2 nlm C NIT per bond forward (Y R msg accumulated into the
+    A-basis), 2 nlm C (1 + 3) NIT per bond reverse (dE/dx and the three components of the direction gradient), summed
+    over the layers; NIT = message functions coupled in (layer 2: I_n_funcs + the chemical one)."""
+    c = modelgen.CONFIGS[model_cfg]
+    nlm = (c["lmax"] + 1) ** 2
+    per = [(c["c1"], 1)] + ([(c["cr"], 5)] if c["layers"] == 2 else [])
+    if kernel == "bond_bwd_kernel":
+        return n_bonds * sum(2.0 * nlm * C * 4 * nit for C, nit in per)
+    if kernel == "bond_fwd_kernel":
+        fl = [2.0 * nlm * C * nit for C, nit in per]
+        # GRACE-2L on the per-operation path evaluates layer 1 once more for its reverse pass: launches tell
+        extra = fl[0] if (c["layers"] == 2 and launches_per_step >= 3) else 0.0
+        return n_bonds * (sum(fl) + extra)
+    return None
+
+
 def run_batch(args, rank, world, local_rank):
     """Batches of small structures: sharded by structure over the ranks (greedy by atom count), no data-path
     collective; `value` = max-over-ranks time per step x n_gpus / total atoms."""
@@ -549,6 +566,19 @@ def run_ours(args, rank, world, local_rank):
                 "launches_per_step": lps,
                 "note": "dense-network kernel: shared-memory resident, compute-bound (not HBM-bound); useful fp32-equivalent "
                         "flops of the plan / average launch time"}
+    elif top.startswith("bond_"):
+        # bond kernels: table look-ups from L1 / L2 and fp32 arithmetic per bond and channel - issue-bound, not HBM-bound
+        # (their HBM fraction is in hbm_kernels); all launches of a step together (GRACE-2L: both layers)
+        lps = top_n / args.steps
+        flop = bond_flops(top, wl["cfg"], n_bonds, lps)
+        ach = flop / (top_ms / args.steps * 1e-3) / 1e12
+        peak_tf = peaks_here["fp32_simt_tflops"]
+        roof = {"bound": "fp32", "kernel": top, "peak": peak_tf, "peak_source": "fp32 FFMA microbenchmark of this run (measured in this run)",
+                "unit": "TFLOP/s", "achieved": ach, "frac": ach / peak_tf, "traffic": traffic_of(top, lps),
+                "algorithmic_bytes_per_launch": (algorithmic_bytes(top, wl["cfg"], n_own, n_bonds, slots) or 0.0) / lps,
+                "flop_per_step": flop, "ms_per_step": top_ms / args.steps, "launches_per_step": lps,
+                "note": "useful flops per bond from the A-basis / reverse-pass formulas x bonds inside the cutoff / time of the "
+                        "kernel's launches of a step"}
     else:
         roof = {"bound": "hbm", "kernel": top, "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "traffic": None}
         ab = algorithmic_bytes(top, wl["cfg"], n_own, n_bonds, slots)
