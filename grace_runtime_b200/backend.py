@@ -71,6 +71,11 @@ SIGNATURES = {
     "grace_system_release_buffers": (_I, [_P]),
     "grace_system_stage_ms": (_I, [_P, _P]),
     "grace_system_free": (None, [_P]),
+    "grace_engine_create": (_I, [_P, _P, _I, _I, _I, _P]),
+    "grace_engine_cutoff": (_D, [_P]),
+    "grace_engine_comm_width": (_I, [_P]),
+    "grace_engine_run": (_I, [_P, _P, _P, _P, _P, _P]),
+    "grace_engine_free": (None, [_P]),
     "grace_batch_create": (_I, [_P, _P, _I, _I, _I, _P]),
     "grace_batch_cutoff": (_D, [_P]),
     "grace_batch_compute": (_I, [_P, _I, _P, _I64, _P, _P, _P, _P, _I, _I64, _P, _P, _P, _P]),
@@ -234,9 +239,10 @@ def comm_size():
 
 
 def measure_peak(kind):
-    """TFLOP/s of a microbenchmark on the module's GPU: "fp32" (SIMT FMA lanes) or "tf32" (tcgen05 tensor cores)."""
+    """TFLOP/s of a microbenchmark on the module's GPU: "fp32" (SIMT FMA lanes), "tf32" (tcgen05 tensor cores, M = 128,
+    N = 256) or an int N (the tf32 one with that N)."""
     v = C.c_double(0.0)
-    _check(load_library().grace_measure_peak({"fp32": 0, "tf32": 1}[kind], C.addressof(v)))
+    _check(load_library().grace_measure_peak({"fp32": 0, "tf32": 1}.get(kind, kind), C.addressof(v)))
     return v.value
 
 
@@ -528,6 +534,67 @@ class System:
         bi, bj, bs = np.zeros(nb, np.int32), np.zeros(nb, np.int32), np.zeros((nb, 3), np.int32)
         _check(_lib.grace_system_neighbor_list(self._h, nb, _ptr(bi), _ptr(bj), _ptr(bs), C.addressof(cnt)))
         return bi.astype(np.int64), bj.astype(np.int64), bs.astype(np.int64)
+
+
+EXCHANGE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p)    # (user, d_rows, width, stream)
+
+
+class RunInput(C.Structure):
+    """grace_run_input of include/grace_b200.h"""
+    _fields_ = [("nlocal", C.c_int), ("nall", C.c_int), ("d_type", C.c_void_p), ("d_x", C.c_void_p),
+                ("d_numneigh", C.c_void_p), ("d_neighbors", C.c_void_p), ("maxneigh", C.c_int), ("flags", C.c_int),
+                ("forward", EXCHANGE_FN), ("reverse", EXCHANGE_FN), ("user", C.c_void_p)]
+
+
+class Engine:
+    """The engine interface for callers with their own neighbour list and ghost atoms (RunInput / RunOutput / Exchange of
+    libgrace/include/grace/kk/grace_2l_kk.h:87-119): `run` adds forces to f [nall, 3] (ghost rows included) and per-atom
+    energies to eatom [nlocal], and returns (energy, virial[6]) of the local atoms.  forward / reverse: callables
+    (rows_address, width, stream_address) for the message rows of GRACE-2L."""
+
+    def __init__(self, model, species, spline=1024, chunksize=-1):
+        lib = load_library()
+        h = C.c_void_p()
+        self._model = model
+        _check(lib.grace_engine_create(model._h, _names(species), len(species), int(spline), int(chunksize), C.addressof(h)))
+        self._h = h
+
+    def __del__(self):
+        if getattr(self, "_h", None) and _lib is not None:
+            _lib.grace_engine_free(self._h)
+            self._h = None
+
+    @property
+    def cutoff(self):
+        return _lib.grace_engine_cutoff(self._h)
+
+    @property
+    def comm_width(self):
+        return _lib.grace_engine_comm_width(self._h)
+
+    def run(self, nlocal, nall, types, x, numneigh, neighbors, maxneigh, f, eatom=None, forward=None, reverse=None,
+            energy_only=False):
+        errors = []
+
+        def wrap(fn):
+            def call(user, rows, width, stream):
+                try:
+                    fn(rows, width, stream)
+                except Exception as e:      # an exception must not cross the C frames
+                    errors.append(e)
+            return EXCHANGE_FN(call) if fn else C.cast(None, EXCHANGE_FN)
+        fw, rv = wrap(forward), wrap(reverse)
+        inp = RunInput(int(nlocal), int(nall), _dev_ptr(types, "types", np.int32, (nall,)),
+                       _dev_ptr(x, "x", np.float64, (nall, 3)), _dev_ptr(numneigh, "numneigh", np.int32, (nlocal,)),
+                       _dev_ptr(neighbors, "neighbors", np.int32, (nlocal, maxneigh)), int(maxneigh),
+                       FLAG_ENERGY_ONLY if energy_only else 0, fw, rv, None)
+        e, v = np.zeros(1), np.zeros(6)
+        _check(_lib.grace_engine_run(self._h, C.addressof(inp), _ptr(e), _ptr(v),
+                                     _dev_ptr(f, "f", np.float64, (nall, 3), optional=energy_only),
+                                     _dev_ptr(eatom, "eatom", np.float64, (nlocal,), optional=True)))
+        if errors:
+            raise errors[0]
+        return float(e[0]), v
 
 
 class Batch:

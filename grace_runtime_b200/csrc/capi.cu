@@ -21,6 +21,9 @@ struct grace_system {
 struct grace_batch {
   std::unique_ptr<BatchObj> b;
 };
+struct grace_engine {
+  std::unique_ptr<EngineRunObj> e;
+};
 
 namespace {
 
@@ -28,6 +31,7 @@ thread_local std::string g_error;
 std::recursive_mutex g_device_mu;    // all device work of the process is serialised (kk_core.cpp:58-63)
 std::set<grace_system *> g_systems;
 std::set<grace_batch *> g_batches;
+std::set<grace_engine *> g_engines;
 
 template<class F> int guarded(F &&f)
 {
@@ -114,6 +118,8 @@ int grace_finalize(void)
       if (s->s) s->s->release();
     for (auto *b : g_batches)
       if (b->b) b->b->release();
+    for (auto *e : g_engines)
+      if (e->e) e->e->release();
     comm_finalize();
     cudaStreamSynchronize(d.stream);
     cudaStreamDestroy(d.stream);
@@ -180,7 +186,8 @@ int grace_measure_peak(int kind, double *tflops)
     if (!tflops) throw InvalidArgument("tflops must be given");
     if (kind == 0) *tflops = measure_peak_fp32_tflops();
     else if (kind == 1) *tflops = measure_peak_tf32_tflops();
-    else throw InvalidArgument("kind must be 0 (fp32 FMA) or 1 (tf32 tensor cores)");
+    else if (kind >= 16) *tflops = measure_peak_tf32_tflops(kind);    // the same with N = kind instead of 256
+    else throw InvalidArgument("kind must be 0 (fp32 FMA), 1 (tf32 tensor cores, N = 256) or N (a multiple of 16 up to 256)");
   });
 }
 
@@ -367,6 +374,41 @@ void grace_system_free(grace_system *s)
   if (!s) return;
   g_systems.erase(s);
   delete s;
+}
+
+int grace_engine_create(const grace_model *m, const char *const *species, int n_species, int spline, int chunksize,
+                        grace_engine **out)
+{
+  return guarded([&] {
+    if (!m || !out) throw InvalidArgument("model and out must be given");
+    auto e = std::make_unique<EngineRunObj>(m->m, names(species, n_species), spline, chunksize);
+    *out = new grace_engine{std::move(e)};
+    g_engines.insert(*out);
+  });
+}
+
+double grace_engine_cutoff(const grace_engine *e) { return e ? e->e->cutoff() : 0.0; }
+int grace_engine_comm_width(const grace_engine *e) { return e ? e->e->comm_width() : 0; }
+
+int grace_engine_run(grace_engine *e, const grace_run_input *in, double *energy, double *virial6, double *d_f, double *d_eatom)
+{
+  return guarded([&] {
+    if (!e || !in) throw InvalidArgument("engine and input must be given");
+    ExchangeHooks h;
+    h.forward = in->forward;
+    h.reverse = in->reverse;
+    h.user = in->user;
+    e->e->run(in->nlocal, in->nall, in->d_type, in->d_x, in->d_numneigh, in->d_neighbors, in->maxneigh, in->flags, h, energy,
+              virial6, d_f, d_eatom);
+  });
+}
+
+void grace_engine_free(grace_engine *e)
+{
+  std::lock_guard<std::recursive_mutex> lk(g_device_mu);
+  if (!e) return;
+  g_engines.erase(e);
+  delete e;
 }
 
 int grace_batch_create(const grace_model *m, const char *const *species, int n_species, int spline, int chunksize,

@@ -516,6 +516,54 @@ void launch_msg_grad_gather(const BondsDev &b, const int *rev, const float *gslo
   GB_LAUNCH(msg_grad_gather_kernel, (unsigned) ((n + 3) / 4), 128, 0, b, rev, gslot, gmsg, width, ilist, n, perm, nlocal);
 }
 
+// one warp per atom with bonds: own sum by shuffles, neighbours by atomics
+__global__ void __launch_bounds__(128) force_scatter_kernel(BondsDev b, const float *__restrict__ fv, double *forces, long long n)
+{
+  const long long i = (long long) blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  const int lane = threadIdx.x & 31;
+  if (i >= n) return;
+  const long long base = b.off[i];
+  const int nb = b.cnt[i];
+  double f0 = 0.0, f1 = 0.0, f2 = 0.0;
+  for (int e = lane; e < nb; e += 32) {
+    const size_t q = (size_t) b.cslot[base + e];
+    const size_t j = (size_t) __float_as_int(b.rec[base + e].w);
+    const double x = fv[3 * q], y = fv[3 * q + 1], z = fv[3 * q + 2];
+    f0 += x; f1 += y; f2 += z;
+    atomicAdd(forces + 3 * j, -x);
+    atomicAdd(forces + 3 * j + 1, -y);
+    atomicAdd(forces + 3 * j + 2, -z);
+  }
+  for (int s = 16; s > 0; s >>= 1) {
+    f0 += __shfl_xor_sync(0xffffffffu, f0, s);
+    f1 += __shfl_xor_sync(0xffffffffu, f1, s);
+    f2 += __shfl_xor_sync(0xffffffffu, f2, s);
+  }
+  if (lane == 0 && nb > 0) {
+    atomicAdd(forces + 3 * (size_t) i, f0);
+    atomicAdd(forces + 3 * (size_t) i + 1, f1);
+    atomicAdd(forces + 3 * (size_t) i + 2, f2);
+  }
+}
+
+void launch_force_scatter(const BondsDev &b, const float *fv, double *forces, long long n)
+{
+  if (n == 0) return;
+  GB_LAUNCH(force_scatter_kernel, (unsigned) ((n + 3) / 4), 128, 0, b, fv, forces, n);
+}
+
+__global__ void __launch_bounds__(256) add_f64_kernel(const double *__restrict__ v, double *out, long long n)
+{
+  const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] += v[i];
+}
+
+void launch_add_f64(const double *v, double *out, long long n)
+{
+  if (n == 0) return;
+  GB_LAUNCH(add_f64_kernel, (unsigned) ((n + 255) / 256), 256, 0, v, out, n);
+}
+
 // ---- per-structure sums (deterministic: fixed tree per segment) ------------------------------------------------
 // one block per (segment, component)
 __global__ void __launch_bounds__(256) segment_sum_kernel(const double *__restrict__ v, int K,

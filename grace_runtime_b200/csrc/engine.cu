@@ -353,7 +353,7 @@ float *Engine::message_gradient_slots(NeighborList &nl)
   const size_t need = (size_t) std::max<int64_t>(nl.nslots(), 1) * plan_.nI * plan_.cr;
   cudaStream_t st = dev().stream;
   float *p = nullptr;
-  if (!getenv("GRACE_B200_MSG_ATOMICS")) {
+  if (!getenv("GRACE_B200_MSG_ATOMICS") && !nl.external()) {
     try {
       p = gmsg_slot_.ensure(need);
     } catch (const OutOfMemory &) {
@@ -642,6 +642,7 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
     launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
     run_fused(L1_, FUSED_STORE_MSG | (saved ? FUSED_SAVE : 0), NA, (int) a0, na, mu, R.list1, saved);
   }
+  call_hook(true);
   for (int64_t a0 = 0; a0 < n0; a0 += NA) {    // layer 2, energy, layer-2 reverse
     const int na = (int) std::min<int64_t>(NA, n0 - a0);
     launch_bond_fwd(P.lmax, b0, Lb, Q, NA, (int) a0, na);
@@ -652,6 +653,7 @@ void Engine::evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTim
   if (energy_only) return;
   if (tm) tm->begin(StageTimer::BWD);
   gather_message_gradients(nl, gslots, R);
+  call_hook(false);
   for (int64_t a0 = 0; a0 < n1; a0 += NA) {    // layer 1 recomputed and reversed from dE/dI, dE/drho
     const int na = (int) std::min<int64_t>(NA, n1 - a0);
     if (!saved) launch_bond_fwd(P.lmax, b1, La, Q, NA, (int) a0, na);
@@ -726,6 +728,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, NA, na, (int) a0);
     }
     if (tm) tm->end(StageTimer::FWD);
+    call_hook(true);
     // layer 2 forward, energy and layer-2 reverse per chunk
     for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
       const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
@@ -746,6 +749,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     if (!energy_only) {
       if (tm) tm->begin(StageTimer::BWD);
       gather_message_gradients(nl, gslots, R);
+      call_hook(false);
       for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {
         const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
         launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
@@ -794,9 +798,20 @@ ActiveRanges Engine::active_ranges(NeighborList &nl, int nlocal, int ninner, DBu
   return R;
 }
 
-void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm,
-                      const ActiveRanges *act)
+void Engine::call_hook(bool forward)
 {
+  if (!hooks_) return;
+  auto fn = forward ? hooks_->forward : hooks_->reverse;
+  if (!fn) return;
+  cudaStream_t st = dev().stream;
+  GB_CUDA(cudaStreamSynchronize(st));
+  fn(hooks_->user, forward ? I_rows_.get() : gI_rows_.get(), plan_.nI * plan_.cr, (void *) st);
+}
+
+void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm,
+                      const ActiveRanges *act, const ExchangeHooks *hooks)
+{
+  hooks_ = plan_.layers == 2 ? hooks : nullptr;
   const int64_t n = nl.n();
   const int nsys = nl.nsys();
   ActiveRanges R;
@@ -876,7 +891,10 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
   if (out.energies) launch_scatter_f64(e_atom_.get(), nl.perm(), out.energies, (int) n);
   if (!energy_only) {
     if (out.virial) launch_segment_sum(vir_atom_.get(), 6, nl.seg(), nsys, out.virial, scr, nb);
-    if (out.forces) launch_force_gather(nl.off(), nl.rev(), fv, nl.perm(), out.forces, (int) n);
+    if (out.forces) {
+      if (nl.external()) launch_force_scatter(nl.bonds(), fv, out.forces, (long long) n);    // accumulates
+      else launch_force_gather(nl.off(), nl.rev(), fv, nl.perm(), out.forces, (int) n);
+    }
   }
 }
 
@@ -1106,6 +1124,73 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     have_list_ = false;
     throw InvalidArgument("two atoms at the same position (a bond of length 0): not a physical structure");
   }
+}
+
+// ---- engine interface with the caller's list -------------------------------------------------------------------
+EngineRunObj::EngineRunObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &species, int spline, int chunk)
+    : model_(std::move(m)), chunk_req_(chunk)
+{
+  require_initialized();
+  t2m_ = species_to_elements(model_->model, species);
+  engine_ = model_->get_engine(model_->effective_spline(spline));
+  cutoff_ = 0.0;
+  for (int a : t2m_)
+    for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));
+  label_ws(ws_);
+}
+
+int EngineRunObj::comm_width() const { return engine_->plan().layers == 2 ? engine_->plan().nI * engine_->plan().cr : 0; }
+
+void EngineRunObj::release()
+{
+  nl_.release();
+  ws_ = Workspace{};
+  label_ws(ws_);
+  engine_->release_work();
+}
+
+void EngineRunObj::run(int nlocal, int nall, const int *d_type, const double *d_x, const int *d_numneigh,
+                       const int *d_neighbors, int maxneigh, int flags, const ExchangeHooks &hooks, double *energy,
+                       double *virial6, double *d_f, double *d_eatom)
+{
+  require_initialized();
+  check_flags(flags);
+  if (nlocal < 0 || nall < nlocal) throw InvalidArgument("nlocal must be in 0 .. nall");
+  if (nall > 0 && (!d_type || !d_x)) throw InvalidArgument("types and positions must be given");
+  const bool eonly = flags & 2;
+  if (!eonly && nall > 0 && !d_f) throw InvalidArgument("the force array must be given");
+  std::lock_guard<std::mutex> lk(engine_->mu);
+  cudaStream_t st = dev().stream;
+  const int n = nall, ns = (int) t2m_.size();
+  ws_.flag.ensure(1);
+  GB_CUDA(cudaMemsetAsync(ws_.flag.get(), 0, sizeof(int), st));
+  ws_.energy.ensure(1);
+  ws_.virial.ensure(6);
+  OutputsDev o;
+  o.energy = ws_.energy.get();
+  if (!eonly) {
+    o.virial = ws_.virial.get();
+    o.forces = d_f;
+  }
+  if (d_eatom) o.energies = ws_.energies.ensure(std::max(n, 1));
+  if (n > 0) {
+    ws_.mu.ensure(n);
+    ws_.t2m.upload(t2m_);
+    GB_LAUNCH(types_to_mu, nblocks(n, 256), 256, 0, d_type, ws_.t2m.get(), ns, ws_.mu.get(), ws_.flag.get(), (long long) n);
+    if (read_int(ws_.flag.get()) & 1) throw InvalidArgument("types must be 1 .. len(species)");
+  }
+  nl_.adopt(nlocal, nall, ws_.mu.get(), d_numneigh, d_neighbors, maxneigh);
+  ActiveRanges ranges = engine_->active_ranges(nl_, nlocal, nlocal, list0_, list1_);
+  float *fv = engine_->bond_forces(nl_.nslots());
+  nl_.prepare(d_x, engine_->rcsq(), model_->model.n_elements, fv);
+  const int chunk = chunk_req_ < 0 ? engine_->auto_chunk(std::max(nlocal, 1)) : chunk_req_;
+  engine_->evaluate(nl_, eonly, o, chunk, nullptr, &ranges, &hooks);
+  if (d_eatom && nlocal > 0) launch_add_f64(o.energies, d_eatom, nlocal);
+  if (energy) GB_CUDA(cudaMemcpyAsync(energy, o.energy, sizeof(double), cudaMemcpyDeviceToHost, st));
+  if (virial6 && !eonly) GB_CUDA(cudaMemcpyAsync(virial6, o.virial, sizeof(double) * 6, cudaMemcpyDeviceToHost, st));
+  const int fl = n > 0 ? nl_.take_flag() : 0;    // synchronises the stream
+  GB_CUDA(cudaStreamSynchronize(st));
+  if (fl & 2) throw InvalidArgument("two atoms at the same position (a bond of length 0): not a physical structure");
 }
 
 // ---- batch -----------------------------------------------------------------------------------------------------

@@ -60,6 +60,18 @@ struct ActiveRanges {
   int64_t n0 = 0, n1 = 0;
 };
 
+// Message exchange of a caller with ghost atoms that are images of its local atoms (GRACE-2L): forward copies the
+// message rows of the owners to their ghosts after layer 1, reverse adds the dE/dmsg rows of the ghosts into their
+// owners before layer 1 is reversed (Exchange::forward / reverse of the reference's engine interface,
+// libgrace/include/grace/kk/grace_2l_kk.h:92-96, libgrace/include/grace/system.h:53-64).  rows: device, [atoms][width]
+// fp32; stream: the library's stream, already synchronised when the hook is called - work enqueued on it, or finished
+// before the hook returns, is ordered before the library's next kernel.
+struct ExchangeHooks {
+  void (*forward)(void *user, float *d_rows, int width, void *stream) = nullptr;
+  void (*reverse)(void *user, float *d_rows, int width, void *stream) = nullptr;
+  void *user = nullptr;
+};
+
 // outputs of one evaluation, device pointers (null: not wanted)
 struct OutputsDev {
   double *energy = nullptr;      // [nsys]
@@ -76,7 +88,7 @@ class Engine {
   // evaluates the structures of the neighbour list nl (positions prepared by nl.prepare); chunk: atoms per pass
   // act (optional): owned atoms and active ranges of a domain-decomposed caller
   void evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm,
-                const ActiveRanges *act = nullptr);
+                const ActiveRanges *act = nullptr, const ExchangeHooks *hooks = nullptr);
   // ranges of the list order that hold the atoms with caller index < nlocal / < ninner (reads back 4 integers)
   ActiveRanges active_ranges(NeighborList &nl, int nlocal, int ninner, DBuf<int> &list0, DBuf<int> &list1);
   // bond-force slots [3 * nslots] the list zeroes for bonds outside the cutoff (grown here)
@@ -115,6 +127,8 @@ class Engine {
   bool use_fused(int64_t n_eval) const;
   bool use_tc(int64_t n_eval) const;
   bool tc_now_ = false;       // the evaluation in progress runs eligible MV operations on the tensor cores
+  const ExchangeHooks *hooks_ = nullptr;    // of the evaluation in progress
+  void call_hook(bool forward);
   // exact radial MLP per bond on the tensor cores instead of the tables (spline N = 0)
   bool exact_ = false;
   RadialMlpTC rad1_, rad2_;
@@ -221,6 +235,33 @@ class BatchObj {
   int chunk_req_;
   NeighborList nl_;
   Workspace ws_;
+};
+
+// The engine interface of MD codes that bring their own neighbour list and ghost atoms (the LAMMPS glue of the
+// reference: RunInput / RunOutput / Exchange, libgrace/include/grace/kk/grace_2l_kk.h:87-119): local atoms first, then
+// ghosts; a padded neighbour table of the local atoms over all atoms; forces are ADDED to f [nall][3] (ghost rows too:
+// the caller returns them to their owners), per-atom energies to eatom [nlocal]; energy and virial of the local atoms
+// are returned.  GRACE-2L exchanges its message rows through the caller's hooks.
+class EngineRunObj {
+ public:
+  EngineRunObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &species, int spline, int chunk);
+  double cutoff() const { return cutoff_; }
+  int comm_width() const;    // floats per atom the hooks move (0: one-layer model, no exchange)
+  void run(int nlocal, int nall, const int *d_type, const double *d_x, const int *d_numneigh, const int *d_neighbors,
+           int maxneigh, int flags, const ExchangeHooks &hooks, double *energy, double *virial6, double *d_f,
+           double *d_eatom);
+  void release();
+  std::mutex mu;
+
+ private:
+  std::shared_ptr<ModelObj> model_;
+  std::shared_ptr<Engine> engine_;
+  std::vector<int> t2m_;
+  double cutoff_;
+  int chunk_req_;
+  NeighborList nl_;
+  Workspace ws_;
+  DBuf<int> list0_, list1_;
 };
 
 std::vector<int> species_to_elements(const GraceModel &m, const std::vector<std::string> &species);

@@ -166,6 +166,11 @@ void launch_msg_grad_gather(const BondsDev &b, const int *rev, const float *gslo
 // F_i = sum over the slots q of atom i of fv[q] - fv[rev[q]], written at the caller's index of atom i
 void launch_force_gather(const long long *off, const int *rev, const float *fv, const int *perm, double *forces,
                          int n);
+// lists without a reverse-bond index (a caller's own list with ghost atoms): forces[i] += sum of the atom's bond forces,
+// forces[j] -= each bond force, with fp64 atomic adds (forces is accumulated into, indexed like the list's atoms)
+void launch_force_scatter(const BondsDev &b, const float *fv, double *forces, long long n);
+// out[i] += v[i]
+void launch_add_f64(const double *v, double *out, long long n);
 // per-structure sums of per-atom values: out[s][k] = sum_{i in [seg[s], seg[s+1])} v[i][k]
 // column sums of values[n][K] into out[K] with the partial sums in a static device array: no allocation
 // (static_sum.cu); throws InvalidArgument beyond static_sum_max_rows() / static_sum_max_cols()

@@ -514,6 +514,100 @@ void NeighborList::build(int nsys, const int *natoms, int64_t n, const double *d
   nslots_ = total;
 }
 
+namespace {
+
+// a caller's padded neighbour table [nlocal][maxneigh] -> CSR slots; ghosts (i >= nlocal) have none
+__global__ void __launch_bounds__(256) nl_adopt_counts(const int *__restrict__ numneigh, int nlocal, int maxneigh, int *cnt,
+                                                       int *flag, long long nall)
+{
+  const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nall) return;
+  int c = 0;
+  if (i < nlocal) {
+    c = numneigh[i];
+    if (c < 0 || c > maxneigh) { atomicOr(flag, 8); c = 0; }
+  }
+  cnt[i] = c;
+}
+
+__global__ void __launch_bounds__(128) nl_adopt_fill(const int *__restrict__ neighbors, int maxneigh,
+                                                     const long long *__restrict__ off, int *nbr_j, int *nbr_S, int *rev,
+                                                     int *flag, long long nlocal, long long nall)
+{
+  const long long i = (long long) blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  const int lane = threadIdx.x & 31;
+  if (i >= nlocal) return;
+  const long long base = off[i];
+  const int c = (int) (off[i + 1] - base);
+  for (int q = lane; q < c; q += 32) {
+    int j = neighbors[i * maxneigh + q];
+    if (j < 0 || j >= nall) { atomicOr(flag, 8); j = (int) i; }
+    nbr_j[base + q] = j;
+    nbr_S[base + q] = 0;      // ghosts are atoms of their own: no cell shift
+    rev[base + q] = -1;       // no reverse bond: a ghost has no list
+  }
+}
+
+__global__ void __launch_bounds__(256) nl_identity(int *perm, int *sid, int *img, long long n)
+{
+  const long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  perm[i] = (int) i;
+  sid[i] = 0;
+  img[3 * i] = img[3 * i + 1] = img[3 * i + 2] = 0;
+}
+
+}    // namespace
+
+void NeighborList::adopt(int nlocal, int nall, const int *d_mu, const int *d_numneigh, const int *d_neighbors, int maxneigh)
+{
+  if (nlocal < 0 || nall < nlocal) throw InvalidArgument("nlocal must be in 0 .. nall");
+  if (maxneigh < 0 || (nlocal > 0 && (!d_numneigh || (maxneigh > 0 && !d_neighbors)))) throw InvalidArgument("the neighbour table must be given");
+  cudaStream_t st = dev().stream;
+  const int64_t n = nall;
+  nsys_ = 1;
+  external_ = true;
+  st_.assign(1, NLStructHost{});
+  NLStructHost &S = st_[0];
+  const double eye[9] = {1, 0, 0, 0, 1, 0, 0, 0, 1};
+  std::memcpy(S.cell, eye, sizeof(eye));
+  std::memcpy(S.inv, eye, sizeof(eye));
+  for (int k = 0; k < 3; k++) { S.pbc[k] = 0; S.lo[k] = 0.0; S.span[k] = 1.0; S.nbin[k] = 1; S.reach[k] = 0; S.width[k] = 1.0; }
+  S.bin_base = 0; S.atom0 = 0; S.atom1 = (int) n;
+  d_st_.upload(st_);
+  std::vector<int> seg = {0, (int) n};
+  seg_.upload(seg);
+  flag_.ensure(1);
+  GB_CUDA(cudaMemsetAsync(flag_.get(), 0, sizeof(int), st));
+  off_.ensure(n + 1);
+  cnt_.ensure(n + 1);
+  if (n == 0) {
+    GB_CUDA(cudaMemsetAsync(off_.get(), 0, sizeof(long long), st));
+    GB_CUDA(cudaStreamSynchronize(st));
+    n_ = 0;
+    nslots_ = 0;
+    return;
+  }
+  perm_.ensure(n); sid_s_.ensure(n); img_s_.ensure(3 * n); mu_s_.ensure(n); xs_.ensure(3 * n); cnt_full_.ensure(n);
+  scan_tmp_.ensure(n / 1024 + 64);
+  GB_LAUNCH(nl_identity, blocks(n, 256), 256, 0, perm_.get(), sid_s_.get(), img_s_.get(), (long long) n);
+  GB_CUDA(cudaMemcpyAsync(mu_s_.get(), d_mu, sizeof(int) * (size_t) n, cudaMemcpyDeviceToDevice, st));
+  GB_LAUNCH(nl_adopt_counts, blocks(n, 256), 256, 0, d_numneigh, nlocal, maxneigh, cnt_full_.get(), flag_.get(), (long long) n);
+  launch_scan(cnt_full_.get(), off_.get(), scan_tmp_.get(), n);
+  long long total = 0;
+  GB_CUDA(cudaMemcpyAsync(&total, off_.get() + n, sizeof(long long), cudaMemcpyDeviceToHost, st));
+  GB_CUDA(cudaStreamSynchronize(st));    // also: the host vectors uploaded above
+  if (total >= ((long long) 1 << 31)) throw Unsupported("more than 2^31 neighbour-list entries in one pass");
+  const long long cap = std::max<long long>(total, 1);
+  nbr_j_.ensure(cap); nbr_S_.ensure(cap); rev_.ensure(cap); cslot_.ensure(cap); rec_.ensure(cap);
+  if (nlocal > 0)
+    GB_LAUNCH(nl_adopt_fill, blocks(nlocal, 4), 128, 0, d_neighbors, maxneigh, off_.get(), nbr_j_.get(), nbr_S_.get(), rev_.get(),
+              flag_.get(), (long long) nlocal, (long long) n);
+  if (read_flag(flag_.get()) & 8) throw InvalidArgument("neighbour table: a count beyond maxneigh or an index outside the atoms");
+  n_ = n;
+  nslots_ = total;
+}
+
 bool NeighborList::moved_beyond(const double *d_pos, double half_skin)
 {
   if (n_ == 0) return false;
@@ -589,6 +683,7 @@ void NeighborList::release()
   scan_tmp_.release(); rec_.release(); d_st_.release(); flag_.release();
   n_ = 0;
   nslots_ = 0;
+  external_ = false;
 }
 
 size_t NeighborList::bytes() const

@@ -27,6 +27,13 @@ class NeighborList {
   // cells [nsys][9], pbc [nsys][3] on the host; radius = cutoff + skin
   void build(int nsys, const int *natoms, int64_t n, const double *d_pos, const int *d_mu, const double *cells,
              const unsigned char *pbc, double radius);
+  // A caller's own list instead of a search (the engine interface of MD codes with ghost atoms,
+  // libgrace/include/grace/kk/grace_2l_kk.h:97-119): nall atoms, local ones first; d_numneigh [nlocal] and the padded table
+  // d_neighbors [nlocal][maxneigh] of indices into the nall atoms (device).  Ghosts are atoms of their own (no cell
+  // shifts, no lists), so the list has no reverse-bond index: external() tells the engine to scatter bond forces with
+  // atomic adds and to add the neighbours' message gradients atomically, as the reference's engines do.
+  void adopt(int nlocal, int nall, const int *d_mu, const int *d_numneigh, const int *d_neighbors, int maxneigh);
+  bool external() const { return external_; }
   // true when an atom moved more than half the skin since the build (device max-reduce, one int read back)
   bool moved_beyond(const double *d_pos, double half_skin);
   // the same check without the read-back: sets `bit` of the caller's device flag
@@ -56,6 +63,7 @@ class NeighborList {
  private:
   int64_t n_ = 0, nslots_ = 0;
   int nsys_ = 0;
+  bool external_ = false;
   std::vector<NLStructHost> st_;
   DBuf<NLStructHost> d_st_;
   DBuf<double> frac_, xs_, xbuild_, lohi_;

@@ -56,14 +56,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned mbar, unsigned parity)
 
 // one warp per CTA, one CTA per SM: lane 0 issues `iters` x 4 MMAs (K = 32 in steps of 8) into two accumulators in
 // turn, with a commit and a bounded wait every 32 iterations so that the issue queue stays short
-__global__ void __launch_bounds__(32, 1) peak_tf32_kernel(int iters, int *error)
+__global__ void __launch_bounds__(32, 1) peak_tf32_kernel(int iters, int n, int *error)
 {
   extern __shared__ __align__(1024) char smem[];
   __shared__ unsigned long long s_mbar;
   __shared__ unsigned s_tmem;
   const int lane = threadIdx.x;
   float *A = reinterpret_cast<float *>(smem), *B = A + TM * TK;
-  for (int i = lane; i < (TM + TN) * TK; i += 32) A[i] = 1.0f + (float) ((i * 2654435761u) >> 20) * 1.0e-4f;
+  for (int i = lane; i < (TM + n) * TK; i += 32) A[i] = 1.0f + (float) ((i * 2654435761u) >> 20) * 1.0e-4f;
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(512) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   if (lane == 0) {
@@ -75,8 +75,8 @@ __global__ void __launch_bounds__(32, 1) peak_tf32_kernel(int iters, int *error)
   __syncwarp();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = s_tmem, mbar = smem_u32(&s_mbar);
-  // fp32 accumulate, tf32 x tf32, both operands K-major, M = 128, N = 256
-  const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned) (TN >> 3) << 17) | ((unsigned) (TM >> 4) << 24);
+  // fp32 accumulate, tf32 x tf32, both operands K-major, M = 128, N = n
+  const unsigned idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned) (n >> 3) << 17) | ((unsigned) (TM >> 4) << 24);
   const unsigned a0 = smem_u32(A), b0 = smem_u32(B);
   unsigned phase = 0;
   bool ok = true;
@@ -138,8 +138,9 @@ double measure_peak_fp32_tflops()
   return best;
 }
 
-double measure_peak_tf32_tflops()
+double measure_peak_tf32_tflops(int n)
 {
+  if (n < 16 || n > TN || n % 16 != 0) throw InvalidArgument("N of the tensor-core microbenchmark must be a multiple of 16 up to 256");
   require_initialized();
   cudaStream_t st = dev().stream;
   DBuf<int> err("peaks:flag");
@@ -154,12 +155,12 @@ double measure_peak_tf32_tflops()
   double best = 0.0;
   for (int rep = 0; rep < 4; rep++) {
     GB_CUDA(cudaEventRecord(a, st));
-    peak_tf32_kernel<<<grid, 32, smem, st>>>(iters, err.get());
+    peak_tf32_kernel<<<grid, 32, smem, st>>>(iters, n, err.get());
     GB_CUDA(cudaGetLastError());
     GB_CUDA(cudaEventRecord(b, st));
     GB_CUDA(cudaEventSynchronize(b));
     dev().launches++;
-    const double flop = 2.0 * TM * TN * TK * (double) iters * grid;
+    const double flop = 2.0 * TM * n * TK * (double) iters * grid;
     if (rep > 0) best = std::max(best, flop / (time_ms(a, b) * 1e-3) / 1e12);
   }
   cudaEventDestroy(a);

@@ -63,7 +63,8 @@ int grace_debug_fail_alloc(const char *label, int nth);           /* debug_fail_
 int grace_debug_fail_launch(int nth);                             /* debug_fail_launch(nth) */
 /* Microbenchmarks of this device's compute peaks in TFLOP/s, the denominators of compute-bound rooflines: kind 0 the
  * fp32 FMA rate of the SIMT lanes (register-only FFMA loop at full occupancy), kind 1 the tf32 rate of the tensor
- * cores (tcgen05.mma kind::tf32, M = 128, N = 256, operands in shared memory).  A few milliseconds each.  Diagnostics;
+ * cores (tcgen05.mma kind::tf32, M = 128, N = 256, operands in shared memory), kind 16 .. 256 (a multiple of 16) the
+ * same with N = kind, which shows the instruction-rate limit of narrow tiles.  A few milliseconds each.  Diagnostics;
  * no counterpart in the reference. */
 int grace_measure_peak(int kind, double *tflops);
 /* _debug_track_alloc(on), _debug_peak_alloc(), _debug_live_alloc() (kk_module.cpp:221-224, kk_core.cpp:143-184): from
@@ -179,6 +180,37 @@ int grace_comm_size(void);                                                /* 0 w
  * compute of the system is collective: forces of owned atoms, energy and virial are the totals of the structure. */
 int grace_system_set_exchange(grace_system *s, int n, int nlocal, int ninner, const int32_t *send_counts,
                               const int32_t *send_index, const int32_t *recv_counts, const int32_t *recv_index);
+
+/* ---- Engine interface for hosts with their own neighbour list and ghost atoms ----
+ * The interface the reference's LAMMPS glue drives (RunInput / RunOutput / Exchange,
+ * libgrace/include/grace/kk/grace_2l_kk.h:87-119; CPU side libgrace/include/grace/system.h:53-64): nall atoms, the nlocal
+ * local ones first, then ghosts; the padded neighbour table of the local atoms over all atoms; forces are ADDED to
+ * d_f [nall][3] including the ghost rows (the caller returns those to their owners, LAMMPS: reverse_comm), per-atom
+ * energies to d_eatom [nlocal] (null: not wanted); energy and virial6 of the local atoms are returned on the host.
+ * GRACE-2L needs the message rows of the ghosts: after layer 1 `forward` must copy the rows of the owners into their
+ * ghosts, before layer 1 is reversed `reverse` must add the rows of the ghosts into their owners (rows: device,
+ * [nall][width] fp32, width = grace_engine_comm_width(); stream: the library's cudaStream_t, idle when the hook is
+ * called).  Null hooks: no ghost is an image of a local atom.  All pointers of grace_run_input are device pointers. */
+typedef struct grace_engine grace_engine;
+typedef void (*grace_exchange_fn)(void *user, float *d_rows, int width, void *stream);
+typedef struct {
+  int nlocal, nall;
+  const int32_t *d_type;         /* [nall] 1-based types into species */
+  const double *d_x;             /* [nall][3] */
+  const int32_t *d_numneigh;     /* [nlocal] */
+  const int32_t *d_neighbors;    /* [nlocal][maxneigh] indices into the nall atoms */
+  int maxneigh;
+  int flags;                     /* GRACE_FLAG_ENERGY_ONLY */
+  grace_exchange_fn forward, reverse;
+  void *user;
+} grace_run_input;
+int grace_engine_create(const grace_model *m, const char *const *species, int n_species, int spline, int chunksize,
+                        grace_engine **out);                              /* set_model + setup */
+double grace_engine_cutoff(const grace_engine *e);
+int grace_engine_comm_width(const grace_engine *e);                       /* comm_width() */
+int grace_engine_run(grace_engine *e, const grace_run_input *in, double *energy, double *virial6, double *d_f,
+                     double *d_eatom);                                    /* run(RunInput) -> RunOutput */
+void grace_engine_free(grace_engine *e);
 
 /* ---- Batch (kk_api.h:92-156): many structures per engine pass ---- */
 int grace_batch_create(const grace_model *m, const char *const *species, int n_species, int spline, int chunksize,
