@@ -208,7 +208,7 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   if (getenv("GRACE_B200_RECOMPUTE_L1")) keep_l1_ = false;
   rcsq_.set_label("engine:cutoffs"); eW_.set_label("engine:energy_mlp"); shift_.set_label("engine:shift");
   lnI_.set_label("engine:norm_scale"); ln0_.set_label("engine:norm_scale"); rcf_.set_label("engine:cutoffs");
-  arena_.set_label("work:chunk_tensors"); fv_.set_label("work:bond_forces"); I_rows_.set_label("work:messages");
+  arena_.set_label("work:chunk_tensors"); arena1_.set_label("work:layer1_tensors"); fv_.set_label("work:bond_forces"); I_rows_.set_label("work:messages");
   gmsg_slot_.set_label("work:message_gradient_shares");
   gI_rows_.set_label("work:message_gradients"); rho_rows_.set_label("work:rho"); e_atom_.set_label("work:atom_energy");
   vir_atom_.set_label("work:atom_virial"); sum_scratch_.set_label("work:sums"); grho_rows_.set_label("work:rho_gradients");
@@ -308,14 +308,17 @@ void Engine::release_work()
   arena_.release(); fv_.release(); I_rows_.release(); gI_rows_.release(); rho_rows_.release();
   e_atom_.release(); vir_atom_.release(); grho_rows_.release(); sum_scratch_.release();
   xs_.release(); R1_.release(); dR1_.release(); R2_.release(); dR2_.release(); l1_saved_.release(); gmsg_slot_.release();
+  arena1_.release();
+  arena1_bound_ = nullptr;
+  arena1_NA_ = 0;
   arena_NA_ = 0;
 }
 
-void Engine::bind_arena(LayerEngine &E, int NA)
+void Engine::bind_arena(LayerEngine &E, float *base, int NA)
 {
   if (!E.plan) return;
   for (size_t t = 0; t < E.tensors_host.size(); t++)
-    E.tensors_host[t] = TensorDev{arena_.get() + E.toff[t] * NA, E.plan->tensors[t].channels};
+    E.tensors_host[t] = TensorDev{base + E.toff[t] * NA, E.plan->tensors[t].channels};
   E.tensors.upload(E.tensors_host);
 }
 
@@ -371,9 +374,10 @@ void Engine::gather_message_gradients(NeighborList &nl, const float *slots, cons
                          R.nlocal >= 0 ? nl.perm() : nullptr, R.nlocal);
 }
 
-void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA)
+void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA, int stride)
 {
-  // NA here is the number of atoms in use; the stride of the tensors is arena_NA_
+  // NA here is the number of atoms in use; stride: the atom stride of the layer's chunk tensors
+  const int arena_NA_ = stride;
   static const bool tag_ops = getenv("GRACE_B200_PROFILE_OPS") != nullptr;
   for (const Op &o : prog.ops) {
     if (tag_ops) launch_tag(o.kind == Op::MV ? E.plan->mv[o.index].name.c_str() : E.plan->prod[o.index].name.c_str());
@@ -671,19 +675,42 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
   cudaStream_t st = dev().stream;
   const ModelPlan &P = plan_;
   const long long per_atom = std::max(L1_.per_atom, L2_.per_atom);
+  // GRACE-2L with forces: layer 1 gets tensors of its own for all of its atoms in one pass when they fit, so that its
+  // reverse pass finds the forward tensors where they were left instead of evaluating the layer a second time
+  float *base1 = nullptr;
+  int NA1 = 0;
+  if (P.layers == 2 && !energy_only && keep_l1_ && R.hi1 > R.lo1) {
+    const int64_t w1 = (R.hi1 - R.lo1 + 3) / 4 * 4;
+    size_t free_b = 0, total_b = 0;
+    const size_t need = (size_t) L1_.per_atom * (size_t) w1 * sizeof(float);
+    if (w1 < ((int64_t) 1 << 30) && cudaMemGetInfo(&free_b, &total_b) == cudaSuccess &&
+        need <= (size_t) (0.45 * (double) free_b) + arena1_.capacity() * sizeof(float)) {
+      try {
+        base1 = arena1_.ensure((size_t) L1_.per_atom * (size_t) w1);
+        NA1 = (int) w1;
+      } catch (const OutOfMemory &) {
+        base1 = nullptr;
+      }
+    }
+  }
   const float *arena_before = arena_.get();
-  arena_.ensure((size_t) per_atom * NA);
-  if (arena_.get() != arena_before || arena_NA_ != NA) {
+  arena_.ensure((size_t) (base1 ? L2_.per_atom : per_atom) * NA);
+  if (arena_.get() != arena_before || arena_NA_ != NA || arena1_bound_ != base1 || arena1_NA_ != NA1) {
     arena_NA_ = NA;
-    bind_arena(L1_, NA);
-    bind_arena(L2_, NA);
+    arena1_bound_ = base1;
+    arena1_NA_ = NA1;
+    bind_arena(L1_, base1 ? base1 : arena_.get(), base1 ? NA1 : NA);
+    bind_arena(L2_, arena_.get(), NA);
   }
   const BondsDev bonds = nl.bonds();
   const int *mu = nl.mu_sorted();
   float *fv = fv_.get();
-  auto zero_grads = [&](LayerEngine &E) {
-    GB_CUDA(cudaMemsetAsync(arena_.get() + E.grad_begin * NA, 0, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * NA, st));
+  auto zero_grads = [&](LayerEngine &E, float *base, int stride) {
+    GB_CUDA(cudaMemsetAsync(base + E.grad_begin * stride, 0, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * stride, st));
   };
+  const int S1 = base1 ? NA1 : NA;                   // atom stride of the layer-1 tensors
+  const int64_t step1 = base1 ? (int64_t) NA1 : NA;    // atoms per layer-1 pass
+  float *const abase1 = base1 ? base1 : arena_.get();
   auto T1 = [&](int t) { return L1_.tensors_host[t].p; };
   auto T2 = [&](int t) { return L2_.tensors_host[t].p; };
 
@@ -693,13 +720,13 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
       if (tm) tm->begin(StageTimer::FWD);
       launch_bond_fwd(P.lmax, bonds, L, T1(P.L1.tQ), NA, (int) a0, na);
-      run(L1_, P.L1.fwd, mu + a0, na);
+      run(L1_, P.L1.fwd, mu + a0, na, NA);
       launch_readout_1l(readout_, T1(P.t1_rho), T1(P.t1_grho), mu, e_atom_.get(), NA, na, (int) a0, !energy_only);
       if (tm) tm->end(StageTimer::FWD);
       if (energy_only) continue;
       if (tm) tm->begin(StageTimer::BWD);
-      zero_grads(L1_);
-      run(L1_, P.L1.bwd, mu + a0, na);
+      zero_grads(L1_, arena_.get(), NA);
+      run(L1_, P.L1.bwd, mu + a0, na, NA);
       launch_bond_bwd(P.lmax, bonds, L, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0);
       if (tm) tm->end(StageTimer::BWD);
     }
@@ -720,12 +747,12 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     Lb.gmsg_slot = gslots;
     // layer 1 forward of every chunk: messages I and rho of all atoms
     if (tm) tm->begin(StageTimer::FWD);
-    for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
-      { TagScope tg("layer1"); launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na); }
-      run(L1_, P.L1.fwd, mu + a0, na);
-      launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, NA, na, (int) a0);
-      launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, NA, na, (int) a0);
+    for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += step1) {
+      const int na = (int) std::min<int64_t>(step1, R.hi1 - a0);
+      { TagScope tg("layer1"); launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), S1, (int) a0, na); }
+      run(L1_, P.L1.fwd, mu + a0, na, S1);
+      launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, S1, na, (int) a0);
+      launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, S1, na, (int) a0);
     }
     if (tm) tm->end(StageTimer::FWD);
     call_hook(true);
@@ -734,14 +761,14 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
       if (tm) tm->begin(StageTimer::FWD);
       { TagScope tg("layer2"); launch_bond_fwd(P.lmax, bonds, Lb, T2(P.L2.tQ), NA, (int) a0, na); }
-      run(L2_, P.L2.fwd, mu + a0, na);
+      run(L2_, P.L2.fwd, mu + a0, na, NA);
       launch_readout_2l(readout_, rho_rows_.get(), T2(P.t2_I2), grho_rows_.get(), T2(P.t2_gI2), mu, e_atom_.get(), NA,
                         na, (int) a0, !energy_only);
       if (tm) tm->end(StageTimer::FWD);
       if (energy_only) continue;
       if (tm) tm->begin(StageTimer::BWD);
-      zero_grads(L2_);
-      run(L2_, P.L2.bwd, mu + a0, na);
+      zero_grads(L2_, arena_.get(), NA);
+      run(L2_, P.L2.bwd, mu + a0, na, NA);
       { TagScope tg("layer2"); launch_bond_bwd(P.lmax, bonds, Lb, T2(P.L2.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0); }
       if (tm) tm->end(StageTimer::BWD);
     }
@@ -750,15 +777,17 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       if (tm) tm->begin(StageTimer::BWD);
       gather_message_gradients(nl, gslots, R);
       call_hook(false);
-      for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += NA) {
-        const int na = (int) std::min<int64_t>(NA, R.hi1 - a0);
-        launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), NA, (int) a0, na);
-        run(L1_, P.L1.fwd, mu + a0, na);
-        zero_grads(L1_);
-        launch_chunk_from_rows(T1(P.t1_gI), gI_rows_.get(), nI, CR, NA, na, (int) a0);
-        launch_chunk_from_rows_f64(T1(P.t1_grho), grho_rows_.get(), 1, nrho, NA, na, (int) a0);
-        run(L1_, P.L1.bwd, mu + a0, na);
-        { TagScope tg("layer1"); launch_bond_bwd(P.lmax, bonds, La, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 1); }
+      for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += step1) {
+        const int na = (int) std::min<int64_t>(step1, R.hi1 - a0);
+        if (!base1) {    // the tensors of layer 1 were overwritten by layer 2: evaluate it again
+          launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), S1, (int) a0, na);
+          run(L1_, P.L1.fwd, mu + a0, na, S1);
+        }
+        zero_grads(L1_, abase1, S1);
+        launch_chunk_from_rows(T1(P.t1_gI), gI_rows_.get(), nI, CR, S1, na, (int) a0);
+        launch_chunk_from_rows_f64(T1(P.t1_grho), grho_rows_.get(), 1, nrho, S1, na, (int) a0);
+        run(L1_, P.L1.bwd, mu + a0, na, S1);
+        { TagScope tg("layer1"); launch_bond_bwd(P.lmax, bonds, La, T1(P.L1.tGQ), S1, (int) a0, na, fv, vir_atom_.get(), 1); }
       }
       if (tm) tm->end(StageTimer::BWD);
     }

@@ -139,8 +139,11 @@ class Engine {
   void evaluate_fused(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
   void evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageTimer *tm, const ActiveRanges &R);
   void run_fused(LayerEngine &E, int mode, int NA, int a0, int na, const int *mu, const int *ilist, float *saved = nullptr);
-  void bind_arena(LayerEngine &E, int NA);
-  void run(LayerEngine &E, const Program &prog, const int *mu, int NA);
+  void bind_arena(LayerEngine &E, float *base, int NA);
+  void run(LayerEngine &E, const Program &prog, const int *mu, int NA, int stride);
+  DBuf<float> arena1_;               // chunk tensors of layer 1 for all of its atoms (GRACE-2L on the per-operation path)
+  const float *arena1_bound_ = nullptr;
+  int arena1_NA_ = 0;
   LayerDev layer_dev(const LayerEngine &E) const;
 };
 
