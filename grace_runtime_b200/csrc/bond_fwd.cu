@@ -11,6 +11,8 @@
 // over n: no global atomics, bit-reproducible.
 #include "bond_common.cuh"
 
+#include <cstdlib>
+
 namespace gb {
 
 namespace {
@@ -128,6 +130,105 @@ __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, S
   }
 }
 
+// The same for layers that couple message functions in (NIT > 1) with at most 16 channels: a whole warp per bond, lane
+// = (channel n, half h) with the lm split between the halves (lm = 2 k + h), so that a lane keeps NIT x NLM / 2 partial
+// sums in registers instead of NIT x NLM (twice the resident warps) and the two halves share the work of a bond:
+//   Q[(I, lm)][n] += (Y_lm R_l) msg_I      with R of the lm's degree selected per lm.
+template<int LMAX, int NIT>
+__global__ void __launch_bounds__(128) bond_fwd_split_kernel(BondsDev b, LayerDev L, SHTable sht, float *__restrict__ Q, int NA,
+                                                             int a0)
+{
+  constexpr int NL = LMAX + 1, NLM = NL * NL, NLMP = NLM | 1, NQ = NIT * NLM, NK = (NLM + 1) / 2;
+  __shared__ float Ys[EB][NLMP];
+  __shared__ float st[EB];
+  __shared__ int sk[EB], smu[EB], sj[EB];
+  __shared__ float red[NQ][16];
+
+  const int a = blockIdx.x, i = b.ilist ? b.ilist[a0 + a] : a0 + a, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int n = lane & 15, h = lane >> 4;
+  const long long base = b.off[i];
+  const int nb = b.cnt[i];
+  const int mui = b.mu[i];
+  const int C = L.C, nel = L.n_elements;
+
+  float acc[NIT][NK];
+#pragma unroll
+  for (int I = 0; I < NIT; I++)
+#pragma unroll
+    for (int k = 0; k < NK; k++) acc[I][k] = 0.0f;
+
+  for (int b0 = 0; b0 < nb; b0 += EB) {
+    const int nbat = min(EB, nb - b0);
+    for (int e = tid; e < nbat; e += 128) {
+      const float4 rec = b.rec[base + b0 + e];
+      const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
+      const int j = __float_as_int(rec.w);
+      const int muj = b.mu[j];
+      int k;
+      float t;
+      spline_locate(r / L.rc[mui * nel + muj], L.N, k, t);
+      sk[e] = k; st[e] = t; smu[e] = muj; sj[e] = j;
+      float *y = Ys[e];
+      sph_harm<LMAX, false>(sht, rec.x * ir, rec.y * ir, rec.z * ir,
+                            [&](int lm, float v, float, float, float) { y[lm] = v; });
+    }
+    __syncthreads();
+    for (int e = w; e < nbat; e += 4) {    // a warp per bond
+      if (n < C) {
+        const int k0 = sk[e], muj = smu[e], j = sj[e];
+        const float t = st[e];
+        const float *y = Ys[e];
+        float R[NL];
+        const float4 *cf = reinterpret_cast<const float4 *>(L.tab) + (size_t) k0 * NL * C + n;
+#pragma unroll
+        for (int l = 0; l < NL; l++) {
+          const float4 c = __ldg(cf + l * C);
+          R[l] = c.x + t * (c.y + t * (c.z + t * c.w));
+        }
+        float m[NIT];
+#pragma unroll
+        for (int I = 0; I < NIT; I++) {
+          m[I] = 0.0f;
+          if (I < L.n_msg) m[I] = __ldg(L.msg + ((size_t) j * L.n_msg + I) * C + n);
+          else if (I == L.n_msg) m[I] = __ldg(L.z + (size_t) muj * C + n);
+        }
+#pragma unroll
+        for (int k = 0; k < NK; k++) {
+          constexpr auto deg = [](int q) { int l = 0; while ((l + 1) * (l + 1) <= q) l++; return l; };
+          const int q = 2 * k + h;
+          const int l0 = deg(2 * k), l1 = deg(2 * k + 1 < NLM ? 2 * k + 1 : NLM - 1);
+          if (q < NLM) {
+            const float yr = y[q] * (h ? R[l1] : R[l0]);
+#pragma unroll
+            for (int I = 0; I < NIT; I++) acc[I][k] = fmaf(yr, m[I], acc[I][k]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  for (int ww = 0; ww < 4; ww++) {    // the partial sums of the warps, added in warp order
+    if (w == ww && n < C) {
+#pragma unroll
+      for (int I = 0; I < NIT; I++)
+#pragma unroll
+        for (int k = 0; k < NK; k++) {
+          const int q = 2 * k + h;
+          if (q < NLM) {
+            float *r = &red[I * NLM + q][n];
+            *r = (ww == 0) ? acc[I][k] : *r + acc[I][k];
+          }
+        }
+    }
+    __syncthreads();
+  }
+  for (int idx = tid; idx < NQ * C; idx += 128) {
+    const int q = idx / C, nn = idx - q * C;
+    if (q / NLM <= L.n_msg) Q[((size_t) q * NA + a) * C + nn] = red[q][nn];
+  }
+}
+
 template<int LMAX, int NIT, int NCH, int LPE>
 void launch_t(const BondsDev &b, const LayerDev &L, float *Q, int NA, int a0, int na)
 {
@@ -142,6 +243,8 @@ template<int LMAX> void launch_l(const BondsDev &b, const LayerDev &L, float *Q,
   if (C > 64) throw Unsupported("bond sums with more than 64 channels are not supported");
   if (C > 32) launch_t<LMAX, 1, 2, 32>(b, L, Q, NA, a0, na);
   else if (C > 16) { if (nI == 5) launch_t<LMAX, 5, 1, 32>(b, L, Q, NA, a0, na); else launch_t<LMAX, 1, 1, 32>(b, L, Q, NA, a0, na); }
+  else if (nI == 5 && !L.Rex && !getenv("GRACE_B200_BOND_NOSPLIT"))
+    GB_LAUNCH((bond_fwd_split_kernel<LMAX, 5>), na, 128, 0, b, L, sh_table_host(), Q, NA, a0);
   else { if (nI == 5) launch_t<LMAX, 5, 1, 16>(b, L, Q, NA, a0, na); else launch_t<LMAX, 1, 1, 16>(b, L, Q, NA, a0, na); }
 }
 

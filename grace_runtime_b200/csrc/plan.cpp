@@ -204,8 +204,35 @@ struct LayerBuilder {
     }
     const Op f = add(std::move(F));
     std::vector<Op> a;
-    a.push_back(add(std::move(BL)));
-    a.push_back(add(std::move(BR)));
+    if (gL == gR && nil == nir) {
+      // both inputs are the same tensor (fc(X, X)): one adjoint operation, every row of the gradient written once with
+      // the left item first and the right items behind it
+      MVOp B;
+      B.name = name + ":adj";
+      B.dst = gL; B.n_out = nil; B.ldw = ldl; B.accumulate = true;
+      const int base = (int) BL.W.size();
+      B.W = BL.W;
+      B.W.insert(B.W.end(), BR.W.begin(), BR.W.end());
+      std::map<int, std::vector<MVItem>> rows;
+      for (size_t r = 0; r < BL.row_out.size(); r++)
+        for (int q = BL.item_off[r]; q < (r + 1 < BL.row_out.size() ? BL.item_off[r + 1] : (int) BL.items.size()); q++)
+          rows[BL.row_out[r]].push_back(BL.items[q]);
+      for (size_t r = 0; r < BR.row_out.size(); r++)
+        for (int q = BR.item_off[r]; q < (r + 1 < BR.row_out.size() ? BR.item_off[r + 1] : (int) BR.items.size()); q++) {
+          MVItem it = BR.items[q];
+          it.mat += base;
+          rows[BR.row_out[r]].push_back(it);
+        }
+      for (auto &kv : rows) {
+        B.row_out.push_back(kv.first);
+        B.item_off.push_back((int) B.items.size());
+        B.items.insert(B.items.end(), kv.second.begin(), kv.second.end());
+      }
+      a.push_back(add(std::move(B)));
+    } else {
+      a.push_back(add(std::move(BL)));
+      a.push_back(add(std::move(BR)));
+    }
     emit(f, a);
   }
 
@@ -242,8 +269,26 @@ struct LayerBuilder {
     }
     const Op f = add(std::move(F));
     std::vector<Op> a;
-    a.push_back(add(std::move(BL)));
-    a.push_back(add(std::move(BR)));
+    if (tL == tR && gL == gR) {
+      // product of a tensor with itself: one adjoint operation over the union of the terms (left terms of a row first)
+      ProdOp B;
+      B.name = name + ":adj";
+      B.dst = gL; B.srcA = gD; B.srcB = tL; B.accumulate = true;
+      std::map<int, std::vector<ProdTerm>> rows;
+      for (auto &kv : by_l)
+        for (int t : kv.second) rows[kv.first].push_back({p.m_sum[t], p.right[t], (float) p.cg[t]});
+      for (auto &kv : by_r)
+        for (int t : kv.second) rows[kv.first].push_back({p.m_sum[t], p.left[t], (float) p.cg[t]});
+      for (auto &kv : rows) {
+        B.row_out.push_back(kv.first);
+        B.term_off.push_back((int) B.terms.size());
+        B.terms.insert(B.terms.end(), kv.second.begin(), kv.second.end());
+      }
+      a.push_back(add(std::move(B)));
+    } else {
+      a.push_back(add(std::move(BL)));
+      a.push_back(add(std::move(BR)));
+    }
     emit(f, a);
   }
 
