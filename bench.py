@@ -548,7 +548,30 @@ def run_ours(args, rank, world, local_rank):
         e = traffic_tab.get((kernel, wl["cfg"]))
         return e["dram_bytes_per_atom"] * n_own / launches_per_step if e else None
 
-    if top.startswith("chain_"):
+    dense_names = {"mv_tc_kernel": "tensor", "prod_tile_kernel": "products", "mv_elem_tile_kernel": "elementwise"}
+    if top in dense_names:
+        # per-operation dense path: all launches of the kernel in a step together (one per operation of the plan; GRACE-2L
+        # per 262,144-atom pass); flops and algorithmic bytes per atom from the plan
+        lps = top_n / args.steps
+        fl_atom, by_atom = model.dense_stats[dense_names[top]]
+        step_ms = top_ms / args.steps
+        gbs = by_atom * n_own / (step_ms * 1e-3) / 1e9
+        if top == "mv_tc_kernel":
+            ach = fl_atom * n_own / (step_ms * 1e-3) / 1e12
+            peak_tf = peaks_here["tf32_tensor_tflops"] / 3.0
+            roof = {"bound": "tensor", "kernel": top, "peak": peak_tf,
+                    "peak_source": "tf32 tcgen05 microbenchmark of this run (M 128, N 256) / 3: three tf32 instructions per fp32-accurate product",
+                    "unit": "TFLOP/s", "achieved": ach, "frac": ach / peak_tf, "traffic": traffic_of(top, lps),
+                    "hbm_achieved_GBs": gbs, "hbm_frac_of_measured": gbs / hbm_peak,
+                    "note": "FC layers and adjoints as 3 x tf32 grouped GEMMs with N = 32 / 64; the tf32 rate of an N = 32 (64) "
+                            "instruction is 0.29 (0.57) of the N = 256 one (grace_measure_peak), and the kernel streams its "
+                            "operands from HBM: hbm_frac_of_measured is the tighter bound"}
+        else:
+            roof = {"bound": "hbm", "kernel": top, "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "achieved": gbs,
+                    "frac": gbs / hbm_peak, "traffic": traffic_of(top, lps)}
+        roof.update(flop_per_atom=fl_atom, algorithmic_bytes_per_atom=by_atom, ms_per_step=step_ms, launches_per_step=lps,
+                    algorithmic_bytes_per_launch=by_atom * n_own / lps)
+    elif top.startswith("chain_"):
         # dense network: useful fp32 multiply-adds of the forward and reverse programs (GRACE-2L may evaluate layer 1
         # twice: counted once) per launch, against the measured peak of the unit the kernel computes on
         lps = top_n / args.steps
@@ -599,6 +622,11 @@ def run_ours(args, rank, world, local_rank):
         if ab is not None and v[0] > 0:
             gbs = ab * args.steps / v[0] / (v[1] / v[0] * 1e-3) / 1e9
             hbm_kernels[name] = {"achieved_GBs": gbs, "frac_of_measured_hbm": gbs / hbm_peak, "avg_launch_ms": v[1] / v[0]}
+        elif name in ("mv_tc_kernel", "prod_tile_kernel", "mv_elem_tile_kernel") and v[1] > 0:
+            by_atom = model.dense_stats[{"mv_tc_kernel": "tensor", "prod_tile_kernel": "products", "mv_elem_tile_kernel": "elementwise"}[name]][1]
+            gbs = by_atom * n_own / (v[1] / args.steps * 1e-3) / 1e9
+            hbm_kernels[name] = {"achieved_GBs": gbs, "frac_of_measured_hbm": gbs / hbm_peak, "ms_per_step": v[1] / args.steps,
+                                 "algorithmic_bytes_per_atom": by_atom}
 
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,

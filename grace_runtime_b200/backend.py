@@ -51,6 +51,7 @@ SIGNATURES = {
     "grace_model_element_name": (C.c_char_p, [_P, _I]),
     "grace_model_engine_setups": (_I64, [_P]),
     "grace_model_dense_flops": (_D, [_P]),
+    "grace_model_dense_stats": (_I, [_P, _P]),
     "grace_model_radial_mlp_device": (_I, [_P, _I, _I64, _P, _P, _P]),
     "grace_model_radial_mlp_width": (_I, [_P, _I]),
     "grace_model_free": (None, [_P]),
@@ -409,6 +410,14 @@ class Model:
     @property
     def engine_setups(self):
         return int(_lib.grace_model_engine_setups(self._h))
+
+    @property
+    def dense_stats(self):
+        """per atom on the per-operation path: dict of (flops, bytes) for the tensor-core operations, the products and
+        the per-element operations (see grace_model_dense_stats)"""
+        v = np.zeros(6)
+        _check(_lib.grace_model_dense_stats(self._h, _ptr(v)))
+        return {"tensor": (v[0], v[1]), "products": (v[2], v[3]), "elementwise": (v[4], v[5])}
 
     @property
     def dense_flops(self):

@@ -242,6 +242,16 @@ double grace_model_dense_flops(const grace_model *m)
   std::lock_guard<std::mutex> lk(m->m->mu);
   return m->m->engines.empty() ? 0.0 : m->m->engines.begin()->second->plan().dense_flops_per_atom;
 }
+int grace_model_dense_stats(const grace_model *m, double *out6)
+{
+  return guarded([&] {
+    if (!m || !out6) throw InvalidArgument("model and output must be given");
+    std::lock_guard<std::mutex> lk(m->m->mu);
+    if (m->m->engines.empty()) throw InvalidArgument("the model has no engine yet: create a System or Batch first");
+    m->m->engines.begin()->second->dense_stats(out6);
+  });
+}
+
 int grace_model_radial_mlp_device(grace_model *m, int layer, int64_t nb, const float *d_x, float *d_R, float *d_dR)
 {
   return guarded([&] {

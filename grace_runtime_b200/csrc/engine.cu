@@ -272,6 +272,35 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
 
 Engine::~Engine() = default;
 
+void Engine::dense_stats(double *o) const
+{
+  for (int k = 0; k < 6; k++) o[k] = 0.0;
+  for (const LayerEngine *E : {&L1_, &L2_}) {
+    if (!E->plan) continue;
+    const LayerPlan &P = *E->plan;
+    for (size_t q = 0; q < P.mv.size(); q++) {
+      const MVOp &m = P.mv[q];
+      double fl = 0.0, by = 0.0;
+      for (const MVItem &it : m.items) {
+        fl += 2.0 * it.n_in * m.n_out;
+        by += 4.0 * it.n_in;
+      }
+      by += 4.0 * m.n_out * (double) m.row_out.size() * (m.accumulate ? 2.0 : 1.0);
+      const int k = E->mv_tc[q].ready() ? 0 : 4;
+      o[k] += fl;
+      o[k + 1] += by;
+    }
+    for (const ProdOp &pr : P.prod) {
+      const int C = P.tensors[pr.dst].channels;
+      o[2] += 3.0 * (double) pr.terms.size() * C;
+      double rows = P.tensors[pr.srcA].nfuncs;
+      if (pr.srcB >= 0 && pr.srcB != pr.srcA) rows += P.tensors[pr.srcB].nfuncs;
+      rows += (double) pr.row_out.size() * (pr.accumulate ? 2.0 : 1.0);
+      o[3] += 4.0 * C * rows;
+    }
+  }
+}
+
 bool Engine::use_tc(int64_t n_eval) const
 {
   if (!tc_ready_ || dense_ == Dense::Fused || dense_ == Dense::Ops) return false;

@@ -85,6 +85,11 @@ class Engine {
   Engine(const GraceModel &m, int spline_n);
   ~Engine();
   const ModelPlan &plan() const { return plan_; }
+  // Per atom and evaluation (forward and reverse programs of every layer, each once), on the per-operation path:
+  // [0] useful flops and [1] algorithmic bytes of the MV operations that run on the tensor cores, [2] / [3] of the
+  // products, [4] / [5] of the remaining (per-element) MV operations.  Bytes: every input row once per item or tensor,
+  // every output row once (twice when the operation accumulates).
+  void dense_stats(double *out6) const;
   // evaluates the structures of the neighbour list nl (positions prepared by nl.prepare); chunk: atoms per pass
   // act (optional): owned atoms and active ranges of a domain-decomposed caller
   void evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out, int chunk, StageTimer *tm,

@@ -32,6 +32,7 @@ constexpr int NW = NTH / 32;
 constexpr int TMEM_COLS = 512;
 constexpr int MAX_TILES = 16;   // atom tiles a CTA holds accumulators for
 constexpr int MAX_TENSORS = 64;
+constexpr int MAX_ITEMS = 512, MAX_ROWS = 192;    // tables of an operation staged in shared memory
 constexpr long long WAIT_CYCLES = 40000000LL;    // ~20 ms: far beyond any tile, far below a watchdog
 
 // byte offset of element (r, k) of a K-major operand tile with K columns (canonical layout, no swizzle)
@@ -102,19 +103,6 @@ template<> __device__ __forceinline__ void tmem_ld<16>(unsigned taddr, float (&v
   for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
-// waits for the phase `parity` of the barrier; false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(unsigned mbar, unsigned parity)
-{
-  const long long t0 = clock64();
-  for (;;) {
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
-    if (ok) return true;
-    if (clock64() - t0 > WAIT_CYCLES) return false;
-  }
-}
-
 // position in the loop nest (round of tiles, output row, item of the row, tile of the round)
 struct Cursor {
   int tile0, nt, row, it, i0, i1, tt;
@@ -123,37 +111,60 @@ struct Cursor {
 
 // Activation tile of a fill: K4 = K / 4 float4 per atom row.  A warp instruction covers 8 atom rows x 4 consecutive
 // float4 (64 contiguous bytes of each row in global memory, 512 contiguous bytes = 4 core matrices in shared memory:
-// no bank conflicts); the 16 x CG such units of a tile go round the warps.
+// no bank conflicts); the 16 x CG such units of a tile go round the producer warps.
 template<int K> struct TileRegs {
   static constexpr int K4 = K / 4, CG = (K4 + 3) / 4, UNITS = 16 * CG, PER = (UNITS + NW - 1) / NW;
   float4 v[PER];
 };
 
-// K <= 32: two CTAs per SM (80 KB of shared memory and at most 256 tensor-memory columns each)
-template<int K, int CB>
-__global__ void __launch_bounds__(NTH, (K <= 32 ? 2 : 1)) mv_tc_kernel(MVTCDev op, const TensorDev *__restrict__ Tg, int ntensors,
-                                                                       int NA, int na, int TB, int tmem_cols, int *error)
+// Warp-specialised: warps 0-7 produce (global loads two tiles ahead in registers, tf32 hi / lo operand images of a tile
+// into one of S shared-memory stages, the weight image of an item into a ring of S buffers), warp 8 issues the matrix
+// instructions (one thread; nothing else runs on its critical path), warps 9-12 move finished accumulators from tensor
+// memory to global memory.  Two sets of accumulators (TB tiles x n_out columns each) take turns, so the epilogue of a
+// row overlaps the matrix instructions of the next.  Hand-offs are mbarriers: full[s] (256 producer arrivals) / empty[s]
+// (tcgen05.commit) per stage, accfull[set] (tcgen05.commit after the last item of a row) / accempty[set] (128 epilogue
+// arrivals).  A wait that runs out raises `abort`, which every other wait sees, and all roles leave together.
+constexpr int NPROD = NTH, NTHREADS = NTH + 32 + 128;
+
+template<int K, int CB, int S>
+__global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const TensorDev *__restrict__ Tg, int ntensors, int NA,
+                                                            int na, int TB, int tmem_cols, int *error)
 {
   using TR = TileRegs<K>;
-  constexpr int K4 = TR::K4, CG = TR::CG, UNITS = TR::UNITS, PER = TR::PER;
+  constexpr int K4 = TR::K4, UNITS = TR::UNITS, PER = TR::PER;
   constexpr int A_BYTES = TM * K * 4;    // one image (hi or lo) of an activation tile
   extern __shared__ __align__(1024) char smem[];
-  __shared__ unsigned long long s_bar[2];
+  __shared__ unsigned long long s_full[S], s_empty[S], s_accfull[2], s_accempty[2];
   __shared__ unsigned s_tmem;
+  __shared__ int s_abort;
   __shared__ TensorDev s_T[MAX_TENSORS];
+  // the operation's tables: every role walks them once per fill, so they live in shared memory
+  __shared__ MVItem s_items[MAX_ITEMS];
+  __shared__ int s_item_off[MAX_ROWS + 1], s_row_out[MAX_ROWS];
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int N = op.n_out;
-  const int W_BYTES = N * K * 4;         // one image of a weight matrix
-  char *A_st = smem;                     // stage s at s * 2 * A_BYTES: hi, then lo
-  char *W_st = smem + 4 * A_BYTES;       // buffer b at b * 2 * W_BYTES: hi, then lo
-  for (int q = t; q < ntensors; q += NTH) s_T[q] = Tg[q];
+  const int W_BYTES = N * K * 4;                         // one image of a weight matrix
+  char *A_st = smem;                                     // stage s at s * 2 * A_BYTES: hi, then lo
+  char *W_st = smem + (size_t) S * 2 * A_BYTES;          // buffer b at b * 2 * W_BYTES: hi, then lo
+  float *tr_all = reinterpret_cast<float *>(W_st + (size_t) S * 2 * W_BYTES);    // transpose buffers of the epilogue warps
+  for (int q = t; q < ntensors; q += NTHREADS) s_T[q] = Tg[q];
+  for (int q = t; q <= op.nrows; q += NTHREADS) s_item_off[q] = op.item_off[q];
+  for (int q = t; q < op.nrows; q += NTHREADS) s_row_out[q] = op.row_out[q];
+  for (int q = t; q < op.nitems; q += NTHREADS) s_items[q] = op.items[q];
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (t == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_bar[0])) : "memory");
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_bar[1])) : "memory");
+    for (int s = 0; s < S; s++) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&s_full[s])), "r"(NPROD) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_empty[s])) : "memory");
+    }
+    for (int s = 0; s < 2; s++) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_accfull[s])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(smem_u32(&s_accempty[s])) : "memory");
+    }
+    s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -161,19 +172,33 @@ __global__ void __launch_bounds__(NTH, (K <= 32 ? 2 : 1)) mv_tc_kernel(MVTCDev o
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = s_tmem;
-  const unsigned bar[2] = {smem_u32(&s_bar[0]), smem_u32(&s_bar[1])};
-  const unsigned idesc = make_idesc(N);
   const int ntiles = (na + TM - 1) / TM, per_round = gridDim.x * TB;
-  const TensorDev dstT = s_T[op.dst];
+  volatile int *abort_flag = &s_abort;
 
+  // bounded wait that also gives up when another role did
+  auto wait = [&](unsigned long long *bar, unsigned parity) -> bool {
+    const unsigned addr = smem_u32(bar);
+    const long long t0 = clock64();
+    for (;;) {
+      unsigned ok;
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(ok) : "r"(addr), "r"(parity), "r"(20000u) : "memory");
+      if (ok) return true;
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  };
   auto start = [&](Cursor &c, int tile0, int row) {
     c.tile0 = tile0;
     c.row = row;
     c.valid = tile0 < ntiles && row < op.nrows;
     if (!c.valid) return;
     c.nt = min(TB, ntiles - tile0);
-    c.i0 = c.it = op.item_off[row];
-    c.i1 = op.item_off[row + 1];
+    c.i0 = c.it = s_item_off[row];
+    c.i1 = s_item_off[row + 1];
     c.tt = 0;
   };
   auto advance = [&](Cursor &c) {
@@ -187,138 +212,198 @@ __global__ void __launch_bounds__(NTH, (K <= 32 ? 2 : 1)) mv_tc_kernel(MVTCDev o
     }
     start(c, tile0, row);
   };
-  // global loads of the activation tile at the cursor into registers (zeros past the last atom)
-  auto load_tile = [&](const Cursor &c, TR &r) {
-    const MVItem item = op.items[c.it];
-    const TensorDev src = s_T[item.src];
-    const int atom0 = (c.tile0 + c.tt) * TM, valid = min(TM, na - atom0);
-    const float *base = src.p + ((size_t) item.irow * NA + atom0) * src.C;
-#pragma unroll
-    for (int j = 0; j < PER; j++) {
-      const int u = warp + NW * j, row = (u % 16) * 8 + (lane & 7), c4 = (u / 16) * 4 + (lane >> 3);
-      r.v[j] = (u < UNITS && row < valid && c4 < K4) ? __ldg(reinterpret_cast<const float4 *>(base + (size_t) row * src.C) + c4)
-                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+  auto next_row = [&](Cursor &c) {    // first fill of the row after c's
+    int row = c.row + gridDim.y, tile0 = c.tile0;
+    if (row >= op.nrows) {
+      row = blockIdx.y;
+      tile0 += per_round;
     }
+    start(c, tile0, row);
   };
 
-  // The global loads of two tiles are in flight ahead of the one being converted: two register sets take turns (the
-  // loop body is written once and instantiated for both roles, so no register is copied and no load is waited for
-  // before its tile is converted).
-  Cursor cur, nxt, nxt2;
-  start(cur, blockIdx.x * TB, blockIdx.y);
-  TR regsA, regsB;
-  if (cur.valid) load_tile(cur, regsA);
-  nxt = cur;
-  if (cur.valid) advance(nxt);
-  if (nxt.valid) load_tile(nxt, regsB);
-  unsigned phase[2] = {0, 0};
-  bool pending[2] = {false, false}, ok = true;
-  int fill = 0, wsel = 0;
-  // one fill: `mine` holds the tile at `cur`; after its conversion it receives the tile two fills ahead
-#ifdef GB_TC_TIMING
-  long long tm_[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tq_ = clock64();
-#define GB_TICK(i) do { const long long now_ = clock64(); tm_[i] += now_ - tq_; tq_ = now_; } while (0)
-#else
-#define GB_TICK(i) do {} while (0)
-#endif
-  auto step = [&](TR &mine) {
-    GB_TICK(7);
-    nxt2 = nxt;
-    if (nxt.valid) advance(nxt2);
-    const int s = fill & 1;
-    // the matrix instructions that read this stage two fills ago (and everything issued before them) are done
-    if (pending[s]) {
-      ok = __syncthreads_and(mbar_wait(bar[s], phase[s]));
-      phase[s] ^= 1;
-      pending[s] = false;
-      if (!ok) return;
-    }
-    GB_TICK(0);
-    const MVItem item = op.items[cur.it];
-    if (cur.tt == 0) {    // first tile of an item: its weight image (hi + lo, byte for byte the operand layout)
-      wsel ^= 1;
-      const int4 *src = reinterpret_cast<const int4 *>(op.images + (size_t) item.mat * 2 * W_BYTES);
-      int4 *dst = reinterpret_cast<int4 *>(W_st + (size_t) wsel * 2 * W_BYTES);
-      for (int q = t; q < 2 * W_BYTES / 16; q += NTH) dst[q] = __ldg(src + q);
-    }
-    GB_TICK(1);
-    {    // registers -> tf32 hi / lo operand images of stage s
-      char *hi = A_st + (size_t) s * 2 * A_BYTES, *lo = hi + A_BYTES;
+  if (warp < NW) {
+    // ---------------- producers ----------------
+    auto load_tile = [&](const Cursor &c, TR &r) {
+      const MVItem item = s_items[c.it];
+      const TensorDev src = s_T[item.src];
+      const int atom0 = (c.tile0 + c.tt) * TM, valid = min(TM, na - atom0);
+      const float *base = src.p + ((size_t) item.irow * NA + atom0) * src.C;
 #pragma unroll
       for (int j = 0; j < PER; j++) {
-        const int u = warp + NW * j, c4 = (u / 16) * 4 + (lane >> 3);
-        if (u < UNITS && c4 < K4) {
-          const int off = ((u % 16) * K4 + c4) * 128 + (lane & 7) * 16;
-          float4 h, l;
-          split4(mine.v[j], item.scale, h, l);
-          *reinterpret_cast<float4 *>(hi + off) = h;
-          *reinterpret_cast<float4 *>(lo + off) = l;
+        const int u = warp + NW * j, row = (u % 16) * 8 + (lane & 7), c4 = (u / 16) * 4 + (lane >> 3);
+        r.v[j] = (u < UNITS && row < valid && c4 < K4) ? __ldg(reinterpret_cast<const float4 *>(base + (size_t) row * src.C) + c4)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    };
+    Cursor cur, nxt, nxt2;
+    start(cur, blockIdx.x * TB, blockIdx.y);
+    TR regsA, regsB;
+    if (cur.valid) load_tile(cur, regsA);
+    nxt = cur;
+    if (cur.valid) advance(nxt);
+    if (nxt.valid) load_tile(nxt, regsB);
+    int fill = 0, item_no = -1;
+    bool ok = true;
+#ifdef GB_TC_TIMING
+    long long tp_[4] = {0, 0, 0, 0}, tq_ = clock64();
+#define GB_TICK(a, i) do { const long long now_ = clock64(); a[i] += now_ - tq_; tq_ = now_; } while (0)
+#else
+#define GB_TICK(a, i) do {} while (0)
+#endif
+    // one fill: `mine` holds the tile at `cur`; after its conversion it receives the tile two fills ahead
+    auto step = [&](TR &mine) {
+      GB_TICK(tp_, 3);
+      nxt2 = nxt;
+      if (nxt.valid) advance(nxt2);
+      const int s = fill % S;
+      // the matrix instructions that read this stage S fills ago (and everything issued before them) are done
+      if (fill >= S) {
+        ok = wait(&s_empty[s], (unsigned) ((fill / S - 1) & 1));
+        if (!ok) return;
+      }
+      GB_TICK(tp_, 0);
+      const MVItem item = s_items[cur.it];
+      if (cur.tt == 0) {    // first tile of an item: its weight image (hi + lo, byte for byte the operand layout)
+        item_no++;
+        const int4 *src = reinterpret_cast<const int4 *>(op.images + (size_t) item.mat * 2 * W_BYTES);
+        int4 *dst = reinterpret_cast<int4 *>(W_st + (size_t) (item_no % S) * 2 * W_BYTES);
+        for (int q = t; q < 2 * W_BYTES / 16; q += NPROD) dst[q] = __ldg(src + q);
+      }
+      {    // registers -> tf32 hi / lo operand images of stage s
+        char *hi = A_st + (size_t) s * 2 * A_BYTES, *lo = hi + A_BYTES;
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+          const int u = warp + NW * j, c4 = (u / 16) * 4 + (lane >> 3);
+          if (u < UNITS && c4 < K4) {
+            const int off = ((u % 16) * K4 + c4) * 128 + (lane & 7) * 16;
+            float4 h, l;
+            split4(mine.v[j], item.scale, h, l);
+            *reinterpret_cast<float4 *>(hi + off) = h;
+            *reinterpret_cast<float4 *>(lo + off) = l;
+          }
         }
       }
+      GB_TICK(tp_, 1);
+      if (nxt2.valid) load_tile(nxt2, mine);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_full[s])) : "memory");
+      GB_TICK(tp_, 2);
+      fill++;
+      cur = nxt;
+      nxt = nxt2;
+    };
+    while (cur.valid && ok) {
+      step(regsA);
+      if (!cur.valid || !ok) break;
+      step(regsB);
     }
-    GB_TICK(2);
-    if (nxt2.valid) load_tile(nxt2, mine);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    GB_TICK(3);
-    if (t == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // descriptors of the first K step; a step of 8 columns is 256 bytes further in either tile (16 in the address
-      // field, which cannot carry: shared-memory addresses stay below 2^18).  One thread issues everything, so the
-      // instruction chain per matrix instruction is kept to an add.
-      const unsigned a_hi = smem_u32(A_st + (size_t) s * 2 * A_BYTES), b_hi = smem_u32(W_st + (size_t) wsel * 2 * W_BYTES);
-      const unsigned long long dA[2] = {make_desc(a_hi, K), make_desc(a_hi + A_BYTES, K)};
-      const unsigned long long dB[2] = {make_desc(b_hi, K), make_desc(b_hi + W_BYTES, K)};
-      const unsigned d = tmem + (unsigned) (cur.tt * N);
-      const bool acc0 = cur.it != cur.i0;
-#pragma unroll
-      for (int pass = 0; pass < 3; pass++) {    // small terms first: a_lo b_hi, a_hi b_lo, a_hi b_hi
-        const unsigned long long a = dA[pass == 0 ? 1 : 0], b = dB[pass == 1 ? 1 : 0];
-#pragma unroll
-        for (int ks = 0; ks < K / 8; ks++) mma_tf32_ss(d, a + (unsigned long long) (ks * 16), b + (unsigned long long) (ks * 16), idesc, acc0 || pass > 0 || ks > 0);
-      }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar[s]) : "memory");
-    }
-    pending[s] = true;
-    fill++;
-    GB_TICK(4);
-    const bool row_done = !nxt.valid || nxt.row != cur.row || nxt.tile0 != cur.tile0;
-    if (row_done) {    // every item of the row is in the accumulators: tensor memory -> global, once per output row
-      for (int q = 0; q < 2 && ok; q++) {
-        const int sq = (fill + q) & 1;    // the older commit first
-        if (pending[sq]) {
-          ok = __syncthreads_and(mbar_wait(bar[sq], phase[sq]));
-          phase[sq] ^= 1;
-          pending[sq] = false;
+#ifdef GB_TC_TIMING
+    if (t == 0 && blockIdx.x == 1 && blockIdx.y == 0)
+      printf("mv_tc K %d N %d S %d TB %d fills %d producer: wait-empty %lld W+convert %lld loads+arrive %lld other %lld\n", K, N, S, TB, fill,
+             tp_[0], tp_[1], tp_[2], tp_[3]);
+#endif
+  } else if (warp == NW) {
+    // ---------------- matrix-instruction issuer ----------------
+    if (lane == 0) {
+      const unsigned idesc = make_idesc(N);
+      Cursor cur;
+      start(cur, blockIdx.x * TB, blockIdx.y);
+      int fill = 0, item_no = -1, rowc = 0;
+      bool ok = true;
+#ifdef GB_TC_TIMING
+      long long tm_[4] = {0, 0, 0, 0}, tq_ = clock64();
+#endif
+      while (cur.valid && ok) {
+        GB_TICK(tm_, 3);
+        const int s = fill % S, set = rowc & 1;
+        if (cur.tt == 0) item_no++;
+        if (cur.it == cur.i0 && cur.tt == 0 && rowc >= 2) {    // first fill of a row: its accumulators were read out
+          ok = wait(&s_accempty[set], (unsigned) ((rowc / 2 - 1) & 1));
+          if (!ok) break;
         }
+        GB_TICK(tm_, 0);
+        ok = wait(&s_full[s], (unsigned) ((fill / S) & 1));
+        if (!ok) break;
+        GB_TICK(tm_, 1);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned a_hi = smem_u32(A_st + (size_t) s * 2 * A_BYTES);
+        const unsigned b_hi = smem_u32(W_st + (size_t) (item_no % S) * 2 * W_BYTES);
+        const unsigned long long dA[2] = {make_desc(a_hi, K), make_desc(a_hi + A_BYTES, K)};
+        const unsigned long long dB[2] = {make_desc(b_hi, K), make_desc(b_hi + W_BYTES, K)};
+        const unsigned d = tmem + (unsigned) ((set * TB + cur.tt) * N);
+        const bool acc0 = cur.it != cur.i0;
+#pragma unroll
+        for (int pass = 0; pass < 3; pass++) {    // small terms first: a_lo b_hi, a_hi b_lo, a_hi b_hi
+          const unsigned long long a = dA[pass == 0 ? 1 : 0], b = dB[pass == 1 ? 1 : 0];
+#pragma unroll
+          for (int ks = 0; ks < K / 8; ks++)
+            mma_tf32_ss(d, a + (unsigned long long) (ks * 16), b + (unsigned long long) (ks * 16), idesc, acc0 || pass > 0 || ks > 0);
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s_empty[s])) : "memory");
+        Cursor nx = cur;
+        advance(nx);
+        if (!nx.valid || nx.row != cur.row || nx.tile0 != cur.tile0) {    // the row is complete once these are done
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s_accfull[set])) : "memory");
+          rowc++;
+        }
+        fill++;
+        cur = nx;
+        GB_TICK(tm_, 2);
       }
-      if (!ok) return;
-      GB_TICK(5);
+#ifdef GB_TC_TIMING
+      if (blockIdx.x == 1 && blockIdx.y == 0)
+        printf("mv_tc K %d N %d issuer: wait-accempty %lld wait-full %lld issue %lld other %lld\n", K, N, tm_[0], tm_[1], tm_[2], tm_[3]);
+#endif
+    }
+  } else {
+    // ---------------- epilogue: tensor memory -> global, once per output row ----------------
+    // Each warp moves blocks of 32 atoms x CB columns of its tensor-memory lanes: registers (a lane holds one atom's
+    // columns) -> a padded transpose buffer of its own -> global memory with whole 128-byte lines per store
+    const int ew = warp & 3;    // the quarter of the tensor-memory lanes this warp may read (warp id modulo 4)
+    float *tr = tr_all + ew * (32 * (CB + 4));
+    constexpr int LPR = CB / 4, RPI = 32 / LPR;    // lanes per atom row, atom rows per store instruction
+    const TensorDev dstT = s_T[op.dst];
+    Cursor cur;
+    start(cur, blockIdx.x * TB, blockIdx.y);
+    int rowc = 0;
+    bool ok = true;
+#ifdef GB_TC_TIMING
+    long long te_[2] = {0, 0}, tq_ = clock64();
+#endif
+    while (cur.valid && ok) {
+      const int set = rowc & 1;
+      ok = wait(&s_accfull[set], (unsigned) ((rowc / 2) & 1));
+      if (!ok) break;
+      GB_TICK(te_, 0);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // Each warp moves blocks of 32 atoms x CB columns: tensor memory -> registers (a lane holds one atom's columns)
-      // -> a padded transpose buffer of its own in the activation stages, which no matrix instruction reads any more
-      // -> global memory with a warp writing whole 128-byte lines (row = atom, CB / 4 lanes per row).
-      const int orow = op.row_out[cur.row], quarter = warp & 3, half = warp >> 2, nblk = N / CB;
-      float *tr = reinterpret_cast<float *>(A_st) + warp * (32 * (CB + 4));
-      constexpr int LPR = CB / 4, RPI = 32 / LPR;    // lanes per atom row, atom rows per store instruction
-      for (int b = half; b < cur.nt * nblk; b += 2) {
+      const int orow = s_row_out[cur.row], nblk = N / CB;
+      const int nb = cur.nt * nblk;
+      // the old values of an accumulating operation are fetched one block ahead of the block being written
+      float4 old[32 / RPI], oldn[32 / RPI];
+      auto load_old = [&](int b, float4 (&o)[32 / RPI]) {
+        const int tt = b / nblk, c0 = (b - tt * nblk) * CB, atom0 = (cur.tile0 + tt) * TM + ew * 32;
+#pragma unroll
+        for (int j = 0; j < 32 / RPI; j++) {
+          const int r = j * RPI + lane / LPR, cq = lane % LPR;
+          o[j] = (b < nb && atom0 + r < na) ? __ldcg(reinterpret_cast<const float4 *>(dstT.p + ((size_t) orow * NA + atom0 + r) * dstT.C + c0) + cq)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      };
+      if (op.accumulate) load_old(0, oldn);
+      for (int b = 0; b < nb; b++) {
         const int tt = b / nblk, c0 = (b - tt * nblk) * CB;
         float v[CB];
-        tmem_ld<CB>(tmem + ((unsigned) (quarter * 32) << 16) + (unsigned) (tt * N + c0), v);
+        tmem_ld<CB>(tmem + ((unsigned) (ew * 32) << 16) + (unsigned) ((set * TB + tt) * N + c0), v);
         __syncwarp();
 #pragma unroll
         for (int q = 0; q < CB / 4; q++)
           *reinterpret_cast<float4 *>(tr + lane * (CB + 4) + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         __syncwarp();
-        const int atom0 = (cur.tile0 + tt) * TM + quarter * 32;
-        float4 old[32 / RPI];
-        if (op.accumulate) {    // all loads of the old values first: independent, in flight together
+        const int atom0 = (cur.tile0 + tt) * TM + ew * 32;
+        if (op.accumulate) {
 #pragma unroll
-          for (int j = 0; j < 32 / RPI; j++) {
-            const int r = j * RPI + lane / LPR, cq = lane % LPR;
-            old[j] = atom0 + r < na ? __ldcg(reinterpret_cast<const float4 *>(dstT.p + ((size_t) orow * NA + atom0 + r) * dstT.C + c0) + cq)
-                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+          for (int j = 0; j < 32 / RPI; j++) old[j] = oldn[j];
+          load_old(b + 1, oldn);
         }
 #pragma unroll
         for (int j = 0; j < 32 / RPI; j++) {
@@ -333,54 +418,54 @@ __global__ void __launch_bounds__(NTH, (K <= 32 ? 2 : 1)) mv_tc_kernel(MVTCDev o
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();    // the accumulators are free for the next row
-      GB_TICK(6);
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_accempty[set])) : "memory");
+      rowc++;
+      next_row(cur);
+      GB_TICK(te_, 1);
     }
-    cur = nxt;
-    nxt = nxt2;
-  };
-  while (cur.valid && ok) {
-    step(regsA);
-    if (!cur.valid || !ok) break;
-    step(regsB);
-  }
 #ifdef GB_TC_TIMING
-  if (t == 0 && blockIdx.x == 1 && blockIdx.y == 0)
-    printf("mv_tc K %d N %d rows %d fills %d TB %d grid %d: stage-wait %lld W %lld convert %lld loads+sync %lld issue %lld drain %lld epilogue %lld other %lld\n",
-           K, N, op.nrows, fill, TB, (int) gridDim.x, tm_[0], tm_[1], tm_[2], tm_[3], tm_[4], tm_[5], tm_[6], tm_[7]);
+    if (warp == NW + 1 && lane == 0 && blockIdx.x == 1 && blockIdx.y == 0)
+      printf("mv_tc K %d N %d epilogue: wait-accfull %lld work %lld rows %d\n", K, N, te_[0], te_[1], rowc);
 #endif
-  if (!ok && t == 0) atomicExch(error, 1);
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (t == 0 && s_abort) atomicExch(error, 1);
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
-// activation stages and weight buffers; at least the transpose buffers of the epilogue (one per warp, in the same space)
-size_t smem_bytes(int K, int N)
+// activation stages, weight ring and the transpose buffers of the four epilogue warps
+size_t smem_bytes(int K, int N, int S)
 {
   const size_t cb = N % 32 == 0 ? 32 : 16;
-  return std::max((size_t) 4 * TM * K * 4 + (size_t) 4 * N * K * 4, (size_t) NW * 32 * (cb + 4) * 4);
+  return (size_t) S * 2 * TM * K * 4 + (size_t) S * 2 * N * K * 4 + (size_t) 4 * 32 * (cb + 4) * 4;
+}
+
+int stages_for(int K, int N) { return smem_bytes(K, N, 4) <= 200 * 1024 ? 4 : 2; }
+
+template<int K, int CB, int S>
+void launch_s(const MVTCDev &op, const TensorDev *T, int ntensors, int NA, int na, int TB, int tmem_cols, dim3 grid, int *error)
+{
+  const size_t smem = smem_bytes(K, op.n_out, S);
+  static size_t attr = 0;
+  if (smem > attr) {
+    GB_CUDA(cudaFuncSetAttribute((mv_tc_kernel<K, CB, S>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    attr = smem;
+  }
+  GB_LAUNCH((mv_tc_kernel<K, CB, S>), grid, NTHREADS, smem, op, T, ntensors, NA, na, TB, tmem_cols, error);
 }
 
 template<int K> void launch_k(const MVTCDev &op, const TensorDev *T, int ntensors, int NA, int na, int TB, dim3 grid, int *error)
 {
-  int tmem_cols = 32;    // a power of two that holds the accumulators of TB tiles
-  while (tmem_cols < TB * op.n_out) tmem_cols *= 2;
-  const size_t smem = smem_bytes(K, op.n_out);
+  int tmem_cols = 32;    // a power of two that holds two sets of accumulators of TB tiles
+  while (tmem_cols < 2 * TB * op.n_out) tmem_cols *= 2;
+  const bool s4 = stages_for(K, op.n_out) == 4;
   if (op.n_out % 32 == 0) {
-    static size_t attr = 0;
-    if (smem > attr) {
-      GB_CUDA(cudaFuncSetAttribute(mv_tc_kernel<K, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-      attr = smem;
-    }
-    GB_LAUNCH((mv_tc_kernel<K, 32>), grid, NTH, smem, op, T, ntensors, NA, na, TB, tmem_cols, error);
+    if (s4) launch_s<K, 32, 4>(op, T, ntensors, NA, na, TB, tmem_cols, grid, error);
+    else launch_s<K, 32, 2>(op, T, ntensors, NA, na, TB, tmem_cols, grid, error);
   } else {
-    static size_t attr = 0;
-    if (smem > attr) {
-      GB_CUDA(cudaFuncSetAttribute(mv_tc_kernel<K, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
-      attr = smem;
-    }
-    GB_LAUNCH((mv_tc_kernel<K, 16>), grid, NTH, smem, op, T, ntensors, NA, na, TB, tmem_cols, error);
+    if (s4) launch_s<K, 16, 4>(op, T, ntensors, NA, na, TB, tmem_cols, grid, error);
+    else launch_s<K, 16, 2>(op, T, ntensors, NA, na, TB, tmem_cols, grid, error);
   }
 }
 
@@ -389,7 +474,7 @@ template<int K> void launch_k(const MVTCDev &op, const TensorDev *T, int ntensor
 bool MVTensorCore::eligible(const MVOp &o, const std::vector<TensorSpec> &tensors)
 {
   if (o.elem || o.items.empty() || o.row_out.empty()) return false;
-  if ((int) tensors.size() > MAX_TENSORS) return false;
+  if ((int) tensors.size() > MAX_TENSORS || (int) o.items.size() > MAX_ITEMS || (int) o.row_out.size() > MAX_ROWS) return false;
   const int K = o.items[0].n_in;
   if (K != 8 && K != 16 && K != 32 && K != 64) return false;
   if (o.n_out % 16 != 0 || o.n_out < 16 || o.n_out > 256) return false;
@@ -398,7 +483,7 @@ bool MVTensorCore::eligible(const MVOp &o, const std::vector<TensorSpec> &tensor
     if (it.n_in != K || tensors[it.src].channels % 4 != 0 || tensors[it.src].channels < K) return false;
   for (size_t r = 0; r + 1 < o.item_off.size(); r++)
     if (o.item_off[r + 1] == o.item_off[r]) return false;    // a row without items has no accumulator to write
-  return smem_bytes(K, o.n_out) <= 227 * 1024;
+  return smem_bytes(K, o.n_out, 2) <= 220 * 1024;
 }
 
 void MVTensorCore::setup(const MVOp &o)
@@ -440,6 +525,7 @@ void MVTensorCore::setup(const MVOp &o)
   images_.ensure(img.size());
   GB_CUDA(cudaMemcpyAsync(images_.get(), img.data(), img.size(), cudaMemcpyHostToDevice, dev().stream));
   items_.upload(items);
+  nitems_ = (int) items.size();
   GB_CUDA(cudaStreamSynchronize(dev().stream));
   ready_ = true;
 }
@@ -455,13 +541,14 @@ void MVTensorCore::launch(const MVDev &d, const TensorDev *tensors, int ntensors
   op.images = images_.get();
   op.n_out = d.n_out;
   op.nrows = d.nrows;
+  op.nitems = nitems_;
   op.accumulate = d.accumulate;
   op.dst = d.dst;
-  // CTAs resident at a time: two per SM for narrow inputs, each with half of the tensor memory
-  const int per_sm = K_ <= 32 && smem_bytes(K_, d.n_out) <= 100 * 1024 ? 2 : 1;
-  const int ntiles = (na + TM - 1) / TM, G = dev().sm_count * per_sm;
-  const int tb_max = std::max(1, std::min(MAX_TILES, TMEM_COLS / per_sm / d.n_out));
-  const int TB = std::max(1, std::min(tb_max, (ntiles + G - 1) / G));
+  // one CTA per SM; two sets of accumulators share the 512 tensor-memory columns
+  const int ntiles = (na + TM - 1) / TM, G = dev().sm_count;
+  const int tb_max = std::max(1, std::min(MAX_TILES, TMEM_COLS / 2 / d.n_out));
+  const int rounds = (ntiles + G * tb_max - 1) / (G * tb_max);
+  const int TB = std::max(1, std::min(tb_max, (ntiles + G * rounds - 1) / (G * rounds)));
   const int gx = std::min(G, (ntiles + TB - 1) / TB);
   const int gy = std::max(1, std::min(d.nrows, G / gx));
   const dim3 grid(gx, gy);

@@ -11,7 +11,7 @@ struct MVTCDev {
   const int *item_off;     // rows + 1
   const MVItem *items;     // as MVDev::items with `mat` = index of the matrix's operand image
   const char *images;      // per matrix: [n_out][K] tf32 hi image, then the lo image (canonical K-major layout)
-  int n_out, nrows, accumulate, dst;
+  int n_out, nrows, nitems, accumulate, dst;
 };
 
 class MVTensorCore {
@@ -27,7 +27,7 @@ class MVTensorCore {
 
  private:
   bool ready_ = false;
-  int K_ = 0;
+  int K_ = 0, nitems_ = 0;
   DBuf<char> images_;
   DBuf<MVItem> items_;
 };

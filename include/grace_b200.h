@@ -108,6 +108,11 @@ int64_t grace_model_engine_setups(const grace_model *m);                 /* engi
  * of the engine's plan; 0 before the first System / Batch of the model.  Diagnostics for roofline figures; no
  * counterpart in the reference. */
 double grace_model_dense_flops(const grace_model *m);
+/* Per atom and evaluation on the per-operation path of the dense network (each program of each layer once):
+ * out6 = {useful flops, algorithmic bytes} of the operations on the tensor cores, of the products, of the per-element
+ * operations (bytes: every input row once per item or tensor, every output row once, twice when it accumulates).
+ * Needs an engine (a System or Batch of the model).  Diagnostics for roofline figures. */
+int grace_model_dense_stats(const grace_model *m, double *out6);
 /* The exact radial MLP of layer 1 or 2 (no tables) for nb scaled distances x = r / r_cut in (0, 1): value R[nb][w] and
  * derivative dR/dx [nb][w] with w = grace_model_radial_mlp_width(), outputs ordered [l][channel]; device pointers, fp32.
  * Runs as tcgen05 tensor-core GEMMs with fused activations (shapes: up to 8 basis functions, two hidden layers of 64,
