@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(128) mv_kernel(MVDev op, const TensorDev *__re
   }
 }
 
-// Per-element weights (reduces over the central atom's element and their adjoints) for a tile of 256 atoms, one thread
+// Per-element weights (reduces over the central atom's element and their adjoints) for a tile of 128 atoms, one thread
 // per atom with all NQ x 4 output channels of a row in registers.  The atoms of the tile are taken in order of their
 // element, so the lanes of a warp mostly read the same weights (one broadcast shared-memory read serves them).  A CTA
 // walks the (row, item) pairs of its rows in groups; the weight matrices of a group, for the elements present in the
@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(128) mv_kernel(MVDev op, const TensorDev *__re
 // group costs two barriers.  Same summation order as mv_kernel.
 constexpr int ELEM_MAXS = 4;    // elements staged at a time (tiles with more walk the items once more per group of elements)
 constexpr int ELEM_GROUP = 4;   // items whose weights are staged together
-constexpr int ELEM_TA = 256;
+constexpr int ELEM_TA = 128;
 template<int NQ>
 __global__ void __launch_bounds__(ELEM_TA) mv_elem_tile_kernel(MVDev op, const TensorDev *__restrict__ T,
                                                                const int *__restrict__ mu, int NA, int na, int n_in_max,
@@ -211,7 +211,7 @@ template<int NQ> void launch_elem(const MVDev &op, const TensorDev *tensors, con
     attr = true;
   }
   // rows of a tile go to one CTA unless the tiles alone cannot fill the GPU
-  const int tiles = (na + ELEM_TA - 1) / ELEM_TA, want = 4 * dev().sm_count;
+  const int tiles = (na + ELEM_TA - 1) / ELEM_TA, want = 16 * dev().sm_count;
   const int gy = std::max(1, std::min(op.nrows, (want + tiles - 1) / tiles));
   const int rows_per_cta = (op.nrows + gy - 1) / gy;
   GB_LAUNCH((mv_elem_tile_kernel<NQ>), dim3(tiles, (op.nrows + rows_per_cta - 1) / rows_per_cta), ELEM_TA, smem, op, tensors, mu,

@@ -27,16 +27,32 @@ __global__ void __launch_bounds__(SCAN_T) scan_tile_sums(const int *__restrict__
   if (threadIdx.x == 0) tmp[blockIdx.x] = sh[0];
 }
 
-__global__ void scan_partials(long long *tmp, long long ntiles, long long *out, long long n)
+// exclusive scan of the tile sums in place by one block: 1024 tile sums at a time (Hillis-Steele in shared memory) with
+// a running carry, so that tens of millions of atoms cost a few passes instead of one thread walking every tile
+__global__ void __launch_bounds__(1024) scan_partials(long long *tmp, long long ntiles, long long *out, long long n)
 {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  long long run = 0;
-  for (long long b = 0; b < ntiles; b++) {
-    const long long v = tmp[b];
-    tmp[b] = run;
-    run += v;
+  __shared__ long long sh[1024];
+  __shared__ long long carry;
+  const int t = threadIdx.x;
+  if (t == 0) carry = 0;
+  __syncthreads();
+  for (long long b0 = 0; b0 < ntiles; b0 += 1024) {
+    const long long b = b0 + t;
+    const long long v = b < ntiles ? tmp[b] : 0;
+    sh[t] = v;
+    __syncthreads();
+    for (int st = 1; st < 1024; st <<= 1) {
+      const long long add = t >= st ? sh[t - st] : 0;
+      __syncthreads();
+      sh[t] += add;
+      __syncthreads();
+    }
+    if (b < ntiles) tmp[b] = carry + sh[t] - v;
+    __syncthreads();
+    if (t == 1023) carry += sh[1023];
+    __syncthreads();
   }
-  out[n] = run;
+  if (t == 0) out[n] = carry;
 }
 
 __global__ void __launch_bounds__(SCAN_T) scan_tile_final(const int *__restrict__ in, const long long *__restrict__ tmp,
@@ -72,7 +88,7 @@ void launch_scan(const int *in, long long *out, long long *tmp, int64_t n)
 {
   const long long ntiles = (n + SCAN_TILE - 1) / SCAN_TILE;
   if (ntiles > 0) GB_LAUNCH(scan_tile_sums, (unsigned) ntiles, SCAN_T, 0, in, tmp, (long long) n);
-  GB_LAUNCH(scan_partials, 1, 32, 0, tmp, ntiles, out, (long long) n);
+  GB_LAUNCH(scan_partials, 1, 1024, 0, tmp, ntiles, out, (long long) n);
   if (ntiles > 0) GB_LAUNCH(scan_tile_final, (unsigned) ntiles, SCAN_T, 0, in, tmp, out, (long long) n);
 }
 
