@@ -47,6 +47,9 @@ SIGNATURES = {
     "grace_model_load": (_I, [C.c_char_p, _I, _P]),
     "grace_model_layers": (_I, [_P]),
     "grace_model_has_uq": (_I, [_P]),
+    "grace_model_validate_uq": (_I, [_P]),
+    "grace_system_set_uq_outputs": (_I, [_P, _P, _P, _P]),
+    "grace_batch_set_uq_outputs": (_I, [_P, _P, _P, _P]),
     "grace_model_n_elements": (_I, [_P]),
     "grace_model_element_name": (C.c_char_p, [_P, _I]),
     "grace_model_engine_setups": (_I64, [_P]),
@@ -433,7 +436,8 @@ class Model:
                                                   C.c_void_p(dR_ptr)))
 
     def validate_uq(self):
-        raise ValueError("the model has no UQ head usable by this backend")
+        """ValueError unless the UQ head of the file can be evaluated (python/kk/kk_api.h:59)."""
+        _check(_lib.grace_model_validate_uq(self._h))
 
 
 def _as(a, dtype, shape=None):
@@ -494,7 +498,7 @@ class System:
 
     def compute(self, types, positions, cell, pbc, energies=False, uq=False, energy_only=False):
         """Result dict as python/kk/kk_module.cpp `compute`: energy, virial [6], forces [n, 3] (not with energy_only),
-        energies [n] (when asked)."""
+        energies [n] (when asked), gamma / total_sigma / atomic_sigma / gmm_cluster (with uq)."""
         types = _as(types, np.int32)
         n = len(types)
         positions = _as(positions, np.float64, (n, 3))
@@ -505,9 +509,18 @@ class System:
         v = np.zeros(6)
         f = None if energy_only else np.zeros((n, 3))
         ea = np.zeros(n) if energies else None
-        _check(_lib.grace_system_compute(self._h, n, _ptr(types), _ptr(positions), _ptr(cell), _ptr(pbc), flags,
-                                         _ptr(e), None if energy_only else _ptr(v), _ptr(f), _ptr(ea)))
+        if uq:
+            g, sg, cl = np.zeros(n), np.zeros(n), np.zeros(n)
+            _check(_lib.grace_system_set_uq_outputs(self._h, _ptr(g), _ptr(sg), _ptr(cl)))
+        try:
+            _check(_lib.grace_system_compute(self._h, n, _ptr(types), _ptr(positions), _ptr(cell), _ptr(pbc), flags,
+                                             _ptr(e), None if energy_only else _ptr(v), _ptr(f), _ptr(ea)))
+        finally:
+            if uq:
+                _lib.grace_system_set_uq_outputs(self._h, None, None, None)
         r = {"energy": float(e[0])}
+        if uq:      # keys of python/kk/kk_module.cpp:72-78
+            r.update(gamma=g, total_sigma=float(sg.sum()), atomic_sigma=sg, gmm_cluster=cl)
         if not energy_only:
             r["forces"] = f
             r["virial"] = v
@@ -516,7 +529,7 @@ class System:
         return r
 
     def compute_device(self, types, positions, cell, pbc, energy, forces=None, virial=None, energies=None,
-                       energy_only=False, n=None):
+                       energy_only=False, n=None, gamma=None, atomic_sigma=None, gmm_cluster=None):
         """Device inputs and outputs, no copies (an extension: the reference has compute_device on Batch only; same
         argument rules): types int32 [n], positions float64 [n, 3], energy float64 [1], forces [n, 3], virial [6],
         energies [n] on the module's GPU; cell and pbc on the host.  Raw device addresses (int) need `n`."""
@@ -530,9 +543,18 @@ class System:
         v = _dev_ptr(virial, "virial", np.float64, (6,), optional=True)
         ea = _dev_ptr(energies, "energies", np.float64, (n,), optional=True)
         flags = (FLAG_ENERGIES if ea else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
-        _check(_lib.grace_system_compute_device(self._h, n, _dev_ptr(types, "types", np.int32, (n,)),
-                                                _dev_ptr(positions, "positions", np.float64, (n, 3)), _ptr(cell),
-                                                _ptr(pbc), flags, e, v, f, ea))
+        uq = [_dev_ptr(a, k, np.float64, (n,), optional=True)
+              for a, k in ((gamma, "gamma"), (atomic_sigma, "atomic_sigma"), (gmm_cluster, "gmm_cluster"))]
+        if any(uq):
+            flags |= FLAG_UQ
+            _check(_lib.grace_system_set_uq_outputs(self._h, *uq))
+        try:
+            _check(_lib.grace_system_compute_device(self._h, n, _dev_ptr(types, "types", np.int32, (n,)),
+                                                    _dev_ptr(positions, "positions", np.float64, (n, 3)), _ptr(cell),
+                                                    _ptr(pbc), flags, e, v, f, ea))
+        finally:
+            if any(uq):
+                _lib.grace_system_set_uq_outputs(self._h, None, None, None)
 
     def neighbor_list(self):
         """Diagnostics: the device neighbour list of the last build (radius cutoff + skin) as (i, j, S [nb, 3]) in the
@@ -660,10 +682,19 @@ class Batch:
         v = np.zeros((nsys, 6))
         f = None if energy_only else np.zeros((ntot, 3))
         ea = np.zeros(ntot) if energies else None
-        _check(_lib.grace_batch_compute(self._h, nsys, _ptr(natoms), ntot, _ptr(types), _ptr(positions), _ptr(cells),
-                                        _ptr(pbc), flags, int(max_nall), _ptr(e), None if energy_only else _ptr(v),
-                                        _ptr(f), _ptr(ea)))
+        if uq:
+            g, sg, cl = np.zeros(ntot), np.zeros(ntot), np.zeros(ntot)
+            _check(_lib.grace_batch_set_uq_outputs(self._h, _ptr(g), _ptr(sg), _ptr(cl)))
+        try:
+            _check(_lib.grace_batch_compute(self._h, nsys, _ptr(natoms), ntot, _ptr(types), _ptr(positions),
+                                            _ptr(cells), _ptr(pbc), flags, int(max_nall), _ptr(e),
+                                            None if energy_only else _ptr(v), _ptr(f), _ptr(ea)))
+        finally:
+            if uq:
+                _lib.grace_batch_set_uq_outputs(self._h, None, None, None)
         r = {"energy": e}
+        if uq:      # keys of python/kk/kk_module.cpp:116-119
+            r.update(gamma=g, atomic_sigma=sg, gmm_cluster=cl)
         if not energy_only:
             r["forces"] = f
             r["virial"] = v
@@ -677,13 +708,12 @@ class Batch:
                        dispersion_energies=None):
         """Batch.compute_device of the reference (python/kk/kk_module.cpp:142-197,258-266): types int32 [N], positions
         float64 [N, 3] and the float64 outputs energy [S], forces [N, 3], virial [S, 6], energies [N] on the module's
-        GPU, taken without conversion; natoms, cells, pbc on the host.  UQ and dispersion outputs are not part of this
-        backend: asking for one raises RuntimeError (unsupported)."""
+        GPU, taken without conversion; natoms, cells, pbc on the host; gamma, atomic_sigma, gmm_cluster float64 [N]
+        (all three or none) ask for the UQ outputs.  Dispersion outputs are not part of this backend: asking for one
+        raises RuntimeError (unsupported)."""
         natoms = _as(natoms, np.int32)
         nsys = len(natoms)
         ntot = int(natoms.sum())
-        if any(x is not None for x in (gamma, atomic_sigma, gmm_cluster)):
-            raise RuntimeError("the model has no UQ head usable by this backend")
         if any(x is not None for x in (dispersion_energy, dispersion_forces, dispersion_virial, dispersion_energies)):
             raise RuntimeError("dispersion corrections are not part of this backend")
         cells = _as(cells, np.float64, (nsys, 3, 3))
@@ -695,5 +725,14 @@ class Batch:
         v = _dev_ptr(virial, "virial", np.float64, (nsys, 6), optional=True)
         ea = _dev_ptr(energies, "energies", np.float64, (ntot,), optional=True)
         flags = (FLAG_ENERGIES if ea else 0) | (FLAG_ENERGY_ONLY if energy_only else 0)
-        _check(_lib.grace_batch_compute_device(self._h, nsys, _ptr(natoms), ntot, t, x, _ptr(cells), _ptr(pbc), flags,
-                                               int(max_nall), e, v, f, ea))
+        uq = [_dev_ptr(a, k, np.float64, (ntot,), optional=True)
+              for a, k in ((gamma, "gamma"), (atomic_sigma, "atomic_sigma"), (gmm_cluster, "gmm_cluster"))]
+        if any(uq):
+            flags |= FLAG_UQ
+            _check(_lib.grace_batch_set_uq_outputs(self._h, *uq))
+        try:
+            _check(_lib.grace_batch_compute_device(self._h, nsys, _ptr(natoms), ntot, t, x, _ptr(cells), _ptr(pbc),
+                                                   flags, int(max_nall), e, v, f, ea))
+        finally:
+            if any(uq):
+                _lib.grace_batch_set_uq_outputs(self._h, None, None, None)

@@ -186,16 +186,8 @@ __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, S
             }
           }
         }
-#pragma unroll
-        for (int s = LPE / 2; s > 0; s >>= 1) {
-          gx += __shfl_xor_sync(0xffffffffu, gx, s);
-          gy += __shfl_xor_sync(0xffffffffu, gy, s);
-          gz += __shfl_xor_sync(0xffffffffu, gz, s);
-          dedx += __shfl_xor_sync(0xffffffffu, dedx, s);
-        }
-        if (valid && ln == 0) {    // one owner per bond and tile: no race
-          fe[e][0] += gx; fe[e][1] += gy; fe[e][2] += gz; fe[e][3] += dedx;
-        }
+        const float tot = group_sum4<LPE>(gx, gy, gz, dedx, ln);
+        if (valid && (ln & (LPE / 4 - 1)) == 0) fe[e][ln / (LPE / 4)] += tot;    // one owner per bond, tile and component: no race
       }
       __syncthreads();
     }
@@ -344,14 +336,8 @@ __global__ void __launch_bounds__(128) bond_bwd_split_kernel(BondsDev b, LayerDe
             else atomicAdd(L.gmsg + ((size_t) sj[e] * L.n_msg + I) * C + n, gm[I]);
           }
       }
-#pragma unroll
-      for (int s = 16; s > 0; s >>= 1) {
-        gx += __shfl_xor_sync(0xffffffffu, gx, s);
-        gy += __shfl_xor_sync(0xffffffffu, gy, s);
-        gz += __shfl_xor_sync(0xffffffffu, gz, s);
-        dedx += __shfl_xor_sync(0xffffffffu, dedx, s);
-      }
-      if (lane == 0) { fe[e][0] = gx; fe[e][1] = gy; fe[e][2] = gz; fe[e][3] = dedx; }
+      const float tot = group_sum4<32>(gx, gy, gz, dedx, lane);
+      if ((lane & 7) == 0) fe[e][lane >> 3] = tot;
     }
     __syncthreads();
     for (int e = tid; e < nbat; e += 128) {

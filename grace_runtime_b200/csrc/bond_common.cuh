@@ -65,6 +65,22 @@ __device__ __forceinline__ void sph_harm(const SHTable &t, float rx, float ry, f
   }
 }
 
+// Sums of four per-lane values over the groups of G consecutive lanes of a warp (G = 8, 16 or 32) with 1 + log2(G)
+// shuffles instead of 4 log2(G): the halves of a group first trade two of the values, the quarters one, and from then
+// on every lane carries a single value.  Afterwards lane q G / 4 of a group (q = 0 .. 3) holds the sum of value q in
+// `out`; the additions pair the same lanes as a butterfly per value, so the sums are bit-identical to it.
+template<int G>
+__device__ __forceinline__ float group_sum4(float v0, float v1, float v2, float v3, int lane_in_group)
+{
+  const bool up = lane_in_group & (G / 2), odd = lane_in_group & (G / 4);
+  const float r0 = __shfl_xor_sync(0xffffffffu, up ? v0 : v2, G / 2), r1 = __shfl_xor_sync(0xffffffffu, up ? v1 : v3, G / 2);
+  const float k0 = (up ? v2 : v0) + r0, k1 = (up ? v3 : v1) + r1;
+  float v = (odd ? k1 : k0) + __shfl_xor_sync(0xffffffffu, odd ? k0 : k1, G / 4);
+#pragma unroll
+  for (int s = G / 8; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  return v;
+}
+
 // interval k and offset t of x = r / rcut in a table of N intervals (libgrace/include/grace/fused_cpu.h:1052-1058)
 __device__ __forceinline__ void spline_locate(float x, int N, int &k, float &t)
 {

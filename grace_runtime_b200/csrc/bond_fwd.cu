@@ -23,8 +23,10 @@ template<int LMAX, int NIT, int NCH, int LPE, bool EXACT>
 __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, SHTable sht, float *__restrict__ Q,
                                                        int NA, int a0)
 {
-  constexpr int NL = LMAX + 1, NLM = NL * NL, NLMP = NLM | 1, NQ = NIT * NLM, CP = LPE * NCH, EPW = 32 / LPE;
-  __shared__ float Ys[EB][NLMP];
+  // rows of the staged harmonics: a multiple of 4 floats (the lanes of a bond read them as broadcast 16-byte loads, a
+  // quarter of the shared-memory transactions of scalar reads) plus 4, which spreads the rows over the banks
+  constexpr int NL = LMAX + 1, NLM = NL * NL, NLM4 = (NLM + 3) / 4, NLMP = 4 * NLM4 + ((4 * NLM4 + 4) % 32 ? 4 : 8), NQ = NIT * NLM, CP = LPE * NCH, EPW = 32 / LPE;
+  __shared__ __align__(16) float Ys[EB][NLMP];
   __shared__ float st[EB];
   __shared__ int sk[EB], smu[EB], sj[EB];
   __shared__ float red[NQ][CP];
@@ -66,7 +68,12 @@ __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, S
       if (e < nbat) {
         const int k = sk[e], muj = smu[e], j = sj[e];
         const float t = st[e];
-        const float *y = Ys[e];
+        float y[4 * NLM4];
+#pragma unroll
+        for (int q4 = 0; q4 < NLM4; q4++) {
+          const float4 v = reinterpret_cast<const float4 *>(Ys[e])[q4];
+          y[4 * q4] = v.x; y[4 * q4 + 1] = v.y; y[4 * q4 + 2] = v.z; y[4 * q4 + 3] = v.w;
+        }
 #pragma unroll
         for (int ch = 0; ch < NCH; ch++) {
           const int n = ln + ch * LPE;
@@ -131,15 +138,17 @@ __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, S
 }
 
 // The same for layers that couple message functions in (NIT > 1) with at most 16 channels: a whole warp per bond, lane
-// = (channel n, half h) with the lm split between the halves (lm = 2 k + h), so that a lane keeps NIT x NLM / 2 partial
+// = (channel n, half h) with the lm split between the halves (lm = h NK + k), so that a lane keeps NIT x NLM / 2 partial
 // sums in registers instead of NIT x NLM (twice the resident warps) and the two halves share the work of a bond:
 //   Q[(I, lm)][n] += (Y_lm R_l) msg_I      with R of the lm's degree selected per lm.
 template<int LMAX, int NIT>
 __global__ void __launch_bounds__(128) bond_fwd_split_kernel(BondsDev b, LayerDev L, SHTable sht, float *__restrict__ Q, int NA,
                                                              int a0)
 {
-  constexpr int NL = LMAX + 1, NLM = NL * NL, NLMP = NLM | 1, NQ = NIT * NLM, NK = (NLM + 1) / 2;
-  __shared__ float Ys[EB][NLMP];
+  // half h of a bond's lanes takes lm = h NK .. h NK + NK - 1: contiguous, so that its harmonics come as broadcast
+  // 16-byte loads (rows of NK4 float4 per half)
+  constexpr int NL = LMAX + 1, NLM = NL * NL, NQ = NIT * NLM, NK = (NLM + 1) / 2, NK4 = (NK + 3) / 4, NLMP = 8 * NK4 + 4;
+  __shared__ __align__(16) float Ys[EB][NLMP];
   __shared__ float st[EB];
   __shared__ int sk[EB], smu[EB], sj[EB];
   __shared__ float red[NQ][16];
@@ -170,14 +179,19 @@ __global__ void __launch_bounds__(128) bond_fwd_split_kernel(BondsDev b, LayerDe
       sk[e] = k; st[e] = t; smu[e] = muj; sj[e] = j;
       float *y = Ys[e];
       sph_harm<LMAX, false>(sht, rec.x * ir, rec.y * ir, rec.z * ir,
-                            [&](int lm, float v, float, float, float) { y[lm] = v; });
+                            [&](int lm, float v, float, float, float) { y[lm < NK ? lm : 4 * NK4 + lm - NK] = v; });
     }
     __syncthreads();
     for (int e = w; e < nbat; e += 4) {    // a warp per bond
       if (n < C) {
         const int k0 = sk[e], muj = smu[e], j = sj[e];
         const float t = st[e];
-        const float *y = Ys[e];
+        float y[4 * NK4];
+#pragma unroll
+        for (int q4 = 0; q4 < NK4; q4++) {
+          const float4 v = reinterpret_cast<const float4 *>(Ys[e])[h * NK4 + q4];
+          y[4 * q4] = v.x; y[4 * q4 + 1] = v.y; y[4 * q4 + 2] = v.z; y[4 * q4 + 3] = v.w;
+        }
         float R[NL];
         const float4 *cf = reinterpret_cast<const float4 *>(L.tab) + (size_t) k0 * NL * C + n;
 #pragma unroll
@@ -195,10 +209,10 @@ __global__ void __launch_bounds__(128) bond_fwd_split_kernel(BondsDev b, LayerDe
 #pragma unroll
         for (int k = 0; k < NK; k++) {
           constexpr auto deg = [](int q) { int l = 0; while ((l + 1) * (l + 1) <= q) l++; return l; };
-          const int q = 2 * k + h;
-          const int l0 = deg(2 * k), l1 = deg(2 * k + 1 < NLM ? 2 * k + 1 : NLM - 1);
+          const int q = h * NK + k;
+          const int l0 = deg(k), l1 = deg(NK + k < NLM ? NK + k : NLM - 1);
           if (q < NLM) {
-            const float yr = y[q] * (h ? R[l1] : R[l0]);
+            const float yr = y[k] * (h ? R[l1] : R[l0]);
 #pragma unroll
             for (int I = 0; I < NIT; I++) acc[I][k] = fmaf(yr, m[I], acc[I][k]);
           }
@@ -214,7 +228,7 @@ __global__ void __launch_bounds__(128) bond_fwd_split_kernel(BondsDev b, LayerDe
       for (int I = 0; I < NIT; I++)
 #pragma unroll
         for (int k = 0; k < NK; k++) {
-          const int q = 2 * k + h;
+          const int q = h * NK + k;
           if (q < NLM) {
             float *r = &red[I * NLM + q][n];
             *r = (ww == 0) ? acc[I][k] : *r + acc[I][k];

@@ -186,8 +186,9 @@ int grace_measure_peak(int kind, double *tflops)
     if (!tflops) throw InvalidArgument("tflops must be given");
     if (kind == 0) *tflops = measure_peak_fp32_tflops();
     else if (kind == 1) *tflops = measure_peak_tf32_tflops();
+    else if (kind == 2) *tflops = measure_peak_fp32_tflops(true);
     else if (kind >= 16) *tflops = measure_peak_tf32_tflops(kind);    // the same with N = kind instead of 256
-    else throw InvalidArgument("kind must be 0 (fp32 FMA), 1 (tf32 tensor cores, N = 256) or N (a multiple of 16 up to 256)");
+    else throw InvalidArgument("kind must be 0 (fp32 FMA), 1 (tf32 tensor cores, N = 256), 2 (fp32 packed FMA) or N (a multiple of 16 up to 256)");
   });
 }
 
@@ -228,7 +229,18 @@ int grace_model_load(const char *path, int spline, grace_model **out)
 }
 
 int grace_model_layers(const grace_model *m) { return m ? m->m->model.layers : 0; }
-int grace_model_has_uq(const grace_model *) { return 0; }
+int grace_model_has_uq(const grace_model *m) { return m && m->m->model.has_uq ? 1 : 0; }
+int grace_model_validate_uq(const grace_model *m)
+{
+  return guarded([&] {
+    if (!m) throw InvalidArgument("model must be given");
+    try {
+      m->m->model.validate_uq();
+    } catch (const ModelError &e) {
+      throw InvalidArgument(e.what());
+    }
+  });
+}
 int grace_model_n_elements(const grace_model *m) { return m ? (int) m->m->model.element_names.size() : 0; }
 const char *grace_model_element_name(const grace_model *m, int i)
 {
@@ -302,6 +314,14 @@ int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, 
     if (!s) throw InvalidArgument("system must be given");
     if (!d_energy) throw InvalidArgument("the energy output must be given");
     s->s->compute(n, d_types, d_pos, true, cell, pbc, flags, d_energy, d_virial6, d_forces, d_energies, true);
+  });
+}
+
+int grace_system_set_uq_outputs(grace_system *s, double *gamma, double *sigma, double *cluster)
+{
+  return guarded([&] {
+    if (!s) throw InvalidArgument("system must be given");
+    s->s->uq_out = UqOutputs{gamma, sigma, cluster};
   });
 }
 
@@ -454,6 +474,14 @@ int grace_batch_compute_device(grace_batch *b, int nsys, const int32_t *natoms, 
     if (!d_energy) throw InvalidArgument("the energy output must be given");
     b->b->compute(nsys, natoms, ntot, d_types, d_pos, true, cell, pbc, flags, max_nall, d_energy, d_virial, d_forces,
                   d_energies);
+  });
+}
+
+int grace_batch_set_uq_outputs(grace_batch *b, double *gamma, double *sigma, double *cluster)
+{
+  return guarded([&] {
+    if (!b) throw InvalidArgument("batch must be given");
+    b->b->uq_out = UqOutputs{gamma, sigma, cluster};
   });
 }
 

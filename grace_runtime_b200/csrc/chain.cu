@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(256) prod_tile_kernel(ProdDev op, const Tensor
   const int a0 = blockIdx.x * TA, nta = min(TA, na - a0);
   float4 *sA = reinterpret_cast<float4 *>(psm);
   float4 *sB = sA + (size_t) nfA * TAC4;
-  ProdTerm *sT = reinterpret_cast<ProdTerm *>(sB + (size_t) nfB * TAC4);
+  int4 *sT = reinterpret_cast<int4 *>(sB + (size_t) nfB * TAC4);    // per term: row offsets of both operands, coefficient
   const bool two = op.srcB >= 0 && op.srcB != op.srcA;
   {
     // eight independent 16-byte loads per thread in flight: the tile's rows come from nf separate regions of the
@@ -306,39 +306,57 @@ __global__ void __launch_bounds__(256) prod_tile_kernel(ProdDev op, const Tensor
     };
     stage(T[op.srcA].p, sA, nfA);
     if (two) stage(T[op.srcB].p, sB, nfB);
-    for (int idx = t; idx < nterms; idx += 256) sT[idx] = op.terms[idx];
+    for (int idx = t; idx < nterms; idx += 256) {
+      const ProdTerm tm = op.terms[idx];
+      sT[idx] = make_int4(tm.a * TAC4, tm.b * TAC4, __float_as_int(tm.coef), 0);
+    }
   }
   __syncthreads();
   const float4 *Bs = op.srcB < 0 ? nullptr : (two ? sB : sA);
   float *D = T[op.dst].p;
   const int nvalid = nta * C4, warp = t >> 5, lane = t & 31;
-  // a warp takes an output row and walks its TA x C values 32 float4 at a time: the term loop is uniform in the warp
-  // and a term is one broadcast read
+  // a warp takes an output row and walks its TA x C values 64 float4 at a time, two per lane, so that a term (one
+  // broadcast 16-byte read) serves two positions; the products are packed two-wide FMAs (the same roundings as
+  // fmaf(coef * a, b, acc) per channel)
+  auto f2 = [](float x, float y) { return make_float2(x, y); };
   for (int row = warp; row < op.nrows; row += 8) {
     const int t0 = op.term_off[row], t1 = op.term_off[row + 1];
     float4 *orow = reinterpret_cast<float4 *>(D + ((size_t) op.row_out[row] * NA + a0) * C);
-    for (int r = lane; r < nvalid; r += 32) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = lane; r < nvalid; r += 64) {
+      const bool has1 = r + 32 < nvalid;
+      const int r1 = has1 ? r + 32 : r;
+      float2 a0l = f2(0.f, 0.f), a0h = a0l, a1l = a0l, a1h = a0l;
       if (Bs) {
         for (int q = t0; q < t1; q++) {
-          const ProdTerm tm = sT[q];
-          const float4 av = sA[tm.a * TAC4 + r], bv = Bs[tm.b * TAC4 + r];
-          acc.x = fmaf(tm.coef * av.x, bv.x, acc.x); acc.y = fmaf(tm.coef * av.y, bv.y, acc.y);
-          acc.z = fmaf(tm.coef * av.z, bv.z, acc.z); acc.w = fmaf(tm.coef * av.w, bv.w, acc.w);
+          const int4 tm = sT[q];
+          const float cf = __int_as_float(tm.z);
+          const float2 c2 = f2(cf, cf);
+          const float4 av0 = sA[tm.x + r], bv0 = Bs[tm.y + r], av1 = sA[tm.x + r1], bv1 = Bs[tm.y + r1];
+          a0l = __ffma2_rn(__fmul2_rn(c2, f2(av0.x, av0.y)), f2(bv0.x, bv0.y), a0l);
+          a0h = __ffma2_rn(__fmul2_rn(c2, f2(av0.z, av0.w)), f2(bv0.z, bv0.w), a0h);
+          a1l = __ffma2_rn(__fmul2_rn(c2, f2(av1.x, av1.y)), f2(bv1.x, bv1.y), a1l);
+          a1h = __ffma2_rn(__fmul2_rn(c2, f2(av1.z, av1.w)), f2(bv1.z, bv1.w), a1h);
         }
       } else {
         for (int q = t0; q < t1; q++) {
-          const ProdTerm tm = sT[q];
-          const float4 av = sA[tm.a * TAC4 + r];
-          acc.x = fmaf(tm.coef, av.x, acc.x); acc.y = fmaf(tm.coef, av.y, acc.y);
-          acc.z = fmaf(tm.coef, av.z, acc.z); acc.w = fmaf(tm.coef, av.w, acc.w);
+          const int4 tm = sT[q];
+          const float cf = __int_as_float(tm.z);
+          const float2 c2 = f2(cf, cf);
+          const float4 av0 = sA[tm.x + r], av1 = sA[tm.x + r1];
+          a0l = __ffma2_rn(c2, f2(av0.x, av0.y), a0l);
+          a0h = __ffma2_rn(c2, f2(av0.z, av0.w), a0h);
+          a1l = __ffma2_rn(c2, f2(av1.x, av1.y), a1l);
+          a1h = __ffma2_rn(c2, f2(av1.z, av1.w), a1h);
         }
       }
+      float4 o0 = make_float4(a0l.x, a0l.y, a0h.x, a0h.y), o1 = make_float4(a1l.x, a1l.y, a1h.x, a1h.y);
       if (op.accumulate) {
-        const float4 old = orow[r];
-        acc.x += old.x; acc.y += old.y; acc.z += old.z; acc.w += old.w;
+        const float4 old0 = orow[r], old1 = orow[r1];
+        o0.x += old0.x; o0.y += old0.y; o0.z += old0.z; o0.w += old0.w;
+        o1.x += old1.x; o1.y += old1.y; o1.z += old1.z; o1.w += old1.w;
       }
-      orow[r] = acc;
+      orow[r] = o0;
+      if (has1) orow[r1] = o1;
     }
   }
 }
@@ -349,7 +367,7 @@ void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, in
   // tiled form: channels a multiple of 4 and at least one atom of input rows in shared memory
   if ((C & 3) == 0 && nfA > 0) {
     const bool two = op.srcB >= 0 && op.srcB != op.srcA;
-    const size_t per_atom = (size_t) (nfA + (two ? nfB : 0)) * C * 4, fixed = (size_t) nterms * sizeof(ProdTerm) + 64;
+    const size_t per_atom = (size_t) (nfA + (two ? nfB : 0)) * C * 4, fixed = (size_t) nterms * sizeof(int4) + 64;
     // several CTAs per SM (the load, compute and store phases of a tile overlap only across CTAs): a quarter of the
     // shared memory when that holds 4+ atoms, else half, else all of it
     const size_t quarter = 54 * 1024, half = 110 * 1024, large = 200 * 1024;

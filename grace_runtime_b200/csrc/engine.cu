@@ -162,7 +162,7 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
     E.mv_tc.clear();
     E.mv_tc.resize(P.mv.size());
     for (size_t q = 0; q < P.mv.size(); q++) {
-      const double fl = P.mv[q].flops_per_atom();
+      const double fl = (int) q == P.uq_mv ? 0.0 : P.mv[q].flops_per_atom();    // the UQ projection is not part of a step
       all += fl;
       if (MVTensorCore::eligible(P.mv[q], P.tensors)) {
         E.mv_tc[q].setup(P.mv[q]);
@@ -239,6 +239,16 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
     lnI_.upload(P.lnI);
     ln0_.upload(P.ln0);
   }
+  if (P.uq.ready) {
+    uq_cen_.set_label("engine:uq"); uq_icov_.set_label("engine:uq"); uq_thr_.set_label("engine:uq"); uq_ncl_.set_label("engine:uq");
+    uq_out_.set_label("work:uq"); uq_n2a_.set_label("work:uq"); uq_n2b_.set_label("work:uq"); uq_z1_.set_label("work:uq");
+    uq_cen_.upload(P.uq.centroids);
+    uq_icov_.upload(P.uq.inv_cov);
+    uq_thr_.upload(P.uq.thresholds);
+    uq_ncl_.upload(P.uq.n_clusters);
+    uq_dev_ = UqDev{uq_cen_.get(), uq_icov_.get(), uq_thr_.get(), uq_ncl_.get(), P.uq.rp_dim, P.uq.feature_dim,
+                    P.uq.max_clusters, P.uq.n_density, P.uq.density_scale};
+  }
   ReadoutDev &r = readout_;
   r.W = eW_.get();
   r.WT = eWT_.get();
@@ -279,6 +289,7 @@ void Engine::dense_stats(double *o) const
     if (!E->plan) continue;
     const LayerPlan &P = *E->plan;
     for (size_t q = 0; q < P.mv.size(); q++) {
+      if ((int) q == P.uq_mv) continue;
       const MVOp &m = P.mv[q];
       double fl = 0.0, by = 0.0;
       for (const MVItem &it : m.items) {
@@ -337,6 +348,7 @@ void Engine::release_work()
   arena_.release(); fv_.release(); I_rows_.release(); gI_rows_.release(); rho_rows_.release();
   e_atom_.release(); vir_atom_.release(); grho_rows_.release(); sum_scratch_.release();
   xs_.release(); R1_.release(); dR1_.release(); R2_.release(); dR2_.release(); l1_saved_.release(); gmsg_slot_.release();
+  uq_out_.release(); uq_n2a_.release(); uq_n2b_.release(); uq_z1_.release();
   arena1_.release();
   arena1_bound_ = nullptr;
   arena1_NA_ = 0;
@@ -426,6 +438,34 @@ void Engine::run(LayerEngine &E, const Program &prog, const int *mu, int NA, int
   if (tag_ops) launch_tag(nullptr);
 }
 
+// UQ of GRACE-2L, layer 1 (after the forward program of a chunk of layer 1): projection of the rho block, kept per atom
+// with its squared norm until layer 2 adds its own (libgrace/src/fused_2l.cpp:1116-1170)
+void Engine::uq_layer1(const int *mu, int64_t a0, int na, int stride)
+{
+  const LayerPlan &P = *L1_.plan;
+  const int q = P.uq_mv;
+  if (tc_now_ && L1_.mv_tc[q].ready())
+    L1_.mv_tc[q].launch(L1_.mv[q], L1_.tensors.get(), (int) L1_.tensors_host.size(), stride, na, tc_error_.get());
+  else launch_mv(L1_.mv[q], L1_.tensors.get(), mu, stride, na);
+  launch_uq_norm(L1_.mv[q], L1_.tensors.get(), stride, na, uq_n2b_.get() + a0);
+  launch_rows_from_chunk(L1_.tensors_host[P.tUQ].p, uq_z1_.get(), 1, plan_.uq.rp_dim, stride, na, (int) a0);
+}
+
+// UQ after the forward program of a chunk of the last layer E: its projection and norm, then the mixture model
+void Engine::uq_last(LayerEngine &E, const int *mu, int64_t a0, int na, int stride, int64_t n)
+{
+  const LayerPlan &P = *E.plan;
+  const int q = P.uq_mv;
+  if (tc_now_ && E.mv_tc[q].ready())
+    E.mv_tc[q].launch(E.mv[q], E.tensors.get(), (int) E.tensors_host.size(), stride, na, tc_error_.get());
+  else launch_mv(E.mv[q], E.tensors.get(), mu + a0, stride, na);
+  launch_uq_norm(E.mv[q], E.tensors.get(), stride, na, uq_n2a_.get() + a0);
+  const bool two = plan_.layers == 2;
+  double *o = uq_out_.get();
+  launch_uq_gmm(uq_dev_, E.tensors_host[P.tUQ].p, two ? uq_z1_.get() : nullptr, uq_n2a_.get(), two ? uq_n2b_.get() : nullptr, mu,
+                na, (long long) a0, o, o + n, o + 2 * n);
+}
+
 // shared-memory layout of the tensors of an atom tile: every tensor padded to 4 floats per atom; a gradient that may
 // alias a forward tensor shares its offset; TA = the largest atom tile that fits the 227 KB of an SM
 void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
@@ -437,7 +477,7 @@ void Engine::setup_fused(LayerEngine &E, const LayerPlan &P)
   auto size_of = [&](size_t t) { return ((long long) P.tensors[t].nfuncs * P.tensors[t].channels + 3) / 4 * 4; };
   for (size_t t = 0; t < nt; t++) {
     tch[t] = P.tensors[t].channels;
-    if (P.tensors[t].alias >= 0) continue;
+    if (P.tensors[t].alias >= 0 || (int) t == P.tUQ) continue;    // the UQ projection runs on the per-operation path only
     soff[t] = (int) at;
     at += size_of(t);
   }
@@ -750,6 +790,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       if (tm) tm->begin(StageTimer::FWD);
       launch_bond_fwd(P.lmax, bonds, L, T1(P.L1.tQ), NA, (int) a0, na);
       run(L1_, P.L1.fwd, mu + a0, na, NA);
+      if (uq_now_) uq_last(L1_, mu, a0, na, NA, n);
       launch_readout_1l(readout_, T1(P.t1_rho), T1(P.t1_grho), mu, e_atom_.get(), NA, na, (int) a0, !energy_only);
       if (tm) tm->end(StageTimer::FWD);
       if (energy_only) continue;
@@ -780,6 +821,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       const int na = (int) std::min<int64_t>(step1, R.hi1 - a0);
       { TagScope tg("layer1"); launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), S1, (int) a0, na); }
       run(L1_, P.L1.fwd, mu + a0, na, S1);
+      if (uq_now_) uq_layer1(mu + a0, a0, na, S1);
       launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, S1, na, (int) a0);
       launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, S1, na, (int) a0);
     }
@@ -791,6 +833,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       if (tm) tm->begin(StageTimer::FWD);
       { TagScope tg("layer2"); launch_bond_fwd(P.lmax, bonds, Lb, T2(P.L2.tQ), NA, (int) a0, na); }
       run(L2_, P.L2.fwd, mu + a0, na, NA);
+      if (uq_now_) uq_last(L2_, mu, a0, na, NA, n);
       launch_readout_2l(readout_, rho_rows_.get(), T2(P.t2_I2), grho_rows_.get(), T2(P.t2_gI2), mu, e_atom_.get(), NA,
                         na, (int) a0, !energy_only);
       if (tm) tm->end(StageTimer::FWD);
@@ -884,7 +927,20 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
     return;
   }
   const int64_t n_eval = R.list0 ? std::max(R.n0, R.n1) : std::max(R.hi0 - R.lo0, R.hi1 - R.lo1);
-  const bool fused_now = use_fused(n_eval);
+  uq_now_ = out.gamma != nullptr;
+  if (uq_now_) {
+    if (!plan_.uq.ready) throw InvalidArgument("the model has no usable UQ head");
+    if (!out.sigma || !out.cluster) throw InvalidArgument("uq needs the gamma, sigma and cluster outputs");
+    // results per atom in list order (zero for atoms the call does not own); layer-1 rows of GRACE-2L
+    GB_CUDA(cudaMemsetAsync(uq_out_.ensure(3 * (size_t) n), 0, sizeof(double) * 3 * (size_t) n, st));
+    uq_n2a_.ensure(n);
+    if (plan_.layers == 2) {
+      uq_n2b_.ensure(n);
+      uq_z1_.ensure((size_t) n * plan_.uq.rp_dim);
+    }
+  }
+  // the UQ projection reads the chunk tensors of the per-operation path
+  const bool fused_now = !uq_now_ && use_fused(n_eval);
   tc_now_ = !fused_now && use_tc(n_eval);
   if (!fused_now) R.list0 = R.list1 = nullptr;    // the per-operation path evaluates the enclosing ranges
   const bool partial = R.list0 ? (R.n0 < n || R.n1 < n) : (R.lo0 > 0 || R.hi0 < n || R.lo1 > 0 || R.hi1 < n);
@@ -947,6 +1003,11 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
   double *scr = nb > 1 ? sum_scratch_.ensure((size_t) nsys * 6 * nb) : nullptr;
   if (out.energy) launch_segment_sum(e_atom_.get(), 1, nl.seg(), nsys, out.energy, scr, nb);
   if (out.energies) launch_scatter_f64(e_atom_.get(), nl.perm(), out.energies, (int) n);
+  if (uq_now_) {
+    launch_scatter_f64(uq_out_.get(), nl.perm(), out.gamma, (int) n);
+    launch_scatter_f64(uq_out_.get() + n, nl.perm(), out.sigma, (int) n);
+    launch_scatter_f64(uq_out_.get() + 2 * n, nl.perm(), out.cluster, (int) n);
+  }
   if (!energy_only) {
     if (out.virial) launch_segment_sum(vir_atom_.get(), 6, nl.seg(), nsys, out.virial, scr, nb);
     if (out.forces) {
@@ -1008,10 +1069,14 @@ int read_int(const int *d)
   return h;
 }
 
-void check_flags(int flags)
+// flag 4 (UQ): the engine must have a usable head and the caller must have named the three outputs
+// (python/kk/kk_core.cpp:826-827, 1284-1286)
+void check_flags(int flags, const Engine &e, const UqOutputs &uq)
 {
-  if (flags & 4) throw Unsupported("the model has no UQ head usable by this backend");
   if (flags & ~7) throw InvalidArgument("unknown compute flag");
+  if (!(flags & 4)) return;
+  if (!e.uq_available()) throw InvalidArgument("the model has no usable UQ head (schema 6, gamma only)");
+  if (!uq.gamma || !uq.sigma || !uq.cluster) throw InvalidArgument("uq needs the gamma, sigma and cluster outputs");
 }
 
 }    // namespace
@@ -1058,7 +1123,7 @@ void SystemObj::compute(int n, const int *types, const double *pos, bool device_
                         double *energies, bool device_out)
 {
   require_initialized();
-  check_flags(flags);
+  check_flags(flags, *engine_, uq_out);
   if (n < 0) throw InvalidArgument("negative atom count");
   if (n > 0 && (!types || !pos)) throw InvalidArgument("types and positions must be given");
   if (!cell || !pbc) throw InvalidArgument("cell and pbc must be given");
@@ -1097,7 +1162,7 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
                              double *energies, bool device_out, int chunk)
 {
   cudaStream_t st = dev().stream;
-  const bool eonly = flags & 2, want_e = flags & 1;
+  const bool eonly = flags & 2, want_e = flags & 1, want_uq = flags & 4;
   timer_.reset();
   timer_.begin(StageTimer::TOTAL);
   const int ns = (int) t2m_.size();
@@ -1157,11 +1222,17 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     o.virial = eonly ? nullptr : virial;
     o.forces = eonly ? nullptr : forces;
     o.energies = want_e ? energies : nullptr;
+    if (want_uq) { o.gamma = uq_out.gamma; o.sigma = uq_out.sigma; o.cluster = uq_out.cluster; }
   } else {
     o.energy = ws_.energy.ensure(1);
     if (!eonly && virial) o.virial = ws_.virial.ensure(6);
     if (!eonly && forces) o.forces = ws_.forces.ensure(3 * (size_t) std::max(n, 1));
     if (want_e && energies) o.energies = ws_.energies.ensure(std::max(n, 1));
+    if (want_uq) {
+      o.gamma = ws_.uq.ensure(3 * (size_t) std::max(n, 1));
+      o.sigma = o.gamma + n;
+      o.cluster = o.gamma + 2 * (size_t) n;
+    }
   }
   engine_->evaluate(nl_, eonly, o, chunk, &timer_, nlocal >= 0 ? &ranges : nullptr);
   if (exchange.active()) {
@@ -1173,6 +1244,11 @@ void SystemObj::compute_once(int n, const int *types, const double *pos, bool de
     if (o.virial) GB_CUDA(cudaMemcpyAsync(virial, o.virial, sizeof(double) * 6, cudaMemcpyDeviceToHost, st));
     if (o.forces && n > 0) GB_CUDA(cudaMemcpyAsync(forces, o.forces, sizeof(double) * 3 * n, cudaMemcpyDeviceToHost, st));
     if (o.energies && n > 0) GB_CUDA(cudaMemcpyAsync(energies, o.energies, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+    if (want_uq && n > 0) {
+      GB_CUDA(cudaMemcpyAsync(uq_out.gamma, o.gamma, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+      GB_CUDA(cudaMemcpyAsync(uq_out.sigma, o.sigma, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+      GB_CUDA(cudaMemcpyAsync(uq_out.cluster, o.cluster, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+    }
   }
   timer_.end(StageTimer::TOTAL);
   const int fl = n > 0 ? nl_.take_flag() : 0;    // synchronises the stream
@@ -1212,7 +1288,8 @@ void EngineRunObj::run(int nlocal, int nall, const int *d_type, const double *d_
                        double *virial6, double *d_f, double *d_eatom)
 {
   require_initialized();
-  check_flags(flags);
+  if (flags & 4) throw Unsupported("UQ outputs are not provided through the engine interface");
+  if (flags & ~7) throw InvalidArgument("unknown compute flag");
   if (nlocal < 0 || nall < nlocal) throw InvalidArgument("nlocal must be in 0 .. nall");
   if (nall > 0 && (!d_type || !d_x)) throw InvalidArgument("types and positions must be given");
   const bool eonly = flags & 2;
@@ -1277,7 +1354,7 @@ void BatchObj::compute(int nsys, const int *natoms, int64_t ntot, const int *typ
                        double *virial, double *forces, double *energies)
 {
   require_initialized();
-  check_flags(flags);
+  check_flags(flags, *engine_, uq_out);
   if (nsys < 0 || ntot < 0) throw InvalidArgument("negative structure or atom count");
   if (nsys > 0 && (!natoms || !cell || !pbc)) throw InvalidArgument("natoms, cell and pbc must be given");
   if (ntot > 0 && (!types || !pos)) throw InvalidArgument("types and positions must be given");
@@ -1319,7 +1396,7 @@ void BatchObj::compute_once(int nsys, const int *natoms, int64_t ntot, const int
                             double *energy, double *virial, double *forces, double *energies, int chunk)
 {
   cudaStream_t st = dev().stream;
-  const bool eonly = flags & 2, want_e = flags & 1;
+  const bool eonly = flags & 2, want_e = flags & 1, want_uq = flags & 4;
   const int ns = (int) t2m_.size();
   passes = 0;
   host_seconds = 0.0;
@@ -1347,11 +1424,18 @@ void BatchObj::compute_once(int nsys, const int *natoms, int64_t ntot, const int
     all.virial = eonly ? nullptr : virial;
     all.forces = eonly ? nullptr : forces;
     all.energies = want_e ? energies : nullptr;
+    if (want_uq) { all.gamma = uq_out.gamma; all.sigma = uq_out.sigma; all.cluster = uq_out.cluster; }
   } else {
     all.energy = ws_.energy.ensure(std::max(nsys, 1));
     if (!eonly && virial) all.virial = ws_.virial.ensure(6 * (size_t) std::max(nsys, 1));
     if (!eonly && forces) all.forces = ws_.forces.ensure(3 * (size_t) std::max<int64_t>(ntot, 1));
     if (want_e && energies) all.energies = ws_.energies.ensure(std::max<int64_t>(ntot, 1));
+    if (want_uq) {
+      const size_t m = (size_t) std::max<int64_t>(ntot, 1);
+      all.gamma = ws_.uq.ensure(3 * m);
+      all.sigma = all.gamma + m;
+      all.cluster = all.gamma + 2 * m;
+    }
   }
   // passes of whole structures with at most max_nall atoms (a single larger structure gets a pass of its own)
   int s0 = 0;
@@ -1373,6 +1457,7 @@ void BatchObj::compute_once(int nsys, const int *natoms, int64_t ntot, const int
     o.virial = all.virial ? all.virial + 6 * (size_t) s0 : nullptr;
     o.forces = all.forces ? all.forces + 3 * a0 : nullptr;
     o.energies = all.energies ? all.energies + a0 : nullptr;
+    if (want_uq) { o.gamma = all.gamma + a0; o.sigma = all.sigma + a0; o.cluster = all.cluster + a0; }
     engine_->evaluate(nl_, eonly, o, chunk, nullptr);
     if (na > 0 && (nl_.take_flag() & 2)) zero_bond = true;
     passes++;
@@ -1384,6 +1469,11 @@ void BatchObj::compute_once(int nsys, const int *natoms, int64_t ntot, const int
     if (all.virial && nsys > 0) GB_CUDA(cudaMemcpyAsync(virial, all.virial, sizeof(double) * 6 * nsys, cudaMemcpyDeviceToHost, st));
     if (all.forces && ntot > 0) GB_CUDA(cudaMemcpyAsync(forces, all.forces, sizeof(double) * 3 * ntot, cudaMemcpyDeviceToHost, st));
     if (all.energies && ntot > 0) GB_CUDA(cudaMemcpyAsync(energies, all.energies, sizeof(double) * ntot, cudaMemcpyDeviceToHost, st));
+    if (want_uq && ntot > 0) {
+      GB_CUDA(cudaMemcpyAsync(uq_out.gamma, all.gamma, sizeof(double) * ntot, cudaMemcpyDeviceToHost, st));
+      GB_CUDA(cudaMemcpyAsync(uq_out.sigma, all.sigma, sizeof(double) * ntot, cudaMemcpyDeviceToHost, st));
+      GB_CUDA(cudaMemcpyAsync(uq_out.cluster, all.cluster, sizeof(double) * ntot, cudaMemcpyDeviceToHost, st));
+    }
   }
   GB_CUDA(cudaStreamSynchronize(st));
   if (zero_bond) throw InvalidArgument("two atoms at the same position (a bond of length 0): not a physical structure");

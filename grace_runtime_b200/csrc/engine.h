@@ -78,6 +78,8 @@ struct OutputsDev {
   double *virial = nullptr;      // [nsys][6]
   double *forces = nullptr;      // [n][3] caller's order
   double *energies = nullptr;    // [n] caller's order
+  // UQ (all three or none): extrapolation grade, Mahalanobis distance and cluster per atom, [n] caller's order
+  double *gamma = nullptr, *sigma = nullptr, *cluster = nullptr;
 };
 
 class Engine {
@@ -85,6 +87,7 @@ class Engine {
   Engine(const GraceModel &m, int spline_n);
   ~Engine();
   const ModelPlan &plan() const { return plan_; }
+  bool uq_available() const { return plan_.uq.ready; }
   // Per atom and evaluation (forward and reverse programs of every layer, each once), on the per-operation path:
   // [0] useful flops and [1] algorithmic bytes of the MV operations that run on the tensor cores, [2] / [3] of the
   // products, [4] / [5] of the remaining (per-element) MV operations.  Bytes: every input row once per item or tensor,
@@ -115,6 +118,14 @@ class Engine {
   float *message_gradient_slots(NeighborList &nl);
   void gather_message_gradients(NeighborList &nl, const float *slots, const ActiveRanges &R);
   DBuf<double> e_atom_, vir_atom_, grho_rows_, sum_scratch_;
+  // UQ head: tables, per-atom results in list order, and (GRACE-2L) the layer-1 projection rows and squared norms
+  DBuf<double> uq_cen_, uq_icov_, uq_thr_, uq_out_, uq_n2a_, uq_n2b_;
+  DBuf<int> uq_ncl_;
+  DBuf<float> uq_z1_;
+  UqDev uq_dev_{};
+  bool uq_now_ = false;    // the evaluation in progress computes the UQ outputs
+  void uq_layer1(const int *mu, int64_t a0, int na, int stride);
+  void uq_last(LayerEngine &E, const int *mu, int64_t a0, int na, int stride, int64_t n);
   int arena_NA_ = 0;
   void setup_layer(LayerEngine &E, const LayerPlan &P);
   void setup_fused(LayerEngine &E, const LayerPlan &P);
@@ -170,8 +181,14 @@ struct ModelObj {
   void radial_exact(int layer, const float *d_x, long long nb, float *d_R, float *d_dR);
 };
 
+// where a compute call with the UQ flag leaves gamma, sigma and cluster [atoms] (host or device as the call's other
+// outputs); set by the caller before the call
+struct UqOutputs {
+  double *gamma = nullptr, *sigma = nullptr, *cluster = nullptr;
+};
+
 struct Workspace {
-  DBuf<double> pos, energy, virial, forces, energies;
+  DBuf<double> pos, energy, virial, forces, energies, uq;
   DBuf<int> types, mu, t2m, flag, types_prev;
   std::vector<double> h_cell;
   std::vector<unsigned char> h_pbc;
@@ -187,6 +204,7 @@ class SystemObj {
                bool device_out);
   int64_t rebuilds = 0;
   int last_chunk = 0;
+  UqOutputs uq_out;
   int nlocal = -1, ninner = -1;    // owned atoms / atoms with layer-1 outputs of a domain-decomposed caller (-1: all)
   ActiveRanges ranges;
   DBuf<int> list0_, list1_;
@@ -227,6 +245,7 @@ class BatchObj {
                double *virial, double *forces, double *energies);
   int passes = 0;
   int last_chunk = 0;
+  UqOutputs uq_out;
   double host_seconds = 0.0;
   bool keep_buffers = false;
   void release();

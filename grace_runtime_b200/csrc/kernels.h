@@ -98,6 +98,22 @@ void launch_readout_1l(const ReadoutDev &r, const float *rho, float *grho, const
 void launch_readout_2l(const ReadoutDev &r, const float *rho_rows, const float *I2, double *grho_rows, float *gI2,
                        const int *mu, double *e_atom, int NA, int na, int a0, int want_grad);
 
+// ---- UQ head (uq.cu) ----
+struct UqDev {
+  const double *centroids;     // [n_elements][max_clusters][feature_dim]
+  const double *inv_cov;       // [n_elements][max_clusters][feature_dim][feature_dim]
+  const double *thresholds;    // [n_elements][max_clusters]
+  const int *n_clusters;       // [n_elements]
+  int rp_dim, feature_dim, max_clusters, n_density;
+  double density_scale;
+};
+// n2[a] = |B_a|^2 (fp64) over the inputs of the projection operation `op`, a < na atoms of the chunk
+void launch_uq_norm(const MVDev &op, const TensorDev *tensors, int NA, int na, double *n2);
+// gamma / sigma / cluster of the atoms a0 .. a0 + na (list order) from the projection z [na][rp_dim] of the last layer,
+// the rows z_prev [n][rp_dim] and squared norms n2_prev [n] of the layer before (null: one layer) and n2_last [n]
+void launch_uq_gmm(const UqDev &u, const float *z, const float *z_prev, const double *n2_last, const double *n2_prev,
+                   const int *mu, int na, long long a0, double *gamma, double *sigma, double *cluster);
+
 // ---- the dense network of a layer as one kernel on shared-memory tensors (chain_fused.cu) ----
 // FUSED_SAVE: after the forward operations, the tensors the reverse operations read go to global memory;
 // FUSED_RESTORE: they come back from there instead of the bond sums and the forward operations being run again

@@ -406,6 +406,86 @@ int model_layers_of_file(const Npz &z)
   throw ModelError("the file is no GRACE kokkos.npz model");
 }
 
+namespace {
+
+// the arrays of a schema-6 head with the size checks of libgrace/src/uq_head.cpp:12-78 (every array is indexed flat by
+// the kernels, so a mismatched export has to fail here)
+void load_uq_arrays(const Npz &z, const GraceModel &m, UqHead &h)
+{
+  require_eq("uq_n_elements", z.int_scalar("uq_n_elements", m.n_elements), m.n_elements, "n_elements");
+  h.max_clusters = z.int_in("uq_max_clusters", 0, 1, kMaxDim);
+  h.rp_dim = z.int_in("uq_rp_dim", 0, 1, kMaxDim);
+  h.feature_dim = z.int_in("uq_feature_dim", 0, h.rp_dim, kMaxDim);
+  const int normalize = z.int_scalar("uq_rp_normalize", 0), add_density = z.int_scalar("uq_rp_add_density_channel", 0);
+  const int transform = z.int_scalar("uq_feature_transform", 0);
+  h.density_scale = z.real_scalar("uq_rp_density_scale", 1.0);
+  h.centroids = z.reals("uq_centroids");
+  h.inv_cov = z.reals("uq_inv_cov");
+  h.n_clusters = z.ints("uq_n_clusters");
+  h.thresholds = z.reals("uq_interp_thresholds");
+  h.R = z.reals("uq_rp_matrix");
+  if (normalize != 1 || add_density != 1 || transform != 0)
+    throw ModelError("schema 6 means normalize = 1, add_density_channel = 1, feature_transform = 0; the file has " +
+                     std::to_string(normalize) + ", " + std::to_string(add_density) + ", " + std::to_string(transform));
+  h.n_density = h.feature_dim - h.rp_dim;
+  const auto rs = z.shape("uq_rp_matrix");
+  if (rs.size() != 2) throw bad_array("uq_rp_matrix", "must be a matrix");
+  require_eq("uq_rp_matrix", rs[1], h.rp_dim, "uq_rp_dim columns");
+  h.d_basis = (int) rs[0];
+  const size_t E = m.n_elements, K = h.max_clusters, D = h.feature_dim;
+  require_size("uq_centroids", h.centroids.size(), E * K * D);
+  require_size("uq_inv_cov", h.inv_cov.size(), E * K * D * D);
+  require_size("uq_n_clusters", h.n_clusters.size(), E);
+  require_size("uq_interp_thresholds", h.thresholds.size(), E * K);
+  for (size_t e = 0; e < E; e++) {
+    if (h.n_clusters[e] <= 0) throw ModelError("element index " + std::to_string(e) + " has no clusters");
+    if (h.n_clusters[e] > h.max_clusters)
+      throw ModelError("element index " + std::to_string(e) + " has more clusters than uq_max_clusters");
+  }
+}
+
+void load_uq(const Npz &z, GraceModel &m)
+{
+  UqHead &h = m.uq;
+  h.schema = z.int_scalar("uq_schema_version", 0);
+  h.present = h.schema != 0;
+  m.has_uq = h.present;
+  if (!h.present) return;
+  if (h.schema != 6) {
+    h.error = "UQ schema " + std::to_string(h.schema) + " is not supported (schema 6 only); re-export the UQ artifacts";
+    return;
+  }
+  try {
+    load_uq_arrays(z, m, h);
+  } catch (const std::exception &e) {
+    h.error = std::string("UQ head: ") + e.what();
+  }
+}
+
+}    // namespace
+
+int GraceModel::uq_basis_width() const
+{
+  int w = 0;
+  if (layers == 2)
+    for (const ReduceWeights &r : I2) w += r.present ? r.n_in * (int) r.collect.size() : 0;
+  for (const ReduceWeights &r : rho) w += r.present ? r.n_in * (int) r.collect.size() : 0;
+  return w;
+}
+
+void GraceModel::validate_uq() const
+{
+  if (!uq.present) throw ModelError("the model has no UQ head");
+  if (max_order == 3) throw ModelError("UQ is not supported for max_order 3 models");
+  if (!uq.error.empty()) throw ModelError(uq.error);
+  if (uq.d_basis != uq_basis_width())
+    throw ModelError("UQ head: uq_rp_matrix has " + std::to_string(uq.d_basis) + " rows, the model's invariant basis has " +
+                     std::to_string(uq_basis_width()) + "; re-export the UQ artifacts for this model");
+  if (uq.n_density != 1 + layers)
+    throw ModelError("UQ head: " + std::to_string(uq.n_density) + " density channels, expected " + std::to_string(1 + layers));
+  if (uq.rp_dim > 128) throw ModelError("UQ head: projections wider than 128 are not supported");
+}
+
 int GraceModel::element_index(const std::string &name) const
 {
   for (size_t i = 0; i < element_names.size(); i++)
@@ -421,6 +501,7 @@ GraceModel GraceModel::load(const std::string &path)
   if (m.layers == 1) load_1l(z, m);
   else if (m.layers == 2) load_2l(z, m);
   else throw ModelError("GRACE-3L models are not supported by this backend yet");
+  load_uq(z, m);
   return m;
 }
 

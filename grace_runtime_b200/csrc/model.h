@@ -63,6 +63,23 @@ struct YICoupling {
   double inv_avg = 1.0;
 };
 
+// UQ head of schema 6 (libgrace/include/grace/uq_head.h:16-33): the Gaussian-mixture feature of an atom is
+// phi = concat((B / |B|) R, log-norm density channels), B the collected inputs of the model's scalar reduces.
+// A head that fails its checks leaves the model usable without UQ: the message is kept and raised when UQ is asked for
+// (libgrace/src/model_1l.cpp:216-272).
+struct UqHead {
+  bool present = false;      // uq_schema_version != 0
+  int schema = 0;
+  std::string error;         // why the head cannot be evaluated (empty: it can)
+  int rp_dim = 0, feature_dim = 0, n_density = 0, max_clusters = 0, d_basis = 0;
+  double density_scale = 1.0;
+  std::vector<double> R;              // [d_basis][rp_dim]
+  std::vector<double> centroids;      // [n_elements][max_clusters][feature_dim]
+  std::vector<double> inv_cov;        // [n_elements][max_clusters][feature_dim][feature_dim]
+  std::vector<double> thresholds;     // [n_elements][max_clusters]
+  std::vector<int> n_clusters;        // [n_elements]
+};
+
 struct GraceModel {
   int layers = 0;
   int n_elements = 0, embedding = 0, lmax = 0, nradbase = 0, p = 0, max_order = 4;
@@ -77,6 +94,11 @@ struct GraceModel {
   double output_scale = 1.0;
   std::vector<double> shift;
   bool has_uq = false;
+  UqHead uq;
+  // throws ModelError unless the UQ head is there and can be evaluated (GRACE1LModel::validate_uq,
+  // libgrace/src/model_1l.cpp:275-285; GRACE2LModel::validate_uq, libgrace/src/model_2l.cpp:464-478)
+  void validate_uq() const;
+  int uq_basis_width() const;    // rows the projection matrix must have: the collected inputs of the scalar reduces
 
   // layer 1 (GRACE-1L: the only layer)
   std::vector<MlpLayer> rad1;

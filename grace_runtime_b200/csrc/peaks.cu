@@ -30,6 +30,26 @@ __global__ void __launch_bounds__(FMA_THREADS) peak_fma_kernel(float *out, int i
   if (s == 123.456f) out[0] = s;    // never true for the arguments used: keeps the loop alive
 }
 
+// the same chains with packed two-wide FMAs (fma.rn.f32x2): half the instructions for the same flops
+__global__ void __launch_bounds__(FMA_THREADS) peak_fma2_kernel(float *out, int iters, float a, float b)
+{
+  float2 x[FMA_CHAINS / 2];
+#pragma unroll
+  for (int c = 0; c < FMA_CHAINS / 2; c++) x[c] = make_float2((float) (threadIdx.x + c) * 1.0e-3f, (float) (threadIdx.x - c) * 1.0e-3f);
+  const float2 a2 = make_float2(a, a), b2 = make_float2(b, b);
+  for (int it = 0; it < iters; it++) {
+#pragma unroll
+    for (int u = 0; u < FMA_UNROLL; u++) {
+#pragma unroll
+      for (int c = 0; c < FMA_CHAINS / 2; c++) x[c] = __ffma2_rn(x[c], a2, b2);
+    }
+  }
+  float s = 0.0f;
+#pragma unroll
+  for (int c = 0; c < FMA_CHAINS / 2; c++) s += x[c].x + x[c].y;
+  if (s == 123.456f) out[0] = s;
+}
+
 constexpr int TM = 128, TN = 256, TK = 32;
 constexpr long long WAIT_CYCLES = 40000000LL;
 
@@ -112,7 +132,7 @@ double time_ms(cudaEvent_t a, cudaEvent_t b)
 
 }    // namespace
 
-double measure_peak_fp32_tflops()
+double measure_peak_fp32_tflops(bool packed)
 {
   require_initialized();
   cudaStream_t st = dev().stream;
@@ -125,7 +145,8 @@ double measure_peak_fp32_tflops()
   double best = 0.0;
   for (int rep = 0; rep < 4; rep++) {    // the first repetition warms up
     GB_CUDA(cudaEventRecord(a, st));
-    peak_fma_kernel<<<grid, FMA_THREADS, 0, st>>>(out.get(), iters, 0.999f, 1.0e-3f);
+    if (packed) peak_fma2_kernel<<<grid, FMA_THREADS, 0, st>>>(out.get(), iters, 0.999f, 1.0e-3f);
+    else peak_fma_kernel<<<grid, FMA_THREADS, 0, st>>>(out.get(), iters, 0.999f, 1.0e-3f);
     GB_CUDA(cudaGetLastError());
     GB_CUDA(cudaEventRecord(b, st));
     GB_CUDA(cudaEventSynchronize(b));

@@ -364,6 +364,38 @@ struct LayerBuilder {
     emit(f, adjoint);
   }
 
+  // UQ: z[d] = sum over the collected inputs b of the reduce R of x_b Rp[row0 + b][d]; the inputs of a source are
+  // numbered channel-major (b = n * collected + c: libgrace/include/grace/fused_cpu.h:1291-1305), so the matrix of the
+  // collected function c takes every collected-th row of the source's block.  Returns the rows used.
+  int uq_projection(const ReduceGroup &R, const UqHead &h, int row0)
+  {
+    const int RP = h.rp_dim, ldw = pad4(RP);
+    MVOp F;
+    F.name = "uq:" + R.name;
+    P.tUQ = tensor("uq_" + R.name, 1, RP);
+    P.tensors[P.tUQ].external = true;
+    F.dst = P.tUQ; F.n_out = RP; F.ldw = ldw;
+    F.row_out.push_back(0);
+    F.item_off.push_back(0);
+    int row = row0;
+    for (size_t s = 0; s < R.src.size(); s++) {
+      const ReduceWeights *w = R.src[s];
+      if (!w || !w->present) continue;
+      const int nc = (int) w->collect.size(), nin = w->n_in;
+      for (int c = 0; c < nc; c++) {
+        const int mat = (int) F.W.size();
+        F.W.resize(F.W.size() + (size_t) nin * ldw, 0.0f);
+        for (int n = 0; n < nin; n++)
+          for (int d = 0; d < RP; d++)
+            F.W[(size_t) mat + (size_t) n * ldw + d] = (float) h.R[((size_t) row + (size_t) n * nc + c) * RP + d];
+        F.items.push_back({mat, R.src_tensor[s], R.src_row0[s] + w->collect[c], nin, 1.0f});
+      }
+      row += nin * nc;
+    }
+    P.uq_mv = add(std::move(F)).index;
+    return row - row0;
+  }
+
   struct ChainTensors {
     int X0, X1, XX, XX1, XX2, XXX, XXXX;
     int gX0, gX1, gXX, gXX1, gXX2, gXXX, gXXXX;
@@ -549,6 +581,18 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
       P.rc_max = std::max(P.rc_max, rc);
     }
   P.nrho = m.rho_n_out;
+  // UQ head: evaluated only if it passes the checks (the message is raised when a caller asks for UQ)
+  bool uq_ok = m.uq.present;
+  if (uq_ok) {
+    try {
+      m.validate_uq();
+    } catch (const std::exception &) {
+      uq_ok = false;
+    }
+  }
+  int uq_rows_l2 = 0;    // GRACE-2L: the I2 block comes first in the projection matrix (libgrace/src/model_2l.cpp:520-535)
+  if (uq_ok && m.layers == 2)
+    for (const ReduceWeights &r : m.I2) uq_rows_l2 += r.present ? r.n_in * (int) r.collect.size() : 0;
 
   {    // layer 1
     LayerPlan &L = P.L1;
@@ -580,6 +624,7 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
       L.tensors[P.t1_I].external = L.tensors[P.t1_gI].external = true;
       B.reduce(B.reduce4("I1", m.I1, T, c.order4, m.i1_out, m.nI1, true, tI1, gI1));
       B.reduce(B.reduce4("rho", m.rho, T, c.order4, m.rho_n_out, 1, true, P.t1_rho, P.t1_grho));
+      if (uq_ok) B.uq_projection(B.reduce4("rho", m.rho, T, c.order4, m.rho_n_out, 1, true, P.t1_rho, P.t1_grho), m.uq, uq_rows_l2);
       ReduceGroup R;
       R.name = "I";
       R.src = {&m.I_from_I1};
@@ -590,6 +635,7 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
       B.reduce(R);
     } else {
       B.reduce(B.reduce4("rho", m.rho, T, c.order4, m.rho_n_out, 1, true, P.t1_rho, P.t1_grho));
+      if (uq_ok) B.uq_projection(B.reduce4("rho", m.rho, T, c.order4, m.rho_n_out, 1, true, P.t1_rho, P.t1_grho), m.uq, 0);
     }
     B.finish();
   }
@@ -660,6 +706,7 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
     P.t2_gI2 = B.tensor("gI2", 1, m.nI2);
     L.tensors[P.t2_I2].external = L.tensors[P.t2_gI2].external = true;
     B.reduce(B.reduce4("I2", m.I2, T, c.order4, m.nI2, 1, true, P.t2_I2, P.t2_gI2));
+    if (uq_ok) B.uq_projection(B.reduce4("I2", m.I2, T, c.order4, m.nI2, 1, true, P.t2_I2, P.t2_gI2), m.uq, 0);
     B.finish();
   }
   compact_rows(P.L1);
@@ -680,8 +727,16 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
   P.shift = m.shift;
   P.lnI = m.lnI;
   P.ln0 = m.ln0;
+  if (uq_ok) {
+    UqPlan &u = P.uq;
+    u.ready = true;
+    u.rp_dim = m.uq.rp_dim; u.feature_dim = m.uq.feature_dim; u.n_density = m.uq.n_density;
+    u.max_clusters = m.uq.max_clusters; u.density_scale = m.uq.density_scale;
+    u.centroids = m.uq.centroids; u.inv_cov = m.uq.inv_cov; u.thresholds = m.uq.thresholds; u.n_clusters = m.uq.n_clusters;
+  }
   for (const LayerPlan *L : {&P.L1, &P.L2}) {
-    for (const auto &o : L->mv) P.dense_flops_per_atom += o.flops_per_atom();
+    for (size_t q = 0; q < L->mv.size(); q++)
+      if ((int) q != L->uq_mv) P.dense_flops_per_atom += L->mv[q].flops_per_atom();
     for (const auto &o : L->prod)    // 3 flop per (term, channel): libgrace/include/grace/fused_cpu.h:411-429
       P.dense_flops_per_atom += 3.0 * (double) o.terms.size() * L->tensors[o.dst].channels;
   }

@@ -93,6 +93,19 @@ struct LayerPlan {
   int C = 0;                // channels of the bond sum
   RadialTable radial;
   std::vector<float> z;     // [n_elements][C] chemical weight of the neighbour (the virtual message function)
+  // UQ: index in `mv` of the projection of the layer's invariant basis (the collected inputs of its scalar reduce)
+  // onto the rows of the projection matrix that belong to it, and the [1][rp_dim] tensor it writes; -1: no UQ head.
+  // The operation is not part of `fwd`: the drivers run it after the forward program when UQ is asked for.
+  int uq_mv = -1, tUQ = -1;
+};
+
+// Gaussian-mixture part of the UQ head as the device kernels read it (fp64, libgrace/include/grace/fused_cpu.h:1378-1412)
+struct UqPlan {
+  bool ready = false;
+  int rp_dim = 0, feature_dim = 0, n_density = 0, max_clusters = 0;
+  double density_scale = 1.0;
+  std::vector<double> centroids, inv_cov, thresholds;
+  std::vector<int> n_clusters;
 };
 
 struct ModelPlan {
@@ -114,6 +127,7 @@ struct ModelPlan {
   double out_scale = 1.0;
   std::vector<double> shift;    // [n_elements]
   std::vector<double> lnI, ln0;
+  UqPlan uq;
   double dense_flops_per_atom = 0.0;    // FC / reduce / product flops of the forward and reverse programs (diagnostics)
 };
 

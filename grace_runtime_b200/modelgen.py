@@ -179,3 +179,49 @@ CONFIGS = {
 
 def write_config_model(path, config, elements, seed=0):
     return write_model(path, elements=tuple(elements), seed=seed, **CONFIGS[config])
+
+
+def uq_basis_width(z):
+    """Rows of the UQ projection matrix of a model file (dict of arrays): the collected inputs of its scalar reduces,
+    blocks in the order of the reference (libgrace/src/model_1l.cpp:306-316, libgrace/src/model_2l.cpp:520-535)."""
+    blocks = [("I2", ("B", "BB", "BBB", "BBBB")), ("rho", ("A", "AA", "AAA", "AAAA"))]
+    if "I2_reduce_B_W" not in z:
+        blocks = blocks[1:]
+    width = 0
+    for prefix, sources in blocks:
+        for s in sources:
+            if f"{prefix}_reduce_{s}_W" not in z:
+                raise ValueError("a UQ head needs a max_order 4 model (libgrace/src/model_1l.cpp:278)")
+            width += z[f"{prefix}_reduce_{s}_W"].shape[-2] * len(np.asarray(z[f"{prefix}_collect_ind_{s}"]).reshape(-1))
+    return width, len(blocks)
+
+
+def add_uq_head(src, dst, seed=0, rp_dim=32, max_clusters=3):
+    """Copies the model file `src` to `dst` with a seeded random UQ head of schema 6 (keys and checks:
+    libgrace/src/uq_head.cpp:12-78): projection matrix, Gaussian-mixture centroids, precision matrices and
+    thresholds for every element.  The published models carry fitted heads; a random one has the same arithmetic."""
+    z0 = np.load(src)
+    z = {k: z0[k] for k in z0.files}
+    rng = np.random.default_rng(seed)
+    d_basis, nblocks = uq_basis_width(z)
+    nel = int(np.asarray(z["n_elements"]).reshape(-1)[0]) if "n_elements" in z else 89
+    D = rp_dim + 1 + nblocks
+    z["uq_schema_version"] = _i(6)
+    z["uq_n_elements"] = _i(nel)
+    z["uq_max_clusters"] = _i(max_clusters)
+    z["uq_rp_dim"] = _i(rp_dim)
+    z["uq_feature_dim"] = _i(D)
+    z["uq_rp_normalize"] = _i(1)
+    z["uq_rp_add_density_channel"] = _i(1)
+    z["uq_rp_density_scale"] = _f(1.0)
+    z["uq_feature_transform"] = _i(0)
+    z["uq_rp_matrix"] = rng.standard_normal((d_basis, rp_dim))
+    z["uq_centroids"] = rng.standard_normal((nel, max_clusters, D))
+    m = rng.standard_normal((nel, max_clusters, D, D)) / np.sqrt(D)
+    z["uq_inv_cov"] = m @ m.transpose(0, 1, 3, 2) + np.eye(D)
+    z["uq_n_clusters"] = rng.integers(1, max_clusters + 1, size=nel).astype(np.int64)
+    z["uq_interp_thresholds"] = 1.0 + 2.0 * rng.random((nel, max_clusters))
+    os.makedirs(os.path.dirname(os.path.abspath(dst)), exist_ok=True)
+    with open(dst, "wb") as f:
+        np.savez(f, **z)
+    return dst

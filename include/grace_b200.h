@@ -41,7 +41,7 @@ extern "C" {
 /* compute flags (kk_api.h:84-86: energies, uq, energy_only) */
 #define GRACE_FLAG_ENERGIES 1     /* also write per-atom energies */
 #define GRACE_FLAG_ENERGY_ONLY 2  /* no reverse pass: forces and virial are not written */
-#define GRACE_FLAG_UQ 4           /* rejected with GRACE_UNSUPPORTED: no UQ head in this backend */
+#define GRACE_FLAG_UQ 4           /* also the UQ outputs (gamma, sigma, cluster per atom) where grace_*_set_uq_outputs put them */
 
 typedef struct grace_model grace_model;
 typedef struct grace_system grace_system;
@@ -63,8 +63,9 @@ int grace_debug_fail_alloc(const char *label, int nth);           /* debug_fail_
 int grace_debug_fail_launch(int nth);                             /* debug_fail_launch(nth) */
 /* Microbenchmarks of this device's compute peaks in TFLOP/s, the denominators of compute-bound rooflines: kind 0 the
  * fp32 FMA rate of the SIMT lanes (register-only FFMA loop at full occupancy), kind 1 the tf32 rate of the tensor
- * cores (tcgen05.mma kind::tf32, M = 128, N = 256, operands in shared memory), kind 16 .. 256 (a multiple of 16) the
- * same with N = kind, which shows the instruction-rate limit of narrow tiles.  A few milliseconds each.  Diagnostics;
+ * cores (tcgen05.mma kind::tf32, M = 128, N = 256, operands in shared memory), kind 2 the fp32 rate with packed
+ * two-wide FMAs (fma.rn.f32x2), kind 16 .. 256 (a multiple of 16) the
+ * tensor-core rate with N = kind, which shows the instruction-rate limit of narrow tiles.  A few milliseconds each.  Diagnostics;
  * no counterpart in the reference. */
 int grace_measure_peak(int kind, double *tflops);
 /* _debug_track_alloc(on), _debug_peak_alloc(), _debug_live_alloc() (kk_module.cpp:221-224, kk_core.cpp:143-184): from
@@ -100,7 +101,10 @@ int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_ou
  * device memory per layer and an 8 -> 64 -> 64 -> n radial MLP) */
 int grace_model_load(const char *path, int spline, grace_model **out);   /* Model(path, spline) */
 int grace_model_layers(const grace_model *m);                            /* layers(): 1 or 2 */
-int grace_model_has_uq(const grace_model *m);                            /* has_uq(): 0 */
+int grace_model_has_uq(const grace_model *m);                            /* has_uq(): the file carries a UQ head */
+/* validate_uq() (kk_api.h:59): GRACE_OK, or GRACE_INVALID_ARGUMENT with the reason the head cannot be evaluated (none
+ * in the file, a schema other than 6, a max_order 3 model, array sizes that do not match the model) */
+int grace_model_validate_uq(const grace_model *m);
 int grace_model_n_elements(const grace_model *m);                        /* len(element_names()) */
 const char *grace_model_element_name(const grace_model *m, int i);       /* element_names()[i] */
 int64_t grace_model_engine_setups(const grace_model *m);                 /* engine_setups() */
@@ -141,6 +145,13 @@ int grace_system_compute(grace_system *s, int n, const int32_t *types, const dou
 int grace_system_compute_device(grace_system *s, int n, const int32_t *d_types, const double *d_pos,
                                 const double *cell, const uint8_t *pbc, int flags, double *d_energy,
                                 double *d_virial6, double *d_forces, double *d_energies);
+/* Result::gamma / sigma / cluster (kk_api.h:39) and DeviceOut::gamma / sigma / cluster (kk_api.h:100): where the
+ * calls with GRACE_FLAG_UQ from now on write the extrapolation grade, the Mahalanobis distance and the nearest
+ * mixture component of every atom, [n] doubles each in the caller's atom order; host pointers for
+ * grace_system_compute, device pointers for grace_system_compute_device.  The flag without all three pointers, or on a
+ * model whose head grace_model_validate_uq rejects, is GRACE_INVALID_ARGUMENT (kk_core.cpp:826-827, 1284-1286).  A UQ
+ * call evaluates the dense network on the per-operation path whatever the structure's size. */
+int grace_system_set_uq_outputs(grace_system *s, double *gamma, double *sigma, double *cluster);
 /* Domain decomposition: from now on only the atoms with index < nlocal are owned by this System; the atoms behind
  * them are ghosts (copies of atoms another rank owns), which enter every neighbour sum but whose own energies are
  * left out of `energy`, `energies` (0 there) and the gradient, while forces and virial of everything the owned
@@ -232,6 +243,8 @@ int grace_batch_compute_device(grace_batch *b, int nsys, const int32_t *natoms, 
                                const double *d_pos, const double *cell, const uint8_t *pbc, int flags,
                                int64_t max_nall, double *d_energy, double *d_virial, double *d_forces,
                                double *d_energies);
+/* as grace_system_set_uq_outputs, [ntot] doubles each (BatchResult / DeviceOut, kk_api.h:96,105) */
+int grace_batch_set_uq_outputs(grace_batch *b, double *gamma, double *sigma, double *cluster);
 int grace_batch_passes(const grace_batch *b);                             /* passes() */
 double grace_batch_host_seconds(const grace_batch *b);                    /* host_seconds() */
 int grace_batch_set_keep_buffers(grace_batch *b, int on);                 /* set_keep_buffers(on) */

@@ -479,6 +479,47 @@ class GraceOracle:
                 self.lnI = np.ones(self.nrho - 1)
                 self.ln0 = np.ones(self.nI2)
 
+        # UQ head of schema 6 (libgrace/src/uq_head.cpp:12-78), optional
+        self.uq = None
+        if z.is_("uq_schema_version", 0) == 6:
+            E, K, D = self.n_elements, z.is_("uq_max_clusters"), z.is_("uq_feature_dim")
+            self.uq = dict(RP=z.is_("uq_rp_dim"), D=D, K=K, scale=z.fs("uq_rp_density_scale", 1.0),
+                           R=z.f("uq_rp_matrix"), cen=z.f("uq_centroids").reshape(E, K, D),
+                           icov=z.f("uq_inv_cov").reshape(E, K, D, D), ncl=z.i("uq_n_clusters").reshape(-1),
+                           thr=z.f("uq_interp_thresholds").reshape(E, K))
+
+    @staticmethod
+    def _uq_basis(red, X):
+        """Collected inputs of a scalar reduce per atom, each source flattened channel-major over its collected
+        functions (libgrace/include/grace/fused_cpu.h:1291-1305; libgrace/include/grace/uq.h:1-9)."""
+        cols = []
+        for S, x in zip(red.src, X):
+            if S is None or x is None:
+                continue
+            ci = S[1]
+            cols.append(np.transpose(x[:, ci, :], (0, 2, 1)).reshape(len(x), -1))
+        return np.concatenate(cols, axis=1)
+
+    def _uq_eval(self, blocks, mu):
+        """blocks: per-atom bases in the order of the projection matrix's rows, last layer first.  Returns gamma, sigma,
+        cluster (libgrace/include/grace/fused_cpu.h:1378-1412; libgrace/src/fused_2l.cpp:1172-1184)."""
+        u = self.uq
+        B = np.concatenate(blocks, axis=1)
+        n2 = [(b * b).sum(1) for b in blocks]
+        nrm = np.sqrt(sum(n2))
+        dens = [nrm, np.sqrt(n2[0])] + ([np.sqrt(n2[1])] if len(blocks) == 2 else [])
+        f = np.concatenate([(B @ u["R"]) / (nrm + 1e-12)[:, None]] +
+                           [(np.log(d + 1e-12) * u["scale"])[:, None] for d in dens], axis=1)
+        n = len(mu)
+        gamma, sigma, cluster = np.zeros(n), np.zeros(n), np.zeros(n)
+        for a in range(n):
+            m = mu[a]
+            d = f[a][None, :] - u["cen"][m, :u["ncl"][m]]
+            k = int(np.argmin((d * d).sum(1)))
+            sig = np.sqrt(d[k] @ u["icov"][m, k] @ d[k] + 1e-8)
+            sigma[a], gamma[a], cluster[a] = sig, sig / max(u["thr"][m, k], 1e-10), k
+        return gamma, sigma, cluster
+
     # -- helpers -------------------------------------------------------------------------------------------------
     def cutoff_matrix(self, mus):
         if self.bond_rc is None:
@@ -535,8 +576,11 @@ class GraceOracle:
         return gX0 + a + b
 
     # -- the evaluation ----------------------------------------------------------------------------------------
-    def compute(self, species, types, pos, cell, pbc, bonds=None):
-        """species: element names of types 1..len(species); returns dict(energy, forces, virial, energies)."""
+    def compute(self, species, types, pos, cell, pbc, bonds=None, uq=False):
+        """species: element names of types 1..len(species); returns dict(energy, forces, virial, energies) and, with
+        uq, gamma / sigma / cluster per atom."""
+        if uq and self.uq is None:
+            raise ValueError("the model has no UQ head")
         pos = np.asarray(pos, dtype=np.float64)
         cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
         n = len(pos)
@@ -668,4 +712,10 @@ class GraceOracle:
         dl = -d
         vir = np.array([(dl[:, 0] * fv[:, 0]).sum(), (dl[:, 1] * fv[:, 1]).sum(), (dl[:, 2] * fv[:, 2]).sum(),
                         (dl[:, 0] * fv[:, 1]).sum(), (dl[:, 0] * fv[:, 2]).sum(), (dl[:, 1] * fv[:, 2]).sum()])
-        return dict(energy=float(e_atom.sum()), forces=forces, virial=vir, energies=e_atom)
+        res = dict(energy=float(e_atom.sum()), forces=forces, virial=vir, energies=e_atom)
+        if uq:
+            blocks = [self._uq_basis(self.rRho, X1)]
+            if self.layers == 2:
+                blocks.insert(0, self._uq_basis(self.rI2, X2))
+            res["gamma"], res["sigma"], res["cluster"] = self._uq_eval(blocks, mu)
+        return res

@@ -16,6 +16,7 @@
 #include <cstdio>
 #include <cstring>
 #include <memory>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -125,12 +126,20 @@ double ref_cutoff(void *h)
 
 // energy, forces [n][3], virial [6] (xx yy zz xy xz yz), eatom [n] (may be null) of one structure, caller's atom
 // order. repeats >= 1 computes: seconds[0] = neighbour search, seconds[1] = best compute time, seconds[2] = median.
-int ref_compute(void *h, int n, const int32_t *types, const double *pos, const double *cell, const uint8_t *pbc8,
-                int nthreads, int energy_only, int repeats, double *energy, double *forces, double *virial,
-                double *eatom, double *seconds)
+// gamma, sigma, cluster [n] (all three or none): the UQ outputs of the drivers (ComputeFlags::uq after enable_uq(),
+// libgrace/src/fused_1l.cpp:584-638, libgrace/src/fused_2l.cpp:1101-1187)
+static int compute_impl(void *h, int n, const int32_t *types, const double *pos, const double *cell, const uint8_t *pbc8,
+                        int nthreads, int energy_only, int repeats, double *energy, double *forces, double *virial,
+                        double *eatom, double *seconds, double *gamma, double *sigma, double *cluster)
 {
   auto *r = static_cast<RefModel *>(h);
   try {
+    const bool uq = gamma && sigma && cluster;
+    if (uq) {
+      if (r->d1 && !r->d1->uq_enabled()) r->d1->enable_uq();
+      if (r->d2 && !r->d2->uq_enabled()) r->d2->enable_uq();
+      if (r->d3) throw std::runtime_error("UQ of GRACE-3L is not driven here");
+    }
     const bool pbc[3] = {pbc8[0] != 0, pbc8[1] != 0, pbc8[2] != 0};
     const double rc = ref_cutoff(h);
     double t0 = now_s();
@@ -144,7 +153,7 @@ int ref_compute(void *h, int n, const int32_t *types, const double *pos, const d
       ty[q] = types[a];
     }
     grace::CsrBonds src{ty.data(), nl.offset.data(), nl.j.data(), nullptr, x.data(), nl.image.data(), nl.shifts.data()};
-    std::vector<double> f(3 * (size_t) n), ea(n), times;
+    std::vector<double> f(3 * (size_t) n), ea(n), times, ug(uq ? n : 0), us(uq ? n : 0), uc(uq ? n : 0);
     double e = 0.0, v[6];
     for (int rep = 0; rep < std::max(1, repeats); rep++) {
       std::fill(f.begin(), f.end(), 0.0);
@@ -156,6 +165,12 @@ int ref_compute(void *h, int n, const int32_t *types, const double *pos, const d
       fl.eflag_atom = eatom != nullptr;
       fl.virial = !energy_only;
       fl.energy_only = energy_only != 0;
+      if (uq) {
+        fl.uq = true;
+        out.gamma = ug.data();
+        out.atomic_sigma = us.data();
+        out.gmm_cluster = uc.data();
+      }
       grace::NoExchange ex;
       t0 = now_s();
       if (r->d1) r->d1->compute(n, nullptr, n, n, src, out, fl, nthreads);
@@ -172,6 +187,11 @@ int ref_compute(void *h, int n, const int32_t *types, const double *pos, const d
       if (forces)
         for (int d = 0; d < 3; d++) forces[3 * a + d] = f[3 * (size_t) q + d];
       if (eatom) eatom[a] = ea[q];
+      if (uq) {
+        gamma[a] = ug[q];
+        sigma[a] = us[q];
+        cluster[a] = uc[q];
+      }
     }
     if (seconds) {
       std::sort(times.begin(), times.end());
@@ -184,6 +204,22 @@ int ref_compute(void *h, int n, const int32_t *types, const double *pos, const d
     g_err = e.what();
     return 1;
   }
+}
+
+int ref_compute(void *h, int n, const int32_t *types, const double *pos, const double *cell, const uint8_t *pbc8,
+                int nthreads, int energy_only, int repeats, double *energy, double *forces, double *virial,
+                double *eatom, double *seconds)
+{
+  return compute_impl(h, n, types, pos, cell, pbc8, nthreads, energy_only, repeats, energy, forces, virial, eatom,
+                      seconds, nullptr, nullptr, nullptr);
+}
+
+int ref_compute_uq(void *h, int n, const int32_t *types, const double *pos, const double *cell, const uint8_t *pbc8,
+                   int nthreads, int energy_only, double *energy, double *forces, double *virial, double *eatom,
+                   double *gamma, double *sigma, double *cluster)
+{
+  return compute_impl(h, n, types, pos, cell, pbc8, nthreads, energy_only, 1, energy, forces, virial, eatom, nullptr,
+                      gamma, sigma, cluster);
 }
 
 // the reference neighbour list of one structure as bond triples in the caller's frame, for the device-list parity

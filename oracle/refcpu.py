@@ -54,6 +54,7 @@ def _load():
         L.ref_cutoff.restype = C.c_double
         L.ref_cutoff.argtypes = [C.c_void_p]
         L.ref_compute.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_void_p] * 5
+        L.ref_compute_uq.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 4 + [C.c_int] * 2 + [C.c_void_p] * 7
         L.ref_neighbors.restype = C.c_int64
         L.ref_neighbors.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_double, C.c_int, C.c_int64,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
@@ -84,7 +85,8 @@ class RefModel:
             _lib.ref_model_free(self.h)
             self.h = None
 
-    def compute(self, types, pos, cell, pbc, nthreads=0, energy_only=False, repeats=1):
+    def compute(self, types, pos, cell, pbc, nthreads=0, energy_only=False, repeats=1, uq=False):
+        """uq: also gamma, sigma, cluster per atom (the model needs a UQ head; one evaluation, no timings)."""
         L = _load()
         n = len(types)
         types = np.ascontiguousarray(types, dtype=np.int32)
@@ -97,6 +99,13 @@ class RefModel:
         v = np.zeros(6)
         ea = np.zeros(n)
         sec = np.zeros(3)
+        if uq:
+            g, sg, cl = np.zeros(n), np.zeros(n), np.zeros(n)
+            rc = L.ref_compute_uq(self.h, n, _ptr(types), _ptr(pos), _ptr(cell), _ptr(pbc), nth, int(energy_only),
+                                  C.addressof(e), _ptr(f), _ptr(v), _ptr(ea), _ptr(g), _ptr(sg), _ptr(cl))
+            if rc:
+                raise RuntimeError(L.ref_last_error().decode())
+            return dict(energy=e.value, forces=f, virial=v, energies=ea, gamma=g, sigma=sg, cluster=cl, threads=nth)
         rc = L.ref_compute(self.h, n, _ptr(types), _ptr(pos), _ptr(cell), _ptr(pbc), nth, int(energy_only), repeats,
                            C.addressof(e), _ptr(f), _ptr(v), _ptr(ea), _ptr(sec))
         if rc:

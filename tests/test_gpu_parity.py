@@ -236,7 +236,7 @@ def test_errors(backend, models, cells):
     p = c["positions"].copy(); p[1] = p[0]
     with pytest.raises(ValueError, match="same position"):
         s.compute(c["types"], p, c["cell"], c["pbc"])
-    with pytest.raises(RuntimeError):
+    with pytest.raises(ValueError, match="no usable UQ head"):     # python/kk/kk_core.cpp:826-827
         s.compute(c["types"], c["positions"], c["cell"], c["pbc"], uq=True)
     r = s.compute(c["types"], c["positions"], c["cell"], c["pbc"])       # usable after the failures
     assert np.isfinite(r["energy"])
@@ -433,7 +433,7 @@ def test_compute_device_takes_device_arrays_without_conversion(backend, models, 
         b.compute_device(natoms, d_t, d_x, cells2, pbc2, e, forces=f[:, :2])        # wrong shape / not contiguous
     with pytest.raises(ValueError):
         b.compute_device(natoms, d_t, d_x, cells2, pbc2, e.cpu())                   # host output
-    with pytest.raises(RuntimeError):
+    with pytest.raises(ValueError, match="no usable UQ head"):
         b.compute_device(natoms, d_t, d_x, cells2, pbc2, e, gamma=ea)               # no UQ head
 
 
