@@ -112,6 +112,12 @@ def algorithmic_bytes(kernel, model_cfg, n_atoms, n_bonds, slots):
         return 16.0 * n_bonds + (4.0 * nlm * C + 16.0) * n_atoms
     if kernel == "bond_bwd_kernel":       # bond record and slot in, bond force out; gA in, virial out
         return (16.0 + 4.0 + 12.0) * n_bonds + (4.0 * nlm * C + 48.0 + 16.0) * n_atoms
+    if c["layers"] == 2:                  # the message layer: (4 message functions + the chemical one) x nlm x CR sums per atom
+        CR, nq = c["cr"], 5 * nlm
+        if kernel == "bond_fwd_split_kernel":    # bond record in; every atom's message row once; Q out
+            return 16.0 * n_bonds + (4.0 * nq * CR + 4.0 * 4 * CR + 16.0) * n_atoms
+        if kernel == "bond_bwd_split_kernel":    # as bond_bwd_kernel, plus each bond's share of dE/dmsg (4 x CR floats) out
+            return (16.0 + 4.0 + 12.0 + 4.0 * 4 * CR) * n_bonds + (4.0 * nq * CR + 4.0 * 4 * CR + 48.0 + 16.0) * n_atoms
     if kernel == "nl_compact":            # list entry (j, S) and positions in, record + slot out
         return (8.0 + 16.0 + 4.0) * slots + 24.0 * n_atoms
     if kernel == "force_gather_kernel":   # bond force and reverse index in, force out
@@ -126,13 +132,16 @@ def bond_flops(kernel, model_cfg, n_bonds, launches_per_step):
     c = modelgen.CONFIGS[model_cfg]
     nlm = (c["lmax"] + 1) ** 2
     per = [(c["c1"], 1)] + ([(c["cr"], 5)] if c["layers"] == 2 else [])
-    if kernel == "bond_bwd_kernel":
+    # message layers of at most 16 channels run as the split kernels, the others (and layer 1) as the plain ones
+    split2 = c["layers"] == 2 and c["cr"] <= 16
+    if kernel.startswith(("bond_bwd_split", "bond_fwd_split")):
+        per = per[1:]
+    elif split2:
+        per = per[:1]
+    if kernel.startswith("bond_bwd"):
         return n_bonds * sum(2.0 * nlm * C * 4 * nit for C, nit in per)
-    if kernel == "bond_fwd_kernel":
-        fl = [2.0 * nlm * C * nit for C, nit in per]
-        # GRACE-2L on the per-operation path evaluates layer 1 once more for its reverse pass: launches tell
-        extra = fl[0] if (c["layers"] == 2 and launches_per_step >= 3) else 0.0
-        return n_bonds * (sum(fl) + extra)
+    if kernel.startswith("bond_fwd"):
+        return n_bonds * sum(2.0 * nlm * C * nit for C, nit in per)
     return None
 
 

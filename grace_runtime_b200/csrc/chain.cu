@@ -71,18 +71,28 @@ __global__ void __launch_bounds__(128) mv_kernel(MVDev op, const TensorDev *__re
 // Per-element weights (reduces over the central atom's element and their adjoints) for a tile of 128 atoms, one thread
 // per atom with all NQ x 4 output channels of a row in registers.  The atoms of the tile are taken in order of their
 // element, so the lanes of a warp mostly read the same weights (one broadcast shared-memory read serves them).  A CTA
-// walks the (row, item) pairs of its rows in groups; the weight matrices of a group, for the elements present in the
-// tile, are staged in shared memory together: a weight is fetched from global memory once per tile and element and a
-// group costs two barriers.  Same summation order as mv_kernel.
+// walks the (row, item) pairs of its rows in groups of G items; the weight matrices of a group, for the elements
+// present in the tile, are staged in shared memory together - a weight is fetched from global memory once per tile and
+// element - through asynchronous copies into the half of a double buffer that the group before is not reading: the
+// fetch of a group runs under the arithmetic of the previous one and a group costs one barrier.  Same summation order
+// as mv_kernel.
 constexpr int ELEM_MAXS = 4;    // elements staged at a time (tiles with more walk the items once more per group of elements)
-constexpr int ELEM_GROUP = 4;   // items whose weights are staged together
+constexpr int ELEM_GROUP = 4;   // most items whose weights are staged together
 constexpr int ELEM_TA = 128;
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
+{
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 template<int NQ>
 __global__ void __launch_bounds__(ELEM_TA) mv_elem_tile_kernel(MVDev op, const TensorDev *__restrict__ T,
                                                                const int *__restrict__ mu, int NA, int na, int n_in_max,
-                                                               int rows_per_cta)
+                                                               int rows_per_cta, int G)
 {
-  extern __shared__ __align__(16) float wsm[];    // [ELEM_GROUP][ELEM_MAXS][n_in_max][NQ * 4]
+  extern __shared__ __align__(16) float wsm[];    // [2][G][ELEM_MAXS][n_in_max][NQ * 4]
   __shared__ int s_slot[ELEM_TA], s_el[ELEM_TA], s_mu[ELEM_TA], s_order[ELEM_TA], s_cnt[ELEM_TA + 1], s_nsp;
   const int a0 = blockIdx.x * ELEM_TA, nta = min(ELEM_TA, na - a0), t = threadIdx.x;
   const int row_lo = blockIdx.y * rows_per_cta, row_hi = min(op.nrows, row_lo + rows_per_cta);
@@ -108,8 +118,9 @@ __global__ void __launch_bounds__(ELEM_TA) mv_elem_tile_kernel(MVDev op, const T
   const int p = active ? s_order[t] : 0;    // this thread's atom of the tile
   const int nsp = s_nsp, slot = active ? s_slot[p] : -1;
   const int i_lo = op.item_off[row_lo], i_hi = op.item_off[row_hi];
-  const float4 *w4 = reinterpret_cast<const float4 *>(wsm);
-  const int wstride = n_in_max * NQ;    // float4 per (item of the group, element)
+  const int wstride = n_in_max * NQ;                      // float4 per (item of the group, element)
+  const int bstride = G * ELEM_MAXS * wstride;            // float4 per buffer
+  float4 *const w4 = reinterpret_cast<float4 *>(wsm);
   const TensorDev dst = T[op.dst];
   for (int s0 = 0; s0 < nsp; s0 += ELEM_MAXS) {
     const int ng = min(ELEM_MAXS, nsp - s0);
@@ -144,26 +155,35 @@ __global__ void __launch_bounds__(ELEM_TA) mv_elem_tile_kernel(MVDev op, const T
       for (int k = 0; k < NQ; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
       row++;
     };
-    for (int it0 = i_lo; it0 < i_hi; it0 += ELEM_GROUP) {
-      const int nit = min(ELEM_GROUP, i_hi - it0);
-      __syncthreads();    // the weights of the previous group are no longer read
+    // asynchronous copies of the weights of the items it0 .. it0 + G of the elements s0 .. s0 + ng into buffer `buf`
+    auto stage = [&](int it0, int buf) {
+      const int nit = min(G, i_hi - it0);
       for (int g = 0; g < nit; g++) {
         const MVItem item = op.items[it0 + g];
         const int per = item.n_in * NQ;
         for (int q = t; q < ng * per; q += ELEM_TA) {
           const int s = q / per, r = q - s * per;
-          reinterpret_cast<float4 *>(wsm)[(size_t) (g * ELEM_MAXS + s) * wstride + r] =
-              __ldg(reinterpret_cast<const float4 *>(op.W + (size_t) s_el[s0 + s] * op.ty_stride + item.mat) + r);
+          cp_async16(w4 + (size_t) buf * bstride + (size_t) (g * ELEM_MAXS + s) * wstride + r,
+                     reinterpret_cast<const float4 *>(op.W + (size_t) s_el[s0 + s] * op.ty_stride + item.mat) + r);
         }
       }
-      __syncthreads();
+      cp_async_commit();
+    };
+    __syncthreads();    // the buffers of the previous group of elements are no longer read
+    if (i_lo < i_hi) stage(i_lo, 0);
+    int buf = 0;
+    for (int it0 = i_lo; it0 < i_hi; it0 += G, buf ^= 1) {
+      const int nit = min(G, i_hi - it0);
+      cp_async_wait_all();
+      __syncthreads();    // this group's weights are in place; the other buffer's readers are done
+      if (it0 + G < i_hi) stage(it0 + G, buf ^ 1);
       for (int g = 0; g < nit; g++) {
         while (it0 + g >= op.item_off[row + 1]) flush();
         if (!mine) continue;
         const MVItem item = op.items[it0 + g];
         const TensorDev src = T[item.src];
         const float *x = src.p + ((size_t) item.irow * NA + a0 + p) * src.C;
-        const float4 *w = w4 + (size_t) (g * ELEM_MAXS + slot - s0) * wstride;
+        const float4 *w = w4 + (size_t) buf * bstride + (size_t) (g * ELEM_MAXS + slot - s0) * wstride;
         float4 part[NQ];
 #pragma unroll
         for (int k = 0; k < NQ; k++) part[k] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -204,25 +224,29 @@ __global__ void __launch_bounds__(ELEM_TA) mv_elem_tile_kernel(MVDev op, const T
 
 template<int NQ> void launch_elem(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na)
 {
-  const size_t smem = (size_t) ELEM_GROUP * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float);
-  static bool attr = false;    // static shared memory counts against the 48 KB a kernel gets without the attribute
-  if (!attr && smem > 32 * 1024) {
-    GB_CUDA(cudaFuncSetAttribute(mv_elem_tile_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-    attr = true;
+  // items per group: both halves of the double buffer within ~56 KB, so that several CTAs share an SM
+  const size_t per_item = (size_t) ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float);
+  int G = ELEM_GROUP;
+  while (G > 1 && 2 * G * per_item > 56 * 1024) G--;
+  const size_t smem = 2 * G * per_item;
+  static size_t attr = 32 * 1024;    // static shared memory counts against the 48 KB a kernel gets without the attribute
+  if (smem > attr) {
+    GB_CUDA(cudaFuncSetAttribute(mv_elem_tile_kernel<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = 200 * 1024;
   }
   // rows of a tile go to one CTA unless the tiles alone cannot fill the GPU
   const int tiles = (na + ELEM_TA - 1) / ELEM_TA, want = 16 * dev().sm_count;
   const int gy = std::max(1, std::min(op.nrows, (want + tiles - 1) / tiles));
   const int rows_per_cta = (op.nrows + gy - 1) / gy;
   GB_LAUNCH((mv_elem_tile_kernel<NQ>), dim3(tiles, (op.nrows + rows_per_cta - 1) / rows_per_cta), ELEM_TA, smem, op, tensors, mu,
-            NA, na, op.unit_nmax, rows_per_cta);
+            NA, na, op.unit_nmax, rows_per_cta, G);
 }
 
 void launch_mv(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na)
 {
   if (op.nrows == 0 || na == 0) return;
   if (op.elem && (op.ldw & 3) == 0 && (op.ty_stride & 3) == 0 && op.unit_nmax > 0 &&
-      (size_t) ELEM_GROUP * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float) <= 96 * 1024) {
+      (size_t) 2 * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float) <= 192 * 1024) {
     switch (op.ldw >> 2) {
       case 1: launch_elem<1>(op, tensors, mu, NA, na); return;
       case 2: launch_elem<2>(op, tensors, mu, NA, na); return;
