@@ -6,6 +6,7 @@
 #include "readout.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace gb {
 
@@ -242,9 +243,116 @@ template<int NQ> void launch_elem(const MVDev &op, const TensorDev *tensors, con
             NA, na, op.unit_nmax, rows_per_cta, G);
 }
 
+// Per-element weights with wide outputs (the adjoints of the reduces: 9 - 17 inputs, 32 or 64 outputs per row): LPA =
+// n_out / 4 lanes per atom, each with one float4 of the output row, so that a row of an atom is written (and, when the
+// operation accumulates, read) as whole 128-byte lines; 32 / LPA atoms per warp, 8 warps per CTA, tiles of 128 atoms.
+// The weights of a group of output rows, for the elements present in the tile, are staged in shared memory; the inputs
+// of an atom are broadcast loads shared by its lanes.  Same summation order as mv_kernel.
+template<int LPA>
+__global__ void __launch_bounds__(256) mv_elem_wide_kernel(MVDev op, const TensorDev *__restrict__ T,
+                                                           const int *__restrict__ mu, int NA, int na, int n_in_max,
+                                                           int rows_per_cta, int G)
+{
+  constexpr int APW = 32 / LPA, APP = 8 * APW;    // atoms per warp and per pass of the CTA
+  extern __shared__ __align__(16) float wsm[];    // [G][ELEM_MAXS][n_in_max][LPA * 4]
+  __shared__ int s_slot[ELEM_TA], s_el[ELEM_TA], s_mu[ELEM_TA], s_nsp;
+  const int a0 = blockIdx.x * ELEM_TA, nta = min(ELEM_TA, na - a0), t = threadIdx.x;
+  const int row_lo = blockIdx.y * rows_per_cta, row_hi = min(op.nrows, row_lo + rows_per_cta);
+  if (t < nta) s_mu[t] = mu[a0 + t];
+  __syncthreads();
+  if (t == 0) {    // distinct elements of the tile in order of first appearance
+    int ns = 0;
+    for (int a = 0; a < nta; a++) {
+      const int e = s_mu[a];
+      int s = 0;
+      while (s < ns && s_el[s] != e) s++;
+      if (s == ns) s_el[ns++] = e;
+      s_slot[a] = s;
+    }
+    s_nsp = ns;
+  }
+  __syncthreads();
+  const int lane = t & 31, warp = t >> 5, kq = lane % LPA, asub = lane / LPA;
+  const int nsp = s_nsp, wstride = n_in_max * LPA;    // float4 per (item of the group, element)
+  float4 *const w4 = reinterpret_cast<float4 *>(wsm);
+  const TensorDev dst = T[op.dst];
+  for (int s0 = 0; s0 < nsp; s0 += ELEM_MAXS) {
+    const int ng = min(ELEM_MAXS, nsp - s0);
+    for (int r0 = row_lo; r0 < row_hi;) {
+      const int i_first = op.item_off[r0];
+      int r1 = r0 + 1;    // rows of the group: at most G items (a single row never has more: checked by the launcher)
+      while (r1 < row_hi && op.item_off[r1 + 1] - i_first <= G) r1++;
+      const int nit = op.item_off[r1] - i_first;
+      __syncthreads();    // the weights of the previous group are no longer read
+      for (int g = 0; g < nit; g++) {
+        const MVItem item = op.items[i_first + g];
+        const int per = item.n_in * LPA;
+        for (int q = t; q < ng * per; q += 256) {
+          const int s = q / per, r = q - s * per;
+          w4[(size_t) (g * ELEM_MAXS + s) * wstride + r] =
+              __ldg(reinterpret_cast<const float4 *>(op.W + (size_t) s_el[s0 + s] * op.ty_stride + item.mat) + r);
+        }
+      }
+      __syncthreads();
+      for (int ab = 0; ab < nta; ab += APP) {
+        const int ai = ab + warp * APW + asub;
+        if (ai >= nta) continue;
+        const int slot = s_slot[ai];
+        if (slot < s0 || slot >= s0 + ng) continue;
+        for (int row = r0; row < r1; row++) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int it = op.item_off[row]; it < op.item_off[row + 1]; it++) {
+            const MVItem item = op.items[it];
+            const TensorDev src = T[item.src];
+            const float *x = src.p + ((size_t) item.irow * NA + a0 + ai) * src.C;
+            const float4 *w = w4 + (size_t) ((it - i_first) * ELEM_MAXS + slot - s0) * wstride + kq;
+            float4 part = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int n = 0; n < item.n_in; n++) {
+              const float xv = __ldg(x + n);
+              const float4 wv = w[(size_t) n * LPA];
+              part.x = fmaf(xv, wv.x, part.x); part.y = fmaf(xv, wv.y, part.y);
+              part.z = fmaf(xv, wv.z, part.z); part.w = fmaf(xv, wv.w, part.w);
+            }
+            acc.x = fmaf(item.scale, part.x, acc.x); acc.y = fmaf(item.scale, part.y, acc.y);
+            acc.z = fmaf(item.scale, part.z, acc.z); acc.w = fmaf(item.scale, part.w, acc.w);
+          }
+          float4 *o = reinterpret_cast<float4 *>(dst.p + ((size_t) op.row_out[row] * NA + a0 + ai) * dst.C) + kq;
+          if (op.accumulate) {
+            const float4 old = *o;
+            acc.x += old.x; acc.y += old.y; acc.z += old.z; acc.w += old.w;
+          }
+          *o = acc;
+        }
+      }
+      r0 = r1;
+    }
+  }
+}
+
+template<int LPA> bool launch_elem_wide(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na)
+{
+  const size_t per_item = (size_t) ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float);
+  const int G = (int) std::min<size_t>(16, (40 * 1024) / per_item);
+  if (G < 1 || op.max_row_items > G) return false;
+  const size_t smem = G * per_item;
+  const int tiles = (na + ELEM_TA - 1) / ELEM_TA, want = 8 * dev().sm_count;
+  const int gy = std::max(1, std::min(op.nrows, (want + tiles - 1) / tiles));
+  const int rows_per_cta = (op.nrows + gy - 1) / gy;
+  GB_LAUNCH((mv_elem_wide_kernel<LPA>), dim3(tiles, (op.nrows + rows_per_cta - 1) / rows_per_cta), 256, smem, op, tensors, mu, NA,
+            na, op.unit_nmax, rows_per_cta, G);
+  return true;
+}
+
 void launch_mv(const MVDev &op, const TensorDev *tensors, const int *mu, int NA, int na)
 {
   if (op.nrows == 0 || na == 0) return;
+  // wide per-element operations (adjoints of the reduces): channel-parallel form with whole-line stores
+  static const bool nowide = getenv("GRACE_B200_ELEM_NOWIDE") != nullptr;
+  if (!nowide && op.elem && op.ldw == op.n_out && op.dst_C == op.n_out && (op.ty_stride & 3) == 0 && op.unit_nmax > 0 &&
+      op.unit_nmax <= 20) {
+    if (op.n_out == 32 && launch_elem_wide<8>(op, tensors, mu, NA, na)) return;
+    if (op.n_out == 64 && launch_elem_wide<16>(op, tensors, mu, NA, na)) return;
+  }
   if (op.elem && (op.ldw & 3) == 0 && (op.ty_stride & 3) == 0 && op.unit_nmax > 0 &&
       (size_t) 2 * ELEM_MAXS * op.unit_nmax * op.ldw * sizeof(float) <= 192 * 1024) {
     switch (op.ldw >> 2) {
@@ -394,7 +502,8 @@ void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, in
     const size_t per_atom = (size_t) (nfA + (two ? nfB : 0)) * C * 4, fixed = (size_t) nterms * sizeof(int4) + 64;
     // several CTAs per SM (the load, compute and store phases of a tile overlap only across CTAs): a quarter of the
     // shared memory when that holds 4+ atoms, else half, else all of it
-    const size_t quarter = 54 * 1024, half = 110 * 1024, large = 200 * 1024;
+    static const size_t first = getenv("GRACE_B200_PROD_KB") ? (size_t) atoi(getenv("GRACE_B200_PROD_KB")) * 1024 : 54 * 1024;
+    const size_t quarter = first, half = 110 * 1024, large = 200 * 1024;
     size_t budget = quarter;
     if (fixed + 4 * per_atom > quarter) budget = half;
     if (fixed + 4 * per_atom > half) budget = large;

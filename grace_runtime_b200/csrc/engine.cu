@@ -141,6 +141,9 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
     d.accumulate = o.accumulate;
     d.elem = o.elem;
     d.dst = o.dst;
+    d.dst_C = P.tensors[o.dst].channels;
+    d.max_row_items = 0;
+    for (size_t r = 0; r + 1 < o.item_off.size(); r++) d.max_row_items = std::max(d.max_row_items, o.item_off[r + 1] - o.item_off[r]);
     E.mv.push_back(d);
   }
   for (size_t q = 0; q < P.prod.size(); q++) {

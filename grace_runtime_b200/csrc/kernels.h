@@ -27,6 +27,8 @@ struct MVDev {
   int n_uniform;     // n_in of the items when they all agree, else 0
   int unit_nmax;     // largest n_in of the units
   int unit_exact;    // 32 or 64 when every n_in, n_out and channel stride of the operation equals it, else 0
+  int dst_C;         // channels (row stride) of the output tensor
+  int max_row_items; // most items of one output row
 };
 
 struct ProdDev {
