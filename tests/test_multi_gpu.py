@@ -57,7 +57,7 @@ def test_slabs_of_small_cells_with_many_images(backend, cells, name, world):
 
 @pytest.mark.parametrize("cfg,lattice,a,reps,nsp,sigma", [("1l", "bcc", 3.2, (5, 5, 24), 4, 0.05),
                                                            ("2l", "fcc", 3.6, (3, 18, 3), 3, 0.08)])
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_slabs_of_benchmark_shaped_cells(backend, tmp_path_factory, cfg, lattice, a, reps, nsp, sigma, world):
     """long cells: slabs wider than the halo, so that most ghosts are skipped by the active ranges"""
     path, els, types, pos, cell, pbc = _case(tmp_path_factory, cfg, lattice, a, reps, nsp, sigma, seed=21)

@@ -110,6 +110,35 @@ def test_uq_chunked_passes_and_projection_kernels(backend, cells, uq_gold, uq_pa
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("layers,lmax,lattice,a,reps", [(1, 4, "bcc", 3.2, (4, 4, 5)), (2, 2, "fcc", 3.6, (3, 3, 4))])
+def test_uq_of_generated_order4_models_against_the_compiled_reference(backend, tmp_path, monkeypatch, layers, lmax, lattice, a, reps):
+    """32 / 64-channel models of body order 5 (the shapes the tensor-core kernel covers): the projection runs as
+    mv_tc_kernel; gamma, sigma and cluster against the reference's CPU drivers evaluated here"""
+    from grace_runtime_b200 import modelgen, structures
+    from oracle import refcpu
+    if not refcpu.available():
+        pytest.skip("oracle/_ref is not built")
+    els = modelgen._subset(5, 3)
+    base = str(tmp_path / "m.npz")
+    modelgen.write_model(base, layers=layers, lmax=lmax, max_order=4, elements=tuple(els), c1=32, cr=16, c2=64,
+                         rho_n_out=9, energy_hidden=(32,), avg_neigh=58.0 if lattice == "bcc" else 78.0, seed=3)
+    path = modelgen.add_uq_head(base, str(tmp_path / "m_uq.npz"), seed=9, rp_dim=32, max_clusters=3)
+    types, pos, cell, pbc = structures.crystal(lattice, a, reps, n_species=3, sigma=0.06, seed=4)
+    ref = refcpu.RefModel(path, els).compute(types, pos, cell, pbc, uq=True)
+    monkeypatch.setenv("GRACE_B200_DENSE", "tc")
+    s = backend.System(backend.Model(path), els)
+    backend.profile_enable(True)
+    r = s.compute(types, pos, cell, pbc, uq=True)
+    kernels = backend.profile_report()
+    backend.profile_enable(False)
+    assert any("mv_tc_kernel" in k for k in kernels)
+    assert np.array_equal(r["gmm_cluster"], ref["cluster"])
+    assert np.abs(r["gamma"] / ref["gamma"] - 1.0).max() < UQ_RTOL
+    assert np.abs(r["atomic_sigma"] / ref["sigma"] - 1.0).max() < UQ_RTOL
+    assert abs(r["energy"] - ref["energy"]) / len(types) < 1e-5
+
+
+@pytest.mark.gpu
 def test_batch_uq_and_device_arrays(backend, cells, uq_gold, uq_paths):
     torch = pytest.importorskip("torch")
     name = "grace_2l_small"
