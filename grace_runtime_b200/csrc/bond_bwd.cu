@@ -20,7 +20,7 @@ namespace gb {
 
 namespace {
 
-constexpr int EBB = 32;    // bonds staged per round
+constexpr int EBB = 96;    // bonds staged per round: most atoms in one round, every thread of the block staging one bond
 
 template<int LMAX, int NIT, int NCH, int LPE, bool EXACT>
 __global__ void __launch_bounds__(128) bond_bwd_kernel(BondsDev b, LayerDev L, SHTable sht,

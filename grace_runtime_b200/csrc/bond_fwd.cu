@@ -17,7 +17,7 @@ namespace gb {
 
 namespace {
 
-constexpr int EB = 64;    // bonds staged per round
+constexpr int EB = 96;    // bonds staged per round: most atoms in one round
 
 template<int LMAX, int NIT, int NCH, int LPE, bool EXACT>
 __global__ void __launch_bounds__(128) bond_fwd_kernel(BondsDev b, LayerDev L, SHTable sht, float *__restrict__ Q,
