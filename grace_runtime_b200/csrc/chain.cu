@@ -508,6 +508,10 @@ void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, in
     if (fixed + 4 * per_atom > quarter) budget = half;
     if (fixed + 4 * per_atom > half) budget = large;
     int TA = fixed < budget ? (int) std::min<size_t>(32, (budget - fixed) / per_atom) : 0;
+    {    // a warp walks a row 64 float4 at a time: tiles whose rows are a multiple of that leave no lane idle
+      const int unit = std::max(1, 64 / (C >> 2));
+      if (TA > unit) TA = TA / unit * unit;
+    }
     if (TA >= 1) {
       const size_t smem = fixed + (size_t) TA * per_atom;
       static size_t attr = 48 * 1024;
