@@ -265,9 +265,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
       const MVItem item = s_items[cur.it];
       if (cur.tt == 0) {    // first tile of an item: its weight image (hi + lo, byte for byte the operand layout)
         item_no++;
-        const int4 *src = reinterpret_cast<const int4 *>(op.images + (size_t) item.mat * 2 * W_BYTES);
-        int4 *dst = reinterpret_cast<int4 *>(W_st + (size_t) (item_no % S) * 2 * W_BYTES);
-        for (int q = t; q < 2 * W_BYTES / 16; q += NPROD) dst[q] = __ldg(src + q);
+        if (t == 0) {
+          // one bulk asynchronous copy; its bytes are counted by this stage's `full` barrier, so the matrix instructions
+          // of the fill start when the image and the 256 arrivals are there, and no producer waits for the copy
+          const unsigned bar = smem_u32(&s_full[s]), dst = smem_u32(W_st + (size_t) (item_no % S) * 2 * W_BYTES);
+          const char *src = op.images + (size_t) item.mat * 2 * W_BYTES;
+          asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"((unsigned) (2 * W_BYTES)) : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(dst), "l"(src), "r"((unsigned) (2 * W_BYTES)), "r"(bar) : "memory");
+        }
       }
       {    // registers -> tf32 hi / lo operand images of stage s
         char *hi = A_st + (size_t) s * 2 * A_BYTES, *lo = hi + A_BYTES;
