@@ -56,19 +56,17 @@ __device__ __forceinline__ void mma_tf32_ss(unsigned tmem_d, unsigned long long 
                ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"((unsigned) accumulate) : "memory");
 }
 
+// hi + lo split of four activations for the 3 x tf32 product.  The tensor cores read the upper 19 bits of an fp32
+// operand (sign, exponent, 10 mantissa bits) and ignore the rest, so `hi` is the value itself and lo = x - trunc(x) is
+// exact in fp32; lo in turn is read truncated, which leaves a relative error of 2^-20 of x - the size of the a_lo b_lo
+// term the scheme drops anyway.  Two instructions per value and none of them a conversion.
 __device__ __forceinline__ void split4(float4 x, float sc, float4 &hi, float4 &lo)
 {
   const float v[4] = {x.x * sc, x.y * sc, x.z * sc, x.w * sc};
-  float h[4], l[4];
+  float l[4];
 #pragma unroll
-  for (int q = 0; q < 4; q++) {
-    unsigned a, b;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(a) : "f"(v[q]));
-    h[q] = __uint_as_float(a);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(v[q] - h[q]));
-    l[q] = __uint_as_float(b);
-  }
-  hi = make_float4(h[0], h[1], h[2], h[3]);
+  for (int q = 0; q < 4; q++) l[q] = v[q] - __uint_as_float(__float_as_uint(v[q]) & 0xffffe000u);
+  hi = make_float4(v[0], v[1], v[2], v[3]);
   lo = make_float4(l[0], l[1], l[2], l[3]);
 }
 
