@@ -3,13 +3,14 @@
 // On chunk tensors [function][atom][channel] an operation  out[row] (+)= sum_items scale * W_item^T x[item]  is a
 // grouped GEMM whose long dimension is the atoms: for an output row and a tile of 128 atoms,
 //     D[128 atoms][n_out] = sum_items X_item[128 atoms][K] . W_item[K][n_out],
-// with X_item a contiguous block of the source tensor.  A CTA owns up to 512 / n_out atom tiles at a time and keeps one
-// fp32 accumulator per tile in tensor memory; for every item of the row it converts the tile's activations to tf32
-// hi + lo operand images in shared memory (canonical K-major layout, 8-row x 16-byte core matrices) and issues
-// tcgen05.mma kind::tf32 M = 128, N = n_out against the item's weight image (converted and split on the host once):
-// a b ~ a_lo b_hi + a_hi b_lo + a_hi b_hi keeps fp32-level accuracy.  Activation tiles are double-buffered and the next
-// tile's global loads are in flight while the current one is converted, so the tensor cores, the conversion and the
-// memory system overlap; all items of a row accumulate in tensor memory and each output row is written once.
+// with X_item a contiguous block of the source tensor.  A CTA owns up to 256 / n_out atom tiles at a time and keeps two
+// sets of fp32 accumulators for them in tensor memory; for every item of the row its producer warps write the tile's
+// activations as hi + lo operand images into a ring of shared-memory stages (canonical K-major layout, 8-row x 16-byte
+// core matrices), the item's weight image (split on the host once) arrives by one bulk asynchronous copy, and one
+// thread issues tcgen05.mma kind::tf32 M = 128, N = n_out: a b ~ a_lo b_hi + a_hi b_lo + a_hi b_hi keeps fp32-level
+// accuracy.  The global loads of the next two tiles are in flight in registers while a tile is written, all items of a
+// row accumulate in tensor memory, and the epilogue warps write each output row once while the next row's matrix
+// instructions run.
 // Same mathematics as mv_kernel (chain.cu); reference: fc_fwd / mv_batch, libgrace/include/grace/fused_cpu.h:294-356,
 // GPU fc_fwd4 libgrace/include/grace/kk/fused_dense.h:441-495.
 //
