@@ -560,7 +560,7 @@ def run_ours(args, rank, world, local_rank):
     dense_names = {"mv_tc_kernel": "tensor", "prod_tile_kernel": "products"}
     if top in dense_names:
         # per-operation dense path: all launches of the kernel in a step together (one per operation of the plan; GRACE-2L
-        # per 262,144-atom pass); flops and algorithmic bytes per atom from the plan
+        # per pass of layer 2); flops and algorithmic bytes per atom from the plan
         lps = top_n / args.steps
         fl_atom, by_atom = model.dense_stats[dense_names[top]]
         step_ms = top_ms / args.steps

@@ -341,7 +341,7 @@ int Engine::auto_chunk(int64_t n) const
   const double budget = 0.35 * (double) free_b + 4.0 * (double) arena_.capacity();
   int64_t c = (int64_t) (budget / per_atom_bytes(n));
   // per-operation passes: large enough that the atom tiles of a pass fill the GPU, small enough to bound the work memory
-  c = std::min<int64_t>(c, use_fused(n) ? ((int64_t) 1 << 22) : (use_tc(n) ? 262144 : 32768));
+  c = std::min<int64_t>(c, use_fused(n) ? ((int64_t) 1 << 22) : (use_tc(n) ? 524288 : 32768));
   c = std::max<int64_t>(c, 512);
   return (int) std::min<int64_t>(c, std::max<int64_t>(n, 1));
 }
