@@ -778,6 +778,13 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
   const int *mu = nl.mu_sorted();
   float *fv = fv_.get();
   auto zero_grads = [&](LayerEngine &E, float *base, int stride) {
+    if (!E.plan->zero_grads) {    // every gradient row is written before it is added to, but for the rows listed
+      for (const auto &zr : E.plan->zero_rows) {
+        const TensorDev &t = E.tensors_host[zr.first];
+        GB_CUDA(cudaMemsetAsync(t.p + (size_t) zr.second * stride * t.C, 0, sizeof(float) * (size_t) stride * t.C, st));
+      }
+      return;
+    }
     GB_CUDA(cudaMemsetAsync(base + E.grad_begin * stride, 0, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * stride, st));
   };
   const int S1 = base1 ? NA1 : NA;                   // atom stride of the layer-1 tensors

@@ -147,6 +147,69 @@ struct LayerBuilder {
   {
     for (size_t q = adj.size(); q-- > 0;)
       for (const Op &o : adj[q]) P.bwd.ops.push_back(o);
+    first_writers();
+  }
+
+  // rows `sel` (positions in row_out) of an operation as an operation of its own
+  static MVOp subset(const MVOp &o, const std::vector<int> &sel, const std::string &suffix)
+  {
+    MVOp s;
+    s.name = o.name + suffix; s.dst = o.dst; s.n_out = o.n_out; s.ldw = o.ldw; s.accumulate = o.accumulate; s.elem = o.elem;
+    s.ty_stride = o.ty_stride; s.W = o.W;
+    for (int r : sel) {
+      s.row_out.push_back(o.row_out[r]);
+      s.item_off.push_back((int) s.items.size());
+      s.items.insert(s.items.end(), o.items.begin() + o.item_off[r], o.items.begin() + o.item_off[r + 1]);
+    }
+    s.item_off.push_back((int) s.items.size());
+    return s;
+  }
+
+  // The reverse operations add into gradient tensors.  The first operation that touches a row may as well write it:
+  // then nothing has to clear the gradients before the reverse pass (half of a layer's tensors per pass) and the first
+  // writers do not read zeros back.  An MV operation whose rows are partly new is split in two; a product keeps adding and
+  // its new rows go to zero_rows.  zero_grads stays set if some gradient row has no writer at all.
+  void first_writers()
+  {
+    std::vector<std::vector<char>> written(P.tensors.size());
+    for (size_t t = 0; t < P.tensors.size(); t++) written[t].assign(P.tensors[t].nfuncs, 0);
+    std::vector<Op> out;
+    for (const Op &o : P.bwd.ops) {
+      const bool mv = o.kind == Op::MV;
+      const int dst = mv ? P.mv[o.index].dst : P.prod[o.index].dst;
+      const bool acc = mv ? P.mv[o.index].accumulate : P.prod[o.index].accumulate;
+      const std::vector<int> rows = mv ? P.mv[o.index].row_out : P.prod[o.index].row_out;
+      std::vector<int> fresh, old;
+      for (size_t r = 0; r < rows.size(); r++) (written[dst][rows[r]] ? old : fresh).push_back((int) r);
+      for (int r : rows) written[dst][r] = 1;
+      if (!P.tensors[dst].grad || !acc || fresh.empty()) {
+        out.push_back(o);
+        continue;
+      }
+      if (old.empty()) {
+        if (mv) P.mv[o.index].accumulate = false;
+        else P.prod[o.index].accumulate = false;
+        out.push_back(o);
+        continue;
+      }
+      if (mv) {
+        MVOp a = subset(P.mv[o.index], fresh, ":first"), b = subset(P.mv[o.index], old, "");
+        a.accumulate = false;
+        P.mv[o.index] = std::move(b);
+        P.mv.push_back(std::move(a));
+        out.push_back({Op::MV, (int) P.mv.size() - 1});
+      } else {
+        // a product stages all rows of its inputs per launch, so it is not split: its new rows are cleared one by one
+        for (int r : fresh) P.zero_rows.push_back({dst, rows[r]});
+      }
+      out.push_back(o);
+    }
+    P.bwd.ops = out;
+    P.zero_grads = false;
+    for (size_t t = 0; t < P.tensors.size(); t++)
+      if (P.tensors[t].grad)
+        for (char w : written[t])
+          if (!w) P.zero_grads = true;
   }
 
   // FC: dst = nof (Wl Xl + sum Wr Xr) on the live outputs, and its two adjoints
@@ -521,6 +584,7 @@ void compact_rows(LayerPlan &P)
       if (o.srcB >= 0) tm.b = map[o.srcB][tm.b];
     }
   }
+  for (auto &zr : P.zero_rows) zr.second = map[zr.first][zr.second];
 }
 
 // matrix-major work list of an operation with shared weights (see MVOp::unit_desc)
