@@ -651,6 +651,7 @@ def run_ours(args, rank, world, local_rank):
            "value_definition": "max over ranks of (CUDA-event time of the K steps / K) / atoms of the structure (whole job)",
            "us_per_atom_per_gpu": value * world,
            "ms_per_step_median": float(times[3]), "ms_per_step_max": float(times[4]),
+           "ms_per_step_each_rank0": [round(float(x), 2) for x in per_step],
            "e2e": e2e, "gpu_launches": int(counts[0]), "clocks": clocks, "roofline": roof, "hbm_kernels": hbm_kernels,
            "measured_peaks": peaks_here,
            "details": {"species": species, "cutoff_A": cutoff, "chunk_atoms": system.chunksize,
