@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(256) prod_kernel(ProdDev op, const TensorDev *
     }
   }
   float *o = T[op.dst].p + (long long) op.row_out[row] * row_len + i;
-  *o = op.accumulate ? *o + acc : acc;
+  *o = (op.accumulate && !(op.row_first && op.row_first[row])) ? *o + acc : acc;
 }
 
 // The same for a tile of TA atoms with the input rows staged in shared memory: every input value comes from global
@@ -453,6 +453,7 @@ __global__ void __launch_bounds__(256) prod_tile_kernel(ProdDev op, const Tensor
   auto f2 = [](float x, float y) { return make_float2(x, y); };
   for (int row = warp; row < op.nrows; row += 8) {
     const int t0 = op.term_off[row], t1 = op.term_off[row + 1];
+    const bool add = op.accumulate && !(op.row_first && op.row_first[row]);
     float4 *orow = reinterpret_cast<float4 *>(D + ((size_t) op.row_out[row] * NA + a0) * C);
     for (int r = lane; r < nvalid; r += 64) {
       const bool has1 = r + 32 < nvalid;
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__(256) prod_tile_kernel(ProdDev op, const Tensor
         }
       }
       float4 o0 = make_float4(a0l.x, a0l.y, a0h.x, a0h.y), o1 = make_float4(a1l.x, a1l.y, a1h.x, a1h.y);
-      if (op.accumulate) {
+      if (add) {
         const float4 old0 = orow[r], old1 = orow[r1];
         o0.x += old0.x; o0.y += old0.y; o0.z += old0.z; o0.w += old0.w;
         o1.x += old1.x; o1.y += old1.y; o1.z += old1.z; o1.w += old1.w;

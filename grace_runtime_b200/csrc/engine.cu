@@ -83,7 +83,7 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
   std::vector<int> itab;
   std::vector<MVItem> items;
   std::vector<ProdTerm> terms;
-  std::vector<size_t> mv_row, mv_off, mv_item, mv_ud, mv_so, mv_ue, pr_row, pr_off, pr_term;
+  std::vector<size_t> mv_row, mv_off, mv_item, mv_ud, mv_so, mv_ue, pr_row, pr_off, pr_term, pr_first;
   auto put = [&](const std::vector<int> &v) {
     const size_t at = itab.size();
     itab.insert(itab.end(), v.begin(), v.end());
@@ -102,6 +102,7 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
   for (const ProdOp &o : P.prod) {
     pr_row.push_back(put(o.row_out));
     pr_off.push_back(put(o.term_off));
+    pr_first.push_back(put(o.row_first));
     pr_term.push_back(terms.size());
     terms.insert(terms.end(), o.terms.begin(), o.terms.end());
   }
@@ -152,6 +153,7 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
     d.row_out = E.itab.get() + pr_row[q];
     d.term_off = E.itab.get() + pr_off[q];
     d.terms = E.terms.get() + pr_term[q];
+    d.row_first = o.row_first.empty() ? nullptr : E.itab.get() + pr_first[q];
     d.nrows = (int) o.row_out.size();
     d.accumulate = o.accumulate;
     d.dst = o.dst;
@@ -778,13 +780,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
   const int *mu = nl.mu_sorted();
   float *fv = fv_.get();
   auto zero_grads = [&](LayerEngine &E, float *base, int stride) {
-    if (!E.plan->zero_grads) {    // every gradient row is written before it is added to, but for the rows listed
-      for (const auto &zr : E.plan->zero_rows) {
-        const TensorDev &t = E.tensors_host[zr.first];
-        GB_CUDA(cudaMemsetAsync(t.p + (size_t) zr.second * stride * t.C, 0, sizeof(float) * (size_t) stride * t.C, st));
-      }
-      return;
-    }
+    if (!E.plan->zero_grads) return;    // every gradient row is written before it is added to
     GB_CUDA(cudaMemsetAsync(base + E.grad_begin * stride, 0, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * stride, st));
   };
   const int S1 = base1 ? NA1 : NA;                   // atom stride of the layer-1 tensors

@@ -36,6 +36,8 @@ struct ProdDev {
   const int *term_off;
   const ProdTerm *terms;
   int nrows, accumulate, dst, srcA, srcB;
+  const int *row_first;    // accumulating operation: rows flagged 1 are written instead of added to (null: none); the
+                           // fused kernel clears its gradients beforehand and may ignore it
 };
 
 // the neighbour list of one pass and this call's bond records

@@ -168,7 +168,7 @@ struct LayerBuilder {
   // The reverse operations add into gradient tensors.  The first operation that touches a row may as well write it:
   // then nothing has to clear the gradients before the reverse pass (half of a layer's tensors per pass) and the first
   // writers do not read zeros back.  An MV operation whose rows are partly new is split in two; a product keeps adding and
-  // its new rows go to zero_rows.  zero_grads stays set if some gradient row has no writer at all.
+  // is told which of its rows are new (row_first).  zero_grads stays set if some gradient row has no writer at all.
   void first_writers()
   {
     std::vector<std::vector<char>> written(P.tensors.size());
@@ -199,17 +199,13 @@ struct LayerBuilder {
         P.mv.push_back(std::move(a));
         out.push_back({Op::MV, (int) P.mv.size() - 1});
       } else {
-        // a product stages all rows of its inputs per launch, so it is not split: its new rows are cleared one by one
-        for (int r : fresh) P.zero_rows.push_back({dst, rows[r]});
+        // a product stages all rows of its inputs per launch, so it is not split: it is told which rows to write
+        P.prod[o.index].row_first.assign(rows.size(), 0);
+        for (int r : fresh) P.prod[o.index].row_first[r] = 1;
       }
       out.push_back(o);
     }
     P.bwd.ops = out;
-    P.zero_grads = false;
-    for (size_t t = 0; t < P.tensors.size(); t++)
-      if (P.tensors[t].grad)
-        for (char w : written[t])
-          if (!w) P.zero_grads = true;
   }
 
   // FC: dst = nof (Wl Xl + sum Wr Xr) on the live outputs, and its two adjoints
@@ -584,7 +580,23 @@ void compact_rows(LayerPlan &P)
       if (o.srcB >= 0) tm.b = map[o.srcB][tm.b];
     }
   }
-  for (auto &zr : P.zero_rows) zr.second = map[zr.first][zr.second];
+}
+
+// after compact_rows: the gradients still have to be cleared before the reverse pass if some row of a gradient tensor
+// that survived the pruning has no writing operation at all
+void check_gradient_writers(LayerPlan &P)
+{
+  std::vector<std::vector<char>> written(P.tensors.size());
+  for (size_t t = 0; t < P.tensors.size(); t++) written[t].assign(P.tensors[t].nfuncs, 0);
+  for (const Op &o : P.bwd.ops) {
+    const int dst = o.kind == Op::MV ? P.mv[o.index].dst : P.prod[o.index].dst;
+    for (int r : (o.kind == Op::MV ? P.mv[o.index].row_out : P.prod[o.index].row_out)) written[dst][r] = 1;
+  }
+  P.zero_grads = false;
+  for (size_t t = 0; t < P.tensors.size(); t++)
+    if (P.tensors[t].grad)
+      for (char w : written[t])
+        if (!w) P.zero_grads = true;
 }
 
 // matrix-major work list of an operation with shared weights (see MVOp::unit_desc)
@@ -774,7 +786,11 @@ ModelPlan build_plan(const GraceModel &m, int spline_n)
     B.finish();
   }
   compact_rows(P.L1);
-  if (m.layers == 2) compact_rows(P.L2);
+  check_gradient_writers(P.L1);
+  if (m.layers == 2) {
+    compact_rows(P.L2);
+    check_gradient_writers(P.L2);
+  }
   for (LayerPlan *L : {&P.L1, &P.L2})
     for (MVOp &o : L->mv) build_units(o);
   // readout

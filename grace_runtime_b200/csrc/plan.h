@@ -67,6 +67,7 @@ struct ProdOp {
   std::vector<int> row_out;
   std::vector<int> term_off;
   std::vector<ProdTerm> terms;
+  std::vector<int> row_first;    // accumulating operation: 1 for the rows it is the first to touch (written, not added to); empty: none
 };
 
 struct Op {
@@ -91,7 +92,6 @@ struct LayerPlan {
   Program fwd, bwd;
   bool zero_grads = true;   // some gradient row has no writing operation: the drivers clear the gradients before the
                             // reverse pass (otherwise the first operation on a row writes it: plan.cpp first_writers)
-  std::vector<std::pair<int, int>> zero_rows;    // (tensor, row) cleared before the reverse pass when zero_grads is off
   int tQ = -1, tGQ = -1;    // the bond-sum tensor written by the forward bond kernel and its gradient
   int n_msg = 0;            // message functions of the neighbours coupled in (layer 2: I_n_funcs; layer 1: 0)
   int C = 0;                // channels of the bond sum
