@@ -6,6 +6,7 @@
 #include "readout.cuh"
 
 #include <algorithm>
+#include <cstdint>
 #include <cstdlib>
 
 namespace gb {
@@ -706,6 +707,28 @@ void launch_force_scatter(const BondsDev &b, const float *fv, double *forces, lo
 {
   if (n == 0) return;
   GB_LAUNCH(force_scatter_kernel, (unsigned) ((n + 3) / 4), 128, 0, b, fv, forces, n);
+}
+
+// Zero fill of a 16-byte aligned buffer whose size is a multiple of 4 bytes: 16-byte stores, a grid-stride loop over a
+// grid that fills the GPU.  For buffers of hundreds of megabytes this is several times faster than the driver's memset.
+__global__ void __launch_bounds__(256) fill_zero_kernel(float4 *__restrict__ p4, long long n4, float *__restrict__ tail, int ntail)
+{
+  const long long stride = (long long) gridDim.x * blockDim.x;
+  for (long long i = (long long) blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) p4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (blockIdx.x == 0 && (int) threadIdx.x < ntail) tail[threadIdx.x] = 0.0f;
+}
+
+void launch_fill_zero(void *p, size_t bytes)
+{
+  if (bytes == 0) return;
+  if ((reinterpret_cast<uintptr_t>(p) & 15) != 0 || (bytes & 3) != 0 || bytes < (1u << 20)) {
+    GB_CUDA(cudaMemsetAsync(p, 0, bytes, dev().stream));
+    return;
+  }
+  const long long n4 = (long long) (bytes / 16);
+  const int ntail = (int) ((bytes % 16) / 4);
+  const unsigned grid = (unsigned) std::min<long long>((n4 + 255) / 256, (long long) dev().sm_count * 16);
+  GB_LAUNCH(fill_zero_kernel, grid, 256, 0, reinterpret_cast<float4 *>(p), n4, reinterpret_cast<float *>(p) + 4 * n4, ntail);
 }
 
 __global__ void __launch_bounds__(256) add_f64_kernel(const double *__restrict__ v, double *out, long long n)

@@ -409,7 +409,7 @@ float *Engine::message_gradient_slots(NeighborList &nl)
       p = nullptr;
     }
   }
-  if (!p) GB_CUDA(cudaMemsetAsync(gI_rows_.get(), 0, sizeof(float) * (size_t) nl.n() * plan_.nI * plan_.cr, st));
+  if (!p) launch_fill_zero(gI_rows_.get(), sizeof(float) * (size_t) nl.n() * plan_.nI * plan_.cr);
   return p;
 }
 
@@ -781,7 +781,7 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
   float *fv = fv_.get();
   auto zero_grads = [&](LayerEngine &E, float *base, int stride) {
     if (!E.plan->zero_grads) return;    // every gradient row is written before it is added to
-    GB_CUDA(cudaMemsetAsync(base + E.grad_begin * stride, 0, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * stride, st));
+    launch_fill_zero(base + E.grad_begin * stride, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * stride);
   };
   const int S1 = base1 ? NA1 : NA;                   // atom stride of the layer-1 tensors
   const int64_t step1 = base1 ? (int64_t) NA1 : NA;    // atoms per layer-1 pass
@@ -957,17 +957,17 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
   e_atom_.ensure(n);
   if (!energy_only) vir_atom_.ensure(6 * n);
   if (partial) {    // what the skipped atoms would have written is read below or by the active atoms: zeros
-    GB_CUDA(cudaMemsetAsync(e_atom_.get(), 0, sizeof(double) * n, st));
+    launch_fill_zero(e_atom_.get(), sizeof(double) * n);
     if (!energy_only) {
-      GB_CUDA(cudaMemsetAsync(vir_atom_.get(), 0, sizeof(double) * 6 * n, st));
-      GB_CUDA(cudaMemsetAsync(fv_.get(), 0, sizeof(float) * 3 * (size_t) nl.nslots(), st));
+      launch_fill_zero(vir_atom_.get(), sizeof(double) * 6 * n);
+      launch_fill_zero(fv_.get(), sizeof(float) * 3 * (size_t) nl.nslots());
     }
     if (plan_.layers == 2) {
       I_rows_.ensure((size_t) n * plan_.nI * plan_.cr);
-      GB_CUDA(cudaMemsetAsync(I_rows_.get(), 0, sizeof(float) * (size_t) n * plan_.nI * plan_.cr, st));
+      launch_fill_zero(I_rows_.get(), sizeof(float) * (size_t) n * plan_.nI * plan_.cr);
       if (!energy_only) {
         grho_rows_.ensure((size_t) n * plan_.nrho);
-        GB_CUDA(cudaMemsetAsync(grho_rows_.get(), 0, sizeof(double) * (size_t) n * plan_.nrho, st));
+        launch_fill_zero(grho_rows_.get(), sizeof(double) * (size_t) n * plan_.nrho);
       }
     }
   }

@@ -189,6 +189,8 @@ void launch_force_gather(const long long *off, const int *rev, const float *fv, 
 // lists without a reverse-bond index (a caller's own list with ghost atoms): forces[i] += sum of the atom's bond forces,
 // forces[j] -= each bond force, with fp64 atomic adds (forces is accumulated into, indexed like the list's atoms)
 void launch_force_scatter(const BondsDev &b, const float *fv, double *forces, long long n);
+// zero fill on the library's stream (a kernel for large aligned buffers, the driver's memset otherwise)
+void launch_fill_zero(void *p, size_t bytes);
 // out[i] += v[i]
 void launch_add_f64(const double *v, double *out, long long n);
 // per-structure sums of per-atom values: out[s][k] = sum_{i in [seg[s], seg[s+1])} v[i][k]
