@@ -533,44 +533,59 @@ void launch_prod(const ProdDev &op, const TensorDev *tensors, int NA, int na, in
 // ---- readouts (fp64, one thread per atom) ---------------------------------------------------------------------
 __global__ void __launch_bounds__(64) readout_1l_kernel(ReadoutDev r, const float *__restrict__ rho, float *grho,
                                                         const int *__restrict__ mu, double *e_atom, int NA, int na,
-                                                        int a0, int want_grad)
+                                                        int a0, int want_grad, const int *__restrict__ ilist)
 {
   const int a = blockIdx.x * blockDim.x + threadIdx.x;
   if (a >= na) return;
-  e_atom[a0 + a] = readout_1l_atom(r, rho + (size_t) a * r.nrho, mu[a0 + a], grho + (size_t) a * r.nrho, want_grad,
-                                   r.owned(a0 + a));
+  const int i = ilist ? ilist[a0 + a] : a0 + a;    // the atom of chunk position a
+  e_atom[i] = readout_1l_atom(r, rho + (size_t) a * r.nrho, mu[i], grho + (size_t) a * r.nrho, want_grad, r.owned(i));
 }
 
 void launch_readout_1l(const ReadoutDev &r, const float *rho, float *grho, const int *mu, double *e_atom, int NA,
-                       int na, int a0, int want_grad)
+                       int na, int a0, int want_grad, const int *ilist)
 {
   if (na == 0) return;
-  GB_LAUNCH(readout_1l_kernel, (na + 63) / 64, 64, 0, r, rho, grho, mu, e_atom, NA, na, a0, want_grad);
+  GB_LAUNCH(readout_1l_kernel, (na + 63) / 64, 64, 0, r, rho, grho, mu, e_atom, NA, na, a0, want_grad, ilist);
 }
 
 __global__ void __launch_bounds__(64) readout_2l_kernel(ReadoutDev r, const float *__restrict__ rho_rows,
                                                         const float *__restrict__ I2, double *grho_rows, float *gI2,
                                                         const int *__restrict__ mu, double *e_atom, int NA, int na,
-                                                        int a0, int want_grad)
+                                                        int a0, int want_grad, const int *__restrict__ ilist)
 {
   const int a = blockIdx.x * blockDim.x + threadIdx.x;
   if (a >= na) return;
   const int nr = r.nrho;
-  e_atom[a0 + a] = readout_2l_atom(r, rho_rows + (size_t) (a0 + a) * nr, I2 + (size_t) a * nr, mu[a0 + a],
-                                   grho_rows + (size_t) (a0 + a) * nr, gI2 + (size_t) a * nr, want_grad, r.owned(a0 + a));
+  const size_t i = ilist ? (size_t) ilist[a0 + a] : (size_t) (a0 + a);    // the atom of chunk position a
+  e_atom[i] = readout_2l_atom(r, rho_rows + i * nr, I2 + (size_t) a * nr, mu[i], grho_rows + i * nr, gI2 + (size_t) a * nr,
+                              want_grad, r.owned((long long) i));
 }
 
 void launch_readout_2l(const ReadoutDev &r, const float *rho_rows, const float *I2, double *grho_rows, float *gI2,
-                       const int *mu, double *e_atom, int NA, int na, int a0, int want_grad)
+                       const int *mu, double *e_atom, int NA, int na, int a0, int want_grad, const int *ilist)
 {
   if (na == 0) return;
   GB_LAUNCH(readout_2l_kernel, (na + 63) / 64, 64, 0, r, rho_rows, I2, grho_rows, gI2, mu, e_atom, NA, na, a0,
-            want_grad);
+            want_grad, ilist);
+}
+
+// out[a] = v[list[a]]
+__global__ void __launch_bounds__(256) gather_int_kernel(const int *__restrict__ v, const int *__restrict__ list, int *out, long long n)
+{
+  const long long a = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+  if (a < n) out[a] = v[list[a]];
+}
+
+void launch_gather_int(const int *v, const int *list, int *out, long long n)
+{
+  if (n == 0) return;
+  GB_LAUNCH(gather_int_kernel, (unsigned) ((n + 255) / 256), 256, 0, v, list, out, n);
 }
 
 // ---- chunk tensor <-> per-atom rows ----------------------------------------------------------------------------
 template<class TR, bool TO_ROWS>
-__global__ void __launch_bounds__(256) rows_kernel(float *t, TR *rows, int nf, int C, int NA, int na, int a0)
+__global__ void __launch_bounds__(256) rows_kernel(float *t, TR *rows, int nf, int C, int NA, int na, int a0,
+                                                   const int *__restrict__ ilist)
 {
   const long long idx = (long long) blockIdx.x * blockDim.x + threadIdx.x;
   const long long total = (long long) na * nf * C;
@@ -579,31 +594,32 @@ __global__ void __launch_bounds__(256) rows_kernel(float *t, TR *rows, int nf, i
   const int f = (int) ((idx / C) % nf);
   const int a = (int) (idx / ((long long) C * nf));
   float *tp = t + ((size_t) f * NA + a) * C + c;
-  TR *rp = rows + ((size_t) (a0 + a) * nf + f) * C + c;
+  const size_t i = ilist ? (size_t) ilist[a0 + a] : (size_t) (a0 + a);    // the atom of chunk position a
+  TR *rp = rows + (i * nf + f) * C + c;
   if (TO_ROWS) *rp = (TR) *tp;
   else *tp = (float) *rp;
 }
 
-void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0)
+void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0, const int *ilist)
 {
   const long long total = (long long) na * nf * C;
   if (total == 0) return;
   GB_LAUNCH((rows_kernel<float, true>), (unsigned) ((total + 255) / 256), 256, 0, const_cast<float *>(t), rows, nf, C,
-            NA, na, a0);
+            NA, na, a0, ilist);
 }
-void launch_chunk_from_rows(float *t, const float *rows, int nf, int C, int NA, int na, int a0)
+void launch_chunk_from_rows(float *t, const float *rows, int nf, int C, int NA, int na, int a0, const int *ilist)
 {
   const long long total = (long long) na * nf * C;
   if (total == 0) return;
   GB_LAUNCH((rows_kernel<float, false>), (unsigned) ((total + 255) / 256), 256, 0, t, const_cast<float *>(rows), nf, C,
-            NA, na, a0);
+            NA, na, a0, ilist);
 }
-void launch_chunk_from_rows_f64(float *t, const double *rows, int nf, int C, int NA, int na, int a0)
+void launch_chunk_from_rows_f64(float *t, const double *rows, int nf, int C, int NA, int na, int a0, const int *ilist)
 {
   const long long total = (long long) na * nf * C;
   if (total == 0) return;
   GB_LAUNCH((rows_kernel<double, false>), (unsigned) ((total + 255) / 256), 256, 0, t, const_cast<double *>(rows), nf,
-            C, NA, na, a0);
+            C, NA, na, a0, ilist);
 }
 
 // ---- forces: gather of the bond forces of an atom and of their reverse bonds, no atomics ------------------------

@@ -749,12 +749,25 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
   cudaStream_t st = dev().stream;
   const ModelPlan &P = plan_;
   const long long per_atom = std::max(L1_.per_atom, L2_.per_atom);
+  // Atoms of a pass: positions lo .. hi of the list order, or - for a domain-decomposed caller - of the exact lists of
+  // the atoms each layer needs (position p then stands for atom ilist[p]); mu: the elements by position
+  struct Span {
+    int64_t lo, hi;
+    const int *ilist, *mu;
+  };
+  Span s0{R.lo0, R.hi0, nullptr, nl.mu_sorted()}, s1{R.lo1, R.hi1, nullptr, nl.mu_sorted()};
+  if (R.list0 && R.list1) {
+    launch_gather_int(nl.mu_sorted(), R.list0, mu_l0_.ensure((size_t) std::max<int64_t>(R.n0, 1)), R.n0);
+    launch_gather_int(nl.mu_sorted(), R.list1, mu_l1_.ensure((size_t) std::max<int64_t>(R.n1, 1)), R.n1);
+    s0 = Span{0, R.n0, R.list0, mu_l0_.get()};
+    s1 = Span{0, R.n1, R.list1, mu_l1_.get()};
+  }
   // GRACE-2L with forces: layer 1 gets tensors of its own for all of its atoms in one pass when they fit, so that its
   // reverse pass finds the forward tensors where they were left instead of evaluating the layer a second time
   float *base1 = nullptr;
   int NA1 = 0;
-  if (P.layers == 2 && !energy_only && keep_l1_ && R.hi1 > R.lo1) {
-    const int64_t w1 = (R.hi1 - R.lo1 + 3) / 4 * 4;
+  if (P.layers == 2 && !energy_only && keep_l1_ && s1.hi > s1.lo) {
+    const int64_t w1 = (s1.hi - s1.lo + 3) / 4 * 4;
     size_t free_b = 0, total_b = 0;
     const size_t need = (size_t) L1_.per_atom * (size_t) w1 * sizeof(float);
     if (w1 < ((int64_t) 1 << 30) && cudaMemGetInfo(&free_b, &total_b) == cudaSuccess &&
@@ -776,7 +789,9 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     bind_arena(L1_, base1 ? base1 : arena_.get(), base1 ? NA1 : NA);
     bind_arena(L2_, arena_.get(), NA);
   }
-  const BondsDev bonds = nl.bonds();
+  BondsDev bonds0 = nl.bonds(), bonds1 = nl.bonds();
+  bonds0.ilist = s0.ilist;
+  bonds1.ilist = s1.ilist;
   const int *mu = nl.mu_sorted();
   float *fv = fv_.get();
   auto zero_grads = [&](LayerEngine &E, float *base, int stride) {
@@ -791,19 +806,19 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
 
   if (P.layers == 1) {
     const LayerDev L = layer_dev(L1_);
-    for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
+    for (int64_t a0 = s0.lo; a0 < s0.hi; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, s0.hi - a0);
       if (tm) tm->begin(StageTimer::FWD);
-      launch_bond_fwd(P.lmax, bonds, L, T1(P.L1.tQ), NA, (int) a0, na);
-      run(L1_, P.L1.fwd, mu + a0, na, NA);
+      launch_bond_fwd(P.lmax, bonds0, L, T1(P.L1.tQ), NA, (int) a0, na);
+      run(L1_, P.L1.fwd, s0.mu + a0, na, NA);
       if (uq_now_) uq_last(L1_, mu, a0, na, NA, n);
-      launch_readout_1l(readout_, T1(P.t1_rho), T1(P.t1_grho), mu, e_atom_.get(), NA, na, (int) a0, !energy_only);
+      launch_readout_1l(readout_, T1(P.t1_rho), T1(P.t1_grho), mu, e_atom_.get(), NA, na, (int) a0, !energy_only, s0.ilist);
       if (tm) tm->end(StageTimer::FWD);
       if (energy_only) continue;
       if (tm) tm->begin(StageTimer::BWD);
       zero_grads(L1_, arena_.get(), NA);
-      run(L1_, P.L1.bwd, mu + a0, na, NA);
-      launch_bond_bwd(P.lmax, bonds, L, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0);
+      run(L1_, P.L1.bwd, s0.mu + a0, na, NA);
+      launch_bond_bwd(P.lmax, bonds0, L, T1(P.L1.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0);
       if (tm) tm->end(StageTimer::BWD);
     }
   } else {
@@ -823,31 +838,31 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
     Lb.gmsg_slot = gslots;
     // layer 1 forward of every chunk: messages I and rho of all atoms
     if (tm) tm->begin(StageTimer::FWD);
-    for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += step1) {
-      const int na = (int) std::min<int64_t>(step1, R.hi1 - a0);
-      { TagScope tg("layer1"); launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), S1, (int) a0, na); }
-      run(L1_, P.L1.fwd, mu + a0, na, S1);
+    for (int64_t a0 = s1.lo; a0 < s1.hi; a0 += step1) {
+      const int na = (int) std::min<int64_t>(step1, s1.hi - a0);
+      { TagScope tg("layer1"); launch_bond_fwd(P.lmax, bonds1, La, T1(P.L1.tQ), S1, (int) a0, na); }
+      run(L1_, P.L1.fwd, s1.mu + a0, na, S1);
       if (uq_now_) uq_layer1(mu + a0, a0, na, S1);
-      launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, S1, na, (int) a0);
-      launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, S1, na, (int) a0);
+      launch_rows_from_chunk(T1(P.t1_I), I_rows_.get(), nI, CR, S1, na, (int) a0, s1.ilist);
+      launch_rows_from_chunk(T1(P.t1_rho), rho_rows_.get(), 1, nrho, S1, na, (int) a0, s1.ilist);
     }
     if (tm) tm->end(StageTimer::FWD);
     call_hook(true);
     // layer 2 forward, energy and layer-2 reverse per chunk
-    for (int64_t a0 = R.lo0; a0 < R.hi0; a0 += NA) {
-      const int na = (int) std::min<int64_t>(NA, R.hi0 - a0);
+    for (int64_t a0 = s0.lo; a0 < s0.hi; a0 += NA) {
+      const int na = (int) std::min<int64_t>(NA, s0.hi - a0);
       if (tm) tm->begin(StageTimer::FWD);
-      { TagScope tg("layer2"); launch_bond_fwd(P.lmax, bonds, Lb, T2(P.L2.tQ), NA, (int) a0, na); }
-      run(L2_, P.L2.fwd, mu + a0, na, NA);
+      { TagScope tg("layer2"); launch_bond_fwd(P.lmax, bonds0, Lb, T2(P.L2.tQ), NA, (int) a0, na); }
+      run(L2_, P.L2.fwd, s0.mu + a0, na, NA);
       if (uq_now_) uq_last(L2_, mu, a0, na, NA, n);
       launch_readout_2l(readout_, rho_rows_.get(), T2(P.t2_I2), grho_rows_.get(), T2(P.t2_gI2), mu, e_atom_.get(), NA,
-                        na, (int) a0, !energy_only);
+                        na, (int) a0, !energy_only, s0.ilist);
       if (tm) tm->end(StageTimer::FWD);
       if (energy_only) continue;
       if (tm) tm->begin(StageTimer::BWD);
       zero_grads(L2_, arena_.get(), NA);
-      run(L2_, P.L2.bwd, mu + a0, na, NA);
-      { TagScope tg("layer2"); launch_bond_bwd(P.lmax, bonds, Lb, T2(P.L2.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0); }
+      run(L2_, P.L2.bwd, s0.mu + a0, na, NA);
+      { TagScope tg("layer2"); launch_bond_bwd(P.lmax, bonds0, Lb, T2(P.L2.tGQ), NA, (int) a0, na, fv, vir_atom_.get(), 0); }
       if (tm) tm->end(StageTimer::BWD);
     }
     // layer 1 again (recomputed) and its reverse, seeded with dE/dI and dE/drho of each atom
@@ -855,17 +870,17 @@ void Engine::evaluate_chunked(NeighborList &nl, bool energy_only, int NA, StageT
       if (tm) tm->begin(StageTimer::BWD);
       gather_message_gradients(nl, gslots, R);
       call_hook(false);
-      for (int64_t a0 = R.lo1; a0 < R.hi1; a0 += step1) {
-        const int na = (int) std::min<int64_t>(step1, R.hi1 - a0);
+      for (int64_t a0 = s1.lo; a0 < s1.hi; a0 += step1) {
+        const int na = (int) std::min<int64_t>(step1, s1.hi - a0);
         if (!base1) {    // the tensors of layer 1 were overwritten by layer 2: evaluate it again
-          launch_bond_fwd(P.lmax, bonds, La, T1(P.L1.tQ), S1, (int) a0, na);
-          run(L1_, P.L1.fwd, mu + a0, na, S1);
+          launch_bond_fwd(P.lmax, bonds1, La, T1(P.L1.tQ), S1, (int) a0, na);
+          run(L1_, P.L1.fwd, s1.mu + a0, na, S1);
         }
         zero_grads(L1_, abase1, S1);
-        launch_chunk_from_rows(T1(P.t1_gI), gI_rows_.get(), nI, CR, S1, na, (int) a0);
-        launch_chunk_from_rows_f64(T1(P.t1_grho), grho_rows_.get(), 1, nrho, S1, na, (int) a0);
-        run(L1_, P.L1.bwd, mu + a0, na, S1);
-        { TagScope tg("layer1"); launch_bond_bwd(P.lmax, bonds, La, T1(P.L1.tGQ), S1, (int) a0, na, fv, vir_atom_.get(), 1); }
+        launch_chunk_from_rows(T1(P.t1_gI), gI_rows_.get(), nI, CR, S1, na, (int) a0, s1.ilist);
+        launch_chunk_from_rows_f64(T1(P.t1_grho), grho_rows_.get(), 1, nrho, S1, na, (int) a0, s1.ilist);
+        run(L1_, P.L1.bwd, s1.mu + a0, na, S1);
+        { TagScope tg("layer1"); launch_bond_bwd(P.lmax, bonds1, La, T1(P.L1.tGQ), S1, (int) a0, na, fv, vir_atom_.get(), 1); }
       }
       if (tm) tm->end(StageTimer::BWD);
     }
@@ -948,7 +963,7 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
   // the UQ projection reads the chunk tensors of the per-operation path
   const bool fused_now = !uq_now_ && use_fused(n_eval);
   tc_now_ = !fused_now && use_tc(n_eval);
-  if (!fused_now) R.list0 = R.list1 = nullptr;    // the per-operation path evaluates the enclosing ranges
+  if (uq_now_) R.list0 = R.list1 = nullptr;    // the UQ arrays are indexed by list position: the enclosing ranges
   const bool partial = R.list0 ? (R.n0 < n || R.n1 < n) : (R.lo0 > 0 || R.hi0 < n || R.lo1 > 0 || R.hi1 < n);
   const int64_t widest = std::max<int64_t>(1, R.list0 ? std::max(R.n0, R.n1) : std::max(R.hi0 - R.lo0, R.hi1 - R.lo1));
   // atoms per pass, rounded up to a multiple of 4: it is the atom stride of the chunk tensors, whose rows the vector

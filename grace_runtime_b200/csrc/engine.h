@@ -121,6 +121,7 @@ class Engine {
   // UQ head: tables, per-atom results in list order, and (GRACE-2L) the layer-1 projection rows and squared norms
   DBuf<double> uq_cen_, uq_icov_, uq_thr_, uq_out_, uq_n2a_, uq_n2b_;
   DBuf<int> uq_ncl_;
+  DBuf<int> mu_l0_, mu_l1_;    // elements of the atoms of a domain-decomposed caller's exact lists, by list position
   DBuf<float> uq_z1_;
   UqDev uq_dev_{};
   bool uq_now_ = false;    // the evaluation in progress computes the UQ outputs

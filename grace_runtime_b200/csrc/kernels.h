@@ -96,11 +96,12 @@ struct ReadoutDev {
   __host__ __device__ bool owned(long long i) const { return perm == nullptr || perm[i] < nlocal; }
 };
 // GRACE-1L: E_i = (MLP(rho[1:]) + rho[0]) scale + shift, dE/drho
+// ilist (optional, here and below): chunk position a0 + a stands for atom ilist[a0 + a] instead of atom a0 + a
 void launch_readout_1l(const ReadoutDev &r, const float *rho, float *grho, const int *mu, double *e_atom, int NA,
-                       int na, int a0, int want_grad);
+                       int na, int a0, int want_grad, const int *ilist = nullptr);
 // GRACE-2L: rho from the per-atom rows, I2 of the chunk; dE/drho to the per-atom rows, dE/dI2 to the chunk
 void launch_readout_2l(const ReadoutDev &r, const float *rho_rows, const float *I2, double *grho_rows, float *gI2,
-                       const int *mu, double *e_atom, int NA, int na, int a0, int want_grad);
+                       const int *mu, double *e_atom, int NA, int na, int a0, int want_grad, const int *ilist = nullptr);
 
 // ---- UQ head (uq.cu) ----
 struct UqDev {
@@ -174,9 +175,11 @@ void launch_chain_fused(int TA, const FusedLayerDev &L, const FusedIO &io, int g
 void launch_chain_fused_g1(int TA, const FusedLayerDev &L, const FusedIO &io, int grid);    // one group per CTA
 
 // chunk tensor [nf][NA][C] <-> per-atom rows [n][nf][C] (message I, its gradient) and [n][C] (rho)
-void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0);
-void launch_chunk_from_rows(float *t, const float *rows, int nf, int C, int NA, int na, int a0);
-void launch_chunk_from_rows_f64(float *t, const double *rows, int nf, int C, int NA, int na, int a0);
+void launch_rows_from_chunk(const float *t, float *rows, int nf, int C, int NA, int na, int a0, const int *ilist = nullptr);
+void launch_chunk_from_rows(float *t, const float *rows, int nf, int C, int NA, int na, int a0, const int *ilist = nullptr);
+void launch_chunk_from_rows_f64(float *t, const double *rows, int nf, int C, int NA, int na, int a0, const int *ilist = nullptr);
+// out[a] = v[list[a]], a < n
+void launch_gather_int(const int *v, const int *list, int *out, long long n);
 
 // gmsg[j] = sum over the bonds e of atom j inside the cutoff of gslot[rev[slot of e]]: the shares the bonds i -> j stored,
 // added in the order of j's own list (bit-reproducible).  width = n_msg * C floats per row.  perm / nlocal (optional):
