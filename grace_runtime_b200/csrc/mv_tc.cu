@@ -102,9 +102,9 @@ template<> __device__ __forceinline__ void tmem_ld<16>(unsigned taddr, float (&v
   for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
-// position in the loop nest (unit = group of tiles x output row, item of the row, tile of the group)
+// position in the loop nest (round of tiles, output row, item of the row, tile of the round)
 struct Cursor {
-  int unit, tile0, nt, row, it, i0, i1, tt;
+  int tile0, nt, row, it, i0, i1, tt;
   bool valid;
 };
 
@@ -171,12 +171,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem = s_tmem;
-  // Work units: (group of TB consecutive atom tiles) x (output row), numbered group-major.  Every CTA takes an equal
-  // contiguous share of them, so the last round of tile groups leaves no CTA idle; within a share the rows of a group
-  // follow one another and alternate between the two accumulator sets.
-  const int ntiles = (na + TM - 1) / TM, ngroups = (ntiles + TB - 1) / TB;
-  const long long nunits = (long long) ngroups * op.nrows;
-  const int unit_begin = (int) (nunits * blockIdx.x / gridDim.x), unit_end = (int) (nunits * (blockIdx.x + 1) / gridDim.x);
+  const int ntiles = (na + TM - 1) / TM, per_round = gridDim.x * TB;
   volatile int *abort_flag = &s_abort;
 
   // bounded wait that also gives up when another role did
@@ -195,25 +190,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
       }
     }
   };
-  auto start = [&](Cursor &c, int unit) {
-    c.unit = unit;
-    c.valid = unit < unit_end;
+  auto start = [&](Cursor &c, int tile0, int row) {
+    c.tile0 = tile0;
+    c.row = row;
+    c.valid = tile0 < ntiles && row < op.nrows;
     if (!c.valid) return;
-    const int g = unit / op.nrows;
-    c.row = unit - g * op.nrows;
-    c.tile0 = g * TB;
-    c.nt = min(TB, ntiles - c.tile0);
-    c.i0 = c.it = s_item_off[c.row];
-    c.i1 = s_item_off[c.row + 1];
+    c.nt = min(TB, ntiles - tile0);
+    c.i0 = c.it = s_item_off[row];
+    c.i1 = s_item_off[row + 1];
     c.tt = 0;
   };
   auto advance = [&](Cursor &c) {
     if (++c.tt < c.nt) return;
     c.tt = 0;
     if (++c.it < c.i1) return;
-    start(c, c.unit + 1);
+    int row = c.row + gridDim.y, tile0 = c.tile0;
+    if (row >= op.nrows) {
+      row = blockIdx.y;
+      tile0 += per_round;
+    }
+    start(c, tile0, row);
   };
-  auto next_row = [&](Cursor &c) { start(c, c.unit + 1); };    // first fill of the unit after c's
+  auto next_row = [&](Cursor &c) {    // first fill of the row after c's
+    int row = c.row + gridDim.y, tile0 = c.tile0;
+    if (row >= op.nrows) {
+      row = blockIdx.y;
+      tile0 += per_round;
+    }
+    start(c, tile0, row);
+  };
 
   if (warp < NW) {
     // ---------------- producers ----------------
@@ -230,7 +235,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
       }
     };
     Cursor cur, nxt, nxt2;
-    start(cur, unit_begin);
+    start(cur, blockIdx.x * TB, blockIdx.y);
     TR regsA, regsB;
     if (cur.valid) load_tile(cur, regsA);
     nxt = cur;
@@ -298,7 +303,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
       step(regsB);
     }
 #ifdef GB_TC_TIMING
-    if (t == 0 && blockIdx.x == 1)
+    if (t == 0 && blockIdx.x == 1 && blockIdx.y == 0)
       printf("mv_tc K %d N %d S %d TB %d fills %d producer: wait-empty %lld W+convert %lld loads+arrive %lld other %lld\n", K, N, S, TB, fill,
              tp_[0], tp_[1], tp_[2], tp_[3]);
 #endif
@@ -307,7 +312,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
     if (lane == 0) {
       const unsigned idesc = make_idesc(N);
       Cursor cur;
-      start(cur, unit_begin);
+      start(cur, blockIdx.x * TB, blockIdx.y);
       int fill = 0, item_no = -1, rowc = 0;
       bool ok = true;
 #ifdef GB_TC_TIMING
@@ -342,7 +347,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s_empty[s])) : "memory");
         Cursor nx = cur;
         advance(nx);
-        if (!nx.valid || nx.unit != cur.unit) {    // the row is complete once these are done
+        if (!nx.valid || nx.row != cur.row || nx.tile0 != cur.tile0) {    // the row is complete once these are done
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&s_accfull[set])) : "memory");
           rowc++;
         }
@@ -351,7 +356,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
         GB_TICK(tm_, 2);
       }
 #ifdef GB_TC_TIMING
-      if (blockIdx.x == 1)
+      if (blockIdx.x == 1 && blockIdx.y == 0)
         printf("mv_tc K %d N %d issuer: wait-accempty %lld wait-full %lld issue %lld other %lld\n", K, N, tm_[0], tm_[1], tm_[2], tm_[3]);
 #endif
     }
@@ -364,7 +369,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
     constexpr int LPR = CB / 4, RPI = 32 / LPR;    // lanes per atom row, atom rows per store instruction
     const TensorDev dstT = s_T[op.dst];
     Cursor cur;
-    start(cur, unit_begin);
+    start(cur, blockIdx.x * TB, blockIdx.y);
     int rowc = 0;
     bool ok = true;
 #ifdef GB_TC_TIMING
@@ -424,7 +429,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) mv_tc_kernel(MVTCDev op, const Te
       GB_TICK(te_, 1);
     }
 #ifdef GB_TC_TIMING
-    if (warp == NW + 1 && lane == 0 && blockIdx.x == 1)
+    if (warp == NW + 1 && lane == 0 && blockIdx.x == 1 && blockIdx.y == 0)
       printf("mv_tc K %d N %d epilogue: wait-accfull %lld work %lld rows %d\n", K, N, te_[0], te_[1], rowc);
 #endif
   }
@@ -544,13 +549,14 @@ void MVTensorCore::launch(const MVDev &d, const TensorDev *tensors, int ntensors
   op.nitems = nitems_;
   op.accumulate = d.accumulate;
   op.dst = d.dst;
-  // one CTA per SM; two sets of accumulators share the 512 tensor-memory columns.  The CTAs share the (tile group, output
-  // row) units evenly, so the groups are as large as tensor memory allows (fewest weight images staged)
+  // one CTA per SM; two sets of accumulators share the 512 tensor-memory columns
   const int ntiles = (na + TM - 1) / TM, G = dev().sm_count;
   const int tb_max = std::max(1, std::min(MAX_TILES, TMEM_COLS / 2 / d.n_out));
-  const int TB = std::min(tb_max, ntiles);
-  const long long nunits = (long long) ((ntiles + TB - 1) / TB) * d.nrows;
-  const dim3 grid((unsigned) std::min<long long>(G, nunits));
+  const int rounds = (ntiles + G * tb_max - 1) / (G * tb_max);
+  const int TB = std::max(1, std::min(tb_max, (ntiles + G * rounds - 1) / (G * rounds)));
+  const int gx = std::min(G, (ntiles + TB - 1) / TB);
+  const int gy = std::max(1, std::min(d.nrows, G / gx));
+  const dim3 grid(gx, gy);
   switch (K_) {
     case 8: launch_k<8>(op, tensors, ntensors, NA, na, TB, grid, error); break;
     case 16: launch_k<16>(op, tensors, ntensors, NA, na, TB, grid, error); break;
