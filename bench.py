@@ -42,6 +42,9 @@ WORKLOADS = {
     "grace2l_128k_fcc_alloy": dict(cfg="2l", lattice="fcc", a=3.6, reps=(20, 40, 40), nsp=3, sigma=0.08, full=True),
     # 4096 small periodic structures (16-256 atoms, triclinic, 0.06-0.09 atoms/A^3) through the Batch entry points
     "grace2l_batch4096": dict(cfg="2l", batch=4096, unique=128, nmin=16, nmax=256, nsp=89, full=True),
+    # GRACE-3L (lmax 4, 64 channels, 89 elements) on a 500,094-atom 5-component bcc alloy: reference arm only, the
+    # library does not evaluate GRACE-3L
+    "grace3l_500k_bcc_hea": dict(cfg="3l", lattice="bcc", a=3.2, reps=(63, 63, 63), nsp=5, sigma=0.05, full=True),
 }
 DEFAULT = "grace2l_1m_fcc_alloy"      # the 1,024,000-atom GRACE-2L configuration the target is stated on
 ALSO = "grace1l_128k_bcc_alloy"       # reported beside it at one GPU (`also`)
@@ -51,7 +54,13 @@ def make_workload(name, tmp, reps=None):
     w = WORKLOADS[name]
     species = modelgen._subset(2024, w["nsp"]) if w["full"] else ["W"]
     elements = modelgen.ELEMENTS if w["full"] else species
-    path = modelgen.write_config_model(os.path.join(tmp, f"{name}.npz"), w["cfg"], elements, seed=0)
+    if w["cfg"] == "3l":
+        from grace_runtime_b200 import modelgen3l
+        path = modelgen3l.write_model_3l(os.path.join(tmp, f"{name}.npz"), elements=elements, lmax=4, channels=(64, 64, 64),
+                                         rho_width=32, embedding=16, radial_hidden=128, energy_hidden=64, rcut=6.0,
+                                         avg_neigh=58.0, seed=0)
+    else:
+        path = modelgen.write_config_model(os.path.join(tmp, f"{name}.npz"), w["cfg"], elements, seed=0)
     types, pos, cell, pbc = structures.crystal(w["lattice"], w["a"], reps or w["reps"], n_species=w["nsp"],
                                                sigma=w["sigma"], seed=1)
     return path, species, types, pos, cell, pbc
@@ -261,7 +270,7 @@ def base_config(workload, world):
         return {"workload": workload, "structures": int(wl["batch"]), "model": "GRACE-2L", "elements_in_model": 89,
                 "atoms_per_structure": [int(wl["nmin"]), int(wl["nmax"])], "parallelism": f"structures over {world} rank(s)"}
     n = int(np.prod(wl["reps"])) * (2 if wl["lattice"] == "bcc" else 4)
-    return {"workload": workload, "atoms": n, "model": "GRACE-1L" if wl["cfg"] == "1l" else "GRACE-2L",
+    return {"workload": workload, "atoms": n, "model": {"1l": "GRACE-1L", "2l": "GRACE-2L", "3l": "GRACE-3L"}[wl["cfg"]],
             "elements_in_model": 89 if wl["full"] else 1, "species_in_structure": int(wl["nsp"]),
             "lattice": wl["lattice"], "lattice_constant_A": wl["a"], "cells": list(wl["reps"]),
             "displacement_sigma_A": wl["sigma"], "cutoff_A": 6.0, "skin_A": 0.5,
@@ -276,6 +285,8 @@ def sample_reps(wl):
     n = int(np.prod(wl["reps"])) * (2 if wl["lattice"] == "bcc" else 4)
     if n <= 40000:
         return None
+    if wl["cfg"] == "3l":
+        return (12, 12, 12)      # 3,456 atoms: a GRACE-3L step on the CPU is two orders of magnitude above GRACE-1L
     return (20, 20, 40) if wl["lattice"] == "bcc" else (16, 16, 32)
 
 
@@ -740,6 +751,11 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif WORKLOADS[args.workload]["cfg"] == "3l":
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "unit": UNIT, "config": base_config(args.workload, world),
+                              "unavailable": "GRACE-3L evaluation is not built in this library; --impl reference times the "
+                                             "reference's CPU engine on this workload"}))
     elif "batch" in WORKLOADS[args.workload]:
         run_batch(args, rank, world, local_rank)
     else:

@@ -1,5 +1,7 @@
 #include "model.h"
 
+#include "model3l.h"
+
 #include <algorithm>
 #include <cmath>
 
@@ -500,7 +502,11 @@ GraceModel GraceModel::load(const std::string &path)
   m.layers = model_layers_of_file(z);
   if (m.layers == 1) load_1l(z, m);
   else if (m.layers == 2) load_2l(z, m);
-  else throw ModelError("GRACE-3L models are not supported by this backend yet");
+  else {
+    // the file is read and checked like the other kinds, so that a malformed export fails with the array's name
+    const Grace3LModel m3 = Grace3LModel::load(z);
+    throw ModelError(m3.summary() + ": the file is a valid GRACE-3L model, but this backend evaluates GRACE-1L and GRACE-2L only");
+  }
   load_uq(z, m);
   return m;
 }
