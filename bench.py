@@ -66,6 +66,21 @@ def make_workload(name, tmp, reps=None):
     return path, species, types, pos, cell, pbc
 
 
+def make_batch(wl, count):
+    """The first `count` structures of a batch workload: `unique` generated structures (rejection sampling is slow),
+    repeated with rigid shifts."""
+    un, ut, up, uc, upbc = structures.random_batch(wl["unique"], wl["nmin"], wl["nmax"], wl["nsp"], seed=1)
+    rng = np.random.default_rng(2)
+    start = np.concatenate([[0], np.cumsum(un)])
+    natoms, T, P, Cc = [], [], [], []
+    for s in range(count):
+        u = s % wl["unique"]
+        sl = slice(start[u], start[u + 1])
+        natoms.append(un[u]); T.append(ut[sl]); Cc.append(uc[u])
+        P.append(up[sl] + rng.random(3) @ uc[u])
+    return np.array(natoms, dtype=np.int32), T, P, Cc
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons during the timed region."""
 
@@ -171,17 +186,7 @@ def run_batch(args, rank, world, local_rank):
     tmp = tempfile.mkdtemp(prefix="grace_bench_")
     species = list(modelgen.ELEMENTS)
     path = modelgen.write_config_model(os.path.join(tmp, "batch.npz"), wl["cfg"], modelgen.ELEMENTS, seed=0)
-    # `unique` generated structures (rejection sampling is slow), repeated with rigid shifts to the full batch
-    un, ut, up, uc, upbc = structures.random_batch(wl["unique"], wl["nmin"], wl["nmax"], wl["nsp"], seed=1)
-    rng = np.random.default_rng(2)
-    start = np.concatenate([[0], np.cumsum(un)])
-    natoms, T, P, Cc = [], [], [], []
-    for s in range(wl["batch"]):
-        u = s % wl["unique"]
-        sl = slice(start[u], start[u + 1])
-        natoms.append(un[u]); T.append(ut[sl]); Cc.append(uc[u])
-        P.append(up[sl] + rng.random(3) @ uc[u])
-    natoms = np.array(natoms, dtype=np.int32)
+    natoms, T, P, Cc = make_batch(wl, wl["batch"])
     n_total = int(natoms.sum())
     # this rank's structures: greedy by atom count
     order = np.argsort(-natoms, kind="stable")
@@ -692,7 +697,7 @@ def run_reference(args, rank, world):
     tmp = tempfile.mkdtemp(prefix="grace_bench_ref_")
     wl = WORKLOADS[args.workload]
     if "batch" in wl:
-        print(json.dumps({"impl": "reference", "unavailable": "the reference arm times single structures; not wired for the batch workload"}))
+        run_reference_batch(args, wl, world, tmp)
         return
     reps = sample_reps(wl) or wl["reps"]
     path, species, types, pos, cell, pbc = make_workload(args.workload, tmp, reps)
@@ -731,6 +736,47 @@ def run_reference(args, rank, world):
            "sample_atoms": int(n),
            "cpu_baseline": {"value": value, "unit": "us/atom", "cores": cores, "kind": kind, "sample": sample,
                             "neighbor_search_us_per_atom": nl_us},
+           "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(out))
+
+
+def run_reference_batch(args, wl, world, tmp):
+    """The batch workload on the reference's CPU drivers: a step evaluates the first 64 structures of the batch one after
+    the other (each with all host threads), neighbour search included, as a Batch call rebuilds its lists every step."""
+    from oracle import refcpu
+    if not refcpu.available():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref (the compiled reference) is not built on this box"}))
+        return
+    cores = len(os.sched_getaffinity(0))
+    path = modelgen.write_config_model(os.path.join(tmp, "batch.npz"), wl["cfg"], modelgen.ELEMENTS, seed=0)
+    count = 64
+    natoms, T, P, Cc = make_batch(wl, count)
+    n = int(natoms.sum())
+    rm = refcpu.RefModel(path, list(modelgen.ELEMENTS))
+    pbc = [1, 1, 1]
+
+    def step():
+        ev = nl = 0.0
+        for k in range(count):
+            r = rm.compute(T[k], P[k], Cc[k], pbc, nthreads=cores)
+            ev += r["seconds_best"]
+            nl += r["seconds_nlist"]
+        return ev, nl
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    t = [step() for _ in range(args.steps)]
+    ev, nl = float(np.mean([a for a, _ in t])), float(np.mean([b for _, b in t]))
+    ms = (ev + nl) * 1e3
+    value = ms * 1e3 / n
+    sample = (f"the first {count} structures of the batch ({n} atoms) per step, one call of the reference's CPU driver per "
+              "structure, neighbour search included")
+    out = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+           "dtype": "f32", "data": "synthetic", "config": base_config(args.workload, world), "sample_atoms": n,
+           "structures_per_s": count / (ms * 1e-3),
+           "cpu_baseline": {"value": value, "unit": "us/atom", "cores": cores, "kind": "reference", "sample": sample,
+                            "neighbor_search_us_per_atom": nl * 1e6 / n},
            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(out))
 
