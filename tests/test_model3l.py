@@ -172,3 +172,22 @@ def test_malformed_files_name_the_array(small3l, tmp_path, case):
         with pytest.raises(RuntimeError) as e:
             refcpu.RefModel(bad, ["Al", "Ni"])
         assert key in str(e.value), str(e.value)
+
+
+def test_numpy_restatement_matches_compiled_reference(small3l):
+    """oracle/grace3l_oracle.py (forward pass, fp64) against the reference's CPU engine: periodic cell and open cluster."""
+    from oracle import refcpu
+    from oracle.grace3l_oracle import Grace3LOracle
+    if not refcpu.available():
+        pytest.skip("oracle/_ref is not built")
+    rng = np.random.default_rng(1)
+    a = 4.0
+    base = np.array([[0, 0, 0], [.5, .5, 0], [.5, 0, .5], [0, .5, .5]]) * a
+    pos = np.concatenate([base + np.array([i, j, 0]) * a for i in range(2) for j in range(2)])
+    pos += 0.1 * rng.standard_normal(pos.shape)
+    types = rng.integers(1, 3, len(pos)).astype(np.int32)
+    ref, orc = refcpu.RefModel(small3l, ["Al", "Ni"]), Grace3LOracle(small3l)
+    for cell, pbc, x in ((np.diag([2 * a, 2 * a, a]), [1, 1, 1], pos), (np.eye(3) * 50.0, [0, 0, 0], pos + 20.0)):
+        r, o = ref.compute(types, x, cell, pbc), orc.compute(["Al", "Ni"], types, x, cell, pbc)
+        assert np.abs(r["energies"] - o["energies"]).max() < 2e-6
+        assert abs(r["energy"] - o["energy"]) / len(x) < 2e-7
