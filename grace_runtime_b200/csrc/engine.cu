@@ -195,6 +195,7 @@ void Engine::setup_layer(LayerEngine &E, const LayerPlan &P)
 
 Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n > 0 ? spline_n : 1024))
 {
+  if (spline_n == 0 && m.layers == 3) throw Unsupported("GRACE-3L: the exact radial MLP (spline 0) is not supported");
   if (spline_n == 0) {    // exact radial MLP (what the reference's generic engine evaluates), tensor-core kernel
     exact_ = true;
     rad1_.setup(m, m.rad1, m.chain1.c0);
@@ -220,6 +221,15 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   rcsq_.upload(P.rcsq);
   std::vector<float> rcf(P.rc.begin(), P.rc.end());
   rcf_.upload(rcf);
+  if (P.layers == 3) {    // its own set-up and drivers (engine3l.cu); none of the GRACE-1L / 2L paths below applies
+    if (exact_) throw Unsupported("GRACE-3L: the exact radial MLP (spline 0) is not supported");
+    shift_.upload(P.shift);
+    tc_error_.set_label("engine:flag");
+    tc_error_.ensure(1);
+    GB_CUDA(cudaMemsetAsync(tc_error_.get(), 0, sizeof(int), dev().stream));
+    setup_3l();
+    return;
+  }
   eW_.upload(P.eW);
   {    // transposed copies of the energy MLP layers for the reverse pass of the warp readout
     std::vector<double> wt(P.eW.size());
@@ -289,6 +299,10 @@ Engine::~Engine() = default;
 
 void Engine::dense_stats(double *o) const
 {
+  if (plan_.layers == 3) {
+    for (int q = 0; q < 6; q++) o[q] = 0.0;
+    return;
+  }
   for (int k = 0; k < 6; k++) o[k] = 0.0;
   for (const LayerEngine *E : {&L1_, &L2_}) {
     if (!E->plan) continue;
@@ -338,6 +352,7 @@ double Engine::per_atom_bytes(int64_t n_eval) const
 
 int Engine::auto_chunk(int64_t n) const
 {
+  if (plan_.layers == 3) return (int) std::max<int64_t>(n, 1);    // one pass
   size_t free_b = 0, total_b = 0;
   if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) free_b = (size_t) 8 << 30;
   const double budget = 0.35 * (double) free_b + 4.0 * (double) arena_.capacity();
@@ -947,6 +962,15 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
     if (out.virial && !energy_only) GB_CUDA(cudaMemsetAsync(out.virial, 0, sizeof(double) * 6 * nsys, st));
     return;
   }
+  if (plan_.layers == 3) {
+    if (R.nlocal >= 0) throw Unsupported("GRACE-3L: domain-decomposed callers are not supported");
+    if (out.gamma) throw InvalidArgument("the model has no usable UQ head");
+    e_atom_.ensure(n);
+    if (!energy_only) vir_atom_.ensure(6 * n);
+    evaluate_3l(nl, energy_only, tm);
+    write_outputs(nl, energy_only, out);
+    return;
+  }
   const int64_t n_eval = R.list0 ? std::max(R.n0, R.n1) : std::max(R.hi0 - R.lo0, R.hi1 - R.lo1);
   uq_now_ = out.gamma != nullptr;
   if (uq_now_) {
@@ -1017,8 +1041,15 @@ void Engine::evaluate(NeighborList &nl, bool energy_only, const OutputsDev &out,
     rad1_.check();
     if (plan_.layers == 2) rad2_.check();
   }
+  write_outputs(nl, energy_only, out);
+}
+
+// sums and gathers that leave the engine
+void Engine::write_outputs(NeighborList &nl, bool energy_only, const OutputsDev &out)
+{
+  const int64_t n = nl.n();
+  const int nsys = nl.nsys();
   float *fv = fv_.get();
-  // sums and gathers that leave the engine
   // one or a few large structures: partial sums by 64 blocks per structure and component
   const int nb = (nsys <= 8 && n > 16384) ? 64 : 1;
   double *scr = nb > 1 ? sum_scratch_.ensure((size_t) nsys * 6 * nb) : nullptr;
@@ -1110,6 +1141,7 @@ SystemObj::SystemObj(std::shared_ptr<ModelObj> m, const std::vector<std::string>
   if (!(skin >= 0.0) || !std::isfinite(skin)) throw InvalidArgument("skin must be >= 0");
   t2m_ = species_to_elements(model_->model, species);
   engine_ = model_->get_engine(model_->effective_spline(spline));
+  engine_->prepare_species(t2m_);
   cutoff_ = 0.0;
   for (int a : t2m_)
     for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));
@@ -1287,7 +1319,9 @@ EngineRunObj::EngineRunObj(std::shared_ptr<ModelObj> m, const std::vector<std::s
 {
   require_initialized();
   t2m_ = species_to_elements(model_->model, species);
+  if (model_->model.layers == 3) throw Unsupported("GRACE-3L: the engine interface for callers with their own neighbour lists is not supported");
   engine_ = model_->get_engine(model_->effective_spline(spline));
+  engine_->prepare_species(t2m_);
   cutoff_ = 0.0;
   for (int a : t2m_)
     for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));
@@ -1356,6 +1390,7 @@ BatchObj::BatchObj(std::shared_ptr<ModelObj> m, const std::vector<std::string> &
   require_initialized();
   t2m_ = species_to_elements(model_->model, species);
   engine_ = model_->get_engine(model_->effective_spline(spline));
+  engine_->prepare_species(t2m_);
   cutoff_ = 0.0;
   for (int a : t2m_)
     for (int b : t2m_) cutoff_ = std::max(cutoff_, model_->model.pair_cutoff(a, b));

@@ -19,6 +19,8 @@
 
 namespace gb {
 
+struct State3L;    // device state of a GRACE-3L model (engine3l.cu)
+
 struct LayerEngine {
   const LayerPlan *plan = nullptr;
   DBuf<float> tab, z;
@@ -102,6 +104,8 @@ class Engine {
   // bond-force slots [3 * nslots] the list zeroes for bonds outside the cutoff (grown here)
   float *bond_forces(int64_t nslots) { return fv_.ensure(3 * (size_t) std::max<int64_t>(nslots, 1)); }
   const double *rcsq() const { return rcsq_.get(); }
+  // GRACE-3L: builds the radial tables of every pair of these model elements (the species of a System or Batch) once
+  void prepare_species(const std::vector<int> &elements);
   int auto_chunk(int64_t n) const;
   void release_work();
   double per_atom_bytes(int64_t n_eval) const;
@@ -162,6 +166,11 @@ class Engine {
   const float *arena1_bound_ = nullptr;
   int arena1_NA_ = 0;
   LayerDev layer_dev(const LayerEngine &E) const;
+  // GRACE-3L (engine3l.cu)
+  std::shared_ptr<State3L> s3_;
+  void setup_3l();
+  void evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm);
+  void write_outputs(NeighborList &nl, bool energy_only, const OutputsDev &out);
 };
 
 struct ModelObj {

@@ -1,7 +1,5 @@
 #include "model.h"
 
-#include "model3l.h"
-
 #include <algorithm>
 #include <cmath>
 
@@ -503,9 +501,23 @@ GraceModel GraceModel::load(const std::string &path)
   if (m.layers == 1) load_1l(z, m);
   else if (m.layers == 2) load_2l(z, m);
   else {
-    // the file is read and checked like the other kinds, so that a malformed export fails with the array's name
-    const Grace3LModel m3 = Grace3LModel::load(z);
-    throw ModelError(m3.summary() + ": the file is a valid GRACE-3L model, but this backend evaluates GRACE-1L and GRACE-2L only");
+    // the whole model lives in m3; the common fields are what Systems, Batches and the neighbour list read
+    m.m3 = std::make_shared<Grace3LModel>(Grace3LModel::load(z));
+    const Grace3LModel &t = *m.m3;
+    m.n_elements = t.n_elements;
+    m.embedding = t.embedding_size;
+    m.lmax = t.lmax;
+    m.nradbase = t.nradbase;
+    m.p = t.radial_basis_p;
+    m.rcut = t.rcut;
+    m.bond_specific = t.has_bond_specific_cutoff;
+    m.bond_cutoff = t.bond_cutoff_map;
+    m.element_names = t.element_names;
+    m.chem = t.chem_embedding;
+    m.output_scale = t.output_scale;
+    m.shift = t.shift_values;
+    if (z.has("uq_schema_version")) throw ModelError("GRACE-3L: the UQ head of GRACE-3L models is not supported");
+    return m;
   }
   load_uq(z, m);
   return m;

@@ -4,8 +4,10 @@
 // fourth-order stage here (the reference adds a dead one, libgrace/src/max_order3.h:122-134, with identical results).
 #pragma once
 
+#include "model3l.h"
 #include "npz.h"
 
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -116,6 +118,9 @@ struct GraceModel {
   Chain chain2;
   bool rms = true;
   std::vector<double> lnI, ln0;
+
+  // GRACE-3L: the whole model (the fields above hold only what Systems and the neighbour list read)
+  std::shared_ptr<Grace3LModel> m3;
 
   double pair_cutoff(int mu_i, int mu_j) const
   {

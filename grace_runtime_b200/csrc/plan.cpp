@@ -4,6 +4,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <map>
+#include <memory>
 
 namespace gb {
 
@@ -638,10 +639,375 @@ void build_units(MVOp &o)
 
 }    // namespace
 
+// ---- GRACE-3L ----------------------------------------------------------------------------------------------------
+namespace {
+
+// the dense chain of layer k as MV / PROD operations with their adjoints
+void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Plan &L)
+{
+  const std::string K = "A" + std::to_string(k + 1), ks = std::to_string(k + 1);
+  const Grace3LModel::Spbf &sp = m.spbf[k];
+  const int nl = m.lmax + 1, nlm = nl * nl, C = sp.n_rad_max;
+  L.C = C;
+  L.lt = sp.l_tile;
+  auto find = [](const auto &v, const std::string &name) -> const auto & {
+    for (const auto &c : v)
+      if (c.name == name) return c;
+    throw ModelError("GRACE-3L: component " + name + " is missing");
+  };
+  LayerBuilder B{L.dense, gm, {}};
+  std::map<std::string, std::pair<int, int>> T;    // component -> (tensor, gradient)
+  auto tensors = [&](const std::string &name, int nf, int ch) {
+    const int t = B.tensor(name, nf, ch), g = B.tensor("g" + name, nf, ch, true);
+    T[name] = {t, g};
+    return std::make_pair(t, g);
+  };
+  // keep the reduce weights alive until the plan is finished (the builder reads them through pointers)
+  std::vector<std::unique_ptr<ReduceWeights>> keep;
+  auto reduce = [&](const std::string &name, const std::string &out_name, bool external) {
+    const Grace3LModel::Reduce &r = find(m.reduce, name);
+    const int nfo = r.only_invar ? 1 : r.n_funcs;
+    double scale = 1.0;
+    if (r.has_norm_map) {
+      scale = r.norm_map[0];
+      for (double v : r.norm_map)
+        if (v != scale) throw ModelError("GRACE-3L: reduce " + name + " scales its output functions differently (norm_map)");
+    }
+    const auto out = tensors(out_name, nfo, r.n_out);
+    if (external) L.dense.tensors[out.first].external = L.dense.tensors[out.second].external = true;
+    ReduceGroup G;
+    G.name = name;
+    G.n_out = r.n_out;
+    G.nfo = nfo;
+    G.elem = r.elem_dep;
+    G.t_out = out.first;
+    G.t_gout = out.second;
+    for (const auto &in : r.instr) {
+      auto w = std::make_unique<ReduceWeights>();
+      w->present = true;
+      w->W = in.W;
+      w->norm = in.norm * scale;
+      w->n_in = in.n_in;
+      w->w_shape = in.w_shape;
+      w->n_out = r.n_out;
+      w->elem = r.elem_dep;
+      w->collect = in.collect_ind;
+      w->tile = in.w_l_tile;
+      w->fo = in.total_sum_ind;
+      if (r.only_invar) w->fo.assign(in.collect_ind.size(), 0);
+      G.src.push_back(w.get());
+      G.src_tensor.push_back(T.at(in.name).first);
+      G.src_grad.push_back(T.at(in.name).second);
+      G.src_row0.push_back(0);
+      keep.push_back(std::move(w));
+    }
+    B.reduce(G);
+    return out;
+  };
+  // projection of the functions of `src` by the matrix of their group: out[w] = norm M[group[w]] src[w]
+  auto project = [&](const std::string &name, const std::string &src, const std::vector<double> &M, double norm,
+                     const std::vector<int> &group, int ngroups, int rank, int n_in) {
+    const int nf = (int) group.size();
+    const auto out = tensors(name, nf, rank);
+    auto w = std::make_unique<ReduceWeights>();
+    w->present = true;
+    w->W.assign((size_t) rank * n_in * ngroups, 0.0);    // [rank][n_in][group] from [group][rank][n_in]
+    for (int g = 0; g < ngroups; g++)
+      for (int r = 0; r < rank; r++)
+        for (int n = 0; n < n_in; n++) w->W[((size_t) r * n_in + n) * ngroups + g] = M[((size_t) g * rank + r) * n_in + n];
+    w->norm = norm;
+    w->n_in = n_in;
+    w->w_shape = ngroups;
+    w->n_out = rank;
+    w->tile = group;
+    for (int f = 0; f < nf; f++) {
+      w->collect.push_back(f);
+      w->fo.push_back(f);
+    }
+    ReduceGroup G;
+    G.name = name;
+    G.n_out = rank;
+    G.nfo = nf;
+    G.t_out = out.first;
+    G.t_gout = out.second;
+    G.src.push_back(w.get());
+    G.src_tensor.push_back(T.at(src).first);
+    G.src_grad.push_back(T.at(src).second);
+    G.src_row0.push_back(0);
+    keep.push_back(std::move(w));
+    B.reduce(G);
+  };
+  auto product = [&](const std::string &name, const std::string &left, const std::string &right) {
+    const Grace3LModel::Cpl &c = find(m.prod, name);
+    project(name + "_lp", left, c.U, c.norm_u, c.group_left, c.n_groups_left, c.rank, c.n_left);
+    project(name + "_rp", right, c.V, c.norm_v, c.group_right, c.n_groups_right, c.rank, c.n_right);
+    const auto out = tensors(name, c.nfunc, c.rank);
+    CGProduct p;
+    p.present = true;
+    p.left = c.left_ind;
+    p.right = c.right_ind;
+    p.m_sum = c.m_sum_ind;
+    p.cg = c.cg;
+    p.n_out = c.nfunc;
+    const std::vector<char> need(c.nfunc, 1);
+    B.prod(name, p, need, T.at(name + "_lp").first, T.at(name + "_rp").first, out.first, T.at(name + "_lp").second,
+           T.at(name + "_rp").second, out.second);
+  };
+  // out = nof (left + W right): the left input passes through an identity
+  auto dense = [&](const std::string &name, const std::string &left, const std::string &right) {
+    const Grace3LModel::Fc &f = find(m.fc, name);
+    if (f.left_coefs) throw ModelError("GRACE-3L: FC " + name + " with weights on its left input");
+    FCWeights w;
+    w.present = true;
+    w.n_out = f.n_out;
+    w.n_in_left = f.n_out;
+    w.n_in_right = f.n_in_right;
+    w.tiles_left = 1;
+    w.tiles_right = f.w_shape_right;
+    w.n_funcs = f.n_funcs_left;
+    w.w_left.assign((size_t) f.n_out * f.n_out, 0.0);
+    for (int q = 0; q < f.n_out; q++) w.w_left[(size_t) q * f.n_out + q] = 1.0;
+    w.w_right = f.w_right;
+    w.norm_right = f.norm_right;
+    w.tile_left.assign(f.n_funcs_left, 0);
+    w.tile_right = f.w_tile_right;
+    w.collect_to = f.collect_to;
+    w.collect_from = f.collect_from;
+    w.nof = f.norm_out_factor;
+    const auto out = tensors(name, f.n_funcs_left, f.n_out);
+    const std::vector<char> live(f.n_funcs_left, 1);
+    B.fc(name, w, live, T.at(left).first, T.at(right).first, out.first, T.at(left).second, T.at(right).second, out.second);
+  };
+
+  std::string X = K;
+  if (!sp.equivariant) {
+    L.nfA = nlm;
+    L.nlmi = 1;
+  } else {
+    L.nfA = sp.nfunc;
+    L.nlmi = sp.n_lm_ind;
+  }
+  const auto A = tensors(K, L.nfA, C);
+  L.tA = A.first;
+  L.tGA = A.second;
+  L.dense.tensors[L.tA].external = L.dense.tensors[L.tGA].external = true;
+  if (sp.equivariant) {
+    reduce(K + "_red", K + "_red", false);
+    X = K + "_red";
+  }
+  product(K + "_2", X, X);
+  reduce(K + "_2_red", K + "_2_red", false);
+  dense(K + "_2a", K + "_2_red", X);
+  product(K + "_3", K + "_2a", X);
+  reduce(K + "_3_red", K + "_3_red", false);
+  dense(K + "_2b", K + "_2_red", X);
+  product(K + "_4", K + "_2b", K + "_2b");
+  reduce(K + "_4_red", K + "_4_red", false);
+  if (k < 2) {
+    const auto eq = reduce("eq" + ks, "eq" + ks, true);
+    L.tEQ = eq.first;
+    L.tGEQ = eq.second;
+    const Grace3LModel::EqNorm &e = find(m.eqnorm, "eq" + ks + "_norm");
+    L.nfEQ = e.M;
+    L.cEQ = e.n_out;
+    L.eq_dw.assign(e.degree_weights.begin(), e.degree_weights.end());
+    L.eq_mask.assign(e.l0_mask.begin(), e.l0_mask.end());
+    L.eq_aff.assign(e.affine_weight.begin(), e.affine_weight.end());
+    L.eq_e = e.expand_index;
+    L.eq_eps = e.eps;
+    L.eq_center = e.center_l0;
+  }
+  const auto rho = reduce("rho" + ks, "rho" + ks, true);
+  L.tRHO = rho.first;
+  L.tGRHO = rho.second;
+  const Grace3LModel::RmsNorm &rn = find(m.rmsnorm, "rho" + ks + "_norm");
+  L.wr = rn.n_out;
+  L.rho_n0 = rn.type;
+  L.rho_scale.assign(rn.scale.begin(), rn.scale.end());
+  if (L.dense.tensors[L.tRHO].nfuncs != 1) throw ModelError("GRACE-3L: rho" + ks + " must be an invariant reduce");
+  B.finish();
+  compact_rows(L.dense);
+  check_gradient_writers(L.dense);
+  for (MVOp &o : L.dense.mv) build_units(o);
+  L.dense.C = C;
+
+  // the couple of the bond sums: by output function and by pair
+  const int np = nlm * L.nlmi;
+  L.cg_off.assign(L.nfA + 1, 0);
+  L.cgt_off.assign(np + 1, 0);
+  if (!sp.equivariant) {
+    for (int f = 0; f < nlm; f++) {
+      L.cg_off[f + 1] = L.cgt_off[f + 1] = f + 1;
+      L.cg_p.push_back(f);
+      L.cgt_f.push_back(f);
+      L.cg_v.push_back(1.0f);
+      L.cgt_v.push_back(1.0f);
+    }
+    L.l0mask.assign(1, 1.0f);
+    L.zproj.assign((size_t) m.n_elements * C, 1.0f);
+  } else {
+    std::vector<std::vector<std::pair<int, float>>> by_f(L.nfA), by_q(np);
+    for (int q = 0; q < np; q++)
+      for (int f = 0; f < L.nfA; f++) {
+        const double v = sp.cg_W[(size_t) q * L.nfA + f];
+        if (v != 0.0) {
+          by_f[f].push_back({q, (float) v});
+          by_q[q].push_back({f, (float) v});
+        }
+      }
+    for (int f = 0; f < L.nfA; f++) {
+      for (auto &e : by_f[f]) {
+        L.cg_p.push_back(e.first);
+        L.cg_v.push_back(e.second);
+      }
+      L.cg_off[f + 1] = (int) L.cg_p.size();
+    }
+    for (int q = 0; q < np; q++) {
+      for (auto &e : by_q[q]) {
+        L.cgt_f.push_back(e.first);
+        L.cgt_v.push_back(e.second);
+      }
+      L.cgt_off[q + 1] = (int) L.cgt_f.size();
+    }
+    L.l0mask.assign(sp.chem_l0_mask.begin(), sp.chem_l0_mask.end());
+    L.zproj.assign((size_t) m.n_elements * C, 0.0f);
+    for (int e = 0; e < m.n_elements; e++)
+      for (int c = 0; c < C; c++) {
+        double v = 0.0;
+        for (int q = 0; q < m.embedding_size; q++)
+          v += m.chem_embedding[(size_t) e * m.embedding_size + q] * sp.chem_linear_W[(size_t) q * C + c];
+        L.zproj[(size_t) e * C + c] = (float) (v * sp.chem_linear_norm);
+      }
+  }
+}
+
+}    // namespace
+
+std::vector<float> radial_table_3l(const Grace3LModel &m, int k, int mu_i, int mu_j, int N)
+{
+  const Grace3LModel::Spbf &sp = m.spbf[k];
+  const Grace3LModel::Mlp &mlp = sp.mlp;
+  const int nl = m.lmax + 1, C = sp.n_rad_max, ne = m.embedding_size, nrb = m.nradbase, p = sp.p;
+  const double *zi = m.chem_embedding.data() + (size_t) mu_i * ne, *zj = m.chem_embedding.data() + (size_t) mu_j * ne;
+  // layer 1: the species weight of the neighbour is part of the table
+  std::vector<double> fac(C, sp.inv_avg_n_neigh);
+  if (!sp.equivariant)
+    for (int c = 0; c < C; c++) {
+      double v = 0.0;
+      for (int e = 0; e < ne; e++) v += zj[e] * sp.lin_transform_W[(size_t) e * C + c];
+      fac[c] *= v * sp.lin_transform_norm;
+    }
+  std::vector<double> fv((size_t) (N + 1) * nl * C), dv(fv.size());
+  const double h = 1.0 / N;
+  for (int q = 0; q <= N; q++) {
+    const double x = q * h, t = 2.0 * x - 1.0;
+    std::vector<double> a(nrb + 2 * ne, 0.0), da(a.size(), 0.0);
+    double Tp = 1.0, Tc = t, dTp = 0.0, dTc = 2.0;
+    for (int b = 0; b < nrb; b++) {
+      a[b] = Tc;
+      da[b] = dTc;
+      const double Tn = 2.0 * t * Tc - Tp, dTn = 2.0 * (2.0 * Tc + t * dTc) - dTp;
+      Tp = Tc; dTp = dTc; Tc = Tn; dTc = dTn;
+    }
+    for (int e = 0; e < ne; e++) {
+      a[nrb + e] = zi[e];
+      a[nrb + ne + e] = zj[e];
+    }
+    for (int il = 0; il < mlp.n_layers; il++) {
+      const int ni = mlp.n_in[il], no = mlp.n_out[il];
+      std::vector<double> s(no, 0.0), ds(no, 0.0);
+      for (int i = 0; i < ni; i++) {
+        const double *w = mlp.W[il].data() + (size_t) i * no;
+        for (int j = 0; j < no; j++) {
+          s[j] += w[j] * a[i];
+          ds[j] += w[j] * da[i];
+        }
+      }
+      for (int j = 0; j < no; j++) {
+        s[j] *= mlp.norm[il];
+        ds[j] *= mlp.norm[il];
+        if (il < mlp.n_layers - 1) {
+          if (!mlp.b[il].empty()) s[j] += mlp.norm[il] * mlp.b[il][j];
+          const double sg = 1.0 / (1.0 + std::exp(-s[j]));
+          ds[j] *= sg * (1.0 + s[j] * (1.0 - sg));
+          s[j] *= sg;
+        }
+      }
+      a.swap(s);
+      da.swap(ds);
+    }
+    const double xp = std::pow(x, p), xp1 = xp * x, xp2 = xp1 * x;
+    const double env = 1.0 - 0.5 * (p + 1) * (p + 2) * xp + p * (p + 2) * xp1 - 0.5 * p * (p + 1) * xp2;
+    const double denv = 0.5 * p * (p + 1) * (p + 2) * (-std::pow(x, p - 1) + 2.0 * xp - xp1);
+    for (int c = 0; c < C; c++)
+      for (int l = 0; l < nl; l++) {
+        const int o = c * nl + l;
+        fv[((size_t) q * nl + l) * C + c] = a[o] * env * fac[c];
+        dv[((size_t) q * nl + l) * C + c] = h * (da[o] * env + a[o] * denv) * fac[c];
+      }
+  }
+  std::vector<float> tab((size_t) N * nl * C * 4);
+  for (int q = 0; q < N; q++)
+    for (int l = 0; l < nl; l++)
+      for (int c = 0; c < C; c++) {
+        const size_t i0 = ((size_t) q * nl + l) * C + c, i1 = ((size_t) (q + 1) * nl + l) * C + c;
+        const double f0 = fv[i0], f1 = fv[i1], d0 = dv[i0], d1 = dv[i1];
+        float *o = tab.data() + i0 * 4;
+        o[0] = (float) f0;
+        o[1] = (float) d0;
+        o[2] = (float) (-3.0 * f0 - 2.0 * d0 + 3.0 * f1 - d1);
+        o[3] = (float) (2.0 * f0 + d0 - 2.0 * f1 + d1);
+      }
+  return tab;
+}
+
+static ModelPlan build_plan_3l(const GraceModel &gm, int spline_n)
+{
+  const Grace3LModel &m = *gm.m3;
+  ModelPlan P;
+  P.layers = 3;
+  P.lmax = m.lmax;
+  P.nlm = (m.lmax + 1) * (m.lmax + 1);
+  P.n_elements = m.n_elements;
+  P.rcsq.resize((size_t) m.n_elements * m.n_elements);
+  P.rc.resize(P.rcsq.size());
+  for (int a = 0; a < m.n_elements; a++)
+    for (int b = 0; b < m.n_elements; b++) {
+      const double rc = gm.pair_cutoff(a, b);
+      P.rc[(size_t) a * m.n_elements + b] = rc;
+      P.rcsq[(size_t) a * m.n_elements + b] = rc * rc;
+      P.rc_max = std::max(P.rc_max, rc);
+    }
+  P.out_scale = m.output_scale;
+  P.shift = m.shift_values;
+  P.p3 = std::make_shared<Plan3L>();
+  Plan3L &Q = *P.p3;
+  Q.model = gm.m3;
+  Q.spline_n = spline_n;
+  for (int k = 0; k < 3; k++) build_layer_3l(gm, m, k, Q.L[k]);
+  for (int k = 0; k < 2; k++)
+    if (Q.L[k].nfEQ != Q.L[k + 1].nlmi || Q.L[k].cEQ != Q.L[k + 1].C)
+      throw ModelError("GRACE-3L: the message of layer " + std::to_string(k + 1) + " does not fit the next layer");
+  if (Q.L[0].wr != Q.L[1].wr || Q.L[0].wr != Q.L[2].wr) throw ModelError("GRACE-3L: densities of different widths");
+  const Grace3LModel::Mlp &e = m.energy_mlp;
+  if (e.n_layers != 2 || e.n_out[1] != 1 || e.n_in[0] != Q.L[0].wr - 1 || e.n_out[0] > 256 || e.n_in[0] > 128)
+    throw ModelError("GRACE-3L: the energy MLP must have two layers of at most 128 inputs and 256 hidden units");
+  Q.eW0 = e.W[0];
+  Q.eW1 = e.W[1];
+  Q.en0 = e.norm[0];
+  Q.en1 = e.norm[1];
+  Q.e_nin = e.n_in[0];
+  Q.e_nh = e.n_out[0];
+  Q.e_act = m.energy_mlp_activation;
+  return P;
+}
+
 ModelPlan build_plan(const GraceModel &m, int spline_n)
 {
   if (spline_n < 16) throw std::invalid_argument("spline N must be >= 16");
   ModelPlan P;
+  if (m.layers == 3) return build_plan_3l(m, spline_n);
+  // (P is filled below for GRACE-1L / GRACE-2L)
   P.layers = m.layers;
   P.lmax = m.lmax;
   const int nl = m.lmax + 1, nlm = nl * nl;

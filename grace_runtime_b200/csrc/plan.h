@@ -11,6 +11,7 @@
 
 #include "model.h"
 
+#include <memory>
 #include <string>
 #include <utility>
 #include <vector>
@@ -112,6 +113,43 @@ struct UqPlan {
   std::vector<int> n_clusters;
 };
 
+// One layer of GRACE-3L (libgrace/src/fused_3l.cpp:439-873): the single-particle basis A[f] = sum_q cg[q, f] P[q],
+// P[(ly, li)] = sum_j Y_ly R_l(ly) (msg_j[li] + mask[li] zproj[mu_j])  (layer 1: li = 0 only, msg = 0, mask = zproj = 1,
+// cg the identity), the dense chain as a LayerPlan (cp_l projections and reduces as MV operations, the couples as
+// products, the FCs with an identity on their left input), and the two norms behind its reduces.
+struct Layer3Plan {
+  LayerPlan dense;
+  int C = 0, nfA = 0, nlmi = 1;       // channels, functions of A, message functions coupled in
+  int tA = -1, tGA = -1;              // A and its gradient (written / read by the bond kernels)
+  int tEQ = -1, tGEQ = -1;            // input of the EquivariantRMSNorm (layers 1, 2) and its gradient
+  int tRHO = -1, tGRHO = -1;          // input of the RMSNorm and its gradient
+  int nfEQ = 0, cEQ = 0, wr = 0;      // message functions and channels, density width
+  std::vector<int> lt;                // l of each lm (selects the radial function)
+  std::vector<int> cg_off, cg_p, cgt_off, cgt_f;    // the couple by output function f, and by pair q = ly nlmi + li
+  std::vector<float> cg_v, cgt_v;
+  std::vector<float> l0mask;          // [nlmi]
+  std::vector<float> zproj;           // [n_elements][C]
+  std::vector<float> eq_dw, eq_mask, eq_aff;    // [nfEQ], [nfEQ], [groups][cEQ]
+  std::vector<int> eq_e;              // [nfEQ] group of each function
+  double eq_eps = 0.0;
+  int eq_center = 1;
+  std::vector<float> rho_scale;       // [wr - n0]
+  int rho_n0 = 0;                     // 1: channel 0 passes the norm unchanged
+};
+
+struct Plan3L {
+  std::shared_ptr<const Grace3LModel> model;    // radial MLPs and embeddings, for the per-pair tables
+  Layer3Plan L[3];
+  int spline_n = 1024;
+  std::vector<double> eW0, eW1;       // energy MLP [wr - 1][nh], [nh]
+  double en0 = 1.0, en1 = 1.0;
+  int e_nin = 0, e_nh = 0, e_act = 0;
+};
+
+// cubic Hermite coefficients [N][nl][C][4] of the radial functions of layer k for the element pair (centre, neighbour)
+// (libgrace/src/fused_3l.cpp:307-351, 488-533)
+std::vector<float> radial_table_3l(const Grace3LModel &m, int k, int mu_i, int mu_j, int N);
+
 struct ModelPlan {
   int layers = 0, lmax = 0, nlm = 0, n_elements = 0;
   std::vector<double> rcsq;     // [n_elements][n_elements] squared pair cutoffs
@@ -132,6 +170,7 @@ struct ModelPlan {
   std::vector<double> shift;    // [n_elements]
   std::vector<double> lnI, ln0;
   UqPlan uq;
+  std::shared_ptr<Plan3L> p3;   // GRACE-3L
   double dense_flops_per_atom = 0.0;    // FC / reduce / product flops of the forward and reverse programs (diagnostics)
 };
 

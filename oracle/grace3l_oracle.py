@@ -34,7 +34,9 @@ class Grace3LOracle:
         self.shift = z.f("shift_values")
         self.oscale = z.fs("output_scale", 1.0)
         self.elements = z.names("element_names")
-        self.cutmap = z.f("bond_cutoff_map", np.full((self.ne, self.ne), self.rcut)).reshape(self.ne, self.ne)
+        self.cutmap = np.full((self.ne, self.ne), self.rcut)
+        if z.is_("has_bond_specific_cutoff", 0):
+            self.cutmap = z.f("bond_cutoff_map").reshape(self.ne, self.ne)
         self._tables = {}
 
     # ---- radial ------------------------------------------------------------------------------------------------
