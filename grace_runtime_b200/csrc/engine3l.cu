@@ -47,136 +47,171 @@ __device__ void stage_harmonics(const SHTable &sht, float ux, float uy, float uz
   });
 }
 
+constexpr int S3_BB = 64;    // bonds whose harmonics are staged at once
+
+// Thread layout of both kernels: c = tid % C is the thread's channel, g = tid / C its group (G = 256 / C groups; threads
+// beyond G C idle in the per-channel loops), so that the loops over (function, channel) need no divisions.
+
 // A[f][a][c] = sum_q cg[q, f] P[q][c],  P[(ly, li)][c] = sum_bonds Y_ly R[l(ly)][c] (msg_j[li][c] + mask[li] zproj[mu_j][c])
 __global__ void __launch_bounds__(S3_THREADS) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA)
 {
   extern __shared__ float sm[];
-  const int C = L.C, np = L.nlm * L.nlmi;
-  float *P = sm, *Y = P + (size_t) np * C, *R = Y + L.nlm, *Ic = R + (size_t) L.nl * C;
+  const int C = L.C, np = L.nlm * L.nlmi, nlm = L.nlm, nlmi = L.nlmi;
+  float *P = sm, *Ys = P + (size_t) np * C, *R = Ys + S3_BB * nlm, *Ic = R + (size_t) L.nl * C;
   const int i = blockIdx.x, tid = threadIdx.x;
+  const int G = S3_THREADS / C, c = tid % C, g = tid / C;
+  const bool live = g < G;
   const long long base = b.off[i];
   const int nb = b.cnt[i], mui = b.mu[i];
   for (int e = tid; e < np * C; e += S3_THREADS) P[e] = 0.0f;
-  for (int q = 0; q < nb; q++) {
-    const float4 rec = b.rec[base + q];
-    const int j = __float_as_int(rec.w), muj = b.mu[j];
-    const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
-    const int slot = L.pair_slot[mui * L.nel + muj];
-    if (slot < 0) continue;    // no table for this element pair (uniform over the block): the bond is left out
-    int k0;
-    float t;
-    spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
-    __syncthreads();    // the staging buffers of the previous bond are no longer read
-    if (tid == 0) stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, L.nlm, Y, nullptr);
-    const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) slot * L.tab_stride) + (size_t) k0 * L.nl * C;
-    for (int e = tid; e < L.nl * C; e += S3_THREADS) {
-      const float4 c = tab[e];
-      R[e] = c.x + t * (c.y + t * (c.z + t * c.w));
+  for (int q0 = 0; q0 < nb; q0 += S3_BB) {
+    const int nq = min(S3_BB, nb - q0);
+    __syncthreads();    // the harmonics of the previous batch are no longer read
+    if (tid < nq) {
+      const float4 rec = b.rec[base + q0 + tid];
+      const float ir = rsqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
+      stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + tid * nlm, nullptr);
     }
-    for (int e = tid; e < L.nlmi * C; e += S3_THREADS) {
-      const int li = e / C, c = e - li * C;
-      const float m = L.msg ? L.msg[((size_t) j * L.nlmi + li) * C + c] : 0.0f;
-      Ic[e] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c];
-    }
-    __syncthreads();
-    for (int e = tid; e < np * C; e += S3_THREADS) {
-      const int qq = e / C, c = e - qq * C, ly = qq / L.nlmi, li = qq - ly * L.nlmi;
-      P[e] = fmaf(Y[ly] * R[L.lt[ly] * C + c], Ic[li * C + c], P[e]);
+    for (int q = 0; q < nq; q++) {
+      const float4 rec = b.rec[base + q0 + q];
+      const int j = __float_as_int(rec.w), muj = b.mu[j];
+      const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
+      const int slot = L.pair_slot[mui * L.nel + muj];
+      if (slot < 0) continue;    // no table for this element pair (uniform over the block): the bond is left out
+      int k0;
+      float t;
+      spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
+      __syncthreads();    // R and Ic of the previous bond are no longer read; the harmonics are staged
+      const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) slot * L.tab_stride) + (size_t) k0 * L.nl * C;
+      for (int e = tid; e < L.nl * C; e += S3_THREADS) {
+        const float4 cf = tab[e];
+        R[e] = cf.x + t * (cf.y + t * (cf.z + t * cf.w));
+      }
+      if (live)
+        for (int li = g; li < nlmi; li += G) {
+          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c] : 0.0f;
+          Ic[li * C + c] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c];
+        }
+      __syncthreads();
+      if (live) {
+        const float *Y = Ys + q * nlm;
+        for (int ly = g; ly < nlm; ly += G) {
+          const float u = Y[ly] * R[L.lt[ly] * C + c];
+          float *p = P + (size_t) ly * nlmi * C + c;
+          for (int li = 0; li < nlmi; li++) p[(size_t) li * C] = fmaf(u, Ic[li * C + c], p[(size_t) li * C]);
+        }
+      }
     }
   }
   __syncthreads();
-  for (int e = tid; e < L.nfA * C; e += S3_THREADS) {
-    const int f = e / C, c = e - f * C;
-    float v = 0.0f;
-    for (int t = L.cg_off[f]; t < L.cg_off[f + 1]; t++) v = fmaf(L.cg_v[t], P[L.cg_p[t] * C + c], v);
-    A[((size_t) f * NA + i) * C + c] = v;
-  }
+  if (live)
+    for (int f = g; f < L.nfA; f += G) {
+      float v = 0.0f;
+      for (int t = L.cg_off[f]; t < L.cg_off[f + 1]; t++) v = fmaf(L.cg_v[t], P[L.cg_p[t] * C + c], v);
+      A[((size_t) f * NA + i) * C + c] = v;
+    }
 }
 
 // reverse of the above from gA: bond forces (written or added at the bond's slot), per-atom virial, dE/dmsg of the
-// neighbours
+// neighbours.  Per bond, with gP[(ly, li)][c] = sum_f cg[q, f] gA[f][c] staged once per atom:
+//   W[ly][c] = sum_li gP Ic[li][c]              (owner threads: (ly, c))
+//   dE/dmsg_j[li][c] += sum_ly gP Y_ly R_l[c]   (owner threads: (li, c); atomic on the neighbour's row)
+//   gY[ly] = sum_c W R_l[c] (a warp per ly),  dE/dx = sum_{ly, c} W Y_ly dR_l[c]
 __global__ void __launch_bounds__(S3_THREADS) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, const float *__restrict__ gA,
                                                                int NA, float *__restrict__ fv, double *__restrict__ vir_atom, int add)
 {
   extern __shared__ float sm[];
-  const int C = L.C, np = L.nlm * L.nlmi;
-  float *gP = sm, *Y = gP + (size_t) np * C, *G = Y + L.nlm, *R = G + 3 * L.nlm, *dR = R + (size_t) L.nl * C;
-  float *Ic = dR + (size_t) L.nl * C, *gY = Ic + (size_t) L.nlmi * C, *gR = gY + L.nlm, *gI = gR + (size_t) L.nl * C;
-  float *dedx = gI + (size_t) L.nlmi * C;
-  const int i = blockIdx.x, tid = threadIdx.x;
+  const int C = L.C, np = L.nlm * L.nlmi, nlm = L.nlm, nlmi = L.nlmi;
+  float *gP = sm, *Ys = gP + (size_t) np * C, *Gs = Ys + S3_BB * nlm, *R = Gs + 3 * S3_BB * nlm, *dR = R + (size_t) L.nl * C;
+  float *Ic = dR + (size_t) L.nl * C, *gY = Ic + (size_t) nlmi * C, *W = gY + nlm, *dedx = W + (size_t) nlm * C;
+  const int i = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int G = S3_THREADS / C, c = tid % C, g = tid / C;
+  const bool live = g < G;
   const long long base = b.off[i];
   const int nb = b.cnt[i], mui = b.mu[i];
   double vir[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
-  for (int e = tid; e < np * C; e += S3_THREADS) {
-    const int q = e / C, c = e - q * C;
-    float v = 0.0f;
-    for (int t = L.cgt_off[q]; t < L.cgt_off[q + 1]; t++) v = fmaf(L.cgt_v[t], gA[((size_t) L.cgt_f[t] * NA + i) * C + c], v);
-    gP[e] = v;
-  }
-  for (int q = 0; q < nb; q++) {
-    const float4 rec = b.rec[base + q];
-    const int j = __float_as_int(rec.w), muj = b.mu[j];
-    const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
-    const float ux = rec.x * ir, uy = rec.y * ir, uz = rec.z * ir;
-    const int slot = L.pair_slot[mui * L.nel + muj];
-    const float rc = L.rc[mui * L.nel + muj];
-    if (slot < 0) continue;    // as in the forward kernel
-    int k0;
-    float t;
-    spline_locate(r / rc, L.N, k0, t);
-    __syncthreads();    // the buffers of the previous bond are no longer read
-    if (tid == 0) {
-      stage_harmonics(sht, ux, uy, uz, L.nlm, Y, G);
-      *dedx = 0.0f;
+  if (live)
+    for (int q = g; q < np; q += G) {
+      float v = 0.0f;
+      for (int t = L.cgt_off[q]; t < L.cgt_off[q + 1]; t++) v = fmaf(L.cgt_v[t], gA[((size_t) L.cgt_f[t] * NA + i) * C + c], v);
+      gP[(size_t) q * C + c] = v;
     }
-    const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) slot * L.tab_stride) + (size_t) k0 * L.nl * C;
-    for (int e = tid; e < L.nl * C; e += S3_THREADS) {
-      const float4 c = tab[e];
-      R[e] = c.x + t * (c.y + t * (c.z + t * c.w));
-      dR[e] = (c.y + t * (2.0f * c.z + t * 3.0f * c.w)) * (float) L.N;
-      gR[e] = 0.0f;
+  for (int q0 = 0; q0 < nb; q0 += S3_BB) {
+    const int nq = min(S3_BB, nb - q0);
+    __syncthreads();    // the harmonics of the previous batch are no longer read
+    if (tid < nq) {
+      const float4 rec = b.rec[base + q0 + tid];
+      const float ir = rsqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
+      stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + tid * nlm, Gs + 3 * tid * nlm);
     }
-    for (int e = tid; e < L.nlmi * C; e += S3_THREADS) {
-      const int li = e / C, c = e - li * C;
-      const float m = L.msg ? L.msg[((size_t) j * L.nlmi + li) * C + c] : 0.0f;
-      Ic[e] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c];
-      gI[e] = 0.0f;
-    }
-    for (int e = tid; e < L.nlm; e += S3_THREADS) gY[e] = 0.0f;
-    __syncthreads();
-    for (int e = tid; e < np * C; e += S3_THREADS) {
-      const int qq = e / C, c = e - qq * C, ly = qq / L.nlmi, li = qq - ly * L.nlmi;
-      const float g = gP[e], rl = R[L.lt[ly] * C + c], y = Y[ly];
-      if (L.gmsg) atomicAdd(&gI[li * C + c], g * y * rl);
-      const float w = g * Ic[li * C + c];    // dE/d(Y_ly R_l[c])
-      atomicAdd(&gY[ly], w * rl);
-      atomicAdd(&gR[L.lt[ly] * C + c], w * y);
-    }
-    __syncthreads();
-    {
-      float part = 0.0f;
-      for (int e = tid; e < L.nl * C; e += S3_THREADS) part = fmaf(gR[e], dR[e], part);
-      for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
-      if ((tid & 31) == 0) atomicAdd(dedx, part);
-    }
-    if (L.gmsg)
-      for (int e = tid; e < L.nlmi * C; e += S3_THREADS) atomicAdd(L.gmsg + (size_t) j * L.nlmi * C + e, gI[e]);
-    __syncthreads();
-    if (tid == 0) {
-      float gx = 0.0f, gy = 0.0f, gz = 0.0f;
-      for (int lm = 0; lm < L.nlm; lm++) {
-        gx = fmaf(gY[lm], G[3 * lm], gx);
-        gy = fmaf(gY[lm], G[3 * lm + 1], gy);
-        gz = fmaf(gY[lm], G[3 * lm + 2], gz);
+    for (int q = 0; q < nq; q++) {
+      const float4 rec = b.rec[base + q0 + q];
+      const int j = __float_as_int(rec.w), muj = b.mu[j];
+      const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
+      const float ux = rec.x * ir, uy = rec.y * ir, uz = rec.z * ir;
+      const int slot = L.pair_slot[mui * L.nel + muj];
+      const float rc = L.rc[mui * L.nel + muj];
+      if (slot < 0) continue;    // as in the forward kernel
+      int k0;
+      float t;
+      spline_locate(r / rc, L.N, k0, t);
+      __syncthreads();    // the buffers of the previous bond are no longer read (gP and the harmonics are complete)
+      if (tid == 0) *dedx = 0.0f;
+      const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) slot * L.tab_stride) + (size_t) k0 * L.nl * C;
+      for (int e = tid; e < L.nl * C; e += S3_THREADS) {
+        const float4 cf = tab[e];
+        R[e] = cf.x + t * (cf.y + t * (cf.z + t * cf.w));
+        dR[e] = (cf.y + t * (2.0f * cf.z + t * 3.0f * cf.w)) * (float) L.N;
       }
-      const float dEdr = *dedx / rc, gr = gx * ux + gy * uy + gz * uz;
-      const float f0 = dEdr * ux + (gx - gr * ux) * ir, f1 = dEdr * uy + (gy - gr * uy) * ir, f2 = dEdr * uz + (gz - gr * uz) * ir;
-      float *o = fv + 3 * (size_t) b.cslot[base + q];
-      if (add) { o[0] += f0; o[1] += f1; o[2] += f2; }
-      else { o[0] = f0; o[1] = f1; o[2] = f2; }
-      const double dx = -(double) ux * r, dy = -(double) uy * r, dz = -(double) uz * r;
-      vir[0] += dx * f0; vir[1] += dy * f1; vir[2] += dz * f2;
-      vir[3] += dx * f1; vir[4] += dx * f2; vir[5] += dy * f2;
+      if (live)
+        for (int li = g; li < nlmi; li += G) {
+          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c] : 0.0f;
+          Ic[li * C + c] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c];
+        }
+      __syncthreads();
+      const float *Y = Ys + q * nlm, *Gq = Gs + 3 * q * nlm;
+      float part = 0.0f;    // this thread's share of dE/dx
+      if (live) {
+        for (int ly = g; ly < nlm; ly += G) {
+          const float *gp = gP + (size_t) ly * nlmi * C + c;
+          float w = 0.0f;
+          for (int li = 0; li < nlmi; li++) w = fmaf(gp[(size_t) li * C], Ic[li * C + c], w);
+          W[ly * C + c] = w;
+          part = fmaf(w * Y[ly], dR[L.lt[ly] * C + c], part);
+        }
+        if (L.gmsg)
+          for (int li = g; li < nlmi; li += G) {
+            float v = 0.0f;
+            for (int ly = 0; ly < nlm; ly++) v = fmaf(gP[((size_t) ly * nlmi + li) * C + c], Y[ly] * R[L.lt[ly] * C + c], v);
+            atomicAdd(L.gmsg + ((size_t) j * nlmi + li) * C + c, v);
+          }
+      }
+      for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+      if (lane == 0) atomicAdd(dedx, part);
+      __syncthreads();
+      for (int ly = warp; ly < nlm; ly += S3_THREADS / 32) {    // a warp per ly: the sum over the channels
+        float v = 0.0f;
+        for (int cc = lane; cc < C; cc += 32) v = fmaf(W[ly * C + cc], R[L.lt[ly] * C + cc], v);
+        for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+        if (lane == 0) gY[ly] = v;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        float gx = 0.0f, gy = 0.0f, gz = 0.0f;
+        for (int lm = 0; lm < nlm; lm++) {
+          gx = fmaf(gY[lm], Gq[3 * lm], gx);
+          gy = fmaf(gY[lm], Gq[3 * lm + 1], gy);
+          gz = fmaf(gY[lm], Gq[3 * lm + 2], gz);
+        }
+        const float dEdr = *dedx / rc, gr = gx * ux + gy * uy + gz * uz;
+        const float f0 = dEdr * ux + (gx - gr * ux) * ir, f1 = dEdr * uy + (gy - gr * uy) * ir, f2 = dEdr * uz + (gz - gr * uz) * ir;
+        float *o = fv + 3 * (size_t) b.cslot[base + q0 + q];
+        if (add) { o[0] += f0; o[1] += f1; o[2] += f2; }
+        else { o[0] = f0; o[1] = f1; o[2] = f2; }
+        const double dx = -(double) ux * r, dy = -(double) uy * r, dz = -(double) uz * r;
+        vir[0] += dx * f0; vir[1] += dy * f1; vir[2] += dz * f2;
+        vir[3] += dx * f1; vir[4] += dx * f2; vir[5] += dy * f2;
+      }
     }
   }
   if (tid == 0)
@@ -434,7 +469,18 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
   const int *mu = bonds.mu;
   const SHTable sht = sh_table_host();
   const int nt = 128, nblk = (n + nt - 1) / nt;
-  tc_now_ = false;
+  // large evaluations: the projections, reduces and FCs with 16 / 32 / 64 channels as tensor-core grouped GEMMs (mv_tc.cu)
+  tc_now_ = n >= tc_min_atoms_ && dense_ != Dense::Ops && dense_ != Dense::Fused;
+  auto check_tc = [&]() {
+    if (!tc_now_) return;
+    int e = 0;
+    GB_CUDA(cudaMemcpyAsync(&e, tc_error_.get(), sizeof(int), cudaMemcpyDeviceToHost, dev().stream));
+    GB_CUDA(cudaStreamSynchronize(dev().stream));
+    if (e) {
+      GB_CUDA(cudaMemsetAsync(tc_error_.get(), 0, sizeof(int), dev().stream));
+      throw DeviceError("the tensor-core FC kernel gave up waiting for its matrix instructions");
+    }
+  };
   {    // every bond of the structure needs the table of its element pair: a pair outside the Systems' species has none
     // (checked on the host: the species of every System of the engine were prepared when it was created)
   }
@@ -470,11 +516,12 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     return d;
   };
   auto smem_fwd = [&](const Layer3Plan &L) {
-    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + plan_.nlm + (size_t) (plan_.lmax + 1) * L.C + (size_t) L.nlmi * L.C);
+    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + (size_t) S3_BB * plan_.nlm + (size_t) (plan_.lmax + 1) * L.C +
+                            (size_t) L.nlmi * L.C);
   };
   auto smem_bwd = [&](const Layer3Plan &L) {
-    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + 4 * plan_.nlm + 2 * (size_t) (plan_.lmax + 1) * L.C +
-                            (size_t) L.nlmi * L.C + plan_.nlm + (size_t) (plan_.lmax + 1) * L.C + (size_t) L.nlmi * L.C + 4);
+    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + 4 * (size_t) S3_BB * plan_.nlm + 2 * (size_t) (plan_.lmax + 1) * L.C +
+                            (size_t) L.nlmi * L.C + plan_.nlm + (size_t) plan_.nlm * L.C + 4);
   };
   static bool attr_set = false;
   if (!attr_set) {
@@ -501,7 +548,10 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
   const Readout3Dev ro{S.eW0.get(), S.eW1.get(), shift_.get(), Q.en0, Q.en1, plan_.out_scale, Q.e_nin, Q.e_nh, Q.e_act};
   GB_LAUNCH(readout3_kernel, nblk, nt, 0, ro, S.rho_sum.get(), mu, e_atom_.get(), S.drho.get(), energy_only ? 0 : 1, n);
   if (tm) tm->end(StageTimer::FWD);
-  if (energy_only) return;
+  if (energy_only) {
+    check_tc();
+    return;
+  }
   if (tm) tm->begin(StageTimer::BWD);
   for (int k = 0; k < 2; k++) {
     const Layer3Plan &L = Q.L[k];
@@ -524,6 +574,7 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     GB_LAUNCH(spbf3_bwd_kernel, n, S3_THREADS, smem_bwd(L), bonds, spbf(k), sht, T[L.tGA].p, NA, fv_.get(), vir_atom_.get(), k == 2 ? 0 : 1);
   }
   if (tm) tm->end(StageTimer::BWD);
+  check_tc();
 }
 
 }    // namespace gb
