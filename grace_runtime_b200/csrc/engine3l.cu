@@ -30,7 +30,7 @@ struct Spbf3Dev {
   int N, C, nl, nlm, nlmi, nfA, nel;
 };
 
-constexpr int S3_THREADS = 256;
+constexpr int S3_THREADS = 512;
 
 // Y (and its gradient) of one bond by one thread; lm < nlm are kept
 __device__ void stage_harmonics(const SHTable &sht, float ux, float uy, float uz, int nlm, float *Y, float *G)
@@ -49,7 +49,7 @@ __device__ void stage_harmonics(const SHTable &sht, float ux, float uy, float uz
 
 constexpr int S3_BB = 64;    // bonds whose harmonics are staged at once
 
-// Thread layout of both kernels: c = tid % C is the thread's channel, g = tid / C its group (G = 256 / C groups; threads
+// Thread layout of both kernels: c = tid % C is the thread's channel, g = tid / C its group (G = 512 / C groups; threads
 // beyond G C idle in the per-channel loops), so that the loops over (function, channel) need no divisions.
 
 // A[f][a][c] = sum_q cg[q, f] P[q][c],  P[(ly, li)][c] = sum_bonds Y_ly R[l(ly)][c] (msg_j[li][c] + mask[li] zproj[mu_j][c])
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(S3_THREADS) spbf3_fwd_kernel(BondsDev b, Spbf3
 {
   extern __shared__ float sm[];
   const int C = L.C, np = L.nlm * L.nlmi, nlm = L.nlm, nlmi = L.nlmi;
-  float *P = sm, *Ys = P + (size_t) np * C, *R = Ys + S3_BB * nlm, *Ic = R + (size_t) L.nl * C;
+  float *P = sm, *Ys = P + (size_t) np * C, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) nlm * C;
   const int i = blockIdx.x, tid = threadIdx.x;
   const int G = S3_THREADS / C, c = tid % C, g = tid / C;
   const bool live = g < G;
@@ -83,24 +83,25 @@ __global__ void __launch_bounds__(S3_THREADS) spbf3_fwd_kernel(BondsDev b, Spbf3
       spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
       __syncthreads();    // R and Ic of the previous bond are no longer read; the harmonics are staged
       const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) slot * L.tab_stride) + (size_t) k0 * L.nl * C;
-      for (int e = tid; e < L.nl * C; e += S3_THREADS) {
-        const float4 cf = tab[e];
-        R[e] = cf.x + t * (cf.y + t * (cf.z + t * cf.w));
-      }
-      if (live)
+      if (live) {
+        const float *Y = Ys + q * nlm;
+        for (int ly = g; ly < nlm; ly += G) {    // U[ly][c] = Y_ly R_l(ly)[c]
+          const float4 cf = tab[L.lt[ly] * C + c];
+          U[ly * C + c] = Y[ly] * (cf.x + t * (cf.y + t * (cf.z + t * cf.w)));
+        }
         for (int li = g; li < nlmi; li += G) {
           const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c] : 0.0f;
           Ic[li * C + c] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c];
         }
+      }
       __syncthreads();
-      if (live) {
-        const float *Y = Ys + q * nlm;
+      if (live)
         for (int ly = g; ly < nlm; ly += G) {
-          const float u = Y[ly] * R[L.lt[ly] * C + c];
+          const float u = U[ly * C + c];
           float *p = P + (size_t) ly * nlmi * C + c;
+#pragma unroll 5
           for (int li = 0; li < nlmi; li++) p[(size_t) li * C] = fmaf(u, Ic[li * C + c], p[(size_t) li * C]);
         }
-      }
     }
   }
   __syncthreads();
@@ -123,7 +124,8 @@ __global__ void __launch_bounds__(S3_THREADS) spbf3_bwd_kernel(BondsDev b, Spbf3
   extern __shared__ float sm[];
   const int C = L.C, np = L.nlm * L.nlmi, nlm = L.nlm, nlmi = L.nlmi;
   float *gP = sm, *Ys = gP + (size_t) np * C, *Gs = Ys + S3_BB * nlm, *R = Gs + 3 * S3_BB * nlm, *dR = R + (size_t) L.nl * C;
-  float *Ic = dR + (size_t) L.nl * C, *gY = Ic + (size_t) nlmi * C, *W = gY + nlm, *dedx = W + (size_t) nlm * C;
+  float *Ic = dR + (size_t) L.nl * C, *gY = Ic + (size_t) nlmi * C, *W = gY + nlm, *U = W + (size_t) nlm * C;
+  float *dedx = U + (size_t) nlm * C;
   const int i = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int G = S3_THREADS / C, c = tid % C, g = tid / C;
   const bool live = g < G;
@@ -175,14 +177,22 @@ __global__ void __launch_bounds__(S3_THREADS) spbf3_bwd_kernel(BondsDev b, Spbf3
         for (int ly = g; ly < nlm; ly += G) {
           const float *gp = gP + (size_t) ly * nlmi * C + c;
           float w = 0.0f;
+#pragma unroll 5
           for (int li = 0; li < nlmi; li++) w = fmaf(gp[(size_t) li * C], Ic[li * C + c], w);
+          const int lc = L.lt[ly] * C + c;
           W[ly * C + c] = w;
-          part = fmaf(w * Y[ly], dR[L.lt[ly] * C + c], part);
+          U[ly * C + c] = Y[ly] * R[lc];
+          part = fmaf(w * Y[ly], dR[lc], part);
         }
-        if (L.gmsg)
+      }
+      if (L.gmsg) {
+        __syncthreads();    // U of all ly
+        if (live)
           for (int li = g; li < nlmi; li += G) {
+            const float *gp = gP + (size_t) li * C + c;
             float v = 0.0f;
-            for (int ly = 0; ly < nlm; ly++) v = fmaf(gP[((size_t) ly * nlmi + li) * C + c], Y[ly] * R[L.lt[ly] * C + c], v);
+#pragma unroll 5
+            for (int ly = 0; ly < nlm; ly++) v = fmaf(gp[(size_t) ly * nlmi * C], U[ly * C + c], v);
             atomicAdd(L.gmsg + ((size_t) j * nlmi + li) * C + c, v);
           }
       }
@@ -516,12 +526,12 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     return d;
   };
   auto smem_fwd = [&](const Layer3Plan &L) {
-    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + (size_t) S3_BB * plan_.nlm + (size_t) (plan_.lmax + 1) * L.C +
+    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + (size_t) S3_BB * plan_.nlm + (size_t) plan_.nlm * L.C +
                             (size_t) L.nlmi * L.C);
   };
   auto smem_bwd = [&](const Layer3Plan &L) {
     return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + 4 * (size_t) S3_BB * plan_.nlm + 2 * (size_t) (plan_.lmax + 1) * L.C +
-                            (size_t) L.nlmi * L.C + plan_.nlm + (size_t) plan_.nlm * L.C + 4);
+                            (size_t) L.nlmi * L.C + plan_.nlm + 2 * (size_t) plan_.nlm * L.C + 4);
   };
   static bool attr_set = false;
   if (!attr_set) {
