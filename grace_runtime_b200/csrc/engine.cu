@@ -224,6 +224,11 @@ Engine::Engine(const GraceModel &m, int spline_n) : plan_(build_plan(m, spline_n
   if (P.layers == 3) {    // its own set-up and drivers (engine3l.cu); none of the GRACE-1L / 2L paths below applies
     if (exact_) throw Unsupported("GRACE-3L: the exact radial MLP (spline 0) is not supported");
     shift_.upload(P.shift);
+    if (const char *env = getenv("GRACE_B200_DENSE")) {
+      const std::string v = env;
+      dense_ = v == "fused" ? Dense::Fused : v == "tc" ? Dense::Tc : v == "ops" ? Dense::Ops : Dense::Auto;
+    }
+    if (const char *env = getenv("GRACE_B200_TC_MIN_ATOMS")) tc_min_atoms_ = std::max(1, atoi(env));
     tc_error_.set_label("engine:flag");
     tc_error_.ensure(1);
     GB_CUDA(cudaMemsetAsync(tc_error_.get(), 0, sizeof(int), dev().stream));

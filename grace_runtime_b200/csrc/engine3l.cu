@@ -480,7 +480,7 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
   const SHTable sht = sh_table_host();
   const int nt = 128, nblk = (n + nt - 1) / nt;
   // large evaluations: the projections, reduces and FCs with 16 / 32 / 64 channels as tensor-core grouped GEMMs (mv_tc.cu)
-  tc_now_ = n >= tc_min_atoms_ && dense_ != Dense::Ops && dense_ != Dense::Fused;
+  tc_now_ = dense_ == Dense::Tc || (n >= tc_min_atoms_ && dense_ == Dense::Auto);
   auto check_tc = [&]() {
     if (!tc_now_) return;
     int e = 0;

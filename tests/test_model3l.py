@@ -272,3 +272,16 @@ def test_gpu_batch_and_larger_shape(backend, small3l, tmp_path):
     assert abs(g["energy"] - r["energy"]) / len(types) < 2e-6
     assert np.abs(g["forces"] - r["forces"]).max() < 2e-5 * max(1.0, np.abs(r["forces"]).max())
     assert np.abs(g["virial"] - r["virial"]).max() < 2e-5 * max(1.0, np.abs(r["virial"]).max())
+
+
+@pytest.mark.gpu
+def test_gpu_tensor_core_operations(backend, small3l, monkeypatch):
+    """The projections, reduces and FCs of the layer chains as tensor-core grouped GEMMs (the form large evaluations
+    take), forced on a small structure: same results as the SIMT kernels to 3 x tf32 accuracy."""
+    name, types, pos, cell, pbc = next(_cells())
+    monkeypatch.setenv("GRACE_B200_DENSE", "ops")
+    a = backend.System(backend.Model(small3l), ["Al", "Ni"]).compute(types, pos, cell, pbc)
+    monkeypatch.setenv("GRACE_B200_DENSE", "tc")
+    b = backend.System(backend.Model(small3l), ["Al", "Ni"]).compute(types, pos, cell, pbc)
+    assert abs(a["energy"] - b["energy"]) / len(types) < 1e-6
+    assert np.abs(a["forces"] - b["forces"]).max() < 2e-5 * max(1.0, np.abs(a["forces"]).max())
