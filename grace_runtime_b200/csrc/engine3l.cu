@@ -30,7 +30,6 @@ struct Spbf3Dev {
   int N, C, nl, nlm, nlmi, nfA, nel;
 };
 
-constexpr int S3_THREADS = 512;
 
 // Y (and its gradient) of one bond by one thread; lm < nlm are kept
 __device__ void stage_harmonics(const SHTable &sht, float ux, float uy, float uz, int nlm, float *Y, float *G)
@@ -48,187 +47,239 @@ __device__ void stage_harmonics(const SHTable &sht, float ux, float uy, float uz
 }
 
 constexpr int S3_BB = 64;    // bonds whose harmonics are staged at once
+constexpr int S3_T = 5;      // a thread keeps a tile of S3_T x S3_T (Y lm, message function) pairs of one channel in registers
 
-// Thread layout of both kernels: c = tid % C is the thread's channel, g = tid / C its group (G = 512 / C groups; threads
-// beyond G C idle in the per-channel loops), so that the loops over (function, channel) need no divisions.
+// Thread layout of both kernels.  A CTA works on one atom and a slice of CC = 2^cshift channels (blockIdx.y); thread
+// tid has the channel c = tid % CC of the slice and the tile g = tid / CC of the (ly, li) plane: ly in [5 tl, 5 tl + 5),
+// li in [5 ti, 5 ti + 5) with tl = g / nTI, ti = g % nTI.  The 25 products of a tile and a bond need 5 + 5 shared-memory
+// reads, and the bond sums P (or their gradients) never leave the registers.
+
+constexpr int S3_NBS = 4;    // bonds staged and worked on together: one pair of barriers and one round of global loads for all
 
 // A[f][a][c] = sum_q cg[q, f] P[q][c],  P[(ly, li)][c] = sum_bonds Y_ly R[l(ly)][c] (msg_j[li][c] + mask[li] zproj[mu_j][c])
-__global__ void __launch_bounds__(S3_THREADS) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA)
+__global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA, int cshift,
+                                                        int nTI)
 {
   extern __shared__ float sm[];
-  const int C = L.C, np = L.nlm * L.nlmi, nlm = L.nlm, nlmi = L.nlmi;
-  float *P = sm, *Ys = P + (size_t) np * C, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) nlm * C;
-  const int i = blockIdx.x, tid = threadIdx.x;
-  const int G = S3_THREADS / C, c = tid % C, g = tid / C;
-  const bool live = g < G;
+  const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, CC = 1 << cshift, nth = blockDim.x;
+  const int nU = nlm * CC, nI = nlmi * CC;
+  float *Ys = sm, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) S3_NBS * nU, *As = Ic + (size_t) S3_NBS * nI;
+  const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x;
+  const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
   const long long base = b.off[i];
   const int nb = b.cnt[i], mui = b.mu[i];
-  for (int e = tid; e < np * C; e += S3_THREADS) P[e] = 0.0f;
+  float acc[S3_T][S3_T];
+#pragma unroll
+  for (int a = 0; a < S3_T; a++)
+#pragma unroll
+    for (int q = 0; q < S3_T; q++) acc[a][q] = 0.0f;
   for (int q0 = 0; q0 < nb; q0 += S3_BB) {
     const int nq = min(S3_BB, nb - q0);
     __syncthreads();    // the harmonics of the previous batch are no longer read
-    if (tid < nq) {
-      const float4 rec = b.rec[base + q0 + tid];
+    for (int e = tid; e < nq; e += nth) {
+      const float4 rec = b.rec[base + q0 + e];
       const float ir = rsqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
-      stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + tid * nlm, nullptr);
+      stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + e * nlm, nullptr);
     }
-    for (int q = 0; q < nq; q++) {
-      const float4 rec = b.rec[base + q0 + q];
-      const int j = __float_as_int(rec.w), muj = b.mu[j];
-      const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
-      const int slot = L.pair_slot[mui * L.nel + muj];
-      if (slot < 0) continue;    // no table for this element pair (uniform over the block): the bond is left out
-      int k0;
-      float t;
-      spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
-      __syncthreads();    // R and Ic of the previous bond are no longer read; the harmonics are staged
-      const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) slot * L.tab_stride) + (size_t) k0 * L.nl * C;
-      if (live) {
-        const float *Y = Ys + q * nlm;
-        for (int ly = g; ly < nlm; ly += G) {    // U[ly][c] = Y_ly R_l(ly)[c]
-          const float4 cf = tab[L.lt[ly] * C + c];
-          U[ly * C + c] = Y[ly] * (cf.x + t * (cf.y + t * (cf.z + t * cf.w)));
+    for (int q = 0; q < nq; q += S3_NBS) {
+      const int ns = min(S3_NBS, nq - q);
+      __syncthreads();    // U and Ic of the previous bonds are no longer read; the harmonics are staged
+      for (int s = 0; s < ns; s++) {
+        const float4 rec = b.rec[base + q0 + q + s];
+        const int j = __float_as_int(rec.w), muj = b.mu[j];
+        const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
+        const int slot = L.pair_slot[mui * L.nel + muj];    // < 0: no table for this element pair, the bond is left out
+        int k0;
+        float t;
+        spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
+        const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) max(slot, 0) * L.tab_stride) + (size_t) k0 * L.nl * C + c0;
+        const float *Y = Ys + (q + s) * nlm;
+        for (int e = tid; e < nU; e += nth) {    // U[ly][c] = Y_ly R_l(ly)[c]
+          const int ly = e >> cshift, cc = e & (CC - 1);
+          const float4 cf = tab[L.lt[ly] * C + cc];
+          U[s * nU + e] = slot < 0 ? 0.0f : Y[ly] * (cf.x + t * (cf.y + t * (cf.z + t * cf.w)));
         }
-        for (int li = g; li < nlmi; li += G) {
-          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c] : 0.0f;
-          Ic[li * C + c] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c];
+        for (int e = tid; e < nI; e += nth) {
+          const int li = e >> cshift, cc = e & (CC - 1);
+          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c0 + cc] : 0.0f;
+          Ic[s * nI + e] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c0 + cc];
         }
       }
       __syncthreads();
-      if (live)
-        for (int ly = g; ly < nlm; ly += G) {
-          const float u = U[ly * C + c];
-          float *p = P + (size_t) ly * nlmi * C + c;
-#pragma unroll 5
-          for (int li = 0; li < nlmi; li++) p[(size_t) li * C] = fmaf(u, Ic[li * C + c], p[(size_t) li * C]);
-        }
+      for (int s = 0; s < ns; s++) {
+        float u[S3_T], ic[S3_T];
+#pragma unroll
+        for (int a = 0; a < S3_T; a++) u[a] = ly0 + a < nlm ? U[s * nU + (ly0 + a) * CC + c] : 0.0f;
+#pragma unroll
+        for (int q2 = 0; q2 < S3_T; q2++) ic[q2] = li0 + q2 < nlmi ? Ic[s * nI + (li0 + q2) * CC + c] : 0.0f;
+#pragma unroll
+        for (int a = 0; a < S3_T; a++)
+#pragma unroll
+          for (int q2 = 0; q2 < S3_T; q2++) acc[a][q2] = fmaf(u[a], ic[q2], acc[a][q2]);
+      }
     }
   }
+  // the couple: every pair's sum goes to the functions it feeds (shared-memory adds), then the slice is written
   __syncthreads();
-  if (live)
-    for (int f = g; f < L.nfA; f += G) {
-      float v = 0.0f;
-      for (int t = L.cg_off[f]; t < L.cg_off[f + 1]; t++) v = fmaf(L.cg_v[t], P[L.cg_p[t] * C + c], v);
-      A[((size_t) f * NA + i) * C + c] = v;
+  for (int e = tid; e < L.nfA * CC; e += nth) As[e] = 0.0f;
+  __syncthreads();
+#pragma unroll
+  for (int a = 0; a < S3_T; a++)
+#pragma unroll
+    for (int q2 = 0; q2 < S3_T; q2++) {
+      if (ly0 + a >= nlm || li0 + q2 >= nlmi) continue;
+      const int q = (ly0 + a) * nlmi + li0 + q2;
+      for (int t = L.cgt_off[q]; t < L.cgt_off[q + 1]; t++) atomicAdd(&As[L.cgt_f[t] * CC + c], L.cgt_v[t] * acc[a][q2]);
     }
+  __syncthreads();
+  for (int e = tid; e < L.nfA * CC; e += nth) {
+    const int f = e >> cshift, cc = e & (CC - 1);
+    A[((size_t) f * NA + i) * C + c0 + cc] = As[e];
+  }
 }
 
-// reverse of the above from gA: bond forces (written or added at the bond's slot), per-atom virial, dE/dmsg of the
-// neighbours.  Per bond, with gP[(ly, li)][c] = sum_f cg[q, f] gA[f][c] staged once per atom:
-//   W[ly][c] = sum_li gP Ic[li][c]              (owner threads: (ly, c))
-//   dE/dmsg_j[li][c] += sum_ly gP Y_ly R_l[c]   (owner threads: (li, c); atomic on the neighbour's row)
+// Reverse of the above from gA: bond forces and per-atom virial (added: the caller clears them before the first layer
+// is reversed), dE/dmsg of the neighbours.  The thread's tile of gP[(ly, li)][c] = sum_f cg[q, f] gA[f][c] stays in
+// registers; per bond
+//   W[ly][c] = sum_li gP Ic[li][c],   dE/dmsg_j[li][c] += sum_ly gP Y_ly R_l[c]      (tiles add their shares in shared memory)
 //   gY[ly] = sum_c W R_l[c] (a warp per ly),  dE/dx = sum_{ly, c} W Y_ly dR_l[c]
-__global__ void __launch_bounds__(S3_THREADS) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, const float *__restrict__ gA,
-                                                               int NA, float *__restrict__ fv, double *__restrict__ vir_atom, int add)
+// and the bond force is linear in (gY, dE/dx), so every channel slice adds its own share.
+__global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, const float *__restrict__ gA, int NA,
+                                                        float *__restrict__ fv, double *__restrict__ vir_atom, int cshift, int nTI)
 {
   extern __shared__ float sm[];
-  const int C = L.C, np = L.nlm * L.nlmi, nlm = L.nlm, nlmi = L.nlmi;
-  float *gP = sm, *Ys = gP + (size_t) np * C, *Gs = Ys + S3_BB * nlm, *R = Gs + 3 * S3_BB * nlm, *dR = R + (size_t) L.nl * C;
-  float *Ic = dR + (size_t) L.nl * C, *gY = Ic + (size_t) nlmi * C, *W = gY + nlm, *U = W + (size_t) nlm * C;
-  float *dedx = U + (size_t) nlm * C;
-  const int i = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int G = S3_THREADS / C, c = tid % C, g = tid / C;
-  const bool live = g < G;
+  const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, CC = 1 << cshift, nth = blockDim.x;
+  const int nU = nlm * CC, nI = nlmi * CC;
+  float *Ys = sm, *Gs = Ys + S3_BB * nlm, *Rl = Gs + 3 * S3_BB * nlm, *dRl = Rl + (size_t) S3_NBS * nU, *W = dRl + (size_t) S3_NBS * nU;
+  float *Ic = W + (size_t) S3_NBS * nU, *gI = Ic + (size_t) S3_NBS * nI, *gY = gI + (size_t) S3_NBS * nI, *dedx = gY + S3_NBS * nlm;
+  const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
   const long long base = b.off[i];
   const int nb = b.cnt[i], mui = b.mu[i];
   double vir[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
-  if (live)
-    for (int q = g; q < np; q += G) {
+  float gp[S3_T][S3_T];
+#pragma unroll
+  for (int a = 0; a < S3_T; a++)
+#pragma unroll
+    for (int q2 = 0; q2 < S3_T; q2++) {
       float v = 0.0f;
-      for (int t = L.cgt_off[q]; t < L.cgt_off[q + 1]; t++) v = fmaf(L.cgt_v[t], gA[((size_t) L.cgt_f[t] * NA + i) * C + c], v);
-      gP[(size_t) q * C + c] = v;
+      if (ly0 + a < nlm && li0 + q2 < nlmi) {
+        const int q = (ly0 + a) * nlmi + li0 + q2;
+        for (int t = L.cgt_off[q]; t < L.cgt_off[q + 1]; t++) v = fmaf(L.cgt_v[t], gA[((size_t) L.cgt_f[t] * NA + i) * C + c0 + c], v);
+      }
+      gp[a][q2] = v;
     }
   for (int q0 = 0; q0 < nb; q0 += S3_BB) {
     const int nq = min(S3_BB, nb - q0);
     __syncthreads();    // the harmonics of the previous batch are no longer read
-    if (tid < nq) {
-      const float4 rec = b.rec[base + q0 + tid];
+    for (int e = tid; e < nq; e += nth) {
+      const float4 rec = b.rec[base + q0 + e];
       const float ir = rsqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
-      stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + tid * nlm, Gs + 3 * tid * nlm);
+      stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + e * nlm, Gs + 3 * e * nlm);
     }
-    for (int q = 0; q < nq; q++) {
-      const float4 rec = b.rec[base + q0 + q];
-      const int j = __float_as_int(rec.w), muj = b.mu[j];
-      const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
-      const float ux = rec.x * ir, uy = rec.y * ir, uz = rec.z * ir;
-      const int slot = L.pair_slot[mui * L.nel + muj];
-      const float rc = L.rc[mui * L.nel + muj];
-      if (slot < 0) continue;    // as in the forward kernel
-      int k0;
-      float t;
-      spline_locate(r / rc, L.N, k0, t);
-      __syncthreads();    // the buffers of the previous bond are no longer read (gP and the harmonics are complete)
-      if (tid == 0) *dedx = 0.0f;
-      const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) slot * L.tab_stride) + (size_t) k0 * L.nl * C;
-      for (int e = tid; e < L.nl * C; e += S3_THREADS) {
-        const float4 cf = tab[e];
-        R[e] = cf.x + t * (cf.y + t * (cf.z + t * cf.w));
-        dR[e] = (cf.y + t * (2.0f * cf.z + t * 3.0f * cf.w)) * (float) L.N;
-      }
-      if (live)
-        for (int li = g; li < nlmi; li += G) {
-          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c] : 0.0f;
-          Ic[li * C + c] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c];
+    for (int q = 0; q < nq; q += S3_NBS) {
+      const int ns = min(S3_NBS, nq - q);
+      __syncthreads();    // the buffers of the previous bonds are no longer read; the harmonics are staged
+      if (tid < S3_NBS) dedx[tid] = 0.0f;
+      for (int s = 0; s < ns; s++) {
+        const float4 rec = b.rec[base + q0 + q + s];
+        const int j = __float_as_int(rec.w), muj = b.mu[j];
+        const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
+        const int slot = L.pair_slot[mui * L.nel + muj];    // < 0: the bond is left out, as in the forward kernel
+        int k0;
+        float t;
+        spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
+        const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) max(slot, 0) * L.tab_stride) + (size_t) k0 * L.nl * C + c0;
+        for (int e = tid; e < nU; e += nth) {
+          const int ly = e >> cshift, cc = e & (CC - 1);
+          const float4 cf = tab[L.lt[ly] * C + cc];
+          Rl[s * nU + e] = slot < 0 ? 0.0f : cf.x + t * (cf.y + t * (cf.z + t * cf.w));
+          dRl[s * nU + e] = slot < 0 ? 0.0f : (cf.y + t * (2.0f * cf.z + t * 3.0f * cf.w)) * (float) L.N;
+          W[s * nU + e] = 0.0f;
         }
+        for (int e = tid; e < nI; e += nth) {
+          const int li = e >> cshift, cc = e & (CC - 1);
+          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c0 + cc] : 0.0f;
+          Ic[s * nI + e] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c0 + cc];
+          gI[s * nI + e] = 0.0f;
+        }
+      }
       __syncthreads();
-      const float *Y = Ys + q * nlm, *Gq = Gs + 3 * q * nlm;
-      float part = 0.0f;    // this thread's share of dE/dx
-      if (live) {
-        for (int ly = g; ly < nlm; ly += G) {
-          const float *gp = gP + (size_t) ly * nlmi * C + c;
+      for (int s = 0; s < ns; s++) {
+        const float *Y = Ys + (q + s) * nlm;
+        float u[S3_T], ic[S3_T];
+#pragma unroll
+        for (int a = 0; a < S3_T; a++) u[a] = ly0 + a < nlm ? Y[ly0 + a] * Rl[s * nU + (ly0 + a) * CC + c] : 0.0f;
+#pragma unroll
+        for (int q2 = 0; q2 < S3_T; q2++) ic[q2] = li0 + q2 < nlmi ? Ic[s * nI + (li0 + q2) * CC + c] : 0.0f;
+#pragma unroll
+        for (int a = 0; a < S3_T; a++) {
           float w = 0.0f;
-#pragma unroll 5
-          for (int li = 0; li < nlmi; li++) w = fmaf(gp[(size_t) li * C], Ic[li * C + c], w);
-          const int lc = L.lt[ly] * C + c;
-          W[ly * C + c] = w;
-          U[ly * C + c] = Y[ly] * R[lc];
-          part = fmaf(w * Y[ly], dR[lc], part);
+#pragma unroll
+          for (int q2 = 0; q2 < S3_T; q2++) w = fmaf(gp[a][q2], ic[q2], w);
+          if (ly0 + a < nlm) atomicAdd(&W[s * nU + (ly0 + a) * CC + c], w);
+        }
+        if (L.gmsg) {
+#pragma unroll
+          for (int q2 = 0; q2 < S3_T; q2++) {
+            float v = 0.0f;
+#pragma unroll
+            for (int a = 0; a < S3_T; a++) v = fmaf(gp[a][q2], u[a], v);
+            if (li0 + q2 < nlmi) atomicAdd(&gI[s * nI + (li0 + q2) * CC + c], v);
+          }
         }
       }
-      if (L.gmsg) {
-        __syncthreads();    // U of all ly
-        if (live)
-          for (int li = g; li < nlmi; li += G) {
-            const float *gp = gP + (size_t) li * C + c;
-            float v = 0.0f;
-#pragma unroll 5
-            for (int ly = 0; ly < nlm; ly++) v = fmaf(gp[(size_t) ly * nlmi * C], U[ly * C + c], v);
-            atomicAdd(L.gmsg + ((size_t) j * nlmi + li) * C + c, v);
+      __syncthreads();
+      for (int s = 0; s < ns; s++) {
+        const float *Y = Ys + (q + s) * nlm;
+        float part = 0.0f;    // this thread's share of dE/dx
+        for (int e = tid; e < nU; e += nth) part = fmaf(W[s * nU + e] * Y[e >> cshift], dRl[s * nU + e], part);
+        for (int sh = 16; sh > 0; sh >>= 1) part += __shfl_xor_sync(0xffffffffu, part, sh);
+        if (lane == 0 && part != 0.0f) atomicAdd(&dedx[s], part);
+        if (L.gmsg) {
+          const int j = __float_as_int(b.rec[base + q0 + q + s].w);
+          for (int e = tid; e < nI; e += nth) {
+            const int li = e >> cshift, cc = e & (CC - 1);
+            atomicAdd(L.gmsg + ((size_t) j * nlmi + li) * C + c0 + cc, gI[s * nI + e]);
           }
-      }
-      for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
-      if (lane == 0) atomicAdd(dedx, part);
-      __syncthreads();
-      for (int ly = warp; ly < nlm; ly += S3_THREADS / 32) {    // a warp per ly: the sum over the channels
-        float v = 0.0f;
-        for (int cc = lane; cc < C; cc += 32) v = fmaf(W[ly * C + cc], R[L.lt[ly] * C + cc], v);
-        for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
-        if (lane == 0) gY[ly] = v;
+        }
+        for (int ly = warp; ly < nlm; ly += nth / 32) {    // a warp per ly: the sum over the channels of the slice
+          float v = 0.0f;
+          for (int cc = lane; cc < CC; cc += 32) v = fmaf(W[s * nU + ly * CC + cc], Rl[s * nU + ly * CC + cc], v);
+          for (int sh = 16; sh > 0; sh >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
+          if (lane == 0) gY[s * nlm + ly] = v;
+        }
       }
       __syncthreads();
-      if (tid == 0) {
+      if (tid < ns) {    // one thread per bond of the group
+        const int s = tid;
+        const float4 rec = b.rec[base + q0 + q + s];
+        const int muj = b.mu[__float_as_int(rec.w)];
+        const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
+        const float ux = rec.x * ir, uy = rec.y * ir, uz = rec.z * ir, rc = L.rc[mui * L.nel + muj];
+        const float *Gq = Gs + 3 * (q + s) * nlm;
         float gx = 0.0f, gy = 0.0f, gz = 0.0f;
         for (int lm = 0; lm < nlm; lm++) {
-          gx = fmaf(gY[lm], Gq[3 * lm], gx);
-          gy = fmaf(gY[lm], Gq[3 * lm + 1], gy);
-          gz = fmaf(gY[lm], Gq[3 * lm + 2], gz);
+          const float w = gY[s * nlm + lm];
+          gx = fmaf(w, Gq[3 * lm], gx);
+          gy = fmaf(w, Gq[3 * lm + 1], gy);
+          gz = fmaf(w, Gq[3 * lm + 2], gz);
         }
-        const float dEdr = *dedx / rc, gr = gx * ux + gy * uy + gz * uz;
+        const float dEdr = dedx[s] / rc, gr = gx * ux + gy * uy + gz * uz;
         const float f0 = dEdr * ux + (gx - gr * ux) * ir, f1 = dEdr * uy + (gy - gr * uy) * ir, f2 = dEdr * uz + (gz - gr * uz) * ir;
-        float *o = fv + 3 * (size_t) b.cslot[base + q0 + q];
-        if (add) { o[0] += f0; o[1] += f1; o[2] += f2; }
-        else { o[0] = f0; o[1] = f1; o[2] = f2; }
+        float *o = fv + 3 * (size_t) b.cslot[base + q0 + q + s];
+        atomicAdd(o, f0);
+        atomicAdd(o + 1, f1);
+        atomicAdd(o + 2, f2);
         const double dx = -(double) ux * r, dy = -(double) uy * r, dz = -(double) uz * r;
         vir[0] += dx * f0; vir[1] += dy * f1; vir[2] += dz * f2;
         vir[3] += dx * f1; vir[4] += dx * f2; vir[5] += dy * f2;
       }
     }
   }
-  if (tid == 0)
-    for (int k = 0; k < 6; k++) {
-      double *o = vir_atom + 6 * (size_t) i + k;
-      *o = add ? *o + vir[k] : vir[k];
-    }
+  if (tid < S3_NBS)
+    for (int k = 0; k < 6; k++)
+      if (vir[k] != 0.0) atomicAdd(vir_atom + 6 * (size_t) i + k, vir[k]);
 }
 
 struct EqNormDev {
@@ -525,28 +576,42 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     d.nel = plan_.n_elements;
     return d;
   };
-  auto smem_fwd = [&](const Layer3Plan &L) {
-    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + (size_t) S3_BB * plan_.nlm + (size_t) plan_.nlm * L.C +
-                            (size_t) L.nlmi * L.C);
+  // launch shape of the bond kernels of a layer: channel slice, tiles of the (ly, li) plane, threads, shared memory
+  struct Shape {
+    int cshift, nTI, threads, slices;
+    size_t smem_fwd, smem_bwd;
   };
-  auto smem_bwd = [&](const Layer3Plan &L) {
-    return sizeof(float) * ((size_t) plan_.nlm * L.nlmi * L.C + 4 * (size_t) S3_BB * plan_.nlm + 2 * (size_t) (plan_.lmax + 1) * L.C +
-                            (size_t) L.nlmi * L.C + plan_.nlm + 2 * (size_t) plan_.nlm * L.C + 4);
+  auto shape = [&](const Layer3Plan &L) {
+    const int nTL = (plan_.nlm + S3_T - 1) / S3_T, nTI = (L.nlmi + S3_T - 1) / S3_T, groups = nTL * nTI;
+    int cshift = 5;
+    while (cshift > 2 && (L.C % (1 << cshift) != 0 || groups * (1 << cshift) > 832)) cshift--;
+    const int CC = 1 << cshift;
+    if (L.C % CC != 0 || groups * CC > 832) throw Unsupported("GRACE-3L: the coupled bond sums of a layer do not fit a thread block");
+    Shape s{};
+    s.cshift = cshift;
+    s.nTI = nTI;
+    s.threads = (groups * CC + 31) / 32 * 32;
+    s.slices = L.C / CC;
+    s.smem_fwd = sizeof(float) * ((size_t) S3_BB * plan_.nlm + S3_NBS * ((size_t) plan_.nlm * CC + (size_t) L.nlmi * CC) + (size_t) L.nfA * CC);
+    s.smem_bwd = sizeof(float) * (4 * (size_t) S3_BB * plan_.nlm +
+                                  S3_NBS * (3 * (size_t) plan_.nlm * CC + 2 * (size_t) L.nlmi * CC + plan_.nlm) + 8);
+    if (std::max(s.smem_fwd, s.smem_bwd) > 200 * 1024) throw Unsupported("GRACE-3L: the bond sums of a layer do not fit the shared memory");
+    return s;
   };
   static bool attr_set = false;
   if (!attr_set) {
-    GB_CUDA(cudaFuncSetAttribute(spbf3_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    GB_CUDA(cudaFuncSetAttribute(spbf3_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    GB_CUDA(cudaFuncSetAttribute(spbf3_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    GB_CUDA(cudaFuncSetAttribute(spbf3_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set = true;
   }
   for (int k = 0; k < 3; k++) {
     const Layer3Plan &L = Q.L[k];
-    if (smem_bwd(L) > 220 * 1024) throw Unsupported("GRACE-3L: the coupled bond sums of a layer do not fit the shared memory");
+    const Shape sh = shape(L);
     LayerEngine &E = S.E[k];
     float *base = S.arena[k].ensure((size_t) E.per_atom * NA);
     bind_arena(E, base, NA);
     const std::vector<TensorDev> &T = E.tensors_host;
-    GB_LAUNCH(spbf3_fwd_kernel, n, S3_THREADS, smem_fwd(L), bonds, spbf(k), sht, T[L.tA].p, NA);
+    GB_LAUNCH(spbf3_fwd_kernel, dim3(n, sh.slices), sh.threads, sh.smem_fwd, bonds, spbf(k), sht, T[L.tA].p, NA, sh.cshift, sh.nTI);
     run(E, L.dense.fwd, mu, n, NA);
     if (k < 2) {
       S.msg[k].ensure((size_t) n * L.nfEQ * L.cEQ);
@@ -563,6 +628,9 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     return;
   }
   if (tm) tm->begin(StageTimer::BWD);
+  // the reverse bond kernels add their shares (three layers, channel slices) to the bond forces and the virial
+  launch_fill_zero(fv_.get(), sizeof(float) * 3 * (size_t) std::max<int64_t>(nl.nslots(), 1));
+  launch_fill_zero(vir_atom_.get(), sizeof(double) * 6 * (size_t) n);
   for (int k = 0; k < 2; k++) {
     const Layer3Plan &L = Q.L[k];
     S.gmsg[k].ensure((size_t) n * L.nfEQ * L.cEQ);
@@ -581,7 +649,9 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
       GB_LAUNCH(eqnorm_bwd_kernel, nblk, nt, 0, e, T[L.tEQ].p, S.gmsg[k].get(), T[L.tGEQ].p, NA, n);
     }
     run(E, L.dense.bwd, mu, n, NA);
-    GB_LAUNCH(spbf3_bwd_kernel, n, S3_THREADS, smem_bwd(L), bonds, spbf(k), sht, T[L.tGA].p, NA, fv_.get(), vir_atom_.get(), k == 2 ? 0 : 1);
+    const Shape sh = shape(L);
+    GB_LAUNCH(spbf3_bwd_kernel, dim3(n, sh.slices), sh.threads, sh.smem_bwd, bonds, spbf(k), sht, T[L.tGA].p, NA, fv_.get(), vir_atom_.get(), sh.cshift,
+              sh.nTI);
   }
   if (tm) tm->end(StageTimer::BWD);
   check_tc();

@@ -224,7 +224,8 @@ def test_gpu_matches_compiled_reference(backend, small3l):
         assert np.abs(g["forces"] - r["forces"]).max() < 2e-5 * max(1.0, np.abs(r["forces"]).max()), name
         assert np.abs(g["virial"] - r["virial"]).max() < 2e-5 * max(1.0, np.abs(r["virial"]).max()), name
         e_only = sysm.compute(types, pos, cell, pbc, energy_only=True)
-        assert abs(e_only["energy"] - g["energy"]) < 1e-9 * max(1.0, abs(g["energy"])), name
+        # (the couple of the bond sums adds in shared memory in no fixed order: fp32 rounding differs from run to run)
+        assert abs(e_only["energy"] - g["energy"]) < 1e-7 * max(1.0, abs(g["energy"])), name
 
 
 @pytest.mark.gpu
