@@ -54,16 +54,84 @@ constexpr int S3_T = 5;      // a thread keeps a tile of S3_T x S3_T (Y lm, mess
 // li in [5 ti, 5 ti + 5) with tl = g / nTI, ti = g % nTI.  The 25 products of a tile and a bond need 5 + 5 shared-memory
 // reads, and the bond sums P (or their gradients) never leave the registers.
 
+__device__ __forceinline__ void s3_cp16(void *dst_smem, const void *src)
+{
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void s3_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void s3_cp_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// geometry of a bond: neighbour, its element, table of the element pair, table row and offset, distance and cutoff.
+// Worked out once per batch of bonds by one thread per bond (a chain of dependent global loads: record -> element of the
+// neighbour -> table of the pair) and kept in shared memory, 8 words per bond.
+struct S3Bond {
+  int j, muj, slot, k0;
+  float t, r, rc;
+};
+__device__ __forceinline__ void s3_bond_store(const BondsDev &b, const Spbf3Dev &L, long long at, int mui, float *meta)
+{
+  const float4 rec = b.rec[at];
+  const int j = __float_as_int(rec.w), muj = b.mu[j];
+  const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), rc = L.rc[mui * L.nel + muj];
+  int k0;
+  float t;
+  spline_locate(r / rc, L.N, k0, t);
+  meta[0] = __int_as_float(j);
+  meta[1] = __int_as_float(muj);
+  meta[2] = __int_as_float(L.pair_slot[mui * L.nel + muj]);    // < 0: no table for this element pair, the bond is left out
+  meta[3] = __int_as_float(k0);
+  meta[4] = t;
+  meta[5] = r;
+  meta[6] = rc;
+}
+__device__ __forceinline__ S3Bond s3_bond(const float *meta)
+{
+  S3Bond o;
+  o.j = __float_as_int(meta[0]);
+  o.muj = __float_as_int(meta[1]);
+  o.slot = __float_as_int(meta[2]);
+  o.k0 = __float_as_int(meta[3]);
+  o.t = meta[4];
+  o.r = meta[5];
+  o.rc = meta[6];
+  return o;
+}
+
+// asynchronous copies of what the bonds [at, at + ns) of an atom read from global memory, for the channel slice c0 ..
+// c0 + CC: the table rows [nl][CC] float4 of each bond to craw, the message rows [nlmi][CC] of its neighbour to mraw
+__device__ __forceinline__ void s3_issue(const Spbf3Dev &L, const float *meta, int ns, int c0, int cshift, float4 *craw, float *mraw,
+                                         int tid, int nth)
+{
+  const int CC = 1 << cshift, nT = L.nl * CC, nM4 = L.nlmi * CC / 4;
+  for (int s = 0; s < ns; s++) {
+    const S3Bond B = s3_bond(meta + 8 * s);
+    const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) max(B.slot, 0) * L.tab_stride) + (size_t) B.k0 * L.nl * L.C + c0;
+    for (int e = tid; e < nT; e += nth) s3_cp16(craw + s * nT + e, tab + (e >> cshift) * L.C + (e & (CC - 1)));
+    if (L.msg) {
+      const float *m = L.msg + (size_t) B.j * L.nlmi * L.C + c0;
+      for (int e = tid; e < nM4; e += nth) {
+        const int li = (4 * e) >> cshift, cc = (4 * e) & (CC - 1);
+        s3_cp16(mraw + s * L.nlmi * CC + 4 * e, m + (size_t) li * L.C + cc);
+      }
+    }
+  }
+  s3_cp_commit();
+}
+
 constexpr int S3_NBS = 4;    // bonds staged and worked on together: one pair of barriers and one round of global loads for all
 
 // A[f][a][c] = sum_q cg[q, f] P[q][c],  P[(ly, li)][c] = sum_bonds Y_ly R[l(ly)][c] (msg_j[li][c] + mask[li] zproj[mu_j][c])
 __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA, int cshift,
                                                         int nTI)
 {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, CC = 1 << cshift, nth = blockDim.x;
   const int nU = nlm * CC, nI = nlmi * CC;
-  float *Ys = sm, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) S3_NBS * nU, *As = Ic + (size_t) S3_NBS * nI;
+  const int nT = L.nl * CC;
+  float4 *craw = reinterpret_cast<float4 *>(sm);                      // [2][NBS][nl][CC] table rows
+  float *mraw = reinterpret_cast<float *>(craw + 2 * S3_NBS * nT);    // [2][NBS][nlmi][CC] message rows
+  float *meta = mraw + 2 * (size_t) S3_NBS * nI, *Ys = meta + 8 * S3_BB, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) S3_NBS * nU,
+        *As = Ic + (size_t) S3_NBS * nI;
   const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x;
   const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
   const long long base = b.off[i];
@@ -80,29 +148,30 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
       const float4 rec = b.rec[base + q0 + e];
       const float ir = rsqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
       stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + e * nlm, nullptr);
+      s3_bond_store(b, L, base + q0 + e, mui, meta + 8 * e);
     }
-    for (int q = 0; q < nq; q += S3_NBS) {
+    __syncthreads();
+    s3_issue(L, meta, min(S3_NBS, nq), c0, cshift, craw, mraw, tid, nth);    // the first group of the batch
+    for (int q = 0, k = 0; q < nq; q += S3_NBS, k ^= 1) {
       const int ns = min(S3_NBS, nq - q);
-      __syncthreads();    // U and Ic of the previous bonds are no longer read; the harmonics are staged
+      s3_cp_wait();
+      __syncthreads();    // this group's rows have arrived; U and Ic of the previous group are no longer read
+      if (q + S3_NBS < nq)    // the next group's rows travel while this group is worked on
+        s3_issue(L, meta + 8 * (q + S3_NBS), min(S3_NBS, nq - q - S3_NBS), c0, cshift, craw + (k ^ 1) * S3_NBS * nT,
+                 mraw + (size_t) (k ^ 1) * S3_NBS * nI, tid, nth);
       for (int s = 0; s < ns; s++) {
-        const float4 rec = b.rec[base + q0 + q + s];
-        const int j = __float_as_int(rec.w), muj = b.mu[j];
-        const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
-        const int slot = L.pair_slot[mui * L.nel + muj];    // < 0: no table for this element pair, the bond is left out
-        int k0;
-        float t;
-        spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
-        const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) max(slot, 0) * L.tab_stride) + (size_t) k0 * L.nl * C + c0;
-        const float *Y = Ys + (q + s) * nlm;
+        const S3Bond B = s3_bond(meta + 8 * (q + s));
+        const float4 *cr = craw + (k * S3_NBS + s) * nT;
+        const float *mr = mraw + (size_t) (k * S3_NBS + s) * nI, *Y = Ys + (q + s) * nlm;
+        const float t = B.t;
         for (int e = tid; e < nU; e += nth) {    // U[ly][c] = Y_ly R_l(ly)[c]
           const int ly = e >> cshift, cc = e & (CC - 1);
-          const float4 cf = tab[L.lt[ly] * C + cc];
-          U[s * nU + e] = slot < 0 ? 0.0f : Y[ly] * (cf.x + t * (cf.y + t * (cf.z + t * cf.w)));
+          const float4 cf = cr[L.lt[ly] * CC + cc];
+          U[s * nU + e] = B.slot < 0 ? 0.0f : Y[ly] * (cf.x + t * (cf.y + t * (cf.z + t * cf.w)));
         }
         for (int e = tid; e < nI; e += nth) {
           const int li = e >> cshift, cc = e & (CC - 1);
-          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c0 + cc] : 0.0f;
-          Ic[s * nI + e] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c0 + cc];
+          Ic[s * nI + e] = (L.msg ? mr[e] : 0.0f) + L.l0mask[li] * L.zproj[(size_t) B.muj * C + c0 + cc];
         }
       }
       __syncthreads();
@@ -147,10 +216,14 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
 __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, const float *__restrict__ gA, int NA,
                                                         float *__restrict__ fv, double *__restrict__ vir_atom, int cshift, int nTI)
 {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, CC = 1 << cshift, nth = blockDim.x;
   const int nU = nlm * CC, nI = nlmi * CC;
-  float *Ys = sm, *Gs = Ys + S3_BB * nlm, *Rl = Gs + 3 * S3_BB * nlm, *dRl = Rl + (size_t) S3_NBS * nU, *W = dRl + (size_t) S3_NBS * nU;
+  const int nT = L.nl * CC;
+  float4 *craw = reinterpret_cast<float4 *>(sm);                      // [2][NBS][nl][CC] table rows
+  float *mraw = reinterpret_cast<float *>(craw + 2 * S3_NBS * nT);    // [2][NBS][nlmi][CC] message rows
+  float *meta = mraw + 2 * (size_t) S3_NBS * nI, *Ys = meta + 8 * S3_BB, *Gs = Ys + S3_BB * nlm, *Rl = Gs + 3 * S3_BB * nlm, *dRl = Rl + (size_t) S3_NBS * nU,
+        *W = dRl + (size_t) S3_NBS * nU;
   float *Ic = W + (size_t) S3_NBS * nU, *gI = Ic + (size_t) S3_NBS * nI, *gY = gI + (size_t) S3_NBS * nI, *dedx = gY + S3_NBS * nlm;
   const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
@@ -176,31 +249,33 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
       const float4 rec = b.rec[base + q0 + e];
       const float ir = rsqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
       stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + e * nlm, Gs + 3 * e * nlm);
+      s3_bond_store(b, L, base + q0 + e, mui, meta + 8 * e);
     }
-    for (int q = 0; q < nq; q += S3_NBS) {
+    __syncthreads();
+    s3_issue(L, meta, min(S3_NBS, nq), c0, cshift, craw, mraw, tid, nth);    // the first group of the batch
+    for (int q = 0, k = 0; q < nq; q += S3_NBS, k ^= 1) {
       const int ns = min(S3_NBS, nq - q);
-      __syncthreads();    // the buffers of the previous bonds are no longer read; the harmonics are staged
+      s3_cp_wait();
+      __syncthreads();    // this group's rows have arrived; the buffers of the previous group are no longer read
+      if (q + S3_NBS < nq)    // the next group's rows travel while this group is worked on
+        s3_issue(L, meta + 8 * (q + S3_NBS), min(S3_NBS, nq - q - S3_NBS), c0, cshift, craw + (k ^ 1) * S3_NBS * nT,
+                 mraw + (size_t) (k ^ 1) * S3_NBS * nI, tid, nth);
       if (tid < S3_NBS) dedx[tid] = 0.0f;
       for (int s = 0; s < ns; s++) {
-        const float4 rec = b.rec[base + q0 + q + s];
-        const int j = __float_as_int(rec.w), muj = b.mu[j];
-        const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
-        const int slot = L.pair_slot[mui * L.nel + muj];    // < 0: the bond is left out, as in the forward kernel
-        int k0;
-        float t;
-        spline_locate(r / L.rc[mui * L.nel + muj], L.N, k0, t);
-        const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) max(slot, 0) * L.tab_stride) + (size_t) k0 * L.nl * C + c0;
+        const S3Bond B = s3_bond(meta + 8 * (q + s));
+        const float4 *cr = craw + (k * S3_NBS + s) * nT;
+        const float *mr = mraw + (size_t) (k * S3_NBS + s) * nI;
+        const float t = B.t;
         for (int e = tid; e < nU; e += nth) {
           const int ly = e >> cshift, cc = e & (CC - 1);
-          const float4 cf = tab[L.lt[ly] * C + cc];
-          Rl[s * nU + e] = slot < 0 ? 0.0f : cf.x + t * (cf.y + t * (cf.z + t * cf.w));
-          dRl[s * nU + e] = slot < 0 ? 0.0f : (cf.y + t * (2.0f * cf.z + t * 3.0f * cf.w)) * (float) L.N;
+          const float4 cf = cr[L.lt[ly] * CC + cc];
+          Rl[s * nU + e] = B.slot < 0 ? 0.0f : cf.x + t * (cf.y + t * (cf.z + t * cf.w));
+          dRl[s * nU + e] = B.slot < 0 ? 0.0f : (cf.y + t * (2.0f * cf.z + t * 3.0f * cf.w)) * (float) L.N;
           W[s * nU + e] = 0.0f;
         }
         for (int e = tid; e < nI; e += nth) {
           const int li = e >> cshift, cc = e & (CC - 1);
-          const float m = L.msg ? L.msg[((size_t) j * nlmi + li) * C + c0 + cc] : 0.0f;
-          Ic[s * nI + e] = m + L.l0mask[li] * L.zproj[(size_t) muj * C + c0 + cc];
+          Ic[s * nI + e] = (L.msg ? mr[e] : 0.0f) + L.l0mask[li] * L.zproj[(size_t) B.muj * C + c0 + cc];
           gI[s * nI + e] = 0.0f;
         }
       }
@@ -237,7 +312,7 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
         for (int sh = 16; sh > 0; sh >>= 1) part += __shfl_xor_sync(0xffffffffu, part, sh);
         if (lane == 0 && part != 0.0f) atomicAdd(&dedx[s], part);
         if (L.gmsg) {
-          const int j = __float_as_int(b.rec[base + q0 + q + s].w);
+          const int j = __float_as_int(meta[8 * (q + s)]);
           for (int e = tid; e < nI; e += nth) {
             const int li = e >> cshift, cc = e & (CC - 1);
             atomicAdd(L.gmsg + ((size_t) j * nlmi + li) * C + c0 + cc, gI[s * nI + e]);
@@ -254,9 +329,9 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
       if (tid < ns) {    // one thread per bond of the group
         const int s = tid;
         const float4 rec = b.rec[base + q0 + q + s];
-        const int muj = b.mu[__float_as_int(rec.w)];
-        const float r = sqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z), ir = 1.0f / r;
-        const float ux = rec.x * ir, uy = rec.y * ir, uz = rec.z * ir, rc = L.rc[mui * L.nel + muj];
+        const S3Bond B = s3_bond(meta + 8 * (q + s));
+        const float r = B.r, ir = 1.0f / r, rc = B.rc;
+        const float ux = rec.x * ir, uy = rec.y * ir, uz = rec.z * ir;
         const float *Gq = Gs + 3 * (q + s) * nlm;
         float gx = 0.0f, gy = 0.0f, gz = 0.0f;
         for (int lm = 0; lm < nlm; lm++) {
@@ -592,8 +667,9 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     s.nTI = nTI;
     s.threads = (groups * CC + 31) / 32 * 32;
     s.slices = L.C / CC;
-    s.smem_fwd = sizeof(float) * ((size_t) S3_BB * plan_.nlm + S3_NBS * ((size_t) plan_.nlm * CC + (size_t) L.nlmi * CC) + (size_t) L.nfA * CC);
-    s.smem_bwd = sizeof(float) * (4 * (size_t) S3_BB * plan_.nlm +
+    const size_t raw = 2 * (size_t) S3_NBS * (4 * (size_t) (plan_.lmax + 1) * CC + (size_t) L.nlmi * CC);    // the two staging buffers
+    s.smem_fwd = sizeof(float) * (raw + 8 * S3_BB + (size_t) S3_BB * plan_.nlm + S3_NBS * ((size_t) plan_.nlm * CC + (size_t) L.nlmi * CC) + (size_t) L.nfA * CC);
+    s.smem_bwd = sizeof(float) * (raw + 8 * S3_BB + 4 * (size_t) S3_BB * plan_.nlm +
                                   S3_NBS * (3 * (size_t) plan_.nlm * CC + 2 * (size_t) L.nlmi * CC + plan_.nlm) + 8);
     if (std::max(s.smem_fwd, s.smem_bwd) > 200 * 1024) throw Unsupported("GRACE-3L: the bond sums of a layer do not fit the shared memory");
     return s;
