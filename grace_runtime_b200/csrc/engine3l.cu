@@ -280,28 +280,34 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
         }
       }
       __syncthreads();
-      for (int s = 0; s < ns; s++) {
+#pragma unroll
+      for (int s = 0; s < S3_NBS; s++) {    // unrolled: the bonds of the group are independent work for the scheduler
+        if (s >= ns) break;
         const float *Y = Ys + (q + s) * nlm;
         float u[S3_T], ic[S3_T];
 #pragma unroll
         for (int a = 0; a < S3_T; a++) u[a] = ly0 + a < nlm ? Y[ly0 + a] * Rl[s * nU + (ly0 + a) * CC + c] : 0.0f;
 #pragma unroll
         for (int q2 = 0; q2 < S3_T; q2++) ic[q2] = li0 + q2 < nlmi ? Ic[s * nI + (li0 + q2) * CC + c] : 0.0f;
+        float w[S3_T], v[S3_T];
 #pragma unroll
-        for (int a = 0; a < S3_T; a++) {
-          float w = 0.0f;
+        for (int a = 0; a < S3_T; a++) w[a] = 0.0f;
 #pragma unroll
-          for (int q2 = 0; q2 < S3_T; q2++) w = fmaf(gp[a][q2], ic[q2], w);
-          if (ly0 + a < nlm) atomicAdd(&W[s * nU + (ly0 + a) * CC + c], w);
-        }
-        if (L.gmsg) {
+        for (int q2 = 0; q2 < S3_T; q2++) v[q2] = 0.0f;
+#pragma unroll
+        for (int a = 0; a < S3_T; a++)
 #pragma unroll
           for (int q2 = 0; q2 < S3_T; q2++) {
-            float v = 0.0f;
-#pragma unroll
-            for (int a = 0; a < S3_T; a++) v = fmaf(gp[a][q2], u[a], v);
-            if (li0 + q2 < nlmi) atomicAdd(&gI[s * nI + (li0 + q2) * CC + c], v);
+            w[a] = fmaf(gp[a][q2], ic[q2], w[a]);
+            v[q2] = fmaf(gp[a][q2], u[a], v[q2]);
           }
+#pragma unroll
+        for (int a = 0; a < S3_T; a++)
+          if (ly0 + a < nlm) atomicAdd(&W[s * nU + (ly0 + a) * CC + c], w[a]);
+        if (L.gmsg) {
+#pragma unroll
+          for (int q2 = 0; q2 < S3_T; q2++)
+            if (li0 + q2 < nlmi) atomicAdd(&gI[s * nI + (li0 + q2) * CC + c], v[q2]);
         }
       }
       __syncthreads();
@@ -313,9 +319,10 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
         if (lane == 0 && part != 0.0f) atomicAdd(&dedx[s], part);
         if (L.gmsg) {
           const int j = __float_as_int(meta[8 * (q + s)]);
-          for (int e = tid; e < nI; e += nth) {
-            const int li = e >> cshift, cc = e & (CC - 1);
-            atomicAdd(L.gmsg + ((size_t) j * nlmi + li) * C + c0 + cc, gI[s * nI + e]);
+          for (int e = tid; e < nI / 4; e += nth) {    // four channels per atomic (16-byte vector add)
+            const int li = (4 * e) >> cshift, cc = (4 * e) & (CC - 1);
+            atomicAdd(reinterpret_cast<float4 *>(L.gmsg + ((size_t) j * nlmi + li) * C + c0 + cc),
+                      *reinterpret_cast<const float4 *>(gI + s * nI + 4 * e));
           }
         }
         for (int ly = warp; ly < nlm; ly += nth / 32) {    // a warp per ly: the sum over the channels of the slice
