@@ -98,13 +98,15 @@ __device__ __forceinline__ S3Bond s3_bond(const float *meta)
 }
 
 // asynchronous copies of what the bonds [at, at + ns) of an atom read from global memory, for the channel slice c0 ..
-// c0 + CC: the table rows [nl][CC] float4 of each bond to craw, the message rows [nlmi][CC] of its neighbour to mraw
+// c0 + CC: the table rows [nl][CC] float4 of each bond to craw, the message rows [nlmi][CC] of its neighbour to mraw,
+// the chemical weights [CC] of the neighbour's element to zraw
 __device__ __forceinline__ void s3_issue(const Spbf3Dev &L, const float *meta, int ns, int c0, int cshift, float4 *craw, float *mraw,
-                                         int tid, int nth)
+                                         float *zraw, int tid, int nth)
 {
   const int CC = 1 << cshift, nT = L.nl * CC, nM4 = L.nlmi * CC / 4;
   for (int s = 0; s < ns; s++) {
     const S3Bond B = s3_bond(meta + 8 * s);
+    if (tid < CC / 4) s3_cp16(zraw + s * CC + 4 * tid, L.zproj + (size_t) B.muj * L.C + c0 + 4 * tid);
     const float4 *tab = reinterpret_cast<const float4 *>(L.tab + (size_t) max(B.slot, 0) * L.tab_stride) + (size_t) B.k0 * L.nl * L.C + c0;
     for (int e = tid; e < nT; e += nth) s3_cp16(craw + s * nT + e, tab + (e >> cshift) * L.C + (e & (CC - 1)));
     if (L.msg) {
@@ -130,8 +132,10 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
   const int nT = L.nl * CC;
   float4 *craw = reinterpret_cast<float4 *>(sm);                      // [2][NBS][nl][CC] table rows
   float *mraw = reinterpret_cast<float *>(craw + 2 * S3_NBS * nT);    // [2][NBS][nlmi][CC] message rows
-  float *meta = mraw + 2 * (size_t) S3_NBS * nI, *Ys = meta + 8 * S3_BB, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) S3_NBS * nU,
-        *As = Ic + (size_t) S3_NBS * nI;
+  float *zraw = mraw + 2 * (size_t) S3_NBS * nI;                      // [2][NBS][CC] chemical weights of the neighbours' elements
+  float *meta = zraw + 2 * S3_NBS * CC, *Ys = meta + 8 * S3_BB, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) S3_NBS * nU,
+        *As = Ic + (size_t) S3_NBS * nI, *mask = As + (size_t) L.nfA * CC;
+  int *lts = reinterpret_cast<int *>(mask + nlmi);                    // l of each lm, and the mask of the message functions above
   const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x;
   const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
   const long long base = b.off[i];
@@ -141,6 +145,8 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
   for (int a = 0; a < S3_T; a++)
 #pragma unroll
     for (int q = 0; q < S3_T; q++) acc[a][q] = 0.0f;
+  for (int e = tid; e < nlm; e += nth) lts[e] = L.lt[e];
+  for (int e = tid; e < nlmi; e += nth) mask[e] = L.l0mask[e];
   for (int q0 = 0; q0 < nb; q0 += S3_BB) {
     const int nq = min(S3_BB, nb - q0);
     __syncthreads();    // the harmonics of the previous batch are no longer read
@@ -151,14 +157,14 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
       s3_bond_store(b, L, base + q0 + e, mui, meta + 8 * e);
     }
     __syncthreads();
-    s3_issue(L, meta, min(S3_NBS, nq), c0, cshift, craw, mraw, tid, nth);    // the first group of the batch
+    s3_issue(L, meta, min(S3_NBS, nq), c0, cshift, craw, mraw, zraw, tid, nth);    // the first group of the batch
     for (int q = 0, k = 0; q < nq; q += S3_NBS, k ^= 1) {
       const int ns = min(S3_NBS, nq - q);
       s3_cp_wait();
       __syncthreads();    // this group's rows have arrived; U and Ic of the previous group are no longer read
       if (q + S3_NBS < nq)    // the next group's rows travel while this group is worked on
         s3_issue(L, meta + 8 * (q + S3_NBS), min(S3_NBS, nq - q - S3_NBS), c0, cshift, craw + (k ^ 1) * S3_NBS * nT,
-                 mraw + (size_t) (k ^ 1) * S3_NBS * nI, tid, nth);
+                 mraw + (size_t) (k ^ 1) * S3_NBS * nI, zraw + (k ^ 1) * S3_NBS * CC, tid, nth);
       for (int s = 0; s < ns; s++) {
         const S3Bond B = s3_bond(meta + 8 * (q + s));
         const float4 *cr = craw + (k * S3_NBS + s) * nT;
@@ -166,12 +172,12 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
         const float t = B.t;
         for (int e = tid; e < nU; e += nth) {    // U[ly][c] = Y_ly R_l(ly)[c]
           const int ly = e >> cshift, cc = e & (CC - 1);
-          const float4 cf = cr[L.lt[ly] * CC + cc];
+          const float4 cf = cr[lts[ly] * CC + cc];
           U[s * nU + e] = B.slot < 0 ? 0.0f : Y[ly] * (cf.x + t * (cf.y + t * (cf.z + t * cf.w)));
         }
         for (int e = tid; e < nI; e += nth) {
           const int li = e >> cshift, cc = e & (CC - 1);
-          Ic[s * nI + e] = (L.msg ? mr[e] : 0.0f) + L.l0mask[li] * L.zproj[(size_t) B.muj * C + c0 + cc];
+          Ic[s * nI + e] = (L.msg ? mr[e] : 0.0f) + mask[li] * zraw[(k * S3_NBS + s) * CC + cc];
         }
       }
       __syncthreads();
@@ -222,9 +228,12 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
   const int nT = L.nl * CC;
   float4 *craw = reinterpret_cast<float4 *>(sm);                      // [2][NBS][nl][CC] table rows
   float *mraw = reinterpret_cast<float *>(craw + 2 * S3_NBS * nT);    // [2][NBS][nlmi][CC] message rows
-  float *meta = mraw + 2 * (size_t) S3_NBS * nI, *Ys = meta + 8 * S3_BB, *Gs = Ys + S3_BB * nlm, *Rl = Gs + 3 * S3_BB * nlm, *dRl = Rl + (size_t) S3_NBS * nU,
+  float *zraw = mraw + 2 * (size_t) S3_NBS * nI;                      // [2][NBS][CC] chemical weights of the neighbours' elements
+  float *meta = zraw + 2 * S3_NBS * CC, *Ys = meta + 8 * S3_BB, *Gs = Ys + S3_BB * nlm, *Rl = Gs + 3 * S3_BB * nlm, *dRl = Rl + (size_t) S3_NBS * nU,
         *W = dRl + (size_t) S3_NBS * nU;
   float *Ic = W + (size_t) S3_NBS * nU, *gI = Ic + (size_t) S3_NBS * nI, *gY = gI + (size_t) S3_NBS * nI, *dedx = gY + S3_NBS * nlm;
+  float *mask = dedx + 8;
+  int *lts = reinterpret_cast<int *>(mask + nlmi);
   const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
   const long long base = b.off[i];
@@ -242,6 +251,8 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
       }
       gp[a][q2] = v;
     }
+  for (int e = tid; e < nlm; e += nth) lts[e] = L.lt[e];
+  for (int e = tid; e < nlmi; e += nth) mask[e] = L.l0mask[e];
   for (int q0 = 0; q0 < nb; q0 += S3_BB) {
     const int nq = min(S3_BB, nb - q0);
     __syncthreads();    // the harmonics of the previous batch are no longer read
@@ -252,14 +263,14 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
       s3_bond_store(b, L, base + q0 + e, mui, meta + 8 * e);
     }
     __syncthreads();
-    s3_issue(L, meta, min(S3_NBS, nq), c0, cshift, craw, mraw, tid, nth);    // the first group of the batch
+    s3_issue(L, meta, min(S3_NBS, nq), c0, cshift, craw, mraw, zraw, tid, nth);    // the first group of the batch
     for (int q = 0, k = 0; q < nq; q += S3_NBS, k ^= 1) {
       const int ns = min(S3_NBS, nq - q);
       s3_cp_wait();
       __syncthreads();    // this group's rows have arrived; the buffers of the previous group are no longer read
       if (q + S3_NBS < nq)    // the next group's rows travel while this group is worked on
         s3_issue(L, meta + 8 * (q + S3_NBS), min(S3_NBS, nq - q - S3_NBS), c0, cshift, craw + (k ^ 1) * S3_NBS * nT,
-                 mraw + (size_t) (k ^ 1) * S3_NBS * nI, tid, nth);
+                 mraw + (size_t) (k ^ 1) * S3_NBS * nI, zraw + (k ^ 1) * S3_NBS * CC, tid, nth);
       if (tid < S3_NBS) dedx[tid] = 0.0f;
       for (int s = 0; s < ns; s++) {
         const S3Bond B = s3_bond(meta + 8 * (q + s));
@@ -268,14 +279,14 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
         const float t = B.t;
         for (int e = tid; e < nU; e += nth) {
           const int ly = e >> cshift, cc = e & (CC - 1);
-          const float4 cf = cr[L.lt[ly] * CC + cc];
+          const float4 cf = cr[lts[ly] * CC + cc];
           Rl[s * nU + e] = B.slot < 0 ? 0.0f : cf.x + t * (cf.y + t * (cf.z + t * cf.w));
           dRl[s * nU + e] = B.slot < 0 ? 0.0f : (cf.y + t * (2.0f * cf.z + t * 3.0f * cf.w)) * (float) L.N;
           W[s * nU + e] = 0.0f;
         }
         for (int e = tid; e < nI; e += nth) {
           const int li = e >> cshift, cc = e & (CC - 1);
-          Ic[s * nI + e] = (L.msg ? mr[e] : 0.0f) + L.l0mask[li] * L.zproj[(size_t) B.muj * C + c0 + cc];
+          Ic[s * nI + e] = (L.msg ? mr[e] : 0.0f) + mask[li] * zraw[(k * S3_NBS + s) * CC + cc];
           gI[s * nI + e] = 0.0f;
         }
       }
@@ -674,7 +685,7 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     s.nTI = nTI;
     s.threads = (groups * CC + 31) / 32 * 32;
     s.slices = L.C / CC;
-    const size_t raw = 2 * (size_t) S3_NBS * (4 * (size_t) (plan_.lmax + 1) * CC + (size_t) L.nlmi * CC);    // the two staging buffers
+    const size_t raw = 2 * (size_t) S3_NBS * (4 * (size_t) (plan_.lmax + 1) * CC + (size_t) L.nlmi * CC + CC) + plan_.nlm + L.nlmi + 8;    // the two staging buffers
     s.smem_fwd = sizeof(float) * (raw + 8 * S3_BB + (size_t) S3_BB * plan_.nlm + S3_NBS * ((size_t) plan_.nlm * CC + (size_t) L.nlmi * CC) + (size_t) L.nfA * CC);
     s.smem_bwd = sizeof(float) * (raw + 8 * S3_BB + 4 * (size_t) S3_BB * plan_.nlm +
                                   S3_NBS * (3 * (size_t) plan_.nlm * CC + 2 * (size_t) L.nlmi * CC + plan_.nlm) + 8);
