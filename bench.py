@@ -46,6 +46,7 @@ WORKLOADS = {
     # layers of every atom (1.5 MB per atom) in one pass: 31,250 atoms here; the 500,094-atom structure is the reference
     # arm's (which times a block of it)
     "grace3l_31k_bcc_hea": dict(cfg="3l", lattice="bcc", a=3.2, reps=(25, 25, 25), nsp=5, sigma=0.05, full=True),
+    "grace3l_3k_bcc_hea": dict(cfg="3l", lattice="bcc", a=3.2, reps=(12, 12, 12), nsp=5, sigma=0.05, full=True),    # ncu-sized
     "grace3l_500k_bcc_hea": dict(cfg="3l", lattice="bcc", a=3.2, reps=(63, 63, 63), nsp=5, sigma=0.05, full=True),
 }
 DEFAULT = "grace2l_1m_fcc_alloy"      # the 1,024,000-atom GRACE-2L configuration the target is stated on
