@@ -10,6 +10,7 @@
 #include "bond_common.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace gb {
 
@@ -118,6 +119,143 @@ __device__ __forceinline__ void s3_issue(const Spbf3Dev &L, const float *meta, i
     }
   }
   s3_cp_commit();
+}
+
+// ---- forward bond sums on the tensor cores --------------------------------------------------------------------------
+// For one atom and one channel c the bond sums are a small matrix product over the bonds j:
+//     P[ly][li] = sum_j U[j][ly] Ic[j][li],   U[j][ly] = Y_ly(j) R_l(ly)(j)[c],  Ic[j][li] = msg_j[li][c] + mask[li] z[mu_j][c]
+// with M = (lmax + 1)^2 <= 32 rows, N = message functions <= 32 columns, K = bonds.  A warp owns a channel and keeps the
+// 32 x 32 accumulators in registers (mma.sync m16n8k8 tf32, 2 x 4 tiles); every product is three instructions on hi / lo
+// splits (a_lo b_hi + a_hi b_lo + a_hi b_hi), which keeps fp32-level accuracy.  A CTA works on one atom and a slice of
+// 16 channels; the operands of 16 bonds at a time are staged in shared memory with a row stride of 40 floats, which
+// makes the fragment reads of a warp conflict-free.
+constexpr int S3M_CH = 16, S3M_GB = 16, S3M_LD = 40, S3M_CS = S3M_GB * S3M_LD + 1;    // CS: floats per channel block (odd: the
+                                                                                        // channel-major stores of the staging spread over the banks)
+
+__device__ __forceinline__ void s3_split(float x, unsigned &hi, unsigned &lo)
+{
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  const float r = x - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+__device__ __forceinline__ void s3_mma(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2])
+{
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(32 * S3M_CH) spbf3_fwd_mma_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA)
+{
+  extern __shared__ __align__(16) float sm[];
+  const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, nth = blockDim.x;
+  float *Us = sm, *Is = Us + S3M_CH * S3M_CS, *meta = Is + S3M_CH * S3M_CS + 3, *Ys = meta + 8 * S3_BB;
+  float *mask = Ys + S3_BB * nlm;
+  int *lts = reinterpret_cast<int *>(mask + 32);
+  const int i = blockIdx.x, c0 = blockIdx.y * S3M_CH, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const long long base = b.off[i];
+  const int nb = b.cnt[i], mui = b.mu[i];
+  float acc[2][4][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+      for (int r = 0; r < 4; r++) acc[mt][nt][r] = 0.0f;
+  for (int e = tid; e < nlm; e += nth) lts[e] = L.lt[e];
+  for (int e = tid; e < 32; e += nth) mask[e] = e < nlmi ? L.l0mask[e] : 0.0f;
+  for (int q0 = 0; q0 < nb; q0 += S3_BB) {
+    const int nq = min(S3_BB, nb - q0);
+    __syncthreads();    // harmonics and geometry of the previous batch are no longer read
+    for (int e = tid; e < nq; e += nth) {
+      const float4 rec = b.rec[base + q0 + e];
+      const float ir = rsqrtf(rec.x * rec.x + rec.y * rec.y + rec.z * rec.z);
+      stage_harmonics(sht, rec.x * ir, rec.y * ir, rec.z * ir, nlm, Ys + e * nlm, nullptr);
+      s3_bond_store(b, L, base + q0 + e, mui, meta + 8 * e);
+    }
+    for (int q = 0; q < nq; q += S3M_GB) {
+      const int ns = min(S3M_GB, nq - q);
+      __syncthreads();    // the operands of the previous group are no longer read; harmonics and geometry are staged
+      // operands of the group: rows (channel, bond), the function index runs along the lanes; rows of bonds beyond the
+      // group and functions beyond the model's are zero
+      for (int e = tid; e < S3M_CH * S3M_GB * 32; e += nth) {    // U: a warp per (channel, bond) row, the lanes along ly
+        const int f = e & 31, row = e >> 5, s = row % S3M_GB, ch = row / S3M_GB;
+        float u = 0.0f;
+        if (s < ns && f < nlm) {
+          const S3Bond B = s3_bond(meta + 8 * (q + s));
+          if (B.slot >= 0) {
+            const float4 cf = reinterpret_cast<const float4 *>(L.tab + (size_t) B.slot * L.tab_stride)[((size_t) B.k0 * L.nl + lts[f]) * C + c0 + ch];
+            u = Ys[(q + s) * nlm + f] * (cf.x + B.t * (cf.y + B.t * (cf.z + B.t * cf.w)));
+          }
+        }
+        Us[ch * S3M_CS + s * S3M_LD + f] = u;
+      }
+      for (int e = tid; e < S3M_GB * 32 * S3M_CH; e += nth) {    // Ic: the lanes along the channels (whole 64-byte pieces of a row)
+        const int ch = e % S3M_CH, f = (e / S3M_CH) & 31, s = e / (S3M_CH * 32);
+        float ic = 0.0f;
+        if (s < ns && f < nlmi) {
+          const S3Bond B = s3_bond(meta + 8 * (q + s));
+          ic = (L.msg ? L.msg[((size_t) B.j * nlmi + f) * C + c0 + ch] : 0.0f) + mask[f] * L.zproj[(size_t) B.muj * C + c0 + ch];
+        }
+        Is[ch * S3M_CS + s * S3M_LD + f] = ic;
+      }
+      __syncthreads();
+      const float *Uw = Us + warp * S3M_CS, *Iw = Is + warp * S3M_CS;
+#pragma unroll
+      for (int k8 = 0; k8 < S3M_GB; k8 += 8) {
+        if (k8 >= ns) break;
+        // A[m = ly][k = bond] = U[bond][ly], B[k = bond][n = li] = Ic[bond][li]
+        unsigned ah[2][4], al[2][4], bh[4][2], bl[4][2];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+          s3_split(Uw[(k8 + t) * S3M_LD + 16 * mt + g], ah[mt][0], al[mt][0]);
+          s3_split(Uw[(k8 + t) * S3M_LD + 16 * mt + g + 8], ah[mt][1], al[mt][1]);
+          s3_split(Uw[(k8 + t + 4) * S3M_LD + 16 * mt + g], ah[mt][2], al[mt][2]);
+          s3_split(Uw[(k8 + t + 4) * S3M_LD + 16 * mt + g + 8], ah[mt][3], al[mt][3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+          s3_split(Iw[(k8 + t) * S3M_LD + 8 * nt + g], bh[nt][0], bl[nt][0]);
+          s3_split(Iw[(k8 + t + 4) * S3M_LD + 8 * nt + g], bh[nt][1], bl[nt][1]);
+        }
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+          for (int nt = 0; nt < 4; nt++) {
+            s3_mma(acc[mt][nt], al[mt], bh[nt]);
+            s3_mma(acc[mt][nt], ah[mt], bl[nt]);
+            s3_mma(acc[mt][nt], ah[mt], bh[nt]);
+          }
+      }
+    }
+  }
+  // P of the 16 channels to shared memory [channel][ly][li] (32 x 33), then the couple: one thread per (function, channel)
+  __syncthreads();
+  float *Ps = sm;
+  {
+    float *Pw = Ps + warp * 32 * 33;
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+      for (int nt = 0; nt < 4; nt++) {
+        Pw[(16 * mt + g) * 33 + 8 * nt + 2 * t] = acc[mt][nt][0];
+        Pw[(16 * mt + g) * 33 + 8 * nt + 2 * t + 1] = acc[mt][nt][1];
+        Pw[(16 * mt + g + 8) * 33 + 8 * nt + 2 * t] = acc[mt][nt][2];
+        Pw[(16 * mt + g + 8) * 33 + 8 * nt + 2 * t + 1] = acc[mt][nt][3];
+      }
+  }
+  __syncthreads();
+  for (int e = tid; e < L.nfA * S3M_CH; e += nth) {
+    const int f = e / S3M_CH, ch = e - f * S3M_CH;
+    const float *Pc = Ps + ch * 32 * 33;
+    float v = 0.0f;
+    for (int k = L.cg_off[f]; k < L.cg_off[f + 1]; k++) {
+      const int q = L.cg_p[k], ly = q / nlmi, li = q - ly * nlmi;
+      v = fmaf(L.cg_v[k], Pc[ly * 33 + li], v);
+    }
+    A[((size_t) f * NA + i) * C + c0 + ch] = v;
+  }
 }
 
 constexpr int S3_NBS = 4;    // bonds staged and worked on together: one pair of barriers and one round of global loads for all
@@ -705,7 +843,21 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     float *base = S.arena[k].ensure((size_t) E.per_atom * NA);
     bind_arena(E, base, NA);
     const std::vector<TensorDev> &T = E.tensors_host;
-    GB_LAUNCH(spbf3_fwd_kernel, dim3(n, sh.slices), sh.threads, sh.smem_fwd, bonds, spbf(k), sht, T[L.tA].p, NA, sh.cshift, sh.nTI);
+    // GRACE_B200_3L_MMA=1: the bond sums as small matrix products on the tensor cores where the shape allows.  Same
+    // results; measured slower than the register-tile kernel so far (its operand staging, not the matrix instructions),
+    // so it is not the default
+    const bool simt_only = getenv("GRACE_B200_3L_MMA") == nullptr;    // read per evaluation
+    const size_t smem_mma = sizeof(float) * std::max<size_t>(2 * S3M_CH * S3M_CS + 3 + 8 * S3_BB + (size_t) S3_BB * plan_.nlm + 32 + 32,
+                                                              (size_t) S3M_CH * 32 * 33);
+    if (!simt_only && plan_.nlm <= 32 && L.nlmi <= 32 && L.C % S3M_CH == 0) {
+      static bool mma_attr = false;
+      if (!mma_attr) {
+        GB_CUDA(cudaFuncSetAttribute(spbf3_fwd_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        mma_attr = true;
+      }
+      GB_LAUNCH(spbf3_fwd_mma_kernel, dim3(n, L.C / S3M_CH), 32 * S3M_CH, smem_mma, bonds, spbf(k), sht, T[L.tA].p, NA);
+    } else
+      GB_LAUNCH(spbf3_fwd_kernel, dim3(n, sh.slices), sh.threads, sh.smem_fwd, bonds, spbf(k), sht, T[L.tA].p, NA, sh.cshift, sh.nTI);
     run(E, L.dense.fwd, mu, n, NA);
     if (k < 2) {
       S.msg[k].ensure((size_t) n * L.nfEQ * L.cEQ);

@@ -286,3 +286,22 @@ def test_gpu_tensor_core_operations(backend, small3l, monkeypatch):
     b = backend.System(backend.Model(small3l), ["Al", "Ni"]).compute(types, pos, cell, pbc)
     assert abs(a["energy"] - b["energy"]) / len(types) < 1e-6
     assert np.abs(a["forces"] - b["forces"]).max() < 2e-5 * max(1.0, np.abs(a["forces"]).max())
+
+
+@pytest.mark.gpu
+def test_gpu_forward_bond_sums_on_tensor_cores(backend, small3l, tmp_path, monkeypatch):
+    """GRACE_B200_3L_MMA=1: the forward bond sums as mma.sync tf32 matrix products (three instructions per product on
+    hi / lo splits) instead of the register-tile kernel: same energies."""
+    from oracle import refcpu
+    if not refcpu.available():
+        pytest.skip("oracle/_ref is not built")
+    monkeypatch.setenv("GRACE_B200_3L_MMA", "1")
+    p = modelgen3l.write_model_3l(str(tmp_path / "l4.npz"), elements=("Al", "Ni"), lmax=4, channels=(32, 16, 32), rho_width=16,
+                                  embedding=8, radial_hidden=32, seed=9)
+    for path in (small3l, p):
+        ref = refcpu.RefModel(path, ["Al", "Ni"])
+        sysm = backend.System(backend.Model(path), ["Al", "Ni"])
+        for name, types, pos, cell, pbc in list(_cells())[:3]:
+            r, g = ref.compute(types, pos, cell, pbc), sysm.compute(types, pos, cell, pbc, energies=True)
+            assert np.abs(g["energies"] - r["energies"]).max() < 5e-6, name
+            assert np.abs(g["forces"] - r["forces"]).max() < 2e-5 * max(1.0, np.abs(r["forces"]).max()), name
