@@ -42,9 +42,8 @@ WORKLOADS = {
     "grace2l_128k_fcc_alloy": dict(cfg="2l", lattice="fcc", a=3.6, reps=(20, 40, 40), nsp=3, sigma=0.08, full=True),
     # 4096 small periodic structures (16-256 atoms, triclinic, 0.06-0.09 atoms/A^3) through the Batch entry points
     "grace2l_batch4096": dict(cfg="2l", batch=4096, unique=128, nmin=16, nmax=256, nsp=89, full=True),
-    # GRACE-3L (lmax 4, 64 channels, 89 elements) on a 5-component bcc alloy.  The library keeps the tensors of all three
-    # layers of every atom (1.5 MB per atom) in one pass: 31,250 atoms here; the 500,094-atom structure is the reference
-    # arm's (which times a block of it)
+    # GRACE-3L (lmax 4, 64 channels, 89 elements) on a 5-component bcc alloy: 31,250 atoms fit one pass that keeps the
+    # tensors of all three layers (1.5 MB per atom); the 500,094-atom structure runs in passes over atom chunks
     "grace3l_31k_bcc_hea": dict(cfg="3l", lattice="bcc", a=3.2, reps=(25, 25, 25), nsp=5, sigma=0.05, full=True),
     "grace3l_3k_bcc_hea": dict(cfg="3l", lattice="bcc", a=3.2, reps=(12, 12, 12), nsp=5, sigma=0.05, full=True),    # ncu-sized
     "grace3l_500k_bcc_hea": dict(cfg="3l", lattice="bcc", a=3.2, reps=(63, 63, 63), nsp=5, sigma=0.05, full=True),
@@ -816,12 +815,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
-    elif WORKLOADS[args.workload]["cfg"] == "3l" and (world > 1 or int(np.prod(WORKLOADS[args.workload]["reps"])) * 2 > 100000):
+    elif WORKLOADS[args.workload]["cfg"] == "3l" and world > 1:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "unit": UNIT, "config": base_config(args.workload, world),
-                              "unavailable": "GRACE-3L runs on one GPU in one pass that keeps 1.5 MB of tensors per atom: up to "
-                                             "about 100,000 atoms (grace3l_31k_bcc_hea); --impl reference times the reference's "
-                                             "CPU engine on a block of this workload"}))
+                              "unavailable": "GRACE-3L runs on one GPU (no domain decomposition for three layers yet)"}))
     elif "batch" in WORKLOADS[args.workload]:
         run_batch(args, rank, world, local_rank)
     else:

@@ -145,14 +145,14 @@ __device__ __forceinline__ void s3_mma(float (&d)[4], const unsigned (&a)[4], co
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-__global__ void __launch_bounds__(32 * S3M_CH) spbf3_fwd_mma_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA)
+__global__ void __launch_bounds__(32 * S3M_CH) spbf3_fwd_mma_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA, int a0)
 {
   extern __shared__ __align__(16) float sm[];
   const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, nth = blockDim.x;
   float *Us = sm, *Is = Us + S3M_CH * S3M_CS, *meta = Is + S3M_CH * S3M_CS + 3, *Ys = meta + 8 * S3_BB;
   float *mask = Ys + S3_BB * nlm;
   int *lts = reinterpret_cast<int *>(mask + 32);
-  const int i = blockIdx.x, c0 = blockIdx.y * S3M_CH, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int a = blockIdx.x, i = a0 + a, c0 = blockIdx.y * S3M_CH, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const long long base = b.off[i];
   const int nb = b.cnt[i], mui = b.mu[i];
@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(32 * S3M_CH) spbf3_fwd_mma_kernel(BondsDev b, 
       const int q = L.cg_p[k], ly = q / nlmi, li = q - ly * nlmi;
       v = fmaf(L.cg_v[k], Pc[ly * 33 + li], v);
     }
-    A[((size_t) f * NA + i) * C + c0 + ch] = v;
+    A[((size_t) f * NA + a) * C + c0 + ch] = v;
   }
 }
 
@@ -262,7 +262,7 @@ constexpr int S3_NBS = 4;    // bonds staged and worked on together: one pair of
 
 // A[f][a][c] = sum_q cg[q, f] P[q][c],  P[(ly, li)][c] = sum_bonds Y_ly R[l(ly)][c] (msg_j[li][c] + mask[li] zproj[mu_j][c])
 __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, float *__restrict__ A, int NA, int cshift,
-                                                        int nTI)
+                                                        int nTI, int a0)
 {
   extern __shared__ __align__(16) float sm[];
   const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, CC = 1 << cshift, nth = blockDim.x;
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
   float *meta = zraw + 2 * S3_NBS * CC, *Ys = meta + 8 * S3_BB, *U = Ys + S3_BB * nlm, *Ic = U + (size_t) S3_NBS * nU,
         *As = Ic + (size_t) S3_NBS * nI, *mask = As + (size_t) L.nfA * CC;
   int *lts = reinterpret_cast<int *>(mask + nlmi);                    // l of each lm, and the mask of the message functions above
-  const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x;
+  const int ap = blockIdx.x, i = a0 + ap, c0 = blockIdx.y * CC, tid = threadIdx.x;
   const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
   const long long base = b.off[i];
   const int nb = b.cnt[i], mui = b.mu[i];
@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
   __syncthreads();
   for (int e = tid; e < L.nfA * CC; e += nth) {
     const int f = e >> cshift, cc = e & (CC - 1);
-    A[((size_t) f * NA + i) * C + c0 + cc] = As[e];
+    A[((size_t) f * NA + ap) * C + c0 + cc] = As[e];
   }
 }
 
@@ -358,7 +358,8 @@ __global__ void __launch_bounds__(832) spbf3_fwd_kernel(BondsDev b, Spbf3Dev L, 
 //   gY[ly] = sum_c W R_l[c] (a warp per ly),  dE/dx = sum_{ly, c} W Y_ly dR_l[c]
 // and the bond force is linear in (gY, dE/dx), so every channel slice adds its own share.
 __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, SHTable sht, const float *__restrict__ gA, int NA,
-                                                        float *__restrict__ fv, double *__restrict__ vir_atom, int cshift, int nTI)
+                                                        float *__restrict__ fv, double *__restrict__ vir_atom, int cshift, int nTI,
+                                                        int a0)
 {
   extern __shared__ __align__(16) float sm[];
   const int C = L.C, nlm = L.nlm, nlmi = L.nlmi, CC = 1 << cshift, nth = blockDim.x;
@@ -372,7 +373,7 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
   float *Ic = W + (size_t) S3_NBS * nU, *gI = Ic + (size_t) S3_NBS * nI, *gY = gI + (size_t) S3_NBS * nI, *dedx = gY + S3_NBS * nlm;
   float *mask = dedx + 8;
   int *lts = reinterpret_cast<int *>(mask + nlmi);
-  const int i = blockIdx.x, c0 = blockIdx.y * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ap = blockIdx.x, i = a0 + ap, c0 = blockIdx.y * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = tid & (CC - 1), g = tid >> cshift, tl = g / nTI, ti = g - tl * nTI, ly0 = S3_T * tl, li0 = S3_T * ti;
   const long long base = b.off[i];
   const int nb = b.cnt[i], mui = b.mu[i];
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(832) spbf3_bwd_kernel(BondsDev b, Spbf3Dev L, 
       float v = 0.0f;
       if (ly0 + a < nlm && li0 + q2 < nlmi) {
         const int q = (ly0 + a) * nlmi + li0 + q2;
-        for (int t = L.cgt_off[q]; t < L.cgt_off[q + 1]; t++) v = fmaf(L.cgt_v[t], gA[((size_t) L.cgt_f[t] * NA + i) * C + c0 + c], v);
+        for (int t = L.cgt_off[q]; t < L.cgt_off[q + 1]; t++) v = fmaf(L.cgt_v[t], gA[((size_t) L.cgt_f[t] * NA + ap) * C + c0 + c], v);
       }
       gp[a][q2] = v;
     }
@@ -521,10 +522,11 @@ struct EqNormDev {
 };
 
 // EquivariantRMSNorm of one atom per thread (libgrace/include/grace/fused_3l_cpu.h:346-370): x [f][NA][C] -> y rows [i][f][C]
-__global__ void eqnorm_fwd_kernel(EqNormDev E, const float *__restrict__ x, float *__restrict__ y, int NA, int n)
+__global__ void eqnorm_fwd_kernel(EqNormDev E, const float *__restrict__ x, float *__restrict__ y, int NA, int n, int a0)
 {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  y += (size_t) a0 * E.nf * E.C;    // rows of the atoms of the pass
   double S = 0.0;
   for (int f = 0; f < E.nf; f++) {
     const float *xf = x + ((size_t) f * NA + i) * E.C;
@@ -555,10 +557,11 @@ __global__ void eqnorm_fwd_kernel(EqNormDev E, const float *__restrict__ x, floa
 
 // gx [f][NA][C] = adjoint of the above for dy rows [i][f][C] (:373-415)
 __global__ void eqnorm_bwd_kernel(EqNormDev E, const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ gx, int NA,
-                                  int n)
+                                  int n, int a0)
 {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  dy += (size_t) a0 * E.nf * E.C;
   double S = 0.0, dot = 0.0;
   for (int f = 0; f < E.nf; f++) {
     const float *xf = x + ((size_t) f * NA + i) * E.C, *a = E.aff + (size_t) E.e[f] * E.C, *d = dy + ((size_t) i * E.nf + f) * E.C;
@@ -595,12 +598,12 @@ __global__ void eqnorm_bwd_kernel(EqNormDev E, const float *__restrict__ x, cons
 
 // RMSNorm of the density (:416-425): x [NA][wr] (one function) -> y rows [i][wr]; sum rows += y
 __global__ void rmsnorm_fwd_kernel(const float *__restrict__ x, const float *__restrict__ scale, int n0, int wr, float *__restrict__ sum,
-                                   int first, int n)
+                                   int first, int n, int a0)
 {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float *xi = x + (size_t) i * wr;
-  float *s = sum + (size_t) i * wr;
+  float *s = sum + (size_t) (a0 + i) * wr;
   double q = 0.0;
   for (int c = n0; c < wr; c++) q += (double) xi[c] * xi[c];
   const double r = 1.0 / sqrt(q / (wr - n0) + 1e-10);
@@ -611,11 +614,11 @@ __global__ void rmsnorm_fwd_kernel(const float *__restrict__ x, const float *__r
 }
 
 __global__ void rmsnorm_bwd_kernel(const float *__restrict__ x, const float *__restrict__ scale, int n0, int wr,
-                                   const float *__restrict__ dy, float *__restrict__ gx, int n)
+                                   const float *__restrict__ dy, float *__restrict__ gx, int n, int a0)
 {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const float *xi = x + (size_t) i * wr, *d = dy + (size_t) i * wr;
+  const float *xi = x + (size_t) i * wr, *d = dy + (size_t) (a0 + i) * wr;
   float *o = gx + (size_t) i * wr;
   double q = 0.0, g = 0.0;
   for (int c = n0; c < wr; c++) {
@@ -836,35 +839,88 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     GB_CUDA(cudaFuncSetAttribute(spbf3_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr_set = true;
   }
+  // Passes.  When the tensors of all three layers of all atoms fit the memory they are kept from the forward to the
+  // reverse pass (arena k holds layer k).  Otherwise every layer runs in passes over atom chunks through one arena, and
+  // the reverse pass of a layer evaluates the forward operations of a chunk again before it reverses them: the messages,
+  // their gradients and the densities live in per-atom rows outside the arenas either way.
+  long long per_all = 0, per_max = 0;
   for (int k = 0; k < 3; k++) {
+    per_all += S.E[k].per_atom;
+    per_max = std::max(per_max, S.E[k].per_atom);
+  }
+  size_t free_b = 0, total_b = 0;
+  if (cudaMemGetInfo(&free_b, &total_b) != cudaSuccess) free_b = (size_t) 8 << 30;
+  double budget = 0.7 * (double) free_b;
+  for (int k = 0; k < 3; k++) budget += 4.0 * (double) S.arena[k].capacity();
+  if (const char *env = getenv("GRACE_B200_3L_CHUNK")) budget = std::min(budget, 4.0 * per_all * std::max(4, atoi(env)) - 1.0);
+  const bool keep = 4.0 * (double) per_all * NA <= budget;
+  int NC = NA;    // atoms per pass (a multiple of 4: the atom stride of the arena)
+  if (!keep) {
+    NC = (int) std::min<double>(NA, std::max(512.0, budget / (4.0 * per_max)));
+    if (const char *env = getenv("GRACE_B200_3L_CHUNK")) NC = std::min(NC, std::max(4, atoi(env)));
+    NC = std::max(4, NC / 4 * 4);
+    for (int k = 1; k < 3; k++) S.arena[k].release();
+  }
+  const bool simt_only = getenv("GRACE_B200_3L_MMA") == nullptr;    // read per evaluation
+  // GRACE_B200_3L_MMA=1: the forward bond sums as small matrix products on the tensor cores where the shape allows.  Same
+  // results; measured slower than the register-tile kernel so far (its operand staging, not the matrix instructions),
+  // so it is not the default
+  const size_t smem_mma = sizeof(float) * std::max<size_t>(2 * S3M_CH * S3M_CS + 3 + 8 * S3_BB + (size_t) S3_BB * plan_.nlm + 32 + 32,
+                                                            (size_t) S3M_CH * 32 * 33);
+  static bool mma_attr = false;
+  if (!simt_only && !mma_attr) {
+    GB_CUDA(cudaFuncSetAttribute(spbf3_fwd_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    mma_attr = true;
+  }
+  // the arena of layer k bound for passes of NC atoms
+  auto bind = [&](int k) {
+    LayerEngine &E = S.E[k];
+    DBuf<float> &ar = S.arena[keep ? k : 0];
+    float *base = ar.ensure((size_t) (keep ? E.per_atom : per_max) * NC);
+    bind_arena(E, base, NC);
+    return base;
+  };
+  // forward operations of layer k for the atoms [a0, a0 + na); outputs: the message rows and the density sums
+  auto forward = [&](int k, int a0, int na, bool outputs) {
     const Layer3Plan &L = Q.L[k];
     const Shape sh = shape(L);
     LayerEngine &E = S.E[k];
-    float *base = S.arena[k].ensure((size_t) E.per_atom * NA);
-    bind_arena(E, base, NA);
     const std::vector<TensorDev> &T = E.tensors_host;
-    // GRACE_B200_3L_MMA=1: the bond sums as small matrix products on the tensor cores where the shape allows.  Same
-    // results; measured slower than the register-tile kernel so far (its operand staging, not the matrix instructions),
-    // so it is not the default
-    const bool simt_only = getenv("GRACE_B200_3L_MMA") == nullptr;    // read per evaluation
-    const size_t smem_mma = sizeof(float) * std::max<size_t>(2 * S3M_CH * S3M_CS + 3 + 8 * S3_BB + (size_t) S3_BB * plan_.nlm + 32 + 32,
-                                                              (size_t) S3M_CH * 32 * 33);
-    if (!simt_only && plan_.nlm <= 32 && L.nlmi <= 32 && L.C % S3M_CH == 0) {
-      static bool mma_attr = false;
-      if (!mma_attr) {
-        GB_CUDA(cudaFuncSetAttribute(spbf3_fwd_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        mma_attr = true;
-      }
-      GB_LAUNCH(spbf3_fwd_mma_kernel, dim3(n, L.C / S3M_CH), 32 * S3M_CH, smem_mma, bonds, spbf(k), sht, T[L.tA].p, NA);
-    } else
-      GB_LAUNCH(spbf3_fwd_kernel, dim3(n, sh.slices), sh.threads, sh.smem_fwd, bonds, spbf(k), sht, T[L.tA].p, NA, sh.cshift, sh.nTI);
-    run(E, L.dense.fwd, mu, n, NA);
+    const int nbk = (na + nt - 1) / nt;
+    if (!simt_only && plan_.nlm <= 32 && L.nlmi <= 32 && L.C % S3M_CH == 0)
+      GB_LAUNCH(spbf3_fwd_mma_kernel, dim3(na, L.C / S3M_CH), 32 * S3M_CH, smem_mma, bonds, spbf(k), sht, T[L.tA].p, NC, a0);
+    else
+      GB_LAUNCH(spbf3_fwd_kernel, dim3(na, sh.slices), sh.threads, sh.smem_fwd, bonds, spbf(k), sht, T[L.tA].p, NC, sh.cshift, sh.nTI, a0);
+    run(E, L.dense.fwd, mu + a0, na, NC);
+    if (!outputs) return;
     if (k < 2) {
-      S.msg[k].ensure((size_t) n * L.nfEQ * L.cEQ);
       const EqNormDev e{S.eq_dw[k].get(), S.eq_mask[k].get(), S.eq_aff[k].get(), S.eq_e[k].get(), L.nfEQ, L.cEQ, L.eq_center, L.eq_eps};
-      GB_LAUNCH(eqnorm_fwd_kernel, nblk, nt, 0, e, T[L.tEQ].p, S.msg[k].get(), NA, n);
+      GB_LAUNCH(eqnorm_fwd_kernel, nbk, nt, 0, e, T[L.tEQ].p, S.msg[k].get(), NC, na, a0);
     }
-    GB_LAUNCH(rmsnorm_fwd_kernel, nblk, nt, 0, T[L.tRHO].p, S.rho_scale[k].get(), L.rho_n0, wr, S.rho_sum.get(), k == 0 ? 1 : 0, n);
+    GB_LAUNCH(rmsnorm_fwd_kernel, nbk, nt, 0, T[L.tRHO].p, S.rho_scale[k].get(), L.rho_n0, wr, S.rho_sum.get(), k == 0 ? 1 : 0, na, a0);
+  };
+  // reverse operations of layer k for the atoms [a0, a0 + na), whose forward tensors are in the bound arena
+  auto reverse = [&](int k, int a0, int na, float *base) {
+    const Layer3Plan &L = Q.L[k];
+    const Shape sh = shape(L);
+    LayerEngine &E = S.E[k];
+    const std::vector<TensorDev> &T = E.tensors_host;
+    const int nbk = (na + nt - 1) / nt;
+    if (L.dense.zero_grads)
+      launch_fill_zero(base + (size_t) E.grad_begin * NC, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * NC);
+    GB_LAUNCH(rmsnorm_bwd_kernel, nbk, nt, 0, T[L.tRHO].p, S.rho_scale[k].get(), L.rho_n0, wr, S.drho.get(), T[L.tGRHO].p, na, a0);
+    if (k < 2) {
+      const EqNormDev e{S.eq_dw[k].get(), S.eq_mask[k].get(), S.eq_aff[k].get(), S.eq_e[k].get(), L.nfEQ, L.cEQ, L.eq_center, L.eq_eps};
+      GB_LAUNCH(eqnorm_bwd_kernel, nbk, nt, 0, e, T[L.tEQ].p, S.gmsg[k].get(), T[L.tGEQ].p, NC, na, a0);
+    }
+    run(E, L.dense.bwd, mu + a0, na, NC);
+    GB_LAUNCH(spbf3_bwd_kernel, dim3(na, sh.slices), sh.threads, sh.smem_bwd, bonds, spbf(k), sht, T[L.tGA].p, NC, fv_.get(), vir_atom_.get(),
+              sh.cshift, sh.nTI, a0);
+  };
+  for (int k = 0; k < 2; k++) S.msg[k].ensure((size_t) n * Q.L[k].nfEQ * Q.L[k].cEQ);
+  for (int k = 0; k < 3; k++) {
+    bind(k);
+    for (int a0 = 0; a0 < n; a0 += NC) forward(k, a0, std::min(NC, n - a0), true);
   }
   const Readout3Dev ro{S.eW0.get(), S.eW1.get(), shift_.get(), Q.en0, Q.en1, plan_.out_scale, Q.e_nin, Q.e_nh, Q.e_act};
   GB_LAUNCH(readout3_kernel, nblk, nt, 0, ro, S.rho_sum.get(), mu, e_atom_.get(), S.drho.get(), energy_only ? 0 : 1, n);
@@ -883,21 +939,12 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
     launch_fill_zero(S.gmsg[k].get(), sizeof(float) * (size_t) n * L.nfEQ * L.cEQ);
   }
   for (int k = 2; k >= 0; k--) {
-    const Layer3Plan &L = Q.L[k];
-    LayerEngine &E = S.E[k];
-    const std::vector<TensorDev> &T = E.tensors_host;
-    bind_arena(E, S.arena[k].get(), NA);
-    if (L.dense.zero_grads)
-      launch_fill_zero(S.arena[k].get() + (size_t) E.grad_begin * NA, sizeof(float) * (size_t) (E.grad_end - E.grad_begin) * NA);
-    GB_LAUNCH(rmsnorm_bwd_kernel, nblk, nt, 0, T[L.tRHO].p, S.rho_scale[k].get(), L.rho_n0, wr, S.drho.get(), T[L.tGRHO].p, n);
-    if (k < 2) {
-      const EqNormDev e{S.eq_dw[k].get(), S.eq_mask[k].get(), S.eq_aff[k].get(), S.eq_e[k].get(), L.nfEQ, L.cEQ, L.eq_center, L.eq_eps};
-      GB_LAUNCH(eqnorm_bwd_kernel, nblk, nt, 0, e, T[L.tEQ].p, S.gmsg[k].get(), T[L.tGEQ].p, NA, n);
+    float *base = bind(k);
+    for (int a0 = 0; a0 < n; a0 += NC) {
+      const int na = std::min(NC, n - a0);
+      if (!keep) forward(k, a0, na, false);    // the chunk's forward tensors again
+      reverse(k, a0, na, base);
     }
-    run(E, L.dense.bwd, mu, n, NA);
-    const Shape sh = shape(L);
-    GB_LAUNCH(spbf3_bwd_kernel, dim3(n, sh.slices), sh.threads, sh.smem_bwd, bonds, spbf(k), sht, T[L.tGA].p, NA, fv_.get(), vir_atom_.get(), sh.cshift,
-              sh.nTI);
   }
   if (tm) tm->end(StageTimer::BWD);
   check_tc();

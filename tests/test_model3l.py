@@ -305,3 +305,18 @@ def test_gpu_forward_bond_sums_on_tensor_cores(backend, small3l, tmp_path, monke
             r, g = ref.compute(types, pos, cell, pbc), sysm.compute(types, pos, cell, pbc, energies=True)
             assert np.abs(g["energies"] - r["energies"]).max() < 5e-6, name
             assert np.abs(g["forces"] - r["forces"]).max() < 2e-5 * max(1.0, np.abs(r["forces"]).max()), name
+
+
+@pytest.mark.gpu
+def test_gpu_passes_over_atom_chunks(backend, small3l, monkeypatch):
+    """GRACE_B200_3L_CHUNK: every layer in passes of at most that many atoms through one arena, the reverse pass
+    recomputing the forward tensors of a chunk (what structures too large to keep all tensors get): same results as
+    the single pass that keeps them."""
+    name, types, pos, cell, pbc = next(_cells())
+    sysm = backend.System(backend.Model(small3l), ["Al", "Ni"])
+    a = sysm.compute(types, pos, cell, pbc, energies=True)
+    monkeypatch.setenv("GRACE_B200_3L_CHUNK", "12")      # 32 atoms: passes of 12, 12 and 8
+    b = sysm.compute(types, pos, cell, pbc, energies=True)
+    assert np.abs(a["energies"] - b["energies"]).max() < 1e-6
+    assert np.abs(a["forces"] - b["forces"]).max() < 2e-5 * max(1.0, np.abs(a["forces"]).max())
+    assert np.abs(a["virial"] - b["virial"]).max() < 2e-5 * max(1.0, np.abs(a["virial"]).max())
