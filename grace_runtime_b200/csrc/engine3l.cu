@@ -2,9 +2,10 @@
 // the single-particle basis (per-pair radial tables, spherical harmonics, the normalised message of the layer before
 // coupled in through the sparse cg_W), the dense chain of the layer as MV / PROD operations of the plan (cp_l
 // projections, couples, reduces, FCs: the same kernels as GRACE-1L / 2L), EquivariantRMSNorm of the message and RMSNorm
-// of the density; the readout on the sum of the three densities; then everything in reverse.  All tensors of the three
-// layers are kept for the reverse pass and every atom is evaluated in one pass: this first form of the path is written
-// for clarity and checked against the reference's CPU engine, not tuned.
+// of the density; the readout on the sum of the three densities; then everything in reverse.  While they fit, the
+// tensors of the three layers of all atoms are kept for the reverse pass; larger structures run every layer in passes
+// over atom chunks and recompute a chunk's forward tensors when it is reversed.  A first form of the path, checked
+// against the reference's CPU engine; its bond kernels are bound by instruction issue and not tuned.
 #include "engine.h"
 
 #include "bond_common.cuh"
@@ -776,9 +777,8 @@ void Engine::evaluate_3l(NeighborList &nl, bool energy_only, StageTimer *tm)
       throw DeviceError("the tensor-core FC kernel gave up waiting for its matrix instructions");
     }
   };
-  {    // every bond of the structure needs the table of its element pair: a pair outside the Systems' species has none
-    // (checked on the host: the species of every System of the engine were prepared when it was created)
-  }
+  // every bond needs the radial table of its element pair: the species of every System / Batch of this engine were
+  // prepared when it was created (prepare_species); a bond of a pair without a table is left out by the kernels
   if (tm) tm->begin(StageTimer::FWD);
   const int wr = Q.L[0].wr;
   S.rho_sum.ensure((size_t) n * wr);
