@@ -95,12 +95,14 @@ int grace_profile_report(char *buf, size_t len);
  * this ABI).  The first call on a device also looks up the array's address: make it before any stream capture. */
 int grace_sum_rows_static(const double *d_values, int64_t n, int k, double *d_out);
 
-/* ---- Model (kk_api.h:51-64): a loaded GRACE-1L / GRACE-2L kokkos.npz ---- */
+/* ---- Model (kk_api.h:51-64): a loaded GRACE-1L / GRACE-2L / GRACE-3L kokkos.npz ---- */
 /* spline: intervals of the radial cubic Hermite tables (reference default 1024; >= 16), or 0: no tables, the exact
  * radial MLP per bond as in the reference's generic engine (tensor-core kernel; needs slots x outputs x 8 bytes of
- * device memory per layer and an 8 -> 64 -> 64 -> n radial MLP) */
+ * device memory per layer and an 8 -> 64 -> 64 -> n radial MLP; GRACE-1L / 2L only).  GRACE-3L models evaluate on one
+ * GPU through the System / Batch entry points below; the UQ flag, grace_system_set_owned / set_exchange and the engine
+ * interface answer GRACE_UNSUPPORTED or GRACE_INVALID_ARGUMENT for them */
 int grace_model_load(const char *path, int spline, grace_model **out);   /* Model(path, spline) */
-int grace_model_layers(const grace_model *m);                            /* layers(): 1 or 2 */
+int grace_model_layers(const grace_model *m);                            /* layers(): 1, 2 or 3 */
 int grace_model_has_uq(const grace_model *m);                            /* has_uq(): the file carries a UQ head */
 /* validate_uq() (kk_api.h:59): GRACE_OK, or GRACE_INVALID_ARGUMENT with the reason the head cannot be evaluated (none
  * in the file, a schema other than 6, a max_order 3 model, array sizes that do not match the model) */
