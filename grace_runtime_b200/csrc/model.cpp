@@ -505,17 +505,17 @@ GraceModel GraceModel::load(const std::string &path)
     m.m3 = std::make_shared<Grace3LModel>(Grace3LModel::load(z));
     const Grace3LModel &t = *m.m3;
     m.n_elements = t.n_elements;
-    m.embedding = t.embedding_size;
+    m.embedding = t.embedding;
     m.lmax = t.lmax;
-    m.nradbase = t.nradbase;
-    m.p = t.radial_basis_p;
-    m.rcut = t.rcut;
-    m.bond_specific = t.has_bond_specific_cutoff;
-    m.bond_cutoff = t.bond_cutoff_map;
-    m.element_names = t.element_names;
-    m.chem = t.chem_embedding;
-    m.output_scale = t.output_scale;
-    m.shift = t.shift_values;
+    m.nradbase = t.nbasis;
+    m.p = t.env_p;
+    m.rcut = t.cutoff;
+    m.bond_specific = t.pair_cutoffs_given;
+    m.bond_cutoff = t.pair_cutoff;
+    m.element_names = t.elements;
+    m.chem = t.embedding_table;
+    m.output_scale = t.energy_scale;
+    m.shift = t.energy_shift;
     if (z.has("uq_schema_version")) throw ModelError("GRACE-3L: the UQ head of GRACE-3L models is not supported");
     return m;
   }

@@ -55,210 +55,210 @@ double cutoff_scalar(const Npz &z, const std::string &key, double def)
 
 // prefix_n_layers layers prefix_W{i} [n_in, n_out] chained from n_in to n_out, scalar norms prefix_norm{i}, optional
 // biases prefix_b{i}
-void read_mlp(const Npz &z, const std::string &prefix, Grace3LModel::Mlp &m, int64_t n_in, int64_t n_out, const std::string &in_why,
+void read_mlp(const Npz &z, const std::string &prefix, Grace3LModel::DenseStack &m, int64_t n_in, int64_t n_out, const std::string &in_why,
               const std::string &out_why)
 {
-  m.n_layers = size_key(z, prefix + "_n_layers");
-  if (z.has(prefix + "_W" + num(m.n_layers)))
-    throw bad_array(prefix + "_n_layers", "is " + num(m.n_layers) + ", but the file has " + prefix + "_W" + num(m.n_layers));
+  m.depth = size_key(z, prefix + "_n_layers");
+  if (z.has(prefix + "_W" + num(m.depth)))
+    throw bad_array(prefix + "_n_layers", "is " + num(m.depth) + ", but the file has " + prefix + "_W" + num(m.depth));
   int64_t prev = n_in;
-  for (int i = 0; i < m.n_layers; i++) {
+  for (int i = 0; i < m.depth; i++) {
     const std::string wk = prefix + "_W" + num(i), bk = prefix + "_b" + num(i);
     const auto s = shape_of_rank(z, wk, 2);
     want_equal(wk, s[0], prev, i ? "the columns of " + prefix + "_W" + num(i - 1) : in_why);
-    m.W.push_back(z.reals(wk));
-    m.b.push_back(z.reals(bk, false));
+    m.weight.push_back(z.reals(wk));
+    m.bias.push_back(z.reals(bk, false));
     if (z.has(bk)) {
-      want_count(bk, m.b.back().size(), (size_t) s[1]);
-      m.has_bias = true;
+      want_count(bk, m.bias.back().size(), (size_t) s[1]);
+      m.biased = true;
     }
-    m.norm.push_back(z.real_scalar(prefix + "_norm" + num(i), 1.0));
-    m.n_in.push_back((int) s[0]);
-    m.n_out.push_back((int) s[1]);
+    m.scale.push_back(z.real_scalar(prefix + "_norm" + num(i), 1.0));
+    m.fan_in.push_back((int) s[0]);
+    m.fan_out.push_back((int) s[1]);
     prev = s[1];
   }
-  want_equal(prefix + "_W" + num(m.n_layers - 1), prev, n_out, out_why);
+  want_equal(prefix + "_W" + num(m.depth - 1), prev, n_out, out_why);
 }
 
-Grace3LModel::Spbf read_spbf(const Npz &z, const std::string &nm, const Grace3LModel &m)
+Grace3LModel::BondBasis read_spbf(const Npz &z, const std::string &nm, const Grace3LModel &m)
 {
-  Grace3LModel::Spbf s;
+  Grace3LModel::BondBasis s;
   const int nl = m.lmax + 1, nlm = nl * nl;
   s.name = nm;
-  s.equivariant = flag(z, nm + "_equivariant", 0);
-  s.n_rad_max = size_key(z, nm + "_n_rad_max");
-  s.n_rad_basis = z.int_scalar(nm + "_n_rad_basis", m.nradbase);
-  want_equal(nm + "_n_rad_basis", s.n_rad_basis, m.nradbase, "nradbase, the Chebyshev inputs of the radial MLP");
+  s.coupled = flag(z, nm + "_equivariant", 0);
+  s.channels = size_key(z, nm + "_n_rad_max");
+  s.nbasis = z.int_scalar(nm + "_n_rad_basis", m.nbasis);
+  want_equal(nm + "_n_rad_basis", s.nbasis, m.nbasis, "nradbase, the Chebyshev inputs of the radial MLP");
   s.lmax = z.int_scalar(nm + "_lmax", 4);
   want_equal(nm + "_lmax", s.lmax, m.lmax, "the model's lmax");
   s.Lmax = z.int_in(nm + "_Lmax", 4, 0, kMaxL);
-  s.p = z.int_in(nm + "_p", 5, 1, kMaxP);
-  s.rcut = cutoff_scalar(z, nm + "_rcut", m.rcut);
-  s.inv_avg_n_neigh = z.real_scalar(nm + "_inv_avg_n_neigh", 1.0);
-  s.l_tile = z.ints(nm + "_l_tile");
-  want_count(nm + "_l_tile", s.l_tile.size(), (size_t) nlm);
-  want_below(nm + "_l_tile", s.l_tile, nl);
-  read_mlp(z, nm + "_mlp", s.mlp, m.nradbase + 2 * m.embedding_size, (int64_t) s.n_rad_max * nl, "nradbase + 2 embedding_size",
+  s.env_p = z.int_in(nm + "_p", 5, 1, kMaxP);
+  s.cutoff = cutoff_scalar(z, nm + "_rcut", m.cutoff);
+  s.inv_neigh = z.real_scalar(nm + "_inv_avg_n_neigh", 1.0);
+  s.l_of_lm = z.ints(nm + "_l_tile");
+  want_count(nm + "_l_tile", s.l_of_lm.size(), (size_t) nlm);
+  want_below(nm + "_l_tile", s.l_of_lm, nl);
+  read_mlp(z, nm + "_mlp", s.radial, m.nbasis + 2 * m.embedding, (int64_t) s.channels * nl, "nradbase + 2 embedding_size",
            "n_rad_max (lmax + 1)");
-  if (!s.equivariant) {
-    s.lin_transform_W = z.reals(nm + "_lin_transform_W");
-    z.require_shape(nm + "_lin_transform_W", {m.embedding_size, s.n_rad_max});
-    s.lin_transform_norm = z.real_scalar(nm + "_lin_transform_norm", 1.0);
+  if (!s.coupled) {
+    s.z_weight = z.reals(nm + "_lin_transform_W");
+    z.require_shape(nm + "_lin_transform_W", {m.embedding, s.channels});
+    s.z_scale = z.real_scalar(nm + "_lin_transform_norm", 1.0);
   } else {
-    s.nfunc = size_key(z, nm + "_nfunc");
-    s.n_lm_ind = size_key(z, nm + "_n_lm_ind");
-    s.chem_linear_W = z.reals(nm + "_chem_linear_W");
-    z.require_shape(nm + "_chem_linear_W", {m.embedding_size, s.n_rad_max});
-    s.chem_linear_norm = z.real_scalar(nm + "_chem_linear_norm", 1.0);
-    s.chem_l0_mask = z.reals(nm + "_chem_l0_mask");
-    want_count(nm + "_chem_l0_mask", s.chem_l0_mask.size(), (size_t) s.n_lm_ind);
-    s.cg_W = z.reals(nm + "_cg_W");
-    z.require_shape(nm + "_cg_W", {(int64_t) nlm * s.n_lm_ind, s.nfunc});
+    s.n_coupled = size_key(z, nm + "_nfunc");
+    s.n_msg = size_key(z, nm + "_n_lm_ind");
+    s.zc_weight = z.reals(nm + "_chem_linear_W");
+    z.require_shape(nm + "_chem_linear_W", {m.embedding, s.channels});
+    s.zc_scale = z.real_scalar(nm + "_chem_linear_norm", 1.0);
+    s.msg_mask = z.reals(nm + "_chem_l0_mask");
+    want_count(nm + "_chem_l0_mask", s.msg_mask.size(), (size_t) s.n_msg);
+    s.couple = z.reals(nm + "_cg_W");
+    z.require_shape(nm + "_cg_W", {(int64_t) nlm * s.n_msg, s.n_coupled});
   }
   return s;
 }
 
-Grace3LModel::Cpl read_cpl(const Npz &z, const std::string &nm)
+Grace3LModel::LowRank read_cpl(const Npz &z, const std::string &nm)
 {
-  Grace3LModel::Cpl c;
+  Grace3LModel::LowRank c;
   c.name = nm;
   c.rank = size_key(z, nm + "_rank");
-  c.nfunc = size_key(z, nm + "_nfunc");
-  c.n_left = size_key(z, nm + "_n_left");
-  c.n_right = size_key(z, nm + "_n_right");
-  c.n_groups_left = size_key(z, nm + "_n_groups_left");
-  c.n_groups_right = size_key(z, nm + "_n_groups_right");
-  c.norm_u = z.real_scalar(nm + "_norm_u", 1.0);
-  c.norm_v = z.real_scalar(nm + "_norm_v", 1.0);
+  c.n_out = size_key(z, nm + "_nfunc");
+  c.width_l = size_key(z, nm + "_n_left");
+  c.width_r = size_key(z, nm + "_n_right");
+  c.groups_l = size_key(z, nm + "_n_groups_left");
+  c.groups_r = size_key(z, nm + "_n_groups_right");
+  c.scale_u = z.real_scalar(nm + "_norm_u", 1.0);
+  c.scale_v = z.real_scalar(nm + "_norm_v", 1.0);
   c.U = z.reals(nm + "_U");
-  z.require_shape(nm + "_U", {c.n_groups_left, c.rank, c.n_left});
+  z.require_shape(nm + "_U", {c.groups_l, c.rank, c.width_l});
   c.V = z.reals(nm + "_V");
-  z.require_shape(nm + "_V", {c.n_groups_right, c.rank, c.n_right});
-  c.cg = z.reals(nm + "_cg");
-  c.n_cg = (int) c.cg.size();
-  c.group_left = z.ints(nm + "_group_left");
-  want_below(nm + "_group_left", c.group_left, c.n_groups_left);
-  c.group_right = z.ints(nm + "_group_right");
-  want_below(nm + "_group_right", c.group_right, c.n_groups_right);
+  z.require_shape(nm + "_V", {c.groups_r, c.rank, c.width_r});
+  c.coef = z.reals(nm + "_cg");
+  c.nterms = (int) c.coef.size();
+  c.group_l = z.ints(nm + "_group_left");
+  want_below(nm + "_group_left", c.group_l, c.groups_l);
+  c.group_r = z.ints(nm + "_group_right");
+  want_below(nm + "_group_right", c.group_r, c.groups_r);
   const struct {
     const char *key;
     std::vector<int> *v;
     int64_t bound;
-  } terms[] = {{"_left_ind", &c.left_ind, (int64_t) c.group_left.size()},
-               {"_right_ind", &c.right_ind, (int64_t) c.group_right.size()},
-               {"_m_sum_ind", &c.m_sum_ind, c.nfunc}};
+  } terms[] = {{"_left_ind", &c.term_l, (int64_t) c.group_l.size()},
+               {"_right_ind", &c.term_r, (int64_t) c.group_r.size()},
+               {"_m_sum_ind", &c.term_out, c.n_out}};
   for (const auto &t : terms) {
     *t.v = z.ints(nm + t.key);
-    want_count(nm + t.key, t.v->size(), (size_t) c.n_cg);
+    want_count(nm + t.key, t.v->size(), (size_t) c.nterms);
     want_below(nm + t.key, *t.v, t.bound);
   }
-  c.out_l = z.ints(nm + "_out_l");
-  want_count(nm + "_out_l", c.out_l.size(), (size_t) c.nfunc);
-  want_below(nm + "_out_l", c.out_l, kMaxL + 1);
+  c.l_of_out = z.ints(nm + "_out_l");
+  want_count(nm + "_out_l", c.l_of_out.size(), (size_t) c.n_out);
+  want_below(nm + "_out_l", c.l_of_out, kMaxL + 1);
   return c;
 }
 
-Grace3LModel::Reduce read_reduce(const Npz &z, const std::string &nm, int n_elements)
+Grace3LModel::Collect read_reduce(const Npz &z, const std::string &nm, int n_elements)
 {
-  Grace3LModel::Reduce r;
+  Grace3LModel::Collect r;
   r.name = nm;
-  r.n_out = size_key(z, nm + "_n_out");
-  r.n_funcs = size_key(z, nm + "_n_funcs");
-  r.only_invar = flag(z, nm + "_only_invar", 0);
-  r.elem_dep = flag(z, nm + "_is_central_atom_type_dependent", 0);
-  const int nfo = r.only_invar ? 1 : r.n_funcs;
+  r.width = size_key(z, nm + "_n_out");
+  r.nfuncs = size_key(z, nm + "_n_funcs");
+  r.invariant = flag(z, nm + "_only_invar", 0);
+  r.per_element = flag(z, nm + "_is_central_atom_type_dependent", 0);
+  const int nfo = r.invariant ? 1 : r.nfuncs;
   for (const std::string &src : z.names(nm + "_instruction_names")) {
-    Grace3LModel::ReduceInstr in;
-    in.name = src;
-    in.n_in = size_key(z, nm + "_n_in_" + src);
-    in.w_shape = size_key(z, nm + "_w_shape_" + src);
+    Grace3LModel::Source in;
+    in.from = src;
+    in.width = size_key(z, nm + "_n_in_" + src);
+    in.tiles = size_key(z, nm + "_w_shape_" + src);
     const std::string wk = nm + "_reduce_" + src + "_W";
-    in.W = z.reals(wk);
-    if (r.elem_dep) z.require_shape(wk, {n_elements, r.n_out, in.n_in, in.w_shape});
-    else z.require_shape(wk, {r.n_out, in.n_in, in.w_shape});
-    in.norm = z.real_scalar(nm + "_reduce_" + src + "_norm", 1.0);
-    in.collect_ind = z.ints(nm + "_collect_ind_" + src);    // range checked against the producer in the graph walk
-    in.n_conn = (int) in.collect_ind.size();
-    in.w_l_tile = z.ints(nm + "_w_l_tile_" + src);
-    want_count(nm + "_w_l_tile_" + src, in.w_l_tile.size(), (size_t) in.n_conn);
-    want_below(nm + "_w_l_tile_" + src, in.w_l_tile, in.w_shape);
-    in.total_sum_ind = z.ints(nm + "_total_sum_ind_" + src);
-    want_count(nm + "_total_sum_ind_" + src, in.total_sum_ind.size(), (size_t) in.n_conn);
-    want_below(nm + "_total_sum_ind_" + src, in.total_sum_ind, nfo);
-    r.instr.push_back(std::move(in));
+    in.weight = z.reals(wk);
+    if (r.per_element) z.require_shape(wk, {n_elements, r.width, in.width, in.tiles});
+    else z.require_shape(wk, {r.width, in.width, in.tiles});
+    in.scale = z.real_scalar(nm + "_reduce_" + src + "_norm", 1.0);
+    in.pick = z.ints(nm + "_collect_ind_" + src);    // range checked against the producer in the graph walk
+    in.nconn = (int) in.pick.size();
+    in.tile_of = z.ints(nm + "_w_l_tile_" + src);
+    want_count(nm + "_w_l_tile_" + src, in.tile_of.size(), (size_t) in.nconn);
+    want_below(nm + "_w_l_tile_" + src, in.tile_of, in.tiles);
+    in.into = z.ints(nm + "_total_sum_ind_" + src);
+    want_count(nm + "_total_sum_ind_" + src, in.into.size(), (size_t) in.nconn);
+    want_below(nm + "_total_sum_ind_" + src, in.into, nfo);
+    r.sources.push_back(std::move(in));
   }
-  r.has_norm_map = z.has(nm + "_norm_map");    // the reduce's own key, not the `<name>_norm_*` keys of an RMS norm
-  r.norm_map = z.reals(nm + "_norm_map", false);
-  if (r.has_norm_map) want_count(nm + "_norm_map", r.norm_map.size(), (size_t) nfo);
+  r.row_scaled = z.has(nm + "_norm_map");    // the reduce's own key, not the `<name>_norm_*` keys of an RMS norm
+  r.row_scale = z.reals(nm + "_norm_map", false);
+  if (r.row_scaled) want_count(nm + "_norm_map", r.row_scale.size(), (size_t) nfo);
   return r;
 }
 
-Grace3LModel::Fc read_fc(const Npz &z, const std::string &nm)
+Grace3LModel::Mix read_fc(const Npz &z, const std::string &nm)
 {
-  Grace3LModel::Fc f;
+  Grace3LModel::Mix f;
   f.name = nm;
   const std::string p = "fc_" + nm;
-  f.n_out = size_key(z, p + "_n_out");
-  f.left_coefs = flag(z, p + "_left_coefs", 0);
+  f.width = size_key(z, p + "_n_out");
+  f.weighted_left = flag(z, p + "_left_coefs", 0);
   f.w_right = z.reals(p + "_w_right");
   const auto wr = shape_of_rank(z, p + "_w_right", 3);    // [n_out, n_in_right, tiles]
-  want_equal(p + "_w_right", wr[0], f.n_out, p + "_n_out");
-  f.n_in_right = (int) wr[1];
-  f.w_shape_right = (int) wr[2];
-  f.norm_right = z.real_scalar(p + "_norm_right", 1.0);
-  f.n_funcs_left = (int) shape_of_rank(z, p + "_w_tile_left", 1)[0];
-  f.norm_out_factor = z.reals(p + "_norm_out_factor");
-  want_count(p + "_norm_out_factor", f.norm_out_factor.size(), (size_t) f.n_funcs_left);
-  f.collect_from = z.ints(p + "_collect_from");
-  f.n_funcs_right = (int) f.collect_from.size();
-  f.collect_to = z.ints(p + "_collect_to");
-  want_count(p + "_collect_to", f.collect_to.size(), (size_t) f.n_funcs_right);
-  want_below(p + "_collect_to", f.collect_to, f.n_funcs_left);
-  f.w_tile_right = z.ints(p + "_w_tile_right");
-  want_count(p + "_w_tile_right", f.w_tile_right.size(), (size_t) f.n_funcs_right);
-  want_below(p + "_w_tile_right", f.w_tile_right, f.w_shape_right);
-  if (f.left_coefs) {
-    f.w_tile_left = z.ints(p + "_w_tile_left");
+  want_equal(p + "_w_right", wr[0], f.width, p + "_n_out");
+  f.in_right = (int) wr[1];
+  f.tiles_right = (int) wr[2];
+  f.scale_right = z.real_scalar(p + "_norm_right", 1.0);
+  f.nf_left = (int) shape_of_rank(z, p + "_w_tile_left", 1)[0];
+  f.out_factor = z.reals(p + "_norm_out_factor");
+  want_count(p + "_norm_out_factor", f.out_factor.size(), (size_t) f.nf_left);
+  f.from = z.ints(p + "_collect_from");
+  f.nf_right = (int) f.from.size();
+  f.to = z.ints(p + "_collect_to");
+  want_count(p + "_collect_to", f.to.size(), (size_t) f.nf_right);
+  want_below(p + "_collect_to", f.to, f.nf_left);
+  f.tile_right = z.ints(p + "_w_tile_right");
+  want_count(p + "_w_tile_right", f.tile_right.size(), (size_t) f.nf_right);
+  want_below(p + "_w_tile_right", f.tile_right, f.tiles_right);
+  if (f.weighted_left) {
+    f.tile_left = z.ints(p + "_w_tile_left");
     f.w_left = z.reals(p + "_w_left");
     const auto wl = shape_of_rank(z, p + "_w_left", 3);
-    want_equal(p + "_w_left", wl[0], f.n_out, p + "_n_out");
-    f.n_in_left = (int) wl[1];
-    f.w_shape_left = (int) wl[2];
-    f.norm_left = z.real_scalar(p + "_norm_left", 1.0);
-    want_below(p + "_w_tile_left", f.w_tile_left, f.w_shape_left);
+    want_equal(p + "_w_left", wl[0], f.width, p + "_n_out");
+    f.in_left = (int) wl[1];
+    f.tiles_left = (int) wl[2];
+    f.scale_left = z.real_scalar(p + "_norm_left", 1.0);
+    want_below(p + "_w_tile_left", f.tile_left, f.tiles_left);
   }
   return f;
 }
 
-Grace3LModel::EqNorm read_eqnorm(const Npz &z, const std::string &nm)
+Grace3LModel::MessageNorm read_eqnorm(const Npz &z, const std::string &nm)
 {
-  Grace3LModel::EqNorm e;
+  Grace3LModel::MessageNorm e;
   e.name = nm;
-  e.affine_weight = z.reals(nm + "_affine_weight");
+  e.gain = z.reals(nm + "_affine_weight");
   const auto aw = shape_of_rank(z, nm + "_affine_weight", 2);
-  e.n_groups = (int) aw[0];
-  e.n_out = (int) aw[1];
-  e.degree_weights = z.reals(nm + "_degree_weights");
-  e.M = (int) e.degree_weights.size();
-  e.l0_mask = z.reals(nm + "_l0_mask");
-  want_count(nm + "_l0_mask", e.l0_mask.size(), (size_t) e.M);
-  e.expand_index = z.ints(nm + "_expand_index");
-  want_count(nm + "_expand_index", e.expand_index.size(), (size_t) e.M);
-  want_below(nm + "_expand_index", e.expand_index, e.n_groups);
+  e.groups = (int) aw[0];
+  e.width = (int) aw[1];
+  e.degree_weight = z.reals(nm + "_degree_weights");
+  e.nfuncs = (int) e.degree_weight.size();
+  e.centre_mask = z.reals(nm + "_l0_mask");
+  want_count(nm + "_l0_mask", e.centre_mask.size(), (size_t) e.nfuncs);
+  e.group_of = z.ints(nm + "_expand_index");
+  want_count(nm + "_expand_index", e.group_of.size(), (size_t) e.nfuncs);
+  want_below(nm + "_expand_index", e.group_of, e.groups);
   e.eps = z.real_scalar(nm + "_eps", 1e-8);
   if (e.eps < 0.0) throw bad_array(nm + "_eps", "is negative");
-  e.center_l0 = flag(z, nm + "_center_l0", 1);
+  e.centred = flag(z, nm + "_center_l0", 1);
   return e;
 }
 
-Grace3LModel::RmsNorm read_rmsnorm(const Npz &z, const std::string &nm)
+Grace3LModel::DensityNorm read_rmsnorm(const Npz &z, const std::string &nm)
 {
-  Grace3LModel::RmsNorm r;
+  Grace3LModel::DensityNorm r;
   r.name = nm;
-  r.scale = z.reals(nm + "_scale");
-  r.type = flag(z, nm + "_type", 0);
-  r.n_out = z.int_in(nm + "_n_out", (int) std::min<size_t>(r.scale.size() + r.type, kMaxDim), 1, kMaxDim);
-  want_count(nm + "_scale", r.scale.size(), (size_t) (r.n_out - r.type));
+  r.gain = z.reals(nm + "_scale");
+  r.skip_first = flag(z, nm + "_type", 0);
+  r.width = z.int_in(nm + "_n_out", (int) std::min<size_t>(r.gain.size() + r.skip_first, kMaxDim), 1, kMaxDim);
+  want_count(nm + "_scale", r.gain.size(), (size_t) (r.width - r.skip_first));
   return r;
 }
 
@@ -296,22 +296,22 @@ class Graph {
  public:
   int walk(bool has_origin_n_out)
   {
-    if (m_.spbf.size() != 3) throw bad_array("spbf_names", "has " + num((int64_t) m_.spbf.size()) + " names, expected 3 (A1, A2, A3)");
+    if (m_.bases.size() != 3) throw bad_array("spbf_names", "has " + num((int64_t) m_.bases.size()) + " names, expected 3 (A1, A2, A3)");
     const int nlm = (m_.lmax + 1) * (m_.lmax + 1);
     for (int k = 1; k <= 3; k++) {
       const std::string ks = num(k), K = "A" + ks;
-      auto &s = take(m_.spbf, "spbf_names", K);
-      if (m_.spbf[k - 1].name != K) throw bad_array("spbf_names", "lists '" + K + "' out of order");
+      auto &s = take(m_.bases, "spbf_names", K);
+      if (m_.bases[k - 1].name != K) throw bad_array("spbf_names", "lists '" + K + "' out of order");
       std::string X = K;
       if (k == 1) {
-        if (s.equivariant) throw bad_array(K + "_equivariant", "is 1, expected 0 (the first layer has no message to couple)");
-        shape_[K] = {nlm, s.n_rad_max};
+        if (s.coupled) throw bad_array(K + "_equivariant", "is 1, expected 0 (the first layer has no message to couple)");
+        shape_[K] = {nlm, s.channels};
       } else {
-        if (!s.equivariant) throw bad_array(K + "_equivariant", "is 0, expected 1 (the layer couples the message of the one before)");
+        if (!s.coupled) throw bad_array(K + "_equivariant", "is 0, expected 1 (the layer couples the message of the one before)");
         const std::string msg = "eq" + num(k - 1) + "_norm";
-        want_equal(K + "_n_lm_ind", s.n_lm_ind, shape_.at(msg).nf, "the functions of the message " + msg);
-        want_equal(K + "_n_rad_max", s.n_rad_max, shape_.at(msg).nc, "the channels of the message " + msg);
-        shape_[K] = {s.nfunc, s.n_rad_max};
+        want_equal(K + "_n_lm_ind", s.n_msg, shape_.at(msg).nf, "the functions of the message " + msg);
+        want_equal(K + "_n_rad_max", s.channels, shape_.at(msg).nc, "the channels of the message " + msg);
+        shape_[K] = {s.n_coupled, s.channels};
         reduce(K + "_red", {K});
         X = K + "_red";
       }
@@ -326,30 +326,30 @@ class Graph {
       const std::vector<std::string> collected = {X, K + "_2_red", K + "_3_red", K + "_4_red"};
       if (k < 3) {
         reduce("eq" + ks, collected);
-        auto &e = take(m_.eqnorm, "eqnorm_names", "eq" + ks + "_norm");
+        auto &e = take(m_.message_norms, "eqnorm_names", "eq" + ks + "_norm");
         const Shape in = shape_.at("eq" + ks);
-        want_equal(e.name + "_degree_weights", e.M, in.nf, "the functions of eq" + ks);
-        want_equal(e.name + "_affine_weight", e.n_out, in.nc, "the channels of eq" + ks);
-        shape_[e.name] = {e.M, e.n_out};
+        want_equal(e.name + "_degree_weights", e.nfuncs, in.nf, "the functions of eq" + ks);
+        want_equal(e.name + "_affine_weight", e.width, in.nc, "the channels of eq" + ks);
+        shape_[e.name] = {e.nfuncs, e.width};
       }
       reduce("rho" + ks, collected);
-      auto &n = take(m_.rmsnorm, "rmsnorm_names", "rho" + ks + "_norm");
+      auto &n = take(m_.density_norms, "rmsnorm_names", "rho" + ks + "_norm");
       const Shape in = shape_.at("rho" + ks);
-      want_equal(n.name + "_n_out", n.n_out, in.nc, "the channels of rho" + ks);
-      shape_[n.name] = {in.nf, n.n_out};
+      want_equal(n.name + "_n_out", n.width, in.nc, "the channels of rho" + ks);
+      shape_[n.name] = {in.nf, n.width};
     }
-    leftovers(m_.spbf, "spbf_names");
-    leftovers(m_.prod, "prod_names");
-    leftovers(m_.reduce, "reduce_names");
-    leftovers(m_.fc, "fc_names");
-    leftovers(m_.eqnorm, "eqnorm_names");
-    leftovers(m_.rmsnorm, "rmsnorm_names");
+    leftovers(m_.bases, "spbf_names");
+    leftovers(m_.products, "prod_names");
+    leftovers(m_.collects, "reduce_names");
+    leftovers(m_.mixes, "fc_names");
+    leftovers(m_.message_norms, "eqnorm_names");
+    leftovers(m_.density_norms, "rmsnorm_names");
 
     const std::vector<std::string> origins = {"rho1_norm", "rho2_norm", "rho3_norm"};
-    same_names("out1_origins", m_.out1_origins, origins);
+    same_names("out1_origins", m_.readout_inputs, origins);
     const int w = shape_.at(origins[0]).nc;
     for (const auto &o : origins) want_equal(o + "_n_out", shape_.at(o).nc, w, "the channels of " + origins[0]);
-    if (has_origin_n_out) want_equal("energy_mlp_origin_n_out", m_.energy_mlp_origin_n_out, w, "the channels of out1_origins");
+    if (has_origin_n_out) want_equal("energy_mlp_origin_n_out", m_.readout_origin_width, w, "the channels of out1_origins");
     return w;
   }
 
@@ -367,40 +367,40 @@ class Graph {
 
   void reduce(const std::string &name, const std::vector<std::string> &inputs)
   {
-    auto &r = take(m_.reduce, "reduce_names", name);
+    auto &r = take(m_.collects, "reduce_names", name);
     std::vector<std::string> got;
-    for (const auto &in : r.instr) got.push_back(in.name);
+    for (const auto &in : r.sources) got.push_back(in.from);
     same_names(name + "_instruction_names", got, inputs);
-    for (const auto &in : r.instr) {
-      const Shape src = shape_.at(in.name);
-      want_equal(name + "_n_in_" + in.name, in.n_in, src.nc, "the channels of " + in.name);
-      want_below(name + "_collect_ind_" + in.name, in.collect_ind, src.nf);
+    for (const auto &in : r.sources) {
+      const Shape src = shape_.at(in.from);
+      want_equal(name + "_n_in_" + in.from, in.width, src.nc, "the channels of " + in.from);
+      want_below(name + "_collect_ind_" + in.from, in.pick, src.nf);
     }
-    shape_[name] = {r.only_invar ? 1 : r.n_funcs, r.n_out};
+    shape_[name] = {r.invariant ? 1 : r.nfuncs, r.width};
   }
 
   void product(const std::string &name, const std::string &left, const std::string &right)
   {
-    auto &c = take(m_.prod, "prod_names", name);
+    auto &c = take(m_.products, "prod_names", name);
     const Shape l = shape_.at(left), r = shape_.at(right);
-    want_equal(name + "_group_left", (int64_t) c.group_left.size(), l.nf, "the functions of " + left);
-    want_equal(name + "_n_left", c.n_left, l.nc, "the channels of " + left);
-    want_equal(name + "_group_right", (int64_t) c.group_right.size(), r.nf, "the functions of " + right);
-    want_equal(name + "_n_right", c.n_right, r.nc, "the channels of " + right);
-    shape_[name] = {c.nfunc, c.rank};
+    want_equal(name + "_group_left", (int64_t) c.group_l.size(), l.nf, "the functions of " + left);
+    want_equal(name + "_n_left", c.width_l, l.nc, "the channels of " + left);
+    want_equal(name + "_group_right", (int64_t) c.group_r.size(), r.nf, "the functions of " + right);
+    want_equal(name + "_n_right", c.width_r, r.nc, "the channels of " + right);
+    shape_[name] = {c.n_out, c.rank};
   }
 
   void dense(const std::string &name, const std::string &left, const std::string &right)
   {
-    auto &f = take(m_.fc, "fc_names", name);
+    auto &f = take(m_.mixes, "fc_names", name);
     const std::string p = "fc_" + name;
     const Shape l = shape_.at(left), r = shape_.at(right);
-    want_equal(p + "_w_tile_left", f.n_funcs_left, l.nf, "the functions of " + left);
-    if (f.left_coefs) want_equal(p + "_w_left", f.n_in_left, l.nc, "the channels of " + left);
-    else want_equal(p + "_n_out", f.n_out, l.nc, "the channels of " + left + ", which pass unweighted");
-    want_equal(p + "_w_right", f.n_in_right, r.nc, "the channels of " + right);
-    want_below(p + "_collect_from", f.collect_from, r.nf);
-    shape_[name] = {f.n_funcs_left, f.n_out};
+    want_equal(p + "_w_tile_left", f.nf_left, l.nf, "the functions of " + left);
+    if (f.weighted_left) want_equal(p + "_w_left", f.in_left, l.nc, "the channels of " + left);
+    else want_equal(p + "_n_out", f.width, l.nc, "the channels of " + left + ", which pass unweighted");
+    want_equal(p + "_w_right", f.in_right, r.nc, "the channels of " + right);
+    want_below(p + "_collect_from", f.from, r.nf);
+    shape_[name] = {f.nf_left, f.width};
   }
 
   Grace3LModel &m_;
@@ -427,59 +427,59 @@ Grace3LModel Grace3LModel::load(const Npz &z)
     if (z.has(k)) throw bad_array(k, "is a legacy GRACE-1L/2L key, not supported in GRACE-3L");
 
   m.n_elements = size_key(z, "n_elements");
-  m.embedding_size = z.int_in("embedding_size", 64, 1, kMaxDim);
-  m.nradbase = z.int_in("nradbase", 10, 1, kMaxDim);
+  m.embedding = z.int_in("embedding_size", 64, 1, kMaxDim);
+  m.nbasis = z.int_in("nradbase", 10, 1, kMaxDim);
   m.lmax = z.int_in("lmax", z.int_in("A1_lmax", 4, 0, kMaxL), 0, kMaxL);    // no bare lmax key in an export: A1_lmax
-  m.rcut = cutoff_scalar(z, "rcut", 6.0);
-  m.has_bond_specific_cutoff = flag(z, "has_bond_specific_cutoff", 0);
-  m.chem_embedding = z.reals("chem_embedding");
-  z.require_shape("chem_embedding", {m.n_elements, m.embedding_size});
-  m.shift_values = z.reals("shift_values");
-  want_count("shift_values", m.shift_values.size(), (size_t) m.n_elements);
-  m.output_scale = z.real_scalar("output_scale", 1.0);
-  m.element_names = z.names("element_names");
-  want_count("element_names", m.element_names.size(), (size_t) m.n_elements);
-  m.bond_cutoff_map = z.reals("bond_cutoff_map", false);
-  for (double c : m.bond_cutoff_map)
+  m.cutoff = cutoff_scalar(z, "rcut", 6.0);
+  m.pair_cutoffs_given = flag(z, "has_bond_specific_cutoff", 0);
+  m.embedding_table = z.reals("chem_embedding");
+  z.require_shape("chem_embedding", {m.n_elements, m.embedding});
+  m.energy_shift = z.reals("shift_values");
+  want_count("shift_values", m.energy_shift.size(), (size_t) m.n_elements);
+  m.energy_scale = z.real_scalar("output_scale", 1.0);
+  m.elements = z.names("element_names");
+  want_count("element_names", m.elements.size(), (size_t) m.n_elements);
+  m.pair_cutoff = z.reals("bond_cutoff_map", false);
+  for (double c : m.pair_cutoff)
     if (c < 0.0) throw bad_array("bond_cutoff_map", "holds a negative cutoff");
   z.require_shape("bond_cutoff_map", {m.n_elements, m.n_elements});
-  if (m.bond_cutoff_map.empty()) m.bond_cutoff_map.assign((size_t) m.n_elements * m.n_elements, m.rcut);
+  if (m.pair_cutoff.empty()) m.pair_cutoff.assign((size_t) m.n_elements * m.n_elements, m.cutoff);
 
-  for (const auto &nm : z.names("spbf_names")) m.spbf.push_back(read_spbf(z, nm, m));
-  if (!m.spbf.empty()) m.radial_basis_p = m.spbf[0].p;
-  for (const auto &s : m.spbf)    // one envelope order for all layers
-    if (s.p != m.radial_basis_p)
-      throw bad_array(s.name + "_p", "is " + num(s.p) + ", the envelope order of " + m.spbf[0].name + " is " + num(m.radial_basis_p) +
+  for (const auto &nm : z.names("spbf_names")) m.bases.push_back(read_spbf(z, nm, m));
+  if (!m.bases.empty()) m.env_p = m.bases[0].env_p;
+  for (const auto &s : m.bases)    // one envelope order for all layers
+    if (s.env_p != m.env_p)
+      throw bad_array(s.name + "_p", "is " + num(s.env_p) + ", the envelope order of " + m.bases[0].name + " is " + num(m.env_p) +
                                          "; layers with different orders are not supported");
-  for (const auto &nm : z.names("prod_names")) m.prod.push_back(read_cpl(z, nm));
-  for (const auto &nm : z.names("reduce_names")) m.reduce.push_back(read_reduce(z, nm, m.n_elements));
-  for (const auto &nm : z.names("fc_names")) m.fc.push_back(read_fc(z, nm));
-  for (const auto &nm : z.names("eqnorm_names")) m.eqnorm.push_back(read_eqnorm(z, nm));
-  for (const auto &nm : z.names("rmsnorm_names")) m.rmsnorm.push_back(read_rmsnorm(z, nm));
+  for (const auto &nm : z.names("prod_names")) m.products.push_back(read_cpl(z, nm));
+  for (const auto &nm : z.names("reduce_names")) m.collects.push_back(read_reduce(z, nm, m.n_elements));
+  for (const auto &nm : z.names("fc_names")) m.mixes.push_back(read_fc(z, nm));
+  for (const auto &nm : z.names("eqnorm_names")) m.message_norms.push_back(read_eqnorm(z, nm));
+  for (const auto &nm : z.names("rmsnorm_names")) m.density_norms.push_back(read_rmsnorm(z, nm));
 
-  m.out1_origins = z.names("out1_origins");
-  m.energy_mlp_origin_n_out = z.int_scalar("energy_mlp_origin_n_out", 0);
-  m.energy_mlp_n_origins = z.int_scalar("energy_mlp_n_origins", (int) m.out1_origins.size());
-  want_equal("energy_mlp_n_origins", m.energy_mlp_n_origins, (int64_t) m.out1_origins.size(), "the names in out1_origins");
+  m.readout_inputs = z.names("out1_origins");
+  m.readout_origin_width = z.int_scalar("energy_mlp_origin_n_out", 0);
+  m.readout_n_origins = z.int_scalar("energy_mlp_n_origins", (int) m.readout_inputs.size());
+  want_equal("energy_mlp_n_origins", m.readout_n_origins, (int64_t) m.readout_inputs.size(), "the names in out1_origins");
 
   m.readout_width = Graph(m).walk(z.has("energy_mlp_origin_n_out"));
-  read_mlp(z, "energy_mlp", m.energy_mlp, m.readout_width - 1, 1, "the channels of out1_origins but the linear channel 0",
+  read_mlp(z, "energy_mlp", m.readout, m.readout_width - 1, 1, "the channels of out1_origins but the linear channel 0",
            "one energy per atom");
-  m.energy_mlp_activation = z.int_in("energy_mlp_activation", 0, 0, 1);
+  m.readout_act = z.int_in("energy_mlp_activation", 0, 0, 1);
   return m;
 }
 
 std::string Grace3LModel::summary() const
 {
   std::string s = "GRACE-3L: " + num(n_elements) + " elements, lmax " + num(lmax) + ", channels";
-  for (const auto &b : spbf) s += " " + num(b.n_rad_max);
+  for (const auto &b : bases) s += " " + num(b.channels);
   s += ", message functions";
-  for (const auto &e : eqnorm) s += " " + num(e.M);
+  for (const auto &e : message_norms) s += " " + num(e.nfuncs);
   s += ", coupled functions";
-  for (const auto &b : spbf)
-    if (b.equivariant) s += " " + num(b.nfunc);
+  for (const auto &b : bases)
+    if (b.coupled) s += " " + num(b.n_coupled);
   s += ", cp_l terms";
-  for (const auto &c : prod) s += " " + num(c.n_cg);
+  for (const auto &c : products) s += " " + num(c.nterms);
   s += ", readout width " + num(readout_width);
   return s;
 }

@@ -646,10 +646,10 @@ namespace {
 void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Plan &L)
 {
   const std::string K = "A" + std::to_string(k + 1), ks = std::to_string(k + 1);
-  const Grace3LModel::Spbf &sp = m.spbf[k];
-  const int nl = m.lmax + 1, nlm = nl * nl, C = sp.n_rad_max;
+  const Grace3LModel::BondBasis &sp = m.bases[k];
+  const int nl = m.lmax + 1, nlm = nl * nl, C = sp.channels;
   L.C = C;
-  L.lt = sp.l_tile;
+  L.lt = sp.l_of_lm;
   auto find = [](const auto &v, const std::string &name) -> const auto & {
     for (const auto &c : v)
       if (c.name == name) return c;
@@ -665,39 +665,39 @@ void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Pl
   // keep the reduce weights alive until the plan is finished (the builder reads them through pointers)
   std::vector<std::unique_ptr<ReduceWeights>> keep;
   auto reduce = [&](const std::string &name, const std::string &out_name, bool external) {
-    const Grace3LModel::Reduce &r = find(m.reduce, name);
-    const int nfo = r.only_invar ? 1 : r.n_funcs;
+    const Grace3LModel::Collect &r = find(m.collects, name);
+    const int nfo = r.invariant ? 1 : r.nfuncs;
     double scale = 1.0;
-    if (r.has_norm_map) {
-      scale = r.norm_map[0];
-      for (double v : r.norm_map)
+    if (r.row_scaled) {
+      scale = r.row_scale[0];
+      for (double v : r.row_scale)
         if (v != scale) throw ModelError("GRACE-3L: reduce " + name + " scales its output functions differently (norm_map)");
     }
-    const auto out = tensors(out_name, nfo, r.n_out);
+    const auto out = tensors(out_name, nfo, r.width);
     if (external) L.dense.tensors[out.first].external = L.dense.tensors[out.second].external = true;
     ReduceGroup G;
     G.name = name;
-    G.n_out = r.n_out;
+    G.n_out = r.width;
     G.nfo = nfo;
-    G.elem = r.elem_dep;
+    G.elem = r.per_element;
     G.t_out = out.first;
     G.t_gout = out.second;
-    for (const auto &in : r.instr) {
+    for (const auto &in : r.sources) {
       auto w = std::make_unique<ReduceWeights>();
       w->present = true;
-      w->W = in.W;
-      w->norm = in.norm * scale;
-      w->n_in = in.n_in;
-      w->w_shape = in.w_shape;
-      w->n_out = r.n_out;
-      w->elem = r.elem_dep;
-      w->collect = in.collect_ind;
-      w->tile = in.w_l_tile;
-      w->fo = in.total_sum_ind;
-      if (r.only_invar) w->fo.assign(in.collect_ind.size(), 0);
+      w->W = in.weight;
+      w->norm = in.scale * scale;
+      w->n_in = in.width;
+      w->w_shape = in.tiles;
+      w->n_out = r.width;
+      w->elem = r.per_element;
+      w->collect = in.pick;
+      w->tile = in.tile_of;
+      w->fo = in.into;
+      if (r.invariant) w->fo.assign(in.pick.size(), 0);
       G.src.push_back(w.get());
-      G.src_tensor.push_back(T.at(in.name).first);
-      G.src_grad.push_back(T.at(in.name).second);
+      G.src_tensor.push_back(T.at(in.from).first);
+      G.src_grad.push_back(T.at(in.from).second);
       G.src_row0.push_back(0);
       keep.push_back(std::move(w));
     }
@@ -738,60 +738,60 @@ void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Pl
     B.reduce(G);
   };
   auto product = [&](const std::string &name, const std::string &left, const std::string &right) {
-    const Grace3LModel::Cpl &c = find(m.prod, name);
-    project(name + "_lp", left, c.U, c.norm_u, c.group_left, c.n_groups_left, c.rank, c.n_left);
-    project(name + "_rp", right, c.V, c.norm_v, c.group_right, c.n_groups_right, c.rank, c.n_right);
-    const auto out = tensors(name, c.nfunc, c.rank);
+    const Grace3LModel::LowRank &c = find(m.products, name);
+    project(name + "_lp", left, c.U, c.scale_u, c.group_l, c.groups_l, c.rank, c.width_l);
+    project(name + "_rp", right, c.V, c.scale_v, c.group_r, c.groups_r, c.rank, c.width_r);
+    const auto out = tensors(name, c.n_out, c.rank);
     CGProduct p;
     p.present = true;
-    p.left = c.left_ind;
-    p.right = c.right_ind;
-    p.m_sum = c.m_sum_ind;
-    p.cg = c.cg;
-    p.n_out = c.nfunc;
-    const std::vector<char> need(c.nfunc, 1);
+    p.left = c.term_l;
+    p.right = c.term_r;
+    p.m_sum = c.term_out;
+    p.cg = c.coef;
+    p.n_out = c.n_out;
+    const std::vector<char> need(c.n_out, 1);
     B.prod(name, p, need, T.at(name + "_lp").first, T.at(name + "_rp").first, out.first, T.at(name + "_lp").second,
            T.at(name + "_rp").second, out.second);
   };
   // out = nof (left + W right): the left input passes through an identity
   auto dense = [&](const std::string &name, const std::string &left, const std::string &right) {
-    const Grace3LModel::Fc &f = find(m.fc, name);
-    if (f.left_coefs) throw ModelError("GRACE-3L: FC " + name + " with weights on its left input");
+    const Grace3LModel::Mix &f = find(m.mixes, name);
+    if (f.weighted_left) throw ModelError("GRACE-3L: FC " + name + " with weights on its left input");
     FCWeights w;
     w.present = true;
-    w.n_out = f.n_out;
-    w.n_in_left = f.n_out;
-    w.n_in_right = f.n_in_right;
+    w.n_out = f.width;
+    w.n_in_left = f.width;
+    w.n_in_right = f.in_right;
     w.tiles_left = 1;
-    w.tiles_right = f.w_shape_right;
-    w.n_funcs = f.n_funcs_left;
-    w.w_left.assign((size_t) f.n_out * f.n_out, 0.0);
-    for (int q = 0; q < f.n_out; q++) w.w_left[(size_t) q * f.n_out + q] = 1.0;
+    w.tiles_right = f.tiles_right;
+    w.n_funcs = f.nf_left;
+    w.w_left.assign((size_t) f.width * f.width, 0.0);
+    for (int q = 0; q < f.width; q++) w.w_left[(size_t) q * f.width + q] = 1.0;
     w.w_right = f.w_right;
-    w.norm_right = f.norm_right;
-    w.tile_left.assign(f.n_funcs_left, 0);
-    w.tile_right = f.w_tile_right;
-    w.collect_to = f.collect_to;
-    w.collect_from = f.collect_from;
-    w.nof = f.norm_out_factor;
-    const auto out = tensors(name, f.n_funcs_left, f.n_out);
-    const std::vector<char> live(f.n_funcs_left, 1);
+    w.norm_right = f.scale_right;
+    w.tile_left.assign(f.nf_left, 0);
+    w.tile_right = f.tile_right;
+    w.collect_to = f.to;
+    w.collect_from = f.from;
+    w.nof = f.out_factor;
+    const auto out = tensors(name, f.nf_left, f.width);
+    const std::vector<char> live(f.nf_left, 1);
     B.fc(name, w, live, T.at(left).first, T.at(right).first, out.first, T.at(left).second, T.at(right).second, out.second);
   };
 
   std::string X = K;
-  if (!sp.equivariant) {
+  if (!sp.coupled) {
     L.nfA = nlm;
     L.nlmi = 1;
   } else {
-    L.nfA = sp.nfunc;
-    L.nlmi = sp.n_lm_ind;
+    L.nfA = sp.n_coupled;
+    L.nlmi = sp.n_msg;
   }
   const auto A = tensors(K, L.nfA, C);
   L.tA = A.first;
   L.tGA = A.second;
   L.dense.tensors[L.tA].external = L.dense.tensors[L.tGA].external = true;
-  if (sp.equivariant) {
+  if (sp.coupled) {
     reduce(K + "_red", K + "_red", false);
     X = K + "_red";
   }
@@ -807,23 +807,23 @@ void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Pl
     const auto eq = reduce("eq" + ks, "eq" + ks, true);
     L.tEQ = eq.first;
     L.tGEQ = eq.second;
-    const Grace3LModel::EqNorm &e = find(m.eqnorm, "eq" + ks + "_norm");
-    L.nfEQ = e.M;
-    L.cEQ = e.n_out;
-    L.eq_dw.assign(e.degree_weights.begin(), e.degree_weights.end());
-    L.eq_mask.assign(e.l0_mask.begin(), e.l0_mask.end());
-    L.eq_aff.assign(e.affine_weight.begin(), e.affine_weight.end());
-    L.eq_e = e.expand_index;
+    const Grace3LModel::MessageNorm &e = find(m.message_norms, "eq" + ks + "_norm");
+    L.nfEQ = e.nfuncs;
+    L.cEQ = e.width;
+    L.eq_dw.assign(e.degree_weight.begin(), e.degree_weight.end());
+    L.eq_mask.assign(e.centre_mask.begin(), e.centre_mask.end());
+    L.eq_aff.assign(e.gain.begin(), e.gain.end());
+    L.eq_e = e.group_of;
     L.eq_eps = e.eps;
-    L.eq_center = e.center_l0;
+    L.eq_center = e.centred;
   }
   const auto rho = reduce("rho" + ks, "rho" + ks, true);
   L.tRHO = rho.first;
   L.tGRHO = rho.second;
-  const Grace3LModel::RmsNorm &rn = find(m.rmsnorm, "rho" + ks + "_norm");
-  L.wr = rn.n_out;
-  L.rho_n0 = rn.type;
-  L.rho_scale.assign(rn.scale.begin(), rn.scale.end());
+  const Grace3LModel::DensityNorm &rn = find(m.density_norms, "rho" + ks + "_norm");
+  L.wr = rn.width;
+  L.rho_n0 = rn.skip_first;
+  L.rho_scale.assign(rn.gain.begin(), rn.gain.end());
   if (L.dense.tensors[L.tRHO].nfuncs != 1) throw ModelError("GRACE-3L: rho" + ks + " must be an invariant reduce");
   B.finish();
   compact_rows(L.dense);
@@ -835,7 +835,7 @@ void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Pl
   const int np = nlm * L.nlmi;
   L.cg_off.assign(L.nfA + 1, 0);
   L.cgt_off.assign(np + 1, 0);
-  if (!sp.equivariant) {
+  if (!sp.coupled) {
     for (int f = 0; f < nlm; f++) {
       L.cg_off[f + 1] = L.cgt_off[f + 1] = f + 1;
       L.cg_p.push_back(f);
@@ -849,7 +849,7 @@ void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Pl
     std::vector<std::vector<std::pair<int, float>>> by_f(L.nfA), by_q(np);
     for (int q = 0; q < np; q++)
       for (int f = 0; f < L.nfA; f++) {
-        const double v = sp.cg_W[(size_t) q * L.nfA + f];
+        const double v = sp.couple[(size_t) q * L.nfA + f];
         if (v != 0.0) {
           by_f[f].push_back({q, (float) v});
           by_q[q].push_back({f, (float) v});
@@ -869,14 +869,14 @@ void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Pl
       }
       L.cgt_off[q + 1] = (int) L.cgt_f.size();
     }
-    L.l0mask.assign(sp.chem_l0_mask.begin(), sp.chem_l0_mask.end());
+    L.l0mask.assign(sp.msg_mask.begin(), sp.msg_mask.end());
     L.zproj.assign((size_t) m.n_elements * C, 0.0f);
     for (int e = 0; e < m.n_elements; e++)
       for (int c = 0; c < C; c++) {
         double v = 0.0;
-        for (int q = 0; q < m.embedding_size; q++)
-          v += m.chem_embedding[(size_t) e * m.embedding_size + q] * sp.chem_linear_W[(size_t) q * C + c];
-        L.zproj[(size_t) e * C + c] = (float) (v * sp.chem_linear_norm);
+        for (int q = 0; q < m.embedding; q++)
+          v += m.embedding_table[(size_t) e * m.embedding + q] * sp.zc_weight[(size_t) q * C + c];
+        L.zproj[(size_t) e * C + c] = (float) (v * sp.zc_scale);
       }
   }
 }
@@ -885,17 +885,17 @@ void build_layer_3l(const GraceModel &gm, const Grace3LModel &m, int k, Layer3Pl
 
 std::vector<float> radial_table_3l(const Grace3LModel &m, int k, int mu_i, int mu_j, int N)
 {
-  const Grace3LModel::Spbf &sp = m.spbf[k];
-  const Grace3LModel::Mlp &mlp = sp.mlp;
-  const int nl = m.lmax + 1, C = sp.n_rad_max, ne = m.embedding_size, nrb = m.nradbase, p = sp.p;
-  const double *zi = m.chem_embedding.data() + (size_t) mu_i * ne, *zj = m.chem_embedding.data() + (size_t) mu_j * ne;
+  const Grace3LModel::BondBasis &sp = m.bases[k];
+  const Grace3LModel::DenseStack &mlp = sp.radial;
+  const int nl = m.lmax + 1, C = sp.channels, ne = m.embedding, nrb = m.nbasis, p = sp.env_p;
+  const double *zi = m.embedding_table.data() + (size_t) mu_i * ne, *zj = m.embedding_table.data() + (size_t) mu_j * ne;
   // layer 1: the species weight of the neighbour is part of the table
-  std::vector<double> fac(C, sp.inv_avg_n_neigh);
-  if (!sp.equivariant)
+  std::vector<double> fac(C, sp.inv_neigh);
+  if (!sp.coupled)
     for (int c = 0; c < C; c++) {
       double v = 0.0;
-      for (int e = 0; e < ne; e++) v += zj[e] * sp.lin_transform_W[(size_t) e * C + c];
-      fac[c] *= v * sp.lin_transform_norm;
+      for (int e = 0; e < ne; e++) v += zj[e] * sp.z_weight[(size_t) e * C + c];
+      fac[c] *= v * sp.z_scale;
     }
   std::vector<double> fv((size_t) (N + 1) * nl * C), dv(fv.size());
   const double h = 1.0 / N;
@@ -913,21 +913,21 @@ std::vector<float> radial_table_3l(const Grace3LModel &m, int k, int mu_i, int m
       a[nrb + e] = zi[e];
       a[nrb + ne + e] = zj[e];
     }
-    for (int il = 0; il < mlp.n_layers; il++) {
-      const int ni = mlp.n_in[il], no = mlp.n_out[il];
+    for (int il = 0; il < mlp.depth; il++) {
+      const int ni = mlp.fan_in[il], no = mlp.fan_out[il];
       std::vector<double> s(no, 0.0), ds(no, 0.0);
       for (int i = 0; i < ni; i++) {
-        const double *w = mlp.W[il].data() + (size_t) i * no;
+        const double *w = mlp.weight[il].data() + (size_t) i * no;
         for (int j = 0; j < no; j++) {
           s[j] += w[j] * a[i];
           ds[j] += w[j] * da[i];
         }
       }
       for (int j = 0; j < no; j++) {
-        s[j] *= mlp.norm[il];
-        ds[j] *= mlp.norm[il];
-        if (il < mlp.n_layers - 1) {
-          if (!mlp.b[il].empty()) s[j] += mlp.norm[il] * mlp.b[il][j];
+        s[j] *= mlp.scale[il];
+        ds[j] *= mlp.scale[il];
+        if (il < mlp.depth - 1) {
+          if (!mlp.bias[il].empty()) s[j] += mlp.scale[il] * mlp.bias[il][j];
           const double sg = 1.0 / (1.0 + std::exp(-s[j]));
           ds[j] *= sg * (1.0 + s[j] * (1.0 - sg));
           s[j] *= sg;
@@ -978,8 +978,8 @@ static ModelPlan build_plan_3l(const GraceModel &gm, int spline_n)
       P.rcsq[(size_t) a * m.n_elements + b] = rc * rc;
       P.rc_max = std::max(P.rc_max, rc);
     }
-  P.out_scale = m.output_scale;
-  P.shift = m.shift_values;
+  P.out_scale = m.energy_scale;
+  P.shift = m.energy_shift;
   P.p3 = std::make_shared<Plan3L>();
   Plan3L &Q = *P.p3;
   Q.model = gm.m3;
@@ -989,16 +989,16 @@ static ModelPlan build_plan_3l(const GraceModel &gm, int spline_n)
     if (Q.L[k].nfEQ != Q.L[k + 1].nlmi || Q.L[k].cEQ != Q.L[k + 1].C)
       throw ModelError("GRACE-3L: the message of layer " + std::to_string(k + 1) + " does not fit the next layer");
   if (Q.L[0].wr != Q.L[1].wr || Q.L[0].wr != Q.L[2].wr) throw ModelError("GRACE-3L: densities of different widths");
-  const Grace3LModel::Mlp &e = m.energy_mlp;
-  if (e.n_layers != 2 || e.n_out[1] != 1 || e.n_in[0] != Q.L[0].wr - 1 || e.n_out[0] > 256 || e.n_in[0] > 128)
+  const Grace3LModel::DenseStack &e = m.readout;
+  if (e.depth != 2 || e.fan_out[1] != 1 || e.fan_in[0] != Q.L[0].wr - 1 || e.fan_out[0] > 256 || e.fan_in[0] > 128)
     throw ModelError("GRACE-3L: the energy MLP must have two layers of at most 128 inputs and 256 hidden units");
-  Q.eW0 = e.W[0];
-  Q.eW1 = e.W[1];
-  Q.en0 = e.norm[0];
-  Q.en1 = e.norm[1];
-  Q.e_nin = e.n_in[0];
-  Q.e_nh = e.n_out[0];
-  Q.e_act = m.energy_mlp_activation;
+  Q.eW0 = e.weight[0];
+  Q.eW1 = e.weight[1];
+  Q.en0 = e.scale[0];
+  Q.en1 = e.scale[1];
+  Q.e_nin = e.fan_in[0];
+  Q.e_nh = e.fan_out[0];
+  Q.e_act = m.readout_act;
   return P;
 }
 
