@@ -701,7 +701,8 @@ void Engine::setup_3l()
   State3L &S = *s3_;
   for (int k = 0; k < 3; k++) {
     const Layer3Plan &L = Q.L[k];
-    if (L.C > 64 || L.C % 4) throw Unsupported("GRACE-3L: channel counts must be multiples of 4 up to 64");
+    // (the reference's CPU engine asks for multiples of 16 as well: libgrace/src/fused_3l.cpp:433)
+    if (L.C > 64 || L.C % 16) throw Unsupported("GRACE-3L: channel counts must be multiples of 16 up to 64");
     setup_layer(S.E[k], L.dense);
     S.zproj[k].upload(L.zproj);
     S.l0mask[k].upload(L.l0mask);
